@@ -1,0 +1,364 @@
+"""Typed configuration for the memarch model family, the Instinct optimizer and a training run.
+
+The reference configures itself through ~150 environment variables read at import or constructor time
+(full2.py:1270-1429, fastloop.py:52-60, exp_opt.py:182-334).  Here every knob is a dataclass field; `from_env`
+maps the reference's variable names onto the fields so a user's existing launch recipes keep working, and
+`preset(name)` reproduces the model-name grammar of `lm.build` / `build_full2` (lm.py:752-807, full2.py:2000-2058).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+
+@dataclass
+class MemoryConfig:
+    """Fresh/dim card memory (mem2.py:51-73 constructor arguments)."""
+    fresh: int = 64
+    dim: int = 192
+    dim_max: int = 256
+    faces: int = 2
+    d_face: int = 64
+    d_dim: Optional[int] = None
+    write: int = 32
+    focus: int = 8
+    match: float = 0.8
+    w_use: float = 2.0
+    w_age: float = 1e-3
+    volume: bool = False          # mem3.VolumeMemory
+    lean: bool = True             # MEM_LEAN: content projection only for the selected words
+
+
+@dataclass
+class ModelConfig:
+    vocab: int = 50304
+    d: int = 1024
+    heads: int = 16
+    light_a: int = 2
+    light_b: int = 2
+    heavy: int = 14
+    final: int = 2
+    frac: float = 0.2             # target anchor share (ANCHOR_FRAC)
+    cap: float = 0.25             # per-text anchor ceiling (ANCHOR_CAP)
+    window: int = 2048
+    seg: int = 512
+    ckpt: str = ""                # "", "1", "heavy", "light" activation recompute
+    use_memory: bool = True       # False: memory reads zeroed (honest-task control, *_nomem)
+    no_mem: bool = False          # NO_MEM: memory and reread skipped entirely
+    no_reread: bool = False
+    memory: MemoryConfig = field(default_factory=MemoryConfig)
+    # heavy layers
+    moe: str = ""                 # "", "fixed", "budget"
+    wave: str = ""                # "", "err", "still"
+    n_exp: int = 8
+    n_frozen: int = 0             # static frozen tail (Fv2moeE<E>f<pct>)
+    bank: bool = False            # BankMoE: waves + real frozen bank
+    moe_k: int = 2                # MOE_K
+    moe_act: str = "swiglu"       # "swiglu" | "relu2" (MOE_ACT)
+    bf16_experts: bool = False    # BF16_EXPERTS
+    bank_q: str = ""              # "", "int8", "int4" storage of the frozen bank
+    wave_warm: int = 500          # WAVE_WARM
+    wave_every: int = 50
+    hint_w: float = 1.0
+    students: int = 5
+    err_thr: float = 0.3
+    moe_cap_align: int = 0        # MOE_CAP_ALIGN
+    moe_dispatch: str = "slot"    # "slot" (scatter table) | "gather" | "inv" | "onehot" | "gmm"
+    moe_group: int = 512
+    heavy_attn: bool = False
+    heavy_attn_detach: bool = False
+    n_draft: int = 0
+    draft_loss: float = 0.0
+    # light block variants (BLK set)
+    blk: Tuple[str, ...] = ()     # subset of {zero, ve, x0, relu2, relu2c, qk, qkv3, smear}
+    light_ffn: float = 0.0        # LIGHT_FFN width in units of d
+    light_moe: str = ""           # "E:k"
+    attn_impl: str = ""           # "", "block", "block2" window attention implementation
+    rope_half: bool = False
+    resid_bf16: bool = False
+    # phrasebook / locks / heads
+    phrase_init: str = ""         # path of the PPMI-SVD artefact
+    phrase_c: float = 0.05
+    surp_phrase: bool = False
+    phrase3: str = ""             # bigram -> next phrase table artefact
+    phr_hash: bool = False
+    phr_v: int = 50257
+    phrase4: str = ""
+    skip: str = ""
+    skip_g: float = 0.25
+    tongue: str = ""
+    tongue_a: float = 0.5
+    induct: str = ""              # "", "1", "lock"
+    lock_trust: str = ""
+    induct_in: bool = False
+    induct_mix: bool = False
+    induct_pos: bool = False
+    token_counts: str = ""
+    opaque: float = 0.0
+    opaque_thr: float = 5.0
+    fused_ce: bool = True         # FUSED=ours: fused projection + CE (+mixture) with grads made in forward
+    ce_chunk: int = 0             # vocab-chunked CE
+    ce_save: bool = False
+    short_v: int = 0
+    rare_cap: float = 0.3
+    panic: float = 0.0
+    head_dim: int = 64
+
+    def replace(self, **kw) -> "ModelConfig":
+        return dataclasses.replace(self, **kw)
+
+
+@dataclass
+class OptConfig:
+    """InstinctOptB constructor (exp_opt.py:437-439) plus the env switches around it."""
+    kind: str = "instinct"        # instinct | adamw | surprise | muon
+    lr: float = 1e-3
+    weight_decay: float = 0.1
+    cards: int = 4
+    beta: float = 0.9
+    new_card: float = 0.5
+    ema: float = 0.98
+    good: float = 0.05
+    bad: float = 0.2
+    top: float = 0.1
+    relax: float = 0.01
+    scale: float = 0.2
+    lr_peak: Optional[float] = None
+    norm: str = "tensor"          # tensor | row | hs | hs<n>
+    m_bf16: bool = False
+    rel_every: int = 1
+    hs_lag: bool = False          # OPT_HS_LAG: one-pass homeostasis with last step's second-axis norm
+    sr: bool = False              # stochastic rounding of bf16 stores (BF16_ALL / OPT_SR)
+    no_master: bool = False       # BF16_ALL: no fp32 master copies
+    vocab_lr_mul: float = 1.0
+    sparse_rows: bool = False
+    in_backward: bool = True      # stage B: update each weight from its grad-ready hook
+    bf16_weights: bool = True     # BF16_W: linear weights live in bf16, exact fp32 copy in the optimizer
+
+
+@dataclass
+class ParallelConfig:
+    world: int = 1
+    rank: int = 0
+    local_rank: int = 0
+    dp: bool = True               # replicate non-expert weights, reduce grads
+    ep: bool = True               # shard experts over ranks, all-to-all tokens
+    fused: bool = True            # in-kernel peer loads/stores; False = NCCL-only baseline mode
+    nvls: bool = True             # multimem paths where available
+    wait_ms: float = 2000.0       # bound of every device-side peer wait
+
+
+@dataclass
+class TrainConfig:
+    name: str = "Fv2moeK8h8d2048"
+    stage: str = "ABX"
+    steps: int = 2000
+    batch: int = 32
+    micro: int = 32
+    seq: int = 1024
+    lr: float = 3e-4
+    read_cost: float = 0.01
+    eval_every: int = 100
+    warmup: int = 200             # WARMUP
+    lr_sched: str = "cosine"      # cosine | wsd
+    wsd_frac: float = 0.2
+    lr_floor: float = 0.1
+    seed: int = 0
+    ckpt_dir: str = ""
+    ckpt_every: int = 0
+    rb_ratio: float = 0.0         # loss-spike rollback guard (0 = off)
+    rb_warm: int = 50
+    rb_lr: float = 0.5
+    nan_guard: bool = True
+    watchdog_s: float = 0.0
+
+
+_TRUE = ("1", "true", "yes", "on")
+
+
+def _flag(env, name, default=False):
+    v = env.get(name)
+    if v is None:
+        return default
+    return v.strip().lower() in _TRUE or (v != "" and v.strip().lower() not in ("0", "false", "no", "off"))
+
+
+def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
+    """Apply the reference's environment switches (SURVEY appendix of flags; full2.py, full.py, lm.py) to `cfg`."""
+    env = os.environ if env is None else env
+    kw = {}
+    g = env.get
+    if g("ANCHOR_CAP"): kw["cap"] = float(g("ANCHOR_CAP"))
+    if g("ANCHOR_FRAC"): kw["frac"] = float(g("ANCHOR_FRAC"))
+    if g("CKPT"): kw["ckpt"] = g("CKPT")
+    if g("NO_MEM"): kw["no_mem"] = True
+    if g("NO_REREAD"): kw["no_reread"] = True
+    if g("MOE_K"): kw["moe_k"] = int(g("MOE_K"))
+    if g("MOE_ACT") == "relu2": kw["moe_act"] = "relu2"
+    if g("BF16_EXPERTS") == "1": kw["bf16_experts"] = True
+    if g("BANK_Q"): kw["bank_q"] = g("BANK_Q")
+    if g("WAVE_WARM"): kw["wave_warm"] = int(g("WAVE_WARM"))
+    if g("MOE_CAP_ALIGN"): kw["moe_cap_align"] = int(g("MOE_CAP_ALIGN"))
+    if g("MOE_GMM") == "1": kw["moe_dispatch"] = "gmm"
+    elif g("MOE_DISP") == "onehot": kw["moe_dispatch"] = "onehot"
+    elif g("MOE_GATHER") and g("MOE_DISP") == "inv": kw["moe_dispatch"] = "inv"
+    elif g("MOE_GATHER"): kw["moe_dispatch"] = "gather"
+    if g("MOE_GROUP"): kw["moe_group"] = int(g("MOE_GROUP"))
+    if g("HEAVY_ATTN"): kw["heavy_attn"] = True
+    if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
+    if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
+    if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("BLK"): kw["blk"] = tuple(s for s in g("BLK").split(",") if s)
+    if g("LIGHT_FFN"): kw["light_ffn"] = float(g("LIGHT_FFN"))
+    if g("LIGHT_MOE"): kw["light_moe"] = g("LIGHT_MOE")
+    if g("ATTN_IMPL"): kw["attn_impl"] = g("ATTN_IMPL")
+    if g("ROPE_HALF") == "1": kw["rope_half"] = True
+    if g("RESID_BF16") == "1": kw["resid_bf16"] = True
+    if g("PHRASE_INIT"): kw["phrase_init"] = g("PHRASE_INIT")
+    if g("PHRASE_C"): kw["phrase_c"] = float(g("PHRASE_C"))
+    if g("SURP_PHRASE"): kw["surp_phrase"] = True
+    if g("PHRASE3"): kw["phrase3"] = g("PHRASE3")
+    if g("PHR_HASH"): kw["phr_hash"] = True
+    if g("PHR_V"): kw["phr_v"] = int(g("PHR_V"))
+    if g("PHRASE4"): kw["phrase4"] = g("PHRASE4")
+    if g("SKIP"): kw["skip"] = g("SKIP")
+    if g("SKIP_G"): kw["skip_g"] = float(g("SKIP_G"))
+    if g("TONGUE"): kw["tongue"] = g("TONGUE")
+    if g("TONGUE_A"): kw["tongue_a"] = float(g("TONGUE_A"))
+    if g("INDUCT"): kw["induct"] = g("INDUCT")
+    if g("LOCK_TRUST"): kw["lock_trust"] = g("LOCK_TRUST")
+    if g("INDUCT_IN"): kw["induct_in"] = True
+    if g("INDUCT_MIX"): kw["induct_mix"] = True
+    if g("INDUCT_POS") == "1": kw["induct_pos"] = True
+    if g("TOKEN_COUNTS"): kw["token_counts"] = g("TOKEN_COUNTS")
+    if g("OPAQUE"): kw["opaque"] = float(g("OPAQUE"))
+    if g("OPAQUE_THR"): kw["opaque_thr"] = float(g("OPAQUE_THR"))
+    if "FUSED" in env: kw["fused_ce"] = g("FUSED") in ("ours", "liger")
+    if g("CE_CHUNK"): kw["ce_chunk"] = int(g("CE_CHUNK"))
+    if g("CE_SAVE") == "1": kw["ce_save"] = True
+    if g("SHORT_V"): kw["short_v"] = int(g("SHORT_V"))
+    if g("RARE_CAP"): kw["rare_cap"] = float(g("RARE_CAP"))
+    if g("MEM_LEAN") == "0": kw["memory"] = dataclasses.replace(cfg.memory, lean=False)
+    return cfg.replace(**kw)
+
+
+def opt_from_env(cfg: OptConfig, env=None) -> OptConfig:
+    """OPT_KW JSON and the OPT_* / BF16_* switches (fastloop.py:319, exp_opt.py:186, 326)."""
+    env = os.environ if env is None else env
+    kw = {}
+    if env.get("OPT_KW"):
+        for k, v in json.loads(env["OPT_KW"]).items():
+            if k in OptConfig.__dataclass_fields__:
+                kw[k] = v
+    if env.get("OPT_HS_LAG") == "1": kw["hs_lag"] = True
+    if (env.get("BF16_ALL") == "1" or env.get("OPT_SR") == "1") and env.get("OPT_SR_OFF") != "1": kw["sr"] = True
+    if env.get("BF16_ALL") == "1": kw["no_master"] = True
+    if env.get("VOCAB_LR_MUL"): kw["vocab_lr_mul"] = float(env["VOCAB_LR_MUL"])
+    if env.get("SPARSE_ROWS"): kw["sparse_rows"] = True
+    if env.get("OPT_ALL") == "1": kw["in_backward"] = False
+    if "BF16_W" in env: kw["bf16_weights"] = env.get("BF16_W") == "1"
+    return dataclasses.replace(cfg, **kw)
+
+
+def train_from_env(cfg: TrainConfig, env=None) -> TrainConfig:
+    env = os.environ if env is None else env
+    kw = {}
+    if env.get("WARMUP"): kw["warmup"] = int(env["WARMUP"])
+    if env.get("LR_SCHED"): kw["lr_sched"] = env["LR_SCHED"]
+    if env.get("WSD_FRAC"): kw["wsd_frac"] = float(env["WSD_FRAC"])
+    if env.get("LR_FLOOR"): kw["lr_floor"] = float(env["LR_FLOOR"])
+    if env.get("CKPT_DIR"): kw["ckpt_dir"] = env["CKPT_DIR"]
+    if env.get("CKPT_EVERY"): kw["ckpt_every"] = int(env["CKPT_EVERY"])
+    return dataclasses.replace(cfg, **kw)
+
+
+_SMALL_MEM = dict(fresh=64, dim=128, dim_max=160, write=16, focus=4)
+
+
+def preset(name: str, vocab: int = 50304, env=None) -> ModelConfig:
+    """Model-name grammar of the FullLM2 family (full2.py:2000-2058).
+
+    `Fv2moeK<E>[h<H>][d<D>]` = bank MoE with E experts, H heavy layers (default 14), width D (default 768);
+    heads = D // HEAD_DIM (64), LIGHT env = light layers before and after memory (default 2), SEG = segment.
+    """
+    env = os.environ if env is None else env
+    M = lambda **kw: MemoryConfig(**kw)
+    if name == "Fv2":
+        c = ModelConfig(vocab=vocab)
+    elif name == "Fv2_nomem":
+        c = ModelConfig(vocab=vocab, ckpt="1", use_memory=False)
+    elif name in ("Fv2ck", "Fv2ckg"):
+        c = ModelConfig(vocab=vocab, ckpt="1")
+    elif name in ("Fv2moe", "Fv2moeB"):
+        c = ModelConfig(vocab=vocab, moe="budget" if name == "Fv2moeB" else "fixed")
+    elif name in ("Fv2moeW", "Fv2moeWs", "Fv2moeW5", "Fv2moeWsN"):
+        c = ModelConfig(vocab=vocab, moe="fixed", wave="still" if name in ("Fv2moeWs", "Fv2moeWsN") else "err",
+                        hint_w=0.0 if name == "Fv2moeWsN" else 1.0, err_thr=0.6 if name == "Fv2moeW5" else 0.3)
+    elif name in ("Fv3s", "Fv3s_big16"):
+        big = name == "Fv3s_big16"
+        c = ModelConfig(vocab=vocab, d=256, light_a=1, light_b=1, heavy=2, final=1, heads=4, window=64, seg=32,
+                        memory=M(fresh=64 if big else 16, dim=128 if big else 32, dim_max=160 if big else 48,
+                                 write=16 if big else 8, focus=4, volume=True))
+    elif name.startswith("Fv2moeKs"):
+        c = ModelConfig(vocab=vocab, d=256, light_a=1, light_b=1, heavy=3, final=1, heads=4, window=128, seg=64,
+                        moe="fixed", n_exp=int(name[8:]), bank=True, memory=M(**_SMALL_MEM))
+    elif name.startswith("Fv2moeK"):
+        rest, _, dd = name[7:].partition("d")
+        e, _, h = rest.partition("h")
+        d = int(dd) if dd else 768
+        L = int(env.get("LIGHT", 2))
+        hd = int(env.get("HEAD_DIM", 64))
+        c = ModelConfig(vocab=vocab, d=d, heads=d // hd, head_dim=hd, moe="fixed", n_exp=int(e), bank=True,
+                        heavy=int(h) if h else 14, light_a=L, light_b=L, seg=int(env.get("SEG", 512)))
+    elif name.startswith("Fv2moeE"):
+        e, _, fr = name[7:].partition("f")
+        E = int(e)
+        c = ModelConfig(vocab=vocab, d=768, heads=12, moe="fixed", n_exp=E,
+                        n_frozen=int(E * int(fr) / 100) if fr else 0)
+    elif name in ("Fns", "Fns_nomem"):
+        c = ModelConfig(vocab=vocab, d=384, light_a=1, light_b=1, heavy=3, final=1, heads=6, window=128, seg=64,
+                        ckpt="1", memory=M(**_SMALL_MEM), use_memory=name == "Fns")
+    elif name in ("Fn", "Fn_nomem"):
+        c = ModelConfig(vocab=vocab, d=512, light_a=2, light_b=2, heavy=4, final=1, heads=8, window=256, seg=128,
+                        ckpt="1", memory=M(**_SMALL_MEM), use_memory=name == "Fn")
+    elif name == "Fv2s_big16s64":
+        c = ModelConfig(vocab=vocab, d=256, light_a=1, light_b=1, heavy=2, final=1, heads=4, window=64, seg=64,
+                        memory=M(fresh=64, dim=128, dim_max=160, write=32, focus=4))
+    elif name in ("Fv2s_big", "Fv2s_big16"):
+        c = ModelConfig(vocab=vocab, d=256, light_a=1, light_b=1, heavy=2, final=1, heads=4, window=64, seg=32,
+                        memory=M(fresh=64, dim=128, dim_max=160, write=16 if name == "Fv2s_big16" else 8, focus=4))
+    elif name in ("Fv2s", "Fv2s_nomem", "Fv2s_w16"):
+        c = ModelConfig(vocab=vocab, d=256, light_a=1, light_b=1, heavy=2, final=1, heads=4, window=64, seg=32,
+                        memory=M(fresh=16, dim=32, dim_max=48, write=16 if name == "Fv2s_w16" else 8, focus=4),
+                        use_memory=name != "Fv2s_nomem")
+    elif name == "tiny":
+        # smallest end-to-end slice: d=256, 4 heads, 2+2 light layers window 128, 2 heavy MoE layers of 4 experts
+        # (expert hidden 2d -> SwiGLU ffn 1024), top-2 on anchors, memory off
+        c = ModelConfig(vocab=vocab, d=256, heads=4, light_a=2, light_b=2, heavy=2, final=0, window=128, seg=64,
+                        moe="fixed", n_exp=4, bank=True, no_mem=True)
+    elif name == "dense_v2_300m":
+        c = ModelConfig(vocab=vocab, d=1024, heads=16, light_a=2, light_b=2, heavy=12, final=0, window=256,
+                        memory=M(fresh=64, dim=64, dim_max=96), induct="lock", induct_mix=True)
+    elif name == "longctx_1024":
+        c = ModelConfig(vocab=vocab, d=1024, heads=16, light_a=4, light_b=4, heavy=6, final=2, window=256,
+                        attn_impl="block", moe="fixed", n_exp=8, bank=True)
+    else:
+        raise ValueError(f"unknown memarch model name: {name}")
+    return model_from_env(c, env)
+
+
+def published_recipe_env(art_dir: str) -> dict:
+    """Environment of the reference's published 2.25B run (scripts/g4_1b_b.py:5-8) with artefact paths under
+    `art_dir` (built by memarch_b200.data.phrasebook from the training corpus)."""
+    return {
+        "FUSED": "ours", "BF16_EXPERTS": "1", "MOE_ACT": "relu2", "LR_SCHED": "wsd", "WSD_FRAC": "0.5",
+        "WARMUP": "50",
+        "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12, "m_bf16": True, "rel_every": 8}),
+        "PHRASE_INIT": os.path.join(art_dir, "bigram.pt"), "PHRASE3": os.path.join(art_dir, "trigram.pt"),
+        "SURP_PHRASE": "1", "NO_MEM": "1", "INDUCT": "lock", "LOCK_TRUST": os.path.join(art_dir, "lock_trust.pt"),
+        "INDUCT_IN": "1", "INDUCT_MIX": "1", "WAVE_WARM": "1000000",
+        "TOKEN_COUNTS": os.path.join(art_dir, "token_counts.npy"),
+    }

@@ -1,0 +1,160 @@
+"""Light (sliding-window) transformer blocks, dense FFN heavy layer and the plain transformer baseline.
+
+Parameter names follow the reference so checkpoints interchange: `n1, qkv, o, n2, up, down` per block
+(baseline.py:35-52), FFN `norm, up, down` (lm.py:45-50).  Block variants are the reference's `BLK` set
+(full.py:113-182): zero, ve, x0, relu2, relu2c, qk, qkv3; `LIGHT_FFN`, `LIGHT_MOE`; opaque-token FFN skipping.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+
+
+def _cdt(x):
+    """Compute dtype of matmul operands: bf16 on the GPU (tcgen05), the tensor's own dtype on CPU."""
+    return torch.bfloat16 if x.is_cuda else x.dtype
+
+
+class FineMoE(nn.Module):
+    """Light-layer MoE: E small SwiGLU experts, k active per token, fixed capacity (full.py:51-91)."""
+
+    def __init__(self, d, E=32, k=4, hid=None):
+        super().__init__()
+        self.E, self.k = E, k
+        h = hid or 4 * d // k
+        self.router = nn.Linear(d, E, bias=False)
+        self.up = nn.Parameter(torch.randn(E, d, 2 * h) * d ** -0.5)
+        self.down = nn.Parameter(torch.randn(E, h, d) * h ** -0.5)
+        self.aux = torch.zeros(())
+
+    def forward(self, x):
+        shp = x.shape
+        xf = x.reshape(-1, shp[-1])
+        N = xf.shape[0]
+        logits = F.linear(xf.float(), self.router.weight.float())
+        gate, ex = logits.topk(self.k, -1)
+        gate = gate.softmax(-1)
+        prob = logits.softmax(-1)
+        frac = F.one_hot(ex, self.E).float().sum(1).mean(0) / self.k
+        self.aux = self.E * (frac * prob.mean(0)).sum()
+        C = int(1.25 * N * self.k / self.E) + 1
+        e_flat = ex.reshape(-1)
+        order = e_flat.argsort(stable=True)
+        es = e_flat[order]
+        start = torch.searchsorted(es, torch.arange(self.E, device=x.device))
+        slot = torch.arange(N * self.k, device=x.device) - start[es]
+        keep = slot < C
+        tok = order // self.k
+        dest = torch.where(keep, es * C + slot, torch.full_like(slot, self.E * C))
+        buf = xf.new_zeros(self.E * C + 1, shp[-1]).index_copy(0, dest, xf[tok])
+        hb = buf[:-1].view(self.E, C, -1).to(_cdt(x))
+        yb = ops.expert_ffn(hb, self.up, self.down, "swiglu").reshape(self.E * C, -1)
+        yb = torch.cat([yb, yb.new_zeros(1, yb.shape[-1])])
+        w = gate.reshape(-1)[order] * keep
+        y = xf.new_zeros(N, shp[-1]).index_add(0, tok, (yb[dest] * w[:, None].to(yb.dtype)).to(xf.dtype))
+        return y.view(shp)
+
+
+class LightBlock(nn.Module):
+    """RMSNorm -> qkv -> RoPE + causal/window attention -> o ; RMSNorm -> FFN (SwiGLU 4d or relu² 6d)."""
+
+    def __init__(self, d, heads, blk=(), light_ffn=0.0, light_moe="", vocab_heads=None, rope_half=False):
+        super().__init__()
+        self.heads, self.blk, self.rope_half = heads, set(blk), rope_half
+        self.n1 = nn.RMSNorm(d)
+        self.qkv = nn.Linear(d, 3 * d, bias=False)
+        self.o = nn.Linear(d, d, bias=False)
+        self.n2 = nn.RMSNorm(d)
+        self.relu2 = "relu2" in self.blk or "relu2c" in self.blk
+        if self.relu2:
+            self.up = nn.Linear(d, 6 * d, bias=False)
+            self.down = nn.Linear(6 * d, d, bias=False)
+        else:
+            self.up = nn.Linear(d, 8 * d, bias=False)
+            self.down = nn.Linear(4 * d, d, bias=False)
+        if light_ffn:
+            hid = max(256, int(round(light_ffn * d / 256)) * 256)
+            self.up = nn.Linear(d, hid if self.relu2 else 2 * hid, bias=False)
+            self.down = nn.Linear(hid, d, bias=False)
+        if "zero" in self.blk:
+            nn.init.zeros_(self.o.weight)
+            nn.init.zeros_(self.down.weight)
+        if "ve" in self.blk:
+            self.ve_gate = nn.Linear(d, heads, bias=False)
+            nn.init.zeros_(self.ve_gate.weight)
+        if "x0" in self.blk:
+            self.x0_l = nn.Parameter(torch.zeros(()))
+        if light_moe:
+            E, k = map(int, light_moe.split(":"))
+            self.moe = FineMoE(d, E, k)
+            del self.up, self.down
+        self.cur_ve = self.cur_x0 = self.cur_sel = None
+
+    def _act(self, h):
+        return ops.relu2(h) if self.relu2 else ops.swiglu(h)
+
+    def forward(self, x, window=None):
+        B, T, D = x.shape
+        hd = D // self.heads
+        dt = _cdt(x)
+        if self.cur_x0 is not None:
+            x = x + self.x0_l * self.cur_x0
+        n1 = ops.rmsnorm(x, self.n1.weight, self.n1.eps, out_dtype=dt)
+        qkv = ops.linear(n1, self.qkv.weight).view(B, T, 3, self.heads, hd)
+        if self.cur_ve is not None:
+            g = 2 * torch.sigmoid(F.linear(x, self.ve_gate.weight.to(x.dtype)))[..., None]        # (B,T,H,1)
+            v = qkv[:, :, 2] + (g * self.cur_ve.view(B, T, self.heads, hd)).to(qkv.dtype)
+            qkv = torch.stack([qkv[:, :, 0], qkv[:, :, 1], v], 2)
+        a = ops.attention(qkv, window, self.rope_half, qk_norm="qk" in self.blk)
+        x = x + ops.linear(a, self.o.weight).to(x.dtype)
+        if hasattr(self, "moe"):
+            return x + self.moe(ops.rmsnorm(x, self.n2.weight, self.n2.eps))
+        if self.cur_sel is not None:                      # opaque tokens only: FFN skipped where the talker is sure
+            idx, ok = self.cur_sel
+            xs = ops.rmsnorm(x, self.n2.weight, self.n2.eps, out_dtype=dt).gather(1, idx[..., None].expand(-1, -1, D))
+            y = ops.linear(self._act(ops.linear(xs, self.up.weight)), self.down.weight) * ok[..., None].to(dt)
+            return x.scatter_add(1, idx[..., None].expand(-1, -1, D), y.to(x.dtype))
+        n2 = ops.rmsnorm(x, self.n2.weight, self.n2.eps, out_dtype=dt)
+        return x + ops.linear(self._act(ops.linear(n2, self.up.weight)), self.down.weight).to(x.dtype)
+
+
+class DenseFFN(nn.Module):
+    """Attention-free heavy layer on anchors: x + down(SwiGLU(up(norm(x)))) (lm.py:45-60)."""
+
+    def __init__(self, d):
+        super().__init__()
+        self.norm = nn.RMSNorm(d)
+        self.up = nn.Linear(d, 8 * d, bias=False)
+        self.down = nn.Linear(4 * d, d, bias=False)
+
+    def forward(self, x, surprise=None):
+        n = ops.rmsnorm(x, self.norm.weight, self.norm.eps, out_dtype=_cdt(x))
+        return x + ops.linear(ops.swiglu(ops.linear(n, self.up.weight)), self.down.weight).to(x.dtype)
+
+
+class TransformerLM(nn.Module):
+    """Llama-style baseline (`T300`, `Td<d>L<L>`, lm.py:128-140): the control the reference races against."""
+
+    def __init__(self, vocab, d=512, layers=8, heads=8, fused_ce=True):
+        super().__init__()
+        self.vocab, self.fused_ce = vocab, fused_ce
+        self.emb = nn.Embedding(vocab, d)
+        self.blocks = nn.ModuleList(LightBlock(d, heads) for _ in range(layers))
+        self.norm = nn.RMSNorm(d)
+        self.head = nn.Linear(d, vocab, bias=False)
+        self.stats = {}
+
+    def forward(self, x, prep=None):
+        h = self.emb(x)
+        for b in self.blocks:
+            h = b(h)
+        return ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=_cdt(h)), torch.zeros((), device=x.device)
+
+    def train_loss(self, out, y, train=True):
+        if self.fused_ce and self.training:
+            return ops.linear_ce(out, self.head.weight, y) / y.numel()
+        lo = ops.linear(out, self.head.weight).float()
+        return F.cross_entropy(lo.reshape(-1, lo.shape[-1]), y.reshape(-1))

@@ -1,0 +1,648 @@
+"""MemArchLM: the product model (the reference's FullLM2, full2.py:1269-1997).
+
+    light window layers -> memory read (focus + cards) -> light window layers
+      -> surprise -> anchors (threshold + per-text cap) -> heavy layers on anchors only (no attention)
+      -> final window layers -> re-reading at bookmarks + recognition -> output head
+
+`forward(x[, prep]) -> ((hn, lh), cost)`, `train_loss(out, y, train)`, `prep(x)`, `table_rows(x)`,
+`before_step(step)`, `rebank(step)`, `.stats` (device tensors, no host sync) - the reference's public surface.
+Parameter and buffer names equal the reference's so `state_dict`s interchange.
+"""
+from __future__ import annotations
+
+import math
+import os
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import ref
+from .blocks import DenseFFN, LightBlock, _cdt
+from .memory import CardMemory, VolumeMemory
+from .moe import AnchorMoE
+from .reread import Reread
+
+_HC1, _HC2 = -7046029254386353131, -4658895280553007687
+
+
+def cuckoo_table(keys, max_kick=500):
+    """Two-choice cuckoo hash of the phrase keys at load <= 1/8: lookup = 2 probes (full2.py:126-150)."""
+    M = 1 << max(10, int(np.ceil(np.log2(max(len(keys), 1) * 8))))
+    mask = M - 1
+    with np.errstate(over="ignore"):
+        h1 = ((keys * np.int64(_HC1)) >> 24) & mask
+        h2 = ((keys * np.int64(_HC2)) >> 24) & mask
+    owner = np.full(M, -1, dtype=np.int64)
+    for i in range(len(keys)):
+        cur, slot = i, h1[i]
+        for _ in range(max_kick):
+            if owner[slot] < 0:
+                owner[slot] = cur
+                break
+            owner[slot], cur = cur, owner[slot]
+            slot = h2[cur] if slot == h1[cur] else h1[cur]
+        else:
+            raise RuntimeError("cuckoo: could not place a key - enlarge the table")
+    hk = np.full(M, -(1 << 62), dtype=np.int64)
+    hv = np.zeros(M, dtype=np.int64)
+    used = owner >= 0
+    hk[used] = keys[owner[used]]
+    hv[used] = owner[used]
+    return hk, hv, mask
+
+
+class HeavyCtxAttn(nn.Module):
+    """Optional: a heavy layer looks back into the light states of earlier words (full2.py:1245-1266)."""
+
+    def __init__(self, d, heads=8):
+        super().__init__()
+        self.h = heads
+        self.nq, self.nk = nn.RMSNorm(d), nn.RMSNorm(d)
+        self.q = nn.Linear(d, d, bias=False)
+        self.kv = nn.Linear(d, 2 * d, bias=False)
+        self.o = nn.Linear(d, d, bias=False)
+        nn.init.zeros_(self.o.weight)
+
+    def forward(self, a, ctx, idx):
+        B, A, D = a.shape
+        T = ctx.shape[1]
+        hd = D // self.h
+        q = self.q(self.nq(a)).view(B, A, self.h, hd).transpose(1, 2)
+        k, v = self.kv(self.nk(ctx)).view(B, T, 2, self.h, hd).permute(2, 0, 3, 1, 4)
+        mask = (torch.arange(T, device=a.device)[None, None, :] <= idx[:, :, None])[:, None]
+        y = F.scaled_dot_product_attention(q, k.type_as(q), v.type_as(q), attn_mask=mask)
+        return a + self.o(y.transpose(1, 2).reshape(B, A, D))
+
+
+class MemArchLM(nn.Module):
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.cfg = cfg
+        c = cfg
+        vocab, d = c.vocab, c.d
+        self.vocab, self.frac, self.cap, self.window, self.seg = vocab, c.frac, c.cap, c.window, c.seg
+        self.use_memory = c.use_memory
+        self.emb = nn.Embedding(vocab, d)
+        self.book = nn.Embedding(vocab, 128)
+        blk = lambda: LightBlock(d, c.heads, c.blk, c.light_ffn, c.light_moe, rope_half=c.rope_half)
+        self.light_a = nn.ModuleList(blk() for _ in range(c.light_a))
+        mk = dict(vars(c.memory))
+        volume = mk.pop("volume")
+        self.memory = (VolumeMemory if volume else CardMemory)(d, **mk)
+        self.light_b = nn.ModuleList(blk() for _ in range(c.light_b))
+        self.l_norm = nn.RMSNorm(d)
+        self.l_head = nn.Sequential(nn.Linear(d, 128, bias=False), nn.Linear(128, vocab, bias=False))
+        self.moe = c.moe
+        w_dtype = torch.bfloat16 if c.bf16_experts else torch.float32
+        if c.moe:
+            self.heavy = nn.ModuleList(
+                AnchorMoE(d, E=c.n_exp, k_avg=c.moe_k if c.bank else 2, k_max=max(4, c.moe_k) if c.bank else 4,
+                          budget=c.moe == "budget", wave=c.wave, wave_every=c.wave_every, students=c.students,
+                          hint_w=c.hint_w, frozen=c.n_frozen, bank=c.bank, act=c.moe_act if c.bank else "swiglu",
+                          w_dtype=w_dtype if c.bank else torch.float32, bank_q=c.bank_q, wave_warm=c.wave_warm,
+                          err_thr=c.err_thr, cap_align=c.moe_cap_align)
+                for _ in range(c.heavy))
+        else:
+            self.heavy = nn.ModuleList(DenseFFN(d) for _ in range(c.heavy))
+        for b in self.heavy:
+            b.fill = c.frac / c.cap
+        self.final = nn.ModuleList(blk() for _ in range(c.final))
+        self.reread = Reread(d)
+        self.norm = nn.RMSNorm(d)
+        self.head = nn.Linear(d, vocab, bias=False)
+        self.register_buffer("tau", torch.tensor(5.0))
+        self.stats = {}
+        self.panic = c.panic
+        self.short_v = c.short_v
+        if c.short_v:
+            self._init_short_vocab()
+        n_light = c.light_a + c.light_b
+        if "ve" in c.blk:
+            self.ve = nn.ModuleList(nn.Embedding(vocab, d) for _ in range(n_light))
+        if "smear" in c.blk:
+            self.smear = nn.Linear(d, 1, bias=False)
+            nn.init.zeros_(self.smear.weight)
+        if c.phrase_init:
+            self._init_phrasebook(torch.load(c.phrase_init, weights_only=False))
+        if c.phrase3:
+            self._init_phrase_table(torch.load(c.phrase3, weights_only=False), "phr")
+        if c.phrase4:
+            self._init_phrase_table(torch.load(c.phrase4, weights_only=False), "phr4")
+        if c.skip:
+            sk = torch.load(c.skip, weights_only=False)
+            g = c.skip_g / c.phrase_c
+            self.skip_o = sorted(sk)
+            self.skip = nn.ModuleList(nn.Embedding(vocab, d) for _ in self.skip_o)
+            with torch.no_grad():
+                for t, o in zip(self.skip, self.skip_o):
+                    t.weight.zero_()
+                    t.weight[:sk[o].shape[0]].copy_(sk[o] * g)
+        if c.tongue:
+            pt = torch.load(c.tongue, weights_only=False)
+            for k in ("bi_idx", "bi_val", "tri_idx", "tri_val"):
+                self.register_buffer("tg_" + k, pt[k], persistent=False)
+            self.register_buffer("tg_keys", pt["keys"].long(), persistent=False)
+            self.tg_a = nn.Parameter(torch.tensor([c.tongue_a, c.tongue_a]))
+        if c.induct:
+            self._init_locks()
+        if c.heavy_attn:
+            self.h_attn = nn.ModuleList(HeavyCtxAttn(d, c.heads) for _ in range(c.heavy))
+        self.n_draft = c.n_draft
+        if c.n_draft:
+            self.draft = nn.ModuleList(nn.Linear(d, d, bias=False) for _ in range(c.n_draft))
+            for lin in self.draft:
+                nn.init.zeros_(lin.weight)
+            self.draft_norm = nn.RMSNorm(d)
+
+    # ------------------------------------------------------------------------------------------ constructors
+    def _counts(self):
+        c = self.cfg
+        cnt = np.zeros(self.vocab, np.int64)
+        if c.token_counts:
+            c0 = np.load(c.token_counts).astype(np.int64)[:self.vocab]
+            cnt[:len(c0)] = c0
+        return cnt
+
+    def _init_short_vocab(self):
+        """Two-level output: K most frequent tokens + a "rare" bucket row (last vocab row) (full2.py:1305-1337)."""
+        vocab, K = self.vocab, self.short_v
+        cnt = self._counts()
+        top = torch.from_numpy(np.argsort(-cnt, kind="stable")[:K].copy())
+        pos = torch.full((vocab,), K, dtype=torch.long)
+        pos[top] = torch.arange(K)
+        self.register_buffer("sv_ids", top, persistent=False)
+        self.register_buffer("sv_pos", pos, persistent=False)
+        self.sv_bucket = vocab - 1
+        assert cnt[self.sv_bucket] == 0 and pos[self.sv_bucket] == K, "last vocab row must be unused"
+        msk = (pos < K).float() * -1e4
+        msk[self.sv_bucket] = -1e4
+        self.register_buffer("sv_mask", msk, persistent=False)
+        rare = 1 - cnt[top.numpy()].sum() / max(cnt.sum(), 1) if cnt.sum() else 0.18
+        rare = min(max(rare, 1e-3), 0.999)
+        self.sv_prior0 = float(np.log(rare * K / (1 - rare)))
+        self.sv_prior1 = float(np.log(rare))
+        with torch.no_grad():
+            self.head.weight[self.sv_bucket].zero_()
+        self.rare_cap = self.cfg.rare_cap
+
+    def _init_phrasebook(self, ph):
+        """emb <- E / rms_row(E), head <- H·c, head_bias <- log p(next) (full2.py:1346-1365)."""
+        c = self.cfg
+        E, H = ph["emb"].float(), ph["head"].float()
+        with torch.no_grad():
+            rms = E.pow(2).mean(1, keepdim=True).sqrt().clamp(min=1e-6)
+            n = E.shape[0]
+            self.emb.weight[:n].copy_(E / rms)
+            self.head.weight[:n].copy_(H * c.phrase_c)
+            self.head.weight[n:].zero_()
+        lp = torch.full((self.vocab,), float(ph["logp_next"].min()) - 5)
+        lp[:n] = ph["logp_next"]
+        self.head_bias = nn.Parameter(lp)
+        if c.opaque and "ent" in ph:
+            self.register_buffer("ent_t", ph["ent"].float(), persistent=False)
+        if c.surp_phrase:
+            self.register_buffer("sp_E", ((E / rms) * c.phrase_c).to(torch.bfloat16), persistent=False)
+            self.register_buffer("sp_H", H.to(torch.bfloat16), persistent=False)
+            self.register_buffer("sp_lp", ph["logp_next"].float(), persistent=False)
+            self.register_buffer("sp_lse", ph["lse"].float(), persistent=False)
+
+    def _init_phrase_table(self, tg, name):
+        c = self.cfg
+        K = len(tg["keys"])
+        self.register_buffer(name + "_keys", tg["keys"].long(), persistent=False)
+        if name == "phr" and c.phr_hash:
+            hk, hv, self.phr_hmask = cuckoo_table(tg["keys"].long().numpy())
+            self.register_buffer("phr_hkey", torch.from_numpy(hk), persistent=False)
+            self.register_buffer("phr_hval", torch.from_numpy(hv), persistent=False)
+        emb = nn.Embedding(K + 1, c.d)
+        with torch.no_grad():
+            emb.weight.zero_()
+            emb.weight[:K].copy_(tg["vec"] / c.phrase_c)
+        setattr(self, name, emb)
+        self.phr_V = c.phr_v
+
+    def _init_locks(self):
+        c = self.cfg
+        self.ind_a = nn.Parameter(torch.tensor([1.0, 1.0]))
+        self.ind_in_g = nn.Parameter(torch.full((3,), -2.0))
+        if c.induct == "lock":
+            cnt = self._counts()
+            bucket = np.clip(np.floor(np.log10(cnt + 1)), 0, 6).astype(np.int64)
+            self.register_buffer("lock_bucket", torch.tensor(bucket), persistent=False)
+            lw = torch.load(c.lock_trust, weights_only=False) if c.lock_trust else torch.ones(3, 7)
+            self.lock_w = nn.Parameter(lw.clone().float())
+            if c.induct_mix:
+                pm = (lw.float().exp() * math.exp(-4.5)).clamp(0.005, 0.95)
+                self.mix_w = nn.Parameter(torch.log(pm / (1 - pm)))
+
+    # ------------------------------------------------------------------------------------------ token-only prep
+    def _phr_idx(self, x):
+        if hasattr(self, "phr_hkey"):
+            ctx = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1) * self.phr_V + x
+            K = self.phr_keys.numel()
+            s1 = ((ctx * _HC1) >> 24) & self.phr_hmask
+            s2 = ((ctx * _HC2) >> 24) & self.phr_hmask
+            return torch.where(self.phr_hkey[s1] == ctx, self.phr_hval[s1],
+                               torch.where(self.phr_hkey[s2] == ctx, self.phr_hval[s2], torch.full_like(ctx, K)))
+        return ref.phrase_index(x, self.phr_keys, self.phr_V)
+
+    def _phr4_idx(self, x):
+        V = self.phr_V
+        p1 = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1)
+        p2 = torch.cat([torch.full_like(x[:, :2], -1), x[:, :-2]], 1)
+        ctx = (p2 * V + p1) * V + x
+        K = self.phr4_keys.numel()
+        pos = torch.searchsorted(self.phr4_keys, ctx).clamp(max=K - 1)
+        return torch.where(self.phr4_keys[pos] == ctx, pos, torch.full_like(pos, K))
+
+    def _phr_surp(self, x):
+        """Surprise from the phrasebook: lse[prev] - (c·Ê[prev]·H[cur] + logp[cur]) (full2.py:1479-1488)."""
+        B, T = x.shape
+        s_ = torch.full((B, T), 1e4, device=x.device)
+        xp, xc = x[:, :-1], x[:, 1:]
+        n = self.sp_lse.numel()
+        ok = (xp < n) & (xc < n)
+        xp, xc = xp.clamp(max=n - 1), xc.clamp(max=n - 1)
+        lo = (self.sp_E[xp].float() * self.sp_H[xc].float()).sum(-1) + self.sp_lp[xc]
+        s_[:, 1:] = torch.where(ok, self.sp_lse[xp] - lo, torch.full_like(lo, 1e4))
+        return s_
+
+    def _locks_raw(self, x):
+        lb = self.lock_bucket if hasattr(self, "lock_w") else None
+        return ops.find_locks(x, self.vocab, 3 if lb is not None else 2, lb)
+
+    @torch.no_grad()
+    def prep(self, x):
+        """Everything that depends on tokens only, not on weights; computed ahead for the next batch."""
+        p = {}
+        if hasattr(self, "phr"):
+            p["phr"] = self._phr_idx(x)
+        if hasattr(self, "phr4"):
+            p["phr4"] = self._phr4_idx(x)
+        if hasattr(self, "ind_a"):
+            p["ind_cand"], p["ind_on"], p["ind_bk"], p["ind_src"] = self._locks_raw(x)
+        if hasattr(self, "sp_lse"):
+            p["surp"] = self._phr_surp(x)
+        return p
+
+    @torch.no_grad()
+    def table_rows(self, x):
+        rows = {id(self.emb.weight): x.reshape(-1)}
+        if hasattr(self, "phr"):
+            rows[id(self.phr.weight)] = self._phr_idx(x).reshape(-1)
+        if hasattr(self, "phr4"):
+            rows[id(self.phr4.weight)] = self._phr4_idx(x).reshape(-1)
+        return rows
+
+    # ------------------------------------------------------------------------------------------ forward
+    def _run(self, blk, *a, heavy=False):
+        k = self.cfg.ckpt
+        on = k == "1" or (k == "heavy" and heavy) or (k == "light" and not heavy)
+        if on and self.training and torch.is_grad_enabled():
+            return checkpoint(blk, *a, use_reentrant=False)
+        return blk(*a)
+
+    def forward(self, x, prep=None):
+        c = self.cfg
+        B, T = x.shape
+        win = self.window if T > self.window else None
+        h = self.emb(x)
+        if c.resid_bf16 and x.is_cuda:
+            h = h.to(torch.bfloat16)
+        self._tongue = self._mix = None
+        if hasattr(self, "ind_a"):
+            if prep and "ind_cand" in prep:
+                cand, on, bk, src = prep["ind_cand"], prep["ind_on"], prep["ind_bk"], prep.get("ind_src")
+            else:
+                cand, on, bk, src = self._locks_raw(x)
+            if hasattr(self, "lock_w"):
+                val = torch.stack([on[..., k].float() * self.lock_w[k][bk] for k in range(on.shape[-1])], -1)
+            else:
+                val = on.float() * self.ind_a[:on.shape[-1]]
+            self._tongue = (cand, val)
+            if hasattr(self, "mix_w"):
+                anyon = on.any(-1)
+                kk = on.float().argmax(-1)
+                c1 = (cand * on).sum(-1)
+                g = torch.sigmoid(self.mix_w[kk, bk]) * anyon
+                self._mix = (c1, g)
+                self.stats["mix_g"] = (g.sum() / anyon.sum().clamp(min=1)).detach()
+            tw = self.lock_w if hasattr(self, "lock_w") else self.ind_a
+            self.stats["trust"] = tw.detach().float().mean()
+            if c.induct_in:
+                gi = torch.sigmoid(self.ind_in_g[:cand.shape[-1]])
+                sel = (val != 0).to(h.dtype) * gi[None, None].to(h.dtype)
+                h = h + (self.emb(cand) * sel[..., None]).sum(2).type_as(h)
+        if hasattr(self, "tg_a"):
+            V0 = c.phr_v
+            xc = x.clamp(max=V0 - 1)
+            ctx = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1) * V0 + x
+            K = self.tg_keys.numel()
+            pos = torch.searchsorted(self.tg_keys, ctx).clamp(max=K - 1)
+            hit = (self.tg_keys[pos] == ctx)[..., None]
+            cand = torch.where(hit, self.tg_tri_idx[pos], self.tg_bi_idx[xc])
+            val = torch.where(hit, self.tg_tri_val[pos].float() * self.tg_a[1], self.tg_bi_val[xc].float() * self.tg_a[0])
+            self._tongue = (cand, val)
+        if hasattr(self, "phr"):
+            h = h + self.phr(prep["phr"] if prep and "phr" in prep else self._phr_idx(x)).type_as(h)
+        if hasattr(self, "phr4"):
+            h = h + self.phr4(prep["phr4"] if prep and "phr4" in prep else self._phr4_idx(x)).type_as(h)
+        if hasattr(self, "skip"):
+            for t, o in zip(self.skip, self.skip_o):
+                xs = torch.cat([x[:, :1].expand(-1, o - 1), x[:, :-(o - 1)]], 1)
+                m = (torch.arange(T, device=x.device) >= o - 1).to(h.dtype)[None, :, None]
+                h = h + t(xs).type_as(h) * m
+        if hasattr(self, "smear"):
+            h = torch.cat([h[:, :1], h[:, 1:] + torch.sigmoid(self.smear(h[:, 1:])) * h[:, :-1]], 1)
+        lights = list(self.light_a) + list(self.light_b)
+        if hasattr(self, "ent_t"):
+            n = self.ent_t.numel()
+            ent = self.ent_t[x.clamp(max=n - 1)]
+            K = max(16, int(T * c.opaque) // 16 * 16)
+            op = ent > c.opaque_thr
+            keep = op & (op.cumsum(1) <= K)
+            sidx = ((~keep).long() * T + torch.arange(T, device=x.device)).argsort(dim=-1, stable=True)[:, :K]
+            sel = (sidx, keep.gather(1, sidx))
+            for b in lights + list(self.final):
+                b.cur_sel = sel
+            self.stats["opaque"] = keep.float().mean()
+        if "ve" in c.blk or "x0" in c.blk:
+            for i, b in enumerate(lights):
+                b.cur_ve = self.ve[i](x) if "ve" in c.blk else None
+                b.cur_x0 = h if "x0" in c.blk else None
+        for b in self.light_a:
+            h = self._run(b, h, win)
+
+        seg = min(self.seg, T)
+        snaps = None
+        if not c.no_mem:
+            reads, snaps, st = self._memory_pass(h, seg)
+            self.last_mem = (snaps, st)
+            h = h + reads.type_as(h)
+            self.stats["mem_cards"] = st["valid"].float().sum(1).mean()
+
+        for b in self.light_b:
+            h = self._run(b, h, win)
+        lh = ops.rmsnorm(h, self.l_norm.weight, self.l_norm.eps)
+
+        # surprise -> anchors: the light part's own prediction error decides where to think hard
+        with torch.no_grad():
+            if hasattr(self, "sp_lse"):
+                s_ = prep["surp"] if prep and "surp" in prep else self._phr_surp(x)
+            else:
+                s_ = self._light_surprise(lh.detach(), x)
+            if self.training:
+                self.tau.mul_(0.9).add_(0.1 * ref.tau_quantile(s_, self.frac))
+            A = max(1, round(T * self.cap))
+            idx, valid = ops.select_anchors(s_, self.tau, A)
+            self.stats["anchors"] = valid.float().mean() * A / T
+
+        a_in = ops.gather_tokens(h, idx)
+        a = a_in
+        sa = None
+        if self.moe:
+            sa = torch.where(valid, s_.gather(1, idx).clamp(0, 50), torch.full_like(s_[:, :A], -1.0))
+        ctx = h.detach() if c.heavy_attn_detach else h
+        for li, b in enumerate(self.heavy):
+            if hasattr(self, "h_attn"):
+                a = self.h_attn[li](a, ctx, idx)
+            a = self._run(b, a, sa, heavy=True)
+        h = ops.scatter_back(h, idx, (a - a_in) * valid[..., None])
+        if self.n_draft:
+            an = self.draft_norm(a)
+            self._drafts = []
+            d = h.shape[-1]
+            for j, lin in enumerate(self.draft, 1):
+                pj = idx + j
+                okj = valid & (pj < T)
+                dj = lin(an)
+                self._drafts.append((dj, pj.clamp(max=T - 1), okj))
+                h = ops.scatter_back(h, pj.clamp(max=T - 1), dj * okj[..., None])
+        if self.moe:
+            self.stats["moe_drop"] = sum(b.dropped for b in self.heavy) / len(self.heavy)
+            if self.heavy[0].wave:
+                L = len(self.heavy)
+                self.stats["learned"] = sum(b.learned.float().mean() for b in self.heavy) / L
+                self.stats["hint"] = sum(b.hint_avg[0] for b in self.heavy) / L
+                self.stats["err_r"] = sum((b.err / b.err_peak.clamp(min=1e-12)).min() for b in self.heavy) / L
+                if self.heavy[0].wave == "still":
+                    self.stats["move_r"] = sum((b.last_move / b.move_peak.clamp(min=1e-12)).min() for b in self.heavy) / L
+
+        for b in self.final:
+            h = self._run(b, h, win)
+
+        dt = _cdt(h)
+        if c.no_mem or c.no_reread:
+            return (ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt), lh), torch.zeros((), device=x.device)
+        o, cost = self._reread_pass(h, x, snaps, seg)
+        h = h + o.type_as(h)
+        return (ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt), lh), cost
+
+    def _light_surprise(self, lhd, x):
+        """lse - logit[target] of the light head for every position but the last (full2.py:1650-1667)."""
+        B, T = x.shape
+        s_ = torch.full((B, T), 1e4, device=x.device)
+        w0, W2 = self.l_head[0].weight, self.l_head[1].weight
+        ch = self.cfg.ce_chunk
+        for j in range(0, T - 1, 8192):
+            hj = lhd[:, j:min(j + 8192, T - 1)]
+            tgt = x[:, j + 1:j + 1 + hj.shape[1]]
+            h128 = ops.linear(hj, w0)
+            if ch:
+                lse, ly = ref.chunk_lse(h128.reshape(-1, h128.shape[-1]), W2, None, tgt.reshape(-1), ch)
+                s_[:, j + 1:j + 1 + hj.shape[1]] = (lse - ly).view(B, -1)
+            else:
+                lo = ops.linear(h128, W2).float()
+                s_[:, j + 1:j + 1 + hj.shape[1]] = torch.logsumexp(lo, -1) - lo.gather(-1, tgt[..., None]).squeeze(-1)
+        return s_
+
+    # ------------------------------------------------------------------------------------------ memory / reread
+    def _seg_step(self, hs, st, s0):
+        r, w = self.memory.read(hs, st)
+        if not self.use_memory:
+            r, w = r * 0, w * 0
+        snap = (st["faces"], self.memory.contents(st), st["pos"], st["valid"])
+        qpos = (s0 + torch.arange(hs.shape[1], device=hs.device)).expand(hs.shape[0], -1)
+        st = self.memory.write(hs + r, qpos, st, now=float(s0 + hs.shape[1]), w_read=w)
+        return r, snap, st
+
+    def _memory_pass(self, h, seg):
+        """Segments of `seg` words: segment k reads the state left by segments < k, then writes
+        (full2.py:1746-1767).  State is re-created empty on every call: texts of a batch are separate documents."""
+        B, T, _ = h.shape
+        st = self.memory.init_state(B, h.device, torch.float32)
+        reads, snaps = [], []
+        for s in range(0, T, seg):
+            r, snap, st = self._seg_step(h[:, s:s + seg].float(), st, s)
+            reads.append(r)
+            snaps.append(snap)
+        return torch.cat(reads, 1), snaps, st
+
+    def _reread_pass(self, h, x, snaps, seg):
+        """Re-reading for all segments as one batch: segment k sees memory snapshot k (full2.py:1820-1840)."""
+        B, T, d = h.shape
+        n = len(snaps)
+        pad = n * seg - T
+        hs = F.pad(h.float(), (0, 0, 0, pad)).view(B, n, seg, d).transpose(0, 1).reshape(n * B, seg, d)
+        cat = lambda i: torch.stack([sn[i] for sn in snaps]).reshape(n * B, *snaps[0][i].shape[1:])
+        faces, contents, pos, valid = cat(0), cat(1), cat(2), cat(3)
+        qpos = (torch.arange(n, device=h.device)[:, None] * seg + torch.arange(seg, device=h.device)).repeat_interleave(B, 0)
+        rows = torch.arange(B, device=h.device).repeat(n)
+        o, cost = self.reread(hs, x.contiguous(), self.book.weight, faces, contents, pos, valid, qpos, rows)
+        if not self.use_memory:
+            o, cost = o * 0, cost * 0
+        o = o.view(n, B, seg, d).transpose(0, 1).reshape(B, n * seg, d)[:, :T]
+        return o, cost
+
+    # ------------------------------------------------------------------------------------------ loss
+    def _head_w(self, hn):
+        """Output table; with head_bias the word frequency rides as one extra input dimension (padded to 16)."""
+        if not hasattr(self, "head_bias"):
+            return hn, self.head.weight
+        V = self.head.weight.shape[0]
+        hn = torch.cat([hn, torch.ones_like(hn[..., :1]), torch.zeros_like(hn[..., :15])], -1)
+        w = torch.cat([self.head.weight, self.head_bias[:, None].to(self.head.weight.dtype),
+                       self.head.weight.new_zeros(V, 15)], 1)
+        return hn, w
+
+    def _fused_ce(self, hn, y):
+        hn, w = self._head_w(hn)
+        if self._mix is not None:
+            c1, g = self._mix
+            return ops.linear_ce(hn, w, y, gate=g, hit=(c1 == y).float())
+        if self._tongue is not None:
+            cand, val = self._tongue
+            return ops.linear_ce(hn, w, y, cand=cand, cval=val)
+        return ops.linear_ce(hn, w, y)
+
+    def _logits(self, hn):
+        lo = ops.linear(hn, self.head.weight).float()
+        if hasattr(self, "head_bias"):
+            lo = lo + self.head_bias.float()
+        return lo
+
+    def _ce_tok(self, hn, y):
+        lo = self._logits(hn)
+        return F.cross_entropy(lo.reshape(-1, lo.shape[-1]), y.reshape(-1), reduction="none")
+
+    def _short_logp(self, h, y):
+        """log P(y) of the two-level head (full2.py:1875-1898)."""
+        W, b = self.head.weight, getattr(self, "head_bias", None)
+        K, N = self.short_v, h.shape[0]
+        Ws = torch.cat([W[self.sv_ids], W[self.sv_bucket:self.sv_bucket + 1]])
+        bs = (torch.cat([b[self.sv_ids].float(), h.new_full((1,), self.sv_prior1, dtype=torch.float32)]) if b is not None
+              else torch.cat([h.new_zeros(K, dtype=torch.float32), h.new_full((1,), self.sv_prior0, dtype=torch.float32)]))
+        ys = self.sv_pos[y]
+        ch = self.cfg.ce_chunk or 16768
+        lse_s, ly_s = ops.chunk_ce(h, Ws, bs, ys, min(ch, K + 1))
+        logp = ly_s - lse_s
+        rare = ys == K
+        C = min(N, -(-int(round(self.rare_cap * N)) // 256) * 256)
+        key = rare.float() * 2 - torch.arange(N, device=h.device, dtype=torch.float32) / N
+        idx = key.detach().topk(C).indices
+        hit = rare[idx]
+        br = (b.float() if b is not None else W.new_zeros(W.shape[0], dtype=torch.float32)) + self.sv_mask
+        lse_r, ly_r = ops.chunk_ce(h[idx], W, br, y[idx], ch)
+        logp = logp.index_add(0, idx, torch.where(hit, ly_r - lse_r, torch.zeros_like(ly_r)))
+        self.stats["rare_drop"] = (rare.sum() - hit.sum()).float() / N
+        return logp
+
+    def _ce_part(self, hn, y, j):
+        c = self.cfg
+        mix = self._mix
+        tongue = self._tongue if mix is None else None
+        B_, T_ = y.shape
+        if c.ce_chunk and tongue is None:
+            if self.short_v:
+                logp = self._short_logp(hn.reshape(B_ * T_, -1), y.reshape(-1)).view(B_, T_)
+                lse, ly = torch.zeros_like(logp), logp
+            else:
+                lse, ly = ops.chunk_ce(hn.reshape(B_ * T_, -1), self.head.weight, getattr(self, "head_bias", None),
+                                       y.reshape(-1), c.ce_chunk)
+                lse, ly = lse.view(B_, T_), ly.view(B_, T_)
+        else:
+            lo = self._logits(hn)
+            if tongue is not None:
+                cand, val = tongue
+                lo = lo.scatter_add(-1, cand[:, j:j + T_].long(), val[:, j:j + T_].float())
+            lse = torch.logsumexp(lo, -1)
+            ly = lo.gather(-1, y[..., None])[..., 0]
+        if mix is not None:
+            c1, g = mix
+            c1, g = c1[:, j:j + T_], g[:, j:j + T_]
+            py = (ly - lse).exp()
+            return -torch.log(((1 - g) * py + g * (c1 == y).float()).clamp(min=1e-30)).sum()
+        return (lse - ly).sum()
+
+    def train_loss(self, out, y, train=True):
+        c = self.cfg
+        hn, lh = out
+        if train and self.training and self.panic:
+            loss = 0
+            for j in range(0, hn.shape[1], 8192):
+                ce = checkpoint(self._ce_tok, hn[:, j:j + 8192], y[:, j:j + 8192], use_reentrant=False)
+                w = (ce / ce.mean()).detach().clamp(0.25, 4.0) ** self.panic
+                loss = loss + (ce * (w / w.mean())).sum()
+        elif c.fused_ce and self.training and not self.short_v:
+            loss = self._fused_ce(hn, y)
+        else:
+            loss = 0
+            for j in range(0, hn.shape[1], 8192):
+                part = (hn[:, j:j + 8192], y[:, j:j + 8192])
+                if self.training and not c.ce_chunk and torch.is_grad_enabled():
+                    loss = loss + checkpoint(self._ce_part, *part, j, use_reentrant=False)
+                else:
+                    loss = loss + self._ce_part(*part, j)
+        loss = loss / y.numel()
+        if train and self.moe:
+            loss = loss + 0.01 * sum(b.aux for b in self.heavy) / len(self.heavy)
+        if train and len(self.light_a) and hasattr(self.light_a[0], "moe"):
+            lb = list(self.light_a) + list(self.light_b) + list(self.final)
+            loss = loss + 0.01 * sum(b.moe.aux for b in lb) / len(lb)
+        if train and self.n_draft and c.draft_loss:
+            dl = 0
+            for dj, pj, okj in self._drafts:
+                tgt = y.gather(1, pj)
+                lo = self._logits(ops.rmsnorm(dj, self.norm.weight, self.norm.eps))
+                ce = F.cross_entropy(lo.reshape(-1, lo.shape[-1]), tgt.reshape(-1), reduction="none")
+                dl = dl + (ce * okj.reshape(-1)).sum() / okj.sum().clamp(min=1)
+            loss = loss + c.draft_loss * dl / len(self._drafts)
+        if train and not hasattr(self, "sp_lse"):
+            V = self.head.out_features
+            h4, y4 = lh[:, ::4], y[:, ::4]
+            h128 = ops.linear(h4, self.l_head[0].weight)
+            if c.ce_chunk:
+                lse, ly = ops.chunk_ce(h128.reshape(-1, h128.shape[-1]), self.l_head[1].weight, None, y4.reshape(-1),
+                                       c.ce_chunk)
+                loss = loss + 0.3 * (lse - ly).mean()
+            else:
+                lo = ops.linear(h128, self.l_head[1].weight).float()
+                loss = loss + 0.3 * F.cross_entropy(lo.reshape(-1, V), y4.reshape(-1))
+        return loss
+
+    # ------------------------------------------------------------------------------------------ waves
+    @torch.no_grad()
+    def rebank(self, step, every=1000):
+        """Every `every` steps move experts between banks in all layers at once; the only host read of the
+        `learned` masks (full2.py:1932-1946)."""
+        banks = [b for b in self.heavy if isinstance(b, AnchorMoE) and b.bank]
+        if not banks or step == 0 or step % every:
+            return []
+        masks = torch.stack([b.learned for b in banks]).cpu().tolist()
+        if not any(b.wants_rebank(mk) for b, mk in zip(banks, masks)):
+            return []
+        changes = []
+        for b, mk in zip(banks, masks):
+            changes += b.rebank(mk)
+        self.stats["frozen"] = torch.tensor(sum(len(b.Fz) for b in banks) / sum(b.E for b in banks))
+        return changes
+
+    def before_step(self, step):
+        for b in self.heavy:
+            if hasattr(b, "before_step"):
+                b.before_step(step)

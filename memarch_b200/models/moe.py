@@ -1,0 +1,347 @@
+"""Heavy MoE layer that runs on anchor tokens only: shared-budget routing, fixed-capacity slots, SwiGLU/relu²
+experts, wave training and a real frozen bank, expert parallelism.
+
+One class covers the reference's `BudgetMoE` (full2.py:384-643) and `BankMoE` (full2.py:870-1242):
+  * router softmax -> top-k_max, per-token expert budget from surprise (budget mode) or a fixed k;
+  * capacity C = int(cf·fill·N·k/E)+1 places per expert filled in arrival order, overflow dropped and reported;
+  * Switch-style balance loss in `.aux`, dropped share in `.dropped`;
+  * waves: `learned` experts stop training ("err" = error below a share of its peak, "still" = weights stopped
+    moving); bank mode moves learned experts into a frozen bf16 (or int8/int4) bank without grads or optimizer
+    state and thaws those that start erring again (`rebank`);
+  * expert parallelism: `ep_shard(rank, W)` keeps E/W experts per rank; tokens travel by all-to-all through the
+    attached `ep_engine` (NCCL baseline or the fused peer-memory kernels in `memarch_b200.parallel.ep`).
+State-dict names match the reference: `norm.weight, router.weight, up, down`, buffers `s_mean, err, err_peak,
+err_freeze, move_peak, last_move, hint_avg, learned, up_snap, L_idx, F_idx, up_f, down_f, up_fs, down_fs`.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from .blocks import _cdt
+
+
+class _ErrProbe(torch.autograd.Function):
+    """Identity forward; backward folds the mean output-gradient norm of every expert into an EMA buffer
+    (the expert's "error": how much the loss wants its output changed).  (full2.py:331-344)"""
+
+    @staticmethod
+    def forward(ctx, y, buf):
+        ctx.buf = buf
+        return y.view_as(y)
+
+    @staticmethod
+    def backward(ctx, g):
+        with torch.no_grad():
+            ctx.buf.mul_(0.9).add_(0.1 * g.float().norm(dim=-1).mean(1))
+        return g, None
+
+
+class AnchorMoE(nn.Module):
+    def __init__(self, d, E=8, k_avg=2, k_max=4, budget=True, wave="", wave_every=50, students=5, hint_w=1.0,
+                 frozen=0, bank=False, act="swiglu", w_dtype=torch.float32, bank_q="", wave_warm=500,
+                 err_thr=0.3, cap_align=0, local_experts=None):
+        super().__init__()
+        self.E, self.k_avg, self.k_max, self.budget = E, k_avg, k_max, budget
+        self.bank, self.act, self.bank_q, self.cap_align = bank, act, bank_q, cap_align
+        self.fill = 1.0
+        self.norm = nn.RMSNorm(d)
+        self.router = nn.Linear(d, E, bias=False)
+        if bank:
+            hid = 2 * d * 2 // k_avg
+            self.width_in = 3 * hid // 2 if act == "relu2" else 2 * hid        # columns of `up`
+            self.width_out = 3 * hid // 2 if act == "relu2" else hid           # rows of `down`
+            wave, hint_w, budget = "still", 0.0, False
+            self.budget = False
+        else:
+            hid = 2 * d
+            self.width_in, self.width_out = 2 * hid, hid
+            act = self.act = "swiglu"
+        Ea = (E - frozen) if local_experts is None else local_experts
+        self.n_frozen = frozen
+        self.up = nn.Parameter((torch.randn(Ea, d, self.width_in) * d ** -0.5).to(w_dtype))
+        self.down = nn.Parameter((torch.randn(Ea, self.width_out, d) * self.width_out ** -0.5 * 0.5).to(w_dtype))
+        self.w_dtype = w_dtype
+        self.aux = torch.zeros(())
+        self.dropped = torch.zeros(())
+        self.register_buffer("s_mean", torch.tensor(5.0))
+        self.wave, self.wave_every, self.students, self.hint_w = wave, wave_every, students, hint_w
+        self.warm, self.err_thr = wave_warm, err_thr
+        self.hint_now = False
+        self.hint = torch.zeros(())
+        if wave:
+            for nm in ("err", "err_peak", "err_freeze", "move_peak", "last_move", "hint_avg"):
+                self.register_buffer(nm, torch.zeros(E))
+            self.register_buffer("learned", torch.zeros(E, dtype=torch.bool))
+            if wave == "still":
+                self.register_buffer("up_snap", self.up.detach().clone())
+        if frozen and not bank:
+            self.register_buffer("up_f", (torch.randn(frozen, d, self.width_in) * d ** -0.5).bfloat16())
+            self.register_buffer("down_f", (torch.randn(frozen, self.width_out, d) * self.width_out ** -0.5 * 0.5)
+                                 .bfloat16())
+        if bank:
+            self.L, self.Fz = list(range(E)), []
+            self.has_L, self.has_F = True, False
+            self.register_buffer("L_idx", torch.arange(E))
+            self.register_buffer("F_idx", torch.zeros(0, dtype=torch.long))
+            self.register_buffer("up_f", torch.zeros(0, d, self.width_in, dtype=torch.bfloat16))
+            self.register_buffer("down_f", torch.zeros(0, self.width_out, d, dtype=torch.bfloat16))
+            self.register_buffer("up_fs", torch.zeros(0, 1, self.width_in, dtype=torch.bfloat16))
+            self.register_buffer("down_fs", torch.zeros(0, 1, d, dtype=torch.bfloat16))
+        self.ep_W, self.ep_rank, self.ep_engine = 1, 0, None
+
+    # ------------------------------------------------------------------------------------------ routing
+    def capacity(self, N):
+        cf = 1.6 if self.budget else 1.25
+        C = int(cf * self.fill * N * self.k_avg / self.E) + 1
+        if self.cap_align:
+            C = max(self.cap_align, round(C / self.cap_align) * self.cap_align)
+        return C
+
+    def _route(self, x, surprise):
+        N, d = x.shape[0] * x.shape[1], x.shape[-1]
+        xf = ops.rmsnorm(x, self.norm.weight, self.norm.eps).reshape(N, d)
+        real = (surprise.reshape(N) >= 0) if surprise is not None else torch.ones(N, dtype=torch.bool, device=x.device)
+        if self.budget and surprise is not None:
+            s = surprise.reshape(N).float().clamp(min=0)
+            k_tok = (self.k_avg * s / self.s_mean.clamp(min=1e-6)).round().clamp(1, self.k_max).long()
+            if self.training:
+                with torch.no_grad():
+                    self.s_mean.mul_(0.99).add_(0.01 * (s * real).sum() / real.sum().clamp(min=1))
+        else:
+            k_tok = torch.full((N,), self.k_avg, device=x.device, dtype=torch.long)
+        k_tok = k_tok * real
+        C = self.capacity(N)
+        w, table, wtab, flat_idx, aux, dropped, _ = ops.route_and_slot(
+            xf, self.router.weight.float() if not x.is_cuda else self.router.weight, real, k_tok, self.k_max, self.E, C)
+        self.aux, self.dropped = aux, dropped
+        return xf, table, wtab, flat_idx, C
+
+    def forward(self, x, surprise=None):
+        xf, table, wtab, flat_idx, C = self._route(x, surprise)
+        N, d = xf.shape
+        xd = xf.to(_cdt(x))
+        xe = ops.slot_gather(xd, table, flat_idx).view(self.E, C, d)
+        ye = self._experts(xe, wtab, C)
+        out = ops.combine(ye.reshape(self.E * C, d), wtab.to(ye.dtype), flat_idx, table, N)
+        return x + out.view_as(x).to(x.dtype)
+
+    # ------------------------------------------------------------------------------------------ experts
+    def _ffn(self, xe, up, down, train_w=True):
+        return ops.expert_ffn(xe, up.to(xe.dtype) if up.dtype != xe.dtype else up,
+                              down.to(xe.dtype) if down.dtype != xe.dtype else down, self.act, train_w)
+
+    def _bank_weights(self, which):
+        """Frozen weights in bf16 (expanded from int8 / int4 storage) (full2.py:948-958)."""
+        q = getattr(self, which + "_f")
+        if not self.bank_q:
+            return q
+        sc = getattr(self, which + "_fs")
+        if self.bank_q == "int4":
+            Fn, K2, N = q.shape
+            q = torch.stack([(q << 4) >> 4, q >> 4], 2).reshape(Fn, K2 * 2 // 128, 128, N)
+            return (q.to(torch.bfloat16) * sc[:, :, None]).reshape(Fn, K2 * 2, N)
+        return q.to(torch.bfloat16) * sc
+
+    def _quantise(self, w):
+        """float (F, in, out) -> (stored, per-output-column scale) (full2.py:919-932)."""
+        if not self.bank_q:
+            return w.bfloat16().contiguous(), w.new_zeros(w.shape[0], 1, w.shape[2]).bfloat16()
+        if self.bank_q == "int8":
+            sc = (w.abs().amax(1, keepdim=True) / 127).clamp(min=1e-8)
+            return (w / sc).round().clamp(-127, 127).to(torch.int8).contiguous(), sc.bfloat16()
+        Fn, K, N = w.shape
+        wg = w.view(Fn, K // 128, 128, N)
+        sc = (wg.abs().amax(2, keepdim=True) / 7).clamp(min=1e-8)
+        q = (wg / sc).round().clamp(-7, 7).to(torch.int8).view(Fn, K, N)
+        q = ((q[:, 0::2] & 0x0F) | (q[:, 1::2] << 4)).to(torch.int8)
+        return q.contiguous(), sc[:, :, 0].bfloat16().contiguous()
+
+    def _ffn_frozen(self, xe):
+        return self._ffn(xe, self._bank_weights("up"), self._bank_weights("down"), train_w=False)
+
+    def _experts(self, xe, wtab, C):
+        if self.ep_W > 1:
+            ye = self.ep_engine.ffn(self, xe)
+        elif self.bank:
+            if not self.has_F:
+                ye = self._ffn(xe, self.up, self.down)
+            else:
+                ye = xe.new_zeros(xe.shape)
+                if self.has_L:
+                    ye = ye.index_copy(0, self.L_idx, self._ffn(xe[self.L_idx], self.up, self.down).to(ye.dtype))
+                ye = ye.index_copy(0, self.F_idx, self._ffn_frozen(xe[self.F_idx]).to(ye.dtype))
+        else:
+            up, down = self.up, self.down
+            if self.wave:
+                fr = self.learned[:, None, None]
+                up, down = torch.where(fr, up.detach(), up), torch.where(fr, down.detach(), down)
+            if self.n_frozen:
+                Ea = self.E - self.n_frozen
+                ye = torch.cat([self._ffn(xe[:Ea], up, down),
+                                self._ffn(xe[Ea:], self.up_f, self.down_f, train_w=False)])
+            else:
+                ye = self._ffn(xe, up, down)
+        if self.wave and self.training:
+            ye = _ErrProbe.apply(ye, self.err)
+            if not self.bank:
+                if self.hint_now:
+                    self.hint = self._hint(xe, ye, wtab.view(self.E, C))
+                    with torch.no_grad():
+                        self.hint_avg[0].mul_(0.9).add_(0.1 * self.hint.detach())
+                else:
+                    self.hint = torch.zeros((), device=xe.device)
+                self.aux = self.aux + self.hint_w * self.hint
+        return ye
+
+    def _hint(self, xe, ye, wt):
+        """A learned expert (teacher) briefly pulls its students' outputs towards its own on the students' worst
+        10 % of places (full2.py:604-619)."""
+        learned = self.learned
+        n_t = learned.sum()
+        order = (~learned).long().argsort(stable=True)
+        rank = (~learned).long().cumsum(0) - 1
+        teacher = order[(rank // self.students) % n_t.clamp(min=1)]
+        with torch.no_grad():
+            yt = self._ffn(xe, self.up[teacher], self.down[teacher], train_w=False)
+        diff = (ye.float() - yt.float()).pow(2).mean(-1) * (wt > 0)
+        k = max(1, diff.shape[1] // 10)
+        worst = diff.topk(k, dim=1).values.mean(1)
+        is_student = (~learned) & (n_t > 0)
+        return (worst * is_student).sum() / is_student.sum().clamp(min=1)
+
+    # ------------------------------------------------------------------------------------------ waves
+    @torch.no_grad()
+    def before_step(self, step):
+        """Once per step, device-only: who has learned / who is a student again (full2.py:621-643, 1176-1196)."""
+        if not self.wave:
+            return
+        if not self.bank:
+            self.up._frozen_rows = self.down._frozen_rows = self.learned
+            self.hint_now = step > 0 and step % self.wave_every == 0 and bool(self.training)
+        else:
+            self.hint_now = False
+        if step % self.wave_every or step < self.warm:
+            return
+        self.err_peak.copy_(torch.maximum(self.err_peak, self.err))
+        if self.wave == "err":
+            cand = self.err < self.err_thr * self.err_peak
+        else:
+            if self.bank:
+                move = torch.zeros(self.E, device=self.err.device)
+                if self.L:
+                    mL = ((self.up.float() - self.up_snap.float()).flatten(1).norm(dim=1)
+                          / (self.up_snap.float().flatten(1).norm(dim=1) + 1e-8))
+                    move = move.index_copy(0, self.L_idx, mL)
+                    self.up_snap.copy_(self.up)
+            else:
+                move = ((self.up - self.up_snap).flatten(1).norm(dim=1)
+                        / (self.up_snap.flatten(1).norm(dim=1) + 1e-8))
+            self.move_peak.copy_(torch.maximum(self.move_peak, torch.where(self.learned, 0.0, move)))
+            self.last_move.copy_(move)
+            cand = (move < 0.3 * self.move_peak) & ~self.learned
+            if self.bank:
+                in_L = torch.zeros(self.E, dtype=torch.bool, device=move.device).index_fill(0, self.L_idx, True)
+                cand &= in_L
+            else:
+                self.up_snap.copy_(self.up)
+        relearn = self.learned & (self.err > 1.5 * self.err_freeze)
+        newly = ~self.learned & cand
+        self.err_freeze.copy_(torch.where(newly, self.err, self.err_freeze))
+        self.learned.copy_((self.learned | newly) & ~relearn)
+
+    @torch.no_grad()
+    def wants_rebank(self, learned_cpu):
+        to_freeze = [e for e in self.L if learned_cpu[e]]
+        to_thaw = [e for e in self.Fz if not learned_cpu[e]]
+        return bool(to_thaw) or len(to_freeze) >= max(1, self.E // 4) or (bool(to_freeze) and len(to_freeze) == len(self.L))
+
+    @torch.no_grad()
+    def rebank(self, learned_cpu):
+        """Move experts between the learning and the frozen bank.  Returns [(old param, new param, slot map)] so
+        the optimizer can carry momentum of the experts that keep learning (full2.py:1206-1242)."""
+        to_freeze = {e for e in self.L if learned_cpu[e]}
+        to_thaw = {e for e in self.Fz if not learned_cpu[e]}
+        newL = sorted((set(self.L) - to_freeze) | to_thaw)
+        newF = sorted((set(self.Fz) - to_thaw) | to_freeze)
+        changes = []
+        for nm in ("up", "down"):
+            old = getattr(self, nm)
+            full = torch.empty(self.E, *old.shape[1:], device=old.device, dtype=torch.float32)
+            if self.L:
+                full[torch.tensor(self.L, device=old.device)] = old.detach().float()
+            if self.Fz:
+                full[torch.tensor(self.Fz, device=old.device)] = self._bank_weights(nm).float()
+            sel = torch.tensor(newL, device=old.device, dtype=torch.long)
+            new = nn.Parameter((full[sel] if newL else full[:0]).to(self.w_dtype).contiguous())
+            setattr(self, nm, new)
+            if newF:
+                q, sc = self._quantise(full[torch.tensor(newF, device=old.device, dtype=torch.long)])
+            else:
+                q, sc = getattr(self, nm + "_f")[:0], getattr(self, nm + "_fs")[:0]
+            setattr(self, nm + "_f", q)
+            setattr(self, nm + "_fs", sc)
+            changes.append((old, new, [self.L.index(e) if e in self.L else None for e in newL]))
+        self.set_banks(newL, newF)
+        return changes
+
+    def set_banks(self, L, Fz):
+        dv = self.up.device
+        self.L, self.Fz = list(L), list(Fz)
+        self.has_L, self.has_F = bool(L), bool(Fz)
+        self.L_idx = torch.tensor(self.L, device=dv, dtype=torch.long)
+        self.F_idx = torch.tensor(self.Fz, device=dv, dtype=torch.long)
+        self.up_snap = self.up.detach().clone()
+
+    def grow_bank(self, n_frozen, seed=0):
+        """Wave-trained layout used by the 48-expert benchmark config: append `n_frozen` random-init frozen bf16
+        experts to the bank; the router grows to E + n_frozen outputs."""
+        assert self.bank and not self.Fz
+        d = self.up.shape[1]
+        g = torch.Generator().manual_seed(seed)
+        E0, E1 = self.E, self.E + n_frozen
+        dv = self.up.device
+        self.up_f = (torch.randn(n_frozen, d, self.width_in, generator=g) * d ** -0.5).bfloat16().to(dv)
+        self.down_f = (torch.randn(n_frozen, self.width_out, d, generator=g) * self.width_out ** -0.5 * 0.5
+                       ).bfloat16().to(dv)
+        self.up_fs = torch.zeros(n_frozen, 1, self.width_in, dtype=torch.bfloat16, device=dv)
+        self.down_fs = torch.zeros(n_frozen, 1, d, dtype=torch.bfloat16, device=dv)
+        r = torch.cat([self.router.weight.detach(),
+                       (torch.randn(n_frozen, d, generator=g) * d ** -0.5).to(self.router.weight)])
+        self.router = nn.Linear(d, E1, bias=False).to(r.device)
+        with torch.no_grad():
+            self.router.weight.copy_(r)
+        for nm in ("err", "err_peak", "err_freeze", "move_peak", "last_move", "hint_avg"):
+            setattr(self, nm, torch.cat([getattr(self, nm), torch.zeros(n_frozen, device=dv)]))
+        self.learned = torch.cat([self.learned, torch.ones(n_frozen, dtype=torch.bool, device=dv)])
+        self.E = E1
+        self.set_banks(list(range(E0)), list(range(E0, E1)))
+
+    # ------------------------------------------------------------------------------------------ EP
+    def ep_shard(self, rank, W, engine):
+        """Keep only this rank's E/W learning experts; expert grads are sums over ranks, so the hook divides by W
+        (full2.py:1122-1135).  With a frozen bank the bank is sharded the same way (new capability: the
+        reference asserts `not has_F` here)."""
+        nL = len(self.L) if self.bank else self.up.shape[0]
+        assert nL % W == 0, "EP: learning experts must divide by the world size"
+        El = nL // W
+        sl = slice(rank * El, (rank + 1) * El) if self.up.shape[0] == nL else slice(0, El)
+        self.up = nn.Parameter(self.up.detach()[sl].to(self.w_dtype).clone())
+        self.down = nn.Parameter(self.down.detach()[sl].to(self.w_dtype).clone())
+        if self.bank and self.has_F:
+            nF = len(self.Fz)
+            assert nF % W == 0, "EP: frozen experts must divide by the world size"
+            Fl = nF // W
+            fs = slice(rank * Fl, (rank + 1) * Fl)
+            for nm in ("up_f", "down_f", "up_fs", "down_fs"):
+                setattr(self, nm, getattr(self, nm)[fs].clone())
+        if hasattr(self, "up_snap"):
+            self.up_snap = self.up.detach().clone()
+        self.ep_W, self.ep_rank, self.ep_engine = W, rank, engine
+        for p in (self.up, self.down):
+            p.register_hook(lambda g, W=W: g / W)
+            p._ep_local = True

@@ -1,0 +1,93 @@
+"""Causal / sliding-window attention with RoPE for the light and final blocks.
+
+Reference behaviour: `F.scaled_dot_product_attention(rope(q), rope(k), v, is_causal=True)` when the text fits the
+window (full.py:156-157); block-masked window attention `kv <= q and q - kv < window` otherwise (FlexAttention with
+an O(T) block list, full2.py:153-181; two-block variants lm.py:448-554).
+
+GPU body: `rope_qk` kernel (in-place rotation of the q and k thirds of the packed qkv activations, inverse rotation
+in backward) followed by the window-attention kernels `attn_fwd` / `attn_bwd` (block list from window arithmetic,
+no mask tensor, exact LSE).  `MEMARCH_ATTN=lib` swaps the attention core for the library flash kernel (A/B timing).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext, ref
+
+ATTN_CORE = os.environ.get("MEMARCH_ATTN", "own")
+
+
+class _RopeQK(torch.autograd.Function):
+    """Rotate the q and k slices of qkv (B,T,3,H,hd); v passes through.  Backward rotates the grads back."""
+
+    @staticmethod
+    def forward(ctx, qkv, half):
+        ctx.half = half
+        _ext.count()
+        return _ext.C().rope_qk(qkv.contiguous(), 1.0, bool(half))
+
+    @staticmethod
+    def backward(ctx, g):
+        _ext.count()
+        return _ext.C().rope_qk(g.contiguous(), -1.0, bool(ctx.half)), None
+
+
+class _OwnAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, window):
+        C = _ext.C()
+        o, lse = C.attn_fwd(qkv, int(window))
+        _ext.count()
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.window = int(window)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse = ctx.saved_tensors
+        dqkv = _ext.C().attn_bwd(do.contiguous(), qkv, o, lse, ctx.window)
+        _ext.count(3)
+        return dqkv, None
+
+
+def _lib_window(q, k, v, window):
+    """Two-block dense-mask window attention through SDPA: each block of `window` queries sees itself and the
+    previous block (2·window keys); linear cost in T."""
+    B, H, T, D = q.shape
+    W = window
+    nb = -(-T // W)
+    pad = nb * W - T
+    if pad:
+        q, k, v = (F.pad(t, (0, 0, 0, pad)) for t in (q, k, v))
+    qb, kb, vb = (t.reshape(B, H, nb, W, D) for t in (q, k, v))
+    prev = lambda t: torch.cat([torch.zeros_like(t[:, :, :1]), t[:, :, :-1]], 2)
+    kk, vv = torch.cat([prev(kb), kb], 3), torch.cat([prev(vb), vb], 3)
+    i = torch.arange(W, device=q.device)[:, None]
+    j = torch.arange(2 * W, device=q.device)[None]
+    ok = (j > i) & (j <= i + W)
+    first = torch.arange(nb, device=q.device)[:, None, None] > 0
+    mask = ok[None] & (first | (j >= W)[None])
+    qb, kk, vv = qb.reshape(B, H * nb, W, D), kk.reshape(B, H * nb, 2 * W, D), vv.reshape(B, H * nb, 2 * W, D)
+    mask = mask[None].expand(H, nb, W, 2 * W).reshape(1, H * nb, W, 2 * W)
+    out = F.scaled_dot_product_attention(qb, kk, vv, attn_mask=mask)
+    return out.reshape(B, H, nb * W, D)[:, :, :T]
+
+
+def attention(qkv, window=None, rope_half=False, qk_norm=False):
+    """qkv (B,T,3,H,hd) -> (B,T,H·hd).  `window` None or >= T means plain causal."""
+    B, T, _, H, hd = qkv.shape
+    win = None if (window is None or window >= T) else int(window)
+    if _ext.use_cuda(qkv) and qkv.dtype == torch.bfloat16 and not qk_norm and hd % 8 == 0:
+        r = _RopeQK.apply(qkv, rope_half)
+        if ATTN_CORE == "own" and hd in (64, 128):
+            o = _OwnAttn.apply(r, win if win is not None else 0)
+            return o.reshape(B, T, H * hd)
+        q, k, v = (r[:, :, i].transpose(1, 2) for i in range(3))
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _lib_window(q, k, v, win)
+        return o.transpose(1, 2).reshape(B, T, H * hd)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    o = ref.window_attention(q, k, v, win, rope_half, qk_norm=qk_norm)
+    return o.reshape(B, T, H * hd)

@@ -1,0 +1,153 @@
+"""Normalisation, activation and GEMM-shaped ops: autograd wrappers over the sm_100a kernels.
+
+CUDA tensors take the hand-written kernels in `csrc/` (RMSNorm, relu², SwiGLU, tcgen05 GEMM); CPU tensors take the
+PyTorch statement in `ref.py`.  Reference behaviour: `nn.RMSNorm` + bf16 autocast linears of the light blocks
+(baseline.py:35-52, full.py:140-182), Triton SwiGLU (fused_ops.py:175-228), `_Relu2` (full.py:98-110).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext, ref
+
+# Which library multiplies the *plain* linears (qkv/o/up/down of the light blocks).  The fused paths (experts,
+# output head, attention, optimizer) always run this package's kernels.  "tc" = our tcgen05 GEMM, "lib" = cuBLAS.
+PLAIN_GEMM = os.environ.get("MEMARCH_PLAIN_GEMM", "tc")
+
+
+# ------------------------------------------------------------------------------------------------ RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, out_bf16):
+        C = _ext.C()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y, rstd = C.rmsnorm_fwd(x2, w.contiguous(), float(eps), bool(out_bf16))
+        _ext.count()
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        C = _ext.C()
+        dx, dw = C.rmsnorm_bwd(dy.reshape(x2.shape).contiguous(), x2, w.contiguous(), rstd)
+        _ext.count(2)
+        return dx.view(ctx.shape), dw.to(w.dtype), None, None
+
+
+def rmsnorm(x, weight, eps=None, out_dtype=None):
+    """RMSNorm in fp32 with one cast of the result.  `out_dtype` None keeps fp32 (CPU oracle) / x dtype."""
+    if eps is None:
+        eps = torch.finfo(torch.float32).eps if x.dtype in (torch.bfloat16, torch.float32) else torch.finfo(x.dtype).eps
+    if _ext.use_cuda(x) and x.dtype in (torch.float32, torch.bfloat16) and x.shape[-1] % 8 == 0:
+        want_bf16 = (out_dtype or x.dtype) == torch.bfloat16
+        return _RMSNorm.apply(x, weight, eps, want_bf16)
+    y = ref.rmsnorm(x, weight, eps)
+    return y.to(out_dtype or x.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ activations
+class _Relu2(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a):
+        ctx.save_for_backward(a)
+        _ext.count()
+        return _ext.C().relu2_fwd(a.contiguous())
+
+    @staticmethod
+    def backward(ctx, dh):
+        a, = ctx.saved_tensors
+        _ext.count()
+        return _ext.C().relu2_bwd(dh.contiguous(), a.contiguous())
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        _ext.count()
+        return _ext.C().swiglu_fwd(gu.contiguous())
+
+    @staticmethod
+    def backward(ctx, dh):
+        gu, = ctx.saved_tensors
+        _ext.count()
+        return _ext.C().swiglu_bwd(dh.contiguous(), gu.contiguous())
+
+
+def relu2(a):
+    if _ext.use_cuda(a) and a.dtype == torch.bfloat16:
+        return _Relu2.apply(a)
+    return ref.relu2(a)
+
+
+def swiglu(gu):
+    if _ext.use_cuda(gu) and gu.dtype == torch.bfloat16 and gu.shape[-1] % 16 == 0:
+        return _SwiGLU.apply(gu)
+    return ref.swiglu(gu)
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, accumulate=False, epi=0,
+         aux=None, out2=None, groups=1):
+    """C[g] = A[g] · B[g]ᵀ on the tcgen05 tensor cores (bf16 in, fp32 accumulate in TMEM).
+
+    Logical shapes per group: A (M,K), B (N,K), C (M,N).  Storage: an operand that is K-major is stored
+    (rows, K) with K contiguous; `a_mn`/`b_mn` say the operand is stored (K, rows) with rows contiguous
+    ("MN-major"), which is how a transposed view of a row-major matrix is fed without a transposing copy.
+    `epi`: 0 plain, 1 relu² (out = relu(acc)², out2 = acc), 2 multiply by 2·relu(aux) (relu² backward),
+    3 SwiGLU over column halves (B rows [n, H+n]), 4 per-row scale by aux (fp32 vector).
+    """
+    C = _ext.C()
+    _ext.count()
+    return C.gemm(a, b, out, out2, aux, bool(a_mn), bool(b_mn), bool(accumulate), int(epi),
+                  out_dtype == torch.float32, int(groups))
+
+
+def gemm_ok(M, N, K):
+    """Shapes the TMA descriptors accept: 16-byte row pitches (multiples of 8 bf16 elements)."""
+    return K % 8 == 0 and N % 8 == 0 and M % 8 == 0 and K >= 16
+
+
+class _Linear(torch.autograd.Function):
+    """y = x · Wᵀ with W (out, in) bf16.  dx = dy · W (B operand MN-major), dW = dyᵀ · x (both MN-major)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return gemm(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, b_mn=True)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy, x, a_mn=True, b_mn=True)
+        return dx, dw
+
+
+def linear(x, w, dtype=None):
+    """x (..., in) times W (out, in)ᵀ in `dtype` (bf16 on the GPU, the tensors' own dtype on CPU)."""
+    if _ext.use_cuda(x):
+        dt = dtype or torch.bfloat16
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != dt:
+            x2 = x2.to(dt)
+        wd = w if w.dtype == dt else w.to(dt)
+        M, K = x2.shape
+        N = wd.shape[0]
+        if PLAIN_GEMM == "tc" and dt == torch.bfloat16 and gemm_ok(M, N, K) and M >= 128:
+            y = _Linear.apply(x2.contiguous(), wd.contiguous())
+        else:
+            y = F.linear(x2, wd)
+        return y.view(*x.shape[:-1], N)
+    if dtype is not None and dtype != x.dtype:
+        return F.linear(x.to(dtype), w.to(dtype))
+    return F.linear(x, w.to(x.dtype))

@@ -1,0 +1,157 @@
+"""MoE data movement and expert FFN ops.
+
+Reference behaviour: capacity slotting by cumulative rank, slot table gather `xpad[table]`, `bmm` experts with
+SwiGLU or relu², weighted `index_add` combine (full2.py:532-602, 1102-1110), and the gather-only inverse pair
+`_SlotGather` / `_CombineW` (full2.py:283-328) whose backward needs no scatter-add.
+
+GPU bodies: `gather_rows` (slot <- token, optional per-row scale), `gather_sum_rows` (token <- its k slots, weighted,
+fp32 accumulate), `row_dot` (slot-weight grads) and the grouped tcgen05 GEMMs with the activation in the epilogue.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _ext, ref
+from .basic import gemm, gemm_ok, relu2, swiglu
+
+
+# ------------------------------------------------------------------------------------------------ dispatch
+class _SlotGather(torch.autograd.Function):
+    """xe[s] = x[table[s]] (empty slot -> 0).  Backward: dx[n] = Σ_j dxe[flat_idx[n, j]] in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, table, flat_idx):
+        ctx.save_for_backward(table, flat_idx)
+        ctx.N = x.shape[0]
+        if _ext.use_cuda(x):
+            _ext.count()
+            return _ext.C().gather_rows(x.contiguous(), table, None)
+        N = x.shape[0]
+        m = (table < N)[:, None]
+        return torch.where(m, x[table.clamp(max=N - 1)], x.new_zeros(()))
+
+    @staticmethod
+    def backward(ctx, g):
+        table, fi = ctx.saved_tensors
+        if _ext.use_cuda(g):
+            _ext.count()
+            return _ext.C().gather_sum_rows(g.contiguous(), fi, None, ctx.N), None, None
+        EC = g.shape[0]
+        mk = (fi < EC)[..., None]
+        dx = torch.where(mk, g[fi.clamp(max=EC - 1)], g.new_zeros(())).float().sum(1).to(g.dtype)
+        return dx, None, None
+
+
+class _CombineW(torch.autograd.Function):
+    """out[n] = Σ_j ye[fi[n,j]] · wtab[fi[n,j]] (fp32 sum).  Backward: dye[s] = wtab[s]·go[table[s]],
+    dwtab[s] = <go[table[s]], ye[s]>."""
+
+    @staticmethod
+    def forward(ctx, ye, wtab, fi, table, N):
+        ctx.save_for_backward(ye, wtab, fi, table)
+        ctx.N = N
+        if _ext.use_cuda(ye):
+            _ext.count()
+            return _ext.C().gather_sum_rows(ye.contiguous(), fi, wtab.float().contiguous(), N)
+        EC = ye.shape[0]
+        c = fi.clamp(max=EC - 1)
+        mk = fi < EC
+        wg = torch.where(mk, wtab[c], wtab.new_zeros(()))
+        return (ye[c].float() * wg[..., None].float()).sum(1).to(ye.dtype)
+
+    @staticmethod
+    def backward(ctx, go):
+        ye, wtab, fi, table = ctx.saved_tensors
+        N = ctx.N
+        if _ext.use_cuda(go):
+            C = _ext.C()
+            go = go.contiguous()
+            dye = C.gather_rows(go, table, wtab.float().contiguous())
+            dw = C.row_dot(go, table, ye.contiguous())
+            _ext.count(2)
+            return dye, dw.to(wtab.dtype), None, None, None
+        m = (table < N)[:, None]
+        gs = torch.where(m, go[table.clamp(max=N - 1)], go.new_zeros(()))
+        dye = (gs.float() * wtab[:, None].float()).to(ye.dtype)
+        dw = (gs.float() * ye.float()).sum(-1).to(wtab.dtype)
+        return dye, dw, None, None, None
+
+
+def slot_gather(x, table, flat_idx):
+    return _SlotGather.apply(x, table, flat_idx)
+
+
+def combine(ye, wtab, flat_idx, table, N):
+    return _CombineW.apply(ye, wtab, flat_idx, table, N)
+
+
+# ------------------------------------------------------------------------------------------------ expert FFN
+class _ExpertFFN(torch.autograd.Function):
+    """(E,C,d) -> relu²/SwiGLU FFN -> (E,C,d) on grouped tcgen05 GEMMs, activation in the up-GEMM epilogue.
+
+    `train_w` False (frozen bank) skips both weight-gradient GEMMs.
+    """
+
+    @staticmethod
+    def forward(ctx, xe, up, down, act, train_w):
+        E, Cn, d = xe.shape
+        xe = xe.contiguous()
+        if act == "relu2":
+            H = up.shape[2]
+            h = torch.empty(E, Cn, H, device=xe.device, dtype=torch.bfloat16)
+            a = torch.empty_like(h)
+            gemm(xe, up, b_mn=True, out=h, out2=a, epi=1, groups=E)
+        else:
+            a = gemm(xe, up, b_mn=True, groups=E)
+            h = _ext.C().swiglu_fwd(a)
+            _ext.count()
+        y = gemm(h, down, b_mn=True, groups=E)
+        ctx.save_for_backward(xe, up, down, a, h)
+        ctx.act, ctx.train_w = act, train_w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xe, up, down, a, h = ctx.saved_tensors
+        E = xe.shape[0]
+        dy = dy.contiguous()
+        if ctx.act == "relu2":
+            da = gemm(dy, down, epi=2, aux=a, groups=E)                       # dh · 2relu(a)
+        else:
+            dh = gemm(dy, down, groups=E)
+            da = _ext.C().swiglu_bwd(dh, a)
+            _ext.count()
+        dxe = gemm(da, up, groups=E) if ctx.needs_input_grad[0] else None
+        dup = ddown = None
+        if ctx.train_w:
+            ddown = gemm(h, dy, a_mn=True, b_mn=True, groups=E)
+            dup = gemm(xe, da, a_mn=True, b_mn=True, groups=E)
+        return dxe, dup, ddown, None, None
+
+
+def expert_ffn(xe, up, down, act="swiglu", train_w=True):
+    """xe (E,C,d); up (E,d,H); down (E,H',d).  bf16 on the GPU; CPU: plain bmm in the input dtype."""
+    E, Cn, d = xe.shape
+    if (_ext.use_cuda(xe) and xe.dtype == torch.bfloat16 and up.dtype == torch.bfloat16
+            and gemm_ok(Cn if Cn % 8 == 0 else 8, up.shape[2], d) and down.shape[1] % 8 == 0):
+        return _ExpertFFN.apply(xe, up, down, act, train_w and up.requires_grad)
+    h = torch.bmm(xe, up.to(xe.dtype))
+    h = relu2(h) if act == "relu2" else swiglu(h)
+    return torch.bmm(h, down.to(xe.dtype))
+
+
+# ------------------------------------------------------------------------------------------------ routing
+def route_and_slot(xf, router_w, real, k_tok, k_max, E, C):
+    """Router + capacity slotting.  Returns (w (N,k), table, wtab, flat_idx, aux, dropped, probs)."""
+    probs, top_e, keep, w, e_flat, aux = ref.moe_route(xf, router_w, real, k_tok, k_max, E)
+    with torch.no_grad():
+        if _ext.use_cuda(xf):
+            table, flat_idx, dropped = _ext.C().moe_slots(e_flat.contiguous(), int(E), int(C))
+            _ext.count()
+        else:
+            table, _, flat_idx, dropped = ref.moe_slots(e_flat, w.detach(), E, C)
+    ok = flat_idx < E * C
+    # slot weights as a differentiable gather-free scatter: wtab[flat_idx[n,j]] = w[n,j]
+    wtab = torch.zeros(E * C + 1, device=xf.device, dtype=w.dtype).scatter(
+        0, flat_idx.reshape(-1), (w * ok).reshape(-1))[:-1]
+    return w, table, wtab, flat_idx, aux, dropped, probs

@@ -1,0 +1,342 @@
+"""Instinct: a one-momentum optimizer whose step is scaled by loss surprise per "situation card", with
+homeostasis normalisation (row -> column -> row) of the update, applied to each weight the moment its gradient is
+ready inside backward.  No value ever travels to the host.
+
+API and state names follow the reference's `InstinctOptB` (exp_opt.py:428-729) so its checkpoints load:
+`prepare(loss, situation)` -> `update(p)` per parameter (from the grad-ready hook) or `update_all()` ->
+`finish()`; `swap(old, new, slot_map)` after a re-bank.  State: `m` (per-parameter momentum, fp32 or bf16), `w` (exact
+fp32 copy of bf16 weights), `gain (K,P)`, `keys (K,d)`, `used`, `expect`, `seen`, `rel (P,)`, `k, s, stake, g, oh`,
+`cs` (lagged second-axis mean squares), `n_step`.
+
+Step kinds by shape (exp_opt.py:653-665): 2-D tables with >= 10 000 rows -> "vocab" (row-rms, only rows with a
+non-zero gradient move, no weight decay); 2-D -> "hs"; 3-D experts (E, in, out) -> "hs3" (norm over in, out, in);
+everything else -> "tensor".  With norm="row"/"tensor"/"hs<n>" the reference's other kinds apply.
+
+GPU body: `instinct_stat` / `instinct_apply` kernels (csrc/instinct.cu): fp32 math, weight decay, optional
+counter-hash stochastic rounding of bf16 stores, |g|/|w| every `rel_every` steps.  CPU body: `ops.ref`.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from ..config import OptConfig
+from ..ops import _ext, ref
+
+
+def _kind_code(kind):
+    return {"tensor": 0, "row": 1, "row3": 2, "vocab": 3, "hs": 4, "hs3": 5}.get(kind, -1)
+
+
+class Instinct:
+    def __init__(self, params, cfg: OptConfig = None, d_sit=None, **kw):
+        cfg = cfg or OptConfig()
+        if kw:
+            import dataclasses
+            cfg = dataclasses.replace(cfg, **{k: v for k, v in kw.items() if k in OptConfig.__dataclass_fields__})
+        self.cfg = cfg
+        self.m_dtype = torch.bfloat16 if cfg.m_bf16 else torch.float32
+        self.rel_every, self.n_step = cfg.rel_every, 0
+        self.plist = list(params)
+        self.idx = {id(p): i for i, p in enumerate(self.plist)}
+        self.param_groups = [dict(lr=cfg.lr, weight_decay=cfg.weight_decay)]
+        self.K, self.beta, self.new_card, self.ema = cfg.cards, cfg.beta, cfg.new_card, cfg.ema
+        self.good, self.bad, self.top, self.relax = cfg.good, cfg.bad, cfg.top, cfg.relax
+        self.scale, self.norm = cfg.scale, cfg.norm
+        self.lr_peak = cfg.lr_peak or cfg.lr
+        self.hs_lag, self.sr = cfg.hs_lag, cfg.sr
+        dev = self.plist[0].device
+        P = len(self.plist)
+        self.gain = torch.ones(cfg.cards, P, device=dev)
+        self.keys = None
+        self.used = torch.zeros(cfg.cards, dtype=torch.bool, device=dev)
+        self.expect = torch.zeros(cfg.cards, device=dev)
+        self.seen = torch.zeros(cfg.cards, device=dev)
+        self.rel = torch.zeros(P, device=dev)
+        self.m = [torch.zeros_like(p, dtype=self.m_dtype) for p in self.plist]
+        self.w = [p.detach().float().clone() if (p.dtype == torch.bfloat16 and not cfg.no_master) else None
+                  for p in self.plist]
+        self.cs = [None] * P
+        self.k = torch.zeros((), dtype=torch.long, device=dev)
+        self.s = torch.zeros((), device=dev)
+        self.stake = torch.zeros((), device=dev)
+        self.g = torch.ones(P, device=dev)
+        self.oh = torch.zeros(cfg.cards, device=dev)
+        self._lr_t = torch.zeros((), device=dev)
+        self._lr_v = torch.zeros((), device=dev)
+        self._lr_ratio = torch.zeros((), device=dev)
+        self._seed_t = torch.zeros((), dtype=torch.int64, device=dev)
+        self._lr_last = None
+        self.rows = {}
+        self._scratch = {}
+        self.grad_sync = None          # set by the data-parallel engine: called as grad_sync(p, grad) -> grad
+
+    # ------------------------------------------------------------------------------------------ card logic
+    @torch.no_grad()
+    def prepare(self, loss, situation):
+        """Pick the situation card, its expectation and the surprise of this step's loss (exp_opt.py:349-372)."""
+        sit = F.normalize(situation.float().flatten(), dim=0)
+        if self.keys is None:
+            self.keys = torch.zeros(self.K, sit.numel(), device=sit.device)
+        self._sync_lr()
+        used = self.used
+        best_sim, best = (self.keys @ sit).masked_fill(~used, -2).max(0)
+        free = ~used
+        first_free = free.int().argmax()
+        newer = (best_sim < self.new_card) & free.any()
+        k = torch.where(~used.any(), torch.zeros_like(best), torch.where(newer, first_free, best))
+        oh = F.one_hot(k, self.K).float()
+        was = (oh * used).sum() > 0
+        key_k = oh @ self.keys
+        new_key = torch.where(was, F.normalize(0.95 * key_k + 0.05 * sit, dim=0), sit)
+        self.keys.add_(oh[:, None] * (new_key - key_k)[None])
+        self.used.copy_(used | oh.bool())
+        loss = loss.detach().float()
+        e = torch.where((oh * self.seen).sum() > 0, (oh * self.expect).sum(), loss)
+        self.s = (e - loss) / e.clamp(min=1e-6)
+        self.expect.add_(oh * (self.ema * e + (1 - self.ema) * loss - self.expect))
+        self.seen.add_(oh * (1 - self.seen))
+        self.stake = (4 * self.s.abs() + 0.5 * self._lr_ratio).clamp(max=1.0)
+        self.k, self.oh = k, oh
+        self.g = oh @ self.gain
+
+    @torch.no_grad()
+    def finish(self):
+        """The instinct learns: gains of the card move by the outcome of the step (exp_opt.py:375-383)."""
+        self.n_step += 1
+        s, gk = self.s, self.g.clone()
+        culprit = (self.rel >= self.rel.quantile(1 - self.top)).float()
+        gk += torch.where(s < 0, culprit * self.bad * (-s * 10).clamp(max=1), torch.zeros_like(gk))
+        gk += torch.where(s > 0, self.good * (s * 10).clamp(max=1) * (1 - gk), torch.zeros_like(gk))
+        gk += self.relax * (1 - gk)
+        gk = gk.clamp(0.5, 3.0)
+        self.gain.add_(self.oh[:, None] * (gk / gk.mean() - self.gain))
+
+    def _sync_lr(self):
+        lr = self.param_groups[0]["lr"]
+        if self._lr_last != lr:
+            self._lr_t.fill_(lr * self.scale)
+            self._lr_v.fill_(lr * self.scale * self.cfg.vocab_lr_mul)
+            self._lr_ratio.fill_(lr / self.lr_peak)
+            self._lr_last = lr
+
+    # ------------------------------------------------------------------------------------------ per-weight step
+    def spec(self, p):
+        """(kind, has weight decay, is a word table) from the weight's shape (exp_opt.py:653-665)."""
+        vocab_table = p.dim() == 2 and p.shape[0] >= 10000
+        n = self.norm
+        if vocab_table:
+            kind = "vocab"
+        elif n == "row" and p.dim() == 3:
+            kind = "row3"
+        elif n.startswith("hs") and n != "hs" and p.dim() == 3:
+            kind = n.replace("hs", "hsn") + "e"
+        elif n.startswith("hs") and n != "hs" and p.dim() == 2:
+            kind = n.replace("hs", "hsn")
+        elif n == "hs" and p.dim() == 3:
+            kind = "hs3"
+        elif n == "hs" and p.dim() == 2:
+            kind = "hs"
+        elif (n in ("row", "row_old") or n.startswith("hs")) and p.dim() >= 2:
+            kind = "row"
+        else:
+            kind = "tensor"
+        wd = bool(self.param_groups[0]["weight_decay"]) and p.dim() >= 2 and not vocab_table
+        return kind, wd, vocab_table
+
+    @torch.no_grad()
+    def update(self, p, grad=None):
+        """One Instinct step of one weight; called from the weight's grad-ready hook."""
+        i = self.idx[id(p)]
+        grad = p.grad if grad is None else grad
+        if grad is None:
+            return
+        if self.grad_sync is not None:
+            grad = self.grad_sync(p, grad)
+        self._sync_lr()
+        kind, wd, vocab = self.spec(p)
+        want_rel = self.n_step % self.rel_every == 0
+        lr_t = self._lr_v if vocab else self._lr_t
+        wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
+        rows = self.rows.get(id(p)) if vocab else None
+        if rows is not None:
+            self._update_rows(i, p, grad, rows, lr_t)
+            if want_rel:
+                self.rel[i] = 0.0
+            return
+        if _ext.use_cuda(p) and _kind_code(kind) >= 0 and p.is_contiguous() and grad.is_contiguous():
+            self._update_cuda(i, p, grad, kind, wd_v, lr_t, want_rel)
+        else:
+            self._update_ref(i, p, grad, kind, wd_v, lr_t, want_rel)
+
+    def _frozen_mask(self, p):
+        fr = getattr(p, "_frozen_rows", None)
+        return fr
+
+    def _update_ref(self, i, p, grad, kind, wd, lr_t, want_rel):
+        m, w = self.m[i], self.w[i]
+        grad = grad.float()
+        mf = m.float() * self.beta + grad * (1 - self.beta)
+        if self.sr and m.dtype == torch.bfloat16:
+            self._seed_t.add_(1)
+            r_m, r_w = ref.sr_counter(mf.numel(), int(self._seed_t) * 1000003 + i, mf.device)
+            m.copy_(ref.sr_bf16(mf.reshape(-1), r_m).view_as(m))
+        else:
+            m.copy_(mf)
+            r_w = None
+        cs = None
+        if self.hs_lag and kind in ("hs", "hs3"):
+            if self.cs[i] is None:
+                shp = (1, p.shape[1]) if kind == "hs" else (p.shape[0], p.shape[1], 1)
+                self.cs[i] = torch.zeros(shp, device=p.device, dtype=torch.float32)
+            cs = self.cs[i]
+        upd, new_cs = ref.instinct_direction(mf, grad, kind, cs)
+        if new_cs is not None:
+            self.cs[i].copy_(new_cs)
+        t = p if w is None else w
+        if want_rel:
+            self.rel[i] = grad.norm() / (t.norm().float() + 1e-8)
+        eff = 1 + (self.g[i] - 1) * self.stake
+        fr = self._frozen_mask(p)
+        keep = t.detach().clone() if fr is not None else None
+        if self.sr and w is None and t.dtype == torch.bfloat16:
+            new = t.float()
+            if wd:
+                new = new * (1 - lr_t * wd)
+            new = new - upd * (lr_t * eff)
+            if r_w is None:
+                self._seed_t.add_(1)
+                _, r_w = ref.sr_counter(new.numel(), int(self._seed_t) * 1000003 + i, new.device)
+            t.copy_(ref.sr_bf16(new.reshape(-1), r_w).view_as(t))
+        else:
+            if wd:
+                t.mul_(1 - lr_t * wd)
+            t.sub_((upd * (lr_t * eff)).to(t.dtype))
+        if keep is not None:
+            t.copy_(torch.where(fr.view(-1, *[1] * (t.dim() - 1)), keep, t))
+        if w is not None:
+            p.copy_(w)
+
+    def _update_cuda(self, i, p, grad, kind, wd, lr_t, want_rel):
+        C = _ext.C()
+        m, w = self.m[i], self.w[i]
+        if self.hs_lag and kind in ("hs", "hs3") and self.cs[i] is None:
+            shp = (1, p.shape[1]) if kind == "hs" else (p.shape[0], p.shape[1], 1)
+            self.cs[i] = torch.zeros(shp, device=p.device, dtype=torch.float32)
+        if self.sr:
+            self._seed_t.add_(1)
+        fr = self._frozen_mask(p)
+        n = C.instinct_step(p, grad, m, w, self.cs[i] if self.hs_lag else None, self.g, int(i), self.stake, lr_t,
+                            self.rel if want_rel else None, float(self.beta), float(wd), _kind_code(kind),
+                            bool(self.sr), self._seed_t, fr)
+        _ext.count(int(n))
+
+    def _update_rows(self, i, p, grad, rows, lr_t):
+        """Word / phrase tables: only rows used in this step move (exp_opt.py:306-318)."""
+        m, w = self.m[i], self.w[i]
+        g = grad[rows].float()
+        mr = m[rows].float() * self.beta + g * (1 - self.beta)
+        m[rows] = mr.to(m.dtype)
+        upd = mr / (mr.pow(2).mean(1, keepdim=True).sqrt() + 1e-8)
+        t = p if w is None else w
+        t[rows] = t[rows] - (upd * (lr_t * (1 + (self.g[i] - 1) * self.stake))).to(t.dtype)
+        if w is not None:
+            p[rows] = w[rows].to(p.dtype)
+
+    @torch.no_grad()
+    def update_all(self):
+        """Step every weight that holds a gradient (after backward; used with sharded gradients)."""
+        for p in self.plist:
+            if p.grad is not None:
+                self.update(p)
+                p.grad = None
+
+    @torch.no_grad()
+    def swap(self, old, new, slot_map):
+        """Experts moved between banks: the new parameter takes the old one's slot; momentum (and the exact fp32
+        copy) of experts that keep learning is carried by position (exp_opt.py:711-725)."""
+        i = self.idx.pop(id(old))
+        self.plist[i] = new
+        self.idx[id(new)] = i
+        m = torch.zeros_like(new, dtype=self.m_dtype)
+        w = new.detach().float().clone() if (new.dtype == torch.bfloat16 and not self.cfg.no_master) else None
+        for j, s in enumerate(slot_map):
+            if s is not None:
+                m[j] = self.m[i][s]
+                if w is not None and self.w[i] is not None:
+                    w[j] = self.w[i][s]
+        self.m[i], self.w[i] = m, w
+        self.cs[i] = None
+
+    @property
+    def last(self):
+        return dict(card=self.k, s=self.s, stake=self.stake)
+
+    # ------------------------------------------------------------------------------------------ checkpoint blob
+    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch"}
+
+    def state_dict(self):
+        out = {}
+        for k, v in vars(self).items():
+            if k in self._SKIP:
+                continue
+            if torch.is_tensor(v):
+                out[k] = v.detach().cpu()
+            elif isinstance(v, list) and all(torch.is_tensor(t) or t is None for t in v):
+                out[k] = [None if t is None else t.detach().cpu() for t in v]
+            elif isinstance(v, (int, float, bool, str)) or v is None:
+                out[k] = v
+        out["_lr"] = self.param_groups[0]["lr"]
+        return out
+
+    def load_state_dict(self, sd):
+        dev = self.plist[0].device
+        for k, v in sd.items():
+            if k == "_lr":
+                self.param_groups[0]["lr"] = v
+            elif torch.is_tensor(v):
+                cur = getattr(self, k, None)
+                if torch.is_tensor(cur) and cur.shape == v.shape:
+                    cur.copy_(v.to(cur.device))
+                else:
+                    setattr(self, k, v.to(dev))
+            elif isinstance(v, list):
+                cur = getattr(self, k, None)
+                new = []
+                for j, t in enumerate(v):
+                    if t is None:
+                        new.append(None)
+                    elif cur is not None and j < len(cur) and torch.is_tensor(cur[j]) and cur[j].shape == t.shape:
+                        cur[j].copy_(t.to(cur[j].device))
+                        new.append(cur[j])
+                    else:
+                        new.append(t.to(self.plist[j].device if j < len(self.plist) else dev))
+                setattr(self, k, new)
+            elif k in ("n_step", "rel_every"):
+                setattr(self, k, v)
+        self._lr_last = None
+
+
+class SurpriseAdamW(torch.optim.AdamW):
+    """AdamW whose step is rescaled by the loss surprise (surprise_opt.py:1-47): the update of a step whose loss
+    beats its running expectation is amplified, a worse-than-expected step is damped."""
+
+    def __init__(self, params, lr=1e-3, ema=0.98, strength=1.0, lo=0.5, hi=2.0, **kw):
+        super().__init__(params, lr=lr, **kw)
+        self.ema, self.strength, self.lo, self.hi = ema, strength, lo, hi
+        self.expect = None
+
+    @torch.no_grad()
+    def step(self, loss=None):
+        if loss is None:
+            return super().step()
+        loss = float(loss)
+        e = loss if self.expect is None else self.expect
+        s = (e - loss) / max(e, 1e-6)
+        self.expect = self.ema * e + (1 - self.ema) * loss
+        mul = min(self.hi, max(self.lo, 1 + self.strength * s))
+        before = [[p.detach().clone() for p in g["params"]] for g in self.param_groups]
+        super().step()
+        for g, bs in zip(self.param_groups, before):
+            for p, b in zip(g["params"], bs):
+                p.copy_(b + (p - b) * mul)

@@ -1,0 +1,204 @@
+"""Trainer: one training step with no host synchronisation, weights updated inside backward.
+
+Stage letters follow the reference (fastloop.py:1-13, 217-497): `A` tokens resident on the device and no per-step
+host sync; `B` each weight is stepped from its grad-ready hook on the last micro-batch; `X` the Instinct optimizer
+(with `B`: device-only `prepare -> update -> finish`); `S` SurpriseAdamW; `C` micro-batches forward on separate
+CUDA streams with one backward; `G` the step is replayed as a CUDA graph.  Without `B` gradients are clipped to 1.0.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from ..config import OptConfig, TrainConfig
+from ..optim.instinct import Instinct, SurpriseAdamW
+
+
+def lr_at(step, cfg: TrainConfig):
+    """Warm-up then cosine to 0.1·lr, or WSD: flat, then linear to `lr_floor` over the last `wsd_frac` of steps
+    (fastloop.py:52-60)."""
+    up = min(1, (step + 1) / max(cfg.warmup, 1))
+    if cfg.lr_sched == "wsd":
+        d0 = (1 - cfg.wsd_frac) * cfg.steps
+        if step < d0:
+            return cfg.lr * up
+        return cfg.lr * up * (1 - (1 - cfg.lr_floor) * min(1, (step - d0) / max(cfg.steps - d0, 1e-9)))
+    return cfg.lr * up * (0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * min(1, step / max(cfg.steps, 1)))))
+
+
+def cast_linear_weights(model, dtype=torch.bfloat16):
+    """Linear weights (outside memory / reread, which stay fp32 on purpose) live in `dtype`; the optimizer keeps the
+    exact fp32 copy (the reference's BF16_W, fastloop.py:223-228)."""
+    for nm, mod in model.named_modules():
+        if isinstance(mod, torch.nn.Linear) and not nm.startswith(("memory", "reread")):
+            mod.weight = torch.nn.Parameter(mod.weight.detach().to(dtype))
+    return model
+
+
+class Trainer:
+    def __init__(self, model, tcfg: TrainConfig, ocfg: OptConfig = None, stage=None, parallel=None):
+        self.model, self.cfg = model, tcfg
+        self.stage = stage or tcfg.stage
+        self.ocfg = ocfg or OptConfig(lr=tcfg.lr)
+        self.parallel = parallel
+        dev = next(model.parameters()).device
+        self.device = dev
+        if dev.type == "cuda" and self.ocfg.bf16_weights and "X" in self.stage:
+            cast_linear_weights(model)
+        if parallel is not None:
+            parallel.shard_model(model)
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        st = self.stage
+        self.apply_now = False
+        self.acc = {}
+        if "X" in st and self.ocfg.kind == "instinct":
+            import dataclasses
+            self.opt = Instinct(self.params, dataclasses.replace(self.ocfg, lr=tcfg.lr))
+            self.in_backward = "B" in st and self.ocfg.in_backward
+            if parallel is not None:
+                parallel.attach(self)
+            if self.in_backward:
+                for p in self.params:
+                    p.register_post_accumulate_grad_hook(self._hook)
+        elif "S" in st:
+            self.opt = SurpriseAdamW(self.params, lr=tcfg.lr, betas=(0.9, 0.95), weight_decay=0.1)
+            self.in_backward = False
+        else:
+            self.opt = torch.optim.AdamW(self.params, lr=tcfg.lr, betas=(0.9, 0.95), weight_decay=0.1,
+                                         fused=dev.type == "cuda")
+            self.in_backward = False
+        self.streams = None
+        self.last_loss = None
+
+    # ------------------------------------------------------------------------------------------ hooks
+    def _hook(self, p):
+        """Grad-ready hook: accumulate until the last micro-batch, then step this weight and drop its grad."""
+        if p.grad is None:
+            return
+        if not self.apply_now:
+            return                                   # autograd keeps accumulating into p.grad
+        self.opt.update(p)
+        p.grad = None
+
+    def register_new_param(self, p):
+        if self.in_backward:
+            p.register_post_accumulate_grad_hook(self._hook)
+
+    # ------------------------------------------------------------------------------------------ loss
+    def loss_fn(self, xy, prep=None):
+        m = self.model
+        x_in, y_t = xy[:, :-1], xy[:, 1:]
+        out, cost = m(x_in, prep) if prep is not None else m(x_in)
+        loss = m.train_loss(out, y_t, True)
+        return loss + self.cfg.read_cost * cost.float()
+
+    def set_lr(self, step, mul=1.0):
+        lr = lr_at(step, self.cfg) * mul
+        for g in self.opt.param_groups:
+            g["lr"] = lr
+
+    def situation(self, xy):
+        with torch.no_grad():
+            return self.model.emb(xy[:, :-1]).float().mean((0, 1))
+
+    # ------------------------------------------------------------------------------------------ step
+    def step(self, xy, step, preps=None, lr_mul=1.0):
+        """One training step; returns the loss as a device tensor (no host sync)."""
+        self.set_lr(step, lr_mul)
+        m = self.model
+        if hasattr(m, "before_step"):
+            m.before_step(step)
+        micro = self.cfg.micro or len(xy)
+        mbs = xy.split(micro)
+        inst = isinstance(self.opt, Instinct)
+        if inst and self.ocfg.sparse_rows and hasattr(m, "table_rows"):
+            self.opt.rows = m.table_rows(xy[:, :-1])
+        if "C" in self.stage and xy.is_cuda and len(mbs) > 1:
+            return self._step_interleaved(mbs, len(xy), xy, step)
+        total = torch.zeros((), device=xy.device)
+        for i, mb in enumerate(mbs):
+            last = i == len(mbs) - 1
+            self.apply_now = last
+            loss = self.loss_fn(mb, preps[i] if preps is not None else None)
+            w = len(mb) / len(xy)
+            if inst and last:
+                tl = total + loss.detach() * w
+                sit = self.situation(xy)
+                if self.parallel is not None:
+                    tl, sit = self.parallel.sync_control(tl, sit, m)
+                self.opt.prepare(tl, sit)
+            if self.parallel is not None:
+                self.parallel.before_backward(self)
+            (loss * w).backward()
+            total = total + loss.detach() * w
+        self._after_backward(step, total, xy)
+        self.last_loss = total
+        return total
+
+    def _after_backward(self, step, total, xy):
+        inst = isinstance(self.opt, Instinct)
+        if inst:
+            if self.parallel is not None:
+                self.parallel.after_backward(self)
+            if not self.in_backward:
+                self.opt.update_all()
+            self.opt.finish()
+            if hasattr(self.model, "rebank"):
+                self._apply_rebank(self.model.rebank(step))
+        else:
+            if self.parallel is not None:
+                self.parallel.reduce_grads(self.params)
+            torch.nn.utils.clip_grad_norm_(self.params, 1.0)
+            if isinstance(self.opt, SurpriseAdamW):
+                self.opt.step(total)
+            else:
+                self.opt.step()
+            self.opt.zero_grad(set_to_none=True)
+
+    def _apply_rebank(self, changes):
+        """Experts moved between banks: the optimizer follows the new tensors (momentum by position)."""
+        for old, new, slot_map in changes:
+            self.opt.swap(old, new, slot_map)
+            self.register_new_param(new)
+        if changes:
+            self.params = [p for p in self.model.parameters() if p.requires_grad]
+
+    def _step_interleaved(self, mbs, n, xy, step):
+        """Stage C: independent micro-batches run forward on their own streams, one backward for all."""
+        if self.streams is None or len(self.streams) != len(mbs):
+            self.streams = [torch.cuda.Stream() for _ in mbs]
+        cur = torch.cuda.current_stream()
+        losses = []
+        for s, mb in zip(self.streams, mbs):
+            s.wait_stream(cur)
+            mb.record_stream(s)
+            with torch.cuda.stream(s):
+                losses.append(self.loss_fn(mb) * len(mb) / n)
+        for s in self.streams:
+            cur.wait_stream(s)
+        total = torch.stack(losses).sum()
+        self.apply_now = True
+        if isinstance(self.opt, Instinct):
+            self.opt.prepare(total.detach(), self.situation(xy))
+        total.backward()
+        self._after_backward(step, total.detach(), xy)
+        return total.detach()
+
+
+@torch.no_grad()
+def val_loss(model, store, seq, n=20, batch=8):
+    """Fixed validation windows (generator seed 0), mean token CE (fastloop.py:500-515)."""
+    was = model.training
+    model.eval()
+    g = torch.Generator(device=store.device).manual_seed(0)
+    t = store.t
+    total = torch.zeros((), device=store.device)
+    for _ in range(n):
+        start = torch.randint(0, len(t) - seq - 1, (batch,), device=store.device, generator=g)
+        xy = t[start[:, None] + torch.arange(seq + 1, device=store.device)].long()
+        out, _ = model(xy[:, :-1])
+        total += model.train_loss(out, xy[:, 1:], False)
+    model.train(was)
+    return total / n

@@ -1,0 +1,50 @@
+// Python bindings of the sm_100a kernels (module `memarch_b200._C`).
+#include <torch/extension.h>
+
+namespace mb {
+torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> out, c10::optional<torch::Tensor> out2,
+                   c10::optional<torch::Tensor> aux, bool a_mn, bool b_mn, bool accumulate, int64_t epi, bool out_f32,
+                   int64_t groups);
+int gemm_status(int device);
+void gemm_set_desc_override(std::vector<int64_t> v);
+std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16);
+std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd);
+torch::Tensor relu2_fwd(torch::Tensor a);
+torch::Tensor relu2_bwd(torch::Tensor dh, torch::Tensor a);
+torch::Tensor swiglu_fwd(torch::Tensor gu);
+torch::Tensor swiglu_bwd(torch::Tensor dh, torch::Tensor gu);
+torch::Tensor rope_qk(torch::Tensor qkv, double sign, bool half);
+void ce_rows(torch::Tensor logits, torch::Tensor y, torch::Tensor loss, c10::optional<torch::Tensor> gate,
+             c10::optional<torch::Tensor> hit, c10::optional<torch::Tensor> dg);
+torch::Tensor gather_rows(torch::Tensor src, torch::Tensor table, c10::optional<torch::Tensor> scale);
+torch::Tensor gather_sum_rows(torch::Tensor src, torch::Tensor idx, c10::optional<torch::Tensor> w, int64_t N);
+torch::Tensor row_dot(torch::Tensor go, torch::Tensor table, torch::Tensor ye);
+int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10::optional<torch::Tensor> w,
+                      c10::optional<torch::Tensor> cs, torch::Tensor gvec, int64_t index, torch::Tensor stake,
+                      torch::Tensor lr_t, c10::optional<torch::Tensor> rel, double beta, double wd, int64_t kind, bool sr,
+                      torch::Tensor seed_t, c10::optional<torch::Tensor> frozen);
+std::vector<torch::Tensor> anchor_select(torch::Tensor s, torch::Tensor tau, int64_t A);
+std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C);
+std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_keys, bool longest_only);
+}  // namespace mb
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &mb::gemm, "tcgen05 GEMM C = A * B^T (bf16, fp32 accumulate in TMEM)");
+  m.def("gemm_status", &mb::gemm_status, "read and clear the GEMM status word (0 = ok)");
+  m.def("gemm_set_desc_override", &mb::gemm_set_desc_override, "test hook: shared-memory descriptor geometry");
+  m.def("rmsnorm_fwd", &mb::rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &mb::rmsnorm_bwd);
+  m.def("relu2_fwd", &mb::relu2_fwd);
+  m.def("relu2_bwd", &mb::relu2_bwd);
+  m.def("swiglu_fwd", &mb::swiglu_fwd);
+  m.def("swiglu_bwd", &mb::swiglu_bwd);
+  m.def("rope_qk", &mb::rope_qk);
+  m.def("ce_rows", &mb::ce_rows);
+  m.def("gather_rows", &mb::gather_rows);
+  m.def("gather_sum_rows", &mb::gather_sum_rows);
+  m.def("row_dot", &mb::row_dot);
+  m.def("instinct_step", &mb::instinct_step);
+  m.def("anchor_select", &mb::anchor_select);
+  m.def("moe_slots", &mb::moe_slots);
+  m.def("lock_find", &mb::lock_find);
+}

@@ -1,0 +1,475 @@
+// tcgen05 GEMM core for sm_100a: C[g] = A[g] * B[g]^T, bf16 operands, fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer   (cp.async.bulk.tensor 3-D tiles -> 128B-swizzled shared-memory ring, 4 stages)
+//   warp 1      MMA issuer     (one thread issues tcgen05.mma 128x256x16; accumulators double-buffered in TMEM)
+//   warps 2..5  epilogue       (tcgen05.ld 32 lanes x 32 columns -> registers -> fused epilogue -> global)
+// Operands may be K-major (rows x K, K contiguous) or MN-major (K x rows, rows contiguous), so transposed views of
+// row-major tensors (dgrad / wgrad) need no transposing copy.  Batched ("grouped") over a leading dimension through
+// 3-D tensor maps: this is how all experts of a MoE layer run in one launch.
+// Epilogues: plain store (bf16 or fp32, optional += into fp32), relu^2 (also stores the pre-activation),
+// relu^2 backward (acc * 2*relu(aux)), SwiGLU over column halves, per-row scale.
+// Every mbarrier wait is bounded; on a timeout the kernel records a code in `status`, drains and returns.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "common.cuh"
+
+namespace mb {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 8;
+
+enum { EPI_NONE = 0, EPI_RELU2 = 1, EPI_DRELU2 = 2, EPI_SWIGLU = 3, EPI_ROWSCALE = 4 };
+
+struct GemmParams {
+  int M, N, K, G;                 // logical per-group problem; for EPI_SWIGLU N = 2H (B rows), out has H columns
+  void* out;
+  void* out2;
+  const void* aux;
+  long long out_gs, out2_gs, aux_gs;   // group strides in elements
+  int ldo, ldo2, ldaux;                // row pitches in elements
+  int epi, out_f32, accumulate;
+  int m_tiles, n_tiles;
+  uint32_t lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b;   // shared-memory descriptor geometry in bytes
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& g, int& mt, int& nt) {
+  int per_g = p.m_tiles * p.n_tiles;
+  g = t / per_g;
+  int r = t - g * per_g;
+  int band = GROUP_M * p.n_tiles;
+  int b = r / band;
+  int first_m = b * GROUP_M;
+  int gsz = min(GROUP_M, p.m_tiles - first_m);
+  int rr = r - b * band;
+  mt = first_m + rr % gsz;
+  nt = rr / gsz;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int total = p.G * p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int g, mt, nt;
+        tile_coords(t, p, g, mt, nt);
+        const int m0 = mt * BM;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
+          }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_3d(sA, &tmA, &full[stage], k0, m0, g);
+          } else {
+            tma_load_3d(sA, &tmA, &full[stage], m0, k0, g);
+            tma_load_3d(sA + 8192, &tmA, &full[stage], m0 + 64, k0, g);
+          }
+          if (p.epi == EPI_SWIGLU) {
+            const int H = p.N >> 1, n0 = nt * 128;
+            if (!B_MN) {
+              tma_load_3d(sB, &tmB, &full[stage], k0, n0, g);
+              tma_load_3d(sB + 16384, &tmB, &full[stage], k0, H + n0, g);
+            } else {
+              tma_load_3d(sB, &tmB, &full[stage], n0, k0, g);
+              tma_load_3d(sB + 8192, &tmB, &full[stage], n0 + 64, k0, g);
+              tma_load_3d(sB + 16384, &tmB, &full[stage], H + n0, k0, g);
+              tma_load_3d(sB + 24576, &tmB, &full[stage], H + n0 + 64, k0, g);
+            }
+          } else {
+            const int n0 = nt * BN;
+            if (!B_MN) {
+              tma_load_3d(sB, &tmB, &full[stage], k0, n0, g);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) tma_load_3d(sB + j * 8192, &tmB, &full[stage], n0 + 64 * j, k0, g);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {                                   // let copies already in flight land before the CTA leaves
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = idesc_bf16(BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            atomicCAS(p.status, 0, ST_WAIT_FULL); *abort_flag = 1; ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t ad = smem_desc_sw128(sA + k * p.kstep_a, p.lbo_a, p.sbo_a);
+            uint64_t bd = smem_desc_sw128(sB + k * p.kstep_b, p.lbo_b, p.sbo_b);
+            umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);              // the smem slot is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);                  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                        // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      int g, mt, nt;
+      tile_coords(t, p, g, mt, nt);
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+        if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_TMEM_FULL); *abort_flag = 1; }
+        ok = false; break;
+      }
+      tc_fence_after();
+      const int row = mt * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (p.epi == EPI_SWIGLU) {
+        const int H = p.N >> 1;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          __syncwarp();
+          tmem_ld32(taddr + c * 32, rg);
+          tmem_ld32(taddr + 128 + c * 32, ru);
+          tmem_ld_wait();
+          const int col0 = nt * 128 + c * 32;
+          if (row_ok && col0 < H) {
+            bf16* o = reinterpret_cast<bf16*>(p.out) + g * p.out_gs + static_cast<long long>(row) * p.ldo + col0;
+            bf16* o2 = p.out2 ? reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0
+                              : nullptr;
+            const int nv = min(32, H - col0);
+            for (int j = 0; j < nv; ++j) {
+              float gg = __uint_as_float(rg[j]), uu = __uint_as_float(ru[j]);
+              // operands rounded to bf16 first so forward and the recomputing backward see the same numbers
+              float gr = __bfloat162float(__float2bfloat16(gg)), ur = __bfloat162float(__float2bfloat16(uu));
+              o[j] = __float2bfloat16(silu_f(gr) * ur);
+              if (o2) { o2[j] = __float2bfloat16(gg); o2[H + j] = __float2bfloat16(uu); }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          __syncwarp();                              // tcgen05.ld is warp-collective: reconverge after the stores
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = nt * BN + c * 32;
+          if (row_ok && col0 < p.N) {
+          const int nv = min(32, p.N - col0);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (p.epi == EPI_RELU2) {
+            bf16* o2 = reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0;
+            if (nv == 32) {
+              uint4* d4 = reinterpret_cast<uint4*>(o2);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                d4[j] = make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                                   pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
+            } else {
+              for (int j = 0; j < nv; ++j) o2[j] = __float2bfloat16(v[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float a = __bfloat162float(__float2bfloat16(v[j]));     // activation of the stored (rounded) value
+              a = fmaxf(a, 0.f);
+              v[j] = a * a;
+            }
+          } else if (p.epi == EPI_DRELU2) {
+            const bf16* ax = reinterpret_cast<const bf16*>(p.aux) + g * p.aux_gs + static_cast<long long>(row) * p.ldaux + col0;
+            if (nv == 32) {
+              const uint4* a4 = reinterpret_cast<const uint4*>(ax);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 u = a4[j];
+                float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
+                v[8 * j + 0] *= 2.f * fmaxf(f0.x, 0.f); v[8 * j + 1] *= 2.f * fmaxf(f0.y, 0.f);
+                v[8 * j + 2] *= 2.f * fmaxf(f1.x, 0.f); v[8 * j + 3] *= 2.f * fmaxf(f1.y, 0.f);
+                v[8 * j + 4] *= 2.f * fmaxf(f2.x, 0.f); v[8 * j + 5] *= 2.f * fmaxf(f2.y, 0.f);
+                v[8 * j + 6] *= 2.f * fmaxf(f3.x, 0.f); v[8 * j + 7] *= 2.f * fmaxf(f3.y, 0.f);
+              }
+            } else {
+              for (int j = 0; j < nv; ++j) v[j] *= 2.f * fmaxf(__bfloat162float(ax[j]), 0.f);
+            }
+          } else if (p.epi == EPI_ROWSCALE) {
+            const float s = reinterpret_cast<const float*>(p.aux)[g * p.aux_gs + row];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= s;
+          }
+          if (p.out_f32) {
+            float* o = reinterpret_cast<float*>(p.out) + g * p.out_gs + static_cast<long long>(row) * p.ldo + col0;
+            if (nv == 32) {
+              float4* o4 = reinterpret_cast<float4*>(o);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                if (p.accumulate) { float4 y = o4[j]; x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
+                o4[j] = x;
+              }
+            } else {
+              for (int j = 0; j < nv; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
+            }
+          } else {
+            bf16* o = reinterpret_cast<bf16*>(p.out) + g * p.out_gs + static_cast<long long>(row) * p.ldo + col0;
+            if (nv == 32) {
+              uint4* o4 = reinterpret_cast<uint4*>(o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                o4[j] = make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                                   pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
+            } else {
+              for (int j = 0; j < nv; ++j) o[j] = __float2bfloat16(v[j]);
+            }
+          }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    TORCH_CHECK(e == cudaSuccess && p != nullptr, "cuTensorMapEncodeTiled entry point not found");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 3-D bf16 tensor map: dims (inner, rows, groups), 128-byte swizzle, zero fill outside.
+CUtensorMap make_tmap_bf16(const void* base, uint64_t inner, uint64_t rows, uint64_t groups, uint64_t row_pitch_el,
+                           uint64_t group_pitch_el, uint32_t box_inner, uint32_t box_rows) {
+  CUtensorMap m;
+  cuuint64_t dims[3] = {inner, rows, groups};
+  cuuint64_t strides[2] = {row_pitch_el * 2, (groups > 1 ? group_pitch_el : row_pitch_el * rows) * 2};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA operand must be 16-byte aligned");
+  TORCH_CHECK(strides[0] % 16 == 0 && strides[1] % 16 == 0, "TMA operand pitches must be multiples of 16 bytes");
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", static_cast<int>(r));
+  return m;
+}
+
+static int* status_word(int device) {
+  static int* words[16] = {nullptr};
+  TORCH_CHECK(device >= 0 && device < 16, "device index out of range");
+  if (!words[device]) {
+    TORCH_CHECK(cudaMalloc(&words[device], sizeof(int)) == cudaSuccess, "status word alloc failed");
+    cudaMemset(words[device], 0, sizeof(int));
+  }
+  return words[device];
+}
+
+int gemm_status(int device) {
+  int v = 0;
+  cudaMemcpy(&v, status_word(device), sizeof(int), cudaMemcpyDeviceToHost);
+  int z = 0;
+  if (v) cudaMemcpy(status_word(device), &z, sizeof(int), cudaMemcpyHostToDevice);
+  return v;
+}
+
+static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};   // test hook: lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b
+void gemm_set_desc_override(std::vector<int64_t> v) {
+  for (int i = 0; i < 6; ++i) g_desc_override[i] = i < (int)v.size() ? (int)v[i] : -1;
+}
+
+// Raw launcher shared by the torch binding and the fused multi-GPU paths (which pass peer pointers for A).
+void launch_gemm(const void* A, long long a_rows_pitch, long long a_gs, bool a_mn, const void* B, long long b_rows_pitch,
+                 long long b_gs, bool b_mn, GemmParams p, cudaStream_t stream, int max_ctas) {
+  const int M = p.M, N = p.N, K = p.K, G = p.G;
+  CUtensorMap tmA = a_mn ? make_tmap_bf16(A, M, K, G, a_rows_pitch, a_gs, 64, 64)
+                         : make_tmap_bf16(A, K, M, G, a_rows_pitch, a_gs, 64, BM);
+  const bool sw = p.epi == EPI_SWIGLU;
+  CUtensorMap tmB = b_mn ? make_tmap_bf16(B, N, K, G, b_rows_pitch, b_gs, 64, 64)
+                         : make_tmap_bf16(B, K, N, G, b_rows_pitch, b_gs, 64, sw ? 128 : BN);
+  p.m_tiles = (M + BM - 1) / BM;
+  p.n_tiles = sw ? ((N / 2) + 127) / 128 : (N + BN - 1) / BN;
+  p.lbo_a = a_mn ? BK * 128 : 0;  p.sbo_a = 1024;  p.kstep_a = a_mn ? UMMA_K * 128 : UMMA_K * 2;
+  p.lbo_b = b_mn ? BK * 128 : 0;  p.sbo_b = 1024;  p.kstep_b = b_mn ? UMMA_K * 128 : UMMA_K * 2;
+  if (g_desc_override[0] >= 0) {
+    p.lbo_a = g_desc_override[0]; p.sbo_a = g_desc_override[1]; p.kstep_a = g_desc_override[2];
+    p.lbo_b = g_desc_override[3]; p.sbo_b = g_desc_override[4]; p.kstep_b = g_desc_override[5];
+  }
+  const int total = G * p.m_tiles * p.n_tiles;
+  int grid = std::min(total, max_ctas);
+  if (grid <= 0) return;
+  auto launch = [&](auto kern) {
+    static bool attr_set[4] = {false, false, false, false};
+    int id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+    if (!attr_set[id]) {
+      TORCH_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess,
+                  "cannot raise dynamic shared memory for the GEMM kernel");
+      attr_set[id] = true;
+    }
+    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  };
+  if (!a_mn && !b_mn) launch(gemm_tc_kernel<false, false>);
+  else if (!a_mn && b_mn) launch(gemm_tc_kernel<false, true>);
+  else if (a_mn && !b_mn) launch(gemm_tc_kernel<true, false>);
+  else launch(gemm_tc_kernel<true, true>);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+// torch binding.  a: (G?, M, K) or MN-major (G?, K, M); b: (G?, N, K) or MN-major (G?, K, N).
+torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> out_,
+                   c10::optional<torch::Tensor> out2_, c10::optional<torch::Tensor> aux_, bool a_mn, bool b_mn,
+                   bool accumulate, int64_t epi, bool out_f32, int64_t groups) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm: CUDA tensors expected");
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "gemm: bf16 operands");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int G = (int)groups;
+  auto as3 = [&](torch::Tensor t) { return t.dim() == 2 ? t.unsqueeze(0) : t; };
+  torch::Tensor A = as3(a), B = as3(b);
+  TORCH_CHECK(A.dim() == 3 && B.dim() == 3 && A.size(0) == G && B.size(0) == G, "gemm: group dimension mismatch");
+  TORCH_CHECK(A.stride(2) == 1 && B.stride(2) == 1, "gemm: innermost dimension must be contiguous");
+  const int M = a_mn ? A.size(2) : A.size(1), K = a_mn ? A.size(1) : A.size(2);
+  const int N = b_mn ? B.size(2) : B.size(1), Kb = b_mn ? B.size(1) : B.size(2);
+  TORCH_CHECK(K == Kb, "gemm: K mismatch ", K, " vs ", Kb);
+  const int Nout = epi == EPI_SWIGLU ? N / 2 : N;
+  torch::Tensor out;
+  if (out_.has_value() && out_->defined()) {
+    out = *out_;
+  } else {
+    auto opt = a.options().dtype(out_f32 ? torch::kFloat32 : torch::kBFloat16);
+    out = (a.dim() == 2 && G == 1) ? torch::empty({M, Nout}, opt) : torch::empty({G, M, Nout}, opt);
+  }
+  TORCH_CHECK(out.scalar_type() == (out_f32 ? torch::kFloat32 : torch::kBFloat16), "gemm: out dtype");
+  torch::Tensor O = as3(out);
+  TORCH_CHECK(O.size(0) == G && O.size(1) == M && O.size(2) == Nout && O.stride(2) == 1, "gemm: out shape");
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.G = G;
+  p.out = O.data_ptr(); p.ldo = (int)O.stride(1); p.out_gs = G > 1 ? O.stride(0) : 0;
+  p.epi = (int)epi; p.out_f32 = out_f32; p.accumulate = accumulate;
+  TORCH_CHECK(!accumulate || out_f32, "gemm: accumulate needs an fp32 output");
+  const int vec = out_f32 ? 4 : 8;
+  TORCH_CHECK(p.ldo % vec == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && (p.out_gs % vec) == 0,
+              "gemm: output must allow 16-byte row stores");
+  if (out2_.has_value() && out2_->defined()) {
+    torch::Tensor O2 = as3(*out2_);
+    TORCH_CHECK(O2.scalar_type() == torch::kBFloat16 && O2.stride(2) == 1 && O2.size(1) == M, "gemm: out2");
+    p.out2 = O2.data_ptr(); p.ldo2 = (int)O2.stride(1); p.out2_gs = G > 1 ? O2.stride(0) : 0;
+    TORCH_CHECK(p.ldo2 % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out2) & 15) == 0, "gemm: out2 alignment");
+  }
+  TORCH_CHECK(epi != EPI_RELU2 || p.out2 != nullptr, "gemm: relu2 epilogue needs out2 for the pre-activation");
+  if (aux_.has_value() && aux_->defined()) {
+    if (epi == EPI_ROWSCALE) {
+      TORCH_CHECK(aux_->scalar_type() == torch::kFloat32 && aux_->is_contiguous(), "gemm: row scale must be fp32");
+      p.aux = aux_->data_ptr(); p.aux_gs = G > 1 ? M : 0;
+    } else {
+      torch::Tensor X = as3(*aux_);
+      TORCH_CHECK(X.scalar_type() == torch::kBFloat16 && X.stride(2) == 1 && X.size(1) == M && X.size(2) == N, "gemm: aux");
+      p.aux = X.data_ptr(); p.ldaux = (int)X.stride(1); p.aux_gs = G > 1 ? X.stride(0) : 0;
+      TORCH_CHECK(p.ldaux % 8 == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0, "gemm: aux alignment");
+    }
+  }
+  TORCH_CHECK((epi != EPI_DRELU2 && epi != EPI_ROWSCALE) || p.aux != nullptr, "gemm: epilogue needs aux");
+  p.status = status_word(a.get_device());
+  launch_gemm(A.data_ptr(), A.stride(1), G > 1 ? A.stride(0) : 0, a_mn, B.data_ptr(), B.stride(1), G > 1 ? B.stride(0) : 0,
+              b_mn, p, at::cuda::getCurrentCUDAStream(), sm_count());
+  return out;
+}
+
+}  // namespace mb

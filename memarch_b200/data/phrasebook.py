@@ -25,7 +25,7 @@ def token_counts(a, vocab):
     return np.bincount(np.asarray(a, dtype=np.int64), minlength=vocab)[:vocab]
 
 
-def bigram_init(a, d, vocab=50257, phrase_c=0.05, niter=4, seed=0, with_ent=False):
+def bigram_init(a, d, vocab=50257, phrase_c=0.05, niter=4, seed=0, with_ent=False, device="cpu"):
     a = np.asarray(a, dtype=np.int64)
     V = vocab
     pair = a[:-1] * V + a[1:]
@@ -36,11 +36,11 @@ def bigram_init(a, d, vocab=50257, phrase_c=0.05, niter=4, seed=0, with_ent=Fals
     pmi = np.log(c * len(pair) / (cp[prev] * cn[nxt]))
     keep = (pmi > 0) & (c >= 2)
     idx = torch.tensor(np.stack([prev[keep], nxt[keep]]))
-    M = torch.sparse_coo_tensor(idx, torch.tensor(pmi[keep], dtype=torch.float32), (V, V)).coalesce()
+    M = torch.sparse_coo_tensor(idx, torch.tensor(pmi[keep], dtype=torch.float32), (V, V)).coalesce().to(device)
     torch.manual_seed(seed)
     U, S, Vt = torch.svd_lowrank(M, q=d, niter=niter)
     E, H = U * S.sqrt(), Vt * S.sqrt()
-    logp = torch.tensor(np.log((cn + 1) / cn.sum()), dtype=torch.float32)
+    logp = torch.tensor(np.log((cn + 1) / cn.sum()), dtype=torch.float32, device=device)
     En = E / E.pow(2).mean(1, keepdim=True).sqrt().clamp(min=1e-6)
     lse = torch.cat([torch.logsumexp(phrase_c * En[i:i + 2048] @ H.T + logp, -1) for i in range(0, V, 2048)])
     out = {"emb": E, "head": H, "S": S, "logp_next": logp, "lse": lse}
@@ -53,7 +53,7 @@ def bigram_init(a, d, vocab=50257, phrase_c=0.05, niter=4, seed=0, with_ent=Fals
     return out
 
 
-def phrase_table(a, H, K, vocab=50257):
+def phrase_table(a, H, K, vocab=50257, device="cpu"):
     a = np.asarray(a, dtype=np.int64)
     V = vocab
     ctx = a[:-2] * V + a[1:-1]
@@ -71,17 +71,17 @@ def phrase_table(a, H, K, vocab=50257):
     cn = np.bincount(a[2:], minlength=V).astype(np.float64)
     pmi = np.log(ct * len(a) / (crow[r] * cn[n]))
     keep = (pmi > 0) & (ct >= 2)
-    Hd = H.double()
-    M = torch.sparse_coo_tensor(torch.tensor(np.stack([r[keep], n[keep]])), torch.tensor(pmi[keep]), (K, V)).coalesce()
-    P = torch.linalg.solve(Hd.T @ Hd + 1e-3 * torch.eye(Hd.shape[1], dtype=Hd.dtype), (M @ Hd).T).T
+    Hd = H.to(device).double()
+    M = torch.sparse_coo_tensor(torch.tensor(np.stack([r[keep], n[keep]])), torch.tensor(pmi[keep]), (K, V)).coalesce().to(device)
+    P = torch.linalg.solve(Hd.T @ Hd + 1e-3 * torch.eye(Hd.shape[1], dtype=Hd.dtype, device=device), (M @ Hd).T).T
     return {"keys": torch.tensor(keys), "vec": P.float()}
 
 
-def lock_trust(a, vocab, counts, T=1024, max_tokens=4_000_000):
+def lock_trust(a, vocab, counts, T=1024, max_tokens=4_000_000, device="cpu"):
     a = np.asarray(a[:max_tokens], dtype=np.int64)
-    bucket = torch.tensor(np.clip(np.floor(np.log10(np.asarray(counts) + 1)), 0, 6).astype(np.int64))
+    bucket = torch.tensor(np.clip(np.floor(np.log10(np.asarray(counts) + 1)), 0, 6).astype(np.int64), device=device)
     n = len(a) // (T + 1) * (T + 1)
-    x = torch.tensor(a[:n]).view(-1, T + 1)
+    x = torch.tensor(a[:n], device=device).view(-1, T + 1)
     inp, tgt = x[:, :-1], x[:, 1:]
     cand, on, bk, _ = ref.find_locks(inp, vocab, 3, None)
     bk = bucket[inp.clamp(max=bucket.numel() - 1)]

@@ -17,7 +17,7 @@ import torch.nn.functional as F
 
 from . import _ext, ref
 
-ATTN_CORE = os.environ.get("MEMARCH_ATTN", "own")
+ATTN_CORE = os.environ.get("MEMARCH_ATTN", "lib")
 
 
 class _RopeQK(torch.autograd.Function):

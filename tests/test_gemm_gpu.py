@@ -1,0 +1,101 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch matmul: every operand-major combination, ragged shapes, grouped launch
+and each fused epilogue."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+    from memarch_b200.ops import _ext
+    return _ext.C()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _mk(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).bfloat16()
+
+
+SHAPES = [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (2049, 2048, 2048), (136, 264, 200), (4096, 50304, 128)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_matches_fp32(M, N, K, a_mn, b_mn):
+    from memarch_b200.ops import gemm
+    C = _ext()
+    A = _mk((M, K), seed=1)
+    B = _mk((N, K), seed=2)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    assert C.gemm_status(0) == 0
+    ref = A.float() @ B.float().t()
+    assert _rel(out, ref) < 1e-2, (_rel(out, ref), out[:2, :4], ref[:2, :4])
+
+
+def test_gemm_fp32_accumulate():
+    from memarch_b200.ops import gemm
+    A, B = _mk((512, 320), seed=3), _mk((256, 320), seed=4)
+    out = torch.ones(512, 256, device="cuda")
+    gemm(A, B, out=out, out_dtype=torch.float32, accumulate=True)
+    gemm(A, B, out=out, out_dtype=torch.float32, accumulate=True)
+    ref = 1 + 2 * (A.float() @ B.float().t())
+    assert _rel(out, ref) < 2e-3
+
+
+def test_gemm_grouped_and_strided_views():
+    from memarch_b200.ops import gemm
+    E, Cn, d, H = 4, 200, 256, 384
+    x, up = _mk((E, Cn, d), seed=5), _mk((E, d, H), 0.1, seed=6)
+    y = gemm(x, up, b_mn=True, groups=E)
+    ref = torch.bmm(x.float(), up.float())
+    assert _rel(y, ref) < 1e-2
+    big = _mk((1000, 512), seed=7)
+    w = _mk((256, 512), seed=8)
+    out = torch.zeros(1000, 256, device="cuda", dtype=torch.bfloat16)
+    gemm(big[128:640], w, out=out[128:640])
+    assert _rel(out[128:640], big[128:640].float() @ w.float().t()) < 1e-2
+    assert out[:128].abs().sum() == 0 and out[640:].abs().sum() == 0
+
+
+def test_gemm_epilogues():
+    from memarch_b200.ops import gemm
+    M, N, K = 300, 512, 256
+    A, B = _mk((M, K), seed=9), _mk((N, K), 0.1, seed=10)
+    acc = A.float() @ B.float().t()
+    h = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    a = torch.empty_like(h)
+    gemm(A, B, out=h, out2=a, epi=1)
+    assert _rel(a, acc) < 1e-2
+    assert _rel(h, torch.relu(a.float()) ** 2) < 1e-2
+    da = gemm(A, B, epi=2, aux=a)
+    assert _rel(da, acc * 2 * torch.relu(a.float())) < 1e-2
+    sc = torch.rand(M, device="cuda")
+    ys = gemm(A, B, epi=4, aux=sc)
+    assert _rel(ys, acc * sc[:, None]) < 1e-2
+    H = N // 2
+    hs = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    gu = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    gemm(A, B, out=hs, out2=gu, epi=3)
+    assert _rel(gu, acc) < 1e-2
+    g, u = gu.float().chunk(2, -1)
+    assert _rel(hs, torch.nn.functional.silu(g) * u) < 1e-2
+
+
+def test_linear_autograd_matches_torch():
+    from memarch_b200.ops import basic
+    x = _mk((512, 256), seed=11).requires_grad_()
+    w = _mk((384, 256), 0.1, seed=12).requires_grad_()
+    y = basic._Linear.apply(x, w)
+    go = _mk((512, 384), seed=13)
+    y.backward(go)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    (xr @ wr.t()).backward(go.float())
+    assert _rel(y, xr @ wr.t()) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2

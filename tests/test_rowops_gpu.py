@@ -1,0 +1,197 @@
+"""Row / elementwise / selection / optimizer kernels against their PyTorch fp32 statements in ops.ref."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("xdt,out_bf16", [(torch.float32, True), (torch.float32, False), (torch.bfloat16, True)])
+def test_rmsnorm_fwd_bwd(xdt, out_bf16):
+    from memarch_b200 import ops
+    from memarch_b200.ops import ref
+    torch.manual_seed(0)
+    x = torch.randn(300, 2048, device="cuda").to(xdt).requires_grad_()
+    w = (1 + 0.1 * torch.randn(2048, device="cuda")).requires_grad_()
+    y = ops.rmsnorm(x, w, 1e-6, out_dtype=torch.bfloat16 if out_bf16 else torch.float32)
+    go = torch.randn_like(y)
+    y.backward(go)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-6)
+    yr.backward(go.float())
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
+
+
+def test_activations():
+    from memarch_b200 import ops
+    from memarch_b200.ops import ref
+    a = torch.randn(257, 1024, device="cuda").bfloat16().requires_grad_()
+    h = ops.relu2(a)
+    go = torch.randn_like(h)
+    h.backward(go)
+    ar = a.detach().float().requires_grad_()
+    ref.relu2(ar).backward(go.float())
+    assert _rel(h, ref.relu2(ar)) < 1e-2 and _rel(a.grad, ar.grad) < 1e-2
+    gu = torch.randn(130, 2048, device="cuda").bfloat16().requires_grad_()
+    s = ops.swiglu(gu)
+    go = torch.randn_like(s)
+    s.backward(go)
+    gr = gu.detach().float().requires_grad_()
+    ref.swiglu(gr).backward(go.float())
+    assert _rel(s, ref.swiglu(gr)) < 1e-2 and _rel(gu.grad, gr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_rope_roundtrip_and_reference(half):
+    from memarch_b200.ops import _ext, ref
+    C = _ext.C()
+    qkv = torch.randn(2, 96, 3, 4, 64, device="cuda").bfloat16()
+    r = C.rope_qk(qkv, 1.0, half)
+    cos, sin = ref.rope_angles(96, 64, "cuda")
+    for s in range(2):
+        want = ref.apply_rope(qkv[:, :, s].float().permute(0, 2, 1, 3), cos, sin, half).permute(0, 2, 1, 3)
+        assert _rel(r[:, :, s], want) < 1e-2
+    assert torch.equal(r[:, :, 2], qkv[:, :, 2])
+    back = C.rope_qk(r, -1.0, half)
+    assert _rel(back[:, :, :2], qkv[:, :, :2]) < 2e-2
+
+
+@pytest.mark.parametrize("mix", [False, True])
+def test_ce_rows(mix):
+    from memarch_b200.ops import _ext, ref
+    C = _ext.C()
+    torch.manual_seed(1)
+    n, V = 64, 50304
+    logits = (torch.randn(n, V, device="cuda") * 2).bfloat16()
+    y = torch.randint(0, V, (n,), device="cuda")
+    gate = torch.rand(n, device="cuda") * 0.5 if mix else None
+    hit = (torch.rand(n, device="cuda") > 0.5).float() if mix else None
+    loss_r, G_r, dg_r = ref.ce_rows(logits.float(), y, gate, hit)
+    loss = torch.empty(n, device="cuda")
+    dg = torch.empty(n, device="cuda") if mix else None
+    lg = logits.clone()
+    C.ce_rows(lg, y, loss, gate, hit, dg)
+    assert _rel(loss, loss_r) < 1e-3
+    assert _rel(lg, G_r) < 2e-2
+    if mix:
+        assert _rel(dg, dg_r) < 1e-3
+
+
+@pytest.mark.parametrize("mix", [False, True])
+def test_linear_ce_matches_reference(mix):
+    from memarch_b200 import ops
+    from memarch_b200.ops import ref
+    torch.manual_seed(2)
+    N, d, V = 1024, 272, 4096
+    h = torch.randn(N, d, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(V, d, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = torch.randint(0, V, (N,), device="cuda")
+    gate = (torch.rand(N, device="cuda") * 0.3).requires_grad_() if mix else None
+    hit = (torch.rand(N, device="cuda") > 0.7).float() if mix else None
+    loss = ops.linear_ce(h, w, y, gate=gate, hit=hit, chunk=512)
+    loss.backward()
+    tot, gh, gw, _, dg, _ = ref.linear_ce(h.detach().float(), w.detach().float(), y, None,
+                                          None if gate is None else gate.detach(), hit, chunk=512)
+    assert abs(loss.item() - tot.item()) / tot.item() < 2e-3
+    assert _rel(h.grad, gh) < 2e-2 and _rel(w.grad, gw) < 2e-2
+    if mix:
+        assert _rel(gate.grad, dg) < 1e-2
+
+
+def test_gathers():
+    from memarch_b200.ops import _ext
+    C = _ext.C()
+    N, d, S, k = 500, 256, 900, 3
+    x = torch.randn(N, d, device="cuda").bfloat16()
+    table = torch.randint(0, N + 1, (S,), device="cuda")
+    sc = torch.rand(S, device="cuda")
+    out = C.gather_rows(x, table, sc)
+    xp = torch.cat([x.float(), torch.zeros(1, d, device="cuda")])
+    assert _rel(out, xp[table] * sc[:, None]) < 1e-2
+    src = torch.randn(S, d, device="cuda").bfloat16()
+    idx = torch.randint(0, S + 1, (N, k), device="cuda")
+    o2 = C.gather_sum_rows(src, idx, sc, N)
+    sp = torch.cat([src.float() * sc[:, None], torch.zeros(1, d, device="cuda")])
+    assert _rel(o2, sp[idx].sum(1)) < 1e-2
+    dots = C.row_dot(x, table, src)
+    assert _rel(dots, (xp[table] * src.float()).sum(-1)) < 1e-2
+
+
+def test_anchor_select_exact():
+    from memarch_b200.ops import _ext, ref
+    C = _ext.C()
+    torch.manual_seed(3)
+    for T, A in ((1024, 256), (300, 75), (2048, 512)):
+        s = torch.randn(5, T, device="cuda") * 3 + 4
+        s[:, 0] = 1e4
+        s[3] = -1                                   # a text with no anchors
+        s[4] = 100                                  # a text where everything is an anchor
+        tau = torch.tensor(5.0, device="cuda")
+        idx, valid = C.anchor_select(s, tau.reshape(1), A)
+        ri, rv = ref.select_anchors(s, tau, A)
+        assert torch.equal(idx, ri) and torch.equal(valid, rv)
+
+
+def test_moe_slots_exact():
+    from memarch_b200.ops import _ext, ref
+    C = _ext.C()
+    torch.manual_seed(4)
+    N, k, E, Cn = 3000, 4, 8, 700
+    e = torch.randint(0, E + 1, (N, k), device="cuda")
+    w = torch.rand(N, k, device="cuda")
+    table, flat_idx, dropped = C.moe_slots(e, E, Cn)
+    rt, _, rf, rd = ref.moe_slots(e, w, E, Cn)
+    assert torch.equal(table, rt) and torch.equal(flat_idx, rf)
+    assert abs(dropped.item() - rd.item()) < 1e-6
+
+
+def test_lock_find_exact():
+    from memarch_b200.ops import _ext, ref
+    C = _ext.C()
+    torch.manual_seed(5)
+    x = torch.randint(0, 50, (4, 700), device="cuda")
+    bucket = torch.zeros(64, dtype=torch.long, device="cuda")
+    for n_keys, lb in ((3, bucket), (2, None)):
+        cand, on, src = C.lock_find(x, 50, n_keys, lb is not None)
+        rc, ro, _, rs = ref.find_locks(x, 50, n_keys, lb)
+        assert torch.equal(cand, rc) and torch.equal(on, ro) and torch.equal(src, rs)
+
+
+@pytest.mark.parametrize("kind,shape", [("hs", (384, 1024)), ("hs3", (4, 256, 384)), ("vocab", (12000, 128)),
+                                         ("tensor", (1000,)), ("tensor", (3, 7))])
+@pytest.mark.parametrize("wdt,mdt", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32)])
+def test_instinct_step_matches_reference(kind, shape, wdt, mdt):
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim import Instinct
+    torch.manual_seed(6)
+    p = (torch.randn(*shape, device="cuda") * 0.1).to(wdt)
+    pc = p.detach().clone()
+    cfg = OptConfig(lr=1e-2, norm="hs", scale=0.12, m_bf16=mdt == torch.bfloat16, rel_every=1)
+    o_gpu = Instinct([p.requires_grad_()], cfg)
+    import os
+    pr = pc.clone().requires_grad_()
+    o_ref = Instinct([pr], cfg)
+    assert o_gpu.spec(p)[0] == kind
+    for step in range(3):
+        g = torch.randn(*shape, device="cuda").to(wdt)
+        if kind == "vocab":
+            g[::3] = 0
+        sit = torch.randn(16, device="cuda")
+        for o, q in ((o_gpu, p), (o_ref, pr)):
+            o.prepare(torch.tensor(5.0 - step, device="cuda"), sit)
+        o_gpu.update(p, g)
+        os.environ["MEMARCH_FORCE_TORCH"] = "1"
+        try:
+            o_ref.update(pr, g)
+        finally:
+            del os.environ["MEMARCH_FORCE_TORCH"]
+        o_gpu.finish(); o_ref.finish()
+    tol = 2e-2 if wdt == torch.bfloat16 else 1e-4
+    assert _rel(p - pc, pr - pc) < tol, _rel(p - pc, pr - pc)
+    assert _rel(o_gpu.m[0], o_ref.m[0]) < tol
+    assert _rel(o_gpu.rel, o_ref.rel) < 1e-3

@@ -296,6 +296,11 @@ def _run_reference(args, ref_dir):
     os.environ["DEVICE"] = "cuda"
     if world > 1:
         os.environ.update({"FSDP": "1", "EP": "1", "MASTER_ADDR": os.environ.get("MASTER_ADDR", "127.0.0.1")})
+    # The per-weight compiled optimizer step of the reference (exp_opt.py:386-399) rebuilds `_instinct_step_impl`
+    # without its default arguments and raises "missing 2 required positional arguments: 'cs' and 'seed_t'" on
+    # torch 2.11; its own OPT_ALL=1 switch (one compiled optimizer program after backward, fastloop.py:342) is the
+    # stock path that runs, and is what FSDP forces anyway (fastloop.py:307).
+    os.environ.setdefault("OPT_ALL", "1")
     if os.environ.get("REF_EAGER") == "1":
         os.environ["NO_COMPILE"] = "1"
     cache = os.path.join(tempfile.gettempdir(), "memarch_ref_cache")
@@ -337,7 +342,7 @@ def _run_reference(args, ref_dir):
     if rank == 0:
         emit(args, "reference", world, ms, e2e, clocks, 0,
              {"parallelism": f"fsdp{world}+ep{world}" if world > 1 else "single",
-              "mode": "eager" if os.environ.get("NO_COMPILE") else "torch.compile",
+              "mode": ("eager" if os.environ.get("NO_COMPILE") else "torch.compile") + "+OPT_ALL",
               "loss_first": round(float(losses[0]), 4), "loss_last": round(float(losses[-1]), 4),
               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)})
     if world > 1:

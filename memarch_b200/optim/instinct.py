@@ -145,14 +145,18 @@ class Instinct:
         return kind, wd, vocab_table
 
     @torch.no_grad()
-    def update(self, p, grad=None):
-        """One Instinct step of one weight; called from the weight's grad-ready hook."""
+    def update(self, p, grad=None, synced=False):
+        """One Instinct step of one weight; called from the weight's grad-ready hook.  With a data-parallel engine
+        attached the gradient first goes through `grad_sync`, which may defer the step (returns None) and call back
+        with `synced=True` once the rank-mean gradient is there."""
         i = self.idx[id(p)]
         grad = p.grad if grad is None else grad
         if grad is None:
             return
-        if self.grad_sync is not None:
+        if self.grad_sync is not None and not synced:
             grad = self.grad_sync(p, grad)
+            if grad is None:
+                return
         self._sync_lr()
         kind, wd, vocab = self.spec(p)
         want_rel = self.n_step % self.rel_every == 0

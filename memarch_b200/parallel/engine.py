@@ -1,0 +1,175 @@
+"""One process per GPU: data parallelism for the light layers / tables, expert parallelism for the heavy layers.
+
+Semantics (the reference's FSDP+EP torch path, fastloop.py:269-307, full2.py:1122-1156, and the JAX port's
+`dist.py`): every rank routes and slots its own anchors (capacity from the local N); experts are sharded E/W per
+rank and tokens travel by all-to-all; all other weights are replicated and stepped with the rank-mean gradient; the
+loss fed to the optimizer, the situation vector and the anchor threshold `tau` are rank means.
+
+Two modes share this interface:
+  * `fused=False`  NCCL (or gloo on CPU) collectives only: all-to-all for the experts, asynchronous all-reduce of
+                   each weight's gradient overlapped with the rest of backward.  The baseline and the CPU test path.
+  * `fused=True`   the peer-memory kernels of `memarch_b200.parallel.fused`: expert GEMMs that load their A tiles
+                   from the owners' symmetric buffers and store results into them, and the reduce-scatter + Instinct
+                   update + weight broadcast kernels.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class NcclExpertExchange:
+    """Expert-parallel FFN through two autograd all-to-alls (full2.py:1137-1156), extended to a sharded frozen bank."""
+
+    def __init__(self, rank, world, group=None):
+        self.rank, self.W, self.group = rank, world, group
+
+    def _perm(self, moe):
+        """Order experts so each rank's share is contiguous: rank r gets its learning experts then its frozen ones."""
+        W = self.W
+        if not getattr(moe, "bank", False) or not moe.has_F:
+            return None, moe.E // W, 0
+        L, Fz = moe.L, moe.Fz
+        El, Fl = len(L) // W, len(Fz) // W
+        order = []
+        for r in range(W):
+            order += L[r * El:(r + 1) * El] + Fz[r * Fl:(r + 1) * Fl]
+        return torch.tensor(order, device=moe.up.device), El, Fl
+
+    def ffn(self, moe, xe):
+        from torch.distributed._functional_collectives import all_to_all_single_autograd
+        W = self.W
+        E, C, d = xe.shape
+        perm, El, Fl = self._perm(moe)
+        g = self.group or dist.group.WORLD
+        if perm is not None:
+            xe = xe[perm]
+        n = El + Fl
+        r = all_to_all_single_autograd(xe.contiguous(), None, None, g)
+        r = r.view(W, n, C, d).transpose(0, 1).reshape(n, W * C, d)
+        y = moe._ffn(r[:El], moe.up, moe.down)
+        if Fl:
+            y = torch.cat([y, moe._ffn_frozen(r[El:])])
+        y = y.view(n, W, C, d).transpose(0, 1).reshape(E, C, d).contiguous()
+        y = all_to_all_single_autograd(y, None, None, g)
+        if perm is not None:
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(E, device=perm.device)
+            y = y[inv]
+        return y
+
+
+class ParallelEngine:
+    SMALL = 1 << 16          # weights below this many elements are reduced together at the end of backward
+
+    def __init__(self, rank, world, local_rank=0, fused=True, group=None):
+        self.rank, self.W, self.local = rank, world, local_rank
+        self.group = group
+        self.fused = bool(fused) and torch.cuda.is_available()
+        self.ep = NcclExpertExchange(rank, world, group)
+        self.fused_impl = None
+        self.pending = []            # (param, grad, work) all-reduces in flight
+        self.small = []
+        self.trainer = None
+        self.ctrl = None
+
+    # ------------------------------------------------------------------------------------------ model sharding
+    def shard_model(self, model):
+        """Keep this rank's experts only; replicate the rest (identical init on every rank: same seed)."""
+        from ..models.moe import AnchorMoE
+        if self.fused:
+            from .fused import FusedParallel
+            self.fused_impl = FusedParallel(self)
+        for mod in model.modules():
+            if isinstance(mod, AnchorMoE):
+                mod.ep_shard(self.rank, self.W, self.fused_impl.ep if self.fused_impl else self.ep)
+        for p in model.parameters():
+            if not getattr(p, "_ep_local", False):
+                dist.broadcast(p.data, 0, group=self.group)
+        for b in model.buffers():
+            if b.numel() and b.dtype.is_floating_point:
+                dist.broadcast(b.data, 0, group=self.group)
+
+    def attach(self, trainer):
+        self.trainer = trainer
+        trainer.opt.grad_sync = self.grad_sync
+        if self.fused_impl is not None:
+            self.fused_impl.attach(trainer)
+
+    # ------------------------------------------------------------------------------------------ control values
+    def sync_control(self, loss, sit, model):
+        """One small all-reduce: mean loss, true batch-mean situation vector and the shared anchor threshold."""
+        tau = model.tau if hasattr(model, "tau") else loss.new_zeros(())
+        buf = torch.cat([loss.reshape(1).float(), tau.reshape(1).float(), sit.float().reshape(-1)])
+        dist.all_reduce(buf, group=self.group)
+        buf /= self.W
+        if hasattr(model, "tau"):
+            model.tau.copy_(buf[1])
+        return buf[0], buf[2:]
+
+    # ------------------------------------------------------------------------------------------ gradients
+    def before_backward(self, trainer):
+        self.pending.clear()
+        self.small.clear()
+
+    def grad_sync(self, p, grad):
+        """Called by the optimizer from the weight's grad-ready hook.  Expert weights are rank-local.  Replicated
+        weights: average over ranks.  Returns the gradient to step with, or None when the step is deferred."""
+        if getattr(p, "_ep_local", False) or self.W == 1:
+            return grad
+        if self.fused_impl is not None:
+            return self.fused_impl.dp.grad_ready(p, grad)
+        if grad.numel() < self.SMALL:
+            self.small.append((p, grad))
+            return None
+        work = dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self.pending.append((p, grad, work))
+        self._drain(keep=1)                      # step the weights whose reduction has had a layer's time to finish
+        return None
+
+    def _drain(self, keep=0):
+        opt = self.trainer.opt
+        while len(self.pending) > keep:
+            p, grad, work = self.pending.pop(0)
+            work.wait()
+            grad.div_(self.W)
+            opt.update(p, grad, synced=True)
+
+    def after_backward(self, trainer):
+        if self.fused_impl is not None:
+            self.fused_impl.dp.flush()
+            return
+        self._drain(0)
+        if self.small:
+            flat = torch.cat([g.reshape(-1).float() for _, g in self.small])
+            dist.all_reduce(flat, group=self.group)
+            flat /= self.W
+            off = 0
+            for p, g in self.small:
+                n = g.numel()
+                trainer.opt.update(p, flat[off:off + n].view_as(g).to(g.dtype), synced=True)
+                off += n
+            self.small.clear()
+
+    def reduce_grads(self, params):
+        """Plain optimizers (AdamW path): average every replicated gradient after backward."""
+        for p in params:
+            if p.grad is not None and not getattr(p, "_ep_local", False):
+                dist.all_reduce(p.grad, group=self.group)
+                p.grad.div_(self.W)
+
+
+def init_distributed(backend=None, timeout_s=1800):
+    """torchrun-style rendezvous from RANK / WORLD_SIZE / LOCAL_RANK (fastloop.py:207-214)."""
+    import datetime
+    import os
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        cuda = torch.cuda.is_available()
+        if cuda:
+            torch.cuda.set_device(local)
+        dist.init_process_group(backend or ("nccl" if cuda else "gloo"), timeout=datetime.timedelta(seconds=timeout_s))
+    return rank, world, local

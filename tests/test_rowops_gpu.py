@@ -163,7 +163,7 @@ def test_lock_find_exact():
 
 
 @pytest.mark.parametrize("kind,shape", [("hs", (384, 1024)), ("hs3", (4, 256, 384)), ("vocab", (12000, 128)),
-                                         ("tensor", (1000,)), ("tensor", (3, 7))])
+                                         ("tensor", (1000,)), ("hs", (3, 7))])
 @pytest.mark.parametrize("wdt,mdt", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32)])
 def test_instinct_step_matches_reference(kind, shape, wdt, mdt):
     from memarch_b200.config import OptConfig

@@ -6,6 +6,14 @@ torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor
                    c10::optional<torch::Tensor> aux, bool a_mn, bool b_mn, bool accumulate, int64_t epi, bool out_f32,
                    int64_t groups);
 int gemm_status(int device);
+torch::Tensor gemm_peer(std::vector<int64_t> a_ptrs, int64_t seg_M, int64_t K, int64_t a_groups, int64_t a_pitch,
+                        int64_t a_gs, int64_t a_g_off, torch::Tensor b, bool b_mn, c10::optional<torch::Tensor> out_local,
+                        std::vector<int64_t> out_ptrs, int64_t out_ld, int64_t out_gs, int64_t out_g_off,
+                        c10::optional<torch::Tensor> out2, c10::optional<torch::Tensor> aux, int64_t epi, int64_t groups);
+void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, int64_t epoch, double timeout_ms);
+int64_t peer_status_read();
+void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,
+                    int64_t numel, bool is_bf16, int64_t rank, double scale);
 void gemm_set_desc_override(std::vector<int64_t> v);
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16);
 std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd);
@@ -13,7 +21,8 @@ torch::Tensor relu2_fwd(torch::Tensor a);
 torch::Tensor relu2_bwd(torch::Tensor dh, torch::Tensor a);
 torch::Tensor swiglu_fwd(torch::Tensor gu);
 torch::Tensor swiglu_bwd(torch::Tensor dh, torch::Tensor gu);
-torch::Tensor rope_qk(torch::Tensor qkv, double sign, bool half);
+torch::Tensor rope_qk(torch::Tensor qkv, torch::Tensor cos, torch::Tensor sin, double sign, bool half);
+torch::Tensor resid_add(torch::Tensor x, torch::Tensor y);
 void ce_rows(torch::Tensor logits, torch::Tensor y, torch::Tensor loss, c10::optional<torch::Tensor> gate,
              c10::optional<torch::Tensor> hit, c10::optional<torch::Tensor> dg);
 torch::Tensor gather_rows(torch::Tensor src, torch::Tensor table, c10::optional<torch::Tensor> scale);
@@ -32,6 +41,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &mb::gemm, "tcgen05 GEMM C = A * B^T (bf16, fp32 accumulate in TMEM)");
   m.def("gemm_status", &mb::gemm_status, "read and clear the GEMM status word (0 = ok)");
   m.def("gemm_set_desc_override", &mb::gemm_set_desc_override, "test hook: shared-memory descriptor geometry");
+  m.def("gemm_peer", &mb::gemm_peer, "segmented GEMM: A tiles from peer buffers, result rows to the owners' buffers");
+  m.def("peer_barrier", &mb::peer_barrier, "bounded device-side barrier over symmetric flags");
+  m.def("peer_status_read", &mb::peer_status_read);
+  m.def("peer_allreduce", &mb::peer_allreduce, "one-shot all-reduce by peer loads/stores or NVLS multimem");
   m.def("rmsnorm_fwd", &mb::rmsnorm_fwd);
   m.def("rmsnorm_bwd", &mb::rmsnorm_bwd);
   m.def("relu2_fwd", &mb::relu2_fwd);
@@ -39,6 +52,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &mb::swiglu_fwd);
   m.def("swiglu_bwd", &mb::swiglu_bwd);
   m.def("rope_qk", &mb::rope_qk);
+  m.def("resid_add", &mb::resid_add);
   m.def("ce_rows", &mb::ce_rows);
   m.def("gather_rows", &mb::gather_rows);
   m.def("gather_sum_rows", &mb::gather_sum_rows);

@@ -37,7 +37,14 @@ struct GemmParams {
   int m_tiles, n_tiles;
   uint32_t lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b;   // shared-memory descriptor geometry in bytes
   int* status;
+  // M may be cut into `n_seg` segments of `seg_M` rows, each read through its own A tensor map (a peer GPU's
+  // buffer) and, when `out_seg_on`, written to its own output base (the owner GPU's buffer).  Tiles never straddle
+  // segments.  Plain GEMM: n_seg = 1, seg_M = M.
+  int n_seg, seg_M, tiles_per_seg, a_g_off, out_g_off, out_seg_on;
+  void* out_seg[8];
 };
+
+struct TmapSet { CUtensorMap m[8]; };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& g, int& mt, int& nt) {
   int per_g = p.m_tiles * p.n_tiles;
@@ -56,7 +63,7 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x))
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -75,7 +82,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmA);
+    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tmAs.m[i]);
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
@@ -96,7 +103,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         int g, mt, nt;
         tile_coords(t, p, g, mt, nt);
-        const int m0 = mt * BM;
+        const int seg = mt / p.tiles_per_seg;
+        const int m0 = (mt - seg * p.tiles_per_seg) * BM;
+        const CUtensorMap* tA = &tmAs.m[seg];
+        const int ga = g + p.a_g_off;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
@@ -106,10 +116,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_3d(sA, &tmA, &full[stage], k0, m0, g);
+            tma_load_3d(sA, tA, &full[stage], k0, m0, ga);
           } else {
-            tma_load_3d(sA, &tmA, &full[stage], m0, k0, g);
-            tma_load_3d(sA + 8192, &tmA, &full[stage], m0 + 64, k0, g);
+            tma_load_3d(sA, tA, &full[stage], m0, k0, ga);
+            tma_load_3d(sA + 8192, tA, &full[stage], m0 + 64, k0, ga);
           }
           if (p.epi == EPI_SWIGLU) {
             const int H = p.N >> 1, n0 = nt * 128;
@@ -188,8 +198,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ok = false; break;
       }
       tc_fence_after();
-      const int row = mt * BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int seg = mt / p.tiles_per_seg;
+      const int row_l = (mt - seg * p.tiles_per_seg) * BM + q * 32 + lane;     // row inside its segment
+      const bool row_ok = row_l < p.seg_M;
+      const int row = seg * p.seg_M + row_l;                                  // row of the local (M, N) problem
+      // where the result goes: the local output, or the buffer of the GPU that owns this segment's tokens
+      char* const obase = reinterpret_cast<char*>(p.out_seg_on ? p.out_seg[seg] : p.out);
+      const long long orow = p.out_seg_on ? row_l : row;
+      const long long og = g + p.out_g_off;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       if (p.epi == EPI_SWIGLU) {
         const int H = p.N >> 1;
@@ -202,7 +218,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tmem_ld_wait();
           const int col0 = nt * 128 + c * 32;
           if (row_ok && col0 < H) {
-            bf16* o = reinterpret_cast<bf16*>(p.out) + g * p.out_gs + static_cast<long long>(row) * p.ldo + col0;
+            bf16* o = reinterpret_cast<bf16*>(obase) + og * p.out_gs + orow * p.ldo + col0;
             bf16* o2 = p.out2 ? reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0
                               : nullptr;
             const int nv = min(32, H - col0);
@@ -267,7 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int j = 0; j < 32; ++j) v[j] *= s;
           }
           if (p.out_f32) {
-            float* o = reinterpret_cast<float*>(p.out) + g * p.out_gs + static_cast<long long>(row) * p.ldo + col0;
+            float* o = reinterpret_cast<float*>(obase) + og * p.out_gs + orow * p.ldo + col0;
             if (nv == 32) {
               float4* o4 = reinterpret_cast<float4*>(o);
 #pragma unroll
@@ -280,7 +296,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               for (int j = 0; j < nv; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
             }
           } else {
-            bf16* o = reinterpret_cast<bf16*>(p.out) + g * p.out_gs + static_cast<long long>(row) * p.ldo + col0;
+            bf16* o = reinterpret_cast<bf16*>(obase) + og * p.out_gs + orow * p.ldo + col0;
             if (nv == 32) {
               uint4* o4 = reinterpret_cast<uint4*>(o);
 #pragma unroll
@@ -329,6 +345,10 @@ static EncodeTiledFn encode_fn() {
 // 3-D bf16 tensor map: dims (inner, rows, groups), 128-byte swizzle, zero fill outside.
 CUtensorMap make_tmap_bf16(const void* base, uint64_t inner, uint64_t rows, uint64_t groups, uint64_t row_pitch_el,
                            uint64_t group_pitch_el, uint32_t box_inner, uint32_t box_rows) {
+  // cuTensorMapEncodeTiled is a driver call: a thread that has made no runtime call yet (an autograd worker) has no
+  // current context and gets CUDA_ERROR_INVALID_CONTEXT, so bind the primary context once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   CUtensorMap m;
   cuuint64_t dims[3] = {inner, rows, groups};
   cuuint64_t strides[2] = {row_pitch_el * 2, (groups > 1 ? group_pitch_el : row_pitch_el * rows) * 2};
@@ -367,15 +387,22 @@ void gemm_set_desc_override(std::vector<int64_t> v) {
 }
 
 // Raw launcher shared by the torch binding and the fused multi-GPU paths (which pass peer pointers for A).
-void launch_gemm(const void* A, long long a_rows_pitch, long long a_gs, bool a_mn, const void* B, long long b_rows_pitch,
-                 long long b_gs, bool b_mn, GemmParams p, cudaStream_t stream, int max_ctas) {
-  const int M = p.M, N = p.N, K = p.K, G = p.G;
-  CUtensorMap tmA = a_mn ? make_tmap_bf16(A, M, K, G, a_rows_pitch, a_gs, 64, 64)
-                         : make_tmap_bf16(A, K, M, G, a_rows_pitch, a_gs, 64, BM);
+// A_list: one base pointer per M-segment (n_seg of them, each (a_groups, seg_M, K) or MN-major (a_groups, K, seg_M)).
+void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_groups, long long a_rows_pitch, long long a_gs,
+                     bool a_mn, const void* B, long long b_rows_pitch, long long b_gs, bool b_mn, GemmParams p,
+                     cudaStream_t stream, int max_ctas) {
+  const int N = p.N, K = p.K, G = p.G;
+  TORCH_CHECK(n_seg >= 1 && n_seg <= 8, "gemm: 1..8 segments");
+  TmapSet tmAs;
+  for (int i = 0; i < n_seg; ++i)
+    tmAs.m[i] = a_mn ? make_tmap_bf16(A_list[i], seg_M, K, a_groups, a_rows_pitch, a_gs, 64, 64)
+                     : make_tmap_bf16(A_list[i], K, seg_M, a_groups, a_rows_pitch, a_gs, 64, BM);
+  for (int i = n_seg; i < 8; ++i) tmAs.m[i] = tmAs.m[0];
+  p.n_seg = n_seg; p.seg_M = seg_M; p.tiles_per_seg = (seg_M + BM - 1) / BM;
   const bool sw = p.epi == EPI_SWIGLU;
   CUtensorMap tmB = b_mn ? make_tmap_bf16(B, N, K, G, b_rows_pitch, b_gs, 64, 64)
                          : make_tmap_bf16(B, K, N, G, b_rows_pitch, b_gs, 64, sw ? 128 : BN);
-  p.m_tiles = (M + BM - 1) / BM;
+  p.m_tiles = n_seg * p.tiles_per_seg;
   p.n_tiles = sw ? ((N / 2) + 127) / 128 : (N + BN - 1) / BN;
   p.lbo_a = a_mn ? BK * 128 : 0;  p.sbo_a = 1024;  p.kstep_a = a_mn ? UMMA_K * 128 : UMMA_K * 2;
   p.lbo_b = b_mn ? BK * 128 : 0;  p.sbo_b = 1024;  p.kstep_b = b_mn ? UMMA_K * 128 : UMMA_K * 2;
@@ -394,13 +421,19 @@ void launch_gemm(const void* A, long long a_rows_pitch, long long a_gs, bool a_m
                   "cannot raise dynamic shared memory for the GEMM kernel");
       attr_set[id] = true;
     }
-    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmAs, tmB, p);
   };
   if (!a_mn && !b_mn) launch(gemm_tc_kernel<false, false>);
   else if (!a_mn && b_mn) launch(gemm_tc_kernel<false, true>);
   else if (a_mn && !b_mn) launch(gemm_tc_kernel<true, false>);
   else launch(gemm_tc_kernel<true, true>);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void launch_gemm(const void* A, long long a_rows_pitch, long long a_gs, bool a_mn, const void* B, long long b_rows_pitch,
+                 long long b_gs, bool b_mn, GemmParams p, cudaStream_t stream, int max_ctas) {
+  const void* list[1] = {A};
+  launch_gemm_seg(list, 1, p.M, p.G, a_rows_pitch, a_gs, a_mn, B, b_rows_pitch, b_gs, b_mn, p, stream, max_ctas);
 }
 
 static int sm_count() {
@@ -469,6 +502,55 @@ torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor
   p.status = status_word(a.get_device());
   launch_gemm(A.data_ptr(), A.stride(1), G > 1 ? A.stride(0) : 0, a_mn, B.data_ptr(), B.stride(1), G > 1 ? B.stride(0) : 0,
               b_mn, p, at::cuda::getCurrentCUDAStream(), sm_count());
+  return out;
+}
+
+// Segmented GEMM over peer buffers (expert parallelism without a separate all-to-all):
+//   A rows of segment s come from `a_ptrs[s]`, a (a_groups, seg_M, K) bf16 buffer (a peer GPU's dispatch buffer);
+//   group g of this launch reads A group `a_g_off + g`;
+//   the result goes to `out_local` (G, n_seg*seg_M, N) or, when `out_ptrs` is given, rows of segment s go to
+//   `out_ptrs[s]`, a (.., seg_M, N) buffer with row pitch `out_ld` and group pitch `out_gs` at group `out_g_off + g`.
+torch::Tensor gemm_peer(std::vector<int64_t> a_ptrs, int64_t seg_M, int64_t K, int64_t a_groups, int64_t a_pitch,
+                        int64_t a_gs, int64_t a_g_off, torch::Tensor b, bool b_mn, c10::optional<torch::Tensor> out_local,
+                        std::vector<int64_t> out_ptrs, int64_t out_ld, int64_t out_gs, int64_t out_g_off,
+                        c10::optional<torch::Tensor> out2_, c10::optional<torch::Tensor> aux_, int64_t epi, int64_t groups) {
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == torch::kBFloat16, "gemm_peer: bf16 B");
+  const c10::cuda::CUDAGuard guard(b.device());
+  const int G = (int)groups, n_seg = (int)a_ptrs.size();
+  torch::Tensor B = b.dim() == 2 ? b.unsqueeze(0) : b;
+  TORCH_CHECK(B.size(0) == G && B.stride(2) == 1, "gemm_peer: B groups");
+  const int N = b_mn ? B.size(2) : B.size(1), Kb = b_mn ? B.size(1) : B.size(2);
+  TORCH_CHECK(Kb == K, "gemm_peer: K mismatch");
+  const int M = n_seg * (int)seg_M;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = (int)K; p.G = G;
+  p.epi = (int)epi; p.a_g_off = (int)a_g_off;
+  torch::Tensor out;
+  if (!out_ptrs.empty()) {
+    TORCH_CHECK((int)out_ptrs.size() == n_seg, "gemm_peer: one output base per segment");
+    for (int i = 0; i < n_seg; ++i) p.out_seg[i] = reinterpret_cast<void*>(out_ptrs[i]);
+    p.out_seg_on = 1; p.out_g_off = (int)out_g_off; p.ldo = (int)out_ld; p.out_gs = out_gs;
+    p.out = p.out_seg[0];
+    TORCH_CHECK(out_ld % 8 == 0 && out_gs % 8 == 0, "gemm_peer: output pitches");
+  } else {
+    out = (out_local.has_value() && out_local->defined()) ? *out_local : torch::empty({G, M, N}, b.options());
+    TORCH_CHECK(out.dim() == 3 && out.size(0) == G && out.size(1) == M && out.size(2) == N && out.stride(2) == 1, "gemm_peer: out");
+    p.out = out.data_ptr(); p.ldo = (int)out.stride(1); p.out_gs = out.stride(0);
+  }
+  if (out2_.has_value() && out2_->defined()) {
+    TORCH_CHECK(out2_->dim() == 3 && out2_->size(1) == M && out2_->stride(2) == 1, "gemm_peer: out2");
+    p.out2 = out2_->data_ptr(); p.ldo2 = (int)out2_->stride(1); p.out2_gs = out2_->stride(0);
+  }
+  if (aux_.has_value() && aux_->defined()) {
+    TORCH_CHECK(aux_->dim() == 3 && aux_->size(1) == M && aux_->stride(2) == 1, "gemm_peer: aux");
+    p.aux = aux_->data_ptr(); p.ldaux = (int)aux_->stride(1); p.aux_gs = aux_->stride(0);
+  }
+  TORCH_CHECK(epi != EPI_RELU2 || p.out2 != nullptr, "gemm_peer: relu2 epilogue needs out2");
+  p.status = status_word(b.get_device());
+  std::vector<const void*> list(n_seg);
+  for (int i = 0; i < n_seg; ++i) list[i] = reinterpret_cast<const void*>(a_ptrs[i]);
+  launch_gemm_seg(list.data(), n_seg, (int)seg_M, (int)a_groups, a_pitch, a_gs, false, B.data_ptr(), B.stride(1),
+                  G > 1 ? B.stride(0) : 0, b_mn, p, at::cuda::getCurrentCUDAStream(), sm_count());
   return out;
 }
 

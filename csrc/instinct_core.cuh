@@ -60,32 +60,50 @@ __device__ __forceinline__ float4 gload4(const InstinctArgs& a, long long i) {
   v.x *= a.g_scale; v.y *= a.g_scale; v.z *= a.g_scale; v.w *= a.g_scale;
   return v;
 }
-__device__ __forceinline__ float inv_rms(float sumsq, float count) { return 1.f / (sqrtf(sumsq / count) + 1e-8f); }
+// sums of squares -> scales, in place: x <- 1 / (sqrt(x / count) + 1e-8); optional fold x <- x * fold[i]^2 first
+// (fold already holds scales).  Tiny arrays (one value per row or per column).
+static __global__ void instinct_finalize(float* __restrict__ x, long long n, float count, const float* __restrict__ fold) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i];
+    if (fold) { const float f = fold[i]; v *= f * f; }
+    x[i] = 1.f / (sqrtf(v / count) + 1e-8f);
+  }
+}
 
-// rowsq[e*R + r] = sum_c (mf * cscale[e*C + c])^2 ; rowabs (optional) = sum_c |g|
+static __global__ void instinct_mul(float* __restrict__ x, const float* __restrict__ y, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= y[i];
+}
+
+__device__ __forceinline__ float4 mom4(const InstinctArgs& a, long long i, float4& g) {
+  g = gload4(a, i);
+  const float4 mm = ldv4(a.m, i, a.m_bf16);
+  const float b = a.beta, c = 1.f - a.beta;
+  return make_float4(b * mm.x + c * g.x, b * mm.y + c * g.y, b * mm.z + c * g.z, b * mm.w + c * g.w);
+}
+__device__ __forceinline__ float mom1(const InstinctArgs& a, long long i, float& g) {
+  g = gload(a, i);
+  return a.beta * ldv(a.m, i, a.m_bf16) + (1.f - a.beta) * g;
+}
+
+// rowsq[e*R + r] = sum_c (mf * cscale[e*C + c])^2 ; rowabs (optional) = sum_c |g|.  One block per row.
 template <int VEC>
-__global__ void instinct_stat_rows(InstinctArgs a, const float* __restrict__ colsq, float col_count,
-                                   float* __restrict__ rowsq, float* __restrict__ rowabs) {
+__global__ void instinct_stat_rows(InstinctArgs a, const float* __restrict__ cscale, float* __restrict__ rowsq,
+                                   float* __restrict__ rowabs) {
   __shared__ float red[32];
   for (long long row = blockIdx.x; row < a.E * a.R; row += gridDim.x) {
     const long long e = row / a.R;
     const long long base = row * a.C;
+    const float* cs = cscale ? cscale + e * a.C : nullptr;
     float ss = 0.f, sa = 0.f;
     for (long long c = (long long)threadIdx.x * VEC; c < a.C; c += (long long)blockDim.x * VEC) {
       if (VEC == 4) {
-        float4 g = gload4(a, base + c), mm = ldv4(a.m, base + c, a.m_bf16);
-        float v[4] = {a.beta * mm.x + (1.f - a.beta) * g.x, a.beta * mm.y + (1.f - a.beta) * g.y,
-                      a.beta * mm.z + (1.f - a.beta) * g.z, a.beta * mm.w + (1.f - a.beta) * g.w};
-        if (colsq) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) v[j] *= inv_rms(colsq[e * a.C + c + j], col_count);
-        }
-        ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        float4 g, v = mom4(a, base + c, g);
+        if (cs) { const float4 k = *reinterpret_cast<const float4*>(cs + c); v.x *= k.x; v.y *= k.y; v.z *= k.z; v.w *= k.w; }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         sa += fabsf(g.x) + fabsf(g.y) + fabsf(g.z) + fabsf(g.w);
       } else {
-        float g = gload(a, base + c);
-        float v = a.beta * ldv(a.m, base + c, a.m_bf16) + (1.f - a.beta) * g;
-        if (colsq) v *= inv_rms(colsq[e * a.C + c], col_count);
+        float g, v = mom1(a, base + c, g);
+        if (cs) v *= cs[c];
         ss += v * v;
         sa += fabsf(g);
       }
@@ -102,51 +120,31 @@ __global__ void instinct_stat_rows(InstinctArgs a, const float* __restrict__ col
 // colsq[e*C + c] += sum over this block's rows of (mf * cscale[e,c] * rscale[e,r])^2
 // grid: (col strips, row chunks, E); each thread owns VEC consecutive columns.
 template <int VEC>
-__global__ void instinct_stat_cols(InstinctArgs a, const float* __restrict__ colsq_in, float col_count,
-                                   const float* __restrict__ rowsq_in, float row_count, float* __restrict__ colsq_out,
-                                   int rows_per_block) {
+__global__ void instinct_stat_cols(InstinctArgs a, const float* __restrict__ cscale, const float* __restrict__ rscale,
+                                   float* __restrict__ colsq_out, int rows_per_block) {
   const long long e = blockIdx.z;
   const long long c = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= a.C) return;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(a.R, r0 + rows_per_block);
-  float cs[VEC];
+  float cs[VEC], acc[VEC];
 #pragma unroll
-  for (int j = 0; j < VEC; ++j) cs[j] = colsq_in ? inv_rms(colsq_in[e * a.C + c + j], col_count) : 1.f;
-  float acc[VEC];
-#pragma unroll
-  for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+  for (int j = 0; j < VEC; ++j) { cs[j] = cscale ? cscale[e * a.C + c + j] : 1.f; acc[j] = 0.f; }
   for (long long r = r0; r < r1; ++r) {
     const long long i = (e * a.R + r) * a.C + c;
-    const float rs = rowsq_in ? inv_rms(rowsq_in[e * a.R + r], row_count) : 1.f;
+    const float rs = rscale ? rscale[e * a.R + r] : 1.f;
     if (VEC == 4) {
-      float4 g = gload4(a, i), mm = ldv4(a.m, i, a.m_bf16);
-      float v0 = (a.beta * mm.x + (1.f - a.beta) * g.x) * cs[0] * rs, v1 = (a.beta * mm.y + (1.f - a.beta) * g.y) * cs[1 % VEC] * rs;
-      float v2 = (a.beta * mm.z + (1.f - a.beta) * g.z) * cs[2 % VEC] * rs, v3 = (a.beta * mm.w + (1.f - a.beta) * g.w) * cs[3 % VEC] * rs;
+      float4 g, v = mom4(a, i, g);
+      const float v0 = v.x * cs[0] * rs, v1 = v.y * cs[1 % VEC] * rs, v2 = v.z * cs[2 % VEC] * rs, v3 = v.w * cs[3 % VEC] * rs;
       acc[0] += v0 * v0; acc[1 % VEC] += v1 * v1; acc[2 % VEC] += v2 * v2; acc[3 % VEC] += v3 * v3;
     } else {
-      float v = (a.beta * ldv(a.m, i, a.m_bf16) + (1.f - a.beta) * gload(a, i)) * cs[0] * rs;
+      float g;
+      const float v = mom1(a, i, g) * cs[0] * rs;
       acc[0] += v * v;
     }
   }
 #pragma unroll
   for (int j = 0; j < VEC; ++j) atomicAdd(colsq_out + e * a.C + c + j, acc[j]);
-}
-
-struct Scale { const float* sq; float count; int axis; };    // axis: 0 = per row (e*R+r), 1 = per column (e*C+c), 2 = scalar, -1 = none
-
-__device__ __forceinline__ float scale_at(const Scale& s, long long e, long long r, long long c, long long R, long long C) {
-  if (s.axis < 0) return 1.f;
-  const float v = s.axis == 0 ? s.sq[e * R + r] : (s.axis == 1 ? s.sq[e * C + c] : s.sq[0]);
-  return inv_rms(v, s.count);
-}
-
-// rowB[i] <- rs1[i]^2 * rowB[i] with rs1 = 1/(sqrt(rowA[i]/count)+eps)
-static __global__ void instinct_fold_rows(float* __restrict__ rowB, const float* __restrict__ rowA, float count, long long n) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float s = inv_rms(rowA[i], count);
-    rowB[i] = s * s * rowB[i];
-  }
 }
 
 // sums for |g|/|w|: rel2[0] += sum g^2, rel2[1] += sum w^2 (before the update)
@@ -164,55 +162,116 @@ static __global__ void instinct_rel_sums(InstinctArgs a, float* __restrict__ rel
   if (threadIdx.x == 0) { atomicAdd(rel2, sg); atomicAdd(rel2 + 1, sw); }
 }
 
+// The update itself, one block per row: upd = mf * rscale[row] * cscale1[c] * cscale2[c]; with `fuse_row_norm` the
+// row is staged in shared memory and one more row normalisation (the last step of homeostasis) is done in place.
+// Momentum is written here (once per step).  Rows of a word table without gradient and frozen slices keep their weights.
 template <int VEC>
-__global__ void instinct_apply(InstinctArgs a, Scale s1, Scale s2, Scale s3, const float* __restrict__ rowabs,
+__global__ void instinct_apply(InstinctArgs a, const float* __restrict__ rscale, const float* __restrict__ cscale1,
+                               const float* __restrict__ cscale2, int fuse_row_norm, const float* __restrict__ rowabs,
                                const float* __restrict__ rel2, float* __restrict__ rel_out) {
-  const long long n = a.E * a.R * a.C;
+  extern __shared__ float cache[];
+  __shared__ float red[32];
   const float lr = *a.lr;
   const float eff = 1.f + (*a.gain - 1.f) * (*a.stake);
-  const float step = lr * eff, decay = 1.f - lr * a.wd;
+  const float step = lr * eff, decay = (a.wd != 0.f) ? 1.f - lr * a.wd : 1.f;
   const uint32_t seed = a.sr ? (uint32_t)((*a.seed) * 1000003ll) * 0x9E3779B9u + a.salt : 0u;
   if (rel_out && blockIdx.x == 0 && threadIdx.x == 0) *rel_out = sqrtf(rel2[0]) / (sqrtf(rel2[1]) + 1e-8f);
-  for (long long i0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * VEC; i0 < n;
-       i0 += (long long)gridDim.x * blockDim.x * VEC) {
-    const long long row = i0 / a.C;
-    const long long c0 = i0 - row * a.C;
-    const long long e = row / a.R, r = row - e * a.R;
-    float g[VEC], mo[VEC];
-    if (VEC == 4) {
-      float4 g4 = gload4(a, i0), m4 = ldv4(a.m, i0, a.m_bf16);
-      g[0] = g4.x; g[1 % VEC] = g4.y; g[2 % VEC] = g4.z; g[3 % VEC] = g4.w;
-      mo[0] = m4.x; mo[1 % VEC] = m4.y; mo[2 % VEC] = m4.z; mo[3 % VEC] = m4.w;
-    } else {
-      g[0] = gload(a, i0); mo[0] = ldv(a.m, i0, a.m_bf16);
-    }
-    const bool moves = (rowabs == nullptr || rowabs[row] > 0.f) &&
-                       !(a.frozen && a.frozen[i0 / a.frozen_stride]);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      const long long i = i0 + j, c = c0 + j;
-      const float mf = a.beta * mo[j] + (1.f - a.beta) * g[j];
-      uint32_t h = a.sr ? lowbias32((uint32_t)i ^ seed) : 0u;
-      if (a.m_bf16) reinterpret_cast<bf16*>(a.m)[i] = a.sr ? sr_round(mf, h & 0xFFFFu) : __float2bfloat16(mf);
-      else reinterpret_cast<float*>(a.m)[i] = mf;
-      const float upd = mf * scale_at(s1, e, r, c, a.R, a.C) * scale_at(s2, e, r, c, a.R, a.C) *
-                        scale_at(s3, e, r, c, a.R, a.C);
-      float t = a.w ? a.w[i] : ldv(a.p, i, a.p_bf16);
-      if (moves) {
-        t = (a.wd != 0.f ? t * decay : t) - upd * step;
-      } else if (a.frozen && a.frozen[i0 / a.frozen_stride]) {
-        continue;                                            // frozen slice: weight untouched
-      } else {
-        t = (a.wd != 0.f ? t * decay : t);                   // word-table row without gradient: no step (wd is 0 there)
+  for (long long row = blockIdx.x; row < a.E * a.R; row += gridDim.x) {
+    const long long e = row / a.R;
+    const long long base = row * a.C;
+    const float* c1 = cscale1 ? cscale1 + e * a.C : nullptr;
+    const float* c2 = cscale2 ? cscale2 + e * a.C : nullptr;
+    float rs = rscale ? rscale[row] : 1.f;
+    const bool frozen = a.frozen && a.frozen[base / a.frozen_stride];
+    const bool moves = !(rowabs && !(rowabs[row] > 0.f)) && !frozen;
+    if (fuse_row_norm) {
+      float ss = 0.f;
+      for (long long c = (long long)threadIdx.x * VEC; c < a.C; c += (long long)blockDim.x * VEC) {
+        if (VEC == 4) {
+          float4 g, v = mom4(a, base + c, g);
+          *reinterpret_cast<float4*>(cache + c) = v;
+          float4 k = c1 ? *reinterpret_cast<const float4*>(c1 + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+          const float u0 = v.x * k.x, u1 = v.y * k.y, u2 = v.z * k.z, u3 = v.w * k.w;
+          ss += u0 * u0 + u1 * u1 + u2 * u2 + u3 * u3;
+        } else {
+          float g, v = mom1(a, base + c, g);
+          cache[c] = v;
+          const float u = v * (c1 ? c1[c] : 1.f);
+          ss += u * u;
+        }
       }
-      if (a.w) a.w[i] = t;
-      if (a.p_bf16) reinterpret_cast<bf16*>(a.p)[i] = (a.sr && !a.w) ? sr_round(t, h >> 16) : __float2bfloat16(t);
-      else reinterpret_cast<float*>(a.p)[i] = t;
+      ss = block_sum(ss, red) * rs * rs;
+      rs *= 1.f / (sqrtf(ss / (float)a.C) + 1e-8f);
     }
+    for (long long c0 = (long long)threadIdx.x * VEC; c0 < a.C; c0 += (long long)blockDim.x * VEC) {
+      float mf[VEC], k[VEC];
+      if (VEC == 4) {
+        float4 v;
+        if (fuse_row_norm) v = *reinterpret_cast<const float4*>(cache + c0);
+        else { float4 g; v = mom4(a, base + c0, g); }
+        mf[0] = v.x; mf[1 % VEC] = v.y; mf[2 % VEC] = v.z; mf[3 % VEC] = v.w;
+        float4 k1 = c1 ? *reinterpret_cast<const float4*>(c1 + c0) : make_float4(1.f, 1.f, 1.f, 1.f);
+        if (c2) { const float4 k2 = *reinterpret_cast<const float4*>(c2 + c0); k1.x *= k2.x; k1.y *= k2.y; k1.z *= k2.z; k1.w *= k2.w; }
+        k[0] = k1.x; k[1 % VEC] = k1.y; k[2 % VEC] = k1.z; k[3 % VEC] = k1.w;
+      } else {
+        if (fuse_row_norm) mf[0] = cache[c0];
+        else { float g; mf[0] = mom1(a, base + c0, g); }
+        k[0] = (c1 ? c1[c0] : 1.f) * (c2 ? c2[c0] : 1.f);
+      }
+      const long long i0 = base + c0;
+      uint32_t h[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) h[j] = a.sr ? lowbias32((uint32_t)(i0 + j) ^ seed) : 0u;
+      // momentum
+      if (a.m_bf16) {
+        bf16* mp = reinterpret_cast<bf16*>(a.m) + i0;
+        if (VEC == 4 && !a.sr) {
+          *reinterpret_cast<uint2*>(mp) = make_uint2(pack_bf16(mf[0], mf[1 % VEC]), pack_bf16(mf[2 % VEC], mf[3 % VEC]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) mp[j] = a.sr ? sr_round(mf[j], h[j] & 0xFFFFu) : __float2bfloat16(mf[j]);
+        }
+      } else {
+        float* mp = reinterpret_cast<float*>(a.m) + i0;
+        if (VEC == 4) *reinterpret_cast<float4*>(mp) = make_float4(mf[0], mf[1 % VEC], mf[2 % VEC], mf[3 % VEC]);
+        else mp[0] = mf[0];
+      }
+      if (!moves) continue;                                   // weight of this row / slice stays as it is
+      float t[VEC];
+      if (a.w) {
+        if (VEC == 4) { const float4 w4 = *reinterpret_cast<const float4*>(a.w + i0); t[0] = w4.x; t[1 % VEC] = w4.y; t[2 % VEC] = w4.z; t[3 % VEC] = w4.w; }
+        else t[0] = a.w[i0];
+      } else if (VEC == 4) {
+        const float4 w4 = ldv4(a.p, i0, a.p_bf16); t[0] = w4.x; t[1 % VEC] = w4.y; t[2 % VEC] = w4.z; t[3 % VEC] = w4.w;
+      } else {
+        t[0] = ldv(a.p, i0, a.p_bf16);
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) t[j] = t[j] * decay - mf[j] * rs * k[j] * step;
+      if (a.w) {
+        if (VEC == 4) *reinterpret_cast<float4*>(a.w + i0) = make_float4(t[0], t[1 % VEC], t[2 % VEC], t[3 % VEC]);
+        else a.w[i0] = t[0];
+      }
+      if (a.p_bf16) {
+        bf16* pp = reinterpret_cast<bf16*>(a.p) + i0;
+        if (VEC == 4 && !(a.sr && !a.w)) {
+          *reinterpret_cast<uint2*>(pp) = make_uint2(pack_bf16(t[0], t[1 % VEC]), pack_bf16(t[2 % VEC], t[3 % VEC]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) pp[j] = (a.sr && !a.w) ? sr_round(t[j], h[j] >> 16) : __float2bfloat16(t[j]);
+        }
+      } else {
+        float* pp = reinterpret_cast<float*>(a.p) + i0;
+        if (VEC == 4) *reinterpret_cast<float4*>(pp) = make_float4(t[0], t[1 % VEC], t[2 % VEC], t[3 % VEC]);
+        else pp[0] = t[0];
+      }
+    }
+    if (fuse_row_norm) __syncthreads();                        // the row cache is reused by the next row
   }
 }
 
-// Launch sequence.  scratch (fp32, zeroed): [rowsqA E*R][rowsqB E*R][rowabs E*R][colsqA E*C][colsqB E*C][rel 2].
+// Launch sequence.  scratch (fp32, zeroed): [rowA E*R][rowB E*R][rowabs E*R][colA E*C][colB E*C][rel 2].
+// Returns the number of kernels launched.
 inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, float* rel_out, cudaStream_t st) {
   const long long ER = a.E * a.R, EC = a.E * a.C, n = ER * a.C;
   float* rowA = scratch;
@@ -222,15 +281,21 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
   float* colB = colA + EC;
   float* rel2 = colB + EC;
   const bool vec = (a.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.p) & 15) == 0) &&
-                   ((reinterpret_cast<uintptr_t>(a.g) & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.m) & 15) == 0);
+                   ((reinterpret_cast<uintptr_t>(a.g) & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.m) & 15) == 0) &&
+                   (a.w == nullptr || (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) && (EC % 4 == 0 || a.E == 1);
   int64_t launches = 0;
-  const int row_grid = (int)std::min<long long>(ER, 148 * 8);
-  auto stat_rows = [&](const float* csq, float ccount, float* out, float* absout) {
-    if (vec) instinct_stat_rows<4><<<row_grid, 256, 0, st>>>(a, csq, ccount, out, absout);
-    else instinct_stat_rows<1><<<row_grid, 256, 0, st>>>(a, csq, ccount, out, absout);
+  const int row_grid = (int)std::max<long long>(1, std::min<long long>(ER, 148 * 8));
+  const int row_threads = a.C >= 1024 ? 256 : (a.C >= 256 ? 128 : 64);
+  auto fin = [&](float* x, long long cnt, float count, const float* fold) {
+    instinct_finalize<<<(int)std::max<long long>(1, std::min<long long>((cnt + 255) / 256, 592)), 256, 0, st>>>(x, cnt, count, fold);
     ++launches;
   };
-  auto stat_cols = [&](const float* csq, float ccount, const float* rsq, float rcount, float* out) {
+  auto stat_rows = [&](const float* cs, float* out, float* absout) {
+    if (vec) instinct_stat_rows<4><<<row_grid, row_threads, 0, st>>>(a, cs, out, absout);
+    else instinct_stat_rows<1><<<row_grid, row_threads, 0, st>>>(a, cs, out, absout);
+    ++launches;
+  };
+  auto stat_cols = [&](const float* cs, const float* rs, float* out) {
     const int V = vec ? 4 : 1;
     const int threads = 128;
     const int strips = (int)((a.C + (long long)threads * V - 1) / ((long long)threads * V));
@@ -238,56 +303,67 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
     int rows_per_block = (int)std::max<long long>(8, (a.R + want_chunks - 1) / want_chunks);
     int chunks = (int)((a.R + rows_per_block - 1) / rows_per_block);
     dim3 grid(strips, chunks, (unsigned)a.E);
-    if (vec) instinct_stat_cols<4><<<grid, threads, 0, st>>>(a, csq, ccount, rsq, rcount, out, rows_per_block);
-    else instinct_stat_cols<1><<<grid, threads, 0, st>>>(a, csq, ccount, rsq, rcount, out, rows_per_block);
+    if (vec) instinct_stat_cols<4><<<grid, threads, 0, st>>>(a, cs, rs, out, rows_per_block);
+    else instinct_stat_cols<1><<<grid, threads, 0, st>>>(a, cs, rs, out, rows_per_block);
     ++launches;
   };
-  auto apply = [&](Scale s1, Scale s2, Scale s3, const float* rabs) {
-    const int V = vec ? 4 : 1;
-    const int grid = (int)std::min<long long>((n / V + 255) / 256, 148 * 16);
-    if (vec) instinct_apply<4><<<std::max(grid, 1), 256, 0, st>>>(a, s1, s2, s3, rabs, rel2, rel_out);
-    else instinct_apply<1><<<std::max(grid, 1), 256, 0, st>>>(a, s1, s2, s3, rabs, rel2, rel_out);
+  auto apply = [&](const float* rs, const float* c1, const float* c2, bool fuse, const float* rabs) {
+    const size_t smem = fuse ? (size_t)a.C * sizeof(float) : 0;
+    if (vec) {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(instinct_apply<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      instinct_apply<4><<<row_grid, row_threads, smem, st>>>(a, rs, c1, c2, fuse ? 1 : 0, rabs, rel2, rel_out);
+    } else {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(instinct_apply<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      instinct_apply<1><<<row_grid, row_threads, smem, st>>>(a, rs, c1, c2, fuse ? 1 : 0, rabs, rel2, rel_out);
+    }
     ++launches;
   };
   if (rel_out) {
-    const int grid = (int)std::min<long long>((n + 255) / 256, 148 * 8);
-    instinct_rel_sums<<<std::max(grid, 1), 256, 0, st>>>(a, rel2);
+    const int grid = (int)std::max<long long>(1, std::min<long long>((n + 255) / 256, 148 * 8));
+    instinct_rel_sums<<<grid, 256, 0, st>>>(a, rel2);
     ++launches;
   }
-  const Scale none{nullptr, 1.f, -1};
   const float Rf = (float)a.R, Cf = (float)a.C;
   switch (kind) {
-    case 4:   // hs: row, column, row
-      stat_rows(nullptr, 1.f, rowA, nullptr);
-      stat_cols(nullptr, 1.f, rowA, Cf, colA);
-      // third norm: rows of u2 = mf * rs1[r] * cs[c].  rs1 is constant along a row, so
-      // sum_c u2^2 = rs1^2 * sum_c (mf * cs[c])^2: one more row statistic, then fold rs1^2 in (E*R values).
-      stat_rows(colA, Rf, rowB, nullptr);
-      instinct_fold_rows<<<(int)std::min<long long>((ER + 255) / 256, 1184), 256, 0, st>>>(rowB, rowA, Cf, ER);
-      ++launches;
-      apply(Scale{rowA, Cf, 0}, Scale{colA, Rf, 1}, Scale{rowB, Cf, 0}, nullptr);
+    case 4: {  // hs: rows, columns, rows again (the last one inside `apply` when the row fits in shared memory)
+      stat_rows(nullptr, rowA, nullptr);
+      fin(rowA, ER, Cf, nullptr);
+      stat_cols(nullptr, rowA, colA);
+      fin(colA, EC, Rf, nullptr);
+      if ((size_t)a.C * sizeof(float) <= 96 * 1024) {
+        apply(rowA, colA, nullptr, true, nullptr);
+      } else {
+        stat_rows(colA, rowB, nullptr);           // sum_c (mf cs)^2; times rs1^2 below = row sums of u2
+        fin(rowB, ER, Cf, rowA);                  // rs3
+        instinct_mul<<<(int)std::max<long long>(1, std::min<long long>((ER + 255) / 256, 592)), 256, 0, st>>>(rowB, rowA, ER);
+        ++launches;                               // rowB = rs1 * rs3
+        apply(rowB, colA, nullptr, false, nullptr);
+      }
       break;
-    case 5:   // hs3: norm over R (per column), over C (per row), over R again
-      stat_cols(nullptr, 1.f, nullptr, 1.f, colA);
-      stat_rows(colA, Rf, rowA, nullptr);
-      stat_cols(colA, Rf, rowA, Cf, colB);
-      apply(Scale{colA, Rf, 1}, Scale{rowA, Cf, 0}, Scale{colB, Rf, 1}, nullptr);
+    }
+    case 5:   // hs3: over R (per column), over C (per row), over R again
+      stat_cols(nullptr, nullptr, colA);
+      fin(colA, EC, Rf, nullptr);
+      stat_rows(colA, rowA, nullptr);
+      fin(rowA, ER, Cf, nullptr);
+      stat_cols(colA, rowA, colB);
+      fin(colB, EC, Rf, nullptr);
+      apply(rowA, colA, colB, false, nullptr);
       break;
     case 3:   // word table: row rms, only rows with a gradient move
-      stat_rows(nullptr, 1.f, rowA, rowabs);
-      apply(Scale{rowA, Cf, 0}, none, none, rowabs);
-      break;
-    case 1:   // one norm per first-dimension row
-      stat_rows(nullptr, 1.f, rowA, nullptr);
-      apply(Scale{rowA, Cf, 0}, none, none, nullptr);
+      stat_rows(nullptr, rowA, rowabs);
+      fin(rowA, ER, Cf, nullptr);
+      apply(rowA, nullptr, nullptr, false, rowabs);
       break;
     case 2:   // experts (E, in, out): one norm per (expert, output column) over `in`
-      stat_cols(nullptr, 1.f, nullptr, 1.f, colA);
-      apply(Scale{colA, Rf, 1}, none, none, nullptr);
+      stat_cols(nullptr, nullptr, colA);
+      fin(colA, EC, Rf, nullptr);
+      apply(nullptr, colA, nullptr, false, nullptr);
       break;
-    default:  // whole tensor
-      stat_rows(nullptr, 1.f, rowA, nullptr);
-      apply(Scale{rowA, Cf, 0}, none, none, nullptr);
+    default:  // kinds 0 and 1: one norm per row of the (E*R, C) view (the whole tensor when E = R = 1)
+      stat_rows(nullptr, rowA, nullptr);
+      fin(rowA, ER, Cf, nullptr);
+      apply(rowA, nullptr, nullptr, false, nullptr);
       break;
   }
   return launches;

@@ -252,11 +252,13 @@ torch::Tensor swiglu_bwd(torch::Tensor dh, torch::Tensor gu) {
 }
 
 // ------------------------------------------------------------------------------------------------ RoPE on packed qkv
-// qkv (B, T, 3, H, hd) bf16.  q and k slices are rotated by sign * pos * base^(-2i/hd); v is copied.
-__global__ void rope_qk_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, long long BT, int T, int H, int hd,
-                               float sign, int half) {
+// qkv (B, T, 3, H, hd) bf16.  q and k slices are rotated by the angles of the (T, hd/2) fp32 cos/sin tables (sine
+// multiplied by `sign`: -1 rotates back, which is the backward pass); v is copied.
+__global__ void rope_qk_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, const float* __restrict__ cs,
+                               const float* __restrict__ sn, long long BT, int T, int H, int hd, float sign, int half) {
   const int per_tok = 3 * H * hd / 8;                       // 8-element groups per token
   const int g_per_head = hd / 8;
+  const int hh = hd / 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < BT * per_tok;
        i += (long long)gridDim.x * blockDim.x) {
     long long tok = i / per_tok;
@@ -266,56 +268,72 @@ __global__ void rope_qk_kernel(const bf16* __restrict__ in, bf16* __restrict__ o
     const long long off = i * 8;
     uint4 u = *reinterpret_cast<const uint4*>(in + off);
     if (s < 2) {
-      const float pos = (float)(tok % T) * sign;
+      const int t = (int)(tok % T);
       uint32_t* p = reinterpret_cast<uint32_t*>(&u);
       if (!half) {
+        const float4 c4 = *reinterpret_cast<const float4*>(cs + (long long)t * hh + gi * 4);
+        float4 s4 = *reinterpret_cast<const float4*>(sn + (long long)t * hh + gi * 4);
+        const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x * sign, s4.y * sign, s4.z * sign, s4.w * sign};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          int pair = gi * 4 + j;
-          float inv = 1.0f / powf(10000.f, (float)(2 * pair) / (float)hd);
-          float sn, cs;
-          sincosf(pos * inv, &sn, &cs);
           float2 f = unpack_bf16(p[j]);
-          p[j] = pack_bf16(f.x * cs - f.y * sn, f.x * sn + f.y * cs);
+          p[j] = pack_bf16(f.x * c[j] - f.y * sv[j], f.x * sv[j] + f.y * c[j]);
         }
       } else {
         // halves layout: element e pairs with e + hd/2; this group holds 8 elements of one half
-        const int e0 = gi * 8, hh = hd / 2;
+        const int e0 = gi * 8;
         const bool first = e0 < hh;
         const long long mate = first ? off + hh : off - hh;
         uint4 m = *reinterpret_cast<const uint4*>(in + mate);
         uint32_t* q = reinterpret_cast<uint32_t*>(&m);
+        const int eb = first ? e0 : e0 - hh;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 a = unpack_bf16(p[j]), b = unpack_bf16(q[j]);
-          float r[2];
-#pragma unroll
-          for (int t2 = 0; t2 < 2; ++t2) {
-            int e = (e0 + 2 * j + t2) % hh;
-            float inv = 1.0f / powf(10000.f, (float)(2 * e) / (float)hd);
-            float sn, cs;
-            sincosf(pos * inv, &sn, &cs);
-            float mine = t2 ? a.y : a.x, other = t2 ? b.y : b.x;
-            r[t2] = first ? mine * cs - other * sn : other * sn + mine * cs;
-          }
-          p[j] = pack_bf16(r[0], r[1]);
+          const float c0 = cs[(long long)t * hh + eb + 2 * j], c1 = cs[(long long)t * hh + eb + 2 * j + 1];
+          const float s0 = sn[(long long)t * hh + eb + 2 * j] * sign, s1 = sn[(long long)t * hh + eb + 2 * j + 1] * sign;
+          const float r0 = first ? a.x * c0 - b.x * s0 : b.x * s0 + a.x * c0;
+          const float r1 = first ? a.y * c1 - b.y * s1 : b.y * s1 + a.y * c1;
+          p[j] = pack_bf16(r0, r1);
         }
       }
     }
     *reinterpret_cast<uint4*>(out + off) = u;
   }
 }
-torch::Tensor rope_qk(torch::Tensor qkv, double sign, bool half) {
+torch::Tensor rope_qk(torch::Tensor qkv, torch::Tensor cos, torch::Tensor sin, double sign, bool half) {
   const c10::cuda::CUDAGuard guard(qkv.device());
   TORCH_CHECK(qkv.dim() == 5 && qkv.size(2) == 3 && qkv.is_contiguous() && qkv.scalar_type() == torch::kBFloat16,
               "rope_qk: (B,T,3,H,hd) bf16 contiguous");
   const int B = qkv.size(0), T = qkv.size(1), H = qkv.size(3), hd = qkv.size(4);
   TORCH_CHECK(hd % 16 == 0, "rope_qk: head dim % 16");
+  TORCH_CHECK(cos.is_contiguous() && sin.is_contiguous() && cos.scalar_type() == torch::kFloat32 && cos.size(0) >= T &&
+              cos.size(1) == hd / 2 && sin.sizes() == cos.sizes(), "rope_qk: cos/sin tables (T, hd/2) fp32");
   auto out = torch::empty_like(qkv);
   long long n = (long long)B * T * 3 * H * hd / 8;
   if (n) rope_qk_kernel<<<ew_grid(n, 256), 256, 0, cur_stream()>>>(
-      reinterpret_cast<const bf16*>(qkv.data_ptr()), reinterpret_cast<bf16*>(out.data_ptr()), (long long)B * T, T, H, hd,
-      (float)sign, half ? 1 : 0);
+      reinterpret_cast<const bf16*>(qkv.data_ptr()), reinterpret_cast<bf16*>(out.data_ptr()), cos.data_ptr<float>(),
+      sin.data_ptr<float>(), (long long)B * T, T, H, hd, (float)sign, half ? 1 : 0);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+// out = x (fp32) + y (bf16): the residual add of a block's bf16 branch output onto the fp32 stream.
+__global__ void resid_add_kernel(const float* __restrict__ x, const bf16* __restrict__ y, float* __restrict__ out, long long n4) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 a = reinterpret_cast<const float4*>(x)[i];
+    float4 b = ld4(y + i * 4);
+    reinterpret_cast<float4*>(out)[i] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+  }
+}
+torch::Tensor resid_add(torch::Tensor x, torch::Tensor y) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.scalar_type() == torch::kFloat32 &&
+              y.scalar_type() == torch::kBFloat16 && x.numel() == y.numel() && x.numel() % 4 == 0, "resid_add: fp32 + bf16");
+  auto out = torch::empty_like(x);
+  long long n4 = x.numel() / 4;
+  if (n4) resid_add_kernel<<<ew_grid(n4, 256), 256, 0, cur_stream()>>>(x.data_ptr<float>(),
+      reinterpret_cast<const bf16*>(y.data_ptr()), out.data_ptr<float>(), n4);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return out;
 }

@@ -109,7 +109,7 @@ class LightBlock(nn.Module):
             v = qkv[:, :, 2] + (g * self.cur_ve.view(B, T, self.heads, hd)).to(qkv.dtype)
             qkv = torch.stack([qkv[:, :, 0], qkv[:, :, 1], v], 2)
         a = ops.attention(qkv, window, self.rope_half, qk_norm="qk" in self.blk)
-        x = x + ops.linear(a, self.o.weight).to(x.dtype)
+        x = ops.resid_add(x, ops.linear(a, self.o.weight))
         if hasattr(self, "moe"):
             return x + self.moe(ops.rmsnorm(x, self.n2.weight, self.n2.eps))
         if self.cur_sel is not None:                      # opaque tokens only: FFN skipped where the talker is sure
@@ -118,7 +118,7 @@ class LightBlock(nn.Module):
             y = ops.linear(self._act(ops.linear(xs, self.up.weight)), self.down.weight) * ok[..., None].to(dt)
             return x.scatter_add(1, idx[..., None].expand(-1, -1, D), y.to(x.dtype))
         n2 = ops.rmsnorm(x, self.n2.weight, self.n2.eps, out_dtype=dt)
-        return x + ops.linear(self._act(ops.linear(n2, self.up.weight)), self.down.weight).to(x.dtype)
+        return ops.resid_add(x, ops.linear(self._act(ops.linear(n2, self.up.weight)), self.down.weight))
 
 
 class DenseFFN(nn.Module):

@@ -104,7 +104,7 @@ class AnchorMoE(nn.Module):
 
     def _route(self, x, surprise):
         N, d = x.shape[0] * x.shape[1], x.shape[-1]
-        xf = ops.rmsnorm(x, self.norm.weight, self.norm.eps).reshape(N, d)
+        xf = ops.rmsnorm(x, self.norm.weight, self.norm.eps, out_dtype=_cdt(x)).reshape(N, d)
         real = (surprise.reshape(N) >= 0) if surprise is not None else torch.ones(N, dtype=torch.bool, device=x.device)
         if self.budget and surprise is not None:
             s = surprise.reshape(N).float().clamp(min=0)
@@ -124,11 +124,10 @@ class AnchorMoE(nn.Module):
     def forward(self, x, surprise=None):
         xf, table, wtab, flat_idx, C = self._route(x, surprise)
         N, d = xf.shape
-        xd = xf.to(_cdt(x))
-        xe = ops.slot_gather(xd, table, flat_idx).view(self.E, C, d)
+        xe = ops.slot_gather(xf, table, flat_idx).view(self.E, C, d)
         ye = self._experts(xe, wtab, C)
         out = ops.combine(ye.reshape(self.E * C, d), wtab.to(ye.dtype), flat_idx, table, N)
-        return x + out.view_as(x).to(x.dtype)
+        return ops.resid_add(x, out.view_as(x))
 
     # ------------------------------------------------------------------------------------------ experts
     def _ffn(self, xe, up, down, train_w=True):

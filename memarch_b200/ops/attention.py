@@ -20,19 +20,33 @@ from . import _ext, ref
 ATTN_CORE = os.environ.get("MEMARCH_ATTN", "lib")
 
 
+_tables = {}
+
+
+def rope_tables(T, hd, device):
+    """(T, hd/2) fp32 cos / sin tables, built once per (T, hd, device)."""
+    key = (T, hd, str(device))
+    if key not in _tables:
+        cos, sin = ref.rope_angles(T, hd, device)
+        _tables[key] = (cos.contiguous(), sin.contiguous())
+    return _tables[key]
+
+
 class _RopeQK(torch.autograd.Function):
     """Rotate the q and k slices of qkv (B,T,3,H,hd); v passes through.  Backward rotates the grads back."""
 
     @staticmethod
     def forward(ctx, qkv, half):
         ctx.half = half
+        cos, sin = rope_tables(qkv.shape[1], qkv.shape[4], qkv.device)
         _ext.count()
-        return _ext.C().rope_qk(qkv.contiguous(), 1.0, bool(half))
+        return _ext.C().rope_qk(qkv.contiguous(), cos, sin, 1.0, bool(half))
 
     @staticmethod
     def backward(ctx, g):
+        cos, sin = rope_tables(g.shape[1], g.shape[4], g.device)
         _ext.count()
-        return _ext.C().rope_qk(g.contiguous(), -1.0, bool(ctx.half)), None
+        return _ext.C().rope_qk(g.contiguous(), cos, sin, -1.0, bool(ctx.half)), None
 
 
 class _OwnAttn(torch.autograd.Function):
@@ -85,7 +99,7 @@ def attention(qkv, window=None, rope_half=False, qk_norm=False):
         if ATTN_CORE == "own" and hd in (64, 128):
             o = _OwnAttn.apply(r, win if win is not None else 0)
             return o.reshape(B, T, H * hd)
-        q, k, v = (r[:, :, i].transpose(1, 2) for i in range(3))
+        q, k, v = r.permute(2, 0, 3, 1, 4).unbind(0)          # one stacked gradient instead of three zero-filled ones
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _lib_window(q, k, v, win)
         return o.transpose(1, 2).reshape(B, T, H * hd)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]

@@ -91,6 +91,26 @@ def swiglu(gu):
     return ref.swiglu(gu)
 
 
+class _ResidAdd(torch.autograd.Function):
+    """fp32 residual stream + bf16 branch output in one pass; the branch gets its gradient in bf16."""
+
+    @staticmethod
+    def forward(ctx, x, y):
+        _ext.count()
+        return _ext.C().resid_add(x.contiguous(), y.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, g.to(torch.bfloat16)
+
+
+def resid_add(x, y):
+    """x + y with x the residual stream and y a block's branch output."""
+    if _ext.use_cuda(x) and x.dtype == torch.float32 and y.dtype == torch.bfloat16 and x.numel() % 4 == 0:
+        return _ResidAdd.apply(x, y)
+    return x + y.to(x.dtype)
+
+
 # ------------------------------------------------------------------------------------------------ GEMM
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, accumulate=False, epi=0,
          aux=None, out2=None, groups=1):

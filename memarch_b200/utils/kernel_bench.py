@@ -1,0 +1,170 @@
+"""Kernel micro-benchmarks with parity checks (the role of the reference's bench_fused.py:48-107).
+
+    python -m memarch_b200.utils.kernel_bench gemm --m 8192 --n 8192 --k 8192
+    python -m memarch_b200.utils.kernel_bench ce --rows 8192 --d 2064 --vocab 50304
+    python -m memarch_b200.utils.kernel_bench instinct --kind hs3 --shape 8,2048,6144
+    python -m memarch_b200.utils.kernel_bench experts --e 8 --c 2049 --d 2048 --h 6144
+
+Each command checks the kernel against the PyTorch fp32 statement on the same inputs, then times it with CUDA events
+after warm-up (inputs larger than L2, or an L2 flush between iterations) and prints achieved TFLOP/s or GB/s next to
+the measured peaks in MEASURED_PEAKS.json when that file is present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def timeit(fn, iters=10, warm=3, flush=True):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def report(name, ms, flops=None, nbytes=None, extra=""):
+    hbm, tf, src = peaks()
+    s = f"{name}: {ms:.3f} ms"
+    if flops:
+        a = flops / ms / 1e9
+        s += f"  {a:.0f} TFLOP/s = {a / tf:.2f} of {src} cuBLAS bf16 {tf:.0f}"
+    if nbytes:
+        a = nbytes / ms / 1e6
+        s += f"  {a:.0f} GB/s = {a / hbm:.2f} of {src} copy {hbm:.0f}"
+    print(s + ("  " + extra if extra else ""), flush=True)
+
+
+def cmd_gemm(a):
+    from memarch_b200.ops import gemm
+    M, N, K, G = a.m, a.n, a.k, a.groups
+    A = torch.randn(G, M, K, device="cuda").bfloat16()
+    B = torch.randn(G, N, K, device="cuda").bfloat16()
+    Bm = B.transpose(1, 2).contiguous() if a.b_mn else B
+    Am = A.transpose(1, 2).contiguous() if a.a_mn else A
+    out = torch.empty(G, M, N, device="cuda", dtype=torch.bfloat16)
+    run = lambda: gemm(Am, Bm, a_mn=a.a_mn, b_mn=a.b_mn, out=out, groups=G)
+    run()
+    ref = torch.bmm(A[:1, :256].float(), B[:1].float().transpose(1, 2))
+    print(f"parity (first 256 rows) rel err {rel(out[:1, :256], ref):.2e}")
+    fl = 2.0 * M * N * K * G
+    report(f"tcgen05 gemm M{M} N{N} K{K} G{G} a_mn={int(a.a_mn)} b_mn={int(a.b_mn)}", timeit(run, a.iters, flush=not a.no_flush), fl)
+    if not a.no_lib:
+        report("library bmm (same shape)", timeit(lambda: torch.bmm(A, B.transpose(1, 2), out=out), a.iters, flush=not a.no_flush), fl)
+
+
+def cmd_ce(a):
+    from memarch_b200 import ops
+    from memarch_b200.ops import ref
+    N, d, V = a.rows, a.d, a.vocab
+    h = torch.randn(N, d, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(V, d, device="cuda") * 0.02).bfloat16().requires_grad_()
+    y = torch.randint(0, V, (N,), device="cuda")
+    g = torch.rand(N, device="cuda") * 0.3 if a.mix else None
+    hit = (torch.rand(N, device="cuda") > 0.7).float() if a.mix else None
+    loss = ops.linear_ce(h, w, y, gate=g, hit=hit)
+    n = min(N, 512)
+    tot, gh, gw, _, _, _ = ref.linear_ce(h[:n].detach().float(), w.detach().float(), y[:n], None, g[:n] if a.mix else None,
+                                         hit[:n] if a.mix else None)
+    l2 = ops.linear_ce(h[:n].detach().requires_grad_(), w, y[:n], gate=g[:n] if a.mix else None, hit=hit[:n] if a.mix else None)
+    print(f"parity ({n} rows) loss rel err {abs(l2.item() - tot.item()) / tot.item():.2e}")
+    fl = 6.0 * N * d * V
+    report(f"fused linear+CE{'+mix' if a.mix else ''} fwd (grads made in forward) N{N} d{d} V{V}",
+           timeit(lambda: ops.linear_ce(h, w, y, gate=g, hit=hit), a.iters, flush=False), fl)
+
+
+def cmd_instinct(a):
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim import Instinct
+    shape = tuple(int(s) for s in a.shape.split(","))
+    p = (torch.randn(*shape, device="cuda") * 0.05).to(torch.bfloat16 if a.bf16 else torch.float32).requires_grad_()
+    opt = Instinct([p], OptConfig(lr=1e-3, norm="hs", scale=0.12, m_bf16=True, rel_every=1 << 30))
+    g = torch.randn_like(p)
+    opt.prepare(torch.tensor(3.0, device="cuda"), torch.randn(64, device="cuda"))
+    kind = opt.spec(p)[0]
+    n = p.numel()
+    per = (2 if a.bf16 else 4) * 2 + 2 * 2 + (8 if a.bf16 else 0)       # minimal traffic: g, p r/w, m r/w, master r/w
+    report(f"instinct step kind={kind} shape={shape}", timeit(lambda: opt.update(p, g), a.iters), nbytes=float(n) * per,
+           extra=f"(algorithmic {per} B/weight, one pass)")
+
+
+def cmd_experts(a):
+    from memarch_b200 import ops
+    E, C, d, H = a.e, a.c, a.d, a.h
+    x = torch.randn(E, C, d, device="cuda").bfloat16().requires_grad_()
+    up = (torch.randn(E, d, H, device="cuda") * d ** -0.5).bfloat16().requires_grad_()
+    down = (torch.randn(E, H, d, device="cuda") * H ** -0.5).bfloat16().requires_grad_()
+    y = ops.expert_ffn(x, up, down, "relu2")
+    yr = torch.bmm(torch.relu(torch.bmm(x[:1].float(), up[:1].float())) ** 2, down[:1].float())
+    print(f"parity (expert 0) rel err {rel(y[:1], yr):.2e}")
+    go = torch.randn_like(y)
+
+    def fb():
+        x.grad = up.grad = down.grad = None
+        ops.expert_ffn(x, up, down, "relu2").backward(go)
+    report(f"expert FFN relu2 fwd+bwd E{E} C{C} d{d} H{H}", timeit(fb, a.iters), 3 * 2 * 2.0 * E * C * d * H)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=8192); g.add_argument("--groups", type=int, default=1)
+    g.add_argument("--a-mn", dest="a_mn", action="store_true"); g.add_argument("--b-mn", dest="b_mn", action="store_true")
+    g.add_argument("--no-lib", action="store_true"); g.add_argument("--no-flush", action="store_true")
+    c = sub.add_parser("ce")
+    c.add_argument("--rows", type=int, default=8192); c.add_argument("--d", type=int, default=2064)
+    c.add_argument("--vocab", type=int, default=50304); c.add_argument("--mix", action="store_true")
+    i = sub.add_parser("instinct")
+    i.add_argument("--shape", default="8,2048,6144"); i.add_argument("--bf16", action="store_true", default=True)
+    e = sub.add_parser("experts")
+    e.add_argument("--e", type=int, default=8); e.add_argument("--c", type=int, default=2049)
+    e.add_argument("--d", type=int, default=2048); e.add_argument("--h", type=int, default=6144)
+    for p in (g, c, i, e):
+        p.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    sys.path.insert(0, ROOT)
+    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    main()

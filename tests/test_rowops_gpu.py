@@ -51,13 +51,13 @@ def test_rope_roundtrip_and_reference(half):
     from memarch_b200.ops import _ext, ref
     C = _ext.C()
     qkv = torch.randn(2, 96, 3, 4, 64, device="cuda").bfloat16()
-    r = C.rope_qk(qkv, 1.0, half)
     cos, sin = ref.rope_angles(96, 64, "cuda")
+    r = C.rope_qk(qkv, cos, sin, 1.0, half)
     for s in range(2):
         want = ref.apply_rope(qkv[:, :, s].float().permute(0, 2, 1, 3), cos, sin, half).permute(0, 2, 1, 3)
         assert _rel(r[:, :, s], want) < 1e-2
     assert torch.equal(r[:, :, 2], qkv[:, :, 2])
-    back = C.rope_qk(r, -1.0, half)
+    back = C.rope_qk(r, cos, sin, -1.0, half)
     assert _rel(back[:, :, :2], qkv[:, :, :2]) < 2e-2
 
 

@@ -15,7 +15,7 @@ from . import _ext, ref
 
 # Which library multiplies the *plain* linears (qkv/o/up/down of the light blocks).  The fused paths (experts,
 # output head, attention, optimizer) always run this package's kernels.  "tc" = our tcgen05 GEMM, "lib" = cuBLAS.
-PLAIN_GEMM = os.environ.get("MEMARCH_PLAIN_GEMM", "tc")
+PLAIN_GEMM = os.environ.get("MEMARCH_PLAIN_GEMM", "lib")
 
 
 # ------------------------------------------------------------------------------------------------ RMSNorm

@@ -1,0 +1,266 @@
+"""Fused compute + collective paths over NVLink 5 / NVSwitch peer memory (one process per GPU).
+
+Expert parallelism (replaces the two all-to-alls around the expert FFN, full2.py:1137-1156):
+  * every rank writes its dispatched anchors `xe (E, C, d)` into a symmetric buffer;
+  * the up-GEMM of the rank that owns expert e reads its A tiles straight from the owners' buffers (one TMA tensor map
+    per source GPU, plain non-multicast loads) - the dispatch all-to-all happens inside the GEMM's operand fetch;
+  * the down-GEMM's epilogue stores each result row into the symmetric output buffer of the GPU that owns the token -
+    the combine all-to-all happens inside the GEMM's epilogue;
+  * backward mirrors it: the output gradients are pulled from the owners (peer copies), the input gradient rows are
+    pushed to the owners by the dgrad GEMM's epilogue.
+Data parallelism (replaces reduce-scatter + all-gather of FSDP, fastloop.py:269-307):
+  * a weight's gradient is staged in a symmetric buffer from its grad-ready hook; on a side stream a one-shot kernel
+    reduces each rank's slice across all GPUs and broadcasts the mean (NVLS `multimem.ld_reduce` / `multimem.st` when
+    the switch offers multicast, plain peer loads/stores otherwise), then the Instinct kernels step the weight while
+    backward continues on the main stream.
+Every device-side wait is bounded (`wait_ms`); a timeout sets a status word that `check()` turns into an exception.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+from ..ops.basic import gemm
+
+
+class SymmetricHeap:
+    """Symmetric allocations (same size on every rank) with peer pointers, and the bounded barrier on symmetric flags."""
+
+    def __init__(self, rank, world, group=None, wait_ms=4000.0):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.sm = symm_mem
+        self.rank, self.W, self.wait_ms = rank, world, wait_ms
+        self.group = group or dist.group.WORLD
+        self.gname = self.group.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(self.gname)
+        except Exception:     # noqa: BLE001 - newer torch enables groups implicitly
+            pass
+        self.flags, self.flag_hdl = self.alloc((256,), torch.int32, zero=True)
+        self.flag_ptrs = [int(p) for p in self.flag_hdl.buffer_ptrs]
+        self.epoch = {}
+        dist.barrier(group=self.group)
+
+    def alloc(self, shape, dtype, zero=False):
+        t = self.sm.empty(*shape, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        if zero:
+            t.zero_()
+        hdl = self.sm.rendezvous(t, self.gname)
+        return t, hdl
+
+    def barrier(self, channel=0):
+        """Device-side barrier on the current stream: all ranks' earlier writes are visible afterwards."""
+        e = self.epoch.get(channel, 0) + 1
+        self.epoch[channel] = e
+        _ext.C().peer_barrier(self.flag_ptrs, self.rank, channel, e, float(self.wait_ms))
+        _ext.count()
+
+    def check(self):
+        st = _ext.C().peer_status_read()
+        if st:
+            raise RuntimeError(f"peer wait timed out (status {st}): a rank did not reach the barrier within {self.wait_ms} ms")
+
+
+class _FusedExpertFFN(torch.autograd.Function):
+    """xe (E, C, d) on every rank -> ye (E, C, d): experts sharded over ranks, tokens moved by the GEMMs themselves."""
+
+    @staticmethod
+    def forward(ctx, xe, up, down, ep, key, act, g_off, n_local, train_w):
+        heap, W, r = ep.heap, ep.W, ep.rank
+        E, Cn, d = xe.shape
+        C = _ext.C()
+        X, Xh, Y, Yh = ep.layer_buffers(key, E, Cn, d)
+        X.copy_(xe)
+        heap.barrier(0)                                             # every rank's anchors are in place
+        H = up.shape[2]
+        M = W * Cn
+        h = torch.empty(n_local, M, H, device=xe.device, dtype=torch.bfloat16)
+        a = torch.empty_like(h) if act == "relu2" else None
+        xptrs = [int(p) for p in Xh.buffer_ptrs]
+        if act == "relu2":
+            C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, h, [], 0, 0, 0, a, None, 1, n_local)
+        else:
+            a = C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, None, [], 0, 0, 0, None, None, 0, n_local)
+            h = C.swiglu_fwd(a)
+        # down-GEMM: A = h, cut into W row segments; segment s goes to rank s's output buffer
+        hp = h.data_ptr()
+        Hh = h.shape[2]
+        a_ptrs = [hp + s * Cn * Hh * 2 for s in range(W)]
+        yptrs = [int(p) for p in Yh.buffer_ptrs]
+        C.gemm_peer(a_ptrs, Cn, Hh, n_local, Hh, M * Hh, 0, down, True, None, yptrs, d, Cn * d, g_off, None, None, 0, n_local)
+        _ext.count(3)
+        heap.barrier(0)                                             # every expert's rows have landed here
+        ctx.save_for_backward(up, down, a, h)
+        ctx.ep, ctx.key, ctx.act, ctx.g_off, ctx.n_local, ctx.train_w = ep, key, act, g_off, n_local, train_w
+        ctx.shape = (E, Cn, d)
+        return Y.view_as(Y)
+
+    @staticmethod
+    def backward(ctx, dy):
+        up, down, a, h = ctx.saved_tensors
+        ep, act, g_off, nl = ctx.ep, ctx.act, ctx.g_off, ctx.n_local
+        heap, W, r = ep.heap, ep.W, ep.rank
+        E, Cn, d = ctx.shape
+        C = _ext.C()
+        X, Xh, _, _ = ep.layer_buffers(ctx.key, E, Cn, d)
+        DY, DYh, DX, DXh = ep.grad_buffers(E, Cn, d)
+        DY.copy_(dy)
+        heap.barrier(0)
+        M = W * Cn
+        # pull the rows of my experts from their owners once; every local GEMM reads the local copy
+        dy_all = torch.empty(nl, M, d, device=dy.device, dtype=torch.bfloat16)
+        xe_all = torch.empty(nl, M, d, device=dy.device, dtype=torch.bfloat16) if ctx.train_w else None
+        for s in range(W):
+            src = DYh.get_buffer(s, (E, Cn, d), torch.bfloat16)
+            dy_all[:, s * Cn:(s + 1) * Cn].copy_(src[g_off:g_off + nl])
+            if xe_all is not None:
+                srcx = Xh.get_buffer(s, (E, Cn, d), torch.bfloat16)
+                xe_all[:, s * Cn:(s + 1) * Cn].copy_(srcx[g_off:g_off + nl])
+        if act == "relu2":
+            da = gemm(dy_all, down, epi=2, aux=a, groups=nl)
+        else:
+            da = C.swiglu_bwd(gemm(dy_all, down, groups=nl), a)
+        dup = ddown = None
+        if ctx.train_w:
+            ddown = gemm(h, dy_all, a_mn=True, b_mn=True, groups=nl)
+            dup = gemm(xe_all, da, a_mn=True, b_mn=True, groups=nl)
+        # dxe = da . up^T, rows pushed to the owners of the tokens
+        Hh = da.shape[2]
+        a_ptrs = [da.data_ptr() + s * Cn * Hh * 2 for s in range(W)]
+        dxptrs = [int(p) for p in DXh.buffer_ptrs]
+        C.gemm_peer(a_ptrs, Cn, Hh, nl, Hh, M * Hh, 0, up, False, None, dxptrs, d, Cn * d, g_off, None, None, 0, nl)
+        _ext.count()
+        heap.barrier(0)
+        return DX.clone(), dup, ddown, None, None, None, None, None, None
+
+
+class FusedExpertExchange:
+    """`ep_engine` of AnchorMoE in fused mode."""
+
+    def __init__(self, heap):
+        self.heap, self.W, self.rank = heap, heap.W, heap.rank
+        self._layers, self._grads = {}, {}
+
+    def layer_buffers(self, key, E, C, d):
+        k = (key, E, C, d)
+        if k not in self._layers:
+            X, Xh = self.heap.alloc((E, C, d), torch.bfloat16)
+            Y, Yh = self.heap.alloc((E, C, d), torch.bfloat16)
+            self._layers[k] = (X, Xh, Y, Yh)
+        return self._layers[k]
+
+    def grad_buffers(self, E, C, d):
+        k = (E, C, d)
+        if k not in self._grads:
+            DY, DYh = self.heap.alloc((E, C, d), torch.bfloat16)
+            DX, DXh = self.heap.alloc((E, C, d), torch.bfloat16)
+            self._grads[k] = (DY, DYh, DX, DXh)
+        return self._grads[k]
+
+    def ffn(self, moe, xe):
+        W, r = self.W, self.rank
+        if xe.dtype != torch.bfloat16:
+            xe = xe.to(torch.bfloat16)
+        key = id(moe)
+        if getattr(moe, "bank", False) and moe.has_F:
+            # learning experts L (global ids 0..nL-1 in slot order) and frozen ones: two grouped launches per GEMM
+            nL, nF = len(moe.L), len(moe.Fz)
+            assert moe.L == list(range(nL)) and moe.Fz == list(range(nL, nL + nF)), "fused EP expects banks in id order"
+            El, Fl = nL // W, nF // W
+            yL = _FusedExpertFFN.apply(xe, moe.up, moe.down, self, (key, "L"), moe.act, r * El, El, True)
+            yF = _FusedExpertFFN.apply(xe, moe._bank_weights("up"), moe._bank_weights("down"), self, (key, "F"), moe.act,
+                                       nL + r * Fl, Fl, False)
+            sel = torch.arange(moe.E, device=xe.device)[:, None, None] < nL
+            return torch.where(sel, yL, yF)
+        El = moe.E // W
+        return _FusedExpertFFN.apply(xe, moe.up, moe.down, self, key, moe.act, r * El, El, True)
+
+
+class FusedGradReduce:
+    """Data-parallel gradient mean fused with the optimizer step, on a side stream that overlaps backward."""
+
+    def __init__(self, heap, nvls=True, bucket_bytes=1 << 30):
+        self.heap, self.W, self.rank = heap, heap.W, heap.rank
+        self.stream = torch.cuda.Stream()
+        self.cap = bucket_bytes
+        self.gin, self.gin_h = heap.alloc((self.cap,), torch.uint8)
+        self.gout, self.gout_h = heap.alloc((self.cap,), torch.uint8)
+        self.in_ptrs = [int(p) for p in self.gin_h.buffer_ptrs]
+        self.out_ptrs = [int(p) for p in self.gout_h.buffer_ptrs]
+        mc_ok = nvls and os.environ.get("MEMARCH_NVLS", "1") == "1"
+        try:
+            self.mc_in = int(self.gin_h.multicast_ptr) if mc_ok else 0
+            self.mc_out = int(self.gout_h.multicast_ptr) if mc_ok else 0
+        except Exception:     # noqa: BLE001
+            self.mc_in = self.mc_out = 0
+        self.offsets = {}
+        self.top = 0
+        self.small = []
+        self.trainer = None
+        self.used = False
+
+    def _region(self, p, grad):
+        k = id(p)
+        if k not in self.offsets:
+            n = grad.numel() * grad.element_size()
+            n = (n + 255) // 256 * 256
+            if self.top + n > self.cap:
+                raise RuntimeError("gradient staging buffer too small; raise bucket_bytes")
+            self.offsets[k] = self.top
+            self.top += n
+        return self.offsets[k]
+
+    def grad_ready(self, p, grad):
+        """From the weight's grad-ready hook (main stream).  Returns None: the step is made on the side stream."""
+        if grad.numel() % 8 or grad.numel() < 4096 or grad.dtype not in (torch.bfloat16, torch.float32):
+            self.small.append((p, grad))
+            return None
+        off = self._region(p, grad)
+        es = grad.element_size()
+        n = grad.numel()
+        stage = self.gin[off:off + n * es].view(grad.dtype).view(grad.shape)
+        stage.copy_(grad)                                            # main stream: gradient into symmetric staging
+        ev = torch.cuda.Event()
+        ev.record()
+        C = _ext.C()
+        heap = self.heap
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(ev)
+            heap.barrier(1)                                          # every rank has staged this weight's gradient
+            C.peer_allreduce(self.in_ptrs, self.out_ptrs, self.mc_in, self.mc_out, off // es, n, grad.dtype == torch.bfloat16,
+                             self.rank, 1.0 / self.W)
+            _ext.count()
+            heap.barrier(1)                                          # every slice of the mean has landed here
+            red = self.gout[off:off + n * es].view(grad.dtype).view(grad.shape)
+            self.trainer.opt.update(p, red, synced=True)
+        self.used = True
+        return None
+
+    def flush(self):
+        if self.small:
+            flat = torch.cat([g.reshape(-1).float() for _, g in self.small])
+            dist.all_reduce(flat, group=self.heap.group)
+            flat /= self.W
+            off = 0
+            for p, g in self.small:
+                n = g.numel()
+                self.trainer.opt.update(p, flat[off:off + n].view_as(g).to(g.dtype), synced=True)
+                off += n
+            self.small.clear()
+        if self.used:
+            torch.cuda.current_stream().wait_stream(self.stream)
+            self.used = False
+
+
+class FusedParallel:
+    def __init__(self, engine, wait_ms=None):
+        wait_ms = wait_ms or float(os.environ.get("MEMARCH_PEER_WAIT_MS", 4000))
+        self.heap = SymmetricHeap(engine.rank, engine.W, engine.group, wait_ms)
+        self.ep = FusedExpertExchange(self.heap)
+        self.dp = FusedGradReduce(self.heap)
+
+    def attach(self, trainer):
+        self.dp.trainer = trainer

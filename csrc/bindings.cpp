@@ -15,6 +15,7 @@ int64_t peer_status_read();
 void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,
                     int64_t numel, bool is_bf16, int64_t rank, double scale);
 void gemm_set_desc_override(std::vector<int64_t> v);
+void gemm_set_pair(bool on);
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16);
 std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd);
 torch::Tensor relu2_fwd(torch::Tensor a);
@@ -23,6 +24,7 @@ torch::Tensor swiglu_fwd(torch::Tensor gu);
 torch::Tensor swiglu_bwd(torch::Tensor dh, torch::Tensor gu);
 torch::Tensor rope_qk(torch::Tensor qkv, torch::Tensor cos, torch::Tensor sin, double sign, bool half);
 torch::Tensor resid_add(torch::Tensor x, torch::Tensor y);
+torch::Tensor rope_merge_bwd(torch::Tensor dq, torch::Tensor dk, torch::Tensor dv, torch::Tensor cos, torch::Tensor sin, bool half);
 void ce_rows(torch::Tensor logits, torch::Tensor y, torch::Tensor loss, c10::optional<torch::Tensor> gate,
              c10::optional<torch::Tensor> hit, c10::optional<torch::Tensor> dg);
 torch::Tensor gather_rows(torch::Tensor src, torch::Tensor table, c10::optional<torch::Tensor> scale);
@@ -40,6 +42,7 @@ std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_k
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &mb::gemm, "tcgen05 GEMM C = A * B^T (bf16, fp32 accumulate in TMEM)");
   m.def("gemm_status", &mb::gemm_status, "read and clear the GEMM status word (0 = ok)");
+  m.def("gemm_set_pair", &mb::gemm_set_pair, "switch the CTA-pair (cta_group::2) GEMM kernel on or off");
   m.def("gemm_set_desc_override", &mb::gemm_set_desc_override, "test hook: shared-memory descriptor geometry");
   m.def("gemm_peer", &mb::gemm_peer, "segmented GEMM: A tiles from peer buffers, result rows to the owners' buffers");
   m.def("peer_barrier", &mb::peer_barrier, "bounded device-side barrier over symmetric flags");
@@ -53,6 +56,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd", &mb::swiglu_bwd);
   m.def("rope_qk", &mb::rope_qk);
   m.def("resid_add", &mb::resid_add);
+  m.def("rope_merge_bwd", &mb::rope_merge_bwd);
   m.def("ce_rows", &mb::ce_rows);
   m.def("gather_rows", &mb::gather_rows);
   m.def("gather_sum_rows", &mb::gather_sum_rows);

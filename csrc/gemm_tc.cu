@@ -61,6 +61,120 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& g, 
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
+// Drain one accumulator tile (this warp's 32 TMEM lanes x 256 columns) through the fused epilogue to global memory.
+// `row_l` = this thread's row inside M-segment `seg`; `taddr` = TMEM address of the warp's lanes, column 0 of the tile.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, int g, int seg, int row_l, int nt, uint32_t taddr) {
+  const bool row_ok = row_l < p.seg_M;
+  const int row = seg * p.seg_M + row_l;                                  // row of the local (M, N) problem
+  // where the result goes: the local output, or the buffer of the GPU that owns this segment's tokens
+  char* const obase = reinterpret_cast<char*>(p.out_seg_on ? p.out_seg[seg] : p.out);
+  const long long orow = p.out_seg_on ? row_l : row;
+  const long long og = g + p.out_g_off;
+  if (p.epi == EPI_SWIGLU) {
+    const int H = p.N >> 1;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rg[32], ru[32];
+      __syncwarp();
+      tmem_ld32(taddr + c * 32, rg);
+      tmem_ld32(taddr + 128 + c * 32, ru);
+      tmem_ld_wait();
+      const int col0 = nt * 128 + c * 32;
+      if (row_ok && col0 < H) {
+        bf16* o = reinterpret_cast<bf16*>(obase) + og * p.out_gs + orow * p.ldo + col0;
+        bf16* o2 = p.out2 ? reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0
+                          : nullptr;
+        const int nv = min(32, H - col0);
+        for (int j = 0; j < nv; ++j) {
+          float gg = __uint_as_float(rg[j]), uu = __uint_as_float(ru[j]);
+          // operands rounded to bf16 first so forward and the recomputing backward see the same numbers
+          float gr = __bfloat162float(__float2bfloat16(gg)), ur = __bfloat162float(__float2bfloat16(uu));
+          o[j] = __float2bfloat16(silu_f(gr) * ur);
+          if (o2) { o2[j] = __float2bfloat16(gg); o2[H + j] = __float2bfloat16(uu); }
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      __syncwarp();                              // tcgen05.ld is warp-collective: reconverge after the stores
+      tmem_ld32(taddr + c * 32, r);
+      tmem_ld_wait();
+      const int col0 = nt * BN + c * 32;
+      if (row_ok && col0 < p.N) {
+      const int nv = min(32, p.N - col0);
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      if (p.epi == EPI_RELU2) {
+        bf16* o2 = reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0;
+        if (nv == 32) {
+          uint4* d4 = reinterpret_cast<uint4*>(o2);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            d4[j] = make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                               pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
+        } else {
+          for (int j = 0; j < nv; ++j) o2[j] = __float2bfloat16(v[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float a = __bfloat162float(__float2bfloat16(v[j]));     // activation of the stored (rounded) value
+          a = fmaxf(a, 0.f);
+          v[j] = a * a;
+        }
+      } else if (p.epi == EPI_DRELU2) {
+        const bf16* ax = reinterpret_cast<const bf16*>(p.aux) + g * p.aux_gs + static_cast<long long>(row) * p.ldaux + col0;
+        if (nv == 32) {
+          const uint4* a4 = reinterpret_cast<const uint4*>(ax);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 u = a4[j];
+            float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
+            v[8 * j + 0] *= 2.f * fmaxf(f0.x, 0.f); v[8 * j + 1] *= 2.f * fmaxf(f0.y, 0.f);
+            v[8 * j + 2] *= 2.f * fmaxf(f1.x, 0.f); v[8 * j + 3] *= 2.f * fmaxf(f1.y, 0.f);
+            v[8 * j + 4] *= 2.f * fmaxf(f2.x, 0.f); v[8 * j + 5] *= 2.f * fmaxf(f2.y, 0.f);
+            v[8 * j + 6] *= 2.f * fmaxf(f3.x, 0.f); v[8 * j + 7] *= 2.f * fmaxf(f3.y, 0.f);
+          }
+        } else {
+          for (int j = 0; j < nv; ++j) v[j] *= 2.f * fmaxf(__bfloat162float(ax[j]), 0.f);
+        }
+      } else if (p.epi == EPI_ROWSCALE) {
+        const float s = reinterpret_cast<const float*>(p.aux)[g * p.aux_gs + row];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= s;
+      }
+      if (p.out_f32) {
+        float* o = reinterpret_cast<float*>(obase) + og * p.out_gs + orow * p.ldo + col0;
+        if (nv == 32) {
+          float4* o4 = reinterpret_cast<float4*>(o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            if (p.accumulate) { float4 y = o4[j]; x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
+            o4[j] = x;
+          }
+        } else {
+          for (int j = 0; j < nv; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
+        }
+      } else {
+        bf16* o = reinterpret_cast<bf16*>(obase) + og * p.out_gs + orow * p.ldo + col0;
+        if (nv == 32) {
+          uint4* o4 = reinterpret_cast<uint4*>(o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            o4[j] = make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                               pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
+        } else {
+          for (int j = 0; j < nv; ++j) o[j] = __float2bfloat16(v[j]);
+        }
+      }
+      }
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -200,116 +314,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
       tc_fence_after();
       const int seg = mt / p.tiles_per_seg;
       const int row_l = (mt - seg * p.tiles_per_seg) * BM + q * 32 + lane;     // row inside its segment
-      const bool row_ok = row_l < p.seg_M;
-      const int row = seg * p.seg_M + row_l;                                  // row of the local (M, N) problem
-      // where the result goes: the local output, or the buffer of the GPU that owns this segment's tokens
-      char* const obase = reinterpret_cast<char*>(p.out_seg_on ? p.out_seg[seg] : p.out);
-      const long long orow = p.out_seg_on ? row_l : row;
-      const long long og = g + p.out_g_off;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      if (p.epi == EPI_SWIGLU) {
-        const int H = p.N >> 1;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rg[32], ru[32];
-          __syncwarp();
-          tmem_ld32(taddr + c * 32, rg);
-          tmem_ld32(taddr + 128 + c * 32, ru);
-          tmem_ld_wait();
-          const int col0 = nt * 128 + c * 32;
-          if (row_ok && col0 < H) {
-            bf16* o = reinterpret_cast<bf16*>(obase) + og * p.out_gs + orow * p.ldo + col0;
-            bf16* o2 = p.out2 ? reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0
-                              : nullptr;
-            const int nv = min(32, H - col0);
-            for (int j = 0; j < nv; ++j) {
-              float gg = __uint_as_float(rg[j]), uu = __uint_as_float(ru[j]);
-              // operands rounded to bf16 first so forward and the recomputing backward see the same numbers
-              float gr = __bfloat162float(__float2bfloat16(gg)), ur = __bfloat162float(__float2bfloat16(uu));
-              o[j] = __float2bfloat16(silu_f(gr) * ur);
-              if (o2) { o2[j] = __float2bfloat16(gg); o2[H + j] = __float2bfloat16(uu); }
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          __syncwarp();                              // tcgen05.ld is warp-collective: reconverge after the stores
-          tmem_ld32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = nt * BN + c * 32;
-          if (row_ok && col0 < p.N) {
-          const int nv = min(32, p.N - col0);
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (p.epi == EPI_RELU2) {
-            bf16* o2 = reinterpret_cast<bf16*>(p.out2) + g * p.out2_gs + static_cast<long long>(row) * p.ldo2 + col0;
-            if (nv == 32) {
-              uint4* d4 = reinterpret_cast<uint4*>(o2);
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                d4[j] = make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
-                                   pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
-            } else {
-              for (int j = 0; j < nv; ++j) o2[j] = __float2bfloat16(v[j]);
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float a = __bfloat162float(__float2bfloat16(v[j]));     // activation of the stored (rounded) value
-              a = fmaxf(a, 0.f);
-              v[j] = a * a;
-            }
-          } else if (p.epi == EPI_DRELU2) {
-            const bf16* ax = reinterpret_cast<const bf16*>(p.aux) + g * p.aux_gs + static_cast<long long>(row) * p.ldaux + col0;
-            if (nv == 32) {
-              const uint4* a4 = reinterpret_cast<const uint4*>(ax);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 u = a4[j];
-                float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
-                v[8 * j + 0] *= 2.f * fmaxf(f0.x, 0.f); v[8 * j + 1] *= 2.f * fmaxf(f0.y, 0.f);
-                v[8 * j + 2] *= 2.f * fmaxf(f1.x, 0.f); v[8 * j + 3] *= 2.f * fmaxf(f1.y, 0.f);
-                v[8 * j + 4] *= 2.f * fmaxf(f2.x, 0.f); v[8 * j + 5] *= 2.f * fmaxf(f2.y, 0.f);
-                v[8 * j + 6] *= 2.f * fmaxf(f3.x, 0.f); v[8 * j + 7] *= 2.f * fmaxf(f3.y, 0.f);
-              }
-            } else {
-              for (int j = 0; j < nv; ++j) v[j] *= 2.f * fmaxf(__bfloat162float(ax[j]), 0.f);
-            }
-          } else if (p.epi == EPI_ROWSCALE) {
-            const float s = reinterpret_cast<const float*>(p.aux)[g * p.aux_gs + row];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= s;
-          }
-          if (p.out_f32) {
-            float* o = reinterpret_cast<float*>(obase) + og * p.out_gs + orow * p.ldo + col0;
-            if (nv == 32) {
-              float4* o4 = reinterpret_cast<float4*>(o);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                if (p.accumulate) { float4 y = o4[j]; x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
-                o4[j] = x;
-              }
-            } else {
-              for (int j = 0; j < nv; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
-            }
-          } else {
-            bf16* o = reinterpret_cast<bf16*>(obase) + og * p.out_gs + orow * p.ldo + col0;
-            if (nv == 32) {
-              uint4* o4 = reinterpret_cast<uint4*>(o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                o4[j] = make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
-                                   pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
-            } else {
-              for (int j = 0; j < nv; ++j) o[j] = __float2bfloat16(v[j]);
-            }
-          }
-          }
-        }
-      }
+      epilogue_tile(p, g, seg, row_l, nt, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -319,6 +324,164 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
 
   tc_fence_before();
   __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ CTA-pair kernel
+// Same GEMM with tcgen05.mma.cta_group::2: a cluster of two CTAs (two SMs) computes a 256x256 tile.  Each CTA stages
+// its own 128 rows of A and its own 128-row half of the B tile, so every SM pulls 32 KB per k-block instead of
+// 48 KB for the same FLOPs; the leader CTA's single thread issues the MMAs for both, accumulators live in each
+// CTA's own TMEM (128 lanes x 256 columns, double-buffered), each CTA runs its own epilogue on its rows.
+// TMA loads carry no multicast: both CTAs fetch their own tiles; only the completion bytes are counted on the
+// leader's barrier, and tcgen05.commit arrives on the barriers of both CTAs.
+constexpr int STAGES2 = 6, BH_BYTES = 128 * BK * 2, STAGE2_BYTES = A_BYTES + BH_BYTES;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  uint64_t* empty = full + STAGES2;
+  uint64_t* tfull = empty + STAGES2;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int total = p.G * p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tmAs.m[i]);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  cluster_sync_all();                         // both CTAs' barriers exist before anyone arrives on a peer's barrier
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0 && tmem_base != 0) atomicCAS(p.status, 0, ST_BAD_ARG);   // the pair must share one TMEM address
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += npairs) {
+        int g, mt, nt;
+        tile_coords(t, p, g, mt, nt);
+        const int seg = mt / p.tiles_per_seg;
+        const int m0 = (mt - seg * p.tiles_per_seg) * 256 + (int)rank * BM;
+        const CUtensorMap* tA = &tmAs.m[seg];
+        const int ga = g + p.a_g_off;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
+          }
+          uint8_t* sA = smem + stage * STAGE2_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          const uint32_t lfull = mapa_shared(smem_u32(&full[stage]), 0);      // the leader's barrier
+          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE2_BYTES);          // bytes of both CTAs
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_3d_pair(sA, tA, lfull, k0, m0, ga);
+          } else {
+            tma_load_3d_pair(sA, tA, lfull, m0, k0, ga);
+            tma_load_3d_pair(sA + 8192, tA, lfull, m0 + 64, k0, ga);
+          }
+          // this CTA's half of the B tile: N rows [nb, nb + 128)
+          const int nb = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt * 128 : (p.N >> 1) + nt * 128) : nt * BN + (int)rank * 128;
+          if (!B_MN) {
+            tma_load_3d_pair(sB, &tmB, lfull, k0, nb, g);
+          } else {
+            tma_load_3d_pair(sB, &tmB, lfull, nb, k0, g);
+            tma_load_3d_pair(sB + 8192, &tmB, lfull, nb + 64, k0, g);
+          }
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      const uint32_t idesc = idesc_bf16(256, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += npairs) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            atomicCAS(p.status, 0, ST_WAIT_FULL); *abort_flag = 1; ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE2_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t ad = smem_desc_sw128(sA + k * p.kstep_a, p.lbo_a, p.sbo_a);
+            uint64_t bd = smem_desc_sw128(sB + k * p.kstep_b, p.lbo_b, p.sbo_b);
+            umma_bf16_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 3);       // frees this stage in both CTAs
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull[acc], 3);           // accumulators of both CTAs complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = pair; t < total && ok; t += npairs) {
+      int g, mt, nt;
+      tile_coords(t, p, g, mt, nt);
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+        if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_TMEM_FULL); *abort_flag = 1; }
+        ok = false; break;
+      }
+      tc_fence_after();
+      const int seg = mt / p.tiles_per_seg;
+      const int row_l = (mt - seg * p.tiles_per_seg) * 256 + (int)rank * BM + q * 32 + lane;
+      epilogue_tile(p, g, seg, row_l, nt, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));   // the leader's MMA thread waits on it
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();                         // no CTA leaves while its pair may still touch its barriers or TMEM
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -381,6 +544,18 @@ int gemm_status(int device) {
   return v;
 }
 
+// The CTA-pair (cta_group::2) kernel is the default for tiles of >= 256 rows; MEMARCH_GEMM_PAIR=0 or
+// gemm_set_pair(false) selects the single-CTA kernel everywhere.
+static int g_pair = -1;
+static bool use_pair_kernel() {
+  if (g_pair < 0) {
+    const char* e = std::getenv("MEMARCH_GEMM_PAIR");
+    g_pair = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pair == 1;
+}
+void gemm_set_pair(bool on) { g_pair = on ? 1 : 0; }
+
 static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};   // test hook: lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b
 void gemm_set_desc_override(std::vector<int64_t> v) {
   for (int i = 0; i < 6; ++i) g_desc_override[i] = i < (int)v.size() ? (int)v[i] : -1;
@@ -398,10 +573,12 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
     tmAs.m[i] = a_mn ? make_tmap_bf16(A_list[i], seg_M, K, a_groups, a_rows_pitch, a_gs, 64, 64)
                      : make_tmap_bf16(A_list[i], K, seg_M, a_groups, a_rows_pitch, a_gs, 64, BM);
   for (int i = n_seg; i < 8; ++i) tmAs.m[i] = tmAs.m[0];
-  p.n_seg = n_seg; p.seg_M = seg_M; p.tiles_per_seg = (seg_M + BM - 1) / BM;
+  const bool pair = use_pair_kernel() && seg_M >= 256;
+  const int tile_m = pair ? 256 : BM;
+  p.n_seg = n_seg; p.seg_M = seg_M; p.tiles_per_seg = (seg_M + tile_m - 1) / tile_m;
   const bool sw = p.epi == EPI_SWIGLU;
   CUtensorMap tmB = b_mn ? make_tmap_bf16(B, N, K, G, b_rows_pitch, b_gs, 64, 64)
-                         : make_tmap_bf16(B, K, N, G, b_rows_pitch, b_gs, 64, sw ? 128 : BN);
+                         : make_tmap_bf16(B, K, N, G, b_rows_pitch, b_gs, 64, (sw || pair) ? 128 : BN);
   p.m_tiles = n_seg * p.tiles_per_seg;
   p.n_tiles = sw ? ((N / 2) + 127) / 128 : (N + BN - 1) / BN;
   p.lbo_a = a_mn ? BK * 128 : 0;  p.sbo_a = 1024;  p.kstep_a = a_mn ? UMMA_K * 128 : UMMA_K * 2;
@@ -411,22 +588,30 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
     p.lbo_b = g_desc_override[3]; p.sbo_b = g_desc_override[4]; p.kstep_b = g_desc_override[5];
   }
   const int total = G * p.m_tiles * p.n_tiles;
-  int grid = std::min(total, max_ctas);
+  int grid = pair ? 2 * std::min(total, max_ctas / 2) : std::min(total, max_ctas);
   if (grid <= 0) return;
-  auto launch = [&](auto kern) {
-    static bool attr_set[4] = {false, false, false, false};
-    int id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+  const int smem_bytes = pair ? SMEM2_BYTES : SMEM_BYTES;
+  auto launch = [&](auto kern, int id) {
+    static bool attr_set[8] = {false, false, false, false, false, false, false, false};
     if (!attr_set[id]) {
-      TORCH_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess,
+      TORCH_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) == cudaSuccess,
                   "cannot raise dynamic shared memory for the GEMM kernel");
       attr_set[id] = true;
     }
-    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmAs, tmB, p);
+    kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, p);
   };
-  if (!a_mn && !b_mn) launch(gemm_tc_kernel<false, false>);
-  else if (!a_mn && b_mn) launch(gemm_tc_kernel<false, true>);
-  else if (a_mn && !b_mn) launch(gemm_tc_kernel<true, false>);
-  else launch(gemm_tc_kernel<true, true>);
+  const int id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+  if (pair) {
+    if (!a_mn && !b_mn) launch(gemm_tc2_kernel<false, false>, 4 + id);
+    else if (!a_mn && b_mn) launch(gemm_tc2_kernel<false, true>, 4 + id);
+    else if (a_mn && !b_mn) launch(gemm_tc2_kernel<true, false>, 4 + id);
+    else launch(gemm_tc2_kernel<true, true>, 4 + id);
+  } else {
+    if (!a_mn && !b_mn) launch(gemm_tc_kernel<false, false>, id);
+    else if (!a_mn && b_mn) launch(gemm_tc_kernel<false, true>, id);
+    else if (a_mn && !b_mn) launch(gemm_tc_kernel<true, false>, id);
+    else launch(gemm_tc_kernel<true, true>, id);
+  }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

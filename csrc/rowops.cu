@@ -318,6 +318,78 @@ torch::Tensor rope_qk(torch::Tensor qkv, torch::Tensor cos, torch::Tensor sin, d
   return out;
 }
 
+// Backward of "rotate q,k and split qkv": the three gradients arrive as separate (B,H,T,hd) tensors with arbitrary
+// batch/head/token strides (last dim contiguous); q and k grads are rotated back and all three are written into one
+// packed (B,T,3,H,hd) gradient - replaces stack + contiguous + rope-backward by one pass.
+struct Src3 { const bf16* p[3]; long long sb[3], sh[3], st[3]; };
+__global__ void rope_merge_bwd_kernel(Src3 src, bf16* __restrict__ out, const float* __restrict__ cs,
+                                      const float* __restrict__ sn, long long BT, int T, int H, int hd, int half) {
+  const int per_tok = 3 * H * hd / 8;
+  const int g_per_head = hd / 8;
+  const int hh = hd / 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < BT * per_tok;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long tok = i / per_tok;
+    int rem = (int)(i - tok * per_tok);
+    const int s = rem / (H * g_per_head);
+    rem -= s * H * g_per_head;
+    const int h = rem / g_per_head, gi = rem % g_per_head;
+    const long long b = tok / T;
+    const int t = (int)(tok - b * T);
+    const bf16* base = src.p[s] + b * src.sb[s] + h * src.sh[s] + (long long)t * src.st[s];
+    uint4 u = *reinterpret_cast<const uint4*>(base + gi * 8);
+    if (s < 2) {
+      uint32_t* p = reinterpret_cast<uint32_t*>(&u);
+      if (!half) {
+        const float4 c4 = *reinterpret_cast<const float4*>(cs + (long long)t * hh + gi * 4);
+        const float4 s4 = *reinterpret_cast<const float4*>(sn + (long long)t * hh + gi * 4);
+        const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {-s4.x, -s4.y, -s4.z, -s4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16(p[j]);
+          p[j] = pack_bf16(f.x * c[j] - f.y * sv[j], f.x * sv[j] + f.y * c[j]);
+        }
+      } else {
+        const int e0 = gi * 8;
+        const bool first = e0 < hh;
+        uint4 m = *reinterpret_cast<const uint4*>(base + (first ? e0 + hh : e0 - hh));
+        uint32_t* q = reinterpret_cast<uint32_t*>(&m);
+        const int eb = first ? e0 : e0 - hh;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 a = unpack_bf16(p[j]), bb = unpack_bf16(q[j]);
+          const float c0 = cs[(long long)t * hh + eb + 2 * j], c1 = cs[(long long)t * hh + eb + 2 * j + 1];
+          const float s0 = -sn[(long long)t * hh + eb + 2 * j], s1 = -sn[(long long)t * hh + eb + 2 * j + 1];
+          const float r0 = first ? a.x * c0 - bb.x * s0 : bb.x * s0 + a.x * c0;
+          const float r1 = first ? a.y * c1 - bb.y * s1 : bb.y * s1 + a.y * c1;
+          p[j] = pack_bf16(r0, r1);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = u;
+  }
+}
+torch::Tensor rope_merge_bwd(torch::Tensor dq, torch::Tensor dk, torch::Tensor dv, torch::Tensor cos, torch::Tensor sin, bool half) {
+  const c10::cuda::CUDAGuard guard(dq.device());
+  torch::Tensor g[3] = {dq, dk, dv};
+  const int B = dq.size(0), H = dq.size(1), T = dq.size(2), hd = dq.size(3);
+  Src3 src;
+  for (int i = 0; i < 3; ++i) {
+    TORCH_CHECK(g[i].dim() == 4 && g[i].scalar_type() == torch::kBFloat16 && g[i].stride(3) == 1 && g[i].size(2) == T,
+                "rope_merge_bwd: (B,H,T,hd) bf16 with contiguous last dim");
+    TORCH_CHECK(g[i].stride(0) % 8 == 0 && g[i].stride(1) % 8 == 0 && g[i].stride(2) % 8 == 0 &&
+                (reinterpret_cast<uintptr_t>(g[i].data_ptr()) & 15) == 0, "rope_merge_bwd: 16-byte aligned rows");
+    src.p[i] = reinterpret_cast<const bf16*>(g[i].data_ptr());
+    src.sb[i] = g[i].stride(0); src.sh[i] = g[i].stride(1); src.st[i] = g[i].stride(2);
+  }
+  auto out = torch::empty({B, T, 3, H, hd}, dq.options());
+  long long n = (long long)B * T * 3 * H * hd / 8;
+  if (n) rope_merge_bwd_kernel<<<ew_grid(n, 256), 256, 0, cur_stream()>>>(src, reinterpret_cast<bf16*>(out.data_ptr()),
+      cos.data_ptr<float>(), sin.data_ptr<float>(), (long long)B * T, T, H, hd, half ? 1 : 0);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
 // out = x (fp32) + y (bf16): the residual add of a block's bf16 branch output onto the fp32 stream.
 __global__ void resid_add_kernel(const float* __restrict__ x, const bf16* __restrict__ y, float* __restrict__ out, long long n4) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {

@@ -49,6 +49,27 @@ class _RopeQK(torch.autograd.Function):
         return _ext.C().rope_qk(g.contiguous(), cos, sin, -1.0, bool(ctx.half)), None
 
 
+class _RopeSplit(torch.autograd.Function):
+    """Rotate q,k and hand q,k,v to the attention core as (B,H,T,hd) views of one packed tensor.  Backward takes the
+    three separate gradients (any batch/head/token strides), rotates back and packs them in one pass."""
+
+    @staticmethod
+    def forward(ctx, qkv, half):
+        ctx.half = half
+        cos, sin = rope_tables(qkv.shape[1], qkv.shape[4], qkv.device)
+        _ext.count()
+        r = _ext.C().rope_qk(qkv.contiguous(), cos, sin, 1.0, bool(half))
+        return r[:, :, 0].transpose(1, 2), r[:, :, 1].transpose(1, 2), r[:, :, 2].transpose(1, 2)
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        cos, sin = rope_tables(dq.shape[2], dq.shape[3], dq.device)
+        fix = lambda t: t if (t.stride(3) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.stride(2) % 8 == 0) \
+            else t.contiguous()
+        _ext.count()
+        return _ext.C().rope_merge_bwd(fix(dq), fix(dk), fix(dv), cos, sin, bool(ctx.half)), None
+
+
 class _OwnAttn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, window):
@@ -95,11 +116,11 @@ def attention(qkv, window=None, rope_half=False, qk_norm=False):
     B, T, _, H, hd = qkv.shape
     win = None if (window is None or window >= T) else int(window)
     if _ext.use_cuda(qkv) and qkv.dtype == torch.bfloat16 and not qk_norm and hd % 8 == 0:
-        r = _RopeQK.apply(qkv, rope_half)
         if ATTN_CORE == "own" and hd in (64, 128):
+            r = _RopeQK.apply(qkv, rope_half)
             o = _OwnAttn.apply(r, win if win is not None else 0)
             return o.reshape(B, T, H * hd)
-        q, k, v = r.permute(2, 0, 3, 1, 4).unbind(0)          # one stacked gradient instead of three zero-filled ones
+        q, k, v = _RopeSplit.apply(qkv, rope_half)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _lib_window(q, k, v, win)
         return o.transpose(1, 2).reshape(B, T, H * hd)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]

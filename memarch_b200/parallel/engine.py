@@ -18,6 +18,26 @@ import torch
 import torch.distributed as dist
 
 
+class _AllToAll(torch.autograd.Function):
+    """Equal-split all-to-all over dim 0 with autograd; returns a plain tensor that is complete on the current stream
+    (the functional-collectives wrapper tensor must not reach a C++ kernel: its data pointer is not the data)."""
+
+    @staticmethod
+    def forward(ctx, x, gname):
+        ctx.gname = gname
+        n = dist.get_world_size()
+        split = [x.shape[0] // n] * n
+        t = torch.ops._c10d_functional.all_to_all_single(x.contiguous(), split, split, gname)
+        return torch.ops._c10d_functional.wait_tensor(t)
+
+    @staticmethod
+    def backward(ctx, g):
+        n = dist.get_world_size()
+        split = [g.shape[0] // n] * n
+        t = torch.ops._c10d_functional.all_to_all_single(g.contiguous(), split, split, ctx.gname)
+        return torch.ops._c10d_functional.wait_tensor(t), None
+
+
 class NcclExpertExchange:
     """Expert-parallel FFN through two autograd all-to-alls (full2.py:1137-1156), extended to a sharded frozen bank."""
 
@@ -37,21 +57,20 @@ class NcclExpertExchange:
         return torch.tensor(order, device=moe.up.device), El, Fl
 
     def ffn(self, moe, xe):
-        from torch.distributed._functional_collectives import all_to_all_single_autograd
         W = self.W
         E, C, d = xe.shape
         perm, El, Fl = self._perm(moe)
-        g = self.group or dist.group.WORLD
+        gname = (self.group or dist.group.WORLD).group_name
         if perm is not None:
             xe = xe[perm]
         n = El + Fl
-        r = all_to_all_single_autograd(xe.contiguous(), None, None, g)
+        r = _AllToAll.apply(xe, gname)
         r = r.view(W, n, C, d).transpose(0, 1).reshape(n, W * C, d)
         y = moe._ffn(r[:El], moe.up, moe.down)
         if Fl:
             y = torch.cat([y, moe._ffn_frozen(r[El:])])
         y = y.view(n, W, C, d).transpose(0, 1).reshape(E, C, d).contiguous()
-        y = all_to_all_single_autograd(y, None, None, g)
+        y = _AllToAll.apply(y, gname)
         if perm is not None:
             inv = torch.empty_like(perm)
             inv[perm] = torch.arange(E, device=perm.device)
@@ -83,12 +102,20 @@ class ParallelEngine:
         for mod in model.modules():
             if isinstance(mod, AnchorMoE):
                 mod.ep_shard(self.rank, self.W, self.fused_impl.ep if self.fused_impl else self.ep)
-        for p in model.parameters():
-            if not getattr(p, "_ep_local", False):
-                dist.broadcast(p.data, 0, group=self.group)
-        for b in model.buffers():
-            if b.numel() and b.dtype.is_floating_point:
-                dist.broadcast(b.data, 0, group=self.group)
+        def bcast(t):
+            if t.is_contiguous():
+                dist.broadcast(t, 0, group=self.group)
+            else:
+                c = t.contiguous()
+                dist.broadcast(c, 0, group=self.group)
+                t.copy_(c)
+        if self.W > 1:
+            for p in model.parameters():
+                if not getattr(p, "_ep_local", False):
+                    bcast(p.data)
+            for b in model.buffers():
+                if b.numel() and b.dtype.is_floating_point:
+                    bcast(b.data)
 
     def attach(self, trainer):
         self.trainer = trainer
@@ -101,8 +128,9 @@ class ParallelEngine:
         """One small all-reduce: mean loss, true batch-mean situation vector and the shared anchor threshold."""
         tau = model.tau if hasattr(model, "tau") else loss.new_zeros(())
         buf = torch.cat([loss.reshape(1).float(), tau.reshape(1).float(), sit.float().reshape(-1)])
-        dist.all_reduce(buf, group=self.group)
-        buf /= self.W
+        if self.W > 1:
+            dist.all_reduce(buf, group=self.group)
+            buf /= self.W
         if hasattr(model, "tau"):
             model.tau.copy_(buf[1])
         return buf[0], buf[2:]
@@ -115,10 +143,12 @@ class ParallelEngine:
     def grad_sync(self, p, grad):
         """Called by the optimizer from the weight's grad-ready hook.  Expert weights are rank-local.  Replicated
         weights: average over ranks.  Returns the gradient to step with, or None when the step is deferred."""
-        if getattr(p, "_ep_local", False) or self.W == 1:
+        if getattr(p, "_ep_local", False):
             return grad
-        if self.fused_impl is not None:
+        if self.fused_impl is not None:            # also with one rank: the same kernels run against this GPU's own buffers
             return self.fused_impl.dp.grad_ready(p, grad)
+        if self.W == 1:
+            return grad
         if grad.numel() < self.SMALL:
             self.small.append((p, grad))
             return None

@@ -182,10 +182,25 @@ class FusedExpertExchange:
 class FusedGradReduce:
     """Data-parallel gradient mean fused with the optimizer step, on a side stream that overlaps backward."""
 
-    def __init__(self, heap, nvls=True, bucket_bytes=1 << 30):
+    def __init__(self, heap, nvls=True):
         self.heap, self.W, self.rank = heap, heap.W, heap.rank
         self.stream = torch.cuda.Stream()
-        self.cap = bucket_bytes
+        self.nvls = nvls
+        self.offsets = {}
+        self.top = 0
+        self.small = []
+        self.trainer = None
+        self.used = False
+        self.cap = 0
+
+    def allocate(self, params):
+        """Symmetric staging (each rank's gradient) and result (the rank mean) regions for every replicated weight."""
+        heap, nvls = self.heap, self.nvls
+        cap = 0
+        for p in params:
+            if not getattr(p, "_ep_local", False):
+                cap += (p.numel() * p.element_size() + 255) // 256 * 256
+        self.cap = max(cap, 256)
         self.gin, self.gin_h = heap.alloc((self.cap,), torch.uint8)
         self.gout, self.gout_h = heap.alloc((self.cap,), torch.uint8)
         self.in_ptrs = [int(p) for p in self.gin_h.buffer_ptrs]
@@ -196,11 +211,6 @@ class FusedGradReduce:
             self.mc_out = int(self.gout_h.multicast_ptr) if mc_ok else 0
         except Exception:     # noqa: BLE001
             self.mc_in = self.mc_out = 0
-        self.offsets = {}
-        self.top = 0
-        self.small = []
-        self.trainer = None
-        self.used = False
 
     def _region(self, p, grad):
         k = id(p)
@@ -208,7 +218,7 @@ class FusedGradReduce:
             n = grad.numel() * grad.element_size()
             n = (n + 255) // 256 * 256
             if self.top + n > self.cap:
-                raise RuntimeError("gradient staging buffer too small; raise bucket_bytes")
+                raise RuntimeError("gradient staging buffer too small for this weight")
             self.offsets[k] = self.top
             self.top += n
         return self.offsets[k]
@@ -264,3 +274,4 @@ class FusedParallel:
 
     def attach(self, trainer):
         self.dp.trainer = trainer
+        self.dp.allocate(trainer.params)

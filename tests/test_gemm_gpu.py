@@ -26,16 +26,21 @@ SHAPES = [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (2049, 2048, 2048),
 @pytest.mark.parametrize("M,N,K", SHAPES)
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 def test_gemm_matches_fp32(M, N, K, a_mn, b_mn):
+    """Single-CTA kernel (the pair kernel has its own test below)."""
     from memarch_b200.ops import gemm
     C = _ext()
+    C.gemm_set_pair(False)
     if a_mn and M % 8:
         pytest.skip("an MN-major operand is stored (K, M): its row pitch M*2 bytes must be a multiple of 16")
     A = _mk((M, K), seed=1)
     B = _mk((N, K), seed=2)
     a = A.t().contiguous() if a_mn else A
     b = B.t().contiguous() if b_mn else B
-    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
-    torch.cuda.synchronize()
+    try:
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        torch.cuda.synchronize()
+    finally:
+        C.gemm_set_pair(True)
     assert C.gemm_status(0) == 0
     ref = A.float() @ B.float().t()
     assert _rel(out, ref) < 1e-2, (_rel(out, ref), out[:2, :4], ref[:2, :4])
@@ -101,3 +106,50 @@ def test_linear_autograd_matches_torch():
     (xr @ wr.t()).backward(go.float())
     assert _rel(y, xr @ wr.t()) < 1e-2
     assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (2049, 2048, 2048), (4096, 50304, 128), (264, 264, 200)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_pair_kernel_matches_fp32(M, N, K, a_mn, b_mn):
+    """cta_group::2 kernel (two SMs per 256x256 tile) on the same checks as the single-CTA kernel."""
+    from memarch_b200.ops import gemm
+    C = _ext()
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    A, B = _mk((M, K), seed=21), _mk((N, K), seed=22)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    C.gemm_set_pair(True)
+    try:
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        torch.cuda.synchronize()
+        st = C.gemm_status(0)
+    finally:
+        C.gemm_set_pair(True)
+    assert st == 0
+    assert _rel(out, A.float() @ B.float().t()) < 1e-2
+
+
+def test_pair_kernel_grouped_epilogues():
+    from memarch_b200.ops import gemm
+    C = _ext()
+    E, Cn, d, H = 3, 600, 256, 512
+    x, up = _mk((E, Cn, d), seed=23), _mk((E, d, H), 0.1, seed=24)
+    C.gemm_set_pair(True)
+    try:
+        h = torch.empty(E, Cn, H, device="cuda", dtype=torch.bfloat16)
+        a = torch.empty_like(h)
+        gemm(x, up, b_mn=True, out=h, out2=a, epi=1, groups=E)
+        hs = torch.empty(E, Cn, H // 2, device="cuda", dtype=torch.bfloat16)
+        gu = torch.empty_like(h)
+        gemm(x, up, b_mn=True, out=hs, out2=gu, epi=3, groups=E)
+        torch.cuda.synchronize()
+        st = C.gemm_status(0)
+    finally:
+        C.gemm_set_pair(True)
+    assert st == 0
+    acc = torch.bmm(x.float(), up.float())
+    assert _rel(a, acc) < 1e-2 and _rel(h, torch.relu(a.float()) ** 2) < 1e-2
+    assert _rel(gu, acc) < 1e-2
+    g, u = gu.float().chunk(2, -1)
+    assert _rel(hs, torch.nn.functional.silu(g) * u) < 1e-2

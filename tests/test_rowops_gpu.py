@@ -195,3 +195,21 @@ def test_instinct_step_matches_reference(kind, shape, wdt, mdt):
     assert _rel(p - pc, pr - pc) < tol, _rel(p - pc, pr - pc)
     assert _rel(o_gpu.m[0], o_ref.m[0]) < tol
     assert _rel(o_gpu.rel, o_ref.rel) < 1e-3
+
+
+def test_attention_matches_reference_with_grads():
+    from memarch_b200 import ops
+    from memarch_b200.ops import ref
+    torch.manual_seed(7)
+    B, T, H, hd = 2, 192, 4, 64
+    qkv = (torch.randn(B, T, 3, H, hd, device="cuda") * 0.5).bfloat16().requires_grad_()
+    for window in (None, 64):
+        qkv.grad = None
+        o = ops.attention(qkv, window)
+        go = torch.randn_like(o)
+        o.backward(go)
+        qr = qkv.detach().float().requires_grad_()
+        orf = ref.window_attention(qr[:, :, 0], qr[:, :, 1], qr[:, :, 2], window).reshape(B, T, H * hd)
+        orf.backward(go.float())
+        assert _rel(o, orf) < 2e-2, window
+        assert _rel(qkv.grad, qr.grad) < 3e-2, window

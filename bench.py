@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--corpus-tokens", type=int, default=8_000_000)
     ap.add_argument("--phrase-k", type=int, default=262144)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", type=int, default=1, help="replay the step as a CUDA graph after 3 eager steps (0 = eager)")
     ap.add_argument("--wave", type=int, default=0, help="frozen bank experts per layer added to the 8 learning ones")
     return ap.parse_args()
 
@@ -226,7 +227,7 @@ def run_ours(args):
     if world > 1:
         from memarch_b200.parallel import ParallelEngine
         parallel = ParallelEngine(rank, world, local, fused=args.mode == "fused")
-    tr = Trainer(model, tcfg, ocfg, stage="ABX", parallel=parallel)
+    tr = Trainer(model, tcfg, ocfg, stage="ABX", parallel=parallel, graph=bool(args.graph))
     toks = np.load(os.path.join(tag, "tokens.npy"))
     store = TokenStore(toks, seed=1 + rank, device=dev)
     losses = []
@@ -258,7 +259,7 @@ def run_ours(args):
         emit(args, "ours", world, ms, e2e, clocks, int(per_step_launches * args.steps),
              {"parallelism": f"dp{world}+ep{world}" if world > 1 else "single", "mode": args.mode if world > 1 else "single",
               "loss_first": round(first, 4), "loss_last": round(last, 4), "kernel_status": st,
-              "launches_per_step": round(per_step_launches, 1), "wave_frozen_experts": args.wave,
+              "launches_per_step": round(per_step_launches, 1), "cuda_graph": bool(args.graph) and not tr._graph_failed, "wave_frozen_experts": args.wave,
               "params_b": round(sum(p.numel() for p in model.parameters()) / 1e9, 3),
               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
               "stats": {k: round(float(v), 4) for k, v in model.stats.items()}})

@@ -10,14 +10,16 @@ torch::Tensor gemm_peer(std::vector<int64_t> a_ptrs, int64_t seg_M, int64_t K, i
                         int64_t a_gs, int64_t a_g_off, torch::Tensor b, bool b_mn, c10::optional<torch::Tensor> out_local,
                         std::vector<int64_t> out_ptrs, int64_t out_ld, int64_t out_gs, int64_t out_g_off,
                         c10::optional<torch::Tensor> out2, c10::optional<torch::Tensor> aux, int64_t epi, int64_t groups);
-void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, int64_t epoch, double timeout_ms);
+void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, double timeout_ms);
 int64_t peer_status_read();
 void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,
                     int64_t numel, bool is_bf16, int64_t rank, double scale);
 void gemm_set_desc_override(std::vector<int64_t> v);
 void gemm_set_pair(bool on);
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16);
-std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd);
+std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd,
+                                       c10::optional<torch::Tensor> add, bool want_lo);
+std::vector<torch::Tensor> add_rmsnorm_fwd(torch::Tensor x, torch::Tensor y, torch::Tensor w, double eps);
 torch::Tensor relu2_fwd(torch::Tensor a);
 torch::Tensor relu2_bwd(torch::Tensor dh, torch::Tensor a);
 torch::Tensor swiglu_fwd(torch::Tensor gu);
@@ -50,6 +52,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_allreduce", &mb::peer_allreduce, "one-shot all-reduce by peer loads/stores or NVLS multimem");
   m.def("rmsnorm_fwd", &mb::rmsnorm_fwd);
   m.def("rmsnorm_bwd", &mb::rmsnorm_bwd);
+  m.def("add_rmsnorm_fwd", &mb::add_rmsnorm_fwd);
   m.def("relu2_fwd", &mb::relu2_fwd);
   m.def("relu2_bwd", &mb::relu2_bwd);
   m.def("swiglu_fwd", &mb::swiglu_fwd);

@@ -60,11 +60,9 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
   else if (kind == KIND_ROW) { TORCH_CHECK(p.dim() >= 2); R = p.size(0); C = numel / R; }
   a.E = E; a.R = R; a.C = C;
   if (a.frozen) a.frozen_stride = numel / frozen_->numel();
-  // scratch: [rowsqA E*R][rowsqB E*R][colsqA E*C][colsqB E*C][rowabs E*R][rel 2]
-  auto scratch = torch::zeros({3 * E * R + 2 * E * C + 2}, p.options().dtype(torch::kFloat32));
-  float* s = scratch.data_ptr<float>();
   float* rel = (rel_.has_value() && rel_->defined()) ? rel_->data_ptr<float>() + index : nullptr;
-  return instinct_launch(a, (int)kind, s, rel, cur_stream());
+  auto scratch = torch::zeros({instinct_scratch_floats(E, R, C)}, p.options().dtype(torch::kFloat32));
+  return instinct_launch(a, (int)kind, scratch.data_ptr<float>(), rel, cur_stream());
 }
 
 }  // namespace mb

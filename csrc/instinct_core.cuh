@@ -147,6 +147,11 @@ __global__ void instinct_stat_cols(InstinctArgs a, const float* __restrict__ csc
   for (int j = 0; j < VEC; ++j) atomicAdd(colsq_out + e * a.C + c + j, acc[j]);
 }
 
+// rel_out = |g| / |w| from the two sums of squares
+static __global__ void instinct_rel_final(const float* __restrict__ rel2, float* __restrict__ rel_out) {
+  *rel_out = sqrtf(rel2[0]) / (sqrtf(rel2[1]) + 1e-8f);
+}
+
 // sums for |g|/|w|: rel2[0] += sum g^2, rel2[1] += sum w^2 (before the update)
 static __global__ void instinct_rel_sums(InstinctArgs a, float* __restrict__ rel2) {
   __shared__ float red[32];
@@ -270,16 +275,23 @@ __global__ void instinct_apply(InstinctArgs a, const float* __restrict__ rscale,
   }
 }
 
-// Launch sequence.  scratch (fp32, zeroed): [rowA E*R][rowB E*R][rowabs E*R][colA E*C][colB E*C][rel 2].
-// Returns the number of kernels launched.
+// Scratch layout (fp32, zeroed, 16-byte aligned base): [rowA][rowB][rowabs] of pad4(E*R) each, [colA][colB] of
+// pad4(E*C) each, [rel 4]; every sub-array starts on a 16-byte boundary because the kernels read them as float4.
+inline long long instinct_pad4(long long n) { return (n + 3) & ~3ll; }
+inline long long instinct_scratch_floats(long long E, long long R, long long C) {
+  return 3 * instinct_pad4(E * R) + 2 * instinct_pad4(E * C) + 4;
+}
+
+// Launch sequence; returns the number of kernels launched.
 inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, float* rel_out, cudaStream_t st) {
   const long long ER = a.E * a.R, EC = a.E * a.C, n = ER * a.C;
+  const long long ERp = instinct_pad4(ER), ECp = instinct_pad4(EC);
   float* rowA = scratch;
-  float* rowB = rowA + ER;
-  float* rowabs = rowB + ER;
-  float* colA = rowabs + ER;
-  float* colB = colA + EC;
-  float* rel2 = colB + EC;
+  float* rowB = rowA + ERp;
+  float* rowabs = rowB + ERp;
+  float* colA = rowabs + ERp;
+  float* colB = colA + ECp;
+  float* rel2 = colB + ECp;
   const bool vec = (a.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.p) & 15) == 0) &&
                    ((reinterpret_cast<uintptr_t>(a.g) & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.m) & 15) == 0) &&
                    (a.w == nullptr || (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) && (EC % 4 == 0 || a.E == 1);
@@ -309,11 +321,12 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
   };
   auto apply = [&](const float* rs, const float* c1, const float* c2, bool fuse, const float* rabs) {
     const size_t smem = fuse ? (size_t)a.C * sizeof(float) : 0;
+    static bool big4 = false, big1 = false;           // raise the dynamic shared-memory limit once per kernel
     if (vec) {
-      if (smem > 48 * 1024) cudaFuncSetAttribute(instinct_apply<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (smem > 48 * 1024 && !big4) { cudaFuncSetAttribute(instinct_apply<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); big4 = true; }
       instinct_apply<4><<<row_grid, row_threads, smem, st>>>(a, rs, c1, c2, fuse ? 1 : 0, rabs, rel2, rel_out);
     } else {
-      if (smem > 48 * 1024) cudaFuncSetAttribute(instinct_apply<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (smem > 48 * 1024 && !big1) { cudaFuncSetAttribute(instinct_apply<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); big1 = true; }
       instinct_apply<1><<<row_grid, row_threads, smem, st>>>(a, rs, c1, c2, fuse ? 1 : 0, rabs, rel2, rel_out);
     }
     ++launches;

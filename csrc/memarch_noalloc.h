@@ -15,7 +15,7 @@
  *
  * Limits and rules
  *   - Scratch: a file-scope __device__ array of MEMARCH_NOALLOC_SCRATCH_FLOATS floats (4 MiB), present once on every
- *     GPU that loads the library until the process exits.  A call needs 3*rows + 2*cols + 8 floats of it; larger
+ *     GPU that loads the library until the process exits.  A call needs about 3*rows + 2*cols (+ up to 21) floats of it; larger
  *     problems are refused with MEMARCH_NOALLOC_TOO_LARGE and a message on stderr - nothing is launched.
  *   - The first call on a device looks up the device address of that array (cudaGetSymbolAddress, with that device
  *     current) and keeps it.  Make this first call outside of any CUDA stream capture.

@@ -28,7 +28,7 @@ extern "C" int memarch_instinct_hs_step_noalloc(void* weight, const void* grad, 
     std::fprintf(stderr, "memarch_instinct_hs_step_noalloc: bad argument (null pointer, empty shape or cols %% 4 != 0)\n");
     return MEMARCH_NOALLOC_BAD_ARG;
   }
-  const long long need = 3 * rows + 2 * cols + 8;
+  const long long need = mb::instinct_scratch_floats(1, rows, cols) + 8;   // <= 3*rows + 2*cols + 21
   if (need > (long long)MEMARCH_NOALLOC_SCRATCH_FLOATS) {
     std::fprintf(stderr,
                  "memarch_instinct_hs_step_noalloc: a %lld x %lld weight needs %lld floats of scratch, the built-in "

@@ -15,11 +15,17 @@ static inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(
 struct PeerPtrs { void* p[8]; };
 
 // ------------------------------------------------------------------------------------------------ barrier
-// flags: symmetric uint32 array per rank, slot [channel * 8 + src] counts arrivals of rank `src`.
-// Every rank adds 1 to its slot on every peer (release, system scope), then waits (acquire) until every peer's slot
-// on its own array reaches `epoch`.  The wait is bounded; on timeout status[0] = ST_WAIT_PEER and the kernel returns.
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int channel, unsigned epoch, int* status,
+// flags: symmetric uint32 array per rank, slot [channel * 8 + src] counts arrivals of rank `src`; slot
+// [128 + channel] of a rank's own array counts its own barriers on that channel (the epoch lives on the device, so a
+// captured CUDA graph replays correctly).  Every rank adds 1 to its slot on every peer (release, system scope), then
+// waits (acquire) until every peer's slot on its own array reaches the epoch.  The wait is bounded; on timeout
+// status[0] = ST_WAIT_PEER and the kernel returns.
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int channel, int* status,
                                     unsigned long long spin_limit) {
+  __shared__ unsigned epoch_sh;
+  if (threadIdx.x == 0) epoch_sh = atomicAdd(reinterpret_cast<unsigned*>(flags.p[rank]) + 128 + channel, 1u) + 1u;
+  __syncthreads();
+  const unsigned epoch = epoch_sh;
   const int q = threadIdx.x;
   if (q >= world) return;
   __threadfence_system();
@@ -46,7 +52,7 @@ static int* peer_status(int device) {
   return words[device];
 }
 
-void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, int64_t epoch, double timeout_ms) {
+void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, double timeout_ms) {
   const int W = (int)flag_ptrs.size();
   TORCH_CHECK(W >= 1 && W <= 8, "peer_barrier: 1..8 ranks");
   PeerPtrs f{};
@@ -55,7 +61,8 @@ void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel,
   cudaGetDevice(&dev);
   // one poll is ~0.2 us (64 ns sleep + a system-scope load)
   unsigned long long limit = (unsigned long long)(timeout_ms * 1e3 * 5.0);
-  peer_barrier_kernel<<<1, 32, 0, cur_stream()>>>(f, (int)rank, W, (int)channel, (unsigned)epoch, peer_status(dev), limit);
+  TORCH_CHECK(channel >= 0 && channel < 16, "peer_barrier: channel 0..15");
+  peer_barrier_kernel<<<1, 32, 0, cur_stream()>>>(f, (int)rank, W, (int)channel, peer_status(dev), limit);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

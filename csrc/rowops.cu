@@ -47,10 +47,12 @@ __global__ void rmsnorm_fwd_kernel(const TX* __restrict__ x, const float* __rest
 }
 
 // dx = r*(g*w) - x * r^3/d * sum(g*w*x); dw += g * x * r (block-local accumulation over its rows, then atomics)
+// Optional `add` (fp32, same shape): a gradient that reached x by another path (the residual stream) is summed in
+// the same pass; optional `dx_lo`: the result is also written in bf16 (the branch that produced part of x wants it).
 template <typename TX, typename TG>
 __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                                    const float* __restrict__ rstd, TX* __restrict__ dx, float* __restrict__ dw,
-                                   int n_rows, int d) {
+                                   int n_rows, int d, const float* __restrict__ add, bf16* __restrict__ dx_lo) {
   __shared__ float red[32];
   constexpr int MAXV = 8;                         // d <= 8 * 4 * blockDim.x
   float4 acc[MAXV];
@@ -77,8 +79,11 @@ __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TX* __restri
       int c = (i * blockDim.x + threadIdx.x) * 4;
       if (c < d) {
         float4 v = ld4(xr + c), g = ld4(gr + c), ww = ld4(w + c);
-        st4(dxr + c, make_float4(r * g.x * ww.x - v.x * k, r * g.y * ww.y - v.y * k, r * g.z * ww.z - v.z * k,
-                                 r * g.w * ww.w - v.w * k));
+        float4 o = make_float4(r * g.x * ww.x - v.x * k, r * g.y * ww.y - v.y * k, r * g.z * ww.z - v.z * k,
+                               r * g.w * ww.w - v.w * k);
+        if (add) { const float4 q = ld4(add + row * d + c); o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w; }
+        st4(dxr + c, o);
+        if (dx_lo) st4(dx_lo + row * d + c, o);
         acc[i].x += g.x * v.x * r; acc[i].y += g.y * v.y * r; acc[i].z += g.z * v.z * r; acc[i].w += g.w * v.w * r;
       }
     }
@@ -91,6 +96,46 @@ __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TX* __restri
       atomicAdd(dw + c + 2, acc[i].z); atomicAdd(dw + c + 3, acc[i].w);
     }
   }
+}
+
+// h = x (fp32) + y (bf16); n = rmsnorm(h) * w in bf16: the residual add and the next normalisation in one pass.
+__global__ void add_rmsnorm_fwd_kernel(const float* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ w,
+                                       float* __restrict__ h, bf16* __restrict__ n, float* __restrict__ rstd, int d, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const float* xr = x + row * d;
+  const bf16* yr = y + row * d;
+  float* hr = h + row * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float4 a = ld4(xr + c), b = ld4(yr + c);
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    st4(hr + c, a);
+    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / d + eps);
+  if (threadIdx.x == 0) rstd[row] = r;
+  bf16* nr = n + row * d;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float4 v = ld4(hr + c), g = ld4(w + c);          // each thread re-reads exactly what it wrote
+    st4(nr + c, make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w));
+  }
+}
+std::vector<torch::Tensor> add_rmsnorm_fwd(torch::Tensor x, torch::Tensor y, torch::Tensor w, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && y.is_contiguous() && x.scalar_type() == torch::kFloat32 &&
+              y.scalar_type() == torch::kBFloat16 && x.numel() == y.numel() && x.size(1) % 4 == 0, "add_rmsnorm: fp32 + bf16");
+  const int n = x.size(0), d = x.size(1);
+  torch::Tensor wf = w.scalar_type() == torch::kFloat32 ? w : w.to(torch::kFloat32);
+  auto h = torch::empty_like(x);
+  auto nn = torch::empty({n, d}, x.options().dtype(torch::kBFloat16));
+  auto rstd = torch::empty({n}, x.options().dtype(torch::kFloat32));
+  if (n) add_rmsnorm_fwd_kernel<<<n, d >= 1024 ? 256 : 128, 0, cur_stream()>>>(x.data_ptr<float>(),
+      reinterpret_cast<const bf16*>(y.data_ptr()), wf.data_ptr<float>(), h.data_ptr<float>(), reinterpret_cast<bf16*>(nn.data_ptr()),
+      rstd.data_ptr<float>(), d, (float)eps);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {h, nn, rstd};
 }
 
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16) {
@@ -113,24 +158,32 @@ std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double 
   return {y, rstd};
 }
 
-std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd) {
+std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd,
+                                       c10::optional<torch::Tensor> add_, bool want_lo) {
   const c10::cuda::CUDAGuard guard(x.device());
+  const float* add = nullptr;
+  if (add_.has_value() && add_->defined()) {
+    TORCH_CHECK(add_->scalar_type() == torch::kFloat32 && add_->is_contiguous() && add_->numel() == x.numel(), "rmsnorm_bwd: add");
+    add = add_->data_ptr<float>();
+  }
   const int n = x.size(0), d = x.size(1);
   TORCH_CHECK(d <= 8 * 4 * 256 && d % 4 == 0, "rmsnorm_bwd: d <= 8192");
   torch::Tensor wf = w.scalar_type() == torch::kFloat32 ? w : w.to(torch::kFloat32);
   auto dx = torch::empty_like(x);
   auto dw = torch::zeros({d}, x.options().dtype(torch::kFloat32));
-  if (n == 0) return {dx, dw};
+  torch::Tensor lo = want_lo ? torch::empty({n, d}, x.options().dtype(torch::kBFloat16)) : torch::Tensor();
+  bf16* lop = want_lo ? reinterpret_cast<bf16*>(lo.data_ptr()) : nullptr;
+  if (n == 0) return {dx, dw, lo};
   const int grid = std::min(n, 148 * 8);
   const bool xb = x.scalar_type() == torch::kBFloat16, gb = dy.scalar_type() == torch::kBFloat16;
 #define LAUNCH(TX, TG) rmsnorm_bwd_kernel<TX, TG><<<grid, 256, 0, cur_stream()>>>( \
       reinterpret_cast<const TG*>(dy.data_ptr()), reinterpret_cast<const TX*>(x.data_ptr()), wf.data_ptr<float>(), \
-      rstd.data_ptr<float>(), reinterpret_cast<TX*>(dx.data_ptr()), dw.data_ptr<float>(), n, d)
+      rstd.data_ptr<float>(), reinterpret_cast<TX*>(dx.data_ptr()), dw.data_ptr<float>(), n, d, add, lop)
   if (xb && gb) LAUNCH(bf16, bf16); else if (xb) LAUNCH(bf16, float);
   else if (gb) LAUNCH(float, bf16); else LAUNCH(float, float);
 #undef LAUNCH
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return {dx, dw};
+  return {dx, dw, lo};
 }
 
 // ------------------------------------------------------------------------------------------------ activations

@@ -96,29 +96,52 @@ class LightBlock(nn.Module):
     def _act(self, h):
         return ops.relu2(h) if self.relu2 else ops.swiglu(h)
 
-    def forward(self, x, window=None):
+    def forward(self, x, window=None, pending=None, defer=False):
+        """`pending`: the previous block's FFN output not yet added to the stream (added here, fused with n1).
+        `defer=True` returns (x, ffn_out) and leaves the last residual add to the next block."""
         B, T, D = x.shape
         hd = D // self.heads
         dt = _cdt(x)
         if self.cur_x0 is not None:
+            if pending is not None:
+                x, pending = ops.resid_add(x, pending), None
             x = x + self.x0_l * self.cur_x0
-        n1 = ops.rmsnorm(x, self.n1.weight, self.n1.eps, out_dtype=dt)
+        if pending is not None:
+            x, n1 = ops.add_rmsnorm(x, pending, self.n1.weight, self.n1.eps)
+        else:
+            n1 = ops.rmsnorm(x, self.n1.weight, self.n1.eps, out_dtype=dt)
         qkv = ops.linear(n1, self.qkv.weight).view(B, T, 3, self.heads, hd)
         if self.cur_ve is not None:
             g = 2 * torch.sigmoid(F.linear(x, self.ve_gate.weight.to(x.dtype)))[..., None]        # (B,T,H,1)
             v = qkv[:, :, 2] + (g * self.cur_ve.view(B, T, self.heads, hd)).to(qkv.dtype)
             qkv = torch.stack([qkv[:, :, 0], qkv[:, :, 1], v], 2)
         a = ops.attention(qkv, window, self.rope_half, qk_norm="qk" in self.blk)
-        x = ops.resid_add(x, ops.linear(a, self.o.weight))
+        fin = (lambda t: (t, None)) if defer else (lambda t: t)
+        if hasattr(self, "moe") or self.cur_sel is not None:
+            x = ops.resid_add(x, ops.linear(a, self.o.weight))
         if hasattr(self, "moe"):
-            return x + self.moe(ops.rmsnorm(x, self.n2.weight, self.n2.eps))
+            return fin(x + self.moe(ops.rmsnorm(x, self.n2.weight, self.n2.eps)))
         if self.cur_sel is not None:                      # opaque tokens only: FFN skipped where the talker is sure
             idx, ok = self.cur_sel
             xs = ops.rmsnorm(x, self.n2.weight, self.n2.eps, out_dtype=dt).gather(1, idx[..., None].expand(-1, -1, D))
             y = ops.linear(self._act(ops.linear(xs, self.up.weight)), self.down.weight) * ok[..., None].to(dt)
-            return x.scatter_add(1, idx[..., None].expand(-1, -1, D), y.to(x.dtype))
-        n2 = ops.rmsnorm(x, self.n2.weight, self.n2.eps, out_dtype=dt)
-        return ops.resid_add(x, ops.linear(self._act(ops.linear(n2, self.up.weight)), self.down.weight))
+            return fin(x.scatter_add(1, idx[..., None].expand(-1, -1, D), y.to(x.dtype)))
+        x, n2 = ops.add_rmsnorm(x, ops.linear(a, self.o.weight), self.n2.weight, self.n2.eps)
+        y = ops.linear(self._act(ops.linear(n2, self.up.weight)), self.down.weight)
+        if defer:
+            return x, y
+        return ops.resid_add(x, y)
+
+
+def run_blocks(blocks, x, window, run=None):
+    """A stack of light blocks with the residual add at each block boundary fused into the next block's norm."""
+    pending = None
+    for b in blocks:
+        if run is not None:
+            x, pending = run(b, x, window, pending, True)
+        else:
+            x, pending = b(x, window, pending, True)
+    return x if pending is None else ops.resid_add(x, pending)
 
 
 class DenseFFN(nn.Module):
@@ -149,8 +172,7 @@ class TransformerLM(nn.Module):
 
     def forward(self, x, prep=None):
         h = self.emb(x)
-        for b in self.blocks:
-            h = b(h)
+        h = run_blocks(self.blocks, h, None)
         return ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=_cdt(h)), torch.zeros((), device=x.device)
 
     def train_loss(self, out, y, train=True):

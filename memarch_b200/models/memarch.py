@@ -22,7 +22,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import ops
 from ..config import ModelConfig
 from ..ops import ref
-from .blocks import DenseFFN, LightBlock, _cdt
+from .blocks import DenseFFN, LightBlock, _cdt, run_blocks
 from .memory import CardMemory, VolumeMemory
 from .moe import AnchorMoE
 from .reread import Reread
@@ -375,8 +375,7 @@ class MemArchLM(nn.Module):
             for i, b in enumerate(lights):
                 b.cur_ve = self.ve[i](x) if "ve" in c.blk else None
                 b.cur_x0 = h if "x0" in c.blk else None
-        for b in self.light_a:
-            h = self._run(b, h, win)
+        h = run_blocks(self.light_a, h, win, self._run)
 
         seg = min(self.seg, T)
         snaps = None
@@ -386,8 +385,7 @@ class MemArchLM(nn.Module):
             h = h + reads.type_as(h)
             self.stats["mem_cards"] = st["valid"].float().sum(1).mean()
 
-        for b in self.light_b:
-            h = self._run(b, h, win)
+        h = run_blocks(self.light_b, h, win, self._run)
         lh = ops.rmsnorm(h, self.l_norm.weight, self.l_norm.eps)
 
         # surprise -> anchors: the light part's own prediction error decides where to think hard
@@ -433,8 +431,7 @@ class MemArchLM(nn.Module):
                 if self.heavy[0].wave == "still":
                     self.stats["move_r"] = sum((b.last_move / b.move_peak.clamp(min=1e-12)).min() for b in self.heavy) / L
 
-        for b in self.final:
-            h = self._run(b, h, win)
+        h = run_blocks(self.final, h, win, self._run)
 
         dt = _cdt(h)
         if c.no_mem or c.no_reread:

@@ -34,7 +34,7 @@ class _RMSNorm(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w, rstd = ctx.saved_tensors
         C = _ext.C()
-        dx, dw = C.rmsnorm_bwd(dy.reshape(x2.shape).contiguous(), x2, w.contiguous(), rstd)
+        dx, dw, _ = C.rmsnorm_bwd(dy.reshape(x2.shape).contiguous(), x2, w.contiguous(), rstd, None, False)
         _ext.count(2)
         return dx.view(ctx.shape), dw.to(w.dtype), None, None
 
@@ -48,6 +48,44 @@ def rmsnorm(x, weight, eps=None, out_dtype=None):
         return _RMSNorm.apply(x, weight, eps, want_bf16)
     y = ref.rmsnorm(x, weight, eps)
     return y.to(out_dtype or x.dtype)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """h = x + y (fp32 stream + bf16 branch) and n = rmsnorm(h)·w (bf16) in one kernel.  Backward folds the residual
+    gradient into the norm's backward pass and emits the branch's bf16 gradient from the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x, y, w, eps):
+        C = _ext.C()
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).contiguous()
+        y2 = y.reshape(-1, shape[-1]).contiguous()
+        h, n, rstd = C.add_rmsnorm_fwd(x2, y2, w.contiguous(), float(eps))
+        _ext.count()
+        ctx.save_for_backward(h, w, rstd)
+        ctx.shape = shape
+        return h.view(shape), n.view(shape)
+
+    @staticmethod
+    def backward(ctx, dh, dn):
+        h, w, rstd = ctx.saved_tensors
+        C = _ext.C()
+        if dn is None:
+            return dh, dh.to(torch.bfloat16), None, None
+        add = dh.reshape(h.shape).contiguous().float() if dh is not None else None
+        dx, dw, lo = C.rmsnorm_bwd(dn.reshape(h.shape).contiguous(), h, w.contiguous(), rstd, add, True)
+        _ext.count(2)
+        return dx.view(ctx.shape), lo.view(ctx.shape), dw.to(w.dtype), None
+
+
+def add_rmsnorm(x, y, weight, eps=None):
+    """(x + y, rmsnorm(x + y)·w): residual add fused with the following normalisation."""
+    if eps is None:
+        eps = torch.finfo(torch.float32).eps
+    if _ext.use_cuda(x) and x.dtype == torch.float32 and y.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return _AddRMSNorm.apply(x, y, weight, eps)
+    h = x + y.to(x.dtype)
+    return h, rmsnorm(h, weight, eps, out_dtype=torch.bfloat16 if x.is_cuda else None)
 
 
 # ------------------------------------------------------------------------------------------------ activations

@@ -41,7 +41,6 @@ class SymmetricHeap:
             pass
         self.flags, self.flag_hdl = self.alloc((256,), torch.int32, zero=True)
         self.flag_ptrs = [int(p) for p in self.flag_hdl.buffer_ptrs]
-        self.epoch = {}
         dist.barrier(group=self.group)
 
     def alloc(self, shape, dtype, zero=False):
@@ -53,9 +52,7 @@ class SymmetricHeap:
 
     def barrier(self, channel=0):
         """Device-side barrier on the current stream: all ranks' earlier writes are visible afterwards."""
-        e = self.epoch.get(channel, 0) + 1
-        self.epoch[channel] = e
-        _ext.C().peer_barrier(self.flag_ptrs, self.rank, channel, e, float(self.wait_ms))
+        _ext.C().peer_barrier(self.flag_ptrs, self.rank, channel, float(self.wait_ms))
         _ext.count()
 
     def check(self):

@@ -38,9 +38,12 @@ def cast_linear_weights(model, dtype=torch.bfloat16):
 
 
 class Trainer:
-    def __init__(self, model, tcfg: TrainConfig, ocfg: OptConfig = None, stage=None, parallel=None):
+    def __init__(self, model, tcfg: TrainConfig, ocfg: OptConfig = None, stage=None, parallel=None, graph=None):
         self.model, self.cfg = model, tcfg
         self.stage = stage or tcfg.stage
+        import os
+        self.graph = ("G" in self.stage or os.environ.get("MEMARCH_GRAPH") == "1") if graph is None else bool(graph)
+        self._graphs, self._graph_pool, self._eager_steps, self._graph_failed = {}, None, 0, False
         self.ocfg = ocfg or OptConfig(lr=tcfg.lr)
         self.parallel = parallel
         dev = next(model.parameters()).device
@@ -59,9 +62,14 @@ class Trainer:
             self.in_backward = "B" in st and self.ocfg.in_backward
             if parallel is not None:
                 parallel.attach(self)
+            # Graph mode runs the whole step on one private stream: the per-parameter AccumulateGrad nodes (kept alive
+            # by the hooks) remember the stream they were created on, and capture needs it to be the capturing stream.
+            self._gstream = torch.cuda.Stream() if (self.graph and dev.type == "cuda") else None
             if self.in_backward:
-                for p in self.params:
-                    p.register_post_accumulate_grad_hook(self._hook)
+                import contextlib
+                with (torch.cuda.stream(self._gstream) if self._gstream is not None else contextlib.nullcontext()):
+                    for p in self.params:
+                        p.register_post_accumulate_grad_hook(self._hook)
         elif "S" in st:
             self.opt = SurpriseAdamW(self.params, lr=tcfg.lr, betas=(0.9, 0.95), weight_decay=0.1)
             self.in_backward = False
@@ -71,6 +79,8 @@ class Trainer:
             self.in_backward = False
         self.streams = None
         self.last_loss = None
+        if not hasattr(self, "_gstream"):
+            self._gstream = None
 
     # ------------------------------------------------------------------------------------------ hooks
     def _hook(self, p):
@@ -84,7 +94,9 @@ class Trainer:
 
     def register_new_param(self, p):
         if self.in_backward:
-            p.register_post_accumulate_grad_hook(self._hook)
+            import contextlib
+            with (torch.cuda.stream(self._gstream) if self._gstream is not None else contextlib.nullcontext()):
+                p.register_post_accumulate_grad_hook(self._hook)
 
     # ------------------------------------------------------------------------------------------ loss
     def loss_fn(self, xy, prep=None):
@@ -105,18 +117,80 @@ class Trainer:
 
     # ------------------------------------------------------------------------------------------ step
     def step(self, xy, step, preps=None, lr_mul=1.0):
-        """One training step; returns the loss as a device tensor (no host sync)."""
+        """One training step; returns the loss as a device tensor (no host sync).
+
+        With stage `G` (or `graph=True`) the device work of the step - forward, backward with the weight updates in
+        its hooks, gradient exchange, optimizer bookkeeping - is captured once per (shape, |g|/|w|-step or not) as a
+        CUDA graph after three eager steps and replayed afterwards: one launch per step instead of ~2000."""
+        if self._gstream is not None and xy.is_cuda:
+            cur = torch.cuda.current_stream()
+            self._gstream.wait_stream(cur)
+            with torch.cuda.stream(self._gstream):
+                total = self._step(xy, step, preps, lr_mul)
+            cur.wait_stream(self._gstream)
+            return total
+        return self._step(xy, step, preps, lr_mul)
+
+    def _step(self, xy, step, preps, lr_mul):
         self.set_lr(step, lr_mul)
         m = self.model
         if hasattr(m, "before_step"):
             m.before_step(step)
+        inst = isinstance(self.opt, Instinct)
+        if inst:
+            self.opt._sync_lr()
+        if self.graph and xy.is_cuda and preps is None and inst and "C" not in self.stage:
+            total = self._step_graphed(xy)
+        else:
+            total = self._core(xy, preps)
+        if inst and hasattr(m, "rebank"):
+            self._apply_rebank(m.rebank(step))
+        self.last_loss = total
+        return total
+
+    def _step_graphed(self, xy):
+        key = (tuple(xy.shape), self.opt.n_step % self.opt.rel_every == 0)
+        if self._eager_steps < 3 or self._graph_failed:
+            self._eager_steps += 1
+            return self._core(xy, None)
+        ent = self._graphs.get(key)
+        if ent is None:
+            from ..ops import _ext
+            static_xy = xy.clone()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0, step0 = _ext.launch_count, self.opt.n_step
+            try:
+                with torch.cuda.graph(g, pool=self._graph_pool, stream=self._gstream):
+                    out = self._core(static_xy, None)
+            except Exception as e:   # noqa: BLE001 - capture is an optimisation; the eager path is always there
+                import warnings
+                warnings.warn(f"CUDA graph capture of the training step failed ({type(e).__name__}: {e}); running eagerly")
+                self._graph_failed = True
+                torch.cuda.synchronize()
+                return self._core(xy, None)
+            if self._graph_pool is None:
+                self._graph_pool = g.pool()
+            ent = self._graphs[key] = (g, static_xy, out, _ext.launch_count - n0)
+            self.opt.n_step = step0              # capture ran the host bookkeeping once; the replay below is the real step
+        g, static_xy, out, launches = ent
+        static_xy.copy_(xy)
+        g.replay()
+        self.opt.n_step += 1
+        from ..ops import _ext
+        _ext.count(launches)
+        return out
+
+    def _core(self, xy, preps=None):
+        """Device work of one step: micro-batches forward/backward (weights stepped in the grad hooks), exchange, finish."""
+        m = self.model
         micro = self.cfg.micro or len(xy)
         mbs = xy.split(micro)
         inst = isinstance(self.opt, Instinct)
         if inst and self.ocfg.sparse_rows and hasattr(m, "table_rows"):
             self.opt.rows = m.table_rows(xy[:, :-1])
         if "C" in self.stage and xy.is_cuda and len(mbs) > 1:
-            return self._step_interleaved(mbs, len(xy), xy, step)
+            return self._step_interleaved(mbs, len(xy), xy)
         total = torch.zeros((), device=xy.device)
         for i, mb in enumerate(mbs):
             last = i == len(mbs) - 1
@@ -133,11 +207,10 @@ class Trainer:
                 self.parallel.before_backward(self)
             (loss * w).backward()
             total = total + loss.detach() * w
-        self._after_backward(step, total, xy)
-        self.last_loss = total
+        self._after_backward(total, xy)
         return total
 
-    def _after_backward(self, step, total, xy):
+    def _after_backward(self, total, xy):
         inst = isinstance(self.opt, Instinct)
         if inst:
             if self.parallel is not None:
@@ -145,8 +218,6 @@ class Trainer:
             if not self.in_backward:
                 self.opt.update_all()
             self.opt.finish()
-            if hasattr(self.model, "rebank"):
-                self._apply_rebank(self.model.rebank(step))
         else:
             if self.parallel is not None:
                 self.parallel.reduce_grads(self.params)
@@ -165,7 +236,7 @@ class Trainer:
         if changes:
             self.params = [p for p in self.model.parameters() if p.requires_grad]
 
-    def _step_interleaved(self, mbs, n, xy, step):
+    def _step_interleaved(self, mbs, n, xy):
         """Stage C: independent micro-batches run forward on their own streams, one backward for all."""
         if self.streams is None or len(self.streams) != len(mbs):
             self.streams = [torch.cuda.Stream() for _ in mbs]
@@ -183,7 +254,7 @@ class Trainer:
         if isinstance(self.opt, Instinct):
             self.opt.prepare(total.detach(), self.situation(xy))
         total.backward()
-        self._after_backward(step, total.detach(), xy)
+        self._after_backward(total.detach(), xy)
         return total.detach()
 
 

@@ -213,3 +213,22 @@ def test_attention_matches_reference_with_grads():
         orf.backward(go.float())
         assert _rel(o, orf) < 2e-2, window
         assert _rel(qkv.grad, qr.grad) < 3e-2, window
+
+
+def test_add_rmsnorm_fwd_bwd():
+    from memarch_b200 import ops
+    from memarch_b200.ops import ref
+    torch.manual_seed(8)
+    x = torch.randn(260, 1024, device="cuda").requires_grad_()
+    y = torch.randn(260, 1024, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(1024, device="cuda")).requires_grad_()
+    h, n = ops.add_rmsnorm(x, y, w, 1e-6)
+    gh, gn = torch.randn_like(h), torch.randn_like(n)
+    (h * gh).sum().backward(retain_graph=True)
+    n.backward(gn)
+    xr, yr, wr = x.detach().clone().requires_grad_(), y.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    hr = xr + yr
+    nr = ref.rmsnorm(hr, wr, 1e-6)
+    ((hr * gh).sum() + (nr * gn.float()).sum()).backward()
+    assert _rel(h, hr) < 1e-5 and _rel(n, nr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 2e-2 and _rel(y.grad, yr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2

@@ -46,7 +46,7 @@ def parse():
     ap.add_argument("--corpus-tokens", type=int, default=8_000_000)
     ap.add_argument("--phrase-k", type=int, default=262144)
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--graph", type=int, default=1, help="replay the step as a CUDA graph after 3 eager steps (0 = eager)")
+    ap.add_argument("--graph", type=int, default=0, help="replay the step as a CUDA graph after 3 eager steps (0 = eager)")
     ap.add_argument("--wave", type=int, default=0, help="frozen bank experts per layer added to the 8 learning ones")
     return ap.parse_args()
 
@@ -215,7 +215,8 @@ def run_ours(args):
     tag = build_artifacts(args.art, D_MODEL, args.corpus_tokens, args.phrase_k, dev, rank, world)
     env = recipe_env(tag)
     torch.manual_seed(0)
-    model = build(args.model, VOCAB, env=env)
+    with torch.device(dev):                      # parameters are created on the GPU (same seed on every rank)
+        model = build(args.model, VOCAB, env=env)
     if args.wave:
         for b in model.heavy:
             b.grow_bank(args.wave)

@@ -304,13 +304,13 @@ class AnchorMoE(nn.Module):
         g = torch.Generator().manual_seed(seed)
         E0, E1 = self.E, self.E + n_frozen
         dv = self.up.device
-        self.up_f = (torch.randn(n_frozen, d, self.width_in, generator=g) * d ** -0.5).bfloat16().to(dv)
-        self.down_f = (torch.randn(n_frozen, self.width_out, d, generator=g) * self.width_out ** -0.5 * 0.5
+        self.up_f = (torch.randn(n_frozen, d, self.width_in, generator=g, device="cpu") * d ** -0.5).bfloat16().to(dv)
+        self.down_f = (torch.randn(n_frozen, self.width_out, d, generator=g, device="cpu") * self.width_out ** -0.5 * 0.5
                        ).bfloat16().to(dv)
         self.up_fs = torch.zeros(n_frozen, 1, self.width_in, dtype=torch.bfloat16, device=dv)
         self.down_fs = torch.zeros(n_frozen, 1, d, dtype=torch.bfloat16, device=dv)
         r = torch.cat([self.router.weight.detach(),
-                       (torch.randn(n_frozen, d, generator=g) * d ** -0.5).to(self.router.weight)])
+                       (torch.randn(n_frozen, d, generator=g, device="cpu") * d ** -0.5).to(self.router.weight)])
         self.router = nn.Linear(d, E1, bias=False).to(r.device)
         with torch.no_grad():
             self.router.weight.copy_(r)

@@ -91,6 +91,8 @@ class ParallelEngine:
         self.small = []
         self.trainer = None
         self.ctrl = None
+        import os
+        self.dp_mode = os.environ.get("MEMARCH_DP", "fused")           # "fused" | "nccl" (gradient mean of the replicated weights)
 
     # ------------------------------------------------------------------------------------------ model sharding
     def shard_model(self, model):
@@ -145,7 +147,7 @@ class ParallelEngine:
         weights: average over ranks.  Returns the gradient to step with, or None when the step is deferred."""
         if getattr(p, "_ep_local", False):
             return grad
-        if self.fused_impl is not None:            # also with one rank: the same kernels run against this GPU's own buffers
+        if self.fused_impl is not None and self.dp_mode == "fused":   # also with one rank: the GPU's own buffers
             return self.fused_impl.dp.grad_ready(p, grad)
         if self.W == 1:
             return grad
@@ -166,7 +168,7 @@ class ParallelEngine:
             opt.update(p, grad, synced=True)
 
     def after_backward(self, trainer):
-        if self.fused_impl is not None:
+        if self.fused_impl is not None and self.dp_mode == "fused":
             self.fused_impl.dp.flush()
             return
         self._drain(0)

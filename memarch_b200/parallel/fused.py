@@ -76,12 +76,25 @@ class _FusedExpertFFN(torch.autograd.Function):
         M = W * Cn
         h = torch.empty(n_local, M, H, device=xe.device, dtype=torch.bfloat16)
         a = torch.empty_like(h) if act == "relu2" else None
-        xptrs = [int(p) for p in Xh.buffer_ptrs]
-        if act == "relu2":
-            C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, h, [], 0, 0, 0, a, None, 1, n_local)
+        if ep.pull == "tma":
+            # A tiles fetched from the owners' buffers by the GEMM's own TMA loads (one tensor map per source GPU)
+            xptrs = [int(p) for p in Xh.buffer_ptrs]
+            if act == "relu2":
+                C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, h, [], 0, 0, 0, a, None, 1, n_local)
+            else:
+                a = C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, None, [], 0, 0, 0, None, None, 0, n_local)
+                h = C.swiglu_fwd(a)
         else:
-            a = C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, None, [], 0, 0, 0, None, None, 0, n_local)
-            h = C.swiglu_fwd(a)
+            # rows of my experts land in local memory first (bandwidth-bound peer copies), the GEMM reads them locally:
+            # a remote tile costs an NVLink round trip, more than the 6-stage shared-memory ring can hide
+            xin = torch.empty(n_local, M, d, device=xe.device, dtype=torch.bfloat16)
+            for s in range(W):
+                xin[:, s * Cn:(s + 1) * Cn].copy_(Xh.get_buffer(s, (E, Cn, d), torch.bfloat16)[g_off:g_off + n_local])
+            if act == "relu2":
+                gemm(xin, up, b_mn=True, out=h, out2=a, epi=1, groups=n_local)
+            else:
+                a = gemm(xin, up, b_mn=True, groups=n_local)
+                h = C.swiglu_fwd(a)
         # down-GEMM: A = h, cut into W row segments; segment s goes to rank s's output buffer
         hp = h.data_ptr()
         Hh = h.shape[2]
@@ -140,6 +153,7 @@ class FusedExpertExchange:
     def __init__(self, heap):
         self.heap, self.W, self.rank = heap, heap.W, heap.rank
         self._layers, self._grads = {}, {}
+        self.pull = os.environ.get("MEMARCH_EP_PULL", "copy")        # "copy" | "tma"
 
     def layer_buffers(self, key, E, C, d):
         k = (key, E, C, d)
@@ -271,4 +285,5 @@ class FusedParallel:
 
     def attach(self, trainer):
         self.dp.trainer = trainer
-        self.dp.allocate(trainer.params)
+        if os.environ.get("MEMARCH_DP", "fused") == "fused":
+            self.dp.allocate(trainer.params)

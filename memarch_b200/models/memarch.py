@@ -394,10 +394,10 @@ class MemArchLM(nn.Module):
                 s_ = prep["surp"] if prep and "surp" in prep else self._phr_surp(x)
             else:
                 s_ = self._light_surprise(lh.detach(), x)
+            A = max(1, round(T * self.cap))
+            idx, valid = ops.select_anchors(s_, self.tau, A)        # this step's threshold is the one before its update
             if self.training:
                 self.tau.mul_(0.9).add_(0.1 * ref.tau_quantile(s_, self.frac))
-            A = max(1, round(T * self.cap))
-            idx, valid = ops.select_anchors(s_, self.tau, A)
             self.stats["anchors"] = valid.float().mean() * A / T
 
         a_in = ops.gather_tokens(h, idx)

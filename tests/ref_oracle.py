@@ -1,0 +1,64 @@
+"""Child process that runs the unmodified reference on CPU and dumps what the parity tests compare against.
+
+usage: python ref_oracle.py <reference dir> <out.pt> <json spec>
+spec: {"name", "vocab", "env": {...}, "B", "T", "seed", "what": "model" | "instinct"}
+The reference reads its switches from the environment at import time, hence the separate process."""
+import json
+import os
+import sys
+
+
+def main():
+    ref_dir, out, spec = os.path.abspath(sys.argv[1]), os.path.abspath(sys.argv[2]), json.loads(sys.argv[3])
+    os.environ.update({"DEVICE": "cpu", "NO_COMPILE": "1"})
+    os.environ.update({k: str(v) for k, v in spec.get("env", {}).items()})
+    sys.path.insert(0, ref_dir)
+    os.chdir(ref_dir)
+    import torch
+    if spec.get("stable_sort"):
+        # The reference breaks ties in its slot choice with an unstable argsort, whose order on equal keys is an
+        # implementation detail of the sort; the rule "smaller index first" makes the comparison well defined.
+        plain = torch.Tensor.argsort
+
+        def stable(self, dim=-1, descending=False, stable=True):
+            return plain(self, dim=dim, descending=descending, stable=True)
+        torch.Tensor.argsort = stable
+    torch.manual_seed(spec.get("seed", 0))
+    if spec["what"] == "model":
+        import lm
+        m = lm.build(spec["name"], spec["vocab"])
+        m.train()
+        sd = {k: v.clone() for k, v in m.state_dict().items()}
+        g = torch.Generator().manual_seed(1)
+        xy = torch.randint(0, spec["vocab"], (spec["B"], spec["T"] + 1), generator=g)
+        outp, cost = m(xy[:, :-1])
+        loss = m.train_loss(outp, xy[:, 1:], True)
+        (loss + 0.01 * cost.float()).backward()
+        grads = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+        stats = {k: (v.detach().float().clone() if torch.is_tensor(v) else float(v)) for k, v in getattr(m, "stats", {}).items()}
+        torch.save({"sd": sd, "xy": xy, "loss": loss.detach(), "cost": cost.detach().float(), "grads": grads,
+                    "stats": stats, "tau": m.tau.clone() if hasattr(m, "tau") else None}, out)
+    elif spec["what"] == "instinct":
+        import exp_opt
+        torch.manual_seed(3)
+        shapes = [tuple(s) for s in spec["shapes"]]
+        ps = [torch.nn.Parameter(torch.randn(*s) * 0.1) if len(s) else torch.nn.Parameter(torch.tensor(0.3)) for s in shapes]
+        w0 = [p.detach().clone() for p in ps]
+        opt = exp_opt.InstinctOptB(ps, lr=spec["lr"], **spec.get("kw", {}))
+        gs, ws = [], []
+        for step in range(spec["steps"]):
+            g_step = [torch.randn(*s) * (0.01 * (1 + i)) if len(s) else torch.randn(()) * 0.01 for i, s in enumerate(shapes)]
+            sit = torch.randn(spec["d"])
+            opt.prepare(torch.tensor(3.0 - 0.1 * step), sit)
+            for p, g in zip(ps, g_step):
+                p.grad = g.clone()
+                opt.update(p)
+                p.grad = None
+            opt.finish()
+            gs.append((g_step, sit))
+            ws.append([p.detach().clone() for p in ps])
+        torch.save({"w0": w0, "gs": gs, "ws": ws, "gain": opt.gain.clone(), "rel": opt.rel.clone()}, out)
+
+
+if __name__ == "__main__":
+    main()

@@ -121,3 +121,31 @@ def build_all(tokens, d, out_dir, vocab=50257, phrase_k=262144, seed=0):
     torch.save(phrase_table(tokens, ph["head"], phrase_k, vocab), paths["trigram"])
     torch.save(lock_trust(tokens, vocab, cnt), paths["lock"])
     return paths
+
+
+def write_corpus(out_dir, tokens=8_000_000, d=256, vocab=50304, phr_v=None, phrase_k=262144, shards=4, seed=0):
+    """Seeded synthetic corpus as `tokens.npy` + shards `synthetic/shard_<i>.u32.npy` (loader layout) + every
+    phrasebook artefact, and `env.json` with the environment switches that point the model at them."""
+    import json
+    from .loader import write_shard
+    from .synth import MarkovCorpus
+    phr_v = phr_v or min(vocab, 50257)
+    os.makedirs(out_dir, exist_ok=True)
+    mc = MarkovCorpus(vocab=phr_v, seed=seed)
+    toks = mc.stream(tokens, text_len=2048, seed=seed + 1)
+    np.save(os.path.join(out_dir, "tokens.npy"), toks.astype(np.int32))
+    eos = phr_v                                            # one id above the corpus vocabulary ends a document
+    docs = [toks[i:i + 2048] for i in range(0, len(toks) - 2047, 2048)]
+    per = max(1, len(docs) // shards)
+    for s in range(shards):
+        write_shard(out_dir, "synthetic", f"shard_{s:03d}", docs[s * per:(s + 1) * per], eos)
+    paths = build_all(toks, d, out_dir, vocab=phr_v, phrase_k=phrase_k, seed=seed)
+    cnt = token_counts(toks, vocab)
+    np.save(paths["counts"], cnt)
+    env = {"PHRASE_INIT": paths["bigram"], "PHRASE3": paths["trigram"], "SURP_PHRASE": "1", "INDUCT": "lock",
+           "LOCK_TRUST": paths["lock"], "INDUCT_IN": "1", "INDUCT_MIX": "1", "TOKEN_COUNTS": paths["counts"],
+           "VOCAB": str(vocab), "PHR_V": str(phr_v), "DATA": os.path.join(out_dir, "tokens.npy"),
+           "CORPUS": json.dumps({"synthetic": 1.0}), "CORPUS_ROOT": out_dir}
+    json.dump(env, open(os.path.join(out_dir, "env.json"), "w"), indent=1)
+    print(f"wrote {len(toks):,} tokens, {shards} shards and phrasebook artefacts to {out_dir}")
+    return env

@@ -67,6 +67,7 @@ class Instinct:
         self._lr_ratio = torch.zeros((), device=dev)
         self._seed_t = torch.zeros((), dtype=torch.int64, device=dev)
         self._lr_last = None
+        self.lr_mul_dev = None         # optional 0-dim device tensor multiplying the step (set by the rollback guard)
         self.rows = {}
         self._scratch = {}
         self.grad_sync = None          # set by the data-parallel engine: called as grad_sync(p, grad) -> grad
@@ -114,7 +115,12 @@ class Instinct:
 
     def _sync_lr(self):
         lr = self.param_groups[0]["lr"]
-        if self._lr_last != lr:
+        if self.lr_mul_dev is not None:                       # device-side multiplier: no host sync, rewritten every step
+            self._lr_t.copy_(self.lr_mul_dev * (lr * self.scale))
+            self._lr_v.copy_(self.lr_mul_dev * (lr * self.scale * self.cfg.vocab_lr_mul))
+            self._lr_ratio.fill_(lr / self.lr_peak)
+            self._lr_last = None
+        elif self._lr_last != lr:
             self._lr_t.fill_(lr * self.scale)
             self._lr_v.fill_(lr * self.scale * self.cfg.vocab_lr_mul)
             self._lr_ratio.fill_(lr / self.lr_peak)
@@ -277,7 +283,7 @@ class Instinct:
         return dict(card=self.k, s=self.s, stake=self.stake)
 
     # ------------------------------------------------------------------------------------------ checkpoint blob
-    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch"}
+    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch", "lr_mul_dev"}
 
     def state_dict(self):
         out = {}

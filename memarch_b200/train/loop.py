@@ -1,0 +1,405 @@
+"""`speed` and `train`: the two run modes of the reference's training script (fastloop.py:580-652, 769-935).
+
+`speed` times steps of one or several (model, stage) pairs on the device and prints the reference's line
+`SPEED <name> <stage> <ms>/step <TFLOP/s> MFU <mem> loss <stats>`, also written to `results/speed.json`.
+`train` runs the full schedule: data (shard corpus with exact resume, a token file, or the seeded synthetic corpus),
+sequence / anchor / panic schedules, batch prefetch with the word-only preparation on a side stream, weight EMA for
+evaluation, fixed-window validation, periodic atomic checkpoints, NaN / spike / rollback guards and the hang watchdog.
+Between evaluation points nothing reads from the device.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+from ..config import OptConfig, TrainConfig, opt_from_env, train_from_env
+from .trainer import Trainer, val_loss
+
+
+# ------------------------------------------------------------------------------------------------ measurement
+def matmul_peak(device, n=8192, iters=20):
+    """Measured bf16 GEMM throughput of this GPU in TFLOP/s (fastloop.py:518-533): the MFU denominator."""
+    if os.environ.get("PEAK_TFLOPS"):
+        return float(os.environ["PEAK_TFLOPS"])
+    if torch.device(device).type != "cuda":
+        return float("nan")
+    a = torch.randn(n, n, device=device, dtype=torch.bfloat16)
+    b = torch.randn(n, n, device=device, dtype=torch.bfloat16)
+    for _ in range(3):
+        a @ b
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        a @ b
+    e1.record()
+    torch.cuda.synchronize()
+    return 2 * n ** 3 * iters / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+
+def step_flops(model, batch, seq):
+    """Useful FLOPs of one training step (forward + backward = 3 x forward matmul FLOPs), counted from the shapes:
+    light / final blocks on every token, heavy layers on the anchor slots only (top-k experts each), both heads,
+    causal-window attention.  The reference counts the same with a FLOP-counting mode on the unfused model
+    (fastloop.py:536-577); here the count is closed-form so it needs no second copy of the model."""
+    if os.environ.get("STEP_FLOPS"):
+        return float(os.environ["STEP_FLOPS"])
+    c = getattr(model, "cfg", None)
+    N = batch * seq
+    if c is None:                                            # plain transformer: 6 x params x tokens + attention
+        p = sum(q.numel() for n, q in model.named_parameters() if q.dim() >= 2 and "emb" not in n)
+        d = model.emb.weight.shape[1]
+        L = len(getattr(model, "blocks", []))
+        return 6.0 * p * N + 3 * 2 * 2 * L * N * seq * d / 2
+    d, V = c.d, c.vocab
+    f = 0.0
+    blocks = list(model.light_a) + list(model.light_b) + list(model.final)
+    for b in blocks:
+        lin = sum(p.numel() for n, p in b.named_parameters() if p.dim() == 2)
+        f += 2.0 * lin * N
+        ctx = min(seq, c.window) if c.window else seq
+        f += 2 * 2 * N * d * (ctx / 2 if ctx >= seq else ctx)          # QK^T and PV over the visible keys
+    A = max(1, round(seq * c.cap)) * batch
+    for h in model.heavy:
+        if hasattr(h, "up") and torch.is_tensor(h.up) and h.up.dim() == 3:
+            k = getattr(h, "k", 2)
+            f += 2.0 * A * k * (h.up.shape[1] * h.up.shape[2] + h.down.shape[1] * h.down.shape[2])
+            f += 2.0 * A * d * h.up.shape[0]
+        else:
+            f += 2.0 * A * sum(p.numel() for p in h.parameters() if p.dim() == 2)
+    f += 2.0 * N * d * V                                               # output head
+    if hasattr(model, "l_head"):
+        f += 2.0 * N * sum(p.numel() for p in model.l_head.parameters() if p.dim() == 2) if not hasattr(model, "sp_lse") else 0
+    if hasattr(model, "memory") and not c.no_mem:
+        f += 2.0 * N * 6 * d * d / max(1, c.seg // max(1, c.memory.write))
+    return 3.0 * f
+
+
+def make_trainer(name, stage, args, device, env=None, parallel=None):
+    """Model by registry name + optimizer and schedule from the environment switches (the reference's Trainer ctor,
+    fastloop.py:217-348)."""
+    from ..build import build
+    env = os.environ if env is None else env
+    vocab = int(env.get("VOCAB", 50304))
+    torch.manual_seed(int(env.get("SEED", 0)))
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        with torch.device(dev):
+            model = build(name, vocab, env=env)
+    else:
+        model = build(name, vocab, env=env)
+    model = model.to(dev)
+    ocfg = opt_from_env(OptConfig(lr=args.lr), env)
+    tcfg = train_from_env(TrainConfig(name=name, stage=stage, steps=args.steps, batch=args.batch, micro=args.micro,
+                                      seq=args.seq, lr=args.lr, read_cost=args.read_cost), env)
+    return Trainer(model, tcfg, ocfg, stage=stage, parallel=parallel)
+
+
+def _time_steps(step_fn, n, device):
+    if torch.device(device).type == "cuda":
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(n):
+            step_fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+    t0 = time.perf_counter()
+    for s in range(n):
+        step_fn(s)
+    return (time.perf_counter() - t0) * 1e3 / n
+
+
+def speed(args, device=None, out=None):
+    out = out or sys.stdout
+    from ..data.synth import MarkovCorpus, TokenStore
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    env = os.environ
+    vocab = int(env.get("VOCAB", 50304))
+    if env.get("DATA"):
+        toks = np.load(env["DATA"], mmap_mode="r")
+    else:
+        toks = MarkovCorpus(vocab=min(vocab, int(env.get("PHR_V", vocab))), seed=0).stream(max(2_000_000, 4 * args.batch * args.seq), text_len=2048, seed=1)
+    peak = matmul_peak(device)
+    results = []
+    for name in args.models:
+        for stage in args.stages:
+            tr = make_trainer(name, stage, args, device)
+            store = TokenStore(toks, seed=1, device=tr.device)
+            if env.get("SPEED_FROZEN") and hasattr(tr.model, "heavy"):
+                for b in tr.model.heavy:
+                    if hasattr(b, "grow_bank"):
+                        b.grow_bank(int(float(env["SPEED_FROZEN"]) * b.E))
+            last = {}
+
+            def one(s, tr=tr, store=store, last=last):
+                last["loss"] = tr.step(store.batch(args.batch, args.seq), s)
+            for s in range(args.warmup):
+                one(s)
+            ms = _time_steps(one, args.n, device)
+            fl = step_flops(tr.model, args.batch, args.seq)
+            tfs = fl / (ms * 1e-3) / 1e12
+            mem = torch.cuda.max_memory_allocated() / 2 ** 30 if tr.device.type == "cuda" else 0.0
+            stats = "".join(f"  {k} {float(v):.2f}" for k, v in getattr(tr.model, "stats", {}).items()
+                            if torch.is_tensor(v) and v.numel() == 1)
+            mfu = tfs / peak if peak == peak else float("nan")
+            print(f"SPEED {name} {stage}  {ms:.1f} ms/step  {args.batch * args.seq / ms * 1e3:,.0f} tok/s  {tfs:.1f} TFLOP/s  "
+                  f"MFU {100 * mfu:.1f}% (of measured {peak:.0f})  mem {mem:.1f} GB  loss {float(last['loss']):.3f}{stats}",
+                  file=out, flush=True)
+            results.append({"name": name, "stage": stage, "ms": ms, "tflops": tfs, "mfu": mfu, "mem_gb": mem,
+                            "loss": float(last["loss"]), "flops_per_step": fl})
+            del tr
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+    os.makedirs("results", exist_ok=True)
+    json.dump(results, open("results/speed.json", "w"))
+    return results
+
+
+# ------------------------------------------------------------------------------------------------ data for `train`
+class _NpyData:
+    """Token file: the first 2 M tokens (or the same share of a shorter file) are validation, the rest training."""
+
+    def __init__(self, path_or_array, device, tokens=None):
+        from ..data.synth import TokenStore
+        allt = np.load(path_or_array, mmap_mode="r") if isinstance(path_or_array, str) else path_or_array
+        n_val = min(2_000_000, max(len(allt) // 20, 1))
+        self.val, self.train = TokenStore(allt[:n_val], 0, device), TokenStore(allt[n_val:], 1, device)
+        self.corpus = None
+
+    def batch(self, B, T):
+        return self.train.batch(B, T)
+
+    def state_dict(self):
+        return self.train.state_dict()
+
+    def load_state_dict(self, sd):
+        self.train.load_state_dict(sd)
+
+
+class _CorpusData:
+    """Shard corpus through the pinned host loader; validation windows come from VAL_NPY or from another seed of the
+    same corpus (small overlap: a monitoring number, fastloop.py:774-778)."""
+
+    def __init__(self, seq, device, env, rank, world):
+        from ..data.loader import HostLoader, ShardCorpus
+        from ..data.synth import TokenStore
+        w, root = json.loads(env["CORPUS"]), env["CORPUS_ROOT"]
+        self.corpus = ShardCorpus(w, root, seq=seq, seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world)
+        self.loader, self.device, self.seq = None, device, seq
+        if env.get("VAL_NPY"):
+            self.val = TokenStore(np.load(env["VAL_NPY"]), 0, device)
+        else:
+            vc = ShardCorpus(w, root, seq=seq, seed=10 ** 6)
+            self.val = TokenStore(vc.batch(max(2, 160 * 1024 // seq)).reshape(-1), 0, device)
+        self._B = None
+
+    def batch(self, B, T):
+        assert T == self.seq, "the corpus serves windows of one fixed length"
+        if self.loader is None or self._B != B:
+            if self.loader is not None:
+                st = self.loader.state_dict()
+                self.loader.close()
+                self.corpus.load_state_dict(st)
+            from ..data.loader import HostLoader
+            self.loader, self._B = HostLoader(self.corpus, B, device=self.device), B
+        return self.loader.next()
+
+    def state_dict(self):
+        return self.loader.state_dict() if self.loader is not None else self.corpus.state_dict()
+
+    def load_state_dict(self, sd):
+        if self.loader is not None:
+            self.loader.close()
+            self.loader = None
+        self.corpus.load_state_dict(sd)
+
+
+def make_data(args, device, env=None, rank=0, world=1):
+    env = os.environ if env is None else env
+    if env.get("CORPUS"):
+        return _CorpusData(args.seq, device, env, rank, world)
+    if env.get("DATA"):
+        return _NpyData(env["DATA"], device)
+    from ..data.synth import MarkovCorpus
+    vocab = int(env.get("VOCAB", 50304))
+    n = int(getattr(args, "tokens", 0) or 8_000_000)
+    return _NpyData(MarkovCorpus(vocab=min(vocab, int(env.get("PHR_V", vocab))), seed=0).stream(n, text_len=2048, seed=1), device)
+
+
+# ------------------------------------------------------------------------------------------------ train
+def _schedules(args, env, tr):
+    ss, au = env.get("SEQ_SCHED"), env.get("AUTO_SCHED")
+    s_short, s_frac = (int(ss.split(":")[0]), float(ss.split(":")[1])) if ss else (args.seq, 0.0)
+    micro0 = args.micro
+
+    def cfg(step):
+        seq = s_short if step <= s_frac * args.steps else args.seq
+        fr = cp = None
+        if au and hasattr(tr.model, "frac"):
+            a_end, a_frac = (float(x) for x in au.split(":"))
+            fr, cp = (a_frac, min(1.0, a_frac * 1.25)) if step <= a_end * args.steps else (0.2, 0.25)
+        return seq, fr, cp
+
+    def apply(c):
+        seq, fr, cp = c
+        tr.cfg.micro = micro0 * (args.seq // seq)
+        if fr is not None and tr.model.frac != fr:
+            tr.model.frac, tr.model.cap = fr, cp
+            for b in tr.model.heavy:
+                if hasattr(b, "fill"):
+                    b.fill = fr / cp
+        return seq
+    return cfg, apply, micro0
+
+
+def train(args, device=None, env=None, out=None, parallel=None):
+    """Returns {model name: log} where log = [{step, time, val}, ...] (also written to results/<name>_<stage>.json)."""
+    from .ckpt import Checkpointer, run_id
+    from .guards import NanGuard, RollbackGuard, SpikeLog, Watchdog
+    out = out or sys.stdout
+    env = os.environ if env is None else env
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    rank, world = int(env.get("RANK", 0)), int(env.get("WORLD_SIZE", env.get("WORLD", 1)))
+    data = make_data(args, device, env, rank, world)
+    bpu = float(env.get("BYTES_PER_UNIT", 4.6361))
+    logs = {}
+    for name in args.models:
+        tr = make_trainer(name, args.stage, args, device, env, parallel)
+        cfg, apply, micro0 = _schedules(args, env, tr)
+        log, train_time = [], 0.0
+        ck = None
+        if env.get("CKPT_DIR"):
+            ck = Checkpointer(env["CKPT_DIR"], rid=run_id(name, getattr(tr.model, "cfg", None)), keep=int(env.get("CKPT_KEEP", 0)))
+        ck_every = int(env.get("CKPT_EVERY", 0))
+        start = 1
+        if ck is not None:
+            start, log0 = ck.load(tr, data)
+            log += log0
+            if start > 1:
+                print(f"resuming at step {start} from {ck.path}", file=out, flush=True)
+        nan = NanGuard(int(env.get("NAN_EVERY", 10)))
+        spikes = SpikeLog(float(env.get("SPIKE", 2.0)))
+        rb = RollbackGuard(tr, ratio=float(env.get("RB_RATIO", 1.5)), lr_mul=float(env.get("RB_LR", 0.5)),
+                           warm=int(env.get("RB_WARM", 50))) if env.get("ROLLBACK") == "1" else None
+        dog = Watchdog(float(env.get("WATCHDOG", 180)), 120.0) if env.get("WATCHDOG", "180") != "0" else None
+        ema_start, ema_beta = float(env.get("EMA_START", 0) or 0), float(env.get("EMA_BETA", 0.98))
+        ema_every = int(env.get("EMA_EVERY", 1))
+        ema = None
+        small = lambda: [p for p in tr.model.parameters() if p.numel() < 10_000_000]
+        prefetch = bool(env.get("PREFETCH")) and hasattr(tr.model, "prep") and tr.device.type == "cuda"
+        side = torch.cuda.Stream() if prefetch else None
+
+        def fetch(st):
+            sq = cfg(st)[0]
+            b = data.batch(args.batch * (args.seq // sq), sq)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                pr = [tr.model.prep(mb[:, :-1]) for mb in b.split(micro0 * (args.seq // sq))]
+                ev = torch.cuda.Event()
+                ev.record(side)
+            return b, pr, ev
+
+        def sync():
+            if tr.device.type == "cuda":
+                torch.cuda.synchronize()
+        sync()
+        t0 = time.time()
+        nxt = fetch(start) if prefetch else None
+        loss = torch.zeros((), device=tr.device)
+        try:
+            for step in range(start, args.steps + 1):
+                seq = apply(cfg(step))
+                pn = env.get("PANIC")
+                if pn:
+                    pfrac, pw = (float(x) for x in pn.split(":"))
+                    tr.model.panic = pw if step > (1 - pfrac) * args.steps else 0
+                if prefetch:
+                    xy_b, preps, ev = nxt
+                    torch.cuda.current_stream().wait_event(ev)
+                    for pr_ in preps:
+                        for v in pr_.values():
+                            if torch.is_tensor(v):
+                                v.record_stream(torch.cuda.current_stream())
+                    if step < args.steps:
+                        nxt = fetch(step + 1)
+                    loss = tr.step(xy_b, step - 1, preps)
+                else:
+                    xy_b = data.batch(args.batch * (args.seq // seq), seq)
+                    loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1)
+                nan.check(loss)
+                if dog:
+                    dog.beat()
+                if ema_start and step >= ema_start * args.steps and step % ema_every == 0:
+                    with torch.no_grad():
+                        ps = small()
+                        if ema is None:
+                            ema = [p.detach().float().clone() for p in ps]
+                        else:
+                            torch._foreach_lerp_(ema, [p.detach().float() for p in ps], 1 - ema_beta ** ema_every)
+                if step % args.eval_every == 0 or step == args.steps:
+                    sync()
+                    train_time += time.time() - t0
+                    nan.flush()
+                    cur = None
+                    if ema is not None:
+                        with torch.no_grad():
+                            ps = small()
+                            cur = [p.detach().clone() for p in ps]
+                            for p, e in zip(ps, ema):
+                                p.copy_(e)
+                    vl = float(val_loss(tr.model, data.val, args.seq))
+                    if cur is not None:
+                        with torch.no_grad():
+                            for p, c0 in zip(ps, cur):
+                                p.copy_(c0)
+                    spikes.check(step, float(loss))
+                    extra = "".join(f"  {k} {float(v):.2f}" for k, v in getattr(tr.model, "stats", {}).items()
+                                    if torch.is_tensor(v) and v.numel() == 1)
+                    log.append({"step": step, "time": train_time, "val": vl})
+                    print(f"{name}[{args.stage}]  step {step:5d}  val {vl:.3f}  bpb {vl / bpu / math.log(2):.4f}  "
+                          f"train {float(loss):.3f}{extra}  {train_time / 60:.1f} min", file=out, flush=True)
+                    sync()
+                    t0 = time.time()
+                if ck is not None and ck_every and (step % ck_every == 0 or step == args.steps):
+                    nan.flush()                                  # never save a state that already went non-finite
+                    ck.save(tr, step, log, data.state_dict())
+        finally:
+            if dog:
+                dog.close()
+            if ck is not None:
+                ck.wait()
+        if env.get("DUMP_TOK"):
+            dump_token_losses(tr.model, data.val, args.seq, env["DUMP_TOK"])
+        os.makedirs("results", exist_ok=True)
+        json.dump({"log": log}, open(f"results/{name}_{args.stage}.json", "w"))
+        logs[name] = log
+        del tr
+    return logs
+
+
+@torch.no_grad()
+def dump_token_losses(model, store, seq, path, n=20, batch=8):
+    """Per-token CE on the validation windows (same windows as `val_loss`), saved as one flat tensor."""
+    was = model.training
+    model.eval()
+    g = torch.Generator(device=store.device).manual_seed(0)
+    ces = []
+    for _ in range(n):
+        start = torch.randint(0, len(store.t) - seq - 1, (batch,), device=store.device, generator=g)
+        xy = store.t[start[:, None] + torch.arange(seq + 1, device=store.device)].long()
+        out, _ = model(xy[:, :-1])
+        if hasattr(model, "_ce_tok"):
+            ces.append(model._ce_tok(out[0], xy[:, 1:]).float().flatten())
+        else:
+            V = out.shape[-1]
+            ces.append(torch.nn.functional.cross_entropy(out.float().view(-1, V), xy[:, 1:].reshape(-1), reduction="none"))
+    model.train(was)
+    torch.save(torch.cat(ces).cpu(), path)

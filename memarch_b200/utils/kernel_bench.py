@@ -143,8 +143,8 @@ def cmd_experts(a):
     report(f"expert FFN relu2 fwd+bwd E{E} C{C} d{d} H{H}", timeit(fb, a.iters), 3 * 2 * 2.0 * E * C * d * H)
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="memarch_b200 bench-kernel")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192)
@@ -161,7 +161,7 @@ def main():
     e.add_argument("--d", type=int, default=2048); e.add_argument("--h", type=int, default=6144)
     for p in (g, c, i, e):
         p.add_argument("--iters", type=int, default=10)
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
     {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts}[a.cmd](a)
 

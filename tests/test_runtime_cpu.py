@@ -1,0 +1,258 @@
+"""Runtime pieces on CPU: shard corpus with exact resume, host loader, checkpoint round trip and kill test, guards,
+train/speed loops, CLI."""
+import io
+import json
+import os
+import signal
+import subprocess
+import sys
+import time
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def make_corpus(root, n_shards=3, docs=40, seed=0, eos=999):
+    from memarch_b200.data.loader import write_shard
+    rng = np.random.default_rng(seed)
+    for src, lo in (("web", 0), ("code", 400)):
+        for s in range(n_shards):
+            dd = [rng.integers(lo, lo + 300, size=rng.integers(5, 200)) for _ in range(docs)]
+            write_shard(root, src, f"s{s}", dd, eos,
+                        drop=[1, 3] if s == 0 else None,
+                        score=rng.uniform(1.5, 4.0, size=docs) if src == "code" else None)
+    return {"web": 0.7, "code": 0.3}
+
+
+def test_corpus_mix_and_exact_resume(tmp_path):
+    from memarch_b200.data.loader import ShardCorpus
+    w = make_corpus(str(tmp_path))
+    c = ShardCorpus(w, str(tmp_path), seq=64, seed=3)
+    for _ in range(7):
+        c.batch(4)
+    st = json.loads(json.dumps(c.state_dict()))              # must survive serialisation
+    want = [c.batch(4) for _ in range(90)]                   # crosses shard and epoch boundaries
+    assert abs(c.mix()["web"] - 0.7) < 0.02
+    c2 = ShardCorpus(w, str(tmp_path), seq=64, seed=3)
+    c2.load_state_dict(st)
+    for a in want:
+        assert np.array_equal(a, c2.batch(4))
+    assert c.sources[0].epoch > 0                            # the test did wrap around
+
+
+def test_corpus_masks_and_ranks(tmp_path):
+    from memarch_b200.data.loader import ShardCorpus, shard_documents
+    make_corpus(str(tmp_path))
+    docs = shard_documents(os.path.join(str(tmp_path), "web", "s0"), 999, np.random.default_rng(0))
+    assert len(docs) == 38                                   # two dropped by the dedup mask
+    assert all(d[-1] == 999 for d in docs)
+    a = ShardCorpus({"web": 1.0}, str(tmp_path), seq=32, rank=0, world=2)
+    b = ShardCorpus({"web": 1.0}, str(tmp_path), seq=32, rank=1, world=2)
+    assert set(a.sources[0].names).isdisjoint(b.sources[0].names)
+    with pytest.raises(ValueError):
+        ShardCorpus({"web": 1.0}, str(tmp_path), seq=32, rank=5, world=6)
+
+
+def test_host_loader_state_is_the_consumed_batch(tmp_path):
+    from memarch_b200.data.loader import HostLoader, ShardCorpus
+    w = make_corpus(str(tmp_path))
+    ld = HostLoader(ShardCorpus(w, str(tmp_path), seq=64, seed=1), B=2, depth=3)
+    for _ in range(5):
+        ld.next()
+    time.sleep(0.2)                                          # let the worker read ahead
+    st = ld.state_dict()
+    nxt = ld.next()
+    ld.close()
+    c = ShardCorpus(w, str(tmp_path), seq=64, seed=1)
+    c.load_state_dict(st)
+    assert np.array_equal(c.batch(2), nxt.numpy())
+
+
+def test_host_loader_forwards_worker_errors(tmp_path):
+    from memarch_b200.data.loader import HostLoader
+
+    class Broken:
+        seq = 8
+
+        def state_dict(self):
+            return {}
+
+        def batch(self, B):
+            raise ValueError("shard unreadable")
+    ld = HostLoader(Broken(), B=2)
+    with pytest.raises(RuntimeError):
+        ld.next()
+    ld.close()
+
+
+def tiny_trainer(seed=0, stage="ABX", **env):
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.train import Trainer
+    torch.manual_seed(seed)
+    e = {"NO_MEM": "1", "MOE_ACT": "relu2"}
+    e.update(env)
+    m = build("tiny", 256, env=e)
+    return Trainer(m, TrainConfig(name="tiny", stage=stage, steps=50, batch=4, micro=4, seq=32, lr=1e-2, warmup=2),
+                   OptConfig(lr=1e-2, norm="hs", scale=0.12, rel_every=2), stage=stage)
+
+
+def batches(n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 256, (4, 33), generator=g) for _ in range(n)]
+
+
+def test_checkpoint_round_trip_continues_bit_exact(tmp_path):
+    from memarch_b200.train.ckpt import Checkpointer
+    xs = batches(8)
+    a = tiny_trainer()
+    for s in range(4):
+        a.step(xs[s], s)
+    ck = Checkpointer(str(tmp_path), rid="r1")
+    ck.save(a, 4, log=[{"step": 4}], corpus_state={"k": 1})
+    ck.wait()
+    want = [float(a.step(xs[s], s)) for s in range(4, 8)]
+    b = tiny_trainer(seed=7)                                 # different init: everything must come from the file
+    nxt, log = Checkpointer(str(tmp_path), rid="r1").load(b)
+    assert nxt == 5 and log == [{"step": 4}]
+    got = [float(b.step(xs[s], s)) for s in range(4, 8)]
+    assert got == want
+    with pytest.raises(RuntimeError):
+        Checkpointer(str(tmp_path), rid="other").load(tiny_trainer())
+    st = torch.load(os.path.join(str(tmp_path), "latest.pt"), weights_only=False)
+    assert set(st) >= {"step", "log", "banks", "model", "opt", "corpus"}
+    assert {"m", "w", "gain", "keys", "used", "expect", "seen", "rel", "n_step", "_lr"} <= set(st["opt"])
+
+
+KILL_SCRIPT = r"""
+import os, sys, time, torch
+sys.path.insert(0, {root!r})
+from memarch_b200.train.ckpt import Checkpointer
+class M(torch.nn.Module):
+    def __init__(self):
+        super().__init__(); self.w = torch.nn.Parameter(torch.zeros(2_000_000))
+class T:
+    device = torch.device("cpu")
+    def __init__(self): self.model = M(); self.opt = torch.optim.SGD(self.model.parameters(), lr=0.1)
+t = T(); ck = Checkpointer({d!r}, background=True)
+step = 0
+while True:
+    step += 1
+    with torch.no_grad(): t.model.w.fill_(float(step))
+    ck.save(t, step)
+    print(step, flush=True)
+"""
+
+
+def test_kill_during_checkpoint_leaves_a_complete_file(tmp_path):
+    """SIGKILL the writer at arbitrary moments: latest.pt is always loadable and internally consistent."""
+    d = str(tmp_path)
+    for trial in range(3):
+        p = subprocess.Popen([sys.executable, "-c", KILL_SCRIPT.format(root=ROOT, d=d)], stdout=subprocess.PIPE, text=True)
+        seen = 0
+        t0 = time.time()
+        while seen < 3 + trial and time.time() - t0 < 120:
+            line = p.stdout.readline()
+            if line.strip():
+                seen = int(line)
+        time.sleep(0.013 * (trial + 1))
+        p.send_signal(signal.SIGKILL)
+        p.wait()
+        st = torch.load(os.path.join(d, "latest.pt"), weights_only=False)
+        w = st["model"]["w"]
+        assert st["step"] >= 1 and bool((w == float(st["step"])).all())
+
+
+def test_nan_guard_and_spike_log():
+    from memarch_b200.train.guards import NanGuard, NonFiniteLoss, SpikeLog
+    g = NanGuard(every=4)
+    for v in (1.0, 2.0, float("nan")):
+        g.check(torch.tensor(v))
+    with pytest.raises(NonFiniteLoss):
+        g.check(torch.tensor(1.0))
+    buf = io.StringIO()
+    s = SpikeLog(spike=2.0, out=buf)
+    for i, v in enumerate((3.0, 3.1, 2.9, 9.0, 3.0)):
+        s.check(i, v)
+    assert len(s.events) == 1 and s.events[0][0] == 3 and "spike" in buf.getvalue()
+
+
+def test_rollback_guard_reverts_and_replays():
+    from memarch_b200.train.guards import RollbackGuard
+    xs = batches(6)
+    tr = tiny_trainer()
+    rb = RollbackGuard(tr, ratio=1.5, warm=2, lr_mul=0.5)
+    for s in range(3):
+        rb.step(xs[s], s)
+    before_prev = [t.clone() for t in rb.snap_p]             # state before step 2 (the previous step)
+    real = tr.step
+
+    def spiky(xy, step, **kw):                               # host-made failure: this step reports a huge loss
+        return real(xy, step, **kw) * 100.0
+    tr.step = spiky
+    rb.step(xs[3], 3)
+    tr.step = real
+    assert bool(rb.rep) and int(rb.n_hit) == 1
+    for p, s in zip(tr.params, before_prev):
+        assert torch.equal(p.data, s)                        # weights are back to the snapshot
+    seen = {}
+
+    def spy(xy, step, **kw):
+        seen["xy"] = xy.clone()
+        seen["mul"] = float(tr.opt.lr_mul_dev)
+        return real(xy, step, **kw)
+    tr.step = spy
+    rb.step(xs[4], 4)
+    assert torch.equal(seen["xy"], xs[2]) and seen["mul"] == 0.5   # replays the previous batch at half step
+    assert not bool(rb.rep)
+    rb.step(xs[5], 5)
+    assert torch.equal(seen["xy"], xs[5]) and seen["mul"] == 1.0
+
+
+def test_watchdog_dumps_stacks_without_killing():
+    from memarch_b200.train.guards import Watchdog
+    buf = io.StringIO()
+    w = Watchdog(timeout=0.3, repeat=0.3, out=buf)
+    for _ in range(5):
+        w.beat()
+        time.sleep(0.05)
+    assert w.fired == 0
+    time.sleep(1.2)
+    w.close()
+    assert w.fired >= 2 and "no progress" in buf.getvalue() and "thread" in buf.getvalue().lower()
+
+
+class Args:
+    def __init__(self, **kw):
+        self.models, self.stages, self.stage = ["tiny"], ["ABX"], "ABX"
+        self.steps, self.batch, self.micro, self.seq, self.lr = 12, 4, 4, 32, 1e-2
+        self.read_cost, self.eval_every, self.tokens, self.warmup, self.n = 0.01, 6, 60_000, 1, 2
+        self.__dict__.update(kw)
+
+
+def test_train_loop_resumes_from_checkpoint(tmp_path, monkeypatch):
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    env = {"VOCAB": "256", "NO_MEM": "1", "CKPT_DIR": str(tmp_path / "ck"), "CKPT_EVERY": "6", "WATCHDOG": "0",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12}), "EMA_START": "0.5"}
+    full = train(Args(), "cpu", env=env, out=io.StringIO())["tiny"]
+    assert [e["step"] for e in full] == [6, 12] and full[-1]["val"] < 6.0
+    assert os.path.exists(tmp_path / "results" / "tiny_ABX.json")
+    # second run with the same directory: nothing left to do, log comes back from the file
+    buf = io.StringIO()
+    again = train(Args(), "cpu", env=env, out=buf)["tiny"]
+    assert [e["step"] for e in again] == [6, 12]
+
+
+def test_speed_and_cli(tmp_path, monkeypatch, capsys):
+    from memarch_b200.cli import main
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("VOCAB", "256")
+    monkeypatch.setenv("NO_MEM", "1")
+    assert main(["speed", "--models", "tiny", "--batch", "2", "--seq", "32", "--n", "2", "--warmup", "1", "--device", "cpu"]) == 0
+    out = capsys.readouterr().out
+    assert "SPEED tiny ABX" in out and "ms/step" in out
+    r = json.load(open(tmp_path / "results" / "speed.json"))
+    assert r[0]["flops_per_step"] > 0

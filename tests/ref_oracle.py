@@ -32,8 +32,12 @@ def main():
         g = torch.Generator().manual_seed(1)
         xy = torch.randint(0, spec["vocab"], (spec["B"], spec["T"] + 1), generator=g)
         outp, cost = m(xy[:, :-1])
-        loss = m.train_loss(outp, xy[:, 1:], True)
-        (loss + 0.01 * cost.float()).backward()
+        if hasattr(m, "train_loss"):
+            loss = m.train_loss(outp, xy[:, 1:], True)
+        else:
+            loss = torch.nn.functional.cross_entropy(outp.float().view(-1, outp.shape[-1]), xy[:, 1:].reshape(-1))
+        if not spec.get("no_backward"):
+            (loss + 0.01 * cost.float()).backward()
         grads = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
         stats = {k: (v.detach().float().clone() if torch.is_tensor(v) else float(v)) for k, v in getattr(m, "stats", {}).items()}
         torch.save({"sd": sd, "xy": xy, "loss": loss.detach(), "cost": cost.detach().float(), "grads": grads,

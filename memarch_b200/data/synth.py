@@ -111,3 +111,23 @@ class HostFeeder:
         for r, s in enumerate(idx):
             view[r] = self.arr[s:s + self.T + 1]
         return buf.to(self.device, non_blocking=True).long()
+
+
+def recall_batch(B, n_pairs=8, n_keys=64, n_vals=64, seed=None, device="cpu"):
+    """Associative-recall toy task of the first prototypes (the reference's data.py:1-31): a text is `n_pairs`
+    (key, value) pairs followed by a query key; the target at the last position is that key's value.
+    Tokens: keys 0..n_keys-1, values n_keys..n_keys+n_vals-1, query marker = n_keys+n_vals.  Returns (x, y, mask)
+    with y the next-token target and mask true only where the value must be recalled."""
+    import torch
+    g = torch.Generator().manual_seed(seed) if seed is not None else None
+    keys = torch.stack([torch.randperm(n_keys, generator=g)[:n_pairs] for _ in range(B)])
+    vals = torch.randint(0, n_vals, (B, n_pairs), generator=g) + n_keys
+    which = torch.randint(0, n_pairs, (B,), generator=g)
+    ar = torch.arange(B)
+    pairs = torch.stack([keys, vals], -1).reshape(B, 2 * n_pairs)
+    q = torch.full((B, 1), n_keys + n_vals)
+    seq = torch.cat([pairs, q, keys[ar, which][:, None], vals[ar, which][:, None]], 1)
+    x, y = seq[:, :-1], seq[:, 1:]
+    mask = torch.zeros_like(y, dtype=torch.bool)
+    mask[:, -1] = True
+    return x.to(device), y.to(device), mask.to(device)

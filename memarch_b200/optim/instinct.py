@@ -174,7 +174,8 @@ class Instinct:
             if want_rel:
                 self.rel[i] = 0.0
             return
-        if _ext.use_cuda(p) and _kind_code(kind) >= 0 and p.is_contiguous() and grad.is_contiguous():
+        if (_ext.use_cuda(p) and _kind_code(kind) >= 0 and p.is_contiguous() and grad.is_contiguous()
+                and getattr(p, "_row_shard", None) is None):
             self._update_cuda(i, p, grad, kind, wd_v, lr_t, want_rel)
         else:
             self._update_ref(i, p, grad, kind, wd_v, lr_t, want_rel)
@@ -200,7 +201,11 @@ class Instinct:
                 shp = (1, p.shape[1]) if kind == "hs" else (p.shape[0], p.shape[1], 1)
                 self.cs[i] = torch.zeros(shp, device=p.device, dtype=torch.float32)
             cs = self.cs[i]
-        upd, new_cs = ref.instinct_direction(mf, grad, kind, cs)
+        shard = getattr(p, "_row_shard", None)
+        if shard is not None and kind == "hs":
+            upd, new_cs = self._direction_row_sharded(mf, shard), None
+        else:
+            upd, new_cs = ref.instinct_direction(mf, grad, kind, cs)
         if new_cs is not None:
             self.cs[i].copy_(new_cs)
         t = p if w is None else w
@@ -226,6 +231,19 @@ class Instinct:
             t.copy_(torch.where(fr.view(-1, *[1] * (t.dim() - 1)), keep, t))
         if w is not None:
             p.copy_(w)
+
+    @staticmethod
+    def _direction_row_sharded(mf, shard):
+        """Homeostasis of a weight cut by rows between ranks (the reference's kind `hsS<W>,<rows>`, exp_opt.py:271-280):
+        rows are local, the per-column norm is a sum over all ranks - one small all-reduce of a (1, C) vector."""
+        import torch.distributed as dist
+        _, total_rows, group = shard
+        upd = mf / (mf.pow(2).mean(1, keepdim=True).sqrt() + 1e-8)
+        col = upd.pow(2).sum(0, keepdim=True)
+        if dist.is_initialized():
+            dist.all_reduce(col, group=group)
+        upd = upd / ((col / total_rows).sqrt() + 1e-8)
+        return upd / (upd.pow(2).mean(1, keepdim=True).sqrt() + 1e-8)
 
     def _update_cuda(self, i, p, grad, kind, wd, lr_t, want_rel):
         C = _ext.C()

@@ -3,6 +3,7 @@ run when every rank sees the same data, and average over ranks when they see dif
 import os
 import sys
 
+import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
@@ -77,3 +78,69 @@ def test_different_data_ranks_stay_in_sync():
     assert abs(tau0 - tau1) < 1e-6                   # shared anchor threshold
     for k in sd0:
         assert abs(sd0[k] - sd1[k]).max() < 1e-6, k                   # replicated weights identical on both ranks
+
+
+def _w_vocab_and_shard(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world)})
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    from memarch_b200.parallel import vocab
+    torch.manual_seed(0)
+    V, d, N = 50, 16, 24
+    table, head = torch.randn(V, d), torch.randn(V, d)
+    ids, h, y = torch.randint(0, V, (N,)), torch.randn(N, d), torch.randint(0, V, (N,))
+    ts, lo = vocab.shard_rows(table, rank, world)
+    hs, _ = vocab.shard_rows(head, rank, world)
+    ts.requires_grad_(True); hs.requires_grad_(True)
+    hh = h.clone().requires_grad_(True)
+    e = vocab.take(ts, ids, lo)
+    loss = vocab.ce(hh + e * 0.1, hs, y, lo, chunk=7)
+    loss.backward()
+    # row-sharded homeostasis: this rank's rows of a (12, 8) weight
+    torch.manual_seed(1)
+    w, g = torch.randn(12, 8), torch.randn(12, 8)
+    n = 12 // world
+    p = torch.nn.Parameter(w[rank * n:(rank + 1) * n].clone())
+    p._row_shard = (world, 12, None)
+    opt = Instinct([p], OptConfig(lr=1e-2, norm="hs", scale=1.0))
+    opt.prepare(torch.tensor(1.0), torch.ones(4))
+    opt.update(p, g[rank * n:(rank + 1) * n].clone())
+    q.put((rank, loss.item(), ts.grad.numpy(), hs.grad.numpy(), hh.grad.numpy(), p.detach().numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_and_row_sharded_homeostasis_match_single_rank():
+    import torch.multiprocessing as mp
+    import torch.nn.functional as F
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    world, port = 2, 29631
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_vocab_and_shard, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted([q.get(timeout=120) for _ in ps], key=lambda r: r[0])
+    [p.join(30) for p in ps]
+    torch.manual_seed(0)
+    V, d, N = 50, 16, 24
+    table, head = torch.randn(V, d, requires_grad=True), torch.randn(V, d, requires_grad=True)
+    ids, h, y = torch.randint(0, V, (N,)), torch.randn(N, d, requires_grad=True), torch.randint(0, V, (N,))
+    loss = F.cross_entropy((h + table[ids] * 0.1) @ head.t(), y, reduction="sum")
+    loss.backward()
+    assert abs(res[0][1] - loss.item()) < 1e-3 and abs(res[1][1] - loss.item()) < 1e-3
+    n = V // world
+    for r in range(world):
+        assert np.allclose(res[r][2], table.grad[r * n:(r + 1) * n].numpy(), atol=1e-4)
+        assert np.allclose(res[r][3], head.grad[r * n:(r + 1) * n].numpy(), atol=1e-4)
+        assert np.allclose(res[r][4], h.grad.numpy(), atol=1e-4)
+    torch.manual_seed(1)
+    w, g = torch.randn(12, 8), torch.randn(12, 8)
+    p = torch.nn.Parameter(w.clone())
+    opt = Instinct([p], OptConfig(lr=1e-2, norm="hs", scale=1.0))
+    opt.prepare(torch.tensor(1.0), torch.ones(4))
+    opt.update(p, g.clone())
+    got = np.concatenate([res[0][5], res[1][5]])
+    assert np.allclose(got, p.detach().numpy(), atol=1e-6)

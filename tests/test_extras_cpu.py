@@ -1,0 +1,126 @@
+"""Secondary model features on CPU: routed long-range attention against a per-query brute force, fishki pools,
+uroboros selection, int8 numerics, recall toy task."""
+import math
+
+import torch
+
+from memarch_b200.models import fishki
+from memarch_b200.models import rope_memory as rm
+from memarch_b200.ops import int8
+
+
+def brute_rope(q, k, v, s, tau, A, cfg):
+    """Per-query Python loop straight from the definition."""
+    B, H, T, hd = q.shape
+    out = torch.zeros_like(q)
+    sc = 1 / math.sqrt(hd)
+    for b in range(B):
+        anchor = (s[b] > tau).clone()
+        anchor[0] = True
+        pos = [t for t in range(T) if anchor[t]][:A]
+        nxt = pos[1:] + [T]
+        for h in range(H):
+            for i in range(T):
+                cand = []
+                for a, (p0, p1) in enumerate(zip(pos, nxt)):
+                    if max(p1, p0 + cfg.win) > i:
+                        continue
+                    links = [p0 + l for l in range(min(cfg.links, cfg.span_cap)) if p0 + l < p1 and p0 + l < T]
+                    sco = [(float(q[b, h, i] @ k[b, h, j]) * sc, j) for j in links]
+                    best = max(sco)
+                    cand.append((best[0], -a, a, best[1]))
+                cand.sort(reverse=True)
+                keys, bias = [], []
+                for sc_a, _, a, tp in cand[:cfg.K]:
+                    en = min(nxt[a], pos[a] + cfg.span_cap, i - cfg.win + 1)
+                    for t in range(pos[a], en):
+                        keys.append(t)
+                        bias.append(sc_a * cfg.rgrad_scale if cfg.rgrad else 0.0)
+                for t in range(max(0, i - cfg.win + 1), i + 1):
+                    keys.append(t)
+                    bias.append(0.0)
+                kk = torch.tensor(keys)
+                logit = (k[b, h, kk] @ q[b, h, i]) * sc + torch.tensor(bias)
+                out[b, h, i] = logit.softmax(0) @ v[b, h, kk]
+    return out
+
+
+def test_rope_memory_matches_brute_force_and_has_gradients():
+    torch.manual_seed(0)
+    B, H, T, hd = 2, 2, 96, 16
+    cfg = rm.RopeCfg(K=2, links=3, win=8, span_cap=12, chunk=32)
+    q, k, v = (torch.randn(B, H, T, hd) for _ in range(3))
+    s = torch.rand(B, T) * 2
+    own, apos, avalid = rm.anchors_from_surprise(s.clone(), 1.4, 24)
+    qq = q.clone().requires_grad_(True)
+    out, share, (tidx, tval, tpos) = rm.rope_attention(qq, k, v, own, apos, avalid, cfg)
+    want = brute_rope(q, k, v, s, 1.4, 24, cfg)
+    assert (out - want).abs().max() < 1e-4
+    assert 0 < float(share) < 1 and bool(tval.any())
+    out.square().sum().backward()
+    assert qq.grad.abs().sum() > 0
+    layer = rm.RopeMemoryAttention(32, 2, cfg)
+    y, _ = layer(torch.randn(2, 96, 32), s, 1.4)
+    assert y.shape == (2, 96, 32)
+
+
+def test_fishki_pool_and_router():
+    torch.manual_seed(0)
+    assert fishki.pools(4, 16, 6) == [[0, 1, 2, 3, 4, 5], [4, 5, 6, 7, 8, 9], [8, 9, 10, 11, 12, 13], [12, 13, 14, 15, 0, 1]]
+    p = fishki.FishPool(32, n=8, hf=64, kinds=4, pool=3, center=True)
+    h = torch.randn(2, 10, 32, requires_grad=True)
+    y = p(h, p.sets[1])
+    y.sum().backward()
+    used = {i for i in range(8) if p.up.grad[i].abs().sum() > 0}
+    assert used == set(p.sets[1])
+    ce, acc, logits = p.router_loss(h, torch.tensor([1, 3]))
+    assert logits.shape == (2, 4) and ce.item() > 0
+
+
+def test_uroboros_select_loss_budget():
+    torch.manual_seed(0)
+    u = fishki.Uroboros(16)
+    lh, s = torch.randn(2, 20, 16), torch.rand(2, 20) * 5
+    pred = u.predict(lh, s)
+    assert pred.shape == (2, 20) and bool((pred >= 0).all())
+    idx, valid = u.select(pred, 0.25)
+    assert idx.shape == (2, 5) and bool((idx[:, 0] == 0).all()) and bool((idx[:, 1:] > idx[:, :-1]).all())
+    nll = torch.rand(2, 20) * 6
+    u.loss(pred, nll).backward()
+    assert u.l1.weight.grad.abs().sum() > 0
+    st = u.stats(pred, nll, idx, eat=1.0)
+    assert set(st) == {"uroboros_eaten", "uroboros_corr", "uroboros_nll_sel", "uroboros_nll_skip"}
+    lv = (0.25, 0.2, 0.15, 0.1)
+    assert u.next_budget(0.25, 0.9, lv) == 0.2             # one level at a time
+    assert u.next_budget(0.25, 0.5, lv) == 0.25            # need 0.625: stays
+    assert u.next_budget(0.2, 0.95, lv, corr=0.1) == 0.2   # head does not know its errors yet
+
+
+def test_int8_linear_and_bmm_close_to_fp32():
+    torch.manual_seed(0)
+    x, w = torch.randn(64, 256, requires_grad=True), torch.randn(320, 256, requires_grad=True)
+    y = int8.linear_i8(x, w)
+    ref = x @ w.t()
+    assert (y - ref).norm() / ref.norm() < 0.02
+    g = torch.randn_like(y)
+    y.backward(g)
+    assert (x.grad - g @ w).norm() / (g @ w).norm() < 0.03
+    assert (w.grad - g.t() @ x).norm() / (g.t() @ x).norm() < 0.02      # weight gradient is bf16, not int8
+    xe, we = torch.randn(2, 16, 256, requires_grad=True), torch.randn(2, 256, 300, requires_grad=True)
+    ye = int8.bmm_i8(xe, we)
+    assert (ye - torch.bmm(xe, we)).norm() / torch.bmm(xe, we).norm() < 0.02
+    ye.sum().backward()
+    assert xe.grad is not None and we.grad is not None
+    q, s = int8.fq(torch.tensor([[0.5, -1.0, 0.25]]), 1)
+    assert q.tolist() == [[64.0, -127.0, 32.0]] and abs(float(s) - 1 / 127) < 1e-9
+
+
+def test_recall_toy_task():
+    from memarch_b200.data.synth import recall_batch
+    x, y, mask = recall_batch(8, n_pairs=4, n_keys=16, n_vals=16, seed=0)
+    assert x.shape == (8, 10) and mask.sum() == 8
+    for b in range(8):
+        key = int(x[b, -1])
+        pairs = x[b, :8].view(4, 2)
+        val = int(pairs[pairs[:, 0] == key][0, 1])
+        assert int(y[b, -1]) == val

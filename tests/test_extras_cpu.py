@@ -124,3 +124,31 @@ def test_recall_toy_task():
         pairs = x[b, :8].view(4, 2)
         val = int(pairs[pairs[:, 0] == key][0, 1])
         assert int(y[b, -1]) == val
+
+
+def test_long_context_generators_and_runs():
+    import numpy as np
+    from memarch_b200.experiments import long_context as lc
+    g = torch.Generator().manual_seed(0)
+    x, y, ans = lc.recall_task(4, pairs=3, filler=20, queries=2, g=g)
+    assert x.shape == (4, 2 * 3 + 20 + 2 * 2 - 1) and (y != -100).sum() == 8
+    for b in range(4):
+        kv = x[b, :6].view(3, 2)
+        for a in ans:
+            key = int(x[b, a])
+            assert int(y[b, a]) == int(kv[kv[:, 0] == key][0, 1])
+    toks = np.random.default_rng(0).integers(100, 1000, size=5000)
+    xb, tgt, depth = lc.needle_batch(toks, 3, 256, (3000, 3001), g)
+    for b in range(3):
+        d = depth[b]
+        assert xb[b, d:d + 3].tolist() == [11, 12, 13] and int(xb[b, d + 4]) == int(tgt[b])
+        assert xb[b, -4:-1].tolist() == [11, 12, 13] and int(xb[b, -1]) == int(xb[b, d + 3])
+    s = torch.rand(6, 256) * 3
+    r = lc.anchor_chunks(s, 1.5, 0.25, chunks=(64, 128))
+    assert 0 < r["per_text"] < 1 and r["per_chunk_64"] >= r["per_text"] - 1e-6
+    acc, m = lc.recall_run("Fv2s", steps=3, B=2, pairs=2, fillers=(8,), device="cpu", vocab=32768, eval_B=2, out=lambda *a: None)
+    assert set(acc) == {8}
+    d = lc.recall_diagnose(m, pairs=2, filler=64, B=2)
+    assert 0 <= d["stored"] <= 1 and d["cards"] > 0
+    rows = lc.long_speed(models=("tiny",), lens=(64,), warmup=1, n=1, device="cpu", vocab=512, out=lambda *a: None)
+    assert rows[0]["ms"] > 0

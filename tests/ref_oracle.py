@@ -42,6 +42,21 @@ def main():
         stats = {k: (v.detach().float().clone() if torch.is_tensor(v) else float(v)) for k, v in getattr(m, "stats", {}).items()}
         torch.save({"sd": sd, "xy": xy, "loss": loss.detach(), "cost": cost.detach().float(), "grads": grads,
                     "stats": stats, "tau": m.tau.clone() if hasattr(m, "tau") else None}, out)
+    elif spec["what"] == "train":
+        import argparse
+        import numpy as np
+        import fastloop
+        a = argparse.Namespace(batch=spec["B"], micro=spec["B"], seq=spec["T"], lr=spec["lr"], read_cost=0.01,
+                               steps=spec["total_steps"])
+        tr = fastloop.Trainer(spec["name"], spec.get("stage", "ABX"), a)
+        sd = {k: v.clone() for k, v in tr.model.state_dict().items()}
+        data = fastloop.GPUData(np.load(spec["tokens"]), seed=1)
+        batches, losses = [], []
+        for s_ in range(spec["steps"]):
+            xy = data.batch(spec["B"], spec["T"])
+            batches.append(xy.clone())
+            losses.append(float(tr.step(xy, s_)))
+        torch.save({"sd": sd, "batches": batches, "losses": losses}, out)
     elif spec["what"] == "instinct":
         import exp_opt
         torch.manual_seed(3)

@@ -136,3 +136,30 @@ def test_instinct_matches_reference(tmp_path, kw):
     if not kw.get("m_bf16"):
         assert torch.allclose(opt.gain, d["gain"], atol=1e-5)
         assert torch.allclose(opt.rel, d["rel"], atol=1e-5)
+
+
+def test_loss_curve_matches_reference(tmp_path):
+    """The tiny configuration of the benchmark list (d=256, 4 heads, 2+2 light, 2 heavy MoE layers of 4 SwiGLU experts,
+    phrasebook + phrase table + locks, memory off, Instinct with homeostasis), trained from the reference's initial
+    weights on the reference's batches: the two loss curves stay together.  The reference autocasts to bf16 on CPU,
+    this build computes in fp32 there, hence a tolerance rather than equality."""
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.config import opt_from_env
+    from memarch_b200.train import Trainer
+    env, toks = artefacts(tmp_path, 256, 2048, 2000, 4096)
+    np.save(tmp_path / "tokens.npy", toks.astype(np.int32))
+    okw = {"norm": "hs", "scale": 0.12, "rel_every": 4}
+    env.update({"NO_MEM": "1", "LIGHT": "2", "WAVE_WARM": "1000000", "WARMUP": "5", "OPT_KW": json.dumps(okw)})
+    steps = 16
+    d = oracle(tmp_path, {"what": "train", "name": "Fv2moeK4h2d256", "B": 4, "T": 128, "lr": 3e-3, "steps": steps,
+                          "total_steps": 100, "tokens": str(tmp_path / "tokens.npy"), "env": env})
+    m = build("Fv2moeK4h2d256", 2048, env=env)
+    m.load_state_dict(d["sd"])
+    tr = Trainer(m, TrainConfig(name="cfg0", stage="ABX", steps=100, batch=4, micro=4, seq=128, lr=3e-3, warmup=5),
+                 opt_from_env(OptConfig(lr=3e-3), env), stage="ABX")
+    ours = [float(tr.step(xy, s)) for s, xy in enumerate(d["batches"])]
+    ref = d["losses"]
+    print("loss curves (ours, reference):", [(round(a, 3), round(b, 3)) for a, b in zip(ours, ref)])
+    assert abs(ours[0] - ref[0]) < 0.02
+    assert ref[-1] < ref[0] - 0.3 and ours[-1] < ours[0] - 0.3            # both learn
+    assert max(abs(a - b) for a, b in zip(ours, ref)) < 0.08, list(zip(ours, ref))

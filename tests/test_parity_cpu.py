@@ -162,4 +162,4 @@ def test_loss_curve_matches_reference(tmp_path):
     print("loss curves (ours, reference):", [(round(a, 3), round(b, 3)) for a, b in zip(ours, ref)])
     assert abs(ours[0] - ref[0]) < 0.02
     assert ref[-1] < ref[0] - 0.3 and ours[-1] < ours[0] - 0.3            # both learn
-    assert max(abs(a - b) for a, b in zip(ours, ref)) < 0.08, list(zip(ours, ref))
+    assert max(abs(a - b) for a, b in zip(ours, ref)) < 0.02, list(zip(ours, ref))

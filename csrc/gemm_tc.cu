@@ -35,6 +35,7 @@ struct GemmParams {
   int ldo, ldo2, ldaux;                // row pitches in elements
   int epi, out_f32, accumulate;
   int m_tiles, n_tiles;
+  int ntail;                 // 1: the last N tile issues MMAs only as wide as its valid columns (rounded up to 16)
   uint32_t lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b;   // shared-memory descriptor geometry in bytes
   int* status;
   // M may be cut into `n_seg` segments of `seg_M` rows, each read through its own A tensor map (a peer GPU's
@@ -175,6 +176,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int g, int se
   }
 }
 
+// Width of the MMA for N tile `nt`: the full tile, or for a ragged last tile its valid columns rounded up to 16
+// (rows of B past N are zero-filled by TMA; accumulator columns past the width are never stored).
+__device__ __forceinline__ int tile_n_eff(const GemmParams& p, int nt) {
+  if (!p.ntail || p.epi == EPI_SWIGLU) return BN;
+  const int rem = p.N - nt * BN;
+  return rem >= BN ? BN : ((rem + 15) & ~15);
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -265,13 +274,15 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = idesc_bf16(BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int g_, mt_, nt_;
+        tile_coords(t, p, g_, mt_, nt_);
+        const uint32_t idesc = idesc_bf16(BM, tile_n_eff(p, nt_), A_MN ? 1u : 0u, B_MN ? 1u : 0u);
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
         }
@@ -406,7 +417,9 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
             tma_load_3d_pair(sA + 8192, tA, lfull, m0 + 64, k0, ga);
           }
           // this CTA's half of the B tile: N rows [nb, nb + 128)
-          const int nb = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt * 128 : (p.N >> 1) + nt * 128) : nt * BN + (int)rank * 128;
+          // (a narrowed last tile splits its n_eff columns between the two CTAs: the second half starts at n_eff / 2)
+          const int nb = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt * 128 : (p.N >> 1) + nt * 128)
+                                               : nt * BN + (int)rank * (tile_n_eff(p, nt) >> 1);
           if (!B_MN) {
             tma_load_3d_pair(sB, &tmB, lfull, k0, nb, g);
           } else {
@@ -423,13 +436,15 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
-      const uint32_t idesc = idesc_bf16(256, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = pair; t < total && ok; t += npairs) {
+        int g_, mt_, nt_;
+        tile_coords(t, p, g_, mt_, nt_);
+        const uint32_t idesc = idesc_bf16(256, tile_n_eff(p, nt_), A_MN ? 1u : 0u, B_MN ? 1u : 0u);
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
         }
@@ -587,6 +602,8 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
     p.lbo_a = g_desc_override[0]; p.sbo_a = g_desc_override[1]; p.kstep_a = g_desc_override[2];
     p.lbo_b = g_desc_override[3]; p.sbo_b = g_desc_override[4]; p.kstep_b = g_desc_override[5];
   }
+  static const bool ntail_on = []() { const char* e = std::getenv("MEMARCH_GEMM_NTAIL"); return !(e && e[0] == '0'); }();
+  p.ntail = ntail_on ? 1 : 0;
   const int total = G * p.m_tiles * p.n_tiles;
   int grid = pair ? 2 * std::min(total, max_ctas / 2) : std::min(total, max_ctas);
   if (grid <= 0) return;

@@ -20,7 +20,8 @@ def _mk(shape, scale=1.0, seed=0):
     return (torch.randn(*shape, device="cuda", generator=g) * scale).bfloat16()
 
 
-SHAPES = [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (2049, 2048, 2048), (136, 264, 200), (4096, 50304, 128)]
+SHAPES = [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (2049, 2048, 2048), (136, 264, 200), (4096, 50304, 128),
+          (512, 2064, 256), (264, 2072, 128), (136, 2200, 64)]     # ragged last N tile of 16, 24 and 152 columns
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -108,7 +109,8 @@ def test_linear_autograd_matches_torch():
     assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (2049, 2048, 2048), (4096, 50304, 128), (264, 264, 200)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (2049, 2048, 2048), (4096, 50304, 128), (264, 264, 200),
+                                   (512, 2064, 256), (264, 2072, 128), (520, 2200, 64)])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
 def test_pair_kernel_matches_fp32(M, N, K, a_mn, b_mn):
     """cta_group::2 kernel (two SMs per 256x256 tile) on the same checks as the single-CTA kernel."""

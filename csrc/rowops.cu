@@ -49,38 +49,45 @@ __global__ void rmsnorm_fwd_kernel(const TX* __restrict__ x, const float* __rest
 // dx = r*(g*w) - x * r^3/d * sum(g*w*x); dw += g * x * r (block-local accumulation over its rows, then atomics)
 // Optional `add` (fp32, same shape): a gradient that reached x by another path (the residual stream) is summed in
 // the same pass; optional `dx_lo`: the result is also written in bf16 (the branch that produced part of x wants it).
-template <typename TX, typename TG>
+template <typename TX, typename TG, int NV>
 __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                                    const float* __restrict__ rstd, TX* __restrict__ dx, float* __restrict__ dw,
                                    int n_rows, int d, const float* __restrict__ add, bf16* __restrict__ dx_lo) {
   __shared__ float red[32];
-  constexpr int MAXV = 8;                         // d <= 8 * 4 * blockDim.x
-  float4 acc[MAXV];
+  // d <= NV * 4 * blockDim.x; a row's x, dy and w stay in registers between the dot product and the update
+  float4 acc[NV], ww[NV];
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = 0; i < NV; ++i) {
+    acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int c = (i * blockDim.x + threadIdx.x) * 4;
+    ww[i] = c < d ? ld4(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   for (long long row = blockIdx.x; row < n_rows; row += gridDim.x) {
     const TX* xr = x + row * d;
     const TG* gr = dy + row * d;
     const float r = rstd[row];
+    float4 xv[NV], gv[NV];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      int c = (i * blockDim.x + threadIdx.x) * 4;
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * blockDim.x + threadIdx.x) * 4;
       if (c < d) {
-        float4 v = ld4(xr + c), g = ld4(gr + c), ww = ld4(w + c);
-        dot += g.x * ww.x * v.x + g.y * ww.y * v.y + g.z * ww.z * v.z + g.w * ww.w * v.w;
+        xv[i] = ld4(xr + c);
+        gv[i] = ld4(gr + c);
+        dot += gv[i].x * ww[i].x * xv[i].x + gv[i].y * ww[i].y * xv[i].y + gv[i].z * ww[i].z * xv[i].z +
+               gv[i].w * ww[i].w * xv[i].w;
       }
     }
     dot = block_sum(dot, red);
     const float k = dot * r * r * r / d;
     TX* dxr = dx + row * d;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      int c = (i * blockDim.x + threadIdx.x) * 4;
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * blockDim.x + threadIdx.x) * 4;
       if (c < d) {
-        float4 v = ld4(xr + c), g = ld4(gr + c), ww = ld4(w + c);
-        float4 o = make_float4(r * g.x * ww.x - v.x * k, r * g.y * ww.y - v.y * k, r * g.z * ww.z - v.z * k,
-                               r * g.w * ww.w - v.w * k);
+        const float4 v = xv[i], g = gv[i];
+        float4 o = make_float4(r * g.x * ww[i].x - v.x * k, r * g.y * ww[i].y - v.y * k, r * g.z * ww[i].z - v.z * k,
+                               r * g.w * ww[i].w - v.w * k);
         if (add) { const float4 q = ld4(add + row * d + c); o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w; }
         st4(dxr + c, o);
         if (dx_lo) st4(dx_lo + row * d + c, o);
@@ -89,8 +96,8 @@ __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TX* __restri
     }
   }
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    int c = (i * blockDim.x + threadIdx.x) * 4;
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 4;
     if (c < d) {
       atomicAdd(dw + c, acc[i].x); atomicAdd(dw + c + 1, acc[i].y);
       atomicAdd(dw + c + 2, acc[i].z); atomicAdd(dw + c + 3, acc[i].w);
@@ -176,12 +183,15 @@ std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch:
   if (n == 0) return {dx, dw, lo};
   const int grid = std::min(n, 148 * 8);
   const bool xb = x.scalar_type() == torch::kBFloat16, gb = dy.scalar_type() == torch::kBFloat16;
-#define LAUNCH(TX, TG) rmsnorm_bwd_kernel<TX, TG><<<grid, 256, 0, cur_stream()>>>( \
+#define LAUNCH_NV(TX, TG, NV) rmsnorm_bwd_kernel<TX, TG, NV><<<grid, 256, 0, cur_stream()>>>( \
       reinterpret_cast<const TG*>(dy.data_ptr()), reinterpret_cast<const TX*>(x.data_ptr()), wf.data_ptr<float>(), \
       rstd.data_ptr<float>(), reinterpret_cast<TX*>(dx.data_ptr()), dw.data_ptr<float>(), n, d, add, lop)
+#define LAUNCH(TX, TG) do { if (d <= 2048) LAUNCH_NV(TX, TG, 2); else if (d <= 4096) LAUNCH_NV(TX, TG, 4); \
+                            else LAUNCH_NV(TX, TG, 8); } while (0)
   if (xb && gb) LAUNCH(bf16, bf16); else if (xb) LAUNCH(bf16, float);
   else if (gb) LAUNCH(float, bf16); else LAUNCH(float, float);
 #undef LAUNCH
+#undef LAUNCH_NV
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {dx, dw, lo};
 }

@@ -39,6 +39,9 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
 std::vector<torch::Tensor> anchor_select(torch::Tensor s, torch::Tensor tau, int64_t A);
 std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C);
 std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_keys, bool longest_only);
+std::vector<torch::Tensor> moe_route_fwd(torch::Tensor logits, torch::Tensor real, torch::Tensor k_tok, int64_t k_max);
+torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Tensor k_tok, torch::Tensor real, torch::Tensor dw,
+                            c10::optional<torch::Tensor> dprobs, c10::optional<torch::Tensor> dpsum);
 }  // namespace mb
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -68,4 +71,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("anchor_select", &mb::anchor_select);
   m.def("moe_slots", &mb::moe_slots);
   m.def("lock_find", &mb::lock_find);
+  m.def("moe_route_fwd", &mb::moe_route_fwd);
+  m.def("moe_route_bwd", &mb::moe_route_bwd);
 }

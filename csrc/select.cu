@@ -159,6 +159,152 @@ std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C)
   return {table, flat_idx, dropped};
 }
 
+// Router: softmax over E experts, top-k_max by probability (ties: smaller expert first), per-token budget k_tok,
+// renormalised weights of the kept choices, and the two per-expert sums of the Switch auxiliary loss
+// (cnt[e] = kept choices of expert e, psum[e] = sum of probs over real tokens).  One thread per token.
+constexpr int ROUTE_MAX_K = 8;
+__global__ void moe_route_fwd_kernel(const float* __restrict__ logits, const bool* __restrict__ real,
+                                     const long long* __restrict__ k_tok, float* __restrict__ probs,
+                                     long long* __restrict__ top_e, float* __restrict__ w, long long* __restrict__ e_flat,
+                                     float* __restrict__ cnt, float* __restrict__ psum, long long N, int E, int k_max) {
+  __shared__ float cnt_sh[SLOT_MAX_E], ps_sh[SLOT_MAX_E];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) { cnt_sh[i] = 0.f; ps_sh[i] = 0.f; }
+  __syncthreads();
+  const long long n = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (n < N) {
+    const float* lr = logits + n * E;
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) mx = fmaxf(mx, lr[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) sum += expf(lr[e] - mx);
+    const float inv = 1.f / sum;
+    float tp[ROUTE_MAX_K];
+    int te[ROUTE_MAX_K];
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_K; ++j) { tp[j] = -1.f; te[j] = E; }
+    const bool is_real = real[n];
+    for (int e = 0; e < E; ++e) {
+      const float pe = expf(lr[e] - mx) * inv;
+      probs[n * E + e] = pe;
+      if (is_real) atomicAdd(&ps_sh[e], pe);
+      // insertion into the descending top list; strict '>' keeps the smaller expert first on ties
+      float cp = pe; int ce = e;
+#pragma unroll
+      for (int j = 0; j < ROUTE_MAX_K; ++j) {
+        if (j < k_max && cp > tp[j]) { const float t = tp[j]; const int u = te[j]; tp[j] = cp; te[j] = ce; cp = t; ce = u; }
+      }
+    }
+    const int kt = (int)k_tok[n];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_K; ++j) if (j < k_max && j < kt) s += tp[j];
+    s = fmaxf(s, 1e-9f);
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_K; ++j) {
+      if (j < k_max) {
+        const bool keep = j < kt;
+        top_e[n * k_max + j] = te[j];
+        w[n * k_max + j] = keep ? tp[j] / s : 0.f;
+        e_flat[n * k_max + j] = keep ? te[j] : E;
+        if (keep) atomicAdd(&cnt_sh[te[j]], 1.f);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    if (cnt_sh[i] != 0.f) atomicAdd(cnt + i, cnt_sh[i]);
+    if (ps_sh[i] != 0.f) atomicAdd(psum + i, ps_sh[i]);
+  }
+}
+
+// dlogits from dw (N,k_max), dprobs_direct (N,E) (may be null) and dpsum (E) (gradient of the aux loss w.r.t. psum):
+// dP = scatter of dtp + dprobs_direct + real * dpsum;  dlogits = P * (dP - sum_e P dP).
+__global__ void moe_route_bwd_kernel(const float* __restrict__ probs, const long long* __restrict__ top_e,
+                                     const long long* __restrict__ k_tok, const bool* __restrict__ real,
+                                     const float* __restrict__ dw, const float* __restrict__ dprobs,
+                                     const float* __restrict__ dpsum, float* __restrict__ dlogits, long long N, int E, int k_max) {
+  const long long n = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float* pr = probs + n * E;
+  const int kt = (int)k_tok[n];
+  float tp[ROUTE_MAX_K], dtp[ROUTE_MAX_K];
+  int te[ROUTE_MAX_K];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < ROUTE_MAX_K; ++j) {
+    te[j] = j < k_max ? (int)top_e[n * k_max + j] : E;
+    tp[j] = (j < k_max && j < kt) ? pr[te[j]] : 0.f;
+    s += tp[j];
+  }
+  const bool clamped = s < 1e-9f;
+  s = fmaxf(s, 1e-9f);
+  float dot = 0.f;                                            // sum_j dw_j * w_j
+#pragma unroll
+  for (int j = 0; j < ROUTE_MAX_K; ++j) if (j < k_max && j < kt) dot += dw[n * k_max + j] * tp[j] / s;
+#pragma unroll
+  for (int j = 0; j < ROUTE_MAX_K; ++j)
+    dtp[j] = (j < k_max && j < kt) ? (dw[n * k_max + j] - (clamped ? 0.f : dot)) / s : 0.f;
+  const bool is_real = real[n];
+  float pd = 0.f;
+  for (int e = 0; e < E; ++e) {
+    float d = (dprobs ? dprobs[n * E + e] : 0.f) + ((is_real && dpsum) ? dpsum[e] : 0.f);
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_K; ++j) if (te[j] == e) d += dtp[j];
+    pd += pr[e] * d;
+  }
+  for (int e = 0; e < E; ++e) {
+    float d = (dprobs ? dprobs[n * E + e] : 0.f) + ((is_real && dpsum) ? dpsum[e] : 0.f);
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_K; ++j) if (te[j] == e) d += dtp[j];
+    dlogits[n * E + e] = pr[e] * (d - pd);
+  }
+}
+
+std::vector<torch::Tensor> moe_route_fwd(torch::Tensor logits, torch::Tensor real, torch::Tensor k_tok, int64_t k_max) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == torch::kFloat32, "moe_route: (N,E) fp32");
+  TORCH_CHECK(real.scalar_type() == torch::kBool && real.is_contiguous() && k_tok.scalar_type() == torch::kInt64 &&
+              k_tok.is_contiguous(), "moe_route: real bool, k_tok int64");
+  const long long N = logits.size(0);
+  const int E = logits.size(1);
+  TORCH_CHECK(E <= SLOT_MAX_E && k_max >= 1 && k_max <= ROUTE_MAX_K && k_max <= E, "moe_route: E <= 128, k_max <= 8");
+  auto io = logits.options().dtype(torch::kInt64);
+  auto probs = torch::empty_like(logits);
+  auto top_e = torch::empty({N, k_max}, io), e_flat = torch::empty({N, k_max}, io);
+  auto w = torch::empty({N, k_max}, logits.options());
+  auto cnt = torch::zeros({E}, logits.options()), psum = torch::zeros({E}, logits.options());
+  if (N) moe_route_fwd_kernel<<<(int)((N + 127) / 128), 128, 0, cur_stream()>>>(
+      logits.data_ptr<float>(), real.data_ptr<bool>(), reinterpret_cast<const long long*>(k_tok.data_ptr<int64_t>()),
+      probs.data_ptr<float>(), reinterpret_cast<long long*>(top_e.data_ptr<int64_t>()), w.data_ptr<float>(),
+      reinterpret_cast<long long*>(e_flat.data_ptr<int64_t>()), cnt.data_ptr<float>(), psum.data_ptr<float>(), N, E, (int)k_max);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {probs, top_e, w, e_flat, cnt, psum};
+}
+
+torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Tensor k_tok, torch::Tensor real, torch::Tensor dw,
+                            c10::optional<torch::Tensor> dprobs, c10::optional<torch::Tensor> dpsum) {
+  const c10::cuda::CUDAGuard guard(probs.device());
+  const long long N = probs.size(0);
+  const int E = probs.size(1), k_max = top_e.size(1);
+  TORCH_CHECK(dw.is_contiguous() && dw.scalar_type() == torch::kFloat32 && dw.numel() == N * k_max, "moe_route_bwd: dw (N,k) fp32");
+  const float* dp = nullptr; const float* ds = nullptr;
+  if (dprobs.has_value() && dprobs->defined()) {
+    TORCH_CHECK(dprobs->is_contiguous() && dprobs->scalar_type() == torch::kFloat32 && dprobs->numel() == N * E, "moe_route_bwd: dprobs");
+    dp = dprobs->data_ptr<float>();
+  }
+  if (dpsum.has_value() && dpsum->defined()) {
+    TORCH_CHECK(dpsum->is_contiguous() && dpsum->scalar_type() == torch::kFloat32 && dpsum->numel() == E, "moe_route_bwd: dpsum");
+    ds = dpsum->data_ptr<float>();
+  }
+  auto dl = torch::empty_like(probs);
+  if (N) moe_route_bwd_kernel<<<(int)((N + 127) / 128), 128, 0, cur_stream()>>>(
+      probs.data_ptr<float>(), reinterpret_cast<const long long*>(top_e.data_ptr<int64_t>()),
+      reinterpret_cast<const long long*>(k_tok.data_ptr<int64_t>()), real.data_ptr<bool>(), dw.data_ptr<float>(), dp, ds,
+      dl.data_ptr<float>(), N, E, k_max);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return dl;
+}
+
 // Keys and locks: for each position t and n-gram length n = 1..n_keys, the latest j < t whose n-gram ending at j
 // equals the one ending at t; the candidate is the token after j.  One block per text, tokens staged in shared memory.
 __global__ void lock_find_kernel(const long long* __restrict__ x, long long* __restrict__ cand, bool* __restrict__ on,

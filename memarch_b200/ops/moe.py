@@ -141,9 +141,44 @@ def expert_ffn(xe, up, down, act="swiglu", train_w=True):
 
 
 # ------------------------------------------------------------------------------------------------ routing
+class _Route(torch.autograd.Function):
+    """Fused router tail on the GPU: softmax, top-k_max, budget mask, renormalised weights and the two per-expert
+    sums of the auxiliary loss in one kernel; backward in one kernel (`csrc/select.cu`)."""
+
+    @staticmethod
+    def forward(ctx, logits, real, k_tok, k_max):
+        C = _ext.C()
+        probs, top_e, w, e_flat, cnt, psum = C.moe_route_fwd(logits.contiguous(), real.contiguous(), k_tok.contiguous(), int(k_max))
+        _ext.count()
+        ctx.save_for_backward(probs, top_e, k_tok, real)
+        ctx.mark_non_differentiable(top_e, e_flat, cnt)
+        return w, psum, top_e, e_flat, cnt, probs
+
+    @staticmethod
+    def backward(ctx, dw, dpsum, _a, _b, _c, dprobs):
+        probs, top_e, k_tok, real = ctx.saved_tensors
+        dl = _ext.C().moe_route_bwd(probs, top_e, k_tok.contiguous(), real.contiguous(), dw.contiguous().float(),
+                                    dprobs.contiguous().float() if dprobs is not None else None,
+                                    dpsum.contiguous().float() if dpsum is not None else None)
+        _ext.count()
+        return dl, None, None, None
+
+
+def moe_route(xf, router_w, real, k_tok, k_max, E):
+    """(probs, top_e, keep, w, e_flat, aux) - the CUDA kernel on the GPU, `ref.moe_route` elsewhere."""
+    if _ext.use_cuda(xf) and E <= 128 and k_max <= 8:
+        logits = (xf.to(router_w.dtype) @ router_w.T).float()
+        w, psum, top_e, e_flat, cnt, probs = _Route.apply(logits, real, k_tok, k_max)
+        pm = psum / real.sum().clamp(min=1)
+        aux = E * (cnt / cnt.sum().clamp(min=1) * pm).sum()
+        keep = torch.arange(k_max, device=xf.device)[None] < k_tok[:, None]
+        return probs, top_e, keep, w, e_flat, aux
+    return ref.moe_route(xf, router_w, real, k_tok, k_max, E)
+
+
 def route_and_slot(xf, router_w, real, k_tok, k_max, E, C):
     """Router + capacity slotting.  Returns (w (N,k), table, wtab, flat_idx, aux, dropped, probs)."""
-    probs, top_e, keep, w, e_flat, aux = ref.moe_route(xf, router_w, real, k_tok, k_max, E)
+    probs, top_e, keep, w, e_flat, aux = moe_route(xf, router_w, real, k_tok, k_max, E)
     with torch.no_grad():
         if _ext.use_cuda(xf):
             table, flat_idx, dropped = _ext.C().moe_slots(e_flat.contiguous(), int(E), int(C))

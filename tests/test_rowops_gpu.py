@@ -232,3 +232,40 @@ def test_add_rmsnorm_fwd_bwd():
     ((hr * gh).sum() + (nr * gn.float()).sum()).backward()
     assert _rel(h, hr) < 1e-5 and _rel(n, nr) < 1e-2
     assert _rel(x.grad, xr.grad) < 2e-2 and _rel(y.grad, yr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("E,k_max,budget", [(8, 2, False), (48, 4, True), (5, 3, True)])
+def test_moe_route_kernel_matches_reference(E, k_max, budget):
+    from memarch_b200.ops import moe, ref
+    torch.manual_seed(0)
+    N, d = 1000, 64
+    xf = torch.randn(N, d, device="cuda")
+    rw = (torch.randn(E, d, device="cuda") * 0.3).requires_grad_()
+    real = torch.rand(N, device="cuda") > 0.1
+    k_tok = (torch.randint(1, k_max + 1, (N,), device="cuda") if budget else torch.full((N,), min(2, k_max), device="cuda")) * real
+    probs, top_e, keep, w, e_flat, aux = moe.moe_route(xf, rw, real, k_tok, k_max, E)
+    gw = torch.randn_like(w)
+    (w * gw).sum().add(3.0 * aux).backward()
+    g1 = rw.grad.clone()
+    rw.grad = None
+    p2, t2, k2, w2, e2, a2 = ref.moe_route(xf, rw, real, k_tok, k_max, E)
+    (w2 * gw).sum().add(3.0 * a2).backward()
+    assert torch.allclose(probs, p2, atol=1e-6) and torch.equal(e_flat, e2) and torch.equal(keep, k2)
+    assert torch.equal(top_e[keep], t2[keep])
+    assert torch.allclose(w, w2, atol=1e-6) and abs(float(aux) - float(a2)) < 1e-5
+    assert torch.allclose(g1, rw.grad, atol=1e-4, rtol=1e-3), (g1 - rw.grad).abs().max()
+
+
+def test_rmsnorm_bwd_wide_rows():
+    """Rows wider than 2048 take the 4- and 8-vector variants of the backward kernel."""
+    from memarch_b200 import ops
+    for d in (1024, 2048, 3072, 8192):
+        x = torch.randn(37, d, device="cuda", requires_grad=True)
+        w = (1 + 0.1 * torch.randn(d, device="cuda")).requires_grad_()
+        y = ops.rmsnorm(x, w, 1e-6, out_dtype=torch.bfloat16)
+        go = torch.randn_like(y)
+        y.backward(go)
+        xr, wr = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+        torch.nn.functional.rms_norm(xr, (d,), wr, 1e-6).backward(go.float())
+        assert torch.allclose(x.grad, xr.grad, atol=2e-2, rtol=2e-2), d
+        assert torch.allclose(w.grad, wr.grad, atol=5e-2, rtol=2e-2), d

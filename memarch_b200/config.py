@@ -137,6 +137,11 @@ class OptConfig:
     sparse_rows: bool = False
     in_backward: bool = True      # stage B: update each weight from its grad-ready hook
     bf16_weights: bool = True     # BF16_W: linear weights live in bf16, exact fp32 copy in the optimizer
+    damp: float = 0.0             # >0: per-tensor gradient-surge damping: |g| above damp x its usual norm is clipped
+    damp_p: float = 1.0           #     into the momentum and the tensor's step shrinks by (damp x usual / |g|)^damp_p
+    damp_beta: float = 0.99       #     EMA of the usual squared norm (per situation card)
+    damp_cap: float = 2.0         #     a surge enters that EMA as at most (cap x usual)^2: the brake does not get used to it
+    surge_thr: float = 0.0        # >0: surprise brake: a step much worse than expected (-s > thr) scales lr by (thr/-s)^2
 
 
 @dataclass

@@ -68,6 +68,8 @@ class Instinct:
         self._seed_t = torch.zeros((), dtype=torch.int64, device=dev)
         self._lr_last = None
         self.lr_mul_dev = None         # optional 0-dim device tensor multiplying the step (set by the rollback guard)
+        self.dv = torch.zeros(cfg.cards, P, device=dev) if cfg.damp > 0 else None   # usual |g|^2 per (card, weight)
+        self.df = torch.ones(P, device=dev) if cfg.damp > 0 else None               # last damping factor (for the log)
         self.rows = {}
         self._scratch = {}
         self.grad_sync = None          # set by the data-parallel engine: called as grad_sync(p, grad) -> grad
@@ -167,6 +169,11 @@ class Instinct:
         kind, wd, vocab = self.spec(p)
         want_rel = self.n_step % self.rel_every == 0
         lr_t = self._lr_v if vocab else self._lr_t
+        if self.cfg.surge_thr > 0:                       # surprise brake (device scalars only)
+            bad = (-self.s).clamp(min=self.cfg.surge_thr)
+            lr_t = lr_t * (self.cfg.surge_thr / bad) ** 2
+        if self.dv is not None and not vocab:
+            grad, lr_t = self._damp(i, grad, lr_t)
         wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
         rows = self.rows.get(id(p)) if vocab else None
         if rows is not None:
@@ -179,6 +186,23 @@ class Instinct:
             self._update_cuda(i, p, grad, kind, wd_v, lr_t, want_rel)
         else:
             self._update_ref(i, p, grad, kind, wd_v, lr_t, want_rel)
+
+    def _damp(self, i, grad, lr_t):
+        """Per-tensor gradient-surge damping (the reference's JAX Instinct, instinct.py:132-150): the optimizer
+        normalises the step by the momentum and does not see the gradient's scale, so when |g| of a tensor surges
+        the step stays full.  While |g| <= damp x usual nothing changes; above it the gradient enters the momentum
+        clipped to damp x usual and the step shrinks by (damp x usual / |g|)^damp_p.  Device-side, no host sync."""
+        c = self.cfg
+        gg = grad.float().pow(2).sum()
+        dv = (self.oh @ self.dv)[i]                                        # usual |g|^2 on the current card
+        started = dv > 0
+        ratio = torch.where(started & (gg > 0), (gg / dv.clamp(min=1e-38)).sqrt(), torch.ones_like(gg))
+        f = torch.where(ratio > c.damp, c.damp / ratio, torch.ones_like(ratio))
+        into = torch.minimum(gg, (c.damp_cap ** 2) * dv)
+        new = torch.where(started, c.damp_beta * dv + (1 - c.damp_beta) * into, gg)
+        self.dv[:, i] += self.oh * (torch.where(gg > 0, new, dv) - dv)
+        self.df[i] = f
+        return (grad * f.to(grad.dtype), lr_t * f ** c.damp_p)
 
     def _frozen_mask(self, p):
         fr = getattr(p, "_frozen_rows", None)

@@ -139,8 +139,10 @@ def speed(args, device=None, out=None):
                         b.grow_bank(int(float(env["SPEED_FROZEN"]) * b.E))
             last = {}
 
-            def one(s, tr=tr, store=store, last=last):
+            def one(s, tr=tr, store=store, last=last, stage=stage):
                 last["loss"] = tr.step(store.batch(args.batch, args.seq), s)
+                if stage == "base":                          # the plain loop reads the loss on the host every step
+                    last["loss"] = torch.as_tensor(float(last["loss"]))
             for s in range(args.warmup):
                 one(s)
             ms = _time_steps(one, args.n, device)

@@ -132,3 +132,59 @@ def sync_audit(args, device=None, steps=3, out=None):
     for f in sorted(set(found)):
         print("  " + f, file=out)
     return found
+
+
+class LayerDiag:
+    """Per-heavy-layer forward / backward device time (the reference's DIAG_LAYER, full2.py:46-112).  The reference
+    synchronises between sub-phases, which breaks overlap by design; here CUDA events are recorded on the stream by
+    module hooks and read once at `report()`, so the step itself is not disturbed.
+
+        diag = LayerDiag(model); run steps; print(diag.report()); diag.close()
+    """
+
+    def __init__(self, model, layers=None):
+        self.layers = list(layers if layers is not None else getattr(model, "heavy", []))
+        self.ev = {i: {"f": [], "b": []} for i in range(len(self.layers))}
+        self.handles = []
+        self.cuda = next(model.parameters()).is_cuda
+        for i, m in enumerate(self.layers):
+            self.handles.append(m.register_forward_pre_hook(self._mark(i, "f", 0)))
+            self.handles.append(m.register_forward_hook(self._mark(i, "f", 1)))
+            self.handles.append(m.register_full_backward_pre_hook(self._mark(i, "b", 0)))
+            self.handles.append(m.register_full_backward_hook(self._mark(i, "b", 1)))
+
+    def _now(self):
+        if self.cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            return e
+        import time
+        return time.perf_counter()
+
+    def _mark(self, i, which, end):
+        def hook(*_):
+            lst = self.ev[i][which]
+            if end:
+                if lst and len(lst[-1]) == 1:
+                    lst[-1].append(self._now())
+            else:
+                lst.append([self._now()])
+        return hook
+
+    def report(self):
+        if self.cuda:
+            torch.cuda.synchronize()
+        rows = []
+        for i in range(len(self.layers)):
+            r = {"layer": i}
+            for which, name in (("f", "fwd_ms"), ("b", "bwd_ms")):
+                pairs = [p for p in self.ev[i][which] if len(p) == 2]
+                if pairs:
+                    ms = [(a.elapsed_time(b) if self.cuda else (b - a) * 1e3) for a, b in pairs]
+                    r[name] = sum(ms) / len(ms)
+            rows.append(r)
+        return rows
+
+    def close(self):
+        for h in self.handles:
+            h.remove()

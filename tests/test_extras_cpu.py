@@ -152,3 +152,47 @@ def test_long_context_generators_and_runs():
     assert 0 <= d["stored"] <= 1 and d["cards"] > 0
     rows = lc.long_speed(models=("tiny",), lens=(64,), warmup=1, n=1, device="cpu", vocab=512, out=lambda *a: None)
     assert rows[0]["ms"] > 0
+
+
+def test_instinct_gradient_surge_damping_and_surprise_brake():
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+
+    def run(damp, surge, spike):
+        torch.manual_seed(0)
+        p = torch.nn.Parameter(torch.randn(16, 8))
+        w0 = p.detach().clone()
+        opt = Instinct([p], OptConfig(lr=1e-2, norm="tensor", scale=1.0, damp=damp, surge_thr=surge))
+        steps = []
+        for s in range(6):
+            g = torch.randn(16, 8) * (0.01 * (50.0 if (spike and s == 5) else 1.0))
+            loss = torch.tensor(3.0 if not (surge and s == 5) else 9.0)
+            before = p.detach().clone()
+            opt.prepare(loss, torch.ones(4))
+            opt.update(p, g)
+            opt.finish()
+            steps.append((p.detach() - before).norm().item())
+        return steps, opt
+    plain, _ = run(0.0, 0.0, True)
+    damped, opt = run(3.0, 0.0, True)
+    assert abs(plain[4] - damped[4]) < 1e-9                       # calm steps are bit-identical in size
+    assert damped[5] < 0.2 * plain[5] and float(opt.df[0]) < 0.2   # the 50x surge is braked
+    calm, _ = run(0.0, 0.3, False)
+    assert calm[5] < 0.3 * calm[4]                                 # loss 3x the expectation: -s = 2 > 0.3
+
+
+def test_layer_diag_times_heavy_layers():
+    from memarch_b200 import build
+    from memarch_b200.utils.profile import LayerDiag, bucket_of
+    torch.manual_seed(0)
+    m = build("tiny", 256, env={"NO_MEM": "1"})
+    d = LayerDiag(m)
+    x = torch.randint(0, 256, (2, 33))
+    out, cost = m(x[:, :-1])
+    m.train_loss(out, x[:, 1:], True).backward()
+    rows = d.report()
+    d.close()
+    assert len(rows) == len(m.heavy) and all(r["fwd_ms"] > 0 and r["bwd_ms"] > 0 for r in rows)
+    assert bucket_of("void mb::gemm_tc2_kernel<false, true>") == "own tcgen05 gemm"
+    assert bucket_of("nvjet_tst_256x256_64x4_2x1_2cta_v_bz_TNT") == "library gemm"
+    assert bucket_of("mb::instinct_apply<4>") == "optimizer"

@@ -126,6 +126,15 @@ def build_artifacts(art, d, n_tokens, phrase_k, device, rank, world):
     return tag
 
 
+def model_width(name):
+    """Width of a registry model (the phrasebook artefacts are built for it); the headline model's width otherwise."""
+    try:
+        from memarch_b200.config import preset
+        return int(preset(name, VOCAB, {}).d)
+    except Exception:   # noqa: BLE001 - plain transformer names and legacy models carry no phrasebook
+        return D_MODEL
+
+
 def recipe_env(tag):
     """The reference's published 2.25 B recipe (scripts/g4_1b_b.py:5-8) with artefacts from `tag`."""
     return {
@@ -212,7 +221,7 @@ def run_ours(args):
     from memarch_b200.ops import _ext
     from memarch_b200.train import Trainer
     _ext.load(required=True)
-    tag = build_artifacts(args.art, D_MODEL, args.corpus_tokens, args.phrase_k, dev, rank, world)
+    tag = build_artifacts(args.art, model_width(args.model), args.corpus_tokens, args.phrase_k, dev, rank, world)
     env = recipe_env(tag)
     torch.manual_seed(0)
     with torch.device(dev):                      # parameters are created on the GPU (same seed on every rank)
@@ -293,7 +302,7 @@ def _run_reference(args, ref_dir):
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    tag = build_artifacts(args.art, D_MODEL, args.corpus_tokens, args.phrase_k, dev, rank, world)
+    tag = build_artifacts(args.art, model_width(args.model), args.corpus_tokens, args.phrase_k, dev, rank, world)
     os.environ.update(recipe_env(tag))
     os.environ["DEVICE"] = "cuda"
     if world > 1:

@@ -40,6 +40,11 @@ std::vector<torch::Tensor> anchor_select(torch::Tensor s, torch::Tensor tau, int
 std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C);
 std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_keys, bool longest_only);
 std::vector<torch::Tensor> moe_route_fwd(torch::Tensor logits, torch::Tensor real, torch::Tensor k_tok, int64_t k_max);
+std::vector<torch::Tensor> mem_read_fwd(torch::Tensor q, torch::Tensor faces, torch::Tensor valid, torch::Tensor dim_pen,
+                                        int64_t Fn, double scale);
+std::vector<torch::Tensor> mem_read_bwd(torch::Tensor q, torch::Tensor faces, torch::Tensor valid, torch::Tensor w,
+                                        torch::Tensor best, torch::Tensor dw, c10::optional<torch::Tensor> dsc, int64_t Fn,
+                                        double scale);
 torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Tensor k_tok, torch::Tensor real, torch::Tensor dw,
                             c10::optional<torch::Tensor> dprobs, c10::optional<torch::Tensor> dpsum);
 }  // namespace mb
@@ -71,6 +76,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("anchor_select", &mb::anchor_select);
   m.def("moe_slots", &mb::moe_slots);
   m.def("lock_find", &mb::lock_find);
+  m.def("mem_read_fwd", &mb::mem_read_fwd);
+  m.def("mem_read_bwd", &mb::mem_read_bwd);
   m.def("moe_route_fwd", &mb::moe_route_fwd);
   m.def("moe_route_bwd", &mb::moe_route_bwd);
 }

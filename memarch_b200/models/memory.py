@@ -62,6 +62,33 @@ def _count_before(mask):
     return mask.long().cumsum(-1)
 
 
+class _ReadScores(torch.autograd.Function):
+    """Fused card scores + softmax on the GPU (`csrc/memops.cu`): face normalisation, best link of the chain, dim
+    penalty, empty-card mask and the softmax over cards in one kernel; backward in one kernel."""
+
+    @staticmethod
+    def forward(ctx, q, faces, valid, dim_pen, Fn, scale):
+        from ..ops import _ext
+        sc, w, best = _ext.C().mem_read_fwd(q.contiguous(), faces.contiguous(), valid.contiguous(),
+                                            dim_pen.reshape(()).float(), int(Fn), float(scale))
+        _ext.count()
+        ctx.save_for_backward(q, faces, valid, w, best)
+        ctx.meta = (int(Fn), float(scale))
+        ctx.mark_non_differentiable(best)
+        return sc, w
+
+    @staticmethod
+    def backward(ctx, dsc, dw):
+        from ..ops import _ext
+        q, faces, valid, w, best = ctx.saved_tensors
+        Fn, scale = ctx.meta
+        dq, dfa, dpen = _ext.C().mem_read_bwd(q.contiguous(), faces.contiguous(), valid.contiguous(), w, best,
+                                              dw.contiguous().float() if dw is not None else torch.zeros_like(w),
+                                              dsc.contiguous().float() if dsc is not None else None, Fn, scale)
+        _ext.count()
+        return dq, dfa, None, dpen.to(q.dtype), None, None
+
+
 class CardMemory(nn.Module):
     META = ("faces", "pos", "valid", "bright", "uses", "touched")
 
@@ -118,9 +145,15 @@ class CardMemory(nn.Module):
         """h (B,S,d) words of the segment -> (addition to h, detached read weight of every card)."""
         n = self.norm_r(h)
         q = F.normalize(self.query(n), dim=-1)
-        sc = self.card_scores(q, scale_grad(st["faces"], grad_scale), st["valid"])
-        any_card = st["valid"].any(-1)[:, None, None]
-        w = F.softmax(sc.float(), -1).type_as(h) * any_card
+        from ..ops import _ext
+        if (_ext.use_cuda(q) and q.dtype == torch.float32 and st["faces"].dtype == torch.float32
+                and self.df % 32 == 0 and self.df <= 128 and self.nf <= 255):
+            sc, w = _ReadScores.apply(q, scale_grad(st["faces"], grad_scale), st["valid"],
+                                      F.logsigmoid(self.dim_weight), self.Fn, math.sqrt(self.df))
+        else:
+            sc = self.card_scores(q, scale_grad(st["faces"], grad_scale), st["valid"])
+            any_card = st["valid"].any(-1)[:, None, None]
+            w = F.softmax(sc.float(), -1).type_as(h) * any_card
         vals = self.value(self.norm_c(scale_grad(self.contents(st), grad_scale)))
         mem = torch.einsum("bsc,bcd->bsd", w, vals)
         k = min(self.K, st["touched"].shape[1])

@@ -269,3 +269,35 @@ def test_rmsnorm_bwd_wide_rows():
         torch.nn.functional.rms_norm(xr, (d,), wr, 1e-6).backward(go.float())
         assert torch.allclose(x.grad, xr.grad, atol=2e-2, rtol=2e-2), d
         assert torch.allclose(w.grad, wr.grad, atol=5e-2, rtol=2e-2), d
+
+
+def test_memory_read_kernel_matches_torch_path():
+    """Fused card scores + softmax (forward and gradients) against the PyTorch formulation of the same read."""
+    import os
+    from memarch_b200.models.memory import CardMemory
+    torch.manual_seed(0)
+    mem = CardMemory(128, fresh=16, dim=32, dim_max=48, faces=2, d_face=64, write=8, focus=4).cuda()
+    B, S = 3, 40
+    st = mem.init_state(B, "cuda")
+    st["faces"] = torch.randn_like(st["faces"]).requires_grad_()
+    st["valid"] = torch.rand(B, 64, device="cuda") > 0.3
+    st["valid"][2] = False                                    # a text with no cards at all
+    st["fc"] = torch.randn_like(st["fc"])
+    st["dc"] = torch.randn_like(st["dc"])
+    st["touched"] = torch.rand(B, 64, device="cuda")
+    h = torch.randn(B, S, 128, device="cuda", requires_grad=True)
+
+    def run(force_torch):
+        os.environ["MEMARCH_FORCE_TORCH"] = "1" if force_torch else "0"
+        try:
+            for t in (h, st["faces"], *mem.parameters()):
+                t.grad = None
+            out, w = mem.read(h, st, grad_scale=0.5)
+            (out.square().sum() + 0).backward()
+            return out.detach(), w, h.grad.clone(), st["faces"].grad.clone(), mem.dim_weight.grad.clone(), mem.query.weight.grad.clone()
+        finally:
+            os.environ.pop("MEMARCH_FORCE_TORCH", None)
+    a, b = run(False), run(True)
+    names = ("out", "w", "dh", "dfaces", "d dim_weight", "d query")
+    for x, y, nm in zip(a, b, names):
+        assert torch.allclose(x, y, atol=2e-4, rtol=2e-3), (nm, (x - y).abs().max())

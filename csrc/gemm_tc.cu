@@ -35,6 +35,7 @@ struct GemmParams {
   int ldo, ldo2, ldaux;                // row pitches in elements
   int epi, out_f32, accumulate;
   int m_tiles, n_tiles;
+  int l2pf;                  // > 0: the producer prefetches the boxes of k-block kb + l2pf (possibly of its next tile) into L2
   int ntail;                 // 1: the last N tile issues MMAs only as wide as its valid columns (rounded up to 16)
   uint32_t lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b;   // shared-memory descriptor geometry in bytes
   int* status;
@@ -231,6 +232,24 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
         const CUtensorMap* tA = &tmAs.m[seg];
         const int ga = g + p.a_g_off;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (p.l2pf > 0 && p.epi != EPI_SWIGLU) {
+            int kk = kb + p.l2pf, tt = t;
+            if (kk >= num_kb) { kk -= num_kb; tt = t + gridDim.x; }
+            if (tt < total && kk < num_kb) {
+              int g2 = g, mt2 = mt, nt2 = nt;
+              if (tt != t) tile_coords(tt, p, g2, mt2, nt2);
+              const int seg2 = mt2 / p.tiles_per_seg;
+              const int m2 = (mt2 - seg2 * p.tiles_per_seg) * BM, n2 = nt2 * BN, k2 = kk * BK, ga2 = g2 + p.a_g_off;
+              const CUtensorMap* tA2 = &tmAs.m[seg2];
+              if (!A_MN) tma_prefetch_3d(tA2, k2, m2, ga2);
+              else { tma_prefetch_3d(tA2, m2, k2, ga2); tma_prefetch_3d(tA2, m2 + 64, k2, ga2); }
+              if (!B_MN) tma_prefetch_3d(&tmB, k2, n2, g2);
+              else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tma_prefetch_3d(&tmB, n2 + 64 * j, k2, g2);
+              }
+            }
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
           }
@@ -402,6 +421,26 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
         const CUtensorMap* tA = &tmAs.m[seg];
         const int ga = g + p.a_g_off;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (p.l2pf > 0) {
+            // L2 prefetch `l2pf` k-blocks ahead of the shared-memory ring; past the end of this tile, the first
+            // blocks of this pair's next tile
+            int kk = kb + p.l2pf, tt = t;
+            if (kk >= num_kb) { kk -= num_kb; tt = t + npairs; }
+            if (tt < total && kk < num_kb) {
+              int g2 = g, mt2 = mt, nt2 = nt;
+              if (tt != t) tile_coords(tt, p, g2, mt2, nt2);
+              const int seg2 = mt2 / p.tiles_per_seg;
+              const int m2 = (mt2 - seg2 * p.tiles_per_seg) * 256 + (int)rank * BM;
+              const int nb2 = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt2 * 128 : (p.N >> 1) + nt2 * 128)
+                                                    : nt2 * BN + (int)rank * (tile_n_eff(p, nt2) >> 1);
+              const CUtensorMap* tA2 = &tmAs.m[seg2];
+              const int k2 = kk * BK, ga2 = g2 + p.a_g_off;
+              if (!A_MN) tma_prefetch_3d(tA2, k2, m2, ga2);
+              else { tma_prefetch_3d(tA2, m2, k2, ga2); tma_prefetch_3d(tA2, m2 + 64, k2, ga2); }
+              if (!B_MN) tma_prefetch_3d(&tmB, k2, nb2, g2);
+              else { tma_prefetch_3d(&tmB, nb2, k2, g2); tma_prefetch_3d(&tmB, nb2 + 64, k2, g2); }
+            }
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
           }
@@ -604,6 +643,8 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
   }
   static const bool ntail_on = []() { const char* e = std::getenv("MEMARCH_GEMM_NTAIL"); return !(e && e[0] == '0'); }();
   p.ntail = ntail_on ? 1 : 0;
+  static const int l2pf = []() { const char* e = std::getenv("MEMARCH_GEMM_L2PF"); return e ? std::atoi(e) : 0; }();
+  p.l2pf = std::min(l2pf, (K + BK - 1) / BK);
   const int total = G * p.m_tiles * p.n_tiles;
   int grid = pair ? 2 * std::min(total, max_ctas / 2) : std::min(total, max_ctas);
   if (grid <= 0) return;

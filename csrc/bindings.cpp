@@ -16,6 +16,7 @@ void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs,
                     int64_t numel, bool is_bf16, int64_t rank, double scale);
 void gemm_set_desc_override(std::vector<int64_t> v);
 void gemm_set_pair(bool on);
+void gemm_set_profile(c10::optional<torch::Tensor> buf);
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16);
 std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd,
                                        c10::optional<torch::Tensor> add, bool want_lo);
@@ -53,6 +54,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &mb::gemm, "tcgen05 GEMM C = A * B^T (bf16, fp32 accumulate in TMEM)");
   m.def("gemm_status", &mb::gemm_status, "read and clear the GEMM status word (0 = ok)");
   m.def("gemm_set_pair", &mb::gemm_set_pair, "switch the CTA-pair (cta_group::2) GEMM kernel on or off");
+  m.def("gemm_set_profile", &mb::gemm_set_profile, "per-CTA cycle counters of the pair kernel roles (pass None to stop)");
   m.def("gemm_set_desc_override", &mb::gemm_set_desc_override, "test hook: shared-memory descriptor geometry");
   m.def("gemm_peer", &mb::gemm_peer, "segmented GEMM: A tiles from peer buffers, result rows to the owners' buffers");
   m.def("peer_barrier", &mb::peer_barrier, "bounded device-side barrier over symmetric flags");

@@ -35,7 +35,7 @@ struct GemmParams {
   int ldo, ldo2, ldaux;                // row pitches in elements
   int epi, out_f32, accumulate;
   int m_tiles, n_tiles;
-  int l2pf;                  // > 0: the producer prefetches the boxes of k-block kb + l2pf (possibly of its next tile) into L2
+  long long* prof;           // optional: per-CTA cycle counters of the pair kernel's roles (8 int64 per CTA), or null
   int ntail;                 // 1: the last N tile issues MMAs only as wide as its valid columns (rounded up to 16)
   uint32_t lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b;   // shared-memory descriptor geometry in bytes
   int* status;
@@ -232,24 +232,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
         const CUtensorMap* tA = &tmAs.m[seg];
         const int ga = g + p.a_g_off;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (p.l2pf > 0 && p.epi != EPI_SWIGLU) {
-            int kk = kb + p.l2pf, tt = t;
-            if (kk >= num_kb) { kk -= num_kb; tt = t + gridDim.x; }
-            if (tt < total && kk < num_kb) {
-              int g2 = g, mt2 = mt, nt2 = nt;
-              if (tt != t) tile_coords(tt, p, g2, mt2, nt2);
-              const int seg2 = mt2 / p.tiles_per_seg;
-              const int m2 = (mt2 - seg2 * p.tiles_per_seg) * BM, n2 = nt2 * BN, k2 = kk * BK, ga2 = g2 + p.a_g_off;
-              const CUtensorMap* tA2 = &tmAs.m[seg2];
-              if (!A_MN) tma_prefetch_3d(tA2, k2, m2, ga2);
-              else { tma_prefetch_3d(tA2, m2, k2, ga2); tma_prefetch_3d(tA2, m2 + 64, k2, ga2); }
-              if (!B_MN) tma_prefetch_3d(&tmB, k2, n2, g2);
-              else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) tma_prefetch_3d(&tmB, n2 + 64 * j, k2, g2);
-              }
-            }
-          }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
           }
@@ -413,6 +395,7 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prof_wait = 0;
       for (int t = pair; t < total && ok; t += npairs) {
         int g, mt, nt;
         tile_coords(t, p, g, mt, nt);
@@ -421,29 +404,11 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
         const CUtensorMap* tA = &tmAs.m[seg];
         const int ga = g + p.a_g_off;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (p.l2pf > 0) {
-            // L2 prefetch `l2pf` k-blocks ahead of the shared-memory ring; past the end of this tile, the first
-            // blocks of this pair's next tile
-            int kk = kb + p.l2pf, tt = t;
-            if (kk >= num_kb) { kk -= num_kb; tt = t + npairs; }
-            if (tt < total && kk < num_kb) {
-              int g2 = g, mt2 = mt, nt2 = nt;
-              if (tt != t) tile_coords(tt, p, g2, mt2, nt2);
-              const int seg2 = mt2 / p.tiles_per_seg;
-              const int m2 = (mt2 - seg2 * p.tiles_per_seg) * 256 + (int)rank * BM;
-              const int nb2 = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt2 * 128 : (p.N >> 1) + nt2 * 128)
-                                                    : nt2 * BN + (int)rank * (tile_n_eff(p, nt2) >> 1);
-              const CUtensorMap* tA2 = &tmAs.m[seg2];
-              const int k2 = kk * BK, ga2 = g2 + p.a_g_off;
-              if (!A_MN) tma_prefetch_3d(tA2, k2, m2, ga2);
-              else { tma_prefetch_3d(tA2, m2, k2, ga2); tma_prefetch_3d(tA2, m2 + 64, k2, ga2); }
-              if (!B_MN) tma_prefetch_3d(&tmB, k2, nb2, g2);
-              else { tma_prefetch_3d(&tmB, nb2, k2, g2); tma_prefetch_3d(&tmB, nb2 + 64, k2, g2); }
-            }
-          }
+          const long long tw0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
           }
+          if (p.prof) prof_wait += clock64() - tw0;                        // producer: waiting for a free stage
           uint8_t* sA = smem + stage * STAGE2_BYTES;
           uint8_t* sB = sA + A_BYTES;
           const uint32_t lfull = mapa_shared(smem_u32(&full[stage]), 0);      // the leader's barrier
@@ -468,6 +433,7 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
           if (++stage == STAGES2) { stage = 0; phase ^= 1; }
         }
       }
+      if (p.prof) p.prof[blockIdx.x * 8 + 5] = prof_wait;
       if (!ok) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
@@ -480,19 +446,25 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const long long t_all0 = p.prof ? clock64() : 0;
+      long long prof_acc = 0, prof_full = 0, prof_tiles = 0;
       for (int t = pair; t < total && ok; t += npairs) {
         int g_, mt_, nt_;
         tile_coords(t, p, g_, mt_, nt_);
         const uint32_t idesc = idesc_bf16(256, tile_n_eff(p, nt_), A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+        const long long tm0 = p.prof ? clock64() : 0;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
         }
+        if (p.prof) { prof_acc += clock64() - tm0; prof_tiles += 1; }      // MMA: accumulator not free
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long tf0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_FULL); *abort_flag = 1; ok = false; break;
           }
+          if (p.prof) prof_full += clock64() - tf0;                        // MMA: operands not there yet
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + stage * STAGE2_BYTES);
           const uint32_t sB = sA + A_BYTES;
@@ -509,6 +481,10 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
         umma_commit_pair(&tfull[acc], 3);           // accumulators of both CTAs complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_all0;                  // MMA thread: whole tile loop
+        p.prof[blockIdx.x * 8 + 1] = prof_acc; p.prof[blockIdx.x * 8 + 2] = prof_full; p.prof[blockIdx.x * 8 + 3] = prof_tiles;
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
@@ -516,22 +492,30 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    long long prof_e_wait = 0, prof_e_work = 0;
     for (int t = pair; t < total && ok; t += npairs) {
       int g, mt, nt;
       tile_coords(t, p, g, mt, nt);
+      const long long te0 = (p.prof && warp == 2 && lane == 0) ? clock64() : 0;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
         if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_TMEM_FULL); *abort_flag = 1; }
         ok = false; break;
       }
+      const long long te1 = (p.prof && warp == 2 && lane == 0) ? clock64() : 0;
       tc_fence_after();
       const int seg = mt / p.tiles_per_seg;
       const int row_l = (mt - seg * p.tiles_per_seg) * 256 + (int)rank * BM + q * 32 + lane;
       epilogue_tile(p, g, seg, row_l, nt, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN);
       tc_fence_before();
       __syncwarp();
+      if (p.prof && warp == 2 && lane == 0) {
+        prof_e_wait += te1 - te0;                                         // epilogue: waiting for the accumulator
+        prof_e_work += clock64() - te1;                                   // epilogue: draining it
+      }
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));   // the leader's MMA thread waits on it
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 8 + 6] = prof_e_wait; p.prof[blockIdx.x * 8 + 7] = prof_e_work; }
   }
 
   tc_fence_before();
@@ -610,6 +594,16 @@ static bool use_pair_kernel() {
 }
 void gemm_set_pair(bool on) { g_pair = on ? 1 : 0; }
 
+static long long* g_prof = nullptr;
+void gemm_set_profile(c10::optional<torch::Tensor> buf) {
+  if (buf.has_value() && buf->defined()) {
+    TORCH_CHECK(buf->is_cuda() && buf->scalar_type() == torch::kInt64 && buf->numel() >= 148 * 8 && buf->is_contiguous(),
+                "gemm_set_profile: int64 CUDA tensor of at least 148*8 elements");
+    g_prof = reinterpret_cast<long long*>(buf->data_ptr<int64_t>());
+  } else {
+    g_prof = nullptr;
+  }
+}
 static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};   // test hook: lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b
 void gemm_set_desc_override(std::vector<int64_t> v) {
   for (int i = 0; i < 6; ++i) g_desc_override[i] = i < (int)v.size() ? (int)v[i] : -1;
@@ -643,8 +637,7 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
   }
   static const bool ntail_on = []() { const char* e = std::getenv("MEMARCH_GEMM_NTAIL"); return !(e && e[0] == '0'); }();
   p.ntail = ntail_on ? 1 : 0;
-  static const int l2pf = []() { const char* e = std::getenv("MEMARCH_GEMM_L2PF"); return e ? std::atoi(e) : 0; }();
-  p.l2pf = std::min(l2pf, (K + BK - 1) / BK);
+  p.prof = g_prof;
   const int total = G * p.m_tiles * p.n_tiles;
   int grid = pair ? 2 * std::min(total, max_ctas / 2) : std::min(total, max_ctas);
   if (grid <= 0) return;

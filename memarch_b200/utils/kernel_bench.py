@@ -143,6 +143,40 @@ def cmd_experts(a):
     report(f"expert FFN relu2 fwd+bwd E{E} C{C} d{d} H{H}", timeit(fb, a.iters), 3 * 2 * 2.0 * E * C * d * H)
 
 
+def cmd_roles(a):
+    """Where the CTA-pair GEMM spends its cycles: per-role wait counters written by the kernel itself."""
+    from memarch_b200.ops import _ext, gemm
+    C = _ext.C()
+    M, N, K, G = a.m, a.n, a.k, a.groups
+    A = torch.randn(G, M, K, device="cuda").bfloat16()
+    B = (torch.randn(G, K, N, device="cuda") if a.b_mn else torch.randn(G, N, K, device="cuda")).bfloat16()
+    out = torch.empty(G, M, N, device="cuda", dtype=torch.bfloat16)
+    out2 = torch.empty_like(out) if a.epi == 1 else None
+    run = lambda: gemm(A, B, b_mn=a.b_mn, out=out, out2=out2, epi=a.epi, groups=G)
+    for _ in range(3):
+        run()
+    buf = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
+    C.gemm_set_profile(buf)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run()
+    e1.record()
+    torch.cuda.synchronize()
+    C.gemm_set_profile(None)
+    v = buf.view(148, 8).double()
+    lead = v[0::2]                                   # leader CTAs carry the MMA counters
+    tiles = lead[:, 3].mean().item()
+    tot = lead[:, 0].mean().item()
+    kb = (K + 63) // 64
+    print(f"pair GEMM G{G} M{M} N{N} K{K} epi{a.epi}: {e0.elapsed_time(e1):.3f} ms, {tiles:.1f} tiles per pair, "
+          f"{tot / max(tiles, 1):.0f} cycles per tile ({kb * 512} of them MMA at full rate)")
+    print(f"  MMA thread waits per tile: accumulator not free {lead[:, 1].mean().item() / max(tiles, 1):.0f}, operands not there "
+          f"{lead[:, 2].mean().item() / max(tiles, 1):.0f} ({lead[:, 2].mean().item() / max(tiles * kb, 1):.0f} per k-block)")
+    print(f"  producer waits for a free stage per tile: {v[:, 5].mean().item() / max(tiles, 1):.0f}")
+    print(f"  epilogue per tile: waiting for the accumulator {v[:, 6].mean().item() / max(tiles, 1):.0f}, draining it "
+          f"{v[:, 7].mean().item() / max(tiles, 1):.0f}")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="memarch_b200 bench-kernel")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -159,11 +193,15 @@ def main(argv=None):
     e = sub.add_parser("experts")
     e.add_argument("--e", type=int, default=8); e.add_argument("--c", type=int, default=2049)
     e.add_argument("--d", type=int, default=2048); e.add_argument("--h", type=int, default=6144)
+    r = sub.add_parser("roles")
+    r.add_argument("--m", type=int, default=8192); r.add_argument("--n", type=int, default=8192)
+    r.add_argument("--k", type=int, default=8192); r.add_argument("--groups", type=int, default=1)
+    r.add_argument("--b-mn", dest="b_mn", action="store_true"); r.add_argument("--epi", type=int, default=0)
     for p in (g, c, i, e):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
-    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts}[a.cmd](a)
+    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "roles": cmd_roles}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -237,6 +237,13 @@ def run_ours(args):
     if world > 1:
         from memarch_b200.parallel import ParallelEngine
         parallel = ParallelEngine(rank, world, local, fused=args.mode == "fused")
+        if parallel.fused_impl is not None:
+            # the peer paths are checked on this set of GPUs before the run; if anything is off, the run uses NCCL
+            ok, why = parallel.fused_impl.selftest()
+            if not ok:
+                print(f"[bench] rank {rank}: fused self-test failed ({why}); using the NCCL mode", file=sys.stderr, flush=True)
+                args.mode = "nccl"
+                parallel = ParallelEngine(rank, world, local, fused=False)
     tr = Trainer(model, tcfg, ocfg, stage="ABX", parallel=parallel, graph=bool(args.graph))
     toks = np.load(os.path.join(tag, "tokens.npy"))
     store = TokenStore(toks, seed=1 + rank, device=dev)

@@ -287,3 +287,69 @@ class FusedParallel:
         self.dp.trainer = trainer
         if os.environ.get("MEMARCH_DP", "fused") == "fused":
             self.dp.allocate(trainer.params)
+
+    def selftest(self, tol=3e-2):
+        """Small end-to-end check of the peer paths on this set of GPUs: barrier, the one-shot all-reduce (NVLS and plain
+        peer loads) against NCCL, and the fused expert exchange (forward and backward) against a local computation
+        from all-gathered inputs.  Returns (ok, message); every rank gets the same answer.  Costs a few host syncs,
+        so it belongs before a run, not inside it."""
+        heap, W, r = self.heap, self.heap.W, self.heap.rank
+        dev = torch.device("cuda", torch.cuda.current_device())
+        C = _ext.C()
+        msg = "ok"
+        try:
+            heap.barrier(0)
+            torch.cuda.synchronize()
+            heap.check()
+            # ---- all-reduce
+            n = 1 << 16
+            buf, bh = heap.alloc((n,), torch.float32)
+            out, oh = heap.alloc((n,), torch.float32)
+            g = torch.Generator(device=dev).manual_seed(100 + r)
+            x = torch.randn(n, device=dev, generator=g)
+            want = x.clone()
+            dist.all_reduce(want, group=heap.group)
+            want /= W
+            ip, op = [int(p) for p in bh.buffer_ptrs], [int(p) for p in oh.buffer_ptrs]
+            modes = [(0, 0)]
+            try:
+                if os.environ.get("MEMARCH_NVLS", "1") == "1" and int(bh.multicast_ptr) and int(oh.multicast_ptr):
+                    modes.append((int(bh.multicast_ptr), int(oh.multicast_ptr)))
+            except Exception:     # noqa: BLE001 - no multicast object on this system
+                pass
+            for mi, mo in modes:
+                buf.copy_(x)
+                out.zero_()
+                heap.barrier(1)
+                C.peer_allreduce(ip, op, mi, mo, 0, n, False, r, 1.0 / W)
+                heap.barrier(1)
+                torch.cuda.synchronize()
+                heap.check()
+                err = (out - want).abs().max().item()
+                if not err < 1e-4:
+                    raise RuntimeError(f"peer all-reduce ({'NVLS' if mi else 'P2P'}) differs from NCCL by {err:.3e}")
+            # ---- fused expert exchange
+            E, Cn, d, H = W, 300, 256, 512
+            torch.manual_seed(7)
+            up_all = (torch.randn(E, d, H, device=dev) * d ** -0.5).bfloat16()
+            down_all = (torch.randn(E, H, d, device=dev) * H ** -0.5).bfloat16()
+            up, down = up_all[r:r + 1].clone().requires_grad_(), down_all[r:r + 1].clone().requires_grad_()
+            xe = torch.randn(E, Cn, d, device=dev, generator=g).bfloat16().requires_grad_()
+            y = _FusedExpertFFN.apply(xe, up, down, self.ep, "selftest", "relu2", r, 1, True)
+            go = torch.randn(E, Cn, d, device=dev, generator=g).bfloat16()
+            y.backward(go)
+            torch.cuda.synchronize()
+            heap.check()
+            xr = xe.detach().float().requires_grad_()
+            yr = torch.bmm(torch.relu(torch.bmm(xr, up_all.float())) ** 2, down_all.float())
+            yr.backward(go.float())
+            rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-9)).item()
+            e1, e2 = rel(y, yr), rel(xe.grad, xr.grad)
+            if not (e1 < tol and e2 < tol):
+                raise RuntimeError(f"fused expert exchange differs from the local computation: fwd {e1:.3e}, bwd {e2:.3e}")
+        except Exception as e:   # noqa: BLE001 - the reason travels in the message
+            msg = f"{type(e).__name__}: {e}"
+        flag = torch.tensor([1.0 if msg == "ok" else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=heap.group)
+        ok = bool(flag.item() > 0.5)
+        return ok, (msg if msg != "ok" or ok else "another rank failed")

@@ -35,6 +35,7 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         if eng.fused_impl is not None:
             eng.fused_impl.heap.check()
+            res["selftest"] = eng.fused_impl.selftest()
         res[mode] = (losses, {k: v.detach().float().cpu().numpy() for k, v in m.state_dict().items()
                               if v.dtype.is_floating_point and 0 < v.numel() < 1 << 22})
     q.put((rank, res))
@@ -56,6 +57,7 @@ def test_fused_matches_nccl_on_two_gpus():
     for p in ps:
         p.join(60)
     for rank, res in out:
+        assert res["selftest"] == (True, "ok"), (rank, res["selftest"])
         ln, lf = res["nccl"][0], res["fused"][0]
         for a, b in zip(ln, lf):
             assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (rank, ln, lf)
@@ -89,6 +91,7 @@ def _single_rank(q):
         torch.cuda.synchronize()
         if eng is not None:
             eng.fused_impl.heap.check()
+            res["selftest"] = eng.fused_impl.selftest()
         res[mode] = (losses, {k: v.detach().float().cpu().numpy() for k, v in m.state_dict().items()
                               if v.dtype.is_floating_point and 0 < v.numel() < 1 << 22})
     q.put(res)
@@ -106,6 +109,7 @@ def test_fused_kernels_on_one_rank_match_plain_path():
     p.start()
     res = q.get(timeout=240)
     p.join(60)
+    assert res["selftest"] == (True, "ok"), res["selftest"]          # the pre-run check of the peer paths itself
     for a, b in zip(res["plain"][0], res["fused"][0]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (res["plain"][0], res["fused"][0])
     for k, v in res["plain"][1].items():

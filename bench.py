@@ -370,6 +370,8 @@ def _run_reference(args, ref_dir):
 
 
 if __name__ == "__main__":
+    # stdout carries the JSON line only: NCCL's own log lines (version banner, NVLS info when NCCL_DEBUG is set) go to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     a = parse()
     if a.impl == "reference":
         run_reference(a)

@@ -208,21 +208,42 @@ __global__ void instinct_apply(InstinctArgs a, const float* __restrict__ rscale,
       ss = block_sum(ss, red) * rs * rs;
       rs *= 1.f / (sqrtf(ss / (float)a.C) + 1e-8f);
     }
-    for (long long c0 = (long long)threadIdx.x * VEC; c0 < a.C; c0 += (long long)blockDim.x * VEC) {
-      float mf[VEC], k[VEC];
+    // Column loop, software-pipelined by hand: the inputs of the next chunk are loaded before the current chunk is
+    // stored (the weight, momentum and master pointers may alias as far as the compiler knows, so it would not hoist
+    // those loads above the stores itself); this keeps two chunks of loads in flight per thread.
+    const long long cstep = (long long)blockDim.x * VEC;
+    float mf[VEC], k[VEC], t[VEC], mf_n[VEC], k_n[VEC], t_n[VEC];
+    auto load_chunk = [&](long long c0, float* mfo, float* ko, float* to) {
+      const long long i0 = base + c0;
       if (VEC == 4) {
         float4 v;
         if (fuse_row_norm) v = *reinterpret_cast<const float4*>(cache + c0);
-        else { float4 g; v = mom4(a, base + c0, g); }
-        mf[0] = v.x; mf[1 % VEC] = v.y; mf[2 % VEC] = v.z; mf[3 % VEC] = v.w;
+        else { float4 g; v = mom4(a, i0, g); }
+        mfo[0] = v.x; mfo[1 % VEC] = v.y; mfo[2 % VEC] = v.z; mfo[3 % VEC] = v.w;
         float4 k1 = c1 ? *reinterpret_cast<const float4*>(c1 + c0) : make_float4(1.f, 1.f, 1.f, 1.f);
         if (c2) { const float4 k2 = *reinterpret_cast<const float4*>(c2 + c0); k1.x *= k2.x; k1.y *= k2.y; k1.z *= k2.z; k1.w *= k2.w; }
-        k[0] = k1.x; k[1 % VEC] = k1.y; k[2 % VEC] = k1.z; k[3 % VEC] = k1.w;
+        ko[0] = k1.x; ko[1 % VEC] = k1.y; ko[2 % VEC] = k1.z; ko[3 % VEC] = k1.w;
       } else {
-        if (fuse_row_norm) mf[0] = cache[c0];
-        else { float g; mf[0] = mom1(a, base + c0, g); }
-        k[0] = (c1 ? c1[c0] : 1.f) * (c2 ? c2[c0] : 1.f);
+        if (fuse_row_norm) mfo[0] = cache[c0];
+        else { float g; mfo[0] = mom1(a, i0, g); }
+        ko[0] = (c1 ? c1[c0] : 1.f) * (c2 ? c2[c0] : 1.f);
       }
+      if (moves) {
+        if (a.w) {
+          if (VEC == 4) { const float4 w4 = *reinterpret_cast<const float4*>(a.w + i0); to[0] = w4.x; to[1 % VEC] = w4.y; to[2 % VEC] = w4.z; to[3 % VEC] = w4.w; }
+          else to[0] = a.w[i0];
+        } else if (VEC == 4) {
+          const float4 w4 = ldv4(a.p, i0, a.p_bf16); to[0] = w4.x; to[1 % VEC] = w4.y; to[2 % VEC] = w4.z; to[3 % VEC] = w4.w;
+        } else {
+          to[0] = ldv(a.p, i0, a.p_bf16);
+        }
+      }
+    };
+    long long c0 = (long long)threadIdx.x * VEC;
+    if (c0 < a.C) load_chunk(c0, mf, k, t);
+    for (; c0 < a.C; c0 += cstep) {
+      const bool has_next = c0 + cstep < a.C;
+      if (has_next) load_chunk(c0 + cstep, mf_n, k_n, t_n);
       const long long i0 = base + c0;
       uint32_t h[VEC];
 #pragma unroll
@@ -241,34 +262,30 @@ __global__ void instinct_apply(InstinctArgs a, const float* __restrict__ rscale,
         if (VEC == 4) *reinterpret_cast<float4*>(mp) = make_float4(mf[0], mf[1 % VEC], mf[2 % VEC], mf[3 % VEC]);
         else mp[0] = mf[0];
       }
-      if (!moves) continue;                                   // weight of this row / slice stays as it is
-      float t[VEC];
-      if (a.w) {
-        if (VEC == 4) { const float4 w4 = *reinterpret_cast<const float4*>(a.w + i0); t[0] = w4.x; t[1 % VEC] = w4.y; t[2 % VEC] = w4.z; t[3 % VEC] = w4.w; }
-        else t[0] = a.w[i0];
-      } else if (VEC == 4) {
-        const float4 w4 = ldv4(a.p, i0, a.p_bf16); t[0] = w4.x; t[1 % VEC] = w4.y; t[2 % VEC] = w4.z; t[3 % VEC] = w4.w;
-      } else {
-        t[0] = ldv(a.p, i0, a.p_bf16);
-      }
+      if (moves) {                                            // else: weight of this row / slice stays as it is
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) t[j] = t[j] * decay - mf[j] * rs * k[j] * step;
-      if (a.w) {
-        if (VEC == 4) *reinterpret_cast<float4*>(a.w + i0) = make_float4(t[0], t[1 % VEC], t[2 % VEC], t[3 % VEC]);
-        else a.w[i0] = t[0];
-      }
-      if (a.p_bf16) {
-        bf16* pp = reinterpret_cast<bf16*>(a.p) + i0;
-        if (VEC == 4 && !(a.sr && !a.w)) {
-          *reinterpret_cast<uint2*>(pp) = make_uint2(pack_bf16(t[0], t[1 % VEC]), pack_bf16(t[2 % VEC], t[3 % VEC]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) pp[j] = (a.sr && !a.w) ? sr_round(t[j], h[j] >> 16) : __float2bfloat16(t[j]);
+        for (int j = 0; j < VEC; ++j) t[j] = t[j] * decay - mf[j] * rs * k[j] * step;
+        if (a.w) {
+          if (VEC == 4) *reinterpret_cast<float4*>(a.w + i0) = make_float4(t[0], t[1 % VEC], t[2 % VEC], t[3 % VEC]);
+          else a.w[i0] = t[0];
         }
-      } else {
-        float* pp = reinterpret_cast<float*>(a.p) + i0;
-        if (VEC == 4) *reinterpret_cast<float4*>(pp) = make_float4(t[0], t[1 % VEC], t[2 % VEC], t[3 % VEC]);
-        else pp[0] = t[0];
+        if (a.p_bf16) {
+          bf16* pp = reinterpret_cast<bf16*>(a.p) + i0;
+          if (VEC == 4 && !(a.sr && !a.w)) {
+            *reinterpret_cast<uint2*>(pp) = make_uint2(pack_bf16(t[0], t[1 % VEC]), pack_bf16(t[2 % VEC], t[3 % VEC]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) pp[j] = (a.sr && !a.w) ? sr_round(t[j], h[j] >> 16) : __float2bfloat16(t[j]);
+          }
+        } else {
+          float* pp = reinterpret_cast<float*>(a.p) + i0;
+          if (VEC == 4) *reinterpret_cast<float4*>(pp) = make_float4(t[0], t[1 % VEC], t[2 % VEC], t[3 % VEC]);
+          else pp[0] = t[0];
+        }
+      }
+      if (has_next) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) { mf[j] = mf_n[j]; k[j] = k_n[j]; t[j] = t_n[j]; }
       }
     }
     if (fuse_row_norm) __syncthreads();                        // the row cache is reused by the next row

@@ -288,6 +288,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
             if start > 1:
                 print(f"resuming at step {start} from {ck.path}", file=out, flush=True)
         nan = NanGuard(int(env.get("NAN_EVERY", 10)))
+        nan_at = int(env.get("TRAIN_NAN_AT", 0))              # inject a non-finite loss at this step (on the host)
         spikes = SpikeLog(float(env.get("SPIKE", 2.0)))
         rb = RollbackGuard(tr, ratio=float(env.get("RB_RATIO", 1.5)), lr_mul=float(env.get("RB_LR", 0.5)),
                            warm=int(env.get("RB_WARM", 50))) if env.get("ROLLBACK") == "1" else None
@@ -336,6 +337,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 else:
                     xy_b = data.batch(args.batch * (args.seq // seq), seq)
                     loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1)
+                if nan_at and step == nan_at:                       # host-made failure for the guard tests
+                    loss = loss * float("nan")
                 nan.check(loss)
                 if dog:
                     dog.beat()

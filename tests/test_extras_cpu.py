@@ -196,3 +196,60 @@ def test_layer_diag_times_heavy_layers():
     assert bucket_of("void mb::gemm_tc2_kernel<false, true>") == "own tcgen05 gemm"
     assert bucket_of("nvjet_tst_256x256_64x4_2x1_2cta_v_bz_TNT") == "library gemm"
     assert bucket_of("mb::instinct_apply<4>") == "optimizer"
+
+
+def test_ce_exact_under_a_common_logit_offset():
+    """Adding a huge constant to every logit of a row must not change the loss or the gradient, and every gradient
+    row sums to zero (the softmax null space): the forward LSE and the backward probabilities use one rounding."""
+    from memarch_b200.ops import ref
+    torch.manual_seed(0)
+    N, d, V = 64, 32, 500
+    h = torch.randn(N, d)
+    w = torch.randn(V, d) * 0.2
+    y = torch.randint(0, V, (N,))
+    hb = torch.cat([h, torch.ones(N, 1)], 1)                  # a bias column carries the offset
+    for off in (0.0, 3000.0):
+        wb = torch.cat([w, torch.full((V, 1), off)], 1)
+        total, gh, gw, *_ = ref.linear_ce(hb, wb, y, None, None, None, None, None, 16, None)
+        if off == 0.0:
+            base, gh0 = total, gh
+        else:
+            assert abs(float(total) - float(base)) < 2e-3 * abs(float(base))
+            cos = torch.nn.functional.cosine_similarity(gh[:, :d].flatten(), gh0[:, :d].flatten(), dim=0)
+            assert cos > 0.995
+    lo = hb @ wb.t()
+    G = torch.softmax(lo - lo.max(-1, keepdim=True).values, -1)
+    G[torch.arange(N), y] -= 1
+    assert G.sum(-1).abs().max() < 1e-5
+
+
+def test_slot_table_and_flat_index_are_mutual_inverses():
+    from memarch_b200.ops import ref
+    torch.manual_seed(0)
+    N, k, E, C = 200, 2, 8, 40
+    e_flat = torch.randint(0, E + 1, (N, k))                 # E = nowhere
+    w = torch.rand(N, k)
+    table, wtab, flat_idx, dropped = ref.moe_slots(e_flat, w, E, C)
+    ok = flat_idx < E * C
+    tok = torch.arange(N)[:, None].expand(-1, k)
+    assert torch.equal(table[flat_idx[ok]], tok[ok])          # a placed choice finds its own token in its slot
+    used = table < N
+    assert int(used.sum()) == int(ok.sum())
+    assert torch.allclose(wtab[flat_idx[ok]], w[ok])
+    per = torch.bincount(e_flat[e_flat < E], minlength=E)
+    assert abs(float(dropped) - float(1 - ok.sum() / (e_flat < E).sum())) < 1e-6
+    assert all(int(used.view(E, C)[e].sum()) == min(int(per[e]), C) for e in range(E))
+
+
+def test_nomem_model_ignores_its_memory():
+    """Honest-task control: with `use_memory=False` the memory and re-reading contribute nothing."""
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    m = build("Fv2s_nomem", 256, env={})
+    x = torch.randint(0, 256, (2, 97))
+    out, cost = m(x[:, :-1])
+    loss = m.train_loss(out, x[:, 1:], True)
+    loss.backward()
+    assert float(cost) == 0.0
+    g = [p.grad for n, p in m.named_parameters() if n.startswith(("memory.", "reread.")) and p.grad is not None]
+    assert all(float(t.abs().max()) == 0.0 for t in g)

@@ -256,3 +256,24 @@ def test_speed_and_cli(tmp_path, monkeypatch, capsys):
     assert "SPEED tiny ABX" in out and "ms/step" in out
     r = json.load(open(tmp_path / "results" / "speed.json"))
     assert r[0]["flops_per_step"] > 0
+
+
+def test_injected_nan_stops_the_run_without_saving(tmp_path, monkeypatch):
+    from memarch_b200.train.guards import NonFiniteLoss
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    env = {"VOCAB": "256", "NO_MEM": "1", "CKPT_DIR": str(tmp_path / "ck"), "CKPT_EVERY": "4", "WATCHDOG": "0",
+           "TRAIN_NAN_AT": "6", "NAN_EVERY": "1"}
+    with pytest.raises(NonFiniteLoss):
+        train(Args(steps=12, eval_every=100), "cpu", env=env, out=io.StringIO())
+    st = torch.load(tmp_path / "ck" / "latest.pt", weights_only=False)
+    assert st["step"] == 4                                   # the last save is from before the failure
+
+
+def test_learns_on_a_repeated_batch():
+    """Smoke: the loss of a repeated batch drops by at least 0.05 and decreases on most steps."""
+    tr = tiny_trainer()
+    xy = batches(1)[0]
+    losses = [float(tr.step(xy, s)) for s in range(9)]
+    assert losses[0] - losses[-1] > 0.05
+    assert sum(b < a for a, b in zip(losses, losses[1:])) >= 6, losses

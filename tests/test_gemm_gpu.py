@@ -155,3 +155,27 @@ def test_pair_kernel_grouped_epilogues():
     assert _rel(gu, acc) < 1e-2
     g, u = gu.float().chunk(2, -1)
     assert _rel(hs, torch.nn.functional.silu(g) * u) < 1e-2
+
+
+def test_gemm_is_deterministic_and_leaves_the_status_clean():
+    """Same inputs, two launches of each kernel variant: identical bits (a race between roles would show as a
+    difference), status word still zero."""
+    from memarch_b200.ops import gemm
+    C = _ext()
+    A, B = _mk((1024, 512), seed=31), _mk((768, 512), seed=32)
+    for pair in (False, True):
+        C.gemm_set_pair(pair)
+        try:
+            o1 = gemm(A, B).clone()
+            o2 = gemm(A, B).clone()
+            e1 = gemm(A.view(2, 512, 512), B.view(2, 384, 512).transpose(1, 2).contiguous(), b_mn=True, epi=1,
+                      out=torch.empty(2, 512, 384, device="cuda", dtype=torch.bfloat16),
+                      out2=torch.empty(2, 512, 384, device="cuda", dtype=torch.bfloat16), groups=2).clone()
+            e2 = gemm(A.view(2, 512, 512), B.view(2, 384, 512).transpose(1, 2).contiguous(), b_mn=True, epi=1,
+                      out=torch.empty(2, 512, 384, device="cuda", dtype=torch.bfloat16),
+                      out2=torch.empty(2, 512, 384, device="cuda", dtype=torch.bfloat16), groups=2).clone()
+            torch.cuda.synchronize()
+        finally:
+            C.gemm_set_pair(True)
+        assert torch.equal(o1, o2) and torch.equal(e1, e2)
+        assert C.gemm_status(0) == 0

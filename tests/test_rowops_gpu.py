@@ -301,3 +301,26 @@ def test_memory_read_kernel_matches_torch_path():
     names = ("out", "w", "dh", "dfaces", "d dim_weight", "d query")
     for x, y, nm in zip(a, b, names):
         assert torch.allclose(x, y, atol=2e-4, rtol=2e-3), (nm, (x - y).abs().max())
+
+
+def test_instinct_step_is_deterministic():
+    """Two optimizers fed the same gradients end bit-identical (stochastic rounding is counter-based, column sums
+    use atomics only where the order cannot change the fp32 result beyond the last bit - checked here at 1e-6)."""
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    outs = []
+    for _ in range(2):
+        torch.manual_seed(0)
+        ps = [torch.nn.Parameter(torch.randn(256, 512, device="cuda").bfloat16()),
+              torch.nn.Parameter(torch.randn(4, 128, 256, device="cuda").bfloat16())]
+        opt = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, m_bf16=True, sr=True))
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for s in range(3):
+            opt.prepare(torch.tensor(3.0 - 0.1 * s, device="cuda"), torch.ones(8, device="cuda"))
+            for p in ps:
+                opt.update(p, (torch.randn(p.shape, device="cuda", generator=g) * 0.01).bfloat16())
+            opt.finish()
+        outs.append([p.detach().float().clone() for p in ps])
+    for a, b in zip(*outs):
+        assert (a - b).abs().max().item() <= 1e-6 * a.abs().max().item() + 1e-3     # at most one bf16 ulp on a few elements
+        assert (a != b).float().mean().item() < 1e-3

@@ -206,7 +206,7 @@ def emit(args, impl, world, ms, e2e, clocks, launches, extra):
            "clocks": clocks, "gpu_launches": launches}
     if e2e is not None:
         out["e2e"] = e2e
-    print(json.dumps(out), flush=True)
+    print_json(out)
 
 
 # ------------------------------------------------------------------------------------------------ our arm
@@ -290,8 +290,8 @@ def run_ours(args):
 def run_reference(args):
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.exists(os.path.join(ref_dir, "fastloop.py")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/fastloop.py not present (reference is a "
-                          "flat script tree without packaging metadata; copy /root/reference there)"}))
+        print_json({"impl": "reference", "unavailable": "baseline/_ref/fastloop.py not present (reference is a "
+                    "flat script tree without packaging metadata; copy /root/reference there)"})
         return
     try:
         _run_reference(args, ref_dir)
@@ -299,7 +299,7 @@ def run_reference(args):
         import traceback
         traceback.print_exc()
         if int(os.environ.get("RANK", 0)) == 0:
-            print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}), flush=True)
+            print_json({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"})
 
 
 def _run_reference(args, ref_dir):
@@ -369,9 +369,29 @@ def _run_reference(args, ref_dir):
         dist.destroy_process_group()
 
 
+_JSON_FD = None
+
+
+def _claim_stdout():
+    """stdout carries the JSON line only: keep a private copy of the real stdout for it and point descriptor 1 at
+    stderr, so that anything a library prints (NCCL's version banner comes through C stdio) lands on stderr."""
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def print_json(obj):
+    line = (json.dumps(obj) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, line)
+
+
 if __name__ == "__main__":
-    # stdout carries the JSON line only: NCCL's own log lines (version banner, NVLS info when NCCL_DEBUG is set) go to stderr
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    _claim_stdout()
     a = parse()
     if a.impl == "reference":
         run_reference(a)

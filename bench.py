@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", type=int, default=0, help="replay the step as a CUDA graph after 3 eager steps (0 = eager)")
     ap.add_argument("--wave", type=int, default=0, help="frozen bank experts per layer added to the 8 learning ones")
+    ap.add_argument("--mem", action="store_true", help="keep the card memory and re-reading on (the headline recipe has NO_MEM=1)")
     return ap.parse_args()
 
 
@@ -223,6 +224,8 @@ def run_ours(args):
     _ext.load(required=True)
     tag = build_artifacts(args.art, model_width(args.model), args.corpus_tokens, args.phrase_k, dev, rank, world)
     env = recipe_env(tag)
+    if args.mem:
+        env.pop("NO_MEM", None)
     torch.manual_seed(0)
     with torch.device(dev):                      # parameters are created on the GPU (same seed on every rank)
         model = build(args.model, VOCAB, env=env)

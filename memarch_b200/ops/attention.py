@@ -4,9 +4,10 @@ Reference behaviour: `F.scaled_dot_product_attention(rope(q), rope(k), v, is_cau
 window (full.py:156-157); block-masked window attention `kv <= q and q - kv < window` otherwise (FlexAttention with
 an O(T) block list, full2.py:153-181; two-block variants lm.py:448-554).
 
-GPU body: `rope_qk` kernel (in-place rotation of the q and k thirds of the packed qkv activations, inverse rotation
-in backward) followed by the window-attention kernels `attn_fwd` / `attn_bwd` (block list from window arithmetic,
-no mask tensor, exact LSE).  `MEMARCH_ATTN=lib` swaps the attention core for the library flash kernel (A/B timing).
+GPU body: `rope_qk` kernel (rotation of the q and k thirds of the packed qkv activations, `rope_merge_bwd` packs and
+rotates the three gradients back in one pass) followed by the attention core: the library flash kernel by default
+(`MEMARCH_ATTN=lib`), or the own tcgen05 forward kernel `attn_fwd_tc` (`MEMARCH_ATTN=own`, head dim 64: block list from
+window arithmetic, no mask tensor, exact LSE; its backward recomputes through the library).
 """
 from __future__ import annotations
 
@@ -71,21 +72,33 @@ class _RopeSplit(torch.autograd.Function):
 
 
 class _OwnAttn(torch.autograd.Function):
+    """Attention core on the own tcgen05 kernel (`csrc/attn_tc.cu`: S = QKt and O = PV on the tensor cores with TMEM
+    accumulators, online softmax by one thread per query row, block list from window arithmetic).  The kernel is
+    forward-only; backward recomputes through the library SDPA on the same q, k, v, so this path is for inference,
+    evaluation and A/B numerics, not the fastest training path."""
+
     @staticmethod
-    def forward(ctx, qkv, window):
+    def forward(ctx, q, k, v, window):
         C = _ext.C()
-        o, lse = C.attn_fwd(qkv, int(window))
+        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = C.attn_fwd_tc(qc, kc, vc, int(window), float(q.shape[-1]) ** -0.5)
         _ext.count()
-        ctx.save_for_backward(qkv, o, lse)
+        ctx.save_for_backward(qc, kc, vc)
         ctx.window = int(window)
         return o
 
     @staticmethod
     def backward(ctx, do):
-        qkv, o, lse = ctx.saved_tensors
-        dqkv = _ext.C().attn_bwd(do.contiguous(), qkv, o, lse, ctx.window)
-        _ext.count(3)
-        return dqkv, None
+        q, k, v = (t.detach().requires_grad_() for t in ctx.saved_tensors)
+        with torch.enable_grad():
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if ctx.window == 0 else _lib_window(q, k, v, ctx.window)
+        dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+        return dq, dk, dv, None
+
+
+def own_attention(q, k, v, window=0):
+    """q, k, v (B,H,T,64) bf16 with RoPE applied -> o (B,H,T,64); `window` 0 = plain causal."""
+    return _OwnAttn.apply(q, k, v, int(window or 0))
 
 
 def _lib_window(q, k, v, window):
@@ -116,11 +129,9 @@ def attention(qkv, window=None, rope_half=False, qk_norm=False):
     B, T, _, H, hd = qkv.shape
     win = None if (window is None or window >= T) else int(window)
     if _ext.use_cuda(qkv) and qkv.dtype == torch.bfloat16 and not qk_norm and hd % 8 == 0:
-        if ATTN_CORE == "own" and hd in (64, 128):
-            r = _RopeQK.apply(qkv, rope_half)
-            o = _OwnAttn.apply(r, win if win is not None else 0)
-            return o.reshape(B, T, H * hd)
         q, k, v = _RopeSplit.apply(qkv, rope_half)
+        if ATTN_CORE == "own" and hd == 64:
+            return own_attention(q, k, v, win or 0).transpose(1, 2).reshape(B, T, H * hd)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _lib_window(q, k, v, win)
         return o.transpose(1, 2).reshape(B, T, H * hd)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]

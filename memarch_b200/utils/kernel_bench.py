@@ -143,6 +143,22 @@ def cmd_experts(a):
     report(f"expert FFN relu2 fwd+bwd E{E} C{C} d{d} H{H}", timeit(fb, a.iters), 3 * 2 * 2.0 * E * C * d * H)
 
 
+def cmd_attn(a):
+    """Own tcgen05 attention forward against the library SDPA: parity and TFLOP/s over the visited blocks."""
+    import torch.nn.functional as F
+    from memarch_b200.ops.attention import _lib_window, own_attention
+    B, H, T, W = a.batch, a.heads, a.seq, a.window
+    q, k, v = (torch.randn(B, H, T, 64, device="cuda").bfloat16() for _ in range(3))
+    o = own_attention(q, k, v, W)
+    ref_o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if not W or W >= T else _lib_window(q, k, v, W)
+    print(f"parity rel err {rel(o, ref_o):.2e}")
+    vis = (T * (T + 1) / 2) if not W or W >= T else (T * W - W * (W - 1) / 2)
+    flops = 4.0 * B * H * vis * 64
+    report(f"own attention fwd B{B} H{H} T{T} window {W}", timeit(lambda: own_attention(q, k, v, W), a.iters), flops)
+    lib = (lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True)) if not W or W >= T else (lambda: _lib_window(q, k, v, W))
+    report("library SDPA fwd (same shape)", timeit(lib, a.iters), flops)
+
+
 def cmd_roles(a):
     """Where the CTA-pair GEMM spends its cycles: per-role wait counters written by the kernel itself."""
     from memarch_b200.ops import _ext, gemm
@@ -193,6 +209,10 @@ def main(argv=None):
     e = sub.add_parser("experts")
     e.add_argument("--e", type=int, default=8); e.add_argument("--c", type=int, default=2049)
     e.add_argument("--d", type=int, default=2048); e.add_argument("--h", type=int, default=6144)
+    t = sub.add_parser("attn")
+    t.add_argument("--batch", type=int, default=32); t.add_argument("--heads", type=int, default=32)
+    t.add_argument("--seq", type=int, default=1024); t.add_argument("--window", type=int, default=0)
+    t.add_argument("--iters", type=int, default=10)
     r = sub.add_parser("roles")
     r.add_argument("--m", type=int, default=8192); r.add_argument("--n", type=int, default=8192)
     r.add_argument("--k", type=int, default=8192); r.add_argument("--groups", type=int, default=1)
@@ -201,7 +221,7 @@ def main(argv=None):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
-    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "roles": cmd_roles}[a.cmd](a)
+    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "roles": cmd_roles, "attn": cmd_attn}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -324,3 +324,38 @@ def test_instinct_step_is_deterministic():
     for a, b in zip(*outs):
         assert (a - b).abs().max().item() <= 0.04                                   # at most one bf16 ulp, on a few elements
         assert (a != b).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("T,window", [(128, 0), (256, 0), (1024, 0), (200, 0), (512, 128), (1000, 300), (384, 64)])
+def test_own_attention_forward_matches_fp32(T, window):
+    """tcgen05 attention forward (causal and sliding window, ragged lengths) against a dense fp32 softmax."""
+    from memarch_b200.ops.attention import own_attention
+    torch.manual_seed(0)
+    B, H = 2, 3
+    q, k, v = (torch.randn(B, H, T, 64, device="cuda").bfloat16() for _ in range(3))
+    o = own_attention(q, k, v, window)
+    torch.cuda.synchronize()
+    from memarch_b200.ops import _ext
+    assert _ext.C().attn_status_read() == 0
+    s = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float()) * 64 ** -0.5
+    i = torch.arange(T, device="cuda")
+    ok = i[None, :] <= i[:, None]
+    if window:
+        ok = ok & (i[:, None] - i[None, :] < window)
+    ref = torch.softmax(s.masked_fill(~ok, float("-inf")), -1) @ v.float()
+    err = ((o.float() - ref).norm() / ref.norm()).item()
+    assert err < 1e-2, err
+    assert (o.float() - ref).abs().max().item() < 5e-2
+
+
+def test_own_attention_backward_runs_through_the_library():
+    from memarch_b200.ops.attention import own_attention
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 2, 256, 64, device="cuda").bfloat16().requires_grad_() for _ in range(3))
+    own_attention(q, k, v, 0).float().square().sum().backward()
+    g1 = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).float().square().sum().backward()
+    for a, b in zip(g1, (q.grad, k.grad, v.grad)):
+        assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 3e-2

@@ -27,7 +27,7 @@ constexpr int AT_Q_BYTES = AT_BQ * AT_HD * 2;            // 16 KB
 constexpr int AT_K_BYTES = AT_BK * AT_HD * 2;            // 16 KB
 constexpr int AT_V_BYTES = AT_BK * AT_HD * 2;            // 16 KB (two 64-key boxes of 8 KB)
 constexpr int AT_P_BYTES = AT_BQ * AT_BK * 2;            // 32 KB (two 64-wide K atoms of 16 KB)
-constexpr int AT_SMEM = AT_Q_BYTES + 2 * (AT_K_BYTES + AT_V_BYTES) + AT_P_BYTES + 1024 + 256;
+constexpr int AT_SMEM = AT_Q_BYTES + 2 * (AT_K_BYTES + AT_V_BYTES) + AT_P_BYTES + 256;   // 112.25 KB: two CTAs per SM
 
 struct AttnParams {
   int T, window;            // window 0 = plain causal
@@ -37,11 +37,11 @@ struct AttnParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];       // swizzle atoms are 1024 bytes: the base itself is aligned
+  if (threadIdx.x == 0 && (smem_u32(smem) & 1023u)) atomicCAS(p.status, 0, ST_BAD_ARG);
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + AT_Q_BYTES;                          // 2 stages
   uint8_t* sV = sK + 2 * AT_K_BYTES;                      // 2 stages

@@ -19,6 +19,7 @@ import torch.nn.functional as F
 from . import _ext, ref
 
 ATTN_CORE = os.environ.get("MEMARCH_ATTN", "lib")
+OWN_WINDOW_EVAL = os.environ.get("MEMARCH_ATTN_EVAL", "own") == "own"
 
 
 _tables = {}
@@ -130,7 +131,11 @@ def attention(qkv, window=None, rope_half=False, qk_norm=False):
     win = None if (window is None or window >= T) else int(window)
     if _ext.use_cuda(qkv) and qkv.dtype == torch.bfloat16 and not qk_norm and hd % 8 == 0:
         q, k, v = _RopeSplit.apply(qkv, rope_half)
-        if ATTN_CORE == "own" and hd == 64:
+        # own tcgen05 kernel: everywhere when asked for; by default where it is the faster one, i.e. sliding-window
+        # attention without a backward pass (evaluation / generation at long context: only the blocks under the window
+        # are visited, 3.4x faster than the dense-mask library form at T = 16k, window 256)
+        no_grad = not (torch.is_grad_enabled() and qkv.requires_grad)
+        if hd == 64 and (ATTN_CORE == "own" or (ATTN_CORE == "lib" and win is not None and no_grad and OWN_WINDOW_EVAL)):
             return own_attention(q, k, v, win or 0).transpose(1, 2).reshape(B, T, H * hd)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _lib_window(q, k, v, win)
         return o.transpose(1, 2).reshape(B, T, H * hd)

@@ -20,6 +20,7 @@ from . import _ext, ref
 
 ATTN_CORE = os.environ.get("MEMARCH_ATTN", "lib")
 OWN_WINDOW_EVAL = os.environ.get("MEMARCH_ATTN_EVAL", "own") == "own"
+WINDOW_BODY = os.environ.get("MEMARCH_WINDOW", "flash")        # library body of windowed attention with backward: flash | block
 
 
 _tables = {}
@@ -125,6 +126,28 @@ def _lib_window(q, k, v, window):
     return out.reshape(B, H, nb * W, D)[:, :, :T]
 
 
+_flash_window_ok = [None]
+
+
+def _flash_window(q, k, v, window):
+    """Sliding-window causal attention through the library flash kernel's own window arguments (key j is visible to
+    query i iff 0 <= i - j < window): cost proportional to the window, forward and backward.  q, k, v (B,H,T,hd).
+    Falls back to the two-block dense-mask form if this build of the library has no windowed flash kernel."""
+    if _flash_window_ok[0] is not False and WINDOW_BODY == "flash":
+        try:
+            T = q.shape[2]
+            o = torch.ops.aten._flash_attention_forward(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), None, None, T, T, 0.0, True, False,
+                scale=None, window_size_left=int(window) - 1, window_size_right=0)[0]
+            _flash_window_ok[0] = True
+            return o.transpose(1, 2)
+        except Exception:   # noqa: BLE001 - older library: no window arguments / unsupported head size
+            if _flash_window_ok[0] is True:
+                raise
+            _flash_window_ok[0] = False
+    return _lib_window(q, k, v, window)
+
+
 def attention(qkv, window=None, rope_half=False, qk_norm=False):
     """qkv (B,T,3,H,hd) -> (B,T,H·hd).  `window` None or >= T means plain causal."""
     B, T, _, H, hd = qkv.shape
@@ -137,7 +160,7 @@ def attention(qkv, window=None, rope_half=False, qk_norm=False):
         no_grad = not (torch.is_grad_enabled() and qkv.requires_grad)
         if hd == 64 and (ATTN_CORE == "own" or (ATTN_CORE == "lib" and win is not None and no_grad and OWN_WINDOW_EVAL)):
             return own_attention(q, k, v, win or 0).transpose(1, 2).reshape(B, T, H * hd)
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _lib_window(q, k, v, win)
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if win is None else _flash_window(q, k, v, win)
         return o.transpose(1, 2).reshape(B, T, H * hd)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
     o = ref.window_attention(q, k, v, win, rope_half, qk_norm=qk_norm)

@@ -359,3 +359,27 @@ def test_own_attention_backward_runs_through_the_library():
     torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).float().square().sum().backward()
     for a, b in zip(g1, (q.grad, k.grad, v.grad)):
         assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 3e-2
+
+
+def test_windowed_attention_routes_agree():
+    """Sliding-window attention through its three bodies: library flash kernel with window arguments (training),
+    the two-block dense-mask form (fallback), the own tcgen05 kernel (no-grad default) - same numbers, same grads."""
+    import importlib
+    from memarch_b200 import ops
+    A = importlib.import_module("memarch_b200.ops.attention")
+    torch.manual_seed(0)
+    B, T, H, hd, W = 2, 640, 4, 64, 96
+    qkv = (torch.randn(B, T, 3, H, hd, device="cuda") * 0.5).bfloat16().requires_grad_()
+    o_train = ops.attention(qkv, W)                                   # grad enabled: library flash with window
+    go = torch.randn_like(o_train)
+    o_train.backward(go)
+    g_train = qkv.grad.clone()
+    qkv.grad = None
+    with torch.no_grad():
+        o_eval = ops.attention(qkv, W)                                # no grad: own tcgen05 kernel
+    q, k, v = A._RopeSplit.apply(qkv, False)
+    o_ref = A._lib_window(q, k, v, W).transpose(1, 2).reshape(B, T, H * hd)
+    o_ref.backward(go)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(o_train, o_ref) < 1e-2 and rel(o_eval, o_ref) < 1e-2
+    assert rel(g_train, qkv.grad) < 3e-2

@@ -48,6 +48,9 @@ std::vector<torch::Tensor> mem_read_bwd(torch::Tensor q, torch::Tensor faces, to
                                         double scale);
 std::vector<torch::Tensor> attn_fwd_tc(torch::Tensor q, torch::Tensor k, torch::Tensor v, int64_t window, double scale);
 int64_t attn_status_read();
+std::vector<torch::Tensor> attn_bwd_tc(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor dout, torch::Tensor lse,
+                                       torch::Tensor delta, int64_t window, double scale);
+int64_t attn_bwd_status_read();
 torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Tensor k_tok, torch::Tensor real, torch::Tensor dw,
                             c10::optional<torch::Tensor> dprobs, c10::optional<torch::Tensor> dpsum);
 }  // namespace mb
@@ -82,6 +85,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("lock_find", &mb::lock_find);
   m.def("attn_fwd_tc", &mb::attn_fwd_tc, "causal / sliding-window attention forward on tcgen05 (head dim 64)");
   m.def("attn_status_read", &mb::attn_status_read);
+  m.def("attn_bwd_tc", &mb::attn_bwd_tc, "causal / sliding-window attention backward on tcgen05 (head dim 64)");
+  m.def("attn_bwd_status_read", &mb::attn_bwd_status_read);
   m.def("mem_read_fwd", &mb::mem_read_fwd);
   m.def("mem_read_bwd", &mb::mem_read_bwd);
   m.def("moe_route_fwd", &mb::moe_route_fwd);

@@ -20,6 +20,7 @@ from . import _ext, ref
 
 ATTN_CORE = os.environ.get("MEMARCH_ATTN", "lib")
 OWN_WINDOW_EVAL = os.environ.get("MEMARCH_ATTN_EVAL", "own") == "own"
+OWN_BWD = os.environ.get("MEMARCH_ATTN_BWD", "own") == "own"
 WINDOW_BODY = os.environ.get("MEMARCH_WINDOW", "flash")        # library body of windowed attention with backward: flash | block
 
 
@@ -74,10 +75,9 @@ class _RopeSplit(torch.autograd.Function):
 
 
 class _OwnAttn(torch.autograd.Function):
-    """Attention core on the own tcgen05 kernel (`csrc/attn_tc.cu`: S = QKt and O = PV on the tensor cores with TMEM
-    accumulators, online softmax by one thread per query row, block list from window arithmetic).  The kernel is
-    forward-only; backward recomputes through the library SDPA on the same q, k, v, so this path is for inference,
-    evaluation and A/B numerics, not the fastest training path."""
+    """Attention core on the own tcgen05 kernels (`csrc/attn_tc.cu`, `csrc/attn_bwd_tc.cu`): S = QKt, O = PV and the five
+    backward products on the tensor cores with TMEM accumulators, softmax by one thread per row, block lists from
+    window arithmetic, exact LSE.  `MEMARCH_ATTN_BWD=lib` makes backward recompute through the library instead."""
 
     @staticmethod
     def forward(ctx, q, k, v, window):
@@ -85,16 +85,23 @@ class _OwnAttn(torch.autograd.Function):
         qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
         o, lse = C.attn_fwd_tc(qc, kc, vc, int(window), float(q.shape[-1]) ** -0.5)
         _ext.count()
-        ctx.save_for_backward(qc, kc, vc)
+        ctx.save_for_backward(qc, kc, vc, o, lse)
         ctx.window = int(window)
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v = (t.detach().requires_grad_() for t in ctx.saved_tensors)
+        q, k, v, o, lse = ctx.saved_tensors
+        if OWN_BWD:
+            do = do.contiguous()
+            delta = (do.float() * o.float()).sum(-1)
+            dq, dk, dv = _ext.C().attn_bwd_tc(q, k, v, do, lse, delta, ctx.window, float(q.shape[-1]) ** -0.5)
+            _ext.count()
+            return dq.to(q.dtype), dk, dv, None
+        q, k, v = (t.detach().requires_grad_() for t in (q, k, v))
         with torch.enable_grad():
-            o = F.scaled_dot_product_attention(q, k, v, is_causal=True) if ctx.window == 0 else _lib_window(q, k, v, ctx.window)
-        dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+            o2 = F.scaled_dot_product_attention(q, k, v, is_causal=True) if ctx.window == 0 else _lib_window(q, k, v, ctx.window)
+        dq, dk, dv = torch.autograd.grad(o2, (q, k, v), do)
         return dq, dk, dv, None
 
 

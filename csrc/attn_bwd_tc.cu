@@ -198,7 +198,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_wait();
         if (q_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) atomicAdd(dqr + c * 32 + j, __uint_as_float(r[j]));
+          for (int j = 0; j < 32; j += 4)                       // 16-byte vector reduction: a quarter of the atomic traffic
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dqr + c * 32 + j), "f"(__uint_as_float(r[j])),
+                         "f"(__uint_as_float(r[j + 1])), "f"(__uint_as_float(r[j + 2])), "f"(__uint_as_float(r[j + 3])) : "memory");
         }
       }
       tc_fence_before();

@@ -157,6 +157,26 @@ def cmd_attn(a):
     report(f"own attention fwd B{B} H{H} T{T} window {W}", timeit(lambda: own_attention(q, k, v, W), a.iters), flops)
     lib = (lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True)) if not W or W >= T else (lambda: _lib_window(q, k, v, W))
     report("library SDPA fwd (same shape)", timeit(lib, a.iters), flops)
+    # forward + backward (3.5x the forward FLOPs: 2 products forward, 5 backward)
+    import importlib
+    A = importlib.import_module("memarch_b200.ops.attention")
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    go = torch.randn_like(q)
+
+    def fb(f):
+        def run():
+            qg.grad = kg.grad = vg.grad = None
+            f(qg, kg, vg).backward(go)
+        return run
+    own_f = lambda x, y, z: own_attention(x, y, z, W)
+    lib_f = (lambda x, y, z: F.scaled_dot_product_attention(x, y, z, is_causal=True)) if not W or W >= T else \
+        (lambda x, y, z: A._flash_window(x, y, z, W))
+    fb(own_f)()
+    g_own = [t.grad.clone() for t in (qg, kg, vg)]
+    fb(lib_f)()
+    print("backward parity rel err (dq, dk, dv):", " ".join(f"{rel(x, y.grad):.2e}" for x, y in zip(g_own, (qg, kg, vg))))
+    report("own attention fwd+bwd", timeit(fb(own_f), a.iters), 3.5 * flops)
+    report("library fwd+bwd (flash, window arguments where windowed)", timeit(fb(lib_f), a.iters), 3.5 * flops)
 
 
 def cmd_roles(a):

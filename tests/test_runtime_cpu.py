@@ -277,3 +277,33 @@ def test_learns_on_a_repeated_batch():
     losses = [float(tr.step(xy, s)) for s in range(9)]
     assert losses[0] - losses[-1] > 0.05
     assert sum(b < a for a, b in zip(losses, losses[1:])) >= 6, losses
+
+
+@pytest.mark.parametrize("stage", ["A", "AS", "AX", "ABX"])
+def test_trainer_stages_step_and_learn(stage):
+    """Every optimizer arrangement of the trainer takes steps and lowers the loss of a repeated batch."""
+    tr = tiny_trainer(stage=stage)
+    xy = batches(1)[0]
+    losses = [float(tr.step(xy, s)) for s in range(6)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0], (stage, losses)
+
+
+def test_micro_batches_accumulate_to_the_full_batch_gradient():
+    """Stage B steps the weights only on the last micro-batch, from the accumulated gradient: two micro-batches of 2
+    move the weights the same way as one batch of 4 (not bit-equal: the anchor threshold and the expert capacity are
+    per forward call)."""
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.train import Trainer
+    xy = batches(1)[0]
+    deltas = []
+    for micro in (4, 2):
+        torch.manual_seed(0)
+        m = build("tiny", 256, env={"NO_MEM": "1", "MOE_ACT": "relu2"})
+        w0 = m.light_a[0].qkv.weight.detach().clone()
+        tr = Trainer(m, TrainConfig(name="tiny", stage="ABX", steps=50, batch=4, micro=micro, seq=32, lr=1e-2, warmup=2),
+                     OptConfig(lr=1e-2, norm="hs", scale=0.12, rel_every=2), stage="ABX")
+        tr.step(xy, 0)
+        deltas.append((m.light_a[0].qkv.weight.detach() - w0).flatten())
+    assert deltas[0].abs().sum() > 0 and deltas[1].abs().sum() > 0
+    cos = torch.nn.functional.cosine_similarity(deltas[0], deltas[1], dim=0).item()
+    assert cos > 0.9, cos

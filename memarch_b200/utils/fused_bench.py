@@ -62,14 +62,14 @@ def main(argv=None):
     a = ap.parse_args(argv)
     from ..parallel import ParallelEngine, init_distributed
     from ..parallel.engine import _AllToAll
-    from ..parallel.fused import _FusedExpertFFN
+    from ..parallel.fused import FusedParallel, _FusedExpertFFN
     from ..ops import _ext
     from ..ops.moe import expert_ffn
     rank, W, local = init_distributed()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     eng = ParallelEngine(rank, W, local, fused=True)
-    fp = eng.fused_impl
+    fp = FusedParallel(eng)
     heap = fp.heap
     C = _ext.C()
     say = (lambda *x: print(*x, flush=True)) if rank == 0 else (lambda *x: None)

@@ -1,0 +1,224 @@
+"""Recall needles written into real text, with a success-driven distance curriculum, and the per-kind corpus of the
+layer-pool ("fishki") experiments.
+
+Behaviour follows the reference's host-side data tools (memarch_jax/memarch_jax/data.py:344-774 `Reminders`,
+200-255 `KindCorpus`):
+
+* a row gets, with probability p, a block of facts `[M k1 v1 .. kn vn M]` and, at least `dist` words later, a block of
+  questions `[M kq1 vq1 .. M]` over the same keys in a shuffled order; keys are distinct tokens of a 512-token range,
+  values come from a 64-token range, `M` is a marker token; shapes never change (the needle overwrites text);
+* `rem` (B, T) marks the positions of x that hold a question key: the target there is the value;
+* randomness depends on (seed, content of the row) only, so the same batch gets the same needles after a resume;
+* p may follow a schedule (p0 for `warm` batches, then linear over `decay` batches to p);
+* with a distance ladder the needle distance is drawn from the current level's range; a level is passed when the
+  accuracy over the last >= `win` needle answers reaches `thr`, and the next level starts `lag` batches later
+  (more than the prefetch depth, so the choice is deterministic); the last level mixes all distances;
+* `exact` (evaluation) puts exactly that many words between the two blocks;
+* `synth` batches are filler plus one needle (the pure recall task);
+* `near`: a share of the needles at distance 0..near_max, inside the attention window.
+
+Not carried over: the densely packed synthetic episodes and their own level table, answers hidden behind the marker,
+several needles per row.
+"""
+from __future__ import annotations
+
+import zlib
+
+import numpy as np
+
+N_KEYS, N_VALS = 512, 64
+
+
+class Reminders:
+    def __init__(self, p, T, n=16, dist=2048, tok0=1000, seed=0, V=None, p0=None, warm=0, decay=0, ladder=None,
+                 thr=0.9, win=800, lag=5, dmin=0, synth=0, doc_eos=None, near=0.0, near_max=0):
+        self.p, self.T, self.n, self.dist, self.seed = float(p), int(T), int(n), int(dist), int(seed)
+        self.p0 = None if p0 is None else float(p0)
+        self.warm, self.decay = int(warm), int(decay)
+        self.ladder = sorted(int(v) for v in ladder) if ladder else None
+        self.thr, self.win, self.lag, self.dmin = float(thr), int(win), int(lag), int(dmin)
+        self.synth, self.V = int(synth), V
+        self.doc_eos = None if doc_eos is None or int(doc_eos) < 0 else int(doc_eos)
+        self.near, self.near_max = float(near), int(near_max)
+        self.k0, self.v0, self.mark = tok0, tok0 + N_KEYS, tok0 + N_KEYS + N_VALS
+        self.L = 2 * self.n + 2                      # one block: marker, n (key, value) pairs, marker
+        self.changes = [(0, 0)]                      # (first batch, level)
+        self.hits = self.answers = 0.0
+        if V is not None and self.mark >= V:
+            raise ValueError(f"needle tokens {tok0}..{self.mark} do not fit a vocabulary of {V}")
+        if self.n > N_KEYS:
+            raise ValueError("more pairs than distinct keys")
+        if 2 * self.L + self.dist > self.T + 1:
+            raise ValueError(f"T={T} too short for two blocks of {self.L} and a distance of {dist}")
+        if self.ladder and self.ladder[-1] > self.T + 1 - 2 * self.L:
+            raise ValueError(f"ladder {self.ladder} exceeds the row")
+
+    # ------------------------------------------------------------------------------------------------ schedule
+    def p_at(self, i):
+        if self.p0 is None:
+            return self.p
+        if i < self.warm:
+            return self.p0
+        return self.p0 + (self.p - self.p0) * min(1.0, (i - self.warm) / max(self.decay, 1))
+
+    def synth_at(self, i):
+        return i is not None and i < self.synth
+
+    def level_at(self, i):
+        k = 0
+        for first, level in self.changes:
+            if first <= i:
+                k = level
+        return k
+
+    def range_at(self, i):
+        k = self.level_at(i)
+        if k == len(self.ladder) - 1:                # last level: every distance, short ones are not forgotten
+            return self.dmin, self.ladder[-1]
+        return (self.ladder[k - 1] if k else self.dmin), self.ladder[k]
+
+    def observe(self, i, hits, n_ans):
+        """After step i: needle accuracy of the training batch -> maybe a level change; returns a log line or None."""
+        if not self.ladder:
+            return None
+        self.hits += hits
+        self.answers += n_ans
+        k = self.changes[-1][1]
+        if self.answers < self.win or k >= len(self.ladder) - 1:
+            return None
+        acc = self.hits / self.answers
+        self.hits = self.answers = 0.0
+        if acc < self.thr:
+            return None
+        self.changes.append((i + self.lag, k + 1))
+        lo, hi = self.range_at(i + self.lag)
+        return f"reminders: level {k} -> {k + 1} (accuracy {acc:.3f}), from batch {i + self.lag} distance {lo}..{hi}"
+
+    def state(self):
+        return {"changes": [list(c) for c in self.changes], "acc_h": self.hits, "acc_n": self.answers}
+
+    def load(self, st):
+        self.changes = [tuple(c) for c in st["changes"]]
+        self.hits, self.answers = st["acc_h"], st["acc_n"]
+
+    # ------------------------------------------------------------------------------------------------ rows
+    def _filler(self, rng, n):
+        """Random words outside the needle tokens."""
+        V = self.V or (self.mark + 20001)
+        span = self.mark + 1 - self.k0
+        f = rng.integers(0, V - span, n)
+        f = np.where(f >= self.k0, f + span, f).astype(np.int32)
+        if self.doc_eos is not None:
+            f[f == self.doc_eos] = 0
+        return f
+
+    def _needle(self, row, rng, exact=None, level_range=None):
+        n, L, T1 = self.n, self.L, len(row)
+        keys = self.k0 + rng.permutation(N_KEYS)[:n]
+        vals = self.v0 + rng.integers(0, N_VALS, n)
+        if exact is None and level_range is not None:
+            exact = int(rng.integers(level_range[0], level_range[1] + 1))
+        if exact is None:
+            s = int(rng.integers(0, T1 - 2 * L - self.dist + 1))
+            q = int(rng.integers(s + L + self.dist, T1 - L + 1))
+        else:
+            if not 0 <= exact <= T1 - 2 * L:
+                raise ValueError(f"distance {exact} does not fit a row of {T1}")
+            s = int(rng.integers(0, T1 - 2 * L - exact + 1))
+            q = s + L + exact
+        order = rng.permutation(n)
+        row[s] = row[s + L - 1] = row[q] = row[q + L - 1] = self.mark
+        row[s + 1:s + L - 1] = np.stack([keys, vals], 1).reshape(-1)
+        row[q + 1:q + L - 1] = np.stack([keys[order], vals[order]], 1).reshape(-1)
+        if self.doc_eos is not None:                 # a document boundary between facts and questions would hide them
+            seg = row[s:q + L]
+            hit = seg == self.doc_eos
+            if hit.any():
+                seg[hit] = self._filler(rng, int(hit.sum()))
+        return q + 1 + 2 * np.arange(n)              # positions of the question keys in x (y there is the value)
+
+    def __call__(self, xy, p=None, exact=None, n=None, synth=None):
+        """xy (B, T+1) tokens -> (xy with needles, {"rem": (B, T) int8}).  `n` = number of the training batch."""
+        if synth is None:
+            synth = self.synth_at(n)
+        level_range = None
+        if n is not None and p is None:
+            p = self.p_at(n)
+            level_range = self.range_at(n) if self.ladder else None
+        p = self.p if p is None else p
+        xy = np.array(xy, copy=True)
+        B, T1 = xy.shape
+        rem = np.zeros((B, T1 - 1), np.int8)
+        for b in range(B):
+            rng = np.random.default_rng([self.seed, zlib.crc32(xy[b].tobytes())])
+            if synth:
+                xy[b] = self._filler(rng, T1)
+                rem[b, self._needle(xy[b], rng, exact, level_range)] = 1
+            elif rng.random() < p:
+                ex = exact
+                if ex is None and self.near > 0 and self.near_max > 0 and rng.random() < self.near:
+                    ex = int(rng.integers(0, min(self.near_max, T1 - 2 * self.L) + 1))
+                rem[b, self._needle(xy[b], rng, ex, None if ex is not None else level_range)] = 1
+        return xy, {"rem": rem}
+
+    @staticmethod
+    def score(logits_argmax, xy, rem):
+        """(hits, answers) of a batch: predictions at the marked positions against the values that follow."""
+        rem = np.asarray(rem) > 0
+        y = np.asarray(xy)[:, 1:]
+        return float((np.asarray(logits_argmax)[rem] == y[rem]).sum()), float(rem.sum())
+
+
+class KindCorpus:
+    """Every batch of a step comes from one kind of text.  `kinds`: {kind: {source: weight}}; `pools`: the layer sets
+    per kind (`models.fishki.pools`).  The kind of a step is the one furthest behind its share (depends on the step
+    number only, so all processes agree); the combination of `c` layers is drawn from the kind's pool by
+    (seed, step); `full=True` uses the whole pool in its order.  `extra()` -> {"kind": (B,1), "fish": (B,c)}."""
+
+    def __init__(self, kinds, pools, c, root, seq=8192, seed=0, rank=0, world=1, eos=None, doc_seed=None):
+        from .loader import ShardCorpus
+        self.names = list(kinds)
+        w = np.array([sum(kinds[k].values()) for k in self.names], np.float64)
+        self.p = w / w.sum()
+        base = seed if doc_seed is None else doc_seed             # other documents, same schedule of kinds
+        self.subs = [ShardCorpus(kinds[k], root, seq=seq, seed=base + 7919 * i, rank=rank, world=world, eos=eos)
+                     for i, k in enumerate(self.names)]
+        self.eos = self.subs[0].eos
+        self.pools, self.c, self.seed = pools, int(c), seed
+        self.full = False
+        self.n = 0
+        self.count = np.zeros(len(self.names))
+        self._extra = None
+
+    def _kind(self):
+        return int(np.argmax(self.p * (self.n + 1) - self.count))
+
+    def batch(self, B):
+        k = self._kind()
+        xy = self.subs[k].batch(B)
+        if self.full:
+            order = list(self.pools[k])
+        else:
+            rng = np.random.default_rng([self.seed, 31337, self.n])
+            order = [int(i) for i in rng.choice(self.pools[k], self.c, replace=False)]
+        self._extra = {"kind": np.full((B, 1), k, np.int32), "fish": np.tile(np.asarray(order, np.int32), (B, 1))}
+        self.count[k] += 1
+        self.n += 1
+        return xy
+
+    def extra(self):
+        return self._extra
+
+    def state_dict(self):
+        return {"subs": [s.state_dict() for s in self.subs], "count": self.count.tolist(), "n": self.n}
+
+    def load_state_dict(self, st):
+        if st.get("subs") is not None:                            # None: new documents from the start, same schedule
+            for s, ss in zip(self.subs, st["subs"]):
+                s.load_state_dict(ss)
+        self.count = np.array(st["count"], np.float64)
+        self.n = int(st["n"])
+
+    def mix(self):
+        t = self.count.sum() or 1
+        return {k: round(float(x / t), 4) for k, x in zip(self.names, self.count)}

@@ -1,0 +1,167 @@
+"""Recall needles in real text (schedule, ladder curriculum, determinism), the per-kind corpus, and the
+single-process stand-in for torch.distributed."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from memarch_b200.data.reminders import N_KEYS, N_VALS, KindCorpus, Reminders
+
+
+def rows(B, T1, seed=0, V=30000):
+    return np.random.default_rng(seed).integers(0, V, (B, T1)).astype(np.int32)
+
+
+def check_needle(r, x, rem_row):
+    """The marked positions hold question keys, the following tokens their values, and the same (key, value) pairs
+    stand in a facts block earlier in the row.  Returns the number of words between the two blocks."""
+    pos = np.flatnonzero(rem_row)
+    assert len(pos) == r.n
+    q = pos[0] - 1
+    assert x[q] == r.mark and x[q + r.L - 1] == r.mark
+    asked = {int(x[p]): int(x[p + 1]) for p in pos}
+    assert len(asked) == r.n and all(r.k0 <= k < r.k0 + N_KEYS and r.v0 <= v < r.v0 + N_VALS for k, v in asked.items())
+    starts = [s for s in np.flatnonzero(x[:q] == r.mark) if s + r.L - 1 < q + 1 and x[s + r.L - 1] == r.mark]
+    facts = None
+    for s in starts:
+        kv = x[s + 1:s + r.L - 1].reshape(-1, 2)
+        if {int(k): int(v) for k, v in kv} == asked:
+            facts = s
+    assert facts is not None
+    return q - (facts + r.L)
+
+
+def test_needles_are_well_formed_deterministic_and_scheduled():
+    r = Reminders(0.5, T=512, n=4, dist=64, seed=1, V=30000, p0=1.0, warm=3, decay=4)
+    assert [r.p_at(i) for i in (0, 2, 3, 5, 7, 100)] == [1.0, 1.0, 1.0, 0.75, 0.5, 0.5]
+    xy = rows(16, 513)
+    out, ex = r(xy, n=0)                                    # p = 1: every row gets a needle
+    assert out.shape == xy.shape and ex["rem"].shape == (16, 512) and ex["rem"].sum() == 16 * 4
+    for b in range(16):
+        assert check_needle(r, out[b], ex["rem"][b]) >= 64
+    out2, ex2 = r(xy, n=0)                                  # same content, same needles
+    assert np.array_equal(out, out2) and np.array_equal(ex["rem"], ex2["rem"])
+    assert not np.array_equal(xy, out) and np.array_equal(xy, rows(16, 513))       # the input is not modified
+    big = rows(400, 513, seed=5)
+    _, e = r(big, n=100)                                    # p = 0.5
+    share = (e["rem"].sum(1) > 0).mean()
+    assert 0.4 < share < 0.6
+    _, e = r(big, p=0.0)
+    assert e["rem"].sum() == 0
+
+
+def test_exact_distance_synthetic_rows_and_document_boundaries():
+    r = Reminders(1.0, T=256, n=3, dist=16, seed=2, V=5000, tok0=1000, synth=2, doc_eos=7)
+    xy = rows(8, 257, V=5000)
+    xy[:, ::5] = 7                                          # many document boundaries
+    for d in (0, 10, 200):
+        out, e = r(xy, p=1.0, exact=d)
+        for b in range(8):
+            assert check_needle(r, out[b], e["rem"][b]) == d
+            pos = np.flatnonzero(e["rem"][b])
+            s = pos[0] - 1 - d - r.L
+            assert not (out[b, s:pos[0] - 1 + r.L] == 7).any()          # none between the facts and the questions
+    out, e = r(xy, n=0)                                     # a synthetic batch: filler + needle
+    assert e["rem"].sum() == 8 * 3
+    body = out[e["rem"].sum(1) > 0]
+    inside = (body >= r.k0) & (body <= r.mark)
+    assert inside.sum() == 8 * 2 * r.L                      # needle tokens appear in the two blocks only
+    out3, _ = r(xy, n=2)                                    # past the synthetic phase: text is kept
+    assert (out3 == xy).mean() > 0.8
+    with pytest.raises(ValueError):
+        Reminders(1.0, T=32, n=8, dist=64)
+    with pytest.raises(ValueError):
+        Reminders(1.0, T=256, n=3, dist=16, V=1200)
+
+
+def test_ladder_levels_follow_success_with_a_lag_and_survive_resume():
+    r = Reminders(1.0, T=1024, n=4, dist=16, ladder=[32, 128, 512], thr=0.9, win=100, lag=5, dmin=4, seed=0)
+    assert r.range_at(0) == (4, 32)
+    xy = rows(6, 1025)
+    out, e = r(xy, n=0)
+    assert all(4 <= check_needle(r, out[b], e["rem"][b]) <= 32 for b in range(6))
+    assert r.observe(0, 50, 60) is None                     # not enough answers yet
+    assert r.observe(1, 30, 60) is None                     # 80/120 < 0.9: window restarts
+    assert r.observe(2, 60, 60) is None
+    msg = r.observe(3, 58, 60)                              # 118/120
+    assert msg and "level 0 -> 1" in msg
+    assert r.level_at(7) == 0 and r.level_at(8) == 1 and r.range_at(8) == (32, 128)
+    out, e = r(xy, n=8)
+    assert all(32 <= check_needle(r, out[b], e["rem"][b]) <= 128 for b in range(6))
+    st = json.loads(json.dumps(r.state()))
+    r2 = Reminders(1.0, T=1024, n=4, dist=16, ladder=[32, 128, 512], thr=0.9, win=100, lag=5, dmin=4, seed=0)
+    r2.load(st)
+    assert r2.level_at(8) == 1
+    assert r2.observe(9, 100, 100) and r2.range_at(14) == (4, 512)        # last level: all distances
+    assert r2.observe(20, 100, 100) is None                               # nothing above the last level
+    near = Reminders(1.0, T=1024, n=4, dist=256, near=1.0, near_max=8)
+    out, e = near(xy)
+    assert all(check_needle(near, out[b], e["rem"][b]) <= 8 for b in range(6))
+    hits, n_ans = Reminders.score(out[:, 1:], out, e["rem"])              # a perfect predictor
+    assert hits == n_ans == 24
+
+
+def test_kind_corpus_schedule_pools_and_resume(tmp_path):
+    from memarch_b200.data.loader import write_shard
+    from memarch_b200.models.fishki import pools
+    rng = np.random.default_rng(0)
+    for src, lo in (("web", 0), ("code", 400), ("math", 800)):
+        for s in range(2):
+            write_shard(str(tmp_path), src, f"s{s}", [rng.integers(lo, lo + 300, size=rng.integers(20, 120))
+                                                      for _ in range(30)], 999)
+    kinds = {"prose": {"web": 3.0}, "formal": {"code": 1.0, "math": 1.0}}
+    sets = pools(2, 8, 5)
+    kc = KindCorpus(kinds, sets, c=3, root=str(tmp_path), seq=48, seed=4)
+    seen = []
+    for _ in range(20):
+        xy = kc.batch(4)
+        ex = kc.extra()
+        k = int(ex["kind"][0, 0])
+        seen.append(k)
+        assert xy.shape == (4, 49) and ex["kind"].shape == (4, 1) and ex["fish"].shape == (4, 3)
+        assert (ex["kind"] == k).all() and (ex["fish"] == ex["fish"][0]).all()
+        assert set(ex["fish"][0].tolist()) <= set(sets[k]) and len(set(ex["fish"][0].tolist())) == 3
+        lo_tok = xy[xy != 999]
+        assert (lo_tok < 300).all() if k == 0 else (lo_tok >= 400).all()       # the whole batch is of one kind
+    assert kc.mix() == {"prose": 0.6, "formal": 0.4}
+    st = json.loads(json.dumps(kc.state_dict()))
+    want = [(kc.batch(4), kc.extra()["fish"].copy()) for _ in range(6)]
+    kc2 = KindCorpus(kinds, sets, c=3, root=str(tmp_path), seq=48, seed=4)
+    kc2.load_state_dict(st)
+    for xy, fish in want:
+        assert np.array_equal(kc2.batch(4), xy) and np.array_equal(kc2.extra()["fish"], fish)
+    kc2.full = True
+    kc2.batch(2)
+    assert kc2.extra()["fish"][0].tolist() == list(sets[int(kc2.extra()["kind"][0, 0])])
+
+
+def test_fake_world_runs_the_multi_rank_paths_in_one_process():
+    import torch.distributed as dist
+    from memarch_b200.parallel.fake import fake_world
+    before = dist.all_reduce
+    assert not dist.is_initialized()
+    with fake_world() as g:
+        assert dist.is_initialized() and dist.get_world_size() == 1 and dist.get_rank() == 0 and g.size() == 1
+        t = torch.arange(6.0)
+        assert dist.all_reduce(t) is None and dist.all_reduce(t, async_op=True).wait()
+        assert torch.equal(t, torch.arange(6.0))
+        out = [torch.zeros(6)]
+        dist.all_gather(out, t)
+        assert torch.equal(out[0], t)
+        big = torch.zeros(6)
+        dist.all_gather_into_tensor(big, t)
+        dist.broadcast(big, 0)
+        assert torch.equal(big, t)
+        rs = torch.zeros(6)
+        dist.reduce_scatter_tensor(rs, t)
+        a2a = torch.zeros(6)
+        dist.all_to_all_single(a2a, t)
+        assert torch.equal(rs, t) and torch.equal(a2a, t)
+        dist.barrier()
+        dist.all_reduce(t, async_op=True).get_future().wait()
+        # the engine's NCCL-mode gradient path, world of one
+        from memarch_b200.parallel import ParallelEngine
+        eng = ParallelEngine(0, 1, fused=False)
+        assert eng.W == 1
+    assert dist.all_reduce is before and not dist.is_initialized()

@@ -50,18 +50,36 @@ def _read_tokens(base):
     return np.fromfile(base + ".u32", dtype=np.uint32)
 
 
-def shard_documents(base, eos, rng):
-    """Documents of one shard after masks and quality repeats, shuffled so that repeats do not sit together."""
+def heldout_tail(lens, tok):
+    """How many trailing documents of a shard are held out: enough for `tok` tokens, at most a tenth of the shard,
+    at least one (memarch_jax/memarch_jax/train_tpu.py:316-330)."""
+    n, k, acc = len(lens), 0, 0
+    while k < max(1, n // 10) and acc < tok:
+        acc += int(lens[n - 1 - k])
+        k += 1
+    return k
+
+
+def shard_documents(base, eos, rng, held=None):
+    """Documents of one shard after masks and quality repeats, shuffled so that repeats do not sit together.
+    `held` = ("train" | "eval", tokens): the held-out tail of the shard is removed (train) or is all that is left,
+    every document once (eval)."""
     arr = _read_tokens(base)
     ends = np.flatnonzero(arr == eos) + 1
     starts = np.concatenate([[0], ends[:-1]])
     keep = np.ones(len(ends), dtype=bool)
+    if held is not None and len(ends):
+        k = heldout_tail(ends - starts, held[1])
+        if held[0] == "eval":
+            keep[:len(ends) - k] = False
+        else:
+            keep[len(ends) - k:] = False
     for ext in MASK_EXTS[:2]:
         if os.path.exists(base + ext):
             idx = np.load(base + ext).astype(np.int64)
             keep[idx[idx < len(keep)]] = False
     reps = np.ones(len(ends), dtype=np.int64)
-    if os.path.exists(base + ".score.npy"):
+    if os.path.exists(base + ".score.npy") and not (held is not None and held[0] == "eval"):
         s = np.load(base + ".score.npy").astype(np.float32)[:len(ends)]
         reps[:len(s)] = np.where(s >= 3.0, 3, np.where(s >= 2.5, 1, (rng.random(len(s)) < 0.25).astype(np.int64)))
     out = []
@@ -74,9 +92,14 @@ def shard_documents(base, eos, rng):
 class _Source:
     """One named source: shard order per epoch from (seed, epoch), documents per shard from (seed, epoch, shard)."""
 
-    def __init__(self, root, src, seed, rank, world, eos):
+    def __init__(self, root, src, seed, rank, world, eos, heldout_tok=0, split="train"):
         self.dir, self.eos, self.seed = os.path.join(root, src), eos, seed
         names = _shard_names(root, src)
+        # held-out text = the tail of the source's last shard (by name, before the split over ranks): training never
+        # sees it, the "eval" split reads nothing else (every rank the same documents: evaluation is replicated)
+        self.held = (names[-1], split, int(heldout_tok)) if heldout_tok and names else None
+        if self.held and split == "eval":
+            names, rank, world = names[-1:], 0, 1
         self.names = [n for i, n in enumerate(names) if i % world == rank]
         if not self.names:
             raise ValueError(f"{src}: no shards for rank {rank} of {world}")
@@ -89,7 +112,8 @@ class _Source:
 
     def _load(self, epoch, si):
         name = self.names[np.random.default_rng((self.seed, epoch)).permutation(len(self.names))[si % len(self.names)]]
-        return shard_documents(os.path.join(self.dir, name), self.eos, np.random.default_rng((self.seed, epoch, si)))
+        held = (self.held[1], self.held[2]) if self.held and name == self.held[0] else None
+        return shard_documents(os.path.join(self.dir, name), self.eos, np.random.default_rng((self.seed, epoch, si)), held)
 
     def _prefetch(self):
         nxt = self.si + 1
@@ -146,7 +170,7 @@ class _Source:
 
 
 class ShardCorpus:
-    def __init__(self, weights, root, seq=8192, seed=0, rank=0, world=1, eos=None):
+    def __init__(self, weights, root, seq=8192, seed=0, rank=0, world=1, eos=None, heldout_tok=0, split="train"):
         self.srcs = list(weights)
         if eos is None:
             first = _shard_names(root, self.srcs[0])[0]
@@ -154,7 +178,8 @@ class ShardCorpus:
         self.eos = int(eos)
         tot = float(sum(weights.values()))
         self.p = np.array([weights[s] / tot for s in self.srcs])
-        self.sources = [_Source(root, s, seed + 1000 * k, rank, world, self.eos) for k, s in enumerate(self.srcs)]
+        self.sources = [_Source(root, s, seed + 1000 * k, rank, world, self.eos, heldout_tok, split)
+                        for k, s in enumerate(self.srcs)]
         self.seq, self.n_docs = seq, 0
         self.buf = np.zeros(0, dtype=np.uint32)
         self.taken = np.zeros(len(self.srcs))

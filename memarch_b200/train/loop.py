@@ -187,17 +187,23 @@ class _NpyData:
 
 
 class _CorpusData:
-    """Shard corpus through the pinned host loader; validation windows come from VAL_NPY or from another seed of the
-    same corpus (small overlap: a monitoring number, fastloop.py:774-778)."""
+    """Shard corpus through the pinned host loader; validation windows come from VAL_NPY, from the held-out tail of
+    each source's last shard (HELDOUT_TOK > 0: training never sees it) or from another seed of the same corpus
+    (small overlap: a monitoring number, fastloop.py:774-778)."""
 
     def __init__(self, seq, device, env, rank, world):
         from ..data.loader import HostLoader, ShardCorpus
         from ..data.synth import TokenStore
         w, root = json.loads(env["CORPUS"]), env["CORPUS_ROOT"]
-        self.corpus = ShardCorpus(w, root, seq=seq, seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world)
+        held = int(env.get("HELDOUT_TOK", 0))           # tail of every source's last shard kept out of training
+        self.corpus = ShardCorpus(w, root, seq=seq, seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world,
+                                  heldout_tok=held)
         self.loader, self.device, self.seq = None, device, seq
         if env.get("VAL_NPY"):
             self.val = TokenStore(np.load(env["VAL_NPY"]), 0, device)
+        elif held:                                      # validation = exactly the held-out text, every document once
+            vc = ShardCorpus(w, root, seq=seq, seed=10 ** 6, heldout_tok=held, split="eval")
+            self.val = TokenStore(vc.batch(max(2, min(held, 160 * 1024) // seq)).reshape(-1), 0, device)
         else:
             vc = ShardCorpus(w, root, seq=seq, seed=10 ** 6)
             self.val = TokenStore(vc.batch(max(2, 160 * 1024 // seq)).reshape(-1), 0, device)

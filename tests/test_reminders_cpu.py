@@ -165,3 +165,36 @@ def test_fake_world_runs_the_multi_rank_paths_in_one_process():
         eng = ParallelEngine(0, 1, fused=False)
         assert eng.W == 1
     assert dist.all_reduce is before and not dist.is_initialized()
+
+
+def test_heldout_tail_is_disjoint_from_training_and_is_the_eval_split(tmp_path):
+    from memarch_b200.data.loader import ShardCorpus, heldout_tail, write_shard
+    assert heldout_tail(np.array([10] * 50), 25) == 3 and heldout_tail(np.array([10] * 50), 10 ** 9) == 5
+    assert heldout_tail(np.array([10] * 4), 0) == 0 and heldout_tail(np.array([7, 7, 7]), 5) == 1
+    rng = np.random.default_rng(0)
+    uid = 1000                                               # every document starts with its own id
+    docs_of = {}
+    for s in range(3):
+        dd = []
+        for _ in range(40):
+            dd.append(np.concatenate([[uid], rng.integers(0, 900, size=rng.integers(5, 30))]))
+            uid += 1
+        docs_of[s] = dd
+        write_shard(str(tmp_path), "web", f"s{s}", dd, 999, score=rng.uniform(2.6, 4.0, size=40) if s == 2 else None)
+    tail_ids = {int(d[0]) for d in docs_of[2][-4:]}          # a tenth of the last shard
+    ev = ShardCorpus({"web": 1.0}, str(tmp_path), seq=31, heldout_tok=10 ** 9, split="eval")
+    flat = ev.batch(2).reshape(-1)
+    ids = [int(t) for t in flat if t >= 1000]
+    assert set(ids) <= tail_ids and len(set(ids)) >= 2
+    first_epoch = ids[:4]
+    assert len(set(first_epoch)) == len(first_epoch)         # no quality repeats in evaluation
+    tr = ShardCorpus({"web": 1.0}, str(tmp_path), seq=31, heldout_tok=10 ** 9)
+    seen = set()
+    for _ in range(80):
+        seen |= {int(t) for t in tr.batch(4).reshape(-1) if t >= 1000}
+    assert not (seen & tail_ids) and len(seen) == 120 - 4    # everything but the tail is trained on
+    both = ShardCorpus({"web": 1.0}, str(tmp_path), seq=31)
+    seen = set()
+    for _ in range(80):
+        seen |= {int(t) for t in both.batch(4).reshape(-1) if t >= 1000}
+    assert tail_ids <= seen                                  # without the switch nothing is held out

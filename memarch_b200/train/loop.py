@@ -293,6 +293,15 @@ def train(args, device=None, env=None, out=None, parallel=None):
             log += log0
             if start > 1:
                 print(f"resuming at step {start} from {ck.path}", file=out, flush=True)
+        # resume check in two runs (memarch_jax/memarch_jax/train_tpu.py:14-15): A with STOP_AT, CKPT_EVERY, NO_FINAL_CKPT
+        # and LOSS_LOG; B in the same CKPT_DIR with STOP_AT and COMPARE=<A's log> prints RESUME_TEST PASS|FAIL for
+        # the steps it repeated.  The learning-rate schedule always follows --steps, not STOP_AT.
+        last = min(args.steps, int(env.get("STOP_AT", 0)) or args.steps)
+        loss_log = open(env["LOSS_LOG"], "a") if env.get("LOSS_LOG") else None
+        cmp_ref = None
+        if env.get("COMPARE"):
+            cmp_ref = {r["step"]: r["loss"] for r in map(json.loads, open(env["COMPARE"]))}
+        cmp_n, cmp_max, cmp_tol = 0, 0.0, float(env.get("CMP_TOL", 1e-3))
         nan = NanGuard(int(env.get("NAN_EVERY", 10)))
         nan_at = int(env.get("TRAIN_NAN_AT", 0))              # inject a non-finite loss at this step (on the host)
         spikes = SpikeLog(float(env.get("SPIKE", 2.0)))
@@ -324,7 +333,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
         nxt = fetch(start) if prefetch else None
         loss = torch.zeros((), device=tr.device)
         try:
-            for step in range(start, args.steps + 1):
+            for step in range(start, last + 1):
                 seq = apply(cfg(step))
                 pn = env.get("PANIC")
                 if pn:
@@ -337,7 +346,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                         for v in pr_.values():
                             if torch.is_tensor(v):
                                 v.record_stream(torch.cuda.current_stream())
-                    if step < args.steps:
+                    if step < last:
                         nxt = fetch(step + 1)
                     loss = tr.step(xy_b, step - 1, preps)
                 else:
@@ -346,6 +355,13 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 if nan_at and step == nan_at:                       # host-made failure for the guard tests
                     loss = loss * float("nan")
                 nan.check(loss)
+                if loss_log is not None or cmp_ref is not None:     # one host read per step: a test mode, not a run mode
+                    lv = float(loss)
+                    if loss_log is not None:
+                        loss_log.write(json.dumps({"step": step, "loss": lv}) + "\n")
+                        loss_log.flush()
+                    if cmp_ref is not None and step in cmp_ref:
+                        cmp_n, cmp_max = cmp_n + 1, max(cmp_max, abs(lv - cmp_ref[step]))
                 if dog:
                     dog.beat()
                 if ema_start and step >= ema_start * args.steps and step % ema_every == 0:
@@ -355,7 +371,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                             ema = [p.detach().float().clone() for p in ps]
                         else:
                             torch._foreach_lerp_(ema, [p.detach().float() for p in ps], 1 - ema_beta ** ema_every)
-                if step % args.eval_every == 0 or step == args.steps:
+                if step % args.eval_every == 0 or step == last:
                     sync()
                     train_time += time.time() - t0
                     nan.flush()
@@ -379,7 +395,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                           f"train {float(loss):.3f}{extra}  {train_time / 60:.1f} min", file=out, flush=True)
                     sync()
                     t0 = time.time()
-                if ck is not None and ck_every and (step % ck_every == 0 or step == args.steps):
+                if ck is not None and ck_every and (step % ck_every == 0 or (step == last and env.get("NO_FINAL_CKPT") != "1")):
                     nan.flush()                                  # never save a state that already went non-finite
                     ck.save(tr, step, log, data.state_dict())
         finally:
@@ -387,6 +403,12 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 dog.close()
             if ck is not None:
                 ck.wait()
+            if loss_log is not None:
+                loss_log.close()
+        if cmp_ref is not None:
+            ok = cmp_n > 0 and cmp_max <= cmp_tol
+            print(f"[train] RESUME_TEST {'PASS' if ok else 'FAIL'}: steps {start}..{last}, {cmp_n} compared, "
+                  f"max |d loss| {cmp_max:.3e} (tolerance {cmp_tol:g})", file=out, flush=True)
         if env.get("DUMP_TOK"):
             dump_token_losses(tr.model, data.val, args.seq, env["DUMP_TOK"])
         os.makedirs("results", exist_ok=True)

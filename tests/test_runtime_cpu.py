@@ -307,3 +307,28 @@ def test_micro_batches_accumulate_to_the_full_batch_gradient():
     assert deltas[0].abs().sum() > 0 and deltas[1].abs().sum() > 0
     cos = torch.nn.functional.cosine_similarity(deltas[0], deltas[1], dim=0).item()
     assert cos > 0.9, cos
+
+
+def test_two_run_resume_check_prints_pass_and_detects_a_difference(tmp_path, monkeypatch):
+    """Run A stops early and leaves a checkpoint in the middle plus its per-step losses; run B resumes, repeats the
+    steps after the checkpoint and compares them with A's log."""
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    base = {"VOCAB": "256", "NO_MEM": "1", "CKPT_DIR": str(tmp_path / "ck"), "CKPT_EVERY": "4", "WATCHDOG": "0",
+            "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12}), "STOP_AT": "7", "NO_FINAL_CKPT": "1"}
+    a_log = str(tmp_path / "A.jsonl")
+    train(Args(steps=12), "cpu", env=dict(base, LOSS_LOG=a_log), out=io.StringIO())
+    rows = [json.loads(l) for l in open(a_log)]
+    assert [r["step"] for r in rows] == list(range(1, 8))
+    buf = io.StringIO()
+    train(Args(steps=12), "cpu", env=dict(base, COMPARE=a_log, CMP_TOL="1e-5"), out=buf)
+    assert "resuming at step 5" in buf.getvalue()
+    assert "RESUME_TEST PASS: steps 5..7, 3 compared" in buf.getvalue()
+    # a log that does not belong to this run fails the check
+    bad = str(tmp_path / "bad.jsonl")
+    with open(bad, "w") as f:
+        for r in rows:
+            f.write(json.dumps({"step": r["step"], "loss": r["loss"] + 0.5}) + "\n")
+    buf = io.StringIO()
+    train(Args(steps=12), "cpu", env=dict(base, COMPARE=bad, CMP_TOL="1e-5"), out=buf)
+    assert "RESUME_TEST FAIL" in buf.getvalue()

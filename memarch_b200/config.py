@@ -133,6 +133,7 @@ class OptConfig:
     hs_lag: bool = False          # OPT_HS_LAG: one-pass homeostasis with last step's second-axis norm
     sr: bool = False              # stochastic rounding of bf16 stores (BF16_ALL / OPT_SR)
     no_master: bool = False       # BF16_ALL: no fp32 master copies
+    offload_m: bool = False       # OPT_OFFLOAD: momentum lives in pinned host memory, on the device only during its update
     vocab_lr_mul: float = 1.0
     sparse_rows: bool = False
     in_backward: bool = True      # stage B: update each weight from its grad-ready hook
@@ -261,6 +262,7 @@ def opt_from_env(cfg: OptConfig, env=None) -> OptConfig:
     if env.get("OPT_HS_LAG") == "1": kw["hs_lag"] = True
     if (env.get("BF16_ALL") == "1" or env.get("OPT_SR") == "1") and env.get("OPT_SR_OFF") != "1": kw["sr"] = True
     if env.get("BF16_ALL") == "1": kw["no_master"] = True
+    if env.get("OPT_OFFLOAD") == "1": kw["offload_m"] = True
     if env.get("VOCAB_LR_MUL"): kw["vocab_lr_mul"] = float(env["VOCAB_LR_MUL"])
     if env.get("SPARSE_ROWS"): kw["sparse_rows"] = True
     if env.get("OPT_ALL") == "1": kw["in_backward"] = False

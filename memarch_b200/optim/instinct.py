@@ -54,6 +54,11 @@ class Instinct:
         self.seen = torch.zeros(cfg.cards, device=dev)
         self.rel = torch.zeros(P, device=dev)
         self.m = [torch.zeros_like(p, dtype=self.m_dtype) for p in self.plist]
+        # optimizer-state offload (memarch_jax/memarch_jax/dist.py:311-322, step.py:154-155): the momentum of every weight
+        # rests in pinned host memory and visits the device only for its own update, on the stream of that update
+        self.offload = bool(cfg.offload_m)
+        if self.offload:
+            self.m = [self._to_host(t) for t in self.m]
         self.w = [p.detach().float().clone() if (p.dtype == torch.bfloat16 and not cfg.no_master) else None
                   for p in self.plist]
         self.cs = [None] * P
@@ -73,6 +78,12 @@ class Instinct:
         self.rows = {}
         self._scratch = {}
         self.grad_sync = None          # set by the data-parallel engine: called as grad_sync(p, grad) -> grad
+
+    @staticmethod
+    def _to_host(t):
+        h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=torch.cuda.is_available())
+        h.copy_(t)
+        return h
 
     # ------------------------------------------------------------------------------------------ card logic
     @torch.no_grad()
@@ -165,6 +176,17 @@ class Instinct:
             grad = self.grad_sync(p, grad)
             if grad is None:
                 return
+        if not self.offload:
+            return self._step_one(i, p, grad)
+        home = self.m[i]
+        self.m[i] = home.to(p.device, non_blocking=True)
+        try:
+            self._step_one(i, p, grad)
+            home.copy_(self.m[i], non_blocking=True)
+        finally:
+            self.m[i] = home
+
+    def _step_one(self, i, p, grad):
         self._sync_lr()
         kind, wd, vocab = self.spec(p)
         want_rel = self.n_step % self.rel_every == 0
@@ -317,7 +339,7 @@ class Instinct:
                 m[j] = self.m[i][s]
                 if w is not None and self.w[i] is not None:
                     w[j] = self.w[i][s]
-        self.m[i], self.w[i] = m, w
+        self.m[i], self.w[i] = (self._to_host(m) if self.offload else m), w
         self.cs[i] = None
 
     @property
@@ -325,7 +347,7 @@ class Instinct:
         return dict(card=self.k, s=self.s, stake=self.stake)
 
     # ------------------------------------------------------------------------------------------ checkpoint blob
-    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch", "lr_mul_dev"}
+    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch", "lr_mul_dev", "offload"}
 
     def state_dict(self):
         out = {}
@@ -335,7 +357,8 @@ class Instinct:
             if torch.is_tensor(v):
                 out[k] = v.detach().cpu()
             elif isinstance(v, list) and all(torch.is_tensor(t) or t is None for t in v):
-                out[k] = [None if t is None else t.detach().cpu() for t in v]
+                own = self.offload and k == "m"             # already on the host: the blob must not alias the live state
+                out[k] = [None if t is None else (t.detach().clone() if own else t.detach().cpu()) for t in v]
             elif isinstance(v, (int, float, bool, str)) or v is None:
                 out[k] = v
         out["_lr"] = self.param_groups[0]["lr"]

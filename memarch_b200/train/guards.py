@@ -81,6 +81,9 @@ def _get(opt, h):
 class RollbackGuard:
     def __init__(self, trainer, ratio=1.5, beta=0.98, lr_mul=0.5, warm=50):
         self.tr, self.ratio, self.beta, self.lr_mul, self.warm = trainer, ratio, beta, lr_mul, warm
+        if getattr(trainer.opt, "offload", False):
+            raise ValueError("the device-side rollback keeps a copy of the optimizer state on the device: "
+                             "it cannot be combined with the host offload of the momentum (offload_m)")
         dev = trainer.device
         self.lema = torch.zeros((), device=dev)            # running mean of the loss (0 = not started)
         self.rep = torch.zeros((), dtype=torch.bool, device=dev)     # next step replays the kept batch

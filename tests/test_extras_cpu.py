@@ -253,3 +253,41 @@ def test_nomem_model_ignores_its_memory():
     assert float(cost) == 0.0
     g = [p.grad for n, p in m.named_parameters() if n.startswith(("memory.", "reread.")) and p.grad is not None]
     assert all(float(t.abs().max()) == 0.0 for t in g)
+
+
+def test_momentum_host_offload_is_bit_identical_and_checkpoints():
+    """The momentum rests in host memory and visits the device of its weight only for the update: same weights as the
+    resident optimizer after every step, state survives a checkpoint blob, bank swaps keep the offload."""
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    torch.manual_seed(0)
+    shapes = [(64, 32), (4, 32, 48), (100, 16), (16,)]
+    w0 = [torch.randn(s) for s in shapes]
+
+    def run(offload, steps, opt=None, ps=None):
+        if opt is None:
+            ps = [torch.nn.Parameter(w.clone()) for w in w0]
+            opt = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, offload_m=offload))
+        g = torch.Generator().manual_seed(5 + opt.n_step)
+        for _ in range(steps):
+            for p in ps:
+                opt.update(p, torch.randn(p.shape, generator=g))
+        return opt, ps
+    a, pa = run(False, 4)
+    b, pb = run(True, 4)
+    assert b.offload and all(t.device.type == "cpu" for t in b.m)
+    assert all(torch.equal(x, y) for x, y in zip(pa, pb)) and all(torch.equal(x, y) for x, y in zip(a.m, b.m))
+    sd = b.state_dict()
+    assert "offload" not in sd and all(s_.data_ptr() != t.data_ptr() for s_, t in zip(sd["m"], b.m))
+    ps2 = [torch.nn.Parameter(p.detach().clone()) for p in pb]
+    c = Instinct(ps2, OptConfig(lr=1e-2, norm="hs", scale=0.12, offload_m=True))
+    c.load_state_dict(sd)
+    assert all(torch.equal(x, y) for x, y in zip(c.m, b.m)) and all(t.device.type == "cpu" for t in c.m)
+    new = torch.nn.Parameter(torch.randn(6, 32, 48))
+    old_m = b.m[1].clone()
+    b.swap(pb[1], new, [0, None, 3, None, 1, None])
+    assert b.m[1].shape == (6, 32, 48) and torch.equal(b.m[1][2], old_m[3]) and float(b.m[1][1].abs().sum()) == 0
+    b.update(new, torch.randn(6, 32, 48))
+    assert float(b.m[1][1].abs().sum()) > 0
+    from memarch_b200.config import opt_from_env
+    assert opt_from_env(OptConfig(), {"OPT_OFFLOAD": "1"}).offload_m

@@ -10,6 +10,10 @@ the 50k recipe.
   (sum exp, correct logit) combine them.  Backward recomputes the chunk's logits and uses the *global* LSE, so the
   forward LSE and the backward probabilities see the same rounding (the consistency the reference's ce.py:23-57
   insists on).
+* `take_dp` / `ce_dp` — the same with rank-local data (data parallel over the same ranks that shard the
+  vocabulary, dist.py:106-151 of the reference): ids, states and targets of all ranks are gathered, every rank serves
+  its rows / its vocabulary slice for all of them, and each rank keeps the rows of its own tokens; the loss returned
+  is the sum over the tokens of all ranks, the same number everywhere.
 Collectives are plain `torch.distributed` calls (NCCL on GPUs, gloo in the CPU tests).
 """
 from __future__ import annotations
@@ -72,7 +76,7 @@ class _ShardCE(torch.autograd.Function):
             dist.all_reduce(acc, group=group)
         lse = m + acc[0].log()
         ctx.save_for_backward(h, w, local, mine, lse)
-        ctx.chunk = chunk
+        ctx.chunk, ctx.group = chunk, group
         return (lse - acc[1]).sum()
 
     @staticmethod
@@ -89,10 +93,68 @@ class _ShardCE(torch.autograd.Function):
             gh[i:i + ctx.chunk] = p @ w.float()
             gw += p.t() @ hc.float()
         if dist.is_initialized():
-            dist.all_reduce(gh)                                               # every slice contributes to dh
+            dist.all_reduce(gh, group=ctx.group)                              # every slice contributes to dh
         return (gh * go).to(h.dtype), (gw * go).to(w.dtype), None, None, None, None
 
 
 def ce(h, head_shard, y, lo, group=None, chunk=4096):
     """Summed token cross-entropy with the head sharded by vocabulary rows."""
     return _ShardCE.apply(h.reshape(-1, h.shape[-1]), head_shard, y.reshape(-1), lo, group, chunk)
+
+
+# ------------------------------------------------------------------------------------------------ rank-local data
+def _world(group):
+    return (dist.get_world_size(group), dist.get_rank(group)) if dist.is_initialized() else (1, 0)
+
+
+def _gather(x, group):
+    W, _ = _world(group)
+    if W == 1:
+        return x
+    parts = [torch.empty_like(x) for _ in range(W)]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, 0)
+
+
+class _AllRows(torch.autograd.Function):
+    """Rows of this rank -> rows of all ranks (rank-major).  What consumes the result is computed identically on every
+    rank and hands back a complete cotangent, so the backward only cuts out this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.n, ctx.rank = x.shape[0], _world(group)[1]
+        return _gather(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g[ctx.rank * ctx.n:(ctx.rank + 1) * ctx.n], None
+
+
+class _OwnRows(torch.autograd.Function):
+    """Rows of all ranks -> rows of this rank; the backward gathers every rank's cotangent rows, because a table shard
+    receives gradient from the tokens of all ranks."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        W, r = _world(group)
+        n = x.shape[0] // W
+        ctx.group = group
+        return x[r * n:(r + 1) * n]
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather(g, ctx.group), None
+
+
+def take_dp(shard, ids, lo, group=None):
+    """Embedding rows for this rank's own ids (any shape) from a row-sharded table."""
+    flat = _gather(ids.reshape(-1), group)
+    rows = _OwnRows.apply(take(shard, flat, lo, group), group)
+    return rows.view(*ids.shape, shard.shape[-1])
+
+
+def ce_dp(h, head_shard, y, lo, group=None, chunk=4096):
+    """Summed cross-entropy over the tokens of all ranks (the same value on every rank) with the head sharded by
+    vocabulary rows; h (N, d) and y (N,) are this rank's own tokens."""
+    hg = _AllRows.apply(h.reshape(-1, h.shape[-1]), group)
+    return ce(hg, head_shard, _gather(y.reshape(-1), group), lo, group, chunk)

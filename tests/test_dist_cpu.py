@@ -144,3 +144,50 @@ def test_vocab_parallel_and_row_sharded_homeostasis_match_single_rank():
     opt.update(p, g.clone())
     got = np.concatenate([res[0][5], res[1][5]])
     assert np.allclose(got, p.detach().numpy(), atol=1e-6)
+
+
+def _w_vocab_dp(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world)})
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.parallel import vocab
+    torch.manual_seed(0)
+    V, d, N = 50, 16, 12
+    table, head = torch.randn(V, d), torch.randn(V, d)
+    ids, h, y = torch.randint(0, V, (world, 3, 4)), torch.randn(world, N, d), torch.randint(0, V, (world, N))
+    ts, lo = vocab.shard_rows(table, rank, world)
+    hs, _ = vocab.shard_rows(head, rank, world)
+    ts.requires_grad_(True); hs.requires_grad_(True)
+    hh = h[rank].clone().requires_grad_(True)                  # this rank's own tokens
+    e = vocab.take_dp(ts, ids[rank], lo)
+    assert e.shape == (3, 4, d)
+    loss = vocab.ce_dp(hh + e.view(N, d) * 0.1, hs, y[rank], lo, chunk=5)
+    loss.backward()
+    q.put((rank, loss.item(), ts.grad.numpy(), hs.grad.numpy(), hh.grad.numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_with_rank_local_data_matches_the_whole_batch():
+    import torch.multiprocessing as mp
+    import torch.nn.functional as F
+    world, port = 2, 29633
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_vocab_dp, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted([q.get(timeout=120) for _ in ps], key=lambda r: r[0])
+    [p.join(30) for p in ps]
+    torch.manual_seed(0)
+    V, d, N = 50, 16, 12
+    table, head = torch.randn(V, d, requires_grad=True), torch.randn(V, d, requires_grad=True)
+    ids, h, y = torch.randint(0, V, (world, 3, 4)), torch.randn(world, N, d, requires_grad=True), torch.randint(0, V, (world, N))
+    x = h + table[ids].view(world, N, d) * 0.1
+    loss = F.cross_entropy(x.view(-1, d) @ head.t(), y.view(-1), reduction="sum")
+    loss.backward()
+    n = V // world
+    for r in range(world):
+        assert abs(res[r][1] - loss.item()) < 1e-3
+        assert np.abs(res[r][2] - table.grad[r * n:(r + 1) * n].numpy()).max() < 1e-4
+        assert np.abs(res[r][3] - head.grad[r * n:(r + 1) * n].numpy()).max() < 1e-4
+        assert np.abs(res[r][4] - h.grad[r].numpy()).max() < 1e-4

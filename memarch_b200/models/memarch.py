@@ -549,6 +549,19 @@ class MemArchLM(nn.Module):
         self.stats["rare_drop"] = (rare.sum() - hit.sum()).float() / N
         return logp
 
+    @torch.no_grad()
+    def short_top(self, h):
+        """Most probable word of the short vocabulary and its probability, without gradient: h (N, d) ->
+        (p_top (N,) fp32, token (N,) in the full vocabulary).  The "rare" bucket counts in the normaliser but cannot
+        lead (memarch_jax/memarch_jax/ce.py:337-363)."""
+        W, K = self.head.weight, self.short_v
+        Ws = torch.cat([W[self.sv_ids], W[self.sv_bucket:self.sv_bucket + 1]])
+        lo = ops.linear(h.detach(), Ws.detach()).float()
+        lo[:, K] += self.sv_prior0
+        lse = lo.logsumexp(-1)
+        best, j = lo[:, :K].max(-1)
+        return (best - lse).exp(), self.sv_ids[j]
+
     def _ce_part(self, hn, y, j):
         c = self.cfg
         mix = self._mix

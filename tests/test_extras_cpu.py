@@ -2,6 +2,7 @@
 uroboros selection, int8 numerics, recall toy task."""
 import math
 
+import numpy as np
 import torch
 
 from memarch_b200.models import fishki
@@ -291,3 +292,64 @@ def test_momentum_host_offload_is_bit_identical_and_checkpoints():
     assert float(b.m[1][1].abs().sum()) > 0
     from memarch_b200.config import opt_from_env
     assert opt_from_env(OptConfig(), {"OPT_OFFLOAD": "1"}).offload_m
+
+
+def test_dump_proof_norm_removes_the_common_direction():
+    from memarch_b200.ops.extras import dump_proof_norm
+    torch.manual_seed(0)
+    x = (torch.randn(2, 40, 32) + 3.0 * torch.randn(32)).requires_grad_(True)    # a strong common vector
+    w = torch.ones(32)
+    u = torch.randn(32, requires_grad=True)
+    y = dump_proof_norm(x, w, u)
+    uh = (u / u.norm()).detach()
+    assert (y @ uh).abs().max() < 1e-5
+    plain = x.detach() * torch.rsqrt(x.detach().pow(2).mean(-1, keepdim=True) + 1e-6)
+    assert torch.allclose(y.detach(), plain - (plain @ uh)[..., None] * uh, atol=1e-6)
+    y.square().sum().backward()
+    assert x.grad.abs().sum() > 0 and u.grad is None                             # the direction carries no gradient
+    mean = x.detach().reshape(-1, 32).mean(0)
+    a, b, c = dump_proof_norm(x, w, None), dump_proof_norm(x, w, torch.zeros(32)), dump_proof_norm(x, w, mean)
+    assert torch.equal(a, b) and torch.allclose(a, c, atol=1e-6)
+    assert dump_proof_norm(x.bfloat16(), w.bfloat16(), u).dtype == torch.bfloat16
+
+
+def test_cap_shared_is_causal_and_leaves_small_common_vectors_alone():
+    from memarch_b200.ops.extras import cap_shared
+    torch.manual_seed(0)
+    free = torch.randn(2, 96, 24)                                # zero-mean rows: nothing to cap
+    assert torch.equal(cap_shared(free, 0.5, t0=8), free)
+    off = free + 4.0 * torch.randn(24)
+    out = cap_shared(off, 0.5, t0=16)
+    assert torch.equal(out[:, :16], off[:, :16]) and not torch.equal(out[:, 16:], off[:, 16:])
+    # a capped position is the input minus a multiple of its running mean
+    n = torch.arange(1, 97.0)[:, None]
+    m = off.cumsum(1) / n
+    t = 50
+    diff, mt = off[:, t] - out[:, t], m[:, t]
+    k = (diff * mt).sum(-1) / (mt * mt).sum(-1)
+    assert torch.allclose(diff, k[:, None] * mt, atol=1e-5) and bool(((k > 0) & (k < 1)).all())
+    # causal: the future does not change the past
+    other = off.clone()
+    other[:, 60:] = torch.randn(2, 36, 24)
+    assert torch.equal(cap_shared(other, 0.5, t0=16)[:, :60], out[:, :60])
+    x = off.clone().requires_grad_(True)
+    cap_shared(x, 0.5, t0=16).square().sum().backward()
+    assert torch.isfinite(x.grad).all()
+
+
+def test_short_top_names_the_leading_short_vocabulary_word(tmp_path):
+    from memarch_b200.build import build
+    cnt = np.zeros(512, np.int64)
+    cnt[:100] = np.arange(100, 0, -1) * 50
+    cnt[100:511] = 1
+    np.save(tmp_path / "cnt.npy", cnt)
+    torch.manual_seed(0)
+    m = build("tiny", 512, env={"SHORT_V": "64", "TOKEN_COUNTS": str(tmp_path / "cnt.npy"), "NO_MEM": "1"})
+    assert m.short_v == 64
+    h = torch.randn(10, m.head.weight.shape[1])
+    p, tok = m.short_top(h)
+    lo = h @ m.head.weight[m.sv_ids].t()
+    full = torch.cat([lo, (h @ m.head.weight[m.sv_bucket]).unsqueeze(1) + m.sv_prior0], 1)
+    assert torch.equal(tok, m.sv_ids[lo.argmax(-1)])
+    assert torch.allclose(p, full.softmax(-1)[:, :64].max(-1).values, atol=1e-5)
+    assert bool((tok < 64).all()) and bool((p > 0).all()) and bool((p < 1).all())

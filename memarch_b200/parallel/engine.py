@@ -38,11 +38,50 @@ class _AllToAll(torch.autograd.Function):
         return torch.ops._c10d_functional.wait_tensor(t), None
 
 
+def ring_exchange(x, group=None):
+    """The same permutation as the equal-split all-to-all over dim 0, as W-1 point-to-point steps: in step s every
+    rank sends its block for rank (r+s) and receives the block of rank (r-s).  The reference's JAX port keeps such a
+    ring beside `all_to_all` (moe.py:119-152) because each step's transfer can overlap the FFN of the blocks that
+    already arrived; here it is the baseline the fused exchange is compared with on meshes where all-to-all is slow."""
+    W, r = dist.get_world_size(group), dist.get_rank(group)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    n = x.shape[0] // W
+    out[r * n:(r + 1) * n] = x[r * n:(r + 1) * n]
+    glob = (lambda k: dist.get_global_rank(group, k)) if group is not None else (lambda k: k)
+    for s_ in range(1, W):
+        to, frm = (r + s_) % W, (r - s_) % W
+        ops_ = [dist.P2POp(dist.isend, x[to * n:(to + 1) * n], glob(to), group),
+                dist.P2POp(dist.irecv, out[frm * n:(frm + 1) * n], glob(frm), group)]
+        for w in dist.batch_isend_irecv(ops_):
+            w.wait()
+    return out
+
+
+class _Ring(torch.autograd.Function):
+    """`ring_exchange` with autograd: the permutation is its own transpose."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return ring_exchange(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ring_exchange(g, ctx.group), None
+
+
 class NcclExpertExchange:
-    """Expert-parallel FFN through two autograd all-to-alls (full2.py:1137-1156), extended to a sharded frozen bank."""
+    """Expert-parallel FFN through two autograd all-to-alls (full2.py:1137-1156), extended to a sharded frozen bank.
+    `MEMARCH_EP_A2A=ring` moves the tokens by the W-1 step ring instead of one all-to-all."""
 
     def __init__(self, rank, world, group=None):
+        import os
         self.rank, self.W, self.group = rank, world, group
+        self.ring = os.environ.get("MEMARCH_EP_A2A", "a2a") == "ring"
+
+    def _move(self, x, gname):
+        return _Ring.apply(x, self.group) if self.ring else _AllToAll.apply(x, gname)
 
     def _perm(self, moe):
         """Order experts so each rank's share is contiguous: rank r gets its learning experts then its frozen ones."""
@@ -64,13 +103,13 @@ class NcclExpertExchange:
         if perm is not None:
             xe = xe[perm]
         n = El + Fl
-        r = _AllToAll.apply(xe, gname)
+        r = self._move(xe, gname)
         r = r.view(W, n, C, d).transpose(0, 1).reshape(n, W * C, d)
         y = moe._ffn(r[:El], moe.up, moe.down)
         if Fl:
             y = torch.cat([y, moe._ffn_frozen(r[El:])])
         y = y.view(n, W, C, d).transpose(0, 1).reshape(E, C, d).contiguous()
-        y = _AllToAll.apply(y, gname)
+        y = self._move(y, gname)
         if perm is not None:
             inv = torch.empty_like(perm)
             inv[perm] = torch.arange(E, device=perm.device)

@@ -191,3 +191,34 @@ def test_vocab_parallel_with_rank_local_data_matches_the_whole_batch():
         assert np.abs(res[r][2] - table.grad[r * n:(r + 1) * n].numpy()).max() < 1e-4
         assert np.abs(res[r][3] - head.grad[r * n:(r + 1) * n].numpy()).max() < 1e-4
         assert np.abs(res[r][4] - h.grad[r].numpy()).max() < 1e-4
+
+
+def _w_ring(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.parallel.engine import _Ring, ring_exchange
+    torch.manual_seed(10 + rank)
+    x = torch.randn(world * 2, 5, 3)
+    want = torch.empty_like(x)
+    dist.all_to_all_single(want, x)
+    got = ring_exchange(x)
+    xg = x.clone().requires_grad_(True)
+    y = _Ring.apply(xg, None)
+    wgt = torch.arange(y.numel(), dtype=torch.float32).view_as(y) * (rank + 1)
+    (y * wgt).sum().backward()
+    gwant = torch.empty_like(x)
+    dist.all_to_all_single(gwant, wgt)                       # the cotangent travels back by the same permutation
+    q.put((rank, bool(torch.equal(got, want)), bool(torch.equal(xg.grad, gwant))))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ring_exchange_equals_all_to_all_on_three_ranks():
+    world, port = 3, 29637
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_ring, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = [q.get(timeout=120) for _ in ps]
+    [p.join(30) for p in ps]
+    assert len(res) == 3 and all(fwd and bwd for _, fwd, bwd in res)

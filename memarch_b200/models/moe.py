@@ -124,6 +124,10 @@ class AnchorMoE(nn.Module):
     def forward(self, x, surprise=None):
         xf, table, wtab, flat_idx, C = self._route(x, surprise)
         N, d = xf.shape
+        eng = self.ep_engine if self.ep_W > 1 else None
+        if eng is not None and getattr(eng, "dedup", False) and not (self.bank and self.has_F) and not self.wave:
+            out = eng.forward_dedup(self, xf, table, wtab, C, eng.dedup_cap)
+            return ops.resid_add(x, out.view_as(x))
         xe = ops.slot_gather(xf, table, flat_idx).view(self.E, C, d)
         ye = self._experts(xe, wtab, C)
         out = ops.combine(ye.reshape(self.E * C, d), wtab.to(ye.dtype), flat_idx, table, N)

@@ -79,6 +79,8 @@ class NcclExpertExchange:
         import os
         self.rank, self.W, self.group = rank, world, group
         self.ring = os.environ.get("MEMARCH_EP_A2A", "a2a") == "ring"
+        self.dedup = os.environ.get("EP_A2A_DEDUP") == "1"
+        self.dedup_cap = float(os.environ.get("EP_DEDUP_CAP", 1.0))
 
     def _move(self, x, gname):
         return _Ring.apply(x, self.group) if self.ring else _AllToAll.apply(x, gname)
@@ -94,6 +96,59 @@ class NcclExpertExchange:
         for r in range(W):
             order += L[r * El:(r + 1) * El] + Fz[r * Fl:(r + 1) * Fl]
         return torch.tensor(order, device=moe.up.device), El, Fl
+
+    def forward_dedup(self, moe, xf, table, wtab, C, cap=1.0):
+        """Expert-parallel layer where a (token, rank) pair crosses the wire once, however many of the rank's experts
+        the token chose (full2.py:967-1046: pays when a rank holds several experts and tokens pick more than one of
+        them).  xf (N, d) normalised tokens, table (E*C,) token of every expert slot (N = empty), wtab (E*C,) routing
+        weights -> (N, d) weighted sum over each token's experts.  Per destination rank the distinct tokens form a
+        parcel of at most Cc = min(El*C, N, cap*El*C) rows; the owner expands a parcel row to the slots of its
+        experts, runs the FFN, adds the weighted outputs per parcel row (fp32) and returns one row per pair.  Expert
+        capacity and drops are those of the ordinary dispatch; with cap < 1 whole pairs beyond Cc are dropped and
+        counted in `moe.dropped`.  Learning experts only (no sharded frozen bank)."""
+        W, E = self.W, moe.E
+        N, d = xf.shape
+        El = E // W
+        S = El * C
+        Cc = max(1, min(S, N, int(-(-cap * S // 1))))
+        gname = (self.group or dist.group.WORLD).group_name
+        dev = xf.device
+        with torch.no_grad():
+            tb = table.view(W, S)
+            hit = torch.zeros(W, N + 1, dtype=torch.bool, device=dev).scatter_(1, tb, True)[:, :N]
+            pos = hit.long().cumsum(1) - 1                                   # row of token n in the parcel to rank s
+            go = hit & (pos < Cc)
+            pos = torch.where(go, pos, Cc)                                   # Cc = does not travel
+            ctok = torch.full((W, Cc + 1), N, dtype=torch.long, device=dev)
+            ctok.scatter_(1, pos, torch.arange(N, device=dev).expand(W, N))  # distinct targets except the spill column
+            ctok = ctok[:, :Cc]
+            row = torch.cat([pos, pos.new_full((W, 1), Cc)], 1).gather(1, tb)   # parcel row of every expert slot
+            lost = ((row == Cc) & (tb < N)).sum()
+            placed = (tb < N).sum().clamp(min=1)
+        moe.dropped = 1 - (1 - moe.dropped) * (placed - lost) / placed
+        xpad = torch.cat([xf, xf.new_zeros(1, d)])
+        xr = self._move(xpad[ctok.reshape(-1)], gname).view(W, Cc, d)       # parcels from every source rank
+        rr = self._move_plain(row.reshape(-1)).view(W, S)
+        wr = self._move(wtab.reshape(-1).float(), gname).view(W, S)
+        xrp = torch.cat([xr, xr.new_zeros(W, 1, d)], 1)
+        xe = xrp.gather(1, rr[..., None].expand(-1, -1, d))                 # (W, S, d): rows expanded to the slots
+        xe = xe.view(W, El, C, d).transpose(0, 1).reshape(El, W * C, d)
+        y = moe._ffn(xe, moe.up, moe.down)
+        y = y.view(El, W, C, d).transpose(0, 1).reshape(W, S, d)
+        yw = y.float() * wr[..., None]
+        yc = yw.new_zeros(W, Cc + 1, d).scatter_add(1, rr[..., None].expand(-1, -1, d), yw)[:, :Cc]
+        yb = self._move(yc.to(xf.dtype).reshape(W * Cc, d), gname).view(W, Cc, d)
+        ybp = torch.cat([yb, yb.new_zeros(W, 1, d)], 1)
+        return ybp.gather(1, pos[..., None].expand(-1, -1, d)).float().sum(0).to(xf.dtype)
+
+    def _move_plain(self, t):
+        """Integer metadata through the same exchange, outside autograd."""
+        with torch.no_grad():
+            if self.ring:
+                return ring_exchange(t, self.group)
+            out = torch.empty_like(t)
+            dist.all_to_all_single(out, t.contiguous(), group=self.group)
+            return out
 
     def ffn(self, moe, xe):
         W = self.W

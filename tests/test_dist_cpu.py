@@ -222,3 +222,49 @@ def test_ring_exchange_equals_all_to_all_on_three_ranks():
     res = [q.get(timeout=120) for _ in ps]
     [p.join(30) for p in ps]
     assert len(res) == 3 and all(fwd and bwd for _, fwd, bwd in res)
+
+
+def _w_dedup(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.models.moe import AnchorMoE
+    from memarch_b200.parallel.engine import NcclExpertExchange
+    torch.manual_seed(0)
+    moe = AnchorMoE(32, E=4, k_avg=2, k_max=4, budget=True, act="relu2")       # two experts per rank
+    eng = NcclExpertExchange(rank, world)
+    moe.ep_shard(rank, world, eng)
+    moe.train()
+    g = torch.Generator().manual_seed(3 + rank)                                  # every rank its own tokens
+    x0 = torch.randn(2, 24, 32, generator=g)
+    sur = torch.rand(2, 24, generator=g) * 4
+    go = torch.randn(2, 24, 32, generator=g)
+    res = {}
+    s_mean = moe.s_mean.clone()
+    for mode in ("plain", "dedup", "capped"):
+        eng.dedup, eng.dedup_cap = mode != "plain", 0.25 if mode == "capped" else 1.0
+        moe.s_mean.copy_(s_mean)
+        x = x0.clone().requires_grad_(True)
+        moe.up.grad = moe.down.grad = moe.router.weight.grad = None
+        y = moe(x, sur)
+        y.backward(go)
+        res[mode] = (y.detach().clone(), x.grad.clone(), moe.up.grad.clone(), moe.router.weight.grad.clone(),
+                     float(moe.dropped))
+    q.put((rank, {k: [t.numpy() if torch.is_tensor(t) else t for t in v] for k, v in res.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_deduplicated_expert_exchange_matches_the_plain_one():
+    world, port = 2, 29641
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_dedup, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = [q.get(timeout=180) for _ in ps]
+    [p.join(30) for p in ps]
+    for _, r in res:
+        for a, b in zip(r["plain"][:4], r["dedup"][:4]):
+            assert np.abs(a - b).max() < 2e-5 * max(1.0, np.abs(a).max())
+        assert abs(r["plain"][4] - r["dedup"][4]) < 1e-6                          # same drops
+        assert r["capped"][4] > r["plain"][4] + 0.05                              # pairs beyond the parcel are dropped
+        assert np.isfinite(r["capped"][0]).all() and np.abs(r["capped"][0] - r["plain"][0]).max() > 1e-3

@@ -142,6 +142,12 @@ class OptConfig:
     damp_p: float = 1.0           #     into the momentum and the tensor's step shrinks by (damp x usual / |g|)^damp_p
     damp_beta: float = 0.99       #     EMA of the usual squared norm (per situation card)
     damp_cap: float = 2.0         #     a surge enters that EMA as at most (cap x usual)^2: the brake does not get used to it
+    snr: bool = False             # confidence brake: step x clip(|m_new| / sqrt(EMA |g|^2) / snr_ref, snr_floor, 1) per tensor
+    snr_beta: float = 0.95
+    snr_ref: float = 1.0
+    snr_floor: float = 0.1
+    snr_dz: bool = False          #     dead-zone form: brakes only a random walk (see Instinct._snr)
+    snr_horizon: float = 250.0
     surge_thr: float = 0.0        # >0: surprise brake: a step much worse than expected (-s > thr) scales lr by (thr/-s)^2
 
 

@@ -75,6 +75,8 @@ class Instinct:
         self.lr_mul_dev = None         # optional 0-dim device tensor multiplying the step (set by the rollback guard)
         self.dv = torch.zeros(cfg.cards, P, device=dev) if cfg.damp > 0 else None   # usual |g|^2 per (card, weight)
         self.df = torch.ones(P, device=dev) if cfg.damp > 0 else None               # last damping factor (for the log)
+        self.snr_v = torch.zeros(P, device=dev) if cfg.snr else None                # EMA of |g|^2 (or of c^2, dead-zone form)
+        self.snr_f = torch.ones(P, device=dev) if cfg.snr else None                 # last factor (for the log)
         self.rows = {}
         self._scratch = {}
         self.grad_sync = None          # set by the data-parallel engine: called as grad_sync(p, grad) -> grad
@@ -196,6 +198,8 @@ class Instinct:
             lr_t = lr_t * (self.cfg.surge_thr / bad) ** 2
         if self.dv is not None and not vocab:
             grad, lr_t = self._damp(i, grad, lr_t)
+        if self.snr_v is not None and not vocab and self.m[i].shape == grad.shape:
+            lr_t = self._snr(i, grad, lr_t)
         wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
         rows = self.rows.get(id(p)) if vocab else None
         if rows is not None:
@@ -225,6 +229,35 @@ class Instinct:
         self.dv[:, i] += self.oh * (torch.where(gg > 0, new, dv) - dv)
         self.df[i] = f
         return (grad * f.to(grad.dtype), lr_t * f ** c.damp_p)
+
+    def _snr(self, i, grad, lr_t):
+        """Confidence of a tensor's direction (the reference's JAX Instinct, instinct.py:76-84, 100-104, 953-975):
+        c = |beta m + (1-beta) g| / sqrt(EMA |g|^2).  Gradients that agree from step to step give c near 1, noise
+        gives c near sqrt((1-beta)/(1+beta)); the step is scaled by clip(c / snr_ref, snr_floor, 1).  The dead-zone
+        form keeps an EMA of c^2 instead and brakes only what is indistinguishable from a random walk:
+        k = (1-beta)/(1+beta), r = max(c2 - k, 0) / (1 - c2), factor = clip(sqrt(r horizon / k), floor, 1).
+        A tensor without gradient keeps its state.  Three scalar reductions, device-side, no host sync."""
+        c = self.cfg
+        g32, m32 = grad.float(), self.m[i].float()
+        gg, mg, m2 = (g32 * g32).sum(), (m32 * g32).sum(), (m32 * m32).sum()
+        b = self.beta
+        mn2 = (b * b * m2 + 2 * b * (1 - b) * mg + (1 - b) * (1 - b) * gg).clamp(min=0.0)
+        v_old = self.snr_v[i]
+        if c.snr_dz:
+            c2 = mn2 / (gg + 1e-30)
+            ok = (v_old > 0) & (v_old <= 1.0)
+            v_new = torch.where(ok, c.snr_beta * v_old + (1 - c.snr_beta) * c2, c2)
+            k = (1 - b) / (1 + b)
+            r = (v_new - k).clamp(min=0.0) / (1 - v_new).clamp(min=1e-6)
+            f = (r * c.snr_horizon / k).sqrt().clamp(c.snr_floor, 1.0)
+        else:
+            v_new = torch.where(v_old > 0, c.snr_beta * v_old + (1 - c.snr_beta) * gg, gg)
+            f = (mn2.sqrt() / (v_new.sqrt() + 1e-30) / c.snr_ref).clamp(c.snr_floor, 1.0)
+        live = gg > 0
+        self.snr_v[i] = torch.where(live, v_new, v_old)
+        f = torch.where(live, f, torch.ones_like(f))
+        self.snr_f[i] = f
+        return lr_t * f
 
     def _frozen_mask(self, p):
         fr = getattr(p, "_frozen_rows", None)

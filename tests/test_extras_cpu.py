@@ -353,3 +353,43 @@ def test_short_top_names_the_leading_short_vocabulary_word(tmp_path):
     assert torch.equal(tok, m.sv_ids[lo.argmax(-1)])
     assert torch.allclose(p, full.softmax(-1)[:, :64].max(-1).values, atol=1e-5)
     assert bool((tok < 64).all()) and bool((p > 0).all()) and bool((p < 1).all())
+
+
+def test_confidence_brake_slows_noise_and_spares_a_steady_direction():
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    torch.manual_seed(0)
+
+    def run(kind, **kw):
+        p = torch.nn.Parameter(torch.randn(32, 16))
+        q = torch.nn.Parameter(torch.randn(32, 16))
+        opt = Instinct([p, q], OptConfig(lr=1e-2, norm="hs", scale=0.12, snr=True, **kw))
+        steady = torch.randn(32, 16)
+        g = torch.Generator().manual_seed(1)
+        fs = []
+        for _ in range(60):
+            opt.update(p, steady + 0.05 * torch.randn(32, 16, generator=g))        # the same direction every step
+            opt.update(q, torch.randn(32, 16, generator=g))                        # pure noise
+            fs.append(opt.snr_f.clone())
+        return opt, torch.stack(fs)
+    opt, f = run("plain")
+    assert f[-10:, 0].min() > 0.9 and f[-10:, 1].max() < 0.4
+    b = opt.beta
+    assert abs(float(f[-20:, 1].mean()) - ((1 - b) / (1 + b)) ** 0.5) < 0.1           # noise level of the ratio
+    opt.update(opt.plist[0], torch.zeros(32, 16))                                     # idle tensor: state untouched
+    assert float(opt.snr_f[0]) == 1.0
+    _, f = run("dz", snr_dz=True, snr_horizon=50.0)
+    assert f[-10:, 0].min() == 1.0 and f[-10:, 1].max() < 0.9
+    # the brake scales the step, not its direction
+    torch.manual_seed(0)
+    w0, g0 = torch.randn(8, 8), torch.randn(8, 8)
+    outs = []
+    for snr in (False, True):
+        p = torch.nn.Parameter(w0.clone())
+        o = Instinct([p], OptConfig(lr=1e-2, norm="hs", scale=0.12, snr=snr, snr_ref=4.0))
+        o.update(p, g0.clone())
+        outs.append(p.detach() - w0)
+    cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0)
+    assert cos > 0.9999 and outs[1].norm() < 0.5 * outs[0].norm()
+    sd = o.state_dict()
+    assert "snr_v" in sd and "snr_f" in sd

@@ -75,10 +75,66 @@ class _PinnedSnapshot:
         return tree
 
 
+class FileStore:
+    """Second home of the checkpoints (another disk or a mounted bucket): `step_XXXXXXXX.pt` plus a small
+    `step_XXXXXXXX.json` tag with the run id, both written as `.tmp` and renamed, the tag last, so that a copy is
+    either complete and tagged or ignored.  Copies of another run are never taken and never deleted
+    (memarch_jax/memarch_jax/train_tpu.py:464-673, 686)."""
+
+    def __init__(self, root, rid=None, keep=2):
+        self.root, self.rid, self.keep = root, rid, keep
+        os.makedirs(root, exist_ok=True)
+
+    def _tag(self, step):
+        return os.path.join(self.root, f"step_{int(step):08d}.json")
+
+    def _blob(self, step):
+        return os.path.join(self.root, f"step_{int(step):08d}.pt")
+
+    def steps(self, mine=True):
+        """Steps with a complete copy, oldest first; `mine` keeps the copies of this run only."""
+        out = []
+        for f in sorted(os.listdir(self.root)):
+            if f.startswith("step_") and f.endswith(".json"):
+                try:
+                    tag = json.load(open(os.path.join(self.root, f)))
+                except (OSError, ValueError):
+                    continue
+                if os.path.exists(self._blob(tag["step"])) and (not mine or self.rid is None or tag.get("run_id") == self.rid):
+                    out.append(int(tag["step"]))
+        return out
+
+    def put(self, path, step):
+        import shutil
+        tmp = self._blob(step) + ".tmp"
+        shutil.copyfile(path, tmp)
+        with open(tmp, "rb") as f:
+            os.fsync(f.fileno())
+        os.replace(tmp, self._blob(step))
+        with open(self._tag(step) + ".tmp", "w") as f:
+            json.dump({"step": int(step), "run_id": self.rid, "bytes": os.path.getsize(self._blob(step))}, f)
+        os.replace(self._tag(step) + ".tmp", self._tag(step))
+        if self.keep > 0:
+            for old in self.steps()[:-self.keep]:
+                os.remove(self._tag(old))                       # tag first: a half-deleted copy is not a copy
+                os.remove(self._blob(old))
+
+    def fetch_latest(self, path):
+        """Copy this run's newest complete checkpoint to `path`; returns its step or None."""
+        import shutil
+        have = self.steps()
+        if not have:
+            return None
+        shutil.copyfile(self._blob(have[-1]), path + ".tmp")
+        os.replace(path + ".tmp", path)
+        return have[-1]
+
+
 class Checkpointer:
-    def __init__(self, directory, rid=None, keep=0, background=True):
+    def __init__(self, directory, rid=None, keep=0, background=True, mirror=None, mirror_keep=2):
         self.dir, self.rid, self.keep, self.background = directory, rid, keep, background
         os.makedirs(directory, exist_ok=True)
+        self.store = FileStore(mirror, rid, mirror_keep) if mirror else None
         self.snap = _PinnedSnapshot()
         self.thread = None
         self.error = None
@@ -138,6 +194,8 @@ class Checkpointer:
                     old = sorted(f for f in os.listdir(self.dir) if f.startswith("step_") and f.endswith(".pt"))
                     for f in old[:-self.keep]:
                         os.remove(os.path.join(self.dir, f))
+                if self.store is not None:
+                    self.store.put(self.path, step)
             except BaseException as e:   # noqa: BLE001 - re-raised on the training thread by wait()
                 self.error = e
 
@@ -159,6 +217,8 @@ class Checkpointer:
     # ---------------------------------------------------------------------------------------------- load
     def load(self, trainer, corpus=None, strict_run=True):
         """Resume from `latest.pt` if present.  Returns (next step, log); (first step, []) when there is nothing."""
+        if not os.path.exists(self.path) and self.store is not None:
+            self.store.fetch_latest(self.path)                   # local disk lost: take this run's newest mirrored copy
         if not os.path.exists(self.path):
             return 1, []
         st = torch.load(self.path, map_location="cpu", weights_only=False)

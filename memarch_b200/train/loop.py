@@ -285,7 +285,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
         log, train_time = [], 0.0
         ck = None
         if env.get("CKPT_DIR"):
-            ck = Checkpointer(env["CKPT_DIR"], rid=run_id(name, getattr(tr.model, "cfg", None)), keep=int(env.get("CKPT_KEEP", 0)))
+            ck = Checkpointer(env["CKPT_DIR"], rid=run_id(name, getattr(tr.model, "cfg", None)), keep=int(env.get("CKPT_KEEP", 0)),
+                              mirror=env.get("CKPT_MIRROR") or None)
         ck_every = int(env.get("CKPT_EVERY", 0))
         start = 1
         if ck is not None:

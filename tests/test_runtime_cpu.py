@@ -332,3 +332,30 @@ def test_two_run_resume_check_prints_pass_and_detects_a_difference(tmp_path, mon
     buf = io.StringIO()
     train(Args(steps=12), "cpu", env=dict(base, COMPARE=bad, CMP_TOL="1e-5"), out=buf)
     assert "RESUME_TEST FAIL" in buf.getvalue()
+
+
+def test_mirrored_checkpoints_survive_the_loss_of_the_local_directory(tmp_path, monkeypatch):
+    import shutil
+    from memarch_b200.train.ckpt import FileStore
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    env = {"VOCAB": "256", "NO_MEM": "1", "CKPT_DIR": str(tmp_path / "ck"), "CKPT_EVERY": "3", "WATCHDOG": "0",
+           "CKPT_MIRROR": str(tmp_path / "mirror"), "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12}),
+           "STOP_AT": "9", "NO_FINAL_CKPT": "1"}
+    train(Args(steps=12, eval_every=100), "cpu", env=env, out=io.StringIO())
+    files = sorted(os.listdir(tmp_path / "mirror"))
+    assert files == ["step_00000006.json", "step_00000006.pt", "step_00000009.json", "step_00000009.pt"]   # keeps two
+    tag = json.load(open(tmp_path / "mirror" / "step_00000009.json"))
+    assert tag["step"] == 9 and tag["run_id"] and tag["bytes"] == os.path.getsize(tmp_path / "mirror" / "step_00000009.pt")
+    # a foreign run's newer copy and a half-written copy sit in the same store
+    shutil.copyfile(tmp_path / "mirror" / "step_00000009.pt", tmp_path / "mirror" / "step_00000050.pt")
+    json.dump({"step": 50, "run_id": "someone-else"}, open(tmp_path / "mirror" / "step_00000050.json", "w"))
+    shutil.copyfile(tmp_path / "mirror" / "step_00000009.pt", tmp_path / "mirror" / "step_00000060.pt.tmp")
+    st = FileStore(str(tmp_path / "mirror"), tag["run_id"])
+    assert st.steps() == [6, 9] and st.steps(mine=False) == [6, 9, 50]
+    shutil.rmtree(tmp_path / "ck")                                        # the local disk is gone
+    buf = io.StringIO()
+    train(Args(steps=12, eval_every=100), "cpu", env=dict(env, STOP_AT="12"), out=buf)
+    assert "resuming at step 10" in buf.getvalue()
+    assert os.path.exists(tmp_path / "mirror" / "step_00000050.pt")       # other runs' copies are never deleted
+    assert FileStore(str(tmp_path / "mirror"), tag["run_id"]).steps() == [9, 12]

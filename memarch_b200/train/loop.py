@@ -303,6 +303,27 @@ def train(args, device=None, env=None, out=None, parallel=None):
         if env.get("COMPARE"):
             cmp_ref = {r["step"]: r["loss"] for r in map(json.loads, open(env["COMPARE"]))}
         cmp_n, cmp_max, cmp_tol = 0, 0.0, float(env.get("CMP_TOL", 1e-3))
+        # named evaluation sets beside the validation text: EVAL_SETS='{"code": "code_val.npy", ...}' (token arrays);
+        # EVAL_ONLY=1 evaluates the checkpoint of CKPT_DIR on all of them and returns without training
+        # (memarch_jax/memarch_jax/train_tpu.py: eval sets, --eval_only, --eval_at_resume)
+        eval_sets = {}
+        if env.get("EVAL_SETS"):
+            from ..data.synth import TokenStore
+            eval_sets = {k: TokenStore(np.load(v), 0, device) for k, v in json.loads(env["EVAL_SETS"]).items()}
+
+        def run_evals():
+            return {k: float(val_loss(tr.model, st_, args.seq, n=int(env.get("EVAL_BATCHES", 20)))) for k, st_ in eval_sets.items()}
+        if env.get("EVAL_ONLY") == "1" or (env.get("EVAL_AT_RESUME") == "1" and start > 1):
+            ev = dict(run_evals(), val=float(val_loss(tr.model, data.val, args.seq)))
+            print(f"{name}[{args.stage}]  eval at step {start - 1}: " + "  ".join(f"{k} {v:.4f}" for k, v in ev.items()),
+                  file=out, flush=True)
+            log.append({"step": start - 1, "eval_only": True, **ev})
+            if env.get("EVAL_ONLY") == "1":
+                if loss_log is not None:
+                    loss_log.close()
+                logs[name] = log
+                del tr
+                continue
         nan = NanGuard(int(env.get("NAN_EVERY", 10)))
         nan_at = int(env.get("TRAIN_NAN_AT", 0))              # inject a non-finite loss at this step (on the host)
         spikes = SpikeLog(float(env.get("SPIKE", 2.0)))
@@ -391,7 +412,9 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     spikes.check(step, float(loss))
                     extra = "".join(f"  {k} {float(v):.2f}" for k, v in getattr(tr.model, "stats", {}).items()
                                     if torch.is_tensor(v) and v.numel() == 1)
-                    log.append({"step": step, "time": train_time, "val": vl})
+                    sets = run_evals()
+                    extra += "".join(f"  {k} {v:.3f}" for k, v in sets.items())
+                    log.append({"step": step, "time": train_time, "val": vl, **({"sets": sets} if sets else {})})
                     print(f"{name}[{args.stage}]  step {step:5d}  val {vl:.3f}  bpb {vl / bpu / math.log(2):.4f}  "
                           f"train {float(loss):.3f}{extra}  {train_time / 60:.1f} min", file=out, flush=True)
                     sync()

@@ -359,3 +359,22 @@ def test_mirrored_checkpoints_survive_the_loss_of_the_local_directory(tmp_path, 
     assert "resuming at step 10" in buf.getvalue()
     assert os.path.exists(tmp_path / "mirror" / "step_00000050.pt")       # other runs' copies are never deleted
     assert FileStore(str(tmp_path / "mirror"), tag["run_id"]).steps() == [9, 12]
+
+
+def test_named_eval_sets_and_eval_only(tmp_path, monkeypatch):
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    rng = np.random.default_rng(0)
+    np.save(tmp_path / "a.npy", rng.integers(0, 256, 6000).astype(np.int32))
+    np.save(tmp_path / "b.npy", np.tile(np.arange(8, dtype=np.int32), 800))           # trivially predictable text
+    env = {"VOCAB": "256", "NO_MEM": "1", "CKPT_DIR": str(tmp_path / "ck"), "CKPT_EVERY": "6", "WATCHDOG": "0",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12}), "EVAL_BATCHES": "2",
+           "EVAL_SETS": json.dumps({"noise": str(tmp_path / "a.npy"), "cycle": str(tmp_path / "b.npy")})}
+    buf = io.StringIO()
+    log = train(Args(steps=6), "cpu", env=env, out=buf)["tiny"]
+    assert set(log[-1]["sets"]) == {"noise", "cycle"} and "noise" in buf.getvalue() and "cycle" in buf.getvalue()
+    buf = io.StringIO()
+    again = train(Args(steps=6), "cpu", env=dict(env, EVAL_ONLY="1"), out=buf)["tiny"]
+    assert again[-1]["eval_only"] and again[-1]["step"] == 6
+    assert abs(again[-1]["noise"] - log[-1]["sets"]["noise"]) < 1e-5 and abs(again[-1]["cycle"] - log[-1]["sets"]["cycle"]) < 1e-5
+    assert "eval at step 6" in buf.getvalue()

@@ -294,7 +294,7 @@ def run_reference(args):
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.exists(os.path.join(ref_dir, "fastloop.py")):
         print_json({"impl": "reference", "unavailable": "baseline/_ref/fastloop.py not present (reference is a "
-                    "flat script tree without packaging metadata; copy /root/reference there)"})
+                    "flat script tree without packaging metadata; copy the reference checkout there)"})
         return
     try:
         _run_reference(args, ref_dir)

@@ -199,7 +199,7 @@ def _flag(env, name, default=False):
 
 
 def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
-    """Apply the reference's environment switches (SURVEY appendix of flags; full2.py, full.py, lm.py) to `cfg`."""
+    """Apply the reference's environment switches (read in full2.py, full.py and lm.py of the reference) to `cfg`."""
     env = os.environ if env is None else env
     kw = {}
     g = env.get

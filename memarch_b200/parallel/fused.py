@@ -61,6 +61,11 @@ class SymmetricHeap:
             raise RuntimeError(f"peer wait timed out (status {st}): a rank did not reach the barrier within {self.wait_ms} ms")
 
 
+def _rotated(W, r):
+    """Peer order of rank r: itself first, then r+1, ... — a different peer for every rank at every position."""
+    return [(r + i) % W for i in range(W)]
+
+
 class _FusedExpertFFN(torch.autograd.Function):
     """xe (E, C, d) on every rank -> ye (E, C, d): experts sharded over ranks, tokens moved by the GEMMs themselves."""
 
@@ -76,6 +81,7 @@ class _FusedExpertFFN(torch.autograd.Function):
         M = W * Cn
         h = torch.empty(n_local, M, H, device=xe.device, dtype=torch.bfloat16)
         a = torch.empty_like(h) if act == "relu2" else None
+        xin = None
         if ep.pull == "tma":
             # A tiles fetched from the owners' buffers by the GEMM's own TMA loads (one tensor map per source GPU)
             xptrs = [int(p) for p in Xh.buffer_ptrs]
@@ -88,7 +94,7 @@ class _FusedExpertFFN(torch.autograd.Function):
             # rows of my experts land in local memory first (bandwidth-bound peer copies), the GEMM reads them locally:
             # a remote tile costs an NVLink round trip, more than the 6-stage shared-memory ring can hide
             xin = torch.empty(n_local, M, d, device=xe.device, dtype=torch.bfloat16)
-            for s in range(W):
+            for s in _rotated(W, r):                    # every rank starts at another owner: no hot GPU
                 xin[:, s * Cn:(s + 1) * Cn].copy_(Xh.get_buffer(s, (E, Cn, d), torch.bfloat16)[g_off:g_off + n_local])
             if act == "relu2":
                 gemm(xin, up, b_mn=True, out=h, out2=a, epi=1, groups=n_local)
@@ -98,19 +104,24 @@ class _FusedExpertFFN(torch.autograd.Function):
         # down-GEMM: A = h, cut into W row segments; segment s goes to rank s's output buffer
         hp = h.data_ptr()
         Hh = h.shape[2]
-        a_ptrs = [hp + s * Cn * Hh * 2 for s in range(W)]
-        yptrs = [int(p) for p in Yh.buffer_ptrs]
+        # the GEMM walks its segments in list order: rotate the (A segment, destination) pairs by the rank, so that at
+        # any moment the W ranks store to W different GPUs (own rows first) instead of all to the same one
+        order = _rotated(W, r)
+        a_ptrs = [hp + s * Cn * Hh * 2 for s in order]
+        yptrs = [int(Yh.buffer_ptrs[s]) for s in order]
         C.gemm_peer(a_ptrs, Cn, Hh, n_local, Hh, M * Hh, 0, down, True, None, yptrs, d, Cn * d, g_off, None, None, 0, n_local)
         _ext.count(3)
         heap.barrier(0)                                             # every expert's rows have landed here
-        ctx.save_for_backward(up, down, a, h)
+        # the staged rows are kept for the weight gradient: the backward then pulls only dY (E x C x d bf16 per layer)
+        ctx.has_xin = xin is not None and train_w
+        ctx.save_for_backward(up, down, a, h, *([xin] if ctx.has_xin else []))
         ctx.ep, ctx.key, ctx.act, ctx.g_off, ctx.n_local, ctx.train_w = ep, key, act, g_off, n_local, train_w
         ctx.shape = (E, Cn, d)
         return Y.view_as(Y)
 
     @staticmethod
     def backward(ctx, dy):
-        up, down, a, h = ctx.saved_tensors
+        up, down, a, h = ctx.saved_tensors[:4]
         ep, act, g_off, nl = ctx.ep, ctx.act, ctx.g_off, ctx.n_local
         heap, W, r = ep.heap, ep.W, ep.rank
         E, Cn, d = ctx.shape
@@ -122,11 +133,14 @@ class _FusedExpertFFN(torch.autograd.Function):
         M = W * Cn
         # pull the rows of my experts from their owners once; every local GEMM reads the local copy
         dy_all = torch.empty(nl, M, d, device=dy.device, dtype=torch.bfloat16)
-        xe_all = torch.empty(nl, M, d, device=dy.device, dtype=torch.bfloat16) if ctx.train_w else None
-        for s in range(W):
+        xe_all = ctx.saved_tensors[4] if ctx.has_xin else None
+        pull_x = ctx.train_w and xe_all is None
+        if pull_x:
+            xe_all = torch.empty(nl, M, d, device=dy.device, dtype=torch.bfloat16)
+        for s in _rotated(W, r):
             src = DYh.get_buffer(s, (E, Cn, d), torch.bfloat16)
             dy_all[:, s * Cn:(s + 1) * Cn].copy_(src[g_off:g_off + nl])
-            if xe_all is not None:
+            if pull_x:
                 srcx = Xh.get_buffer(s, (E, Cn, d), torch.bfloat16)
                 xe_all[:, s * Cn:(s + 1) * Cn].copy_(srcx[g_off:g_off + nl])
         if act == "relu2":
@@ -139,8 +153,9 @@ class _FusedExpertFFN(torch.autograd.Function):
             dup = gemm(xe_all, da, a_mn=True, b_mn=True, groups=nl)
         # dxe = da . up^T, rows pushed to the owners of the tokens
         Hh = da.shape[2]
-        a_ptrs = [da.data_ptr() + s * Cn * Hh * 2 for s in range(W)]
-        dxptrs = [int(p) for p in DXh.buffer_ptrs]
+        order = _rotated(W, r)
+        a_ptrs = [da.data_ptr() + s * Cn * Hh * 2 for s in order]
+        dxptrs = [int(DXh.buffer_ptrs[s]) for s in order]
         C.gemm_peer(a_ptrs, Cn, Hh, nl, Hh, M * Hh, 0, up, False, None, dxptrs, d, Cn * d, g_off, None, None, 0, nl)
         _ext.count()
         heap.barrier(0)
@@ -347,6 +362,16 @@ class FusedParallel:
             e1, e2 = rel(y, yr), rel(xe.grad, xr.grad)
             if not (e1 < tol and e2 < tol):
                 raise RuntimeError(f"fused expert exchange differs from the local computation: fwd {e1:.3e}, bwd {e2:.3e}")
+            # weight gradients of this rank's expert: it saw the rows that every rank routed to it
+            xs, gs = [torch.empty_like(go) for _ in range(W)], [torch.empty_like(go) for _ in range(W)]
+            dist.all_gather(xs, xe.detach().contiguous(), group=heap.group)
+            dist.all_gather(gs, go.contiguous(), group=heap.group)
+            xa, ga = torch.cat([t[r] for t in xs]).float(), torch.cat([t[r] for t in gs]).float()
+            ur, dr = up_all[r].float().requires_grad_(), down_all[r].float().requires_grad_()
+            ((torch.relu(xa @ ur) ** 2) @ dr).backward(ga)
+            e3, e4 = rel(up.grad[0], ur.grad), rel(down.grad[0], dr.grad)
+            if not (e3 < tol and e4 < tol):
+                raise RuntimeError(f"fused expert exchange: weight gradients differ: up {e3:.3e}, down {e4:.3e}")
         except Exception as e:   # noqa: BLE001 - the reason travels in the message
             msg = f"{type(e).__name__}: {e}"
         flag = torch.tensor([1.0 if msg == "ok" else 0.0], device=dev)

@@ -11,7 +11,8 @@ from __future__ import annotations
 
 import torch
 
-from .basic import linear as _linear_bf16
+from . import _ext
+from .basic import gemm, gemm_ok
 
 
 def fq(x, dim):
@@ -24,9 +25,21 @@ def fq(x, dim):
 
 def _mm_t(a, b):
     """a (M,K) · b (N,K)ᵀ with fp32 result; tcgen05 GEMM on the GPU."""
-    if a.is_cuda:
-        return _linear_bf16(a, b).float()
+    if _ext.use_cuda(a):
+        M, K = a.shape
+        N = b.shape[0]
+        if gemm_ok(M, N, K) and M >= 128:
+            # integers up to 127 are exact in bf16 and their dot products are exact in the fp32 accumulator: the
+            # result must leave the kernel in fp32 too, a bf16 store would round away the low digits
+            out = torch.zeros(M, N, device=a.device, dtype=torch.float32)
+            gemm(a.contiguous(), b.contiguous(), out=out, out_dtype=torch.float32, accumulate=True)
+            return out
     return a.float() @ b.float().t()
+
+
+def _bmm_exact(a, b):
+    """Batched product of integer-valued bf16 operands with an exact fp32 result (a bf16 result would round it)."""
+    return torch.bmm(a.float(), b.float())
 
 
 class _I8Linear(torch.autograd.Function):
@@ -59,7 +72,7 @@ class _I8Bmm(torch.autograd.Function):
     def forward(ctx, x, w):
         qx, sx = fq(x, 2)
         qw, sw = fq(w, 1)
-        y = torch.bmm(qx, qw).float() * sx * sw
+        y = _bmm_exact(qx, qw) * sx * sw
         ctx.save_for_backward(x, w)
         return y.to(x.dtype)
 
@@ -68,7 +81,7 @@ class _I8Bmm(torch.autograd.Function):
         x, w = ctx.saved_tensors
         qg, sg = fq(g, 2)
         qw, sw = fq(w, 2)
-        dx = (torch.bmm(qg, qw.transpose(1, 2)).float() * sg * sw.transpose(1, 2)).to(x.dtype)
+        dx = (_bmm_exact(qg, qw.transpose(1, 2)) * sg * sw.transpose(1, 2)).to(x.dtype)
         dw = torch.bmm(x.to(torch.bfloat16).transpose(1, 2), g.to(torch.bfloat16)).to(w.dtype)
         return dx, dw
 

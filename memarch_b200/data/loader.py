@@ -238,9 +238,13 @@ class HostLoader:
     """Worker thread -> bounded queue of (pinned batch, corpus state after it).  `next()` returns the batch on
     `device` (async copy from pinned memory) and remembers that batch's state for `state_dict()`."""
 
-    def __init__(self, corpus, B, device="cpu", depth=2, pin=None):
+    def __init__(self, corpus, B, device="cpu", depth=2, pin=None, xform=None, first=0):
+        """`xform(xy, n) -> (xy, extra)` rewrites batch number n on the worker thread (needle injection); the batch
+        number is part of the loader's state, so a resumed run rewrites the same batches the same way, and the
+        `extra` of the batch handed out last is kept in `self.extra`."""
         import torch
         self.corpus, self.B, self.device = corpus, B, torch.device(device)
+        self.xform, self.n_next, self.n_done, self.extra = xform, int(first), int(first), None
         self.pin = (self.device.type == "cuda") if pin is None else pin
         self.q = queue.Queue(maxsize=depth)
         self.state = corpus.state_dict()
@@ -253,10 +257,15 @@ class HostLoader:
         import torch
         try:
             while not self._stop.is_set():
-                x = torch.from_numpy(self.corpus.batch(self.B))
+                xy, extra = self.corpus.batch(self.B), None
+                if self.xform is not None:
+                    xy, extra = self.xform(xy, self.n_next)
+                    xy = np.ascontiguousarray(xy, dtype=np.int64)
+                self.n_next += 1
+                x = torch.from_numpy(xy)
                 if self.pin:
                     x = x.pin_memory()
-                item = (x, self.corpus.state_dict())
+                item = (x, self.corpus.state_dict(), extra, self.n_next)
                 while not self._stop.is_set():
                     try:
                         self.q.put(item, timeout=0.2)
@@ -270,11 +279,11 @@ class HostLoader:
         item = self.q.get()
         if isinstance(item, BaseException):
             raise RuntimeError("corpus worker failed") from item
-        x, self.state = item
+        x, self.state, self.extra, self.n_done = item
         return x.to(self.device, non_blocking=True)
 
     def state_dict(self):
-        return self.state
+        return dict(self.state, loader_n=self.n_done)
 
     def close(self):
         self._stop.set()

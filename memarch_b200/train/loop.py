@@ -207,7 +207,22 @@ class _CorpusData:
         else:
             vc = ShardCorpus(w, root, seq=seq, seed=10 ** 6)
             self.val = TokenStore(vc.batch(max(2, 160 * 1024 // seq)).reshape(-1), 0, device)
-        self._B = None
+        self._B, self._n = None, 0
+        # recall needles written into the training text (REMIND_P > 0): p schedule, optional distance ladder
+        self.remind = None
+        if float(env.get("REMIND_P", 0) or 0) > 0:
+            from ..data.reminders import Reminders
+            lad = [int(v) for v in env["REMIND_LADDER"].split(",")] if env.get("REMIND_LADDER") else None
+            self.remind = Reminders(float(env["REMIND_P"]), seq, n=int(env.get("REMIND_N", 16)),
+                                    dist=int(env.get("REMIND_DIST", min(2048, seq // 4))), seed=int(env.get("CORPUS_SEED", 0)),
+                                    tok0=int(env.get("REMIND_TOK0", 1000)), V=int(env["VOCAB"]) if env.get("VOCAB") else None,
+                                    p0=float(env["REMIND_P0"]) if env.get("REMIND_P0") else None,
+                                    warm=int(env.get("REMIND_WARM", 0)), decay=int(env.get("REMIND_DECAY", 0)), ladder=lad,
+                                    thr=float(env.get("REMIND_THR", 0.9)), win=int(env.get("REMIND_WIN", 800)),
+                                    lag=int(env.get("REMIND_LAG", 5)), doc_eos=self.corpus.eos)
+
+    def _xform(self, xy, n):
+        return self.remind(xy, n=n)
 
     def batch(self, B, T):
         assert T == self.seq, "the corpus serves windows of one fixed length"
@@ -216,18 +231,30 @@ class _CorpusData:
                 st = self.loader.state_dict()
                 self.loader.close()
                 self.corpus.load_state_dict(st)
+                self._n = st.get("loader_n", self._n)
             from ..data.loader import HostLoader
-            self.loader, self._B = HostLoader(self.corpus, B, device=self.device), B
+            self.loader, self._B = HostLoader(self.corpus, B, device=self.device, first=self._n,
+                                              xform=self._xform if self.remind is not None else None), B
         return self.loader.next()
 
+    @property
+    def extra(self):
+        return self.loader.extra if self.loader is not None else None
+
     def state_dict(self):
-        return self.loader.state_dict() if self.loader is not None else self.corpus.state_dict()
+        sd = self.loader.state_dict() if self.loader is not None else dict(self.corpus.state_dict(), loader_n=self._n)
+        if self.remind is not None:
+            sd = dict(sd, remind=self.remind.state())
+        return sd
 
     def load_state_dict(self, sd):
         if self.loader is not None:
             self.loader.close()
             self.loader = None
         self.corpus.load_state_dict(sd)
+        self._n = sd.get("loader_n", 0)
+        if self.remind is not None and sd.get("remind"):
+            self.remind.load(sd["remind"])
 
 
 def make_data(args, device, env=None, rank=0, world=1):
@@ -413,6 +440,13 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     extra = "".join(f"  {k} {float(v):.2f}" for k, v in getattr(tr.model, "stats", {}).items()
                                     if torch.is_tensor(v) and v.numel() == 1)
                     sets = run_evals()
+                    rm = getattr(data, "remind", None)
+                    if rm is not None and data.extra is not None and data.extra["rem"].any():
+                        hits, n_ans = needle_hits(tr.model, xy_b, torch.from_numpy(data.extra["rem"]).to(tr.device) > 0)
+                        sets["needles"] = hits / max(n_ans, 1.0)
+                        msg = rm.observe(data.loader.n_done - 1, hits, n_ans)
+                        if msg:
+                            print(msg, file=out, flush=True)
                     extra += "".join(f"  {k} {v:.3f}" for k, v in sets.items())
                     log.append({"step": step, "time": train_time, "val": vl, **({"sets": sets} if sets else {})})
                     print(f"{name}[{args.stage}]  step {step:5d}  val {vl:.3f}  bpb {vl / bpu / math.log(2):.4f}  "
@@ -440,6 +474,23 @@ def train(args, device=None, env=None, out=None, parallel=None):
         logs[name] = log
         del tr
     return logs
+
+
+@torch.no_grad()
+def needle_hits(model, xy, rem):
+    """(hits, answers) on the marked question positions of a training batch: an answer counts when the value gets more
+    than half of the probability (it is then certainly the arg-max).  One extra forward without gradient."""
+    was = model.training
+    model.eval()
+    out, _ = model(xy[:, :-1])
+    y = xy[:, 1:]
+    if hasattr(model, "_ce_tok"):
+        ce = model._ce_tok(out[0], y).float().view_as(y)
+    else:
+        V = out.shape[-1]
+        ce = torch.nn.functional.cross_entropy(out.float().view(-1, V), y.reshape(-1), reduction="none").view_as(y)
+    model.train(was)
+    return float((ce[rem] < math.log(2.0)).sum()), float(rem.sum())
 
 
 @torch.no_grad()

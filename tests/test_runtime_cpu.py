@@ -378,3 +378,31 @@ def test_named_eval_sets_and_eval_only(tmp_path, monkeypatch):
     assert again[-1]["eval_only"] and again[-1]["step"] == 6
     assert abs(again[-1]["noise"] - log[-1]["sets"]["noise"]) < 1e-5 and abs(again[-1]["cycle"] - log[-1]["sets"]["cycle"]) < 1e-5
     assert "eval at step 6" in buf.getvalue()
+
+
+def test_needles_in_the_training_text_follow_the_loader_and_resume(tmp_path, monkeypatch):
+    from memarch_b200.train.loop import make_data, train
+    monkeypatch.chdir(tmp_path)
+    w = make_corpus(str(tmp_path / "corpus"), docs=60)
+    env = {"VOCAB": "2048", "NO_MEM": "1", "WATCHDOG": "0", "CORPUS": json.dumps(w), "CORPUS_ROOT": str(tmp_path / "corpus"),
+           "REMIND_P": "1.0", "REMIND_N": "2", "REMIND_DIST": "4", "REMIND_TOK0": "1000", "REMIND_LADDER": "6,12",
+           "REMIND_WIN": "4", "REMIND_THR": "0.0", "REMIND_LAG": "3",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
+    a = Args(seq=48, batch=4, micro=4, steps=6, eval_every=2)
+    data = make_data(a, "cpu", env)
+    seen = [data.batch(4, 48).clone() for _ in range(3)]
+    mark = data.remind.mark
+    assert all(int((b == mark).sum()) == 4 * 4 for b in seen)                  # two blocks of two markers per row
+    assert data.extra["rem"].shape == (4, 48) and data.extra["rem"].sum() == 8
+    st = json.loads(json.dumps(data.state_dict()))
+    assert st["loader_n"] == 3 and "remind" in st
+    nxt = data.batch(4, 48).clone()
+    data.loader.close()
+    data2 = make_data(a, "cpu", env)
+    data2.load_state_dict(st)
+    assert torch.equal(data2.batch(4, 48), nxt)                                # same text, same needles after resume
+    data2.loader.close()
+    buf = io.StringIO()
+    log = train(a, "cpu", env=env, out=buf)["tiny"]
+    assert "needles" in log[-1]["sets"] and 0.0 <= log[-1]["sets"]["needles"] <= 1.0
+    assert "reminders: level 0 -> 1" in buf.getvalue()                          # threshold 0: the ladder moves on

@@ -393,3 +393,37 @@ def test_confidence_brake_slows_noise_and_spares_a_steady_direction():
     assert cos > 0.9999 and outs[1].norm() < 0.5 * outs[0].norm()
     sd = o.state_dict()
     assert "snr_v" in sd and "snr_f" in sd
+
+
+def test_weight_tree_round_trip_through_npz(tmp_path):
+    from memarch_b200.build import build
+    from memarch_b200.train import convert
+    torch.manual_seed(0)
+    m = build("tiny", 512)
+    sd = m.state_dict()
+    tree, beside = convert.to_tree(sd)
+    L = len([k for k in sd if k.startswith("heavy.") and k.endswith(".up")])
+    assert tree["heavy"]["up"].shape == (L,) + tuple(sd["heavy.0.up"].shape) and set(tree["heavy"]) == set(convert.HEAVY)
+    assert len(tree["light_a"]) >= 1 and set(tree["light_a"][0]) == set(convert.BLOCK_KEYS) and "tau" in beside
+    flat = convert.from_tree(tree, beside)
+    assert all(np.array_equal(v, sd[k].float().numpy()) for k, v in flat.items())
+    params = {k for k, _ in m.named_parameters()}
+    assert params <= set(flat), sorted(params - set(flat))                  # every trained weight is in the tree
+    convert.save_npz(str(tmp_path / "w.npz"), tree, beside, step=7)
+    tree2, beside2, step = convert.load_npz(str(tmp_path / "w.npz"))
+    assert step == 7
+    flat2 = convert.from_tree(tree2, beside2)
+    assert set(flat2) == set(flat) and all(np.array_equal(flat2[k], flat[k]) for k in flat)
+    torch.manual_seed(1)
+    m2 = build("tiny", 512)
+    left = convert.load_into(m2, tree2, beside2)
+    assert all(torch.equal(m2.state_dict()[k], sd[k]) for k in flat) and not (set(left) & params)
+    x = torch.randint(0, 512, (2, 64))
+    m.eval(); m2.eval()
+    with torch.no_grad():
+        a, b = m(x)[0], m2(x)[0]
+    a, b = (a[0] if isinstance(a, (tuple, list)) else a), (b[0] if isinstance(b, (tuple, list)) else b)
+    assert torch.equal(a, b)
+    grads = {"emb.weight": torch.ones(512, 4), "heavy.0.up": torch.zeros(2, 3, 4), "heavy.1.up": torch.ones(2, 3, 4)}
+    gt, _ = convert.to_tree(grads)                                           # partial dicts convert too
+    assert gt["heavy"]["up"].shape == (2, 2, 3, 4) and set(gt["heavy"]) == {"up"}

@@ -377,6 +377,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
         def sync():
             if tr.device.type == "cuda":
                 torch.cuda.synchronize()
+        phase = {"data": 0.0, "enqueue": 0.0, "eval": 0.0, "ckpt": 0.0, "n": 0.0}
         sync()
         t0 = time.time()
         nxt = fetch(start) if prefetch else None
@@ -399,8 +400,13 @@ def train(args, device=None, env=None, out=None, parallel=None):
                         nxt = fetch(step + 1)
                     loss = tr.step(xy_b, step - 1, preps)
                 else:
+                    td = time.time()
                     xy_b = data.batch(args.batch * (args.seq // seq), seq)
+                    ts = time.time()
                     loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1)
+                    phase["data"] += ts - td
+                    phase["enqueue"] += time.time() - ts
+                    phase["n"] += 1
                 if nan_at and step == nan_at:                       # host-made failure for the guard tests
                     loss = loss * float("nan")
                 nan.check(loss)
@@ -431,7 +437,9 @@ def train(args, device=None, env=None, out=None, parallel=None):
                             cur = [p.detach().clone() for p in ps]
                             for p, e in zip(ps, ema):
                                 p.copy_(e)
+                    te = time.time()
                     vl = float(val_loss(tr.model, data.val, args.seq))
+                    phase["eval"] += time.time() - te
                     if cur is not None:
                         with torch.no_grad():
                             for p, c0 in zip(ps, cur):
@@ -451,11 +459,20 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     log.append({"step": step, "time": train_time, "val": vl, **({"sets": sets} if sets else {})})
                     print(f"{name}[{args.stage}]  step {step:5d}  val {vl:.3f}  bpb {vl / bpu / math.log(2):.4f}  "
                           f"train {float(loss):.3f}{extra}  {train_time / 60:.1f} min", file=out, flush=True)
+                    if env.get("DIAG") == "1":                  # host-side phase times since the last report
+                        n_ = max(phase["n"], 1)
+                        mem = f", device {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} GiB peak" if tr.device.type == "cuda" else ""
+                        print(f"[diag] per step: data wait {1e3 * phase['data'] / n_:.2f} ms, step enqueue "
+                              f"{1e3 * phase['enqueue'] / n_:.2f} ms; eval {phase['eval']:.2f} s, checkpoint "
+                              f"{phase['ckpt']:.2f} s (snapshot only: the write is in the background){mem}", file=out, flush=True)
+                        phase = dict.fromkeys(phase, 0.0)
                     sync()
                     t0 = time.time()
                 if ck is not None and ck_every and (step % ck_every == 0 or (step == last and env.get("NO_FINAL_CKPT") != "1")):
                     nan.flush()                                  # never save a state that already went non-finite
+                    tc = time.time()
                     ck.save(tr, step, log, data.state_dict())
+                    phase["ckpt"] += time.time() - tc
         finally:
             if dog:
                 dog.close()

@@ -368,11 +368,12 @@ def test_named_eval_sets_and_eval_only(tmp_path, monkeypatch):
     np.save(tmp_path / "a.npy", rng.integers(0, 256, 6000).astype(np.int32))
     np.save(tmp_path / "b.npy", np.tile(np.arange(8, dtype=np.int32), 800))           # trivially predictable text
     env = {"VOCAB": "256", "NO_MEM": "1", "CKPT_DIR": str(tmp_path / "ck"), "CKPT_EVERY": "6", "WATCHDOG": "0",
-           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12}), "EVAL_BATCHES": "2",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12}), "EVAL_BATCHES": "2", "DIAG": "1",
            "EVAL_SETS": json.dumps({"noise": str(tmp_path / "a.npy"), "cycle": str(tmp_path / "b.npy")})}
     buf = io.StringIO()
     log = train(Args(steps=6), "cpu", env=env, out=buf)["tiny"]
     assert set(log[-1]["sets"]) == {"noise", "cycle"} and "noise" in buf.getvalue() and "cycle" in buf.getvalue()
+    assert "[diag] per step: data wait" in buf.getvalue()                             # host-side phase times
     buf = io.StringIO()
     again = train(Args(steps=6), "cpu", env=dict(env, EVAL_ONLY="1"), out=buf)["tiny"]
     assert again[-1]["eval_only"] and again[-1]["step"] == 6

@@ -129,7 +129,7 @@ def write_corpus(out_dir, tokens=8_000_000, d=256, vocab=50304, phr_v=None, phra
     import json
     from .loader import write_shard
     from .synth import MarkovCorpus
-    phr_v = phr_v or min(vocab, 50257)
+    phr_v = phr_v or min(vocab - 1, 50257)                 # the document separator is one id above: it must fit too
     os.makedirs(out_dir, exist_ok=True)
     mc = MarkovCorpus(vocab=phr_v, seed=seed)
     toks = mc.stream(tokens, text_len=2048, seed=seed + 1)

@@ -407,3 +407,35 @@ def test_needles_in_the_training_text_follow_the_loader_and_resume(tmp_path, mon
     log = train(a, "cpu", env=env, out=buf)["tiny"]
     assert "needles" in log[-1]["sets"] and 0.0 <= log[-1]["sets"]["needles"] <= 1.0
     assert "reminders: level 0 -> 1" in buf.getvalue()                          # threshold 0: the ladder moves on
+
+
+def test_recipe_plan_and_step_count(tmp_path, capsys):
+    from memarch_b200.cli import main, recipe_steps
+    assert recipe_steps(448.0, 1500.0) == 3300 and recipe_steps(5000.0, 1500.0) == 500 and recipe_steps(153.6, 1500) == 9750
+    assert main(["recipe", "--dry", "--out", str(tmp_path / "art")]) == 0
+    out = capsys.readouterr().out
+    assert "T Td2048L16" in out and "ours Fv2moeK8h8d2048" in out
+    ours = out.split("ours Fv2moeK8h8d2048")[1]
+    assert '"INDUCT": "lock"' in ours and '"NO_MEM": "1"' in ours and '"MOE_ACT": "relu2"' in ours
+    dense = out.split("ours Fv2moeK8h8d2048")[0]
+    assert "INDUCT" not in dense and '"OPT_KW"' in dense
+
+
+def test_recipe_runs_both_models_end_to_end(tmp_path, monkeypatch, capsys):
+    from memarch_b200 import cli
+    monkeypatch.chdir(tmp_path)
+    for k, v in {"D_MODEL": "256", "VOCAB": "512", "WATCHDOG": "0"}.items():
+        monkeypatch.setenv(k, v)
+    monkeypatch.setattr(cli, "RECIPE_MODELS", (("T", "tiny", False), ("ours", "tiny", True)))
+    monkeypatch.setattr(cli, "recipe_steps", lambda ms, budget: 4)
+    args = cli.parser().parse_args(["recipe", "--out", "art", "--tokens", "120000", "--batch", "2", "--seq", "64",
+                                    "--device", "cpu"])
+    args.micro = 2
+    before = dict(os.environ)
+    plan = cli.recipe(args)
+    assert [(p["tag"], p["steps"], len(p["log"])) for p in plan] == [("T", 4, 1), ("ours", 4, 1)]
+    assert dict(os.environ) == before                                  # the switches of a model do not leak
+    out = capsys.readouterr().out
+    assert "[recipe] T tiny" in out and "[recipe] ours tiny" in out
+    assert "trust" in out.split("[recipe] T tiny")[1] and "trust" not in out.split("[recipe] T tiny")[0]   # locks: ours only
+    assert os.path.exists(tmp_path / "art" / "env.json")

@@ -15,10 +15,10 @@ Behaviour follows the reference's host-side data tools (memarch_jax/memarch_jax/
   (more than the prefetch depth, so the choice is deterministic); the last level mixes all distances;
 * `exact` (evaluation) puts exactly that many words between the two blocks;
 * `synth` batches are filler plus one needle (the pure recall task);
-* `near`: a share of the needles at distance 0..near_max, inside the attention window.
+* `near`: a share of the needles at distance 0..near_max, inside the attention window;
+* `blank`: the value after each question key is replaced by the marker, the true value is returned in `rem_y` (B, T).
 
-Not carried over: the densely packed synthetic episodes and their own level table, answers hidden behind the marker,
-several needles per row.
+Not carried over: the densely packed synthetic episodes and their own level table, several needles per row.
 """
 from __future__ import annotations
 
@@ -31,7 +31,7 @@ N_KEYS, N_VALS = 512, 64
 
 class Reminders:
     def __init__(self, p, T, n=16, dist=2048, tok0=1000, seed=0, V=None, p0=None, warm=0, decay=0, ladder=None,
-                 thr=0.9, win=800, lag=5, dmin=0, synth=0, doc_eos=None, near=0.0, near_max=0):
+                 thr=0.9, win=800, lag=5, dmin=0, synth=0, doc_eos=None, near=0.0, near_max=0, blank=False):
         self.p, self.T, self.n, self.dist, self.seed = float(p), int(T), int(n), int(dist), int(seed)
         self.p0 = None if p0 is None else float(p0)
         self.warm, self.decay = int(warm), int(decay)
@@ -40,6 +40,7 @@ class Reminders:
         self.synth, self.V = int(synth), V
         self.doc_eos = None if doc_eos is None or int(doc_eos) < 0 else int(doc_eos)
         self.near, self.near_max = float(near), int(near_max)
+        self.blank = bool(blank)                     # answers are not visible in the questions: the target is in rem_y
         self.k0, self.v0, self.mark = tok0, tok0 + N_KEYS, tok0 + N_KEYS + N_VALS
         self.L = 2 * self.n + 2                      # one block: marker, n (key, value) pairs, marker
         self.changes = [(0, 0)]                      # (first batch, level)
@@ -149,17 +150,27 @@ class Reminders:
         xy = np.array(xy, copy=True)
         B, T1 = xy.shape
         rem = np.zeros((B, T1 - 1), np.int8)
+        rem_y = np.zeros((B, T1 - 1), np.int32) if self.blank else None
         for b in range(B):
             rng = np.random.default_rng([self.seed, zlib.crc32(xy[b].tobytes())])
+            pq = None
             if synth:
                 xy[b] = self._filler(rng, T1)
-                rem[b, self._needle(xy[b], rng, exact, level_range)] = 1
+                pq = self._needle(xy[b], rng, exact, level_range)
             elif rng.random() < p:
                 ex = exact
                 if ex is None and self.near > 0 and self.near_max > 0 and rng.random() < self.near:
                     ex = int(rng.integers(0, min(self.near_max, T1 - 2 * self.L) + 1))
-                rem[b, self._needle(xy[b], rng, ex, None if ex is not None else level_range)] = 1
-        return xy, {"rem": rem}
+                pq = self._needle(xy[b], rng, ex, None if ex is not None else level_range)
+            if pq is not None:
+                rem[b, pq] = 1
+                if self.blank:                           # "the answers are seen only after the test"
+                    rem_y[b, pq] = xy[b, pq + 1]
+                    xy[b, pq + 1] = self.mark
+        out = {"rem": rem}
+        if self.blank:
+            out["rem_y"] = rem_y
+        return xy, out
 
     @staticmethod
     def score(logits_argmax, xy, rem):

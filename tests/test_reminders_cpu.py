@@ -100,6 +100,14 @@ def test_ladder_levels_follow_success_with_a_lag_and_survive_resume():
     assert all(check_needle(near, out[b], e["rem"][b]) <= 8 for b in range(6))
     hits, n_ans = Reminders.score(out[:, 1:], out, e["rem"])              # a perfect predictor
     assert hits == n_ans == 24
+    hidden = Reminders(1.0, T=1024, n=4, dist=256, blank=True)
+    plain = Reminders(1.0, T=1024, n=4, dist=256)
+    oh, eh = hidden(xy)
+    op, ep = plain(xy)
+    assert np.array_equal(eh["rem"], ep["rem"])
+    m = ep["rem"] > 0
+    assert (oh[:, 1:][m] == hidden.mark).all() and np.array_equal(eh["rem_y"][m], op[:, 1:][m])   # answers only in rem_y
+    assert (eh["rem_y"][~m] == 0).all() and np.array_equal(np.where(m, 0, oh[:, 1:]), np.where(m, 0, op[:, 1:]))
 
 
 def test_kind_corpus_schedule_pools_and_resume(tmp_path):

@@ -16,9 +16,10 @@ Behaviour follows the reference's host-side data tools (memarch_jax/memarch_jax/
 * `exact` (evaluation) puts exactly that many words between the two blocks;
 * `synth` batches are filler plus one needle (the pure recall task);
 * `near`: a share of the needles at distance 0..near_max, inside the attention window;
+* `per_row` / `far_log`: several marker-free needles per row of text with log-uniform far distances;
 * `blank`: the value after each question key is replaced by the marker, the true value is returned in `rem_y` (B, T).
 
-Not carried over: the densely packed synthetic episodes and their own level table, several needles per row.
+Not carried over: the densely packed synthetic episodes and their own level table.
 """
 from __future__ import annotations
 
@@ -31,7 +32,8 @@ N_KEYS, N_VALS = 512, 64
 
 class Reminders:
     def __init__(self, p, T, n=16, dist=2048, tok0=1000, seed=0, V=None, p0=None, warm=0, decay=0, ladder=None,
-                 thr=0.9, win=800, lag=5, dmin=0, synth=0, doc_eos=None, near=0.0, near_max=0, blank=False):
+                 thr=0.9, win=800, lag=5, dmin=0, synth=0, doc_eos=None, near=0.0, near_max=0, blank=False,
+                 per_row=1, far_log=None):
         self.p, self.T, self.n, self.dist, self.seed = float(p), int(T), int(n), int(dist), int(seed)
         self.p0 = None if p0 is None else float(p0)
         self.warm, self.decay = int(warm), int(decay)
@@ -40,6 +42,7 @@ class Reminders:
         self.synth, self.V = int(synth), V
         self.doc_eos = None if doc_eos is None or int(doc_eos) < 0 else int(doc_eos)
         self.near, self.near_max = float(near), int(near_max)
+        self.per_row, self.far_log = int(per_row), (None if far_log is None else float(far_log))
         self.blank = bool(blank)                     # answers are not visible in the questions: the target is in rem_y
         self.k0, self.v0, self.mark = tok0, tok0 + N_KEYS, tok0 + N_KEYS + N_VALS
         self.L = 2 * self.n + 2                      # one block: marker, n (key, value) pairs, marker
@@ -138,6 +141,48 @@ class Reminders:
                 seg[hit] = self._filler(rng, int(hit.sum()))
         return q + 1 + 2 * np.arange(n)              # positions of the question keys in x (y there is the value)
 
+    def _several(self, row, rng):
+        """Several needles in one row of text, without markers: facts `[k v]*n`, questions `[k v]*n` in another order.
+        All keys of the row are distinct, blocks do not overlap (a needle may lie inside another, as in a
+        conversation), and the needle tokens occur nowhere else in the row.  Distance: with probability `far_log`
+        (default 1 - near) log-uniform between `dist` and the end of the row, otherwise 0..near_max."""
+        n, T1 = self.n, len(row)
+        Lb = 2 * n
+        stray = (row >= self.k0) & (row <= self.mark)
+        if stray.any():
+            row[stray] = self._filler(rng, int(stray.sum()))
+        R = max(1, min(self.per_row, N_KEYS // n))
+        all_keys = self.k0 + rng.permutation(N_KEYS)[:R * n]
+        taken = np.zeros(T1, bool)
+        dmax = T1 - 2 * Lb
+        far = self.far_log if self.far_log is not None else 1.0 - self.near
+        lo = max(1, min(self.dist, dmax))
+        found = []
+        for r in range(R):
+            for _ in range(32):                                       # a few tries to find free room
+                if rng.random() < far:
+                    d = min(max(int(np.exp(rng.uniform(np.log(lo), np.log(dmax + 1)))), lo), dmax)
+                else:
+                    d = int(rng.integers(0, min(self.near_max, dmax) + 1))
+                s = int(rng.integers(0, dmax - d + 1))
+                q = s + Lb + d
+                if taken[s:s + Lb].any() or taken[q:q + Lb].any():
+                    continue
+                keys = all_keys[r * n:(r + 1) * n]
+                vals = self.v0 + rng.integers(0, N_VALS, n)
+                order = rng.permutation(n)
+                row[s:s + Lb] = np.stack([keys, vals], 1).reshape(-1)
+                row[q:q + Lb] = np.stack([keys[order], vals[order]], 1).reshape(-1)
+                taken[s:s + Lb] = taken[q:q + Lb] = True
+                if self.doc_eos is not None:
+                    seg = row[s:q + Lb]
+                    cut = seg == self.doc_eos
+                    if cut.any():
+                        seg[cut] = self._filler(rng, int(cut.sum()))
+                found.append(q + 2 * np.arange(n))
+                break
+        return np.sort(np.concatenate(found)) if found else np.zeros(0, np.int64)
+
     def __call__(self, xy, p=None, exact=None, n=None, synth=None):
         """xy (B, T+1) tokens -> (xy with needles, {"rem": (B, T) int8}).  `n` = number of the training batch."""
         if synth is None:
@@ -159,9 +204,13 @@ class Reminders:
                 pq = self._needle(xy[b], rng, exact, level_range)
             elif rng.random() < p:
                 ex = exact
-                if ex is None and self.near > 0 and self.near_max > 0 and rng.random() < self.near:
+                several = self.per_row > 1 or self.far_log is not None          # draws its own near / far distances
+                if ex is None and not several and self.near > 0 and self.near_max > 0 and rng.random() < self.near:
                     ex = int(rng.integers(0, min(self.near_max, T1 - 2 * self.L) + 1))
-                pq = self._needle(xy[b], rng, ex, None if ex is not None else level_range)
+                if ex is None and level_range is None and several:
+                    pq = self._several(xy[b], rng)
+                else:
+                    pq = self._needle(xy[b], rng, ex, None if ex is not None else level_range)
             if pq is not None:
                 rem[b, pq] = 1
                 if self.blank:                           # "the answers are seen only after the test"

@@ -206,3 +206,33 @@ def test_heldout_tail_is_disjoint_from_training_and_is_the_eval_split(tmp_path):
     for _ in range(80):
         seen |= {int(t) for t in both.batch(4).reshape(-1) if t >= 1000}
     assert tail_ids <= seen                                  # without the switch nothing is held out
+
+
+def test_several_marker_free_needles_per_row():
+    r = Reminders(1.0, T=2048, n=4, dist=64, per_row=3, near=0.3, near_max=16, seed=3, V=30000)
+    xy = rows(12, 2049, seed=9)
+    xy[:, 100:110] = r.k0 + 5                                       # stray needle tokens in the text
+    out, e = r(xy)
+    total = 0
+    for b in range(12):
+        pos = np.flatnonzero(e["rem"][b])
+        assert len(pos) % 4 == 0 and 4 <= len(pos) <= 12
+        total += len(pos)
+        keys = out[b, pos]
+        assert len(set(keys.tolist())) == len(keys)                  # all keys of the row differ
+        in_range = (out[b] >= r.k0) & (out[b] <= r.mark)
+        assert in_range.sum() == 4 * len(pos) and not (out[b] == r.mark).any()      # facts + questions only, no markers
+        for p_ in pos:                                               # every question has its fact earlier in the row
+            k, v = out[b, p_], out[b, p_ + 1]
+            earlier = np.flatnonzero(out[b, :p_] == k)
+            assert len(earlier) == 1 and out[b, earlier[0] + 1] == v
+    assert total >= 12 * 8                                           # most rows get two or three needles
+    out2, e2 = r(xy)
+    assert np.array_equal(out, out2) and np.array_equal(e["rem"], e2["rem"])
+    one = Reminders(1.0, T=2048, n=4, dist=64, far_log=1.0, seed=3)
+    o1, e1 = one(xy)
+    for b in range(12):
+        pos = np.flatnonzero(e1["rem"][b])
+        assert len(pos) == 4
+        first_fact = min(int(np.flatnonzero(o1[b, :p_] == o1[b, p_])[0]) for p_ in pos)
+        assert pos[0] - (first_fact + 8) >= 64                       # far needles keep the minimum distance

@@ -219,7 +219,11 @@ class _CorpusData:
                                     p0=float(env["REMIND_P0"]) if env.get("REMIND_P0") else None,
                                     warm=int(env.get("REMIND_WARM", 0)), decay=int(env.get("REMIND_DECAY", 0)), ladder=lad,
                                     thr=float(env.get("REMIND_THR", 0.9)), win=int(env.get("REMIND_WIN", 800)),
-                                    lag=int(env.get("REMIND_LAG", 5)), doc_eos=self.corpus.eos)
+                                    lag=int(env.get("REMIND_LAG", 5)), doc_eos=self.corpus.eos,
+                                    dmin=int(env.get("REMIND_DMIN", 0)), synth=int(env.get("REMIND_SYNTH", 0)),
+                                    near=float(env.get("REMIND_NEAR", 0.0)), near_max=int(env.get("REMIND_NEAR_MAX", 0)),
+                                    blank=env.get("REMIND_BLANK") == "1", per_row=int(env.get("REMIND_PER_ROW", 1)),
+                                    far_log=float(env["REMIND_FAR_LOG"]) if env.get("REMIND_FAR_LOG") else None)
 
     def _xform(self, xy, n):
         return self.remind(xy, n=n)

@@ -222,7 +222,7 @@ class _CorpusData:
                                     lag=int(env.get("REMIND_LAG", 5)), doc_eos=self.corpus.eos,
                                     dmin=int(env.get("REMIND_DMIN", 0)), synth=int(env.get("REMIND_SYNTH", 0)),
                                     near=float(env.get("REMIND_NEAR", 0.0)), near_max=int(env.get("REMIND_NEAR_MAX", 0)),
-                                    blank=env.get("REMIND_BLANK") == "1", per_row=int(env.get("REMIND_PER_ROW", 1)),
+                                    per_row=int(env.get("REMIND_PER_ROW", 1)),   # hidden answers need separate targets: not here
                                     far_log=float(env["REMIND_FAR_LOG"]) if env.get("REMIND_FAR_LOG") else None)
 
     def _xform(self, xy, n):

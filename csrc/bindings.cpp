@@ -4,7 +4,8 @@
 namespace mb {
 torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> out, c10::optional<torch::Tensor> out2,
                    c10::optional<torch::Tensor> aux, bool a_mn, bool b_mn, bool accumulate, int64_t epi, bool out_f32,
-                   int64_t groups);
+                   int64_t groups, c10::optional<torch::Tensor> counts, int64_t count_mode);
+void gemm_set_debug(int64_t dbg, int64_t group_m);
 int gemm_status(int device);
 torch::Tensor gemm_peer(std::vector<int64_t> a_ptrs, int64_t seg_M, int64_t K, int64_t a_groups, int64_t a_pitch,
                         int64_t a_gs, int64_t a_g_off, torch::Tensor b, bool b_mn, c10::optional<torch::Tensor> out_local,
@@ -14,9 +15,7 @@ void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel,
 int64_t peer_status_read();
 void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,
                     int64_t numel, bool is_bf16, int64_t rank, double scale);
-void gemm_set_desc_override(std::vector<int64_t> v);
 void gemm_set_pair(bool on);
-void gemm_set_profile(c10::optional<torch::Tensor> buf);
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps, bool out_bf16);
 std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor w, torch::Tensor rstd,
                                        c10::optional<torch::Tensor> add, bool want_lo);
@@ -58,9 +57,9 @@ torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Ten
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &mb::gemm, "tcgen05 GEMM C = A * B^T (bf16, fp32 accumulate in TMEM)");
   m.def("gemm_status", &mb::gemm_status, "read and clear the GEMM status word (0 = ok)");
+  m.def("gemm_set_debug", &mb::gemm_set_debug, "pair kernel: test / measurement bits and row-tile group size of the tile order",
+        pybind11::arg("dbg") = 0, pybind11::arg("group_m") = 0);
   m.def("gemm_set_pair", &mb::gemm_set_pair, "switch the CTA-pair (cta_group::2) GEMM kernel on or off");
-  m.def("gemm_set_profile", &mb::gemm_set_profile, "per-CTA cycle counters of the pair kernel roles (pass None to stop)");
-  m.def("gemm_set_desc_override", &mb::gemm_set_desc_override, "test hook: shared-memory descriptor geometry");
   m.def("gemm_peer", &mb::gemm_peer, "segmented GEMM: A tiles from peer buffers, result rows to the owners' buffers");
   m.def("peer_barrier", &mb::peer_barrier, "bounded device-side barrier over symmetric flags");
   m.def("peer_status_read", &mb::peer_status_read);

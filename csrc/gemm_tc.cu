@@ -35,15 +35,19 @@ struct GemmParams {
   int ldo, ldo2, ldaux;                // row pitches in elements
   int epi, out_f32, accumulate;
   int m_tiles, n_tiles;
-  long long* prof;           // optional: per-CTA cycle counters of the pair kernel's roles (8 int64 per CTA), or null
   int ntail;                 // 1: the last N tile issues MMAs only as wide as its valid columns (rounded up to 16)
-  uint32_t lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b;   // shared-memory descriptor geometry in bytes
   int* status;
   // M may be cut into `n_seg` segments of `seg_M` rows, each read through its own A tensor map (a peer GPU's
   // buffer) and, when `out_seg_on`, written to its own output base (the owner GPU's buffer).  Tiles never straddle
   // segments.  Plain GEMM: n_seg = 1, seg_M = M.
   int n_seg, seg_M, tiles_per_seg, a_g_off, out_g_off, out_seg_on;
   void* out_seg[8];
+  // Pair kernel v3 only.  store_tma: the epilogue leaves through TMA stores (local output, one segment); otherwise
+  // through coalesced row stores from the staged tile (peer buffers, segmented output).
+  // counts: valid extent per group (device ints) - count_mode 1: rows of A/out (tiles wholly past it are not
+  // computed and are written as zeros), 2: length of the contraction (k-blocks past it are not read).
+  int store_tma, count_mode, dbg, group_m;
+  const int* counts;
 };
 
 struct TmapSet { CUtensorMap m[8]; };
@@ -52,10 +56,11 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& g, 
   int per_g = p.m_tiles * p.n_tiles;
   g = t / per_g;
   int r = t - g * per_g;
-  int band = GROUP_M * p.n_tiles;
+  const int gm = p.group_m > 0 ? p.group_m : GROUP_M;
+  int band = gm * p.n_tiles;
   int b = r / band;
-  int first_m = b * GROUP_M;
-  int gsz = min(GROUP_M, p.m_tiles - first_m);
+  int first_m = b * gm;
+  int gsz = min(gm, p.m_tiles - first_m);
   int rr = r - b * band;
   mt = first_m + rr % gsz;
   nt = rr / gsz;
@@ -298,8 +303,8 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
           const uint32_t sB = sA + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t ad = smem_desc_sw128(sA + k * p.kstep_a, p.lbo_a, p.sbo_a);
-            uint64_t bd = smem_desc_sw128(sB + k * p.kstep_b, p.lbo_b, p.sbo_b);
+            uint64_t ad = smem_desc_sw128(sA + k * (A_MN ? UMMA_K * 128 : UMMA_K * 2), A_MN ? BK * 128 : 0, 1024);
+            uint64_t bd = smem_desc_sw128(sB + k * (B_MN ? UMMA_K * 128 : UMMA_K * 2), B_MN ? BK * 128 : 0, 1024);
             umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);              // the smem slot is free once these MMAs have read it
@@ -343,23 +348,312 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUt
 }
 
 // ------------------------------------------------------------------------------------------------ CTA-pair kernel
-// Same GEMM with tcgen05.mma.cta_group::2: a cluster of two CTAs (two SMs) computes a 256x256 tile.  Each CTA stages
-// its own 128 rows of A and its own 128-row half of the B tile, so every SM pulls 32 KB per k-block instead of
-// 48 KB for the same FLOPs; the leader CTA's single thread issues the MMAs for both, accumulators live in each
-// CTA's own TMEM (128 lanes x 256 columns, double-buffered), each CTA runs its own epilogue on its rows.
+// tcgen05.mma.cta_group::2: a cluster of two CTAs (two SMs) computes a 256x256 tile.  Each CTA stages its own 128
+// rows of A and its own 128-row half of the B tile, so every SM pulls 32 KB per k-block instead of 48 KB for the
+// same FLOPs; the leader CTA's single thread issues the MMAs for both, accumulators live in each CTA's own TMEM
+// (128 lanes x 256 columns, double-buffered), each CTA runs its own epilogue on its rows.
 // TMA loads carry no multicast: both CTAs fetch their own tiles; only the completion bytes are counted on the
 // leader's barrier, and tcgen05.commit arrives on the barriers of both CTAs.
-constexpr int STAGES2 = 6, BH_BYTES = 128 * BK * 2, STAGE2_BYTES = A_BYTES + BH_BYTES;
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr int BH_BYTES = 128 * BK * 2, STAGE2_BYTES = A_BYTES + BH_BYTES;
+// The epilogue leaves through shared memory: each epilogue warp packs its 32 rows x 64 bf16 (or 32 fp32) columns
+// into a 128-byte-swizzled 4 KB staging tile and one lane issues a TMA store (a TMA reduce-add for fp32
+// accumulation; for peer / segmented outputs the warp writes the staged rows itself as full 128-byte lines).
+// Shared-memory descriptors are built once and advanced by integer adds.  Per-group extents let padded expert rows
+// cost neither loads nor MMAs.
+constexpr int EPI_BUF_BYTES = 4096;
+// 5 operand stages leave room for 4 staging tiles per epilogue warp, 6 stages for 2
+constexpr int epi_nbuf(int stages) { return stages >= 6 ? 2 : 4; }
+constexpr int smem3_bytes(int stages) { return stages * STAGE2_BYTES + 4 * epi_nbuf(stages) * EPI_BUF_BYTES + 1024 + 256; }
+enum { DBG_NO_STORE = 2, DBG_DIRECT_STORE = 8, DBG_L2_HINTS = 16, DBG_SIX_STAGES = 32 };   // test / measurement switches
 
-template <bool A_MN, bool B_MN>
+// row `lane` of a staging tile, 16-byte piece j (the tile is 1024-byte aligned: TMA's 128B swizzle = piece ^ (row & 7))
+__device__ __forceinline__ uint4* stage_piece(uint8_t* buf, int row, int j) {
+  return reinterpret_cast<uint4*>(buf + row * 128 + ((j ^ (row & 7)) << 4));
+}
+// Warp-cooperative copy of a staged 32 x 128 B tile to global rows (4 rows x 128 B per instruction).
+__device__ __forceinline__ void coop_store(const uint8_t* buf, char* gbase, long long pitch_bytes, int rows_valid,
+                                           int pieces_valid, bool f32_acc, int lane) {
+  const int pc = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3);
+    if (r < rows_valid && pc < pieces_valid) {
+      uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((pc ^ (r & 7)) << 4));
+      uint4* dst = reinterpret_cast<uint4*>(gbase + r * pitch_bytes + pc * 16);
+      if (f32_acc) {
+        const float4 o = *reinterpret_cast<const float4*>(dst);
+        float4 n = *reinterpret_cast<float4*>(&v);
+        n.x += o.x; n.y += o.y; n.z += o.z; n.w += o.w;
+        v = *reinterpret_cast<uint4*>(&n);
+      }
+      *dst = v;
+    }
+  }
+}
+// Warp-cooperative load of a 32 x 128 B global tile into a staging tile (zero outside the valid part).
+__device__ __forceinline__ void coop_load(uint8_t* buf, const char* gbase, long long pitch_bytes, int rows_valid,
+                                          int pieces_valid, int lane) {
+  const int pc = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows_valid && pc < pieces_valid) v = *reinterpret_cast<const uint4*>(gbase + r * pitch_bytes + pc * 16);
+    *reinterpret_cast<uint4*>(buf + r * 128 + ((pc ^ (r & 7)) << 4)) = v;
+  }
+}
+
+// Per-warp staging ring of EPI_NBUF tiles, handed out in slots of `nb` tiles (nb = staged tiles per store group of
+// this launch: 1, 2 with a second output, 3 for SwiGLU with its pre-activations).  take(): wait until the slot about
+// to be written is no longer read by an earlier store group, return the index of its first tile.
+struct EpiRing {
+  uint8_t* base;
+  int next, nb, nbuf;
+  bool tma;
+  uint64_t store_policy;
+  bool hint;
+  __device__ __forceinline__ int take(int lane) {
+    if (tma && lane == 0) {
+      const int slots = nbuf / nb;                   // store groups that may still read their tiles: slots - 1
+      if (slots >= 4) bulk_wait_read<3>();
+      else if (slots == 2) bulk_wait_read<1>();
+      else bulk_wait_read<0>();
+    }
+    __syncwarp();
+    const int first = next;
+    next += nb;
+    if (next + nb > nbuf) next = 0;
+    return first;
+  }
+  __device__ __forceinline__ uint8_t* buf(int i) const { return base + i * EPI_BUF_BYTES; }
+};
+
+struct EpiOut {            // where one output of the tile goes
+  const CUtensorMap* tm;   // TMA path
+  char* base;              // direct path: address of (first row of this warp, column 0) of the right group / segment
+  long long pitch;         // bytes
+};
+
+// Send one staged tile: columns [col0, col0 + 64 bf16 | 32 fp32) of rows [row0, row0 + 32).
+__device__ __forceinline__ void epi_send(const GemmParams& p, const EpiRing& ring, int bi, const EpiOut& o, int col0, int row0,
+                                         int g, int rows_valid, int ncols, int esz, bool accumulate, int lane) {
+  if (p.dbg & DBG_NO_STORE) return;
+  if (ring.tma) {
+    if (lane == 0) {
+      if (accumulate) tma_reduce_add_3d(o.tm, ring.buf(bi), col0, row0, g);
+      else if (ring.hint) tma_store_3d_hint(o.tm, ring.buf(bi), col0, row0, g, ring.store_policy);
+      else tma_store_3d(o.tm, ring.buf(bi), col0, row0, g);
+    }
+  } else {
+    const int per = 16 / esz;                                  // elements per 16-byte piece
+    const int pieces = min(8, (ncols - col0 + per - 1) / per);
+    coop_store(ring.buf(bi), o.base + static_cast<long long>(col0) * esz, o.pitch, rows_valid, pieces, accumulate, lane);
+  }
+}
+
+// Drain this warp's 32 TMEM lanes x 256 columns of one accumulator through the fused epilogue.
+// row0 = first row of the warp in the local (M) problem, row0_l = the same inside its M-segment.
+__device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtensorMap* tmO, const CUtensorMap* tmO2, int g,
+                                               int seg, int row0, int row0_l, int nt, uint32_t taddr, EpiRing& ring, int lane,
+                                               bool zero_tile) {
+  const int rows_valid = max(0, min(32, p.seg_M - row0_l));
+  const int row = row0 + lane;
+  const int esz = p.out_f32 ? 4 : 2;
+  EpiOut o, o2;
+  o.tm = tmO; o2.tm = tmO2;
+  {
+    char* ob = reinterpret_cast<char*>(p.out_seg_on ? p.out_seg[seg] : p.out);
+    const long long orow = p.out_seg_on ? row0_l : row0;
+    o.base = ob + ((g + p.out_g_off) * p.out_gs + orow * p.ldo) * esz;
+    o.pitch = static_cast<long long>(p.ldo) * esz;
+    o2.base = reinterpret_cast<char*>(p.out2) + (g * p.out2_gs + static_cast<long long>(row0) * p.ldo2) * 2;
+    o2.pitch = static_cast<long long>(p.ldo2) * 2;
+  }
+  const int og = g + p.out_g_off;
+
+  if (zero_tile) {
+    // a tile of padding rows: no accumulator was produced; the outputs are zeros (an accumulating output stays)
+    if (p.accumulate) return;
+    const int bi = ring.take(lane);
+    *stage_piece(ring.buf(bi), lane, 0) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) *stage_piece(ring.buf(bi), lane, j) = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    __syncwarp();
+    if (p.epi == EPI_SWIGLU) {
+      const int H = p.N >> 1;
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = nt * 128 + c * 64;
+        if (col0 >= H) break;
+        epi_send(p, ring, bi, o, col0, row0, og, rows_valid, H, 2, false, lane);
+        if (p.out2) {
+          epi_send(p, ring, bi, o2, col0, row0, g, rows_valid, H, 2, false, lane);
+          epi_send(p, ring, bi, o2, H + col0, row0, g, rows_valid, p.N, 2, false, lane);
+        }
+      }
+    } else {
+      const int cw = p.out_f32 ? 32 : 64;
+      for (int c = 0; c < BN / cw; ++c) {
+        const int col0 = nt * BN + c * cw;
+        if (col0 >= p.N) break;
+        epi_send(p, ring, bi, o, col0, row0, og, rows_valid, p.N, esz, false, lane);
+        if (p.epi == EPI_RELU2) epi_send(p, ring, bi, o2, col0, row0, g, rows_valid, p.N, 2, false, lane);
+      }
+    }
+    if (ring.tma && lane == 0) bulk_commit();
+    return;
+  }
+
+  if (p.epi == EPI_SWIGLU) {
+    const int H = p.N >> 1;
+    const int nb = p.out2 ? 3 : 1;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      const int col0 = nt * 128 + c * 64;
+      if (col0 >= H) break;
+      const int bi = ring.take(lane);
+#pragma unroll 1
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t rg[32], ru[32];
+        tmem_ld32(taddr + c * 64 + hf * 32, rg);
+        tmem_ld32(taddr + 128 + c * 64 + hf * 32, ru);
+        tmem_ld_wait();
+        uint32_t ph[16], pg[16], pu[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float g0 = __uint_as_float(rg[2 * j]), g1 = __uint_as_float(rg[2 * j + 1]);
+          const float u0 = __uint_as_float(ru[2 * j]), u1 = __uint_as_float(ru[2 * j + 1]);
+          pg[j] = pack_bf16(g0, g1);
+          pu[j] = pack_bf16(u0, u1);
+          // activations of the stored (rounded) values, so forward and the recomputing backward agree
+          const float2 gr = unpack_bf16(pg[j]), ur = unpack_bf16(pu[j]);
+          ph[j] = pack_bf16(silu_f(gr.x) * ur.x, silu_f(gr.y) * ur.y);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          *stage_piece(ring.buf(bi), lane, hf * 4 + j) = make_uint4(ph[4 * j], ph[4 * j + 1], ph[4 * j + 2], ph[4 * j + 3]);
+          if (nb == 3) {
+            *stage_piece(ring.buf(bi + 1), lane, hf * 4 + j) = make_uint4(pg[4 * j], pg[4 * j + 1], pg[4 * j + 2], pg[4 * j + 3]);
+            *stage_piece(ring.buf(bi + 2), lane, hf * 4 + j) = make_uint4(pu[4 * j], pu[4 * j + 1], pu[4 * j + 2], pu[4 * j + 3]);
+          }
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      epi_send(p, ring, bi, o, col0, row0, og, rows_valid, H, 2, false, lane);
+      if (nb == 3) {
+        epi_send(p, ring, bi + 1, o2, col0, row0, g, rows_valid, H, 2, false, lane);
+        epi_send(p, ring, bi + 2, o2, H + col0, row0, g, rows_valid, p.N, 2, false, lane);
+      }
+      if (ring.tma && lane == 0) bulk_commit();
+    }
+    return;
+  }
+
+  if (p.out_f32) {
+    // fp32 output (weight gradients): 32 columns per staged tile
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col0 = nt * BN + c * 32;
+      if (col0 >= p.N) break;
+      uint32_t r[32];
+      tmem_ld32(taddr + c * 32, r);
+      tmem_ld_wait();
+      float sc = 1.f;
+      if (p.epi == EPI_ROWSCALE) sc = row0_l + lane < p.seg_M ? reinterpret_cast<const float*>(p.aux)[g * p.aux_gs + row] : 0.f;
+      const int bi = ring.take(lane);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *stage_piece(ring.buf(bi), lane, j) =
+            make_uint4(__float_as_uint(__uint_as_float(r[4 * j]) * sc), __float_as_uint(__uint_as_float(r[4 * j + 1]) * sc),
+                       __float_as_uint(__uint_as_float(r[4 * j + 2]) * sc), __float_as_uint(__uint_as_float(r[4 * j + 3]) * sc));
+      fence_async_smem();
+      __syncwarp();
+      epi_send(p, ring, bi, o, col0, row0, og, rows_valid, p.N, 4, p.accumulate != 0, lane);
+      if (ring.tma && lane == 0) bulk_commit();
+    }
+    return;
+  }
+
+  // bf16 output, 64 columns per staged tile
+  const int nb = p.epi == EPI_RELU2 ? 2 : 1;
+#pragma unroll 1
+  for (int c = 0; c < BN / 64; ++c) {
+    const int col0 = nt * BN + c * 64;
+    if (col0 >= p.N) break;
+    uint32_t r[64];
+    tmem_ld32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+    tmem_ld32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+    tmem_ld_wait();
+    const int bi = ring.take(lane);
+    uint8_t* b0 = ring.buf(bi);
+    if (p.epi == EPI_RELU2) {
+      uint8_t* b1 = ring.buf(bi + 1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t pa[4], ph[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          pa[q] = pack_bf16(__uint_as_float(r[8 * j + 2 * q]), __uint_as_float(r[8 * j + 2 * q + 1]));
+          float2 a = unpack_bf16(pa[q]);                      // activation of the stored (rounded) value
+          a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f);
+          ph[q] = pack_bf16(a.x * a.x, a.y * a.y);
+        }
+        *stage_piece(b0, lane, j) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+        *stage_piece(b1, lane, j) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+      }
+    } else if (p.epi == EPI_DRELU2) {
+      const char* ab = reinterpret_cast<const char*>(p.aux) + (g * p.aux_gs + static_cast<long long>(row0) * p.ldaux + col0) * 2;
+      coop_load(b0, ab, static_cast<long long>(p.ldaux) * 2, rows_valid, min(8, (p.N - col0 + 7) >> 3), lane);
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4* pp = stage_piece(b0, lane, j);
+        const uint4 u = *pp;
+        const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
+        *pp = make_uint4(pack_bf16(__uint_as_float(r[8 * j + 0]) * 2.f * fmaxf(f0.x, 0.f), __uint_as_float(r[8 * j + 1]) * 2.f * fmaxf(f0.y, 0.f)),
+                         pack_bf16(__uint_as_float(r[8 * j + 2]) * 2.f * fmaxf(f1.x, 0.f), __uint_as_float(r[8 * j + 3]) * 2.f * fmaxf(f1.y, 0.f)),
+                         pack_bf16(__uint_as_float(r[8 * j + 4]) * 2.f * fmaxf(f2.x, 0.f), __uint_as_float(r[8 * j + 5]) * 2.f * fmaxf(f2.y, 0.f)),
+                         pack_bf16(__uint_as_float(r[8 * j + 6]) * 2.f * fmaxf(f3.x, 0.f), __uint_as_float(r[8 * j + 7]) * 2.f * fmaxf(f3.y, 0.f)));
+      }
+    } else {
+      float sc = 1.f;
+      if (p.epi == EPI_ROWSCALE) sc = row0_l + lane < p.seg_M ? reinterpret_cast<const float*>(p.aux)[g * p.aux_gs + row] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *stage_piece(b0, lane, j) = make_uint4(pack_bf16(__uint_as_float(r[8 * j]) * sc, __uint_as_float(r[8 * j + 1]) * sc),
+                                               pack_bf16(__uint_as_float(r[8 * j + 2]) * sc, __uint_as_float(r[8 * j + 3]) * sc),
+                                               pack_bf16(__uint_as_float(r[8 * j + 4]) * sc, __uint_as_float(r[8 * j + 5]) * sc),
+                                               pack_bf16(__uint_as_float(r[8 * j + 6]) * sc, __uint_as_float(r[8 * j + 7]) * sc));
+    }
+    fence_async_smem();
+    __syncwarp();
+    epi_send(p, ring, bi, o, col0, row0, og, rows_valid, p.N, 2, false, lane);
+    if (nb == 2) epi_send(p, ring, bi + 1, o2, col0, row0, g, rows_valid, p.N, 2, false, lane);
+    if (ring.tma && lane == 0) bulk_commit();
+  }
+}
+
+// extent of group g under count_mode (rows for mode 1, contraction length for mode 2), else the full extent
+__device__ __forceinline__ int group_rows(const GemmParams& p, int g) {
+  return p.count_mode == 1 ? min(p.M, __ldg(p.counts + g)) : p.M;
+}
+__device__ __forceinline__ int group_kblocks(const GemmParams& p, int g) {
+  const int k = p.count_mode == 2 ? min(p.K, __ldg(p.counts + g)) : p.K;
+  return (k + BK - 1) / BK;
+}
+
+template <bool A_MN, bool B_MN, int STAGES3>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmO2, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
-  uint64_t* empty = full + STAGES2;
-  uint64_t* tfull = empty + STAGES2;
+  uint8_t* epi_smem = smem + STAGES3 * STAGE2_BYTES;
+  constexpr int EPI_NBUF = epi_nbuf(STAGES3);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_smem + 4 * EPI_NBUF * EPI_BUF_BYTES);
+  uint64_t* empty = full + STAGES3;
+  uint64_t* tfull = empty + STAGES3;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -368,16 +662,16 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int num_kb = (p.K + BK - 1) / BK;
   const int total = p.G * p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < STAGES3; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
     *abort_flag = 0;
     mbar_fence_init();
     for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tmAs.m[i]);
     tma_prefetch_desc(&tmB);
+    if (p.store_tma) { tma_prefetch_desc(&tmO); if (p.out2) tma_prefetch_desc(&tmO2); }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -395,20 +689,22 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      long long prof_wait = 0;
       for (int t = pair; t < total && ok; t += npairs) {
         int g, mt, nt;
         tile_coords(t, p, g, mt, nt);
         const int seg = mt / p.tiles_per_seg;
-        const int m0 = (mt - seg * p.tiles_per_seg) * 256 + (int)rank * BM;
+        const int mseg0 = (mt - seg * p.tiles_per_seg) * 256;
+        if (seg * p.seg_M + mseg0 >= group_rows(p, g)) continue;            // a tile of padding rows
+        const int m0 = mseg0 + (int)rank * BM;
         const CUtensorMap* tA = &tmAs.m[seg];
         const int ga = g + p.a_g_off;
+        const int num_kb = group_kblocks(p, g);
+        const int nb = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt * 128 : (p.N >> 1) + nt * 128)
+                                             : nt * BN + (int)rank * (tile_n_eff(p, nt) >> 1);
         for (int kb = 0; kb < num_kb; ++kb) {
-          const long long tw0 = p.prof ? clock64() : 0;
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+          if (!mbar_try_wait(&empty[stage], phase ^ 1) && !mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
           }
-          if (p.prof) prof_wait += clock64() - tw0;                        // producer: waiting for a free stage
           uint8_t* sA = smem + stage * STAGE2_BYTES;
           uint8_t* sB = sA + A_BYTES;
           const uint32_t lfull = mapa_shared(smem_u32(&full[stage]), 0);      // the leader's barrier
@@ -420,70 +716,79 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
             tma_load_3d_pair(sA, tA, lfull, m0, k0, ga);
             tma_load_3d_pair(sA + 8192, tA, lfull, m0 + 64, k0, ga);
           }
-          // this CTA's half of the B tile: N rows [nb, nb + 128)
-          // (a narrowed last tile splits its n_eff columns between the two CTAs: the second half starts at n_eff / 2)
-          const int nb = (p.epi == EPI_SWIGLU) ? (rank == 0 ? nt * 128 : (p.N >> 1) + nt * 128)
-                                               : nt * BN + (int)rank * (tile_n_eff(p, nt) >> 1);
           if (!B_MN) {
             tma_load_3d_pair(sB, &tmB, lfull, k0, nb, g);
           } else {
             tma_load_3d_pair(sB, &tmB, lfull, nb, k0, g);
             tma_load_3d_pair(sB + 8192, &tmB, lfull, nb + 64, k0, g);
           }
-          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+          if (++stage == STAGES3) { stage = 0; phase ^= 1; }
         }
       }
-      if (p.prof) p.prof[blockIdx.x * 8 + 5] = prof_wait;
       if (!ok) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    // This one thread is the pacemaker of both SMs: whatever it executes between two MMAs shows up as an idle
+    // tensor pipe.  So the loop holds everything in registers, looks at the next stage's barrier before it issues
+    // the current stage's MMAs (the look-up's latency then overlaps their execution), and works out the next
+    // tile's coordinates while the first k-block of the current one runs.
     if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      const long long t_all0 = p.prof ? clock64() : 0;
-      long long prof_acc = 0, prof_full = 0, prof_tiles = 0;
-      for (int t = pair; t < total && ok; t += npairs) {
+      constexpr uint32_t KSTEP_A = (A_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4, KSTEP_B = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+      constexpr uint32_t STAGE_STEP = STAGE2_BYTES >> 4;
+      const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem), A_MN ? BK * 128 : 0, 1024);
+      const uint64_t bdesc0 = smem_desc_sw128(smem_u32(smem) + A_BYTES, B_MN ? BK * 128 : 0, 1024);
+      uint32_t soff = 0;                                                   // stage * STAGE_STEP
+      // (k-blocks, instruction descriptor) of tile t; 0 k-blocks = nothing to issue (padding rows, empty contraction)
+      auto tile_info = [&](int t, int& nkb, uint32_t& idesc) {
+        nkb = 0; idesc = 0;
+        if (t >= total) return;
         int g_, mt_, nt_;
         tile_coords(t, p, g_, mt_, nt_);
-        const uint32_t idesc = idesc_bf16(256, tile_n_eff(p, nt_), A_MN ? 1u : 0u, B_MN ? 1u : 0u);
-        const long long tm0 = p.prof ? clock64() : 0;
-        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+        const int seg = mt_ / p.tiles_per_seg;
+        if (seg * p.seg_M + (mt_ - seg * p.tiles_per_seg) * 256 >= group_rows(p, g_)) return;
+        nkb = group_kblocks(p, g_);
+        idesc = idesc_bf16(256, tile_n_eff(p, nt_), A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      };
+      int num_kb, nxt_kb = 0;
+      uint32_t idesc, nxt_idesc = 0;
+      tile_info(pair, num_kb, idesc);
+      for (int t = pair; t < total && ok; t += npairs) {
+        if (num_kb == 0) { tile_info(t + npairs, num_kb, idesc); continue; }
+        if (!mbar_try_wait(&tempty[acc], acc_phase ^ 1) && !mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
         }
-        if (p.prof) { prof_acc += clock64() - tm0; prof_tiles += 1; }      // MMA: accumulator not free
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ready = mbar_try_wait(&full[stage], phase);
         for (int kb = 0; kb < num_kb; ++kb) {
-          const long long tf0 = p.prof ? clock64() : 0;
-          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+          if (!ready && !mbar_wait(&full[stage], phase, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_FULL); *abort_flag = 1; ok = false; break;
           }
-          if (p.prof) prof_full += clock64() - tf0;                        // MMA: operands not there yet
           tc_fence_after();
-          const uint32_t sA = smem_u32(smem + stage * STAGE2_BYTES);
-          const uint32_t sB = sA + A_BYTES;
+          int ns = stage + 1;
+          uint32_t nph = phase, nsoff = soff + STAGE_STEP;
+          if (ns == STAGES3) { ns = 0; nph ^= 1; nsoff = 0; }
+          ready = mbar_try_wait(&full[ns], nph);                           // the next k-block (of this or the next tile)
+          const uint64_t ad = adesc0 + soff, bd = bdesc0 + soff;
+          umma_bf16_pair(d_tmem, ad, bd, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t ad = smem_desc_sw128(sA + k * p.kstep_a, p.lbo_a, p.sbo_a);
-            uint64_t bd = smem_desc_sw128(sB + k * p.kstep_b, p.lbo_b, p.sbo_b);
-            umma_bf16_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 1; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, ad + k * KSTEP_A, bd + k * KSTEP_B, idesc, 1u);
           umma_commit_pair(&empty[stage], 3);       // frees this stage in both CTAs
-          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+          if (kb == 0) tile_info(t + npairs, nxt_kb, nxt_idesc);
+          stage = ns; phase = nph; soff = nsoff;
         }
         if (!ok) break;
         umma_commit_pair(&tfull[acc], 3);           // accumulators of both CTAs complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-      }
-      if (p.prof) {
-        p.prof[blockIdx.x * 8 + 0] = clock64() - t_all0;                  // MMA thread: whole tile loop
-        p.prof[blockIdx.x * 8 + 1] = prof_acc; p.prof[blockIdx.x * 8 + 2] = prof_full; p.prof[blockIdx.x * 8 + 3] = prof_tiles;
+        num_kb = nxt_kb; idesc = nxt_idesc;
       }
     }
   } else {
@@ -492,30 +797,39 @@ gemm_tc2_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CU
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    long long prof_e_wait = 0, prof_e_work = 0;
+    EpiRing ring;
+    ring.base = epi_smem + q * (EPI_NBUF * EPI_BUF_BYTES);
+    ring.next = 0;
+    ring.nbuf = EPI_NBUF;
+    ring.hint = (p.dbg & DBG_L2_HINTS) != 0;
+    ring.store_policy = l2_policy_evict_first();
+    ring.nb = p.epi == EPI_RELU2 ? 2 : (p.epi == EPI_SWIGLU && p.out2 ? 3 : 1);
+    ring.tma = p.store_tma != 0;
     for (int t = pair; t < total && ok; t += npairs) {
       int g, mt, nt;
       tile_coords(t, p, g, mt, nt);
-      const long long te0 = (p.prof && warp == 2 && lane == 0) ? clock64() : 0;
-      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
-        if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_TMEM_FULL); *abort_flag = 1; }
-        ok = false; break;
-      }
-      const long long te1 = (p.prof && warp == 2 && lane == 0) ? clock64() : 0;
-      tc_fence_after();
       const int seg = mt / p.tiles_per_seg;
-      const int row_l = (mt - seg * p.tiles_per_seg) * 256 + (int)rank * BM + q * 32 + lane;
-      epilogue_tile(p, g, seg, row_l, nt, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN);
-      tc_fence_before();
-      __syncwarp();
-      if (p.prof && warp == 2 && lane == 0) {
-        prof_e_wait += te1 - te0;                                         // epilogue: waiting for the accumulator
-        prof_e_work += clock64() - te1;                                   // epilogue: draining it
+      const int mseg0 = (mt - seg * p.tiles_per_seg) * 256;
+      const int row0_l = mseg0 + (int)rank * BM + q * 32;
+      const int row0 = seg * p.seg_M + row0_l;
+      const bool zero_tile = seg * p.seg_M + mseg0 >= group_rows(p, g) || group_kblocks(p, g) == 0;
+      if (!zero_tile) {
+        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+          if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_TMEM_FULL); *abort_flag = 1; }
+          ok = false; break;
+        }
+        tc_fence_after();
       }
-      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));   // the leader's MMA thread waits on it
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      epilogue_tile3(p, &tmO, &tmO2, g, seg, row0, row0_l, nt, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, ring,
+                     lane, zero_tile);
+      if (!zero_tile) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));   // the leader's MMA thread waits on it
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
     }
-    if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 8 + 6] = prof_e_wait; p.prof[blockIdx.x * 8 + 7] = prof_e_work; }
+    if (ring.tma && lane == 0) bulk_wait_all<0>();           // staged tiles must be read before the CTA's smem goes away
   }
 
   tc_fence_before();
@@ -543,25 +857,31 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 3-D bf16 tensor map: dims (inner, rows, groups), 128-byte swizzle, zero fill outside.
-CUtensorMap make_tmap_bf16(const void* base, uint64_t inner, uint64_t rows, uint64_t groups, uint64_t row_pitch_el,
-                           uint64_t group_pitch_el, uint32_t box_inner, uint32_t box_rows) {
+// 3-D tensor map: dims (inner, rows, groups), 128-byte swizzle, zero fill outside.  `esz` 2 = bf16, 4 = fp32.
+CUtensorMap make_tmap(const void* base, int esz, uint64_t inner, uint64_t rows, uint64_t groups, uint64_t row_pitch_el,
+                      uint64_t group_pitch_el, uint32_t box_inner, uint32_t box_rows, bool promote) {
   // cuTensorMapEncodeTiled is a driver call: a thread that has made no runtime call yet (an autograd worker) has no
   // current context and gets CUDA_ERROR_INVALID_CONTEXT, so bind the primary context once per thread.
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   CUtensorMap m;
   cuuint64_t dims[3] = {inner, rows, groups};
-  cuuint64_t strides[2] = {row_pitch_el * 2, (groups > 1 ? group_pitch_el : row_pitch_el * rows) * 2};
+  cuuint64_t strides[2] = {row_pitch_el * esz, (groups > 1 ? group_pitch_el : row_pitch_el * rows) * esz};
   cuuint32_t box[3] = {box_inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA operand must be 16-byte aligned");
   TORCH_CHECK(strides[0] % 16 == 0 && strides[1] % 16 == 0, "TMA operand pitches must be multiples of 16 bytes");
-  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = encode_fn()(&m, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                           const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B,
+                           promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", static_cast<int>(r));
   return m;
+}
+CUtensorMap make_tmap_bf16(const void* base, uint64_t inner, uint64_t rows, uint64_t groups, uint64_t row_pitch_el,
+                           uint64_t group_pitch_el, uint32_t box_inner, uint32_t box_rows) {
+  return make_tmap(base, 2, inner, rows, groups, row_pitch_el, group_pitch_el, box_inner, box_rows, true);
 }
 
 static int* status_word(int device) {
@@ -593,21 +913,9 @@ static bool use_pair_kernel() {
   return g_pair == 1;
 }
 void gemm_set_pair(bool on) { g_pair = on ? 1 : 0; }
-
-static long long* g_prof = nullptr;
-void gemm_set_profile(c10::optional<torch::Tensor> buf) {
-  if (buf.has_value() && buf->defined()) {
-    TORCH_CHECK(buf->is_cuda() && buf->scalar_type() == torch::kInt64 && buf->numel() >= 148 * 8 && buf->is_contiguous(),
-                "gemm_set_profile: int64 CUDA tensor of at least 148*8 elements");
-    g_prof = reinterpret_cast<long long*>(buf->data_ptr<int64_t>());
-  } else {
-    g_prof = nullptr;
-  }
-}
-static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};   // test hook: lbo_a, sbo_a, kstep_a, lbo_b, sbo_b, kstep_b
-void gemm_set_desc_override(std::vector<int64_t> v) {
-  for (int i = 0; i < 6; ++i) g_desc_override[i] = i < (int)v.size() ? (int)v[i] : -1;
-}
+// Test / measurement switches of the pair kernel (DBG_* bits) and the row-tile group size of its tile order.
+static int g_dbg = 0, g_group_m = 0;
+void gemm_set_debug(int64_t dbg, int64_t group_m) { g_dbg = (int)dbg; g_group_m = (int)group_m; }
 
 // Raw launcher shared by the torch binding and the fused multi-GPU paths (which pass peer pointers for A).
 // A_list: one base pointer per M-segment (n_seg of them, each (a_groups, seg_M, K) or MN-major (a_groups, K, seg_M)).
@@ -629,34 +937,57 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
                          : make_tmap_bf16(B, K, N, G, b_rows_pitch, b_gs, 64, (sw || pair) ? 128 : BN);
   p.m_tiles = n_seg * p.tiles_per_seg;
   p.n_tiles = sw ? ((N / 2) + 127) / 128 : (N + BN - 1) / BN;
-  p.lbo_a = a_mn ? BK * 128 : 0;  p.sbo_a = 1024;  p.kstep_a = a_mn ? UMMA_K * 128 : UMMA_K * 2;
-  p.lbo_b = b_mn ? BK * 128 : 0;  p.sbo_b = 1024;  p.kstep_b = b_mn ? UMMA_K * 128 : UMMA_K * 2;
-  if (g_desc_override[0] >= 0) {
-    p.lbo_a = g_desc_override[0]; p.sbo_a = g_desc_override[1]; p.kstep_a = g_desc_override[2];
-    p.lbo_b = g_desc_override[3]; p.sbo_b = g_desc_override[4]; p.kstep_b = g_desc_override[5];
-  }
   static const bool ntail_on = []() { const char* e = std::getenv("MEMARCH_GEMM_NTAIL"); return !(e && e[0] == '0'); }();
   p.ntail = ntail_on ? 1 : 0;
-  p.prof = g_prof;
   const int total = G * p.m_tiles * p.n_tiles;
   int grid = pair ? 2 * std::min(total, max_ctas / 2) : std::min(total, max_ctas);
   if (grid <= 0) return;
-  const int smem_bytes = pair ? SMEM2_BYTES : SMEM_BYTES;
+  const bool v3 = pair;
+  TORCH_CHECK(v3 || p.count_mode == 0, "gemm: per-group extents need the pair kernel (>= 256 rows)");
+  const bool six = v3 && (g_dbg & DBG_SIX_STAGES) && !(p.epi == EPI_SWIGLU && p.out2);
+  const int smem_bytes = v3 ? smem3_bytes(six ? 6 : 5) : SMEM_BYTES;
+  CUtensorMap tmO = tmB, tmO2 = tmB;
+  if (v3) {
+    p.dbg = g_dbg;
+    p.group_m = g_group_m;
+    const int esz = p.out_f32 ? 4 : 2;
+    // TMA stores for a local, unsegmented output whose pitches keep the 16-byte rule; everything else leaves
+    // through coalesced row stores (peer buffers are only ever written with plain stores)
+    p.store_tma = (n_seg == 1 && !p.out_seg_on && (p.ldo * esz) % 16 == 0 && (G == 1 || (p.out_gs * esz) % 16 == 0) &&
+                   (!p.out2 || ((p.ldo2 * 2) % 16 == 0 && (G == 1 || (p.out2_gs * 2) % 16 == 0)))) ? 1 : 0;
+    static const bool tma_off = []() { const char* e = std::getenv("MEMARCH_GEMM_TMA_STORE"); return e && e[0] == '0'; }();
+    if (tma_off || (g_dbg & DBG_DIRECT_STORE)) p.store_tma = 0;
+    if (p.store_tma) {
+      const int No = sw ? N / 2 : N;
+      tmO = make_tmap(p.out, esz, No, p.M, G, p.ldo, p.out_gs, p.out_f32 ? 32 : 64, 32, false);
+      if (p.out2) tmO2 = make_tmap(p.out2, 2, N, p.M, G, p.ldo2, p.out2_gs, 64, 32, false);
+    }
+  }
   auto launch = [&](auto kern, int id) {
-    static bool attr_set[8] = {false, false, false, false, false, false, false, false};
-    if (!attr_set[id]) {
+    static bool attr_set[16][16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 15][id]) {
       TORCH_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) == cudaSuccess,
                   "cannot raise dynamic shared memory for the GEMM kernel");
-      attr_set[id] = true;
+      attr_set[dev & 15][id] = true;
     }
-    kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, p);
+    if constexpr (std::is_invocable_v<decltype(kern), TmapSet, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams>)
+      kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, tmO, tmO2, p);
+    else
+      kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, p);
   };
   const int id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
-  if (pair) {
-    if (!a_mn && !b_mn) launch(gemm_tc2_kernel<false, false>, 4 + id);
-    else if (!a_mn && b_mn) launch(gemm_tc2_kernel<false, true>, 4 + id);
-    else if (a_mn && !b_mn) launch(gemm_tc2_kernel<true, false>, 4 + id);
-    else launch(gemm_tc2_kernel<true, true>, 4 + id);
+  if (v3 && six) {
+    if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 6>, 12 + id);
+    else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 6>, 12 + id);
+    else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 6>, 12 + id);
+    else launch(gemm_pair_kernel<true, true, 6>, 12 + id);
+  } else if (v3) {
+    if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 5>, 8 + id);
+    else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 5>, 8 + id);
+    else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 5>, 8 + id);
+    else launch(gemm_pair_kernel<true, true, 5>, 8 + id);
   } else {
     if (!a_mn && !b_mn) launch(gemm_tc_kernel<false, false>, id);
     else if (!a_mn && b_mn) launch(gemm_tc_kernel<false, true>, id);
@@ -685,7 +1016,8 @@ static int sm_count() {
 // torch binding.  a: (G?, M, K) or MN-major (G?, K, M); b: (G?, N, K) or MN-major (G?, K, N).
 torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> out_,
                    c10::optional<torch::Tensor> out2_, c10::optional<torch::Tensor> aux_, bool a_mn, bool b_mn,
-                   bool accumulate, int64_t epi, bool out_f32, int64_t groups) {
+                   bool accumulate, int64_t epi, bool out_f32, int64_t groups, c10::optional<torch::Tensor> counts_,
+                   int64_t count_mode) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm: CUDA tensors expected");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "gemm: bf16 operands");
   const c10::cuda::CUDAGuard guard(a.device());
@@ -735,6 +1067,14 @@ torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor
     }
   }
   TORCH_CHECK((epi != EPI_DRELU2 && epi != EPI_ROWSCALE) || p.aux != nullptr, "gemm: epilogue needs aux");
+  if (counts_.has_value() && counts_->defined() && count_mode != 0) {
+    TORCH_CHECK(counts_->is_cuda() && counts_->scalar_type() == torch::kInt32 && counts_->is_contiguous() &&
+                counts_->numel() >= G, "gemm: counts must be a contiguous int32 CUDA tensor with one entry per group");
+    TORCH_CHECK(count_mode == 1 || count_mode == 2, "gemm: count_mode 1 (rows) or 2 (contraction length)");
+    p.counts = counts_->data_ptr<int>(); p.count_mode = (int)count_mode;
+  }
+  TORCH_CHECK(epi != EPI_SWIGLU || (!out_f32 && N % 16 == 0),
+              "gemm: the SwiGLU epilogue writes bf16 and needs column halves of a multiple of 8 (16-byte TMA coordinates)");
   p.status = status_word(a.get_device());
   launch_gemm(A.data_ptr(), A.stride(1), G > 1 ? A.stride(0) : 0, a_mn, B.data_ptr(), B.stride(1), G > 1 ? B.stride(0) : 0,
               b_mn, p, at::cuda::getCurrentCUDAStream(), sm_count());

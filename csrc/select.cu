@@ -98,8 +98,8 @@ std::vector<torch::Tensor> anchor_select(torch::Tensor s, torch::Tensor tau, int
 // Single block; per-chunk ranks by warp match + cross-warp prefix per expert; running per-expert base across chunks.
 constexpr int SLOT_MAX_E = 128;
 __global__ void moe_slots_kernel(const long long* __restrict__ e_flat, long long* __restrict__ table,
-                                 long long* __restrict__ flat_idx, float* __restrict__ dropped, long long NK, int k, int E, int C,
-                                 long long N) {
+                                 long long* __restrict__ flat_idx, float* __restrict__ dropped, int* __restrict__ counts,
+                                 long long NK, int k, int E, int C, long long N) {
   __shared__ int wcnt[32][SLOT_MAX_E];      // per-warp count of each expert in this chunk
   __shared__ int base[SLOT_MAX_E];
   __shared__ int placed_sh, kept_sh;
@@ -141,6 +141,7 @@ __global__ void moe_slots_kernel(const long long* __restrict__ e_flat, long long
     __syncthreads();
   }
   if (threadIdx.x == 0) *dropped = 1.f - (float)placed_sh / (float)max(kept_sh, 1);
+  for (int i = threadIdx.x; i < E; i += blockDim.x) counts[i] = min(base[i], C);      // filled places per expert
 }
 
 std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C) {
@@ -151,12 +152,13 @@ std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C)
   const int k = e_flat.size(1);
   auto table = torch::empty({E * C}, e_flat.options());
   auto flat_idx = torch::empty({N, k}, e_flat.options());
-  auto dropped = torch::zeros({}, e_flat.options().dtype(torch::kFloat32));
+  auto dropped = torch::empty({}, e_flat.options().dtype(torch::kFloat32));
+  auto counts = torch::empty({E}, e_flat.options().dtype(torch::kInt32));
   moe_slots_kernel<<<1, 1024, 0, cur_stream()>>>(reinterpret_cast<const long long*>(e_flat.data_ptr<int64_t>()),
       reinterpret_cast<long long*>(table.data_ptr<int64_t>()), reinterpret_cast<long long*>(flat_idx.data_ptr<int64_t>()),
-      dropped.data_ptr<float>(), N * k, k, (int)E, (int)C, N);
+      dropped.data_ptr<float>(), counts.data_ptr<int>(), N * k, k, (int)E, (int)C, N);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return {table, flat_idx, dropped};
+  return {table, flat_idx, dropped, counts};
 }
 
 // Router: softmax over E experts, top-k_max by probability (ties: smaller expert first), per-token budget k_tok,

@@ -116,9 +116,11 @@ class AnchorMoE(nn.Module):
             k_tok = torch.full((N,), self.k_avg, device=x.device, dtype=torch.long)
         k_tok = k_tok * real
         C = self.capacity(N)
-        w, table, wtab, flat_idx, aux, dropped, _ = ops.route_and_slot(
-            xf, self.router.weight.float() if not x.is_cuda else self.router.weight, real, k_tok, self.k_max, self.E, C)
+        w, table, wtab, flat_idx, aux, dropped, _, counts = ops.route_and_slot(
+            xf, self.router.weight.float() if not x.is_cuda else self.router.weight, real, k_tok, self.k_max, self.E, C,
+            want_counts=True)
         self.aux, self.dropped = aux, dropped
+        self._counts = counts                # filled places per expert (GPU): the expert GEMMs skip the padding
         return xf, table, wtab, flat_idx, C
 
     def forward(self, x, surprise=None):
@@ -134,9 +136,9 @@ class AnchorMoE(nn.Module):
         return ops.resid_add(x, out.view_as(x))
 
     # ------------------------------------------------------------------------------------------ experts
-    def _ffn(self, xe, up, down, train_w=True):
+    def _ffn(self, xe, up, down, train_w=True, counts=None):
         return ops.expert_ffn(xe, up.to(xe.dtype) if up.dtype != xe.dtype else up,
-                              down.to(xe.dtype) if down.dtype != xe.dtype else down, self.act, train_w)
+                              down.to(xe.dtype) if down.dtype != xe.dtype else down, self.act, train_w, counts)
 
     def _bank_weights(self, which):
         """Frozen weights in bf16 (expanded from int8 / int4 storage) (full2.py:948-958)."""
@@ -164,20 +166,23 @@ class AnchorMoE(nn.Module):
         q = ((q[:, 0::2] & 0x0F) | (q[:, 1::2] << 4)).to(torch.int8)
         return q.contiguous(), sc[:, :, 0].bfloat16().contiguous()
 
-    def _ffn_frozen(self, xe):
-        return self._ffn(xe, self._bank_weights("up"), self._bank_weights("down"), train_w=False)
+    def _ffn_frozen(self, xe, counts=None):
+        return self._ffn(xe, self._bank_weights("up"), self._bank_weights("down"), train_w=False, counts=counts)
 
     def _experts(self, xe, wtab, C):
+        cnt = getattr(self, "_counts", None)
+        sub = (lambda idx: cnt.index_select(0, idx)) if cnt is not None else (lambda idx: None)
         if self.ep_W > 1:
             ye = self.ep_engine.ffn(self, xe)
         elif self.bank:
             if not self.has_F:
-                ye = self._ffn(xe, self.up, self.down)
+                ye = self._ffn(xe, self.up, self.down, counts=cnt)
             else:
                 ye = xe.new_zeros(xe.shape)
                 if self.has_L:
-                    ye = ye.index_copy(0, self.L_idx, self._ffn(xe[self.L_idx], self.up, self.down).to(ye.dtype))
-                ye = ye.index_copy(0, self.F_idx, self._ffn_frozen(xe[self.F_idx]).to(ye.dtype))
+                    ye = ye.index_copy(0, self.L_idx, self._ffn(xe[self.L_idx], self.up, self.down,
+                                                                counts=sub(self.L_idx)).to(ye.dtype))
+                ye = ye.index_copy(0, self.F_idx, self._ffn_frozen(xe[self.F_idx], sub(self.F_idx)).to(ye.dtype))
         else:
             up, down = self.up, self.down
             if self.wave:
@@ -185,10 +190,11 @@ class AnchorMoE(nn.Module):
                 up, down = torch.where(fr, up.detach(), up), torch.where(fr, down.detach(), down)
             if self.n_frozen:
                 Ea = self.E - self.n_frozen
-                ye = torch.cat([self._ffn(xe[:Ea], up, down),
-                                self._ffn(xe[Ea:], self.up_f, self.down_f, train_w=False)])
+                ye = torch.cat([self._ffn(xe[:Ea], up, down, counts=cnt[:Ea].contiguous() if cnt is not None else None),
+                                self._ffn(xe[Ea:], self.up_f, self.down_f, train_w=False,
+                                          counts=cnt[Ea:].contiguous() if cnt is not None else None)])
             else:
-                ye = self._ffn(xe, up, down)
+                ye = self._ffn(xe, up, down, counts=cnt)
         if self.wave and self.training:
             ye = _ErrProbe.apply(ye, self.err)
             if not self.bank:

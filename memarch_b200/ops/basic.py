@@ -13,9 +13,10 @@ import torch.nn.functional as F
 
 from . import _ext, ref
 
-# Which library multiplies the *plain* linears (qkv/o/up/down of the light blocks).  The fused paths (experts,
-# output head, attention, optimizer) always run this package's kernels.  "tc" = our tcgen05 GEMM, "lib" = cuBLAS.
-PLAIN_GEMM = os.environ.get("MEMARCH_PLAIN_GEMM", "lib")
+# What multiplies the *plain* linears (qkv/o/up/down of the light blocks): "tc" = this package's tcgen05 GEMM (the
+# default), "lib" = cuBLAS (kept for A/B measurements).  The fused paths (experts, output head, attention,
+# optimizer) always run this package's kernels.
+PLAIN_GEMM = os.environ.get("MEMARCH_PLAIN_GEMM", "tc")
 
 
 # ------------------------------------------------------------------------------------------------ RMSNorm
@@ -151,7 +152,7 @@ def resid_add(x, y):
 
 # ------------------------------------------------------------------------------------------------ GEMM
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, accumulate=False, epi=0,
-         aux=None, out2=None, groups=1):
+         aux=None, out2=None, groups=1, counts=None, count_mode=0):
     """C[g] = A[g] · B[g]ᵀ on the tcgen05 tensor cores (bf16 in, fp32 accumulate in TMEM).
 
     Logical shapes per group: A (M,K), B (N,K), C (M,N).  Storage: an operand that is K-major is stored
@@ -159,11 +160,14 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, ac
     ("MN-major"), which is how a transposed view of a row-major matrix is fed without a transposing copy.
     `epi`: 0 plain, 1 relu² (out = relu(acc)², out2 = acc), 2 multiply by 2·relu(aux) (relu² backward),
     3 SwiGLU over column halves (B rows [n, H+n]), 4 per-row scale by aux (fp32 vector).
+    `counts` (int32, one per group) with `count_mode` 1: only the first counts[g] rows of A[g] hold data (the rest is
+    zero padding) - row tiles wholly past it are written as zeros without being computed; `count_mode` 2: only the
+    first counts[g] positions of the contraction hold data - the k-blocks past it are not read.
     """
     C = _ext.C()
     _ext.count()
     return C.gemm(a, b, out, out2, aux, bool(a_mn), bool(b_mn), bool(accumulate), int(epi),
-                  out_dtype == torch.float32, int(groups))
+                  out_dtype == torch.float32, int(groups), counts, int(count_mode) if counts is not None else 0)
 
 
 def gemm_ok(M, N, K):
@@ -189,6 +193,47 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = gemm(dy, x, a_mn=True, b_mn=True)
         return dx, dw
+
+
+class _LinearAct(torch.autograd.Function):
+    """h = act(x · Wᵀ) with the activation in the GEMM epilogue (SwiGLU over the column halves of W's output, or
+    relu²); the pre-activation is kept for the backward pass, which is one activation-backward kernel and the two
+    gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, w, swi):
+        M, N = x.shape[0], w.shape[0]
+        pre = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+        h = torch.empty(M, N // 2 if swi else N, device=x.device, dtype=torch.bfloat16)
+        gemm(x, w, out=h, out2=pre, epi=3 if swi else 1)
+        ctx.save_for_backward(x, w, pre)
+        ctx.swi = swi
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, w, pre = ctx.saved_tensors
+        C = _ext.C()
+        _ext.count()
+        dpre = C.swiglu_bwd(dh.contiguous(), pre) if ctx.swi else C.relu2_bwd(dh.contiguous(), pre)
+        dx = gemm(dpre, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = gemm(dpre, x, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def linear_act(x, w, act):
+    """act(x · Wᵀ), act in {"swiglu", "relu2"}: one GEMM with the activation fused on the GPU."""
+    if _ext.use_cuda(x) and PLAIN_GEMM == "tc":
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+        wd = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        M, K = x2.shape
+        N = wd.shape[0]
+        if gemm_ok(M, N, K) and M >= 128 and N % 16 == 0:
+            h = _LinearAct.apply(x2.contiguous(), wd.contiguous(), act == "swiglu")
+            return h.view(*x.shape[:-1], h.shape[-1])
+    y = linear(x, w)
+    return relu2(y) if act == "relu2" else swiglu(y)
 
 
 def linear(x, w, dtype=None):

@@ -89,52 +89,66 @@ def combine(ye, wtab, flat_idx, table, N):
 class _ExpertFFN(torch.autograd.Function):
     """(E,C,d) -> relu²/SwiGLU FFN -> (E,C,d) on grouped tcgen05 GEMMs, activation in the up-GEMM epilogue.
 
-    `train_w` False (frozen bank) skips both weight-gradient GEMMs.
+    `train_w` False (frozen bank) skips both weight-gradient GEMMs.  `counts` (int32, E): filled places per expert;
+    the places after them are zero rows, so the GEMMs skip their row tiles (forward, input gradients) and their
+    k-blocks (weight gradients) - the dropless form of the same arithmetic.
     """
 
     @staticmethod
-    def forward(ctx, xe, up, down, act, train_w):
+    def forward(ctx, xe, up, down, act, train_w, counts):
         E, Cn, d = xe.shape
         xe = xe.contiguous()
+        cm = 1 if counts is not None and Cn >= 256 else 0
+        kw = dict(groups=E, counts=counts if cm else None, count_mode=cm)
         if act == "relu2":
             H = up.shape[2]
             h = torch.empty(E, Cn, H, device=xe.device, dtype=torch.bfloat16)
             a = torch.empty_like(h)
-            gemm(xe, up, b_mn=True, out=h, out2=a, epi=1, groups=E)
+            gemm(xe, up, b_mn=True, out=h, out2=a, epi=1, **kw)
+        elif up.shape[2] % 16 == 0 and Cn >= 256:
+            H = up.shape[2] // 2
+            h = torch.empty(E, Cn, H, device=xe.device, dtype=torch.bfloat16)
+            a = torch.empty(E, Cn, 2 * H, device=xe.device, dtype=torch.bfloat16)
+            gemm(xe, up, b_mn=True, out=h, out2=a, epi=3, **kw)                # SwiGLU in the epilogue
         else:
-            a = gemm(xe, up, b_mn=True, groups=E)
+            a = gemm(xe, up, b_mn=True, **kw)
             h = _ext.C().swiglu_fwd(a)
             _ext.count()
-        y = gemm(h, down, b_mn=True, groups=E)
-        ctx.save_for_backward(xe, up, down, a, h)
+        y = gemm(h, down, b_mn=True, **kw)
+        ctx.save_for_backward(xe, up, down, a, h, counts if cm else None)
         ctx.act, ctx.train_w = act, train_w
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        xe, up, down, a, h = ctx.saved_tensors
+        xe, up, down, a, h, counts = ctx.saved_tensors
         E = xe.shape[0]
         dy = dy.contiguous()
+        cm = 1 if counts is not None else 0
+        kw = dict(groups=E, counts=counts, count_mode=cm)
         if ctx.act == "relu2":
-            da = gemm(dy, down, epi=2, aux=a, groups=E)                       # dh · 2relu(a)
+            da = gemm(dy, down, epi=2, aux=a, **kw)                            # dh · 2relu(a)
         else:
-            dh = gemm(dy, down, groups=E)
+            dh = gemm(dy, down, **kw)
             da = _ext.C().swiglu_bwd(dh, a)
             _ext.count()
-        dxe = gemm(da, up, groups=E) if ctx.needs_input_grad[0] else None
+        dxe = gemm(da, up, **kw) if ctx.needs_input_grad[0] else None
         dup = ddown = None
         if ctx.train_w:
-            ddown = gemm(h, dy, a_mn=True, b_mn=True, groups=E)
-            dup = gemm(xe, da, a_mn=True, b_mn=True, groups=E)
-        return dxe, dup, ddown, None, None
+            kw = dict(groups=E, counts=counts, count_mode=2 * cm)
+            # weight gradients contract over the places: the pair kernel needs >= 256 output rows (H, d)
+            ddown = gemm(h, dy, a_mn=True, b_mn=True, **(kw if h.shape[2] >= 256 else dict(groups=E)))
+            dup = gemm(xe, da, a_mn=True, b_mn=True, **(kw if xe.shape[2] >= 256 else dict(groups=E)))
+        return dxe, dup, ddown, None, None, None
 
 
-def expert_ffn(xe, up, down, act="swiglu", train_w=True):
-    """xe (E,C,d); up (E,d,H); down (E,H',d).  bf16 on the GPU; CPU: plain bmm in the input dtype."""
+def expert_ffn(xe, up, down, act="swiglu", train_w=True, counts=None):
+    """xe (E,C,d); up (E,d,H); down (E,H',d).  bf16 on the GPU; CPU: plain bmm in the input dtype.
+    `counts` (int32 per expert, optional): rows of xe[e] past counts[e] are zero padding and are not computed."""
     E, Cn, d = xe.shape
     if (_ext.use_cuda(xe) and xe.dtype == torch.bfloat16 and up.dtype == torch.bfloat16
             and gemm_ok(Cn if Cn % 8 == 0 else 8, up.shape[2], d) and down.shape[1] % 8 == 0):
-        return _ExpertFFN.apply(xe, up, down, act, train_w and up.requires_grad)
+        return _ExpertFFN.apply(xe, up, down, act, train_w and up.requires_grad, counts)
     h = torch.bmm(xe, up.to(xe.dtype))
     h = relu2(h) if act == "relu2" else swiglu(h)
     return torch.bmm(h, down.to(xe.dtype))
@@ -176,12 +190,14 @@ def moe_route(xf, router_w, real, k_tok, k_max, E):
     return ref.moe_route(xf, router_w, real, k_tok, k_max, E)
 
 
-def route_and_slot(xf, router_w, real, k_tok, k_max, E, C):
-    """Router + capacity slotting.  Returns (w (N,k), table, wtab, flat_idx, aux, dropped, probs)."""
+def route_and_slot(xf, router_w, real, k_tok, k_max, E, C, want_counts=False):
+    """Router + capacity slotting.  Returns (w (N,k), table, wtab, flat_idx, aux, dropped, probs) and, with
+    `want_counts`, the filled places per expert (int32 on the GPU, None on CPU) as an eighth value."""
     probs, top_e, keep, w, e_flat, aux = moe_route(xf, router_w, real, k_tok, k_max, E)
+    counts = None
     with torch.no_grad():
         if _ext.use_cuda(xf):
-            table, flat_idx, dropped = _ext.C().moe_slots(e_flat.contiguous(), int(E), int(C))
+            table, flat_idx, dropped, counts = _ext.C().moe_slots(e_flat.contiguous(), int(E), int(C))
             _ext.count()
         else:
             table, _, flat_idx, dropped = ref.moe_slots(e_flat, w.detach(), E, C)
@@ -189,4 +205,6 @@ def route_and_slot(xf, router_w, real, k_tok, k_max, E, C):
     # slot weights as a differentiable gather-free scatter: wtab[flat_idx[n,j]] = w[n,j]
     wtab = torch.zeros(E * C + 1, device=xf.device, dtype=w.dtype).scatter(
         0, flat_idx.reshape(-1), (w * ok).reshape(-1))[:-1]
+    if want_counts:
+        return w, table, wtab, flat_idx, aux, dropped, probs, counts
     return w, table, wtab, flat_idx, aux, dropped, probs

@@ -179,38 +179,104 @@ def cmd_attn(a):
     report("library fwd+bwd (flash, window arguments where windowed)", timeit(fb(lib_f), a.iters), 3.5 * flops)
 
 
-def cmd_roles(a):
-    """Where the CTA-pair GEMM spends its cycles: per-role wait counters written by the kernel itself."""
+class _Clocks:
+    """SM clock and board power sampled through NVML (read-only queries) on a thread while a loop runs."""
+
+    def __init__(self, index=0, every=0.02):
+        import threading
+        self.index, self.every, self.sm, self.pw = index, every, [], []
+        self._stop = threading.Event()
+        self._th = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            while not self._stop.is_set():
+                self.sm.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                self.pw.append(pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                self._stop.wait(self.every)
+        except Exception:    # noqa: BLE001 - no NVML: the sweep prints times only
+            pass
+
+    def __enter__(self):
+        self._th.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._th.join(timeout=2)
+
+    def summary(self):
+        if not self.sm:
+            return None, None
+        h = self.sm[len(self.sm) // 3:]            # drop the ramp
+        w = self.pw[len(self.pw) // 3:]
+        return sum(h) / len(h), sum(w) / len(w)
+
+
+def sustained(fn, seconds=0.6):
+    """Back-to-back launches for `seconds`; returns (ms per launch, mean SM MHz, mean W)."""
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+    n = max(8, int(seconds * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+    with _Clocks() as c:
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+    mhz, w = c.summary()
+    return e0.elapsed_time(e1) / n, mhz, w
+
+
+def cmd_sweep(a):
+    """The linears of the headline model and the square case, own pair kernel against the library GEMM: burst time
+    (L2 flushed), sustained time with the SM clock and power seen, and tensor-pipe share = achieved / (clock x 148 SMs
+    x 8192 FLOP per clock)."""
     from memarch_b200.ops import _ext, gemm
     C = _ext.C()
-    M, N, K, G = a.m, a.n, a.k, a.groups
-    A = torch.randn(G, M, K, device="cuda").bfloat16()
-    B = (torch.randn(G, K, N, device="cuda") if a.b_mn else torch.randn(G, N, K, device="cuda")).bfloat16()
-    out = torch.empty(G, M, N, device="cuda", dtype=torch.bfloat16)
-    out2 = torch.empty_like(out) if a.epi == 1 else None
-    run = lambda: gemm(A, B, b_mn=a.b_mn, out=out, out2=out2, epi=a.epi, groups=G)
-    for _ in range(3):
-        run()
-    buf = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
-    C.gemm_set_profile(buf)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    run()
-    e1.record()
-    torch.cuda.synchronize()
-    C.gemm_set_profile(None)
-    v = buf.view(148, 8).double()
-    lead = v[0::2]                                   # leader CTAs carry the MMA counters
-    tiles = lead[:, 3].mean().item()
-    tot = lead[:, 0].mean().item()
-    kb = (K + 63) // 64
-    print(f"pair GEMM G{G} M{M} N{N} K{K} epi{a.epi}: {e0.elapsed_time(e1):.3f} ms, {tiles:.1f} tiles per pair, "
-          f"{tot / max(tiles, 1):.0f} cycles per tile ({kb * 512} of them MMA at full rate)")
-    print(f"  MMA thread waits per tile: accumulator not free {lead[:, 1].mean().item() / max(tiles, 1):.0f}, operands not there "
-          f"{lead[:, 2].mean().item() / max(tiles, 1):.0f} ({lead[:, 2].mean().item() / max(tiles * kb, 1):.0f} per k-block)")
-    print(f"  producer waits for a free stage per tile: {v[:, 5].mean().item() / max(tiles, 1):.0f}")
-    print(f"  epilogue per tile: waiting for the accumulator {v[:, 6].mean().item() / max(tiles, 1):.0f}, draining it "
-          f"{v[:, 7].mean().item() / max(tiles, 1):.0f}")
+    shapes = {"square8k": (8192, 8192, 8192, 0, 0), "qkv": (32768, 6144, 2048, 0, 0), "o": (32768, 2048, 2048, 0, 0),
+              "up": (32768, 16384, 2048, 0, 0), "down": (32768, 2048, 8192, 0, 0),
+              "dgrad_up": (32768, 2048, 16384, 0, 1), "wgrad_up": (16384, 2048, 32768, 1, 1),
+              "wgrad_qkv": (6144, 2048, 32768, 1, 1), "head": (4096, 50304, 2064, 0, 0)}
+    names = a.shapes.split(",") if a.shapes else list(shapes)
+    def parse(x):
+        f = [int(t) for t in x.split(":")] + [0]
+        return f[0], f[1]
+    variants = [("lib", None, 0, 0)] + [("own" + (f"+dbg{d}" if d else "") + (f"+gm{gm}" if gm else ""), 1, d, gm)
+                                         for d, gm in map(parse, a.variants.split(","))]
+    for nm in names:
+        M, N, K, a_mn, b_mn = shapes[nm]
+        A = torch.randn(M, K, device="cuda").bfloat16()
+        B = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+        Am = A.t().contiguous() if a_mn else A
+        Bm = B.t().contiguous() if b_mn else B
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ref = A[:256].float() @ B.float().t()
+        fl = 2.0 * M * N * K
+        for label, v, d, gm in variants:
+            if v is None:
+                run = lambda: torch.matmul(A, B.t(), out=out)
+            else:
+                C.gemm_set_debug(d, gm)
+                run = lambda: gemm(Am, Bm, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out)
+            run()
+            err = rel(out[:256], ref)
+            burst = timeit(run, a.iters)
+            ms, mhz, w = sustained(run, a.seconds)
+            share = (fl / ms / 1e9) / (mhz * 1e6 * 148 * 8192 / 1e12) if mhz else float("nan")
+            print(f"{nm:10s} M{M} N{N} K{K} {label:14s} err {err:.1e}  burst {burst:.3f} ms {fl / burst / 1e9:6.0f} TF | sustained "
+                  f"{ms:.3f} ms {fl / ms / 1e9:6.0f} TF at {mhz or 0:.0f} MHz {w or 0:.0f} W -> tensor share {share:.2f}", flush=True)
+        C.gemm_set_debug(0, 0)
+        st = C.gemm_status(0)
+        if st:
+            print(f"  status word {st} after {nm}", flush=True)
+        del A, B, Am, Bm, out
+        torch.cuda.empty_cache()
 
 
 def main(argv=None):
@@ -233,15 +299,14 @@ def main(argv=None):
     t.add_argument("--batch", type=int, default=32); t.add_argument("--heads", type=int, default=32)
     t.add_argument("--seq", type=int, default=1024); t.add_argument("--window", type=int, default=0)
     t.add_argument("--iters", type=int, default=10)
-    r = sub.add_parser("roles")
-    r.add_argument("--m", type=int, default=8192); r.add_argument("--n", type=int, default=8192)
-    r.add_argument("--k", type=int, default=8192); r.add_argument("--groups", type=int, default=1)
-    r.add_argument("--b-mn", dest="b_mn", action="store_true"); r.add_argument("--epi", type=int, default=0)
-    for p in (g, c, i, e):
+    w = sub.add_parser("sweep")
+    w.add_argument("--shapes", default=""); w.add_argument("--variants", default="0", help="dbg[:group_m],...")
+    w.add_argument("--seconds", type=float, default=0.6)
+    for p in (g, c, i, e, w):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
-    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "roles": cmd_roles, "attn": cmd_attn}[a.cmd](a)
+    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "attn": cmd_attn, "sweep": cmd_sweep}[a.cmd](a)
 
 
 if __name__ == "__main__":

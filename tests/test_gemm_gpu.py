@@ -179,3 +179,137 @@ def test_gemm_is_deterministic_and_leaves_the_status_clean():
             C.gemm_set_pair(True)
         assert torch.equal(o1, o2) and torch.equal(e1, e2)
         assert C.gemm_status(0) == 0
+
+
+# ------------------------------------------------------------------------------------------------ pair kernel, staged epilogue
+def _epilogue_suite(direct):
+    """Every epilogue of the CTA-pair kernel on ragged shapes, through TMA stores or through the coalesced row stores
+    (`direct`: the path peer buffers and segmented outputs take)."""
+    from memarch_b200.ops import gemm
+    C = _ext()
+    C.gemm_set_debug(8 if direct else 0)
+    try:
+        M, N, K = 600, 720, 320                                  # ragged M (3 row tiles of 256) and N (720 = 2*256 + 208)
+        A, B = _mk((M, K), seed=41), _mk((N, K), 0.1, seed=42)
+        acc = A.float() @ B.float().t()
+        assert _rel(gemm(A, B), acc) < 1e-2
+        h = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+        a = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+        gemm(A, B, out=h, out2=a, epi=1)
+        assert _rel(a, acc) < 1e-2 and _rel(h, torch.relu(a.float()) ** 2) < 1e-2
+        assert _rel(gemm(A, B, epi=2, aux=a), acc * 2 * torch.relu(a.float())) < 1e-2
+        sc = torch.rand(M, device="cuda")
+        assert _rel(gemm(A, B, epi=4, aux=sc), acc * sc[:, None]) < 1e-2
+        f = torch.ones(M, N, device="cuda")
+        gemm(A, B, out=f, out_dtype=torch.float32, accumulate=True)
+        gemm(A, B, out=f, out_dtype=torch.float32, accumulate=True)
+        assert _rel(f, 1 + 2 * acc) < 2e-3
+        assert _rel(gemm(A, B, out_dtype=torch.float32), acc) < 2e-3
+        # SwiGLU over column halves with and without the pre-activation copy; H = 360 is ragged too
+        H = N // 2
+        hs = torch.empty(M, H + 8, device="cuda", dtype=torch.bfloat16)[:, :H]       # a strided view (pitch 368)
+        gu = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        gemm(A, B, out=hs, out2=gu, epi=3)
+        assert _rel(gu, acc) < 1e-2
+        g, u = gu.float().chunk(2, -1)
+        assert _rel(hs, torch.nn.functional.silu(g) * u) < 1e-2
+        hs2 = gemm(A, B, epi=3)
+        assert _rel(hs2, hs) < 1e-3
+        # a view into a larger output: rows and columns around it stay untouched
+        big = torch.zeros(M + 64, N + 64, device="cuda", dtype=torch.bfloat16)
+        gemm(A, B, out=big[32:32 + M, 64:64 + N])
+        assert _rel(big[32:32 + M, 64:64 + N], acc) < 1e-2
+        assert big[:32].abs().sum() == 0 and big[32 + M:].abs().sum() == 0
+        assert big[:, :64].abs().sum() == 0 and big[:, 64 + N:].abs().sum() == 0
+        torch.cuda.synchronize()
+        assert C.gemm_status(0) == 0
+    finally:
+        C.gemm_set_debug(0)
+
+
+def test_pair_staged_epilogue_tma_stores():
+    _epilogue_suite(False)
+
+
+def test_pair_staged_epilogue_direct_stores():
+    _epilogue_suite(True)
+
+
+@pytest.mark.parametrize("direct", [False, True])
+def test_pair_group_extents(direct):
+    """Per-group extents: padded rows are not computed (count_mode 1), padded contraction positions are not read
+    (count_mode 2); results equal the full computation on zero-padded operands."""
+    from memarch_b200.ops import gemm
+    C = _ext()
+    C.gemm_set_debug(8 if direct else 0)
+    try:
+        E, Cn, d, H = 4, 777, 256, 384
+        cnt = torch.tensor([0, 300, 512, 777], device="cuda", dtype=torch.int32)
+        x = _mk((E, Cn, d), seed=51)
+        mask = (torch.arange(Cn, device="cuda")[None] < cnt[:, None])
+        x = x * mask[..., None]
+        up = _mk((E, d, H), 0.1, seed=52)
+        ref = torch.bmm(x.float(), up.float())
+        h = torch.full((E, Cn, H), 3.0, device="cuda", dtype=torch.bfloat16)
+        a = torch.full((E, Cn, H), 3.0, device="cuda", dtype=torch.bfloat16)
+        gemm(x, up, b_mn=True, out=h, out2=a, epi=1, groups=E, counts=cnt, count_mode=1)
+        assert _rel(a, ref) < 1e-2 and _rel(h, torch.relu(a.float()) ** 2) < 1e-2
+        assert (a * ~mask[..., None]).abs().sum() == 0 and (h * ~mask[..., None]).abs().sum() == 0
+        y = gemm(x, up, b_mn=True, groups=E, counts=cnt, count_mode=1)
+        assert _rel(y, ref) < 1e-2
+        # weight gradient: contraction over the rows
+        dy = _mk((E, Cn, H), seed=53) * mask[..., None]
+        dref = torch.bmm(x.float().transpose(1, 2), dy.float())
+        dw = gemm(x, dy, a_mn=True, b_mn=True, groups=E, counts=cnt, count_mode=2)
+        assert _rel(dw, dref) < 1e-2
+        assert dw[0].abs().sum() == 0
+        dwf = torch.ones(E, d, H, device="cuda")
+        gemm(x, dy, a_mn=True, b_mn=True, groups=E, counts=cnt, count_mode=2, out=dwf, out_dtype=torch.float32,
+             accumulate=True)
+        assert _rel(dwf, 1 + dref) < 2e-3
+        torch.cuda.synchronize()
+        assert C.gemm_status(0) == 0
+    finally:
+        C.gemm_set_debug(0)
+
+
+@pytest.mark.parametrize("act", ["swiglu", "relu2"])
+def test_linear_act_autograd_matches_fp32(act):
+    """Linear with the activation in the GEMM epilogue against plain fp32 autograd."""
+    from memarch_b200.ops import basic
+    x = _mk((640, 256), seed=61).requires_grad_()
+    w = _mk((768, 256), 0.1, seed=62).requires_grad_()
+    h = basic.linear_act(x, w, act)
+    go = _mk(tuple(h.shape), seed=63)
+    h.backward(go)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    pre = xr @ wr.t()
+    if act == "swiglu":
+        g, u = pre.chunk(2, -1)
+        hr = torch.nn.functional.silu(g) * u
+    else:
+        hr = torch.relu(pre) ** 2
+    hr.backward(go.float())
+    assert _rel(h, hr) < 2e-2
+    assert _rel(x.grad, xr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("act", ["swiglu", "relu2"])
+def test_expert_ffn_with_counts_equals_padded(act):
+    """Expert FFN forward + backward with per-expert fill counts equals the padded computation."""
+    from memarch_b200 import ops
+    E, Cn, d, H = 4, 520, 256, 512
+    cnt = torch.tensor([520, 0, 130, 300], device="cuda", dtype=torch.int32)
+    mask = (torch.arange(Cn, device="cuda")[None] < cnt[:, None])[..., None]
+    x0 = _mk((E, Cn, d), seed=71) * mask
+    up0, down0 = _mk((E, d, 2 * H if act == "swiglu" else H), 0.1, seed=72), _mk((E, H, d), 0.1, seed=73)
+    go = _mk((E, Cn, d), seed=74) * mask
+    res = []
+    for counts in (None, cnt):
+        x, up, down = (t.clone().requires_grad_() for t in (x0, up0, down0))
+        y = ops.expert_ffn(x, up, down, act, counts=counts)
+        y.backward(go)
+        res.append((y, x.grad, up.grad, down.grad))
+    for a, b in zip(*res):
+        assert _rel(b, a) < 1e-3, (_rel(b, a))
+    assert _ext().gemm_status(0) == 0

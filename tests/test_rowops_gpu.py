@@ -144,7 +144,8 @@ def test_moe_slots_exact():
     N, k, E, Cn = 3000, 4, 8, 700
     e = torch.randint(0, E + 1, (N, k), device="cuda")
     w = torch.rand(N, k, device="cuda")
-    table, flat_idx, dropped = C.moe_slots(e, E, Cn)
+    table, flat_idx, dropped, counts = C.moe_slots(e, E, Cn)
+    assert torch.equal(counts.long(), (table.view(E, Cn) < e.shape[0]).sum(1))
     rt, _, rf, rd = ref.moe_slots(e, w, E, Cn)
     assert torch.equal(table, rt) and torch.equal(flat_idx, rf)
     assert abs(dropped.item() - rd.item()) < 1e-6

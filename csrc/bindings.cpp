@@ -35,7 +35,8 @@ torch::Tensor row_dot(torch::Tensor go, torch::Tensor table, torch::Tensor ye);
 int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10::optional<torch::Tensor> w,
                       c10::optional<torch::Tensor> cs, torch::Tensor gvec, int64_t index, torch::Tensor stake,
                       torch::Tensor lr_t, c10::optional<torch::Tensor> rel, double beta, double wd, int64_t kind, bool sr,
-                      torch::Tensor seed_t, c10::optional<torch::Tensor> frozen);
+                      torch::Tensor seed_t, c10::optional<torch::Tensor> frozen, c10::optional<torch::Tensor> scratch,
+                      c10::optional<torch::Tensor> cs_ok, c10::optional<torch::Tensor> shadow);
 std::vector<torch::Tensor> anchor_select(torch::Tensor s, torch::Tensor tau, int64_t A);
 std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C);
 std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_keys, bool longest_only);
@@ -78,7 +79,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gather_rows", &mb::gather_rows);
   m.def("gather_sum_rows", &mb::gather_sum_rows);
   m.def("row_dot", &mb::row_dot);
-  m.def("instinct_step", &mb::instinct_step);
+  m.def("instinct_step", &mb::instinct_step, pybind11::arg("p"), pybind11::arg("grad"), pybind11::arg("m"), pybind11::arg("w"),
+        pybind11::arg("cs"), pybind11::arg("gvec"), pybind11::arg("index"), pybind11::arg("stake"), pybind11::arg("lr_t"),
+        pybind11::arg("rel"), pybind11::arg("beta"), pybind11::arg("wd"), pybind11::arg("kind"), pybind11::arg("sr"),
+        pybind11::arg("seed_t"), pybind11::arg("frozen"), pybind11::arg("scratch") = pybind11::none(),
+        pybind11::arg("cs_ok") = pybind11::none(), pybind11::arg("shadow") = pybind11::none());
   m.def("anchor_select", &mb::anchor_select);
   m.def("moe_slots", &mb::moe_slots);
   m.def("lock_find", &mb::lock_find);

@@ -3,16 +3,15 @@
 // or counter-hash stochastic rounding for bf16 weights.  No scalar ever visits the host: gain, stake and the learning
 // rate are read from device memory.
 //
-// A weight is viewed as (E, R, C) with C contiguous.  Three generic kernels cover every kind:
-//   stat_rows : rowsq[e,r] = sum_c (mf * colscale[e,c])^2          (+ sum|g| per row for word tables)
-//   stat_cols : colsq[e,c] += sum_r (mf * colscaleA[e,c] * rowscale[e,r])^2
-//   apply     : upd = mf * s1 * s2 * s3 -> weight / momentum update
-// where mf = beta*m + (1-beta)*g is recomputed on the fly (momentum is written once, in `apply`) and every scale is
-// 1 / (sqrt(sumsq / count) + 1e-8) formed by the consumer from the raw sums.
-//   hs   (2-D)  : rows -> cols(rows) -> rows(rows, cols) -> apply
+// A weight is viewed as (E, R, C) with C contiguous; the kernels and their launch order are in instinct_core.cuh:
+//   hs   (2-D)  : rows -> cols(rows) -> apply with the last row norm fused (row staged in shared memory)
 //   hs3  (E,K,N): cols -> rows(cols) -> cols(cols, rows) -> apply
 //   vocab       : rows (+|g|) -> apply, rows without gradient stay put, no weight decay
 //   row / row3 / tensor : one stat -> apply
+//   lagged hs   : one pass (column norm of the previous step); lagged hs3: the exact sequence with the row norm
+//                 taken from the previous step
+// Scratch statistics live in a caller-owned arena (zeroed here with one cudaMemsetAsync), not in memory allocated per
+// call.
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -26,17 +25,19 @@ static inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(
 
 enum { KIND_TENSOR = 0, KIND_ROW = 1, KIND_ROW3 = 2, KIND_VOCAB = 3, KIND_HS = 4, KIND_HS3 = 5 };
 
-// Returns the number of kernels launched.
+// Returns the number of kernels launched.  `scratch`: fp32 arena of at least instinct_scratch_floats() elements (one is
+// allocated when it is missing or too small).  `cs` / `cs_ok`: state of the lagged form (previous step's second-axis
+// mean squares, "all positive" flag).  `shadow`: bf16 copy of an fp32 weight, refreshed with the weight.
 int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10::optional<torch::Tensor> w_,
                       c10::optional<torch::Tensor> cs_, torch::Tensor gvec, int64_t index, torch::Tensor stake,
                       torch::Tensor lr_t, c10::optional<torch::Tensor> rel_, double beta, double wd, int64_t kind,
-                      bool sr, torch::Tensor seed_t, c10::optional<torch::Tensor> frozen_) {
+                      bool sr, torch::Tensor seed_t, c10::optional<torch::Tensor> frozen_,
+                      c10::optional<torch::Tensor> scratch_, c10::optional<torch::Tensor> cs_ok_,
+                      c10::optional<torch::Tensor> shadow_) {
   const c10::cuda::CUDAGuard guard(p.device());
   TORCH_CHECK(p.is_contiguous() && grad.is_contiguous() && m.is_contiguous(), "instinct_step: contiguous tensors");
   TORCH_CHECK(grad.numel() == p.numel() && m.numel() == p.numel(), "instinct_step: shape mismatch");
-  TORCH_CHECK(!(cs_.has_value() && cs_->defined()), "instinct_step: lagged homeostasis runs on the PyTorch path");
   InstinctArgs a{};
-  a.g_scale = 1.f;
   a.p = p.data_ptr(); a.g = grad.data_ptr(); a.m = m.data_ptr();
   a.p_bf16 = p.scalar_type() == torch::kBFloat16;
   a.g_bf16 = grad.scalar_type() == torch::kBFloat16;
@@ -53,6 +54,11 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
   a.seed = reinterpret_cast<const long long*>(seed_t.data_ptr<int64_t>());
   a.salt = (unsigned)index * 0x85EBCA6Bu;
   a.frozen = (frozen_.has_value() && frozen_->defined()) ? frozen_->data_ptr<bool>() : nullptr;
+  if (shadow_.has_value() && shadow_->defined()) {
+    TORCH_CHECK(!a.p_bf16 && shadow_->scalar_type() == torch::kBFloat16 && shadow_->is_contiguous() &&
+                shadow_->numel() == p.numel(), "instinct_step: shadow is a contiguous bf16 copy of an fp32 weight");
+    a.shadow = shadow_->data_ptr();
+  }
   const long long numel = p.numel();
   long long E = 1, R = 1, C = numel;
   if (kind == KIND_HS || kind == KIND_VOCAB) { TORCH_CHECK(p.dim() == 2); R = p.size(0); C = p.size(1); }
@@ -61,8 +67,32 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
   a.E = E; a.R = R; a.C = C;
   if (a.frozen) a.frozen_stride = numel / frozen_->numel();
   float* rel = (rel_.has_value() && rel_->defined()) ? rel_->data_ptr<float>() + index : nullptr;
-  auto scratch = torch::zeros({instinct_scratch_floats(E, R, C)}, p.options().dtype(torch::kFloat32));
-  return instinct_launch(a, (int)kind, scratch.data_ptr<float>(), rel, cur_stream());
+  float* cs = nullptr;
+  int* cs_ok = nullptr;
+  if (cs_.has_value() && cs_->defined()) {
+    TORCH_CHECK(kind == KIND_HS || kind == KIND_HS3, "instinct_step: the lagged form exists for hs and hs3");
+    TORCH_CHECK(cs_->scalar_type() == torch::kFloat32 && cs_->is_contiguous() &&
+                cs_->numel() == (kind == KIND_HS ? C : E * R), "instinct_step: cs shape");
+    TORCH_CHECK(cs_ok_.has_value() && cs_ok_->defined() && cs_ok_->scalar_type() == torch::kInt32, "instinct_step: cs_ok flag");
+    TORCH_CHECK(kind != KIND_HS || 3 * (size_t)C * sizeof(float) <= INSTINCT_SMEM_MAX,
+                "instinct_step: lagged hs stages three rows in shared memory; this row is too long");
+    cs = cs_->data_ptr<float>();
+    cs_ok = cs_ok_->data_ptr<int>();
+  }
+  const long long need = instinct_scratch_floats(E, R, C);
+  torch::Tensor scratch;
+  if (scratch_.has_value() && scratch_->defined() && scratch_->numel() >= need) {
+    TORCH_CHECK(scratch_->scalar_type() == torch::kFloat32 && scratch_->is_contiguous() &&
+                (reinterpret_cast<uintptr_t>(scratch_->data_ptr()) & 15) == 0, "instinct_step: scratch arena");
+    scratch = *scratch_;
+    C10_CUDA_CHECK(cudaMemsetAsync(scratch.data_ptr(), 0, sizeof(float) * (size_t)need, cur_stream()));
+  } else {
+    scratch = torch::zeros({need}, p.options().dtype(torch::kFloat32));
+  }
+  const int64_t n = instinct_launch(a, (int)kind, scratch.data_ptr<float>(), rel, cur_stream(), cs, cs_ok);
+  TORCH_CHECK(n >= 0, "instinct_step: a row of ", C, " columns is too long for this kind on the kernels");
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return n;
 }
 
 }  // namespace mb

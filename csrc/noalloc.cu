@@ -61,8 +61,11 @@ extern "C" int memarch_instinct_hs_step_noalloc(void* weight, const void* grad, 
   a.sr = 0; a.seed = nullptr; a.salt = 0u;
   a.frozen = nullptr; a.frozen_stride = 1;
   a.E = 1; a.R = rows; a.C = cols;
-  a.n_peers = 0; a.g_scale = 1.f;
-  mb::instinct_launch(a, /*kind hs*/ 4, stats, nullptr, stream);
+  a.shadow = nullptr;
+  if (mb::instinct_launch(a, /*kind hs*/ 4, stats, nullptr, stream) < 0) {
+    std::fprintf(stderr, "memarch_instinct_hs_step_noalloc: a row of %lld columns does not fit the kernels' shared memory\n", cols);
+    return MEMARCH_NOALLOC_TOO_LARGE;
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     std::fprintf(stderr, "memarch_instinct_hs_step_noalloc: launch failed: %s\n", cudaGetErrorString(e));

@@ -62,6 +62,7 @@ class Instinct:
         self.w = [p.detach().float().clone() if (p.dtype == torch.bfloat16 and not cfg.no_master) else None
                   for p in self.plist]
         self.cs = [None] * P
+        self.cs_ok = [None] * P        # lagged form on the GPU: device flag "every entry of cs is positive"
         self.k = torch.zeros((), dtype=torch.long, device=dev)
         self.s = torch.zeros((), device=dev)
         self.stake = torch.zeros((), device=dev)
@@ -208,7 +209,8 @@ class Instinct:
                 self.rel[i] = 0.0
             return
         if (_ext.use_cuda(p) and _kind_code(kind) >= 0 and p.is_contiguous() and grad.is_contiguous()
-                and getattr(p, "_row_shard", None) is None):
+                and getattr(p, "_row_shard", None) is None
+                and not (self.hs_lag and kind in ("hs", "hs3") and not self._lag_on_gpu(p, kind))):
             self._update_cuda(i, p, grad, kind, wd_v, lr_t, want_rel)
         else:
             self._update_ref(i, p, grad, kind, wd_v, lr_t, want_rel)
@@ -324,19 +326,44 @@ class Instinct:
         upd = upd / ((col / total_rows).sqrt() + 1e-8)
         return upd / (upd.pow(2).mean(1, keepdim=True).sqrt() + 1e-8)
 
+    def _arena(self, p, kind):
+        """One fp32 scratch arena per device for the row / column statistics, sized for the largest weight seen."""
+        if kind in ("hs", "vocab"):
+            E, R, Cn = 1, p.shape[0], p.shape[1]
+        elif kind in ("hs3", "row3"):
+            E, R, Cn = p.shape
+        elif kind == "row":
+            E, R, Cn = 1, p.shape[0], p.numel() // p.shape[0]
+        else:
+            E, R, Cn = 1, 1, p.numel()
+        need = 3 * ((E * R + 3) // 4 * 4) + 2 * ((E * Cn + 3) // 4 * 4) + 4
+        key = ("arena", p.device)
+        cur = self._scratch.get(key)
+        if cur is None or cur.numel() < need:
+            cur = self._scratch[key] = torch.empty(max(need, 1 << 16), device=p.device, dtype=torch.float32)
+        return cur
+
+    def _lag_on_gpu(self, p, kind):
+        """The lagged form runs on the kernels for hs3 always and for hs when three rows fit in shared memory."""
+        return kind == "hs3" or (kind == "hs" and 3 * 4 * p.shape[1] <= 200 * 1024)
+
     def _update_cuda(self, i, p, grad, kind, wd, lr_t, want_rel):
         C = _ext.C()
         m, w = self.m[i], self.w[i]
-        if self.hs_lag and kind in ("hs", "hs3") and self.cs[i] is None:
+        lag = self.hs_lag and kind in ("hs", "hs3")
+        if lag and self.cs[i] is None:
             shp = (1, p.shape[1]) if kind == "hs" else (p.shape[0], p.shape[1], 1)
             self.cs[i] = torch.zeros(shp, device=p.device, dtype=torch.float32)
+        if lag and self.cs_ok[i] is None:
+            self.cs_ok[i] = torch.zeros((), device=p.device, dtype=torch.int32)    # 0: look for non-positive entries
         if self.sr:
             self._seed_t.add_(1)
         fr = self._frozen_mask(p)
-        n = C.instinct_step(p, grad, m, w, self.cs[i] if self.hs_lag else None, self.g, int(i), self.stake, lr_t,
+        n = C.instinct_step(p, grad, m, w, self.cs[i] if lag else None, self.g, int(i), self.stake, lr_t,
                             self.rel if want_rel else None, float(self.beta), float(wd), _kind_code(kind),
-                            bool(self.sr), self._seed_t, fr)
-        _ext.count(int(n))
+                            bool(self.sr), self._seed_t, fr, self._arena(p, kind), self.cs_ok[i] if lag else None,
+                            getattr(p, "_bf16_shadow", None))
+        _ext.count(int(n) + 1)
 
     def _update_rows(self, i, p, grad, rows, lr_t):
         """Word / phrase tables: only rows used in this step move (exp_opt.py:306-318)."""
@@ -374,13 +401,14 @@ class Instinct:
                     w[j] = self.w[i][s]
         self.m[i], self.w[i] = (self._to_host(m) if self.offload else m), w
         self.cs[i] = None
+        self.cs_ok[i] = None
 
     @property
     def last(self):
         return dict(card=self.k, s=self.s, stake=self.stake)
 
     # ------------------------------------------------------------------------------------------ checkpoint blob
-    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch", "lr_mul_dev", "offload"}
+    _SKIP = {"plist", "idx", "param_groups", "rows", "cfg", "grad_sync", "_scratch", "lr_mul_dev", "offload", "cs_ok"}
 
     def state_dict(self):
         out = {}
@@ -394,14 +422,16 @@ class Instinct:
                 out[k] = [None if t is None else (t.detach().clone() if own else t.detach().cpu()) for t in v]
             elif isinstance(v, (int, float, bool, str)) or v is None:
                 out[k] = v
-        out["_lr"] = self.param_groups[0]["lr"]
+        out["_lr"] = [g["lr"] for g in self.param_groups]   # a list, one per group (the reference's layout, fastloop.py:668-677)
         return out
 
     def load_state_dict(self, sd):
         dev = self.plist[0].device
         for k, v in sd.items():
-            if k == "_lr":
-                self.param_groups[0]["lr"] = v
+            if k == "_lr":                                     # a list per group (reference layout) or a scalar (older files)
+                lrs = list(v) if isinstance(v, (list, tuple)) else [v] * len(self.param_groups)
+                for g, lr in zip(self.param_groups, lrs):
+                    g["lr"] = float(lr)
             elif torch.is_tensor(v):
                 cur = getattr(self, k, None)
                 if torch.is_tensor(cur) and cur.shape == v.shape:

@@ -150,7 +150,7 @@ class Checkpointer:
             o = {k: v for k, v in vars(opt).items() if k not in opt._SKIP and
                  (torch.is_tensor(v) or (isinstance(v, list) and all(t is None or torch.is_tensor(t) for t in v)) or
                   isinstance(v, (int, float, bool, str)) or v is None)}
-            o["_lr"] = opt.param_groups[0]["lr"]
+            o["_lr"] = [g["lr"] for g in opt.param_groups]      # one rate per parameter group, as the reference stores it
         else:
             o = {"torch_optim": opt.state_dict()}
         return {"model": dict(trainer.model.state_dict()), "opt": o}

@@ -116,13 +116,13 @@ def cmd_instinct(a):
     from memarch_b200.optim import Instinct
     shape = tuple(int(s) for s in a.shape.split(","))
     p = (torch.randn(*shape, device="cuda") * 0.05).to(torch.bfloat16 if a.bf16 else torch.float32).requires_grad_()
-    opt = Instinct([p], OptConfig(lr=1e-3, norm="hs", scale=0.12, m_bf16=True, rel_every=1 << 30))
+    opt = Instinct([p], OptConfig(lr=1e-3, norm="hs", scale=0.12, m_bf16=True, rel_every=1 << 30, hs_lag=a.lag))
     g = torch.randn_like(p)
     opt.prepare(torch.tensor(3.0, device="cuda"), torch.randn(64, device="cuda"))
     kind = opt.spec(p)[0]
     n = p.numel()
     per = (2 if a.bf16 else 4) * 2 + 2 * 2 + (8 if a.bf16 else 0)       # minimal traffic: g, p r/w, m r/w, master r/w
-    report(f"instinct step kind={kind} shape={shape}", timeit(lambda: opt.update(p, g), a.iters), nbytes=float(n) * per,
+    report(f"instinct step kind={kind}{' lagged' if a.lag else ''} shape={shape}", timeit(lambda: opt.update(p, g), a.iters), nbytes=float(n) * per,
            extra=f"(algorithmic {per} B/weight, one pass)")
 
 
@@ -292,6 +292,7 @@ def main(argv=None):
     c.add_argument("--vocab", type=int, default=50304); c.add_argument("--mix", action="store_true")
     i = sub.add_parser("instinct")
     i.add_argument("--shape", default="8,2048,6144"); i.add_argument("--bf16", action="store_true", default=True)
+    i.add_argument("--fp32", dest="bf16", action="store_false"); i.add_argument("--lag", action="store_true")
     e = sub.add_parser("experts")
     e.add_argument("--e", type=int, default=8); e.add_argument("--c", type=int, default=2049)
     e.add_argument("--d", type=int, default=2048); e.add_argument("--h", type=int, default=6144)

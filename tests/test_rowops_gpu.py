@@ -166,13 +166,18 @@ def test_lock_find_exact():
 @pytest.mark.parametrize("kind,shape", [("hs", (384, 1024)), ("hs3", (4, 256, 384)), ("vocab", (12000, 128)),
                                          ("tensor", (1000,)), ("hs", (3, 7))])
 @pytest.mark.parametrize("wdt,mdt", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32)])
-def test_instinct_step_matches_reference(kind, shape, wdt, mdt):
+@pytest.mark.parametrize("lag", [False, True])
+def test_instinct_step_matches_reference(kind, shape, wdt, mdt, lag):
+    """Three optimizer steps on the kernels against the PyTorch statement of the same step; `lag`: the one-pass
+    lagged homeostasis (second-axis norm of the previous step, fresh on the first step and where it is zero)."""
     from memarch_b200.config import OptConfig
     from memarch_b200.optim import Instinct
+    if lag and kind not in ("hs", "hs3"):
+        pytest.skip("the lagged form exists for hs and hs3")
     torch.manual_seed(6)
     p = (torch.randn(*shape, device="cuda") * 0.1).to(wdt)
     pc = p.detach().clone()
-    cfg = OptConfig(lr=1e-2, norm="hs", scale=0.12, m_bf16=mdt == torch.bfloat16, rel_every=1)
+    cfg = OptConfig(lr=1e-2, norm="hs", scale=0.12, m_bf16=mdt == torch.bfloat16, rel_every=1, hs_lag=lag)
     o_gpu = Instinct([p.requires_grad_()], cfg)
     import os
     pr = pc.clone().requires_grad_()
@@ -182,6 +187,8 @@ def test_instinct_step_matches_reference(kind, shape, wdt, mdt):
         g = torch.randn(*shape, device="cuda").to(wdt)
         if kind == "vocab":
             g[::3] = 0
+        if lag and step < 2 and len(shape) == 2:
+            g[:, :5] = 0                  # columns without gradient at first: their lagged norm is zero, the fresh one counts
         sit = torch.randn(16, device="cuda")
         for o, q in ((o_gpu, p), (o_ref, pr)):
             o.prepare(torch.tensor(5.0 - step, device="cuda"), sit)
@@ -196,6 +203,8 @@ def test_instinct_step_matches_reference(kind, shape, wdt, mdt):
     assert _rel(p - pc, pr - pc) < tol, _rel(p - pc, pr - pc)
     assert _rel(o_gpu.m[0], o_ref.m[0]) < tol
     assert _rel(o_gpu.rel, o_ref.rel) < 1e-3
+    if lag:
+        assert _rel(o_gpu.cs[0], o_ref.cs[0]) < 1e-3
 
 
 def test_attention_matches_reference_with_grads():
@@ -305,8 +314,10 @@ def test_memory_read_kernel_matches_torch_path():
 
 
 def test_instinct_step_is_deterministic():
-    """Two optimizers fed the same gradients end bit-identical (stochastic rounding is counter-based, column sums
-    use atomics only where the order cannot change the fp32 result beyond the last bit - checked here at 1e-6)."""
+    """Two optimizers fed the same gradients: the stochastic rounding is counter-based and identical, but the column
+    sums are gathered with fp32 atomics whose order differs from run to run, which moves a sum in its last bit and
+    with it a rounding decision on a few elements - so not bit-identical: at most one bf16 step on under 0.1 % of
+    the elements."""
     from memarch_b200.config import OptConfig
     from memarch_b200.optim.instinct import Instinct
     outs = []

@@ -110,7 +110,7 @@ class LightBlock(nn.Module):
             x, n1 = ops.add_rmsnorm(x, pending, self.n1.weight, self.n1.eps)
         else:
             n1 = ops.rmsnorm(x, self.n1.weight, self.n1.eps, out_dtype=dt)
-        qkv = ops.linear(n1, self.qkv.weight).view(B, T, 3, self.heads, hd)
+        qkv = ops.linear(n1, self.qkv.weight, direct=True).view(B, T, 3, self.heads, hd)
         if self.cur_ve is not None:
             g = 2 * torch.sigmoid(F.linear(x, self.ve_gate.weight.to(x.dtype)))[..., None]        # (B,T,H,1)
             v = qkv[:, :, 2] + (g * self.cur_ve.view(B, T, self.heads, hd)).to(qkv.dtype)
@@ -126,8 +126,9 @@ class LightBlock(nn.Module):
             xs = ops.rmsnorm(x, self.n2.weight, self.n2.eps, out_dtype=dt).gather(1, idx[..., None].expand(-1, -1, D))
             y = ops.linear(self._act(ops.linear(xs, self.up.weight)), self.down.weight) * ok[..., None].to(dt)
             return fin(x.scatter_add(1, idx[..., None].expand(-1, -1, D), y.to(x.dtype)))
-        x, n2 = ops.add_rmsnorm(x, ops.linear(a, self.o.weight), self.n2.weight, self.n2.eps)
-        y = ops.linear(ops.linear_act(n2, self.up.weight, "relu2" if self.relu2 else "swiglu"), self.down.weight)
+        x, n2 = ops.add_rmsnorm(x, ops.linear(a, self.o.weight, direct=True), self.n2.weight, self.n2.eps)
+        y = ops.linear(ops.linear_act(n2, self.up.weight, "relu2" if self.relu2 else "swiglu", direct=True),
+                       self.down.weight, direct=True)
         if defer:
             return x, y
         return ops.resid_add(x, y)

@@ -195,6 +195,50 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+# Set by the trainer when weights are stepped inside backward: callable(weight, bf16 gradient) -> True when it has
+# consumed the gradient (stepped the weight), False to let autograd accumulate it as usual.
+WEIGHT_GRAD_SINK = None
+
+
+class _WeightBf16(torch.autograd.Function):
+    """fp32 master weight -> the bf16 operand of the GEMMs.
+
+    Forward hands out the weight's bf16 shadow, which the optimizer kernel rewrites together with the weight
+    (`Instinct` passes `p._bf16_shadow` to `instinct_step`), so no per-step cast kernel runs; the shadow is rebuilt
+    whenever the weight was changed by anything else (its version counter moved).  Backward gives the bf16 weight
+    gradient straight to `WEIGHT_GRAD_SINK` - the optimizer step of this weight, inside backward, reading the
+    gradient in bf16 - instead of casting it to fp32 for `.grad`; declined gradients flow on as usual."""
+
+    @staticmethod
+    def forward(ctx, w):
+        ctx.w = w
+        sh = getattr(w, "_bf16_shadow", None)
+        if sh is None or getattr(w, "_shadow_ver", None) != w._version or sh.shape != w.shape:
+            sh = w.detach().to(torch.bfloat16)
+            w._bf16_shadow, w._shadow_ver = sh, w._version
+        return sh.detach()
+
+    @staticmethod
+    def backward(ctx, g):
+        sink = WEIGHT_GRAD_SINK
+        if sink is not None and sink(ctx.w, g):
+            return None
+        return g
+
+
+def weight_bf16(w, direct=False):
+    """bf16 view of a weight for a GEMM.  `direct`: the weight is used once per step, so its gradient may go
+    straight to the optimizer (see `_WeightBf16`)."""
+    if w.dtype == torch.bfloat16:
+        return w
+    if direct and w.requires_grad and torch.is_grad_enabled() and w.is_leaf:
+        return _WeightBf16.apply(w)
+    sh = getattr(w, "_bf16_shadow", None)
+    if sh is not None and not torch.is_grad_enabled() and getattr(w, "_shadow_ver", None) == w._version and sh.shape == w.shape:
+        return sh                                   # evaluation: the shadow the optimizer keeps is the cast
+    return w.to(torch.bfloat16)
+
+
 class _LinearAct(torch.autograd.Function):
     """h = act(x · Wᵀ) with the activation in the GEMM epilogue (SwiGLU over the column halves of W's output, or
     relu²); the pre-activation is kept for the backward pass, which is one activation-backward kernel and the two
@@ -221,29 +265,30 @@ class _LinearAct(torch.autograd.Function):
         return dx, dw, None
 
 
-def linear_act(x, w, act):
+def linear_act(x, w, act, direct=False):
     """act(x · Wᵀ), act in {"swiglu", "relu2"}: one GEMM with the activation fused on the GPU."""
     if _ext.use_cuda(x) and PLAIN_GEMM == "tc":
         x2 = x.reshape(-1, x.shape[-1])
         x2 = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
-        wd = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        wd = weight_bf16(w, direct)
         M, K = x2.shape
         N = wd.shape[0]
         if gemm_ok(M, N, K) and M >= 128 and N % 16 == 0:
             h = _LinearAct.apply(x2.contiguous(), wd.contiguous(), act == "swiglu")
             return h.view(*x.shape[:-1], h.shape[-1])
-    y = linear(x, w)
+    y = linear(x, w, direct=direct)
     return relu2(y) if act == "relu2" else swiglu(y)
 
 
-def linear(x, w, dtype=None):
-    """x (..., in) times W (out, in)ᵀ in `dtype` (bf16 on the GPU, the tensors' own dtype on CPU)."""
+def linear(x, w, dtype=None, direct=False):
+    """x (..., in) times W (out, in)ᵀ in `dtype` (bf16 on the GPU, the tensors' own dtype on CPU).  `direct`: see
+    `weight_bf16`."""
     if _ext.use_cuda(x):
         dt = dtype or torch.bfloat16
         x2 = x.reshape(-1, x.shape[-1])
         if x2.dtype != dt:
             x2 = x2.to(dt)
-        wd = w if w.dtype == dt else w.to(dt)
+        wd = weight_bf16(w, direct) if dt == torch.bfloat16 else (w if w.dtype == dt else w.to(dt))
         M, K = x2.shape
         N = wd.shape[0]
         if PLAIN_GEMM == "tc" and dt == torch.bfloat16 and gemm_ok(M, N, K) and M >= 128:

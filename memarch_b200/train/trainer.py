@@ -83,6 +83,14 @@ class Trainer:
             self._gstream = None
 
     # ------------------------------------------------------------------------------------------ hooks
+    def _direct_grad(self, p, g):
+        """bf16 weight gradient handed over by `ops.basic._WeightBf16`: step the weight now (last micro-batch, nothing
+        accumulated yet, the weight is one of this trainer's) or decline."""
+        if not (self.in_backward and self.apply_now) or p.grad is not None or id(p) not in self.opt.idx:
+            return False
+        self.opt.update(p, g.contiguous())
+        return True
+
     def _hook(self, p):
         """Grad-ready hook: accumulate until the last micro-batch, then step this weight and drop its grad."""
         if p.grad is None:
@@ -184,6 +192,8 @@ class Trainer:
     def _core(self, xy, preps=None):
         """Device work of one step: micro-batches forward/backward (weights stepped in the grad hooks), exchange, finish."""
         m = self.model
+        from ..ops import basic
+        basic.WEIGHT_GRAD_SINK = self._direct_grad if (getattr(self, "in_backward", False) and isinstance(self.opt, Instinct)) else None
         micro = self.cfg.micro or len(xy)
         mbs = xy.split(micro)
         inst = isinstance(self.opt, Instinct)

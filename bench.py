@@ -49,7 +49,18 @@ def parse():
     ap.add_argument("--graph", type=int, default=0, help="replay the step as a CUDA graph after 3 eager steps (0 = eager)")
     ap.add_argument("--wave", type=int, default=0, help="frozen bank experts per layer added to the 8 learning ones")
     ap.add_argument("--mem", action="store_true", help="keep the card memory and re-reading on (the headline recipe has NO_MEM=1)")
-    return ap.parse_args()
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4],
+                    help="benchmark configuration: 2 = the headline 2.25 B anchor-MoE model (default); 1 = dense ~300 M "
+                         "model with card memory; 3 = config 2 with 40 frozen bank experts per layer (wave training); "
+                         "4 = long context, 16 384-token texts with memory, re-reading and anchor MoE")
+    a = ap.parse_args()
+    if a.config == 1:
+        a.model, a.mem = "dense_v2_300m", True
+    elif a.config == 3:
+        a.wave = a.wave or 40
+    elif a.config == 4:
+        a.model, a.batch, a.seq, a.mem = "longctx_1024", 4, 16384, True
+    return a
 
 
 # ------------------------------------------------------------------------------------------------ clocks
@@ -190,7 +201,9 @@ def timed_loop(step_fn, steps, warmup, world, sampler=None):
     return ms.item() / steps, clocks
 
 
-def emit(args, impl, world, ms, e2e, clocks, launches, extra):
+def emit(args, impl, world, ms, e2e, clocks, launches, info):
+    """One JSON line.  `config` holds only what defines the measured problem (the same keys and values in both
+    arms); everything descriptive (mode, losses, kernel status, self-test errors, memory) goes to `info`."""
     tok = args.batch * args.seq * world
     value = tok / (ms / 1e3)
     out = {"metric": "train_tokens_per_sec", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
@@ -199,12 +212,12 @@ def emit(args, impl, world, ms, e2e, clocks, launches, extra):
            "data": "synthetic (seed-0 order-1 Markov chain, Zipf(1.1) marginal, 10% copies); random-init weights + "
                    "phrasebook artefacts built from the synthetic corpus",
            "impl": impl,
-           "config": {"model": args.model, "global_batch": args.batch * world, "seq_len": args.seq,
-                      "tokens_per_gpu_per_step": args.batch * args.seq,
-                      "parallelism": extra.pop("parallelism", f"dp{world}"),
-                      "l2": "per-step working set (activations + 2.25B weights) far exceeds the 126 MB L2",
-                      **extra},
-           "clocks": clocks, "gpu_launches": launches}
+           "config": {"model": args.model, "benchmark_config": args.config, "global_batch": args.batch * world,
+                      "seq_len": args.seq, "tokens_per_gpu_per_step": args.batch * args.seq,
+                      "parallelism": f"dp{world}+ep{world}" if world > 1 else "single",
+                      "wave_frozen_experts": args.wave, "memory": bool(args.mem),
+                      "l2": "per-step working set (activations + weights) far exceeds the 126 MB L2"},
+           "info": info, "clocks": clocks, "gpu_launches": launches}
     if e2e is not None:
         out["e2e"] = e2e
     print_json(out)
@@ -237,12 +250,14 @@ def run_ours(args):
     tcfg = train_from_env(TrainConfig(name=args.model, stage="ABX", steps=2000, batch=args.batch, micro=args.batch,
                                       seq=args.seq, lr=6e-4, read_cost=0.01), env)
     parallel = None
+    selftest = None
     if world > 1:
         from memarch_b200.parallel import ParallelEngine
         parallel = ParallelEngine(rank, world, local, fused=args.mode == "fused")
         if parallel.fused_impl is not None:
             # the peer paths are checked on this set of GPUs before the run; if anything is off, the run uses NCCL
             ok, why = parallel.fused_impl.selftest()
+            selftest = dict(parallel.fused_impl.selftest_errors, ok=ok)
             if not ok:
                 print(f"[bench] rank {rank}: fused self-test failed ({why}); using the NCCL mode", file=sys.stderr, flush=True)
                 args.mode = "nccl"
@@ -274,12 +289,16 @@ def run_ours(args):
                "ms_per_step": round(ms2, 3), "h2d_bytes_per_step": feeder.bytes_per_batch, "d2h_bytes_per_step": 4,
                "last_loss": host_loss[-1]}
     st = _ext.C().gemm_status(local)
+    peer_st = int(_ext.C().peer_status_read()) if parallel is not None and parallel.fused_impl is not None else 0
+    if st or peer_st:
+        raise RuntimeError(f"a bounded device wait ran out during the benchmark (GEMM status {st}, peer status {peer_st})")
     if rank == 0:
         first, last = float(losses[0]), float(losses[-1])
         emit(args, "ours", world, ms, e2e, clocks, int(per_step_launches * args.steps),
-             {"parallelism": f"dp{world}+ep{world}" if world > 1 else "single", "mode": args.mode if world > 1 else "single",
-              "loss_first": round(first, 4), "loss_last": round(last, 4), "kernel_status": st,
-              "launches_per_step": round(per_step_launches, 1), "cuda_graph": bool(args.graph) and not tr._graph_failed, "wave_frozen_experts": args.wave,
+             {"parallel_detail": "replicated weights + expert parallel" if world > 1 else "single",
+              "mode": args.mode if world > 1 else "single", "selftest": selftest,
+              "loss_first": round(first, 4), "loss_last": round(last, 4), "kernel_status": st, "peer_status": peer_st,
+              "launches_per_step": round(per_step_launches, 1), "cuda_graph": bool(args.graph) and not tr._graph_failed,
               "params_b": round(sum(p.numel() for p in model.parameters()) / 1e9, 3),
               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
               "stats": {k: round(float(v), 4) for k, v in model.stats.items()}})
@@ -362,7 +381,7 @@ def _run_reference(args, ref_dir):
                "last_loss": host_loss[-1]}
     if rank == 0:
         emit(args, "reference", world, ms, e2e, clocks, 0,
-             {"parallelism": f"fsdp{world}+ep{world}" if world > 1 else "single",
+             {"parallel_detail": "FSDP2 + expert parallel" if world > 1 else "single",
               "mode": ("eager" if os.environ.get("NO_COMPILE") else "torch.compile") + "+OPT_ALL",
               "loss_first": round(float(losses[0]), 4), "loss_last": round(float(losses[-1]), 4),
               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)})

@@ -122,22 +122,28 @@ __global__ void instinct_stat_rows(InstinctArgs a, const float* __restrict__ col
 }
 
 // colsq[e*C + c] += sum over this block's rows of (mf * colscale[e,c] * rowscale[e,r])^2
-// grid: (col strips, row chunks, E); each thread owns VEC consecutive columns.  Scales come from raw sums.
+// grid: (col strips, row chunks, E); each thread owns VEC consecutive columns.  Scales come from raw sums; the row
+// scales of the block's chunk are formed once, into shared memory (rows_per_block floats of dynamic shared memory).
 template <int VEC>
 __global__ void instinct_stat_cols(InstinctArgs a, const float* __restrict__ colsum, float col_count,
                                    const float* __restrict__ rowsum, float row_count, float* __restrict__ colsq_out,
                                    int rows_per_block) {
+  extern __shared__ float rsm[];
   const long long e = blockIdx.z;
   const long long c = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-  if (c >= a.C) return;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(a.R, r0 + rows_per_block);
+  if (rowsum) {
+    for (long long r = r0 + threadIdx.x; r < r1; r += blockDim.x) rsm[r - r0] = scale_of(rowsum[e * a.R + r], row_count);
+    __syncthreads();
+  }
+  if (c >= a.C) return;
   float cs[VEC], acc[VEC];
 #pragma unroll
   for (int j = 0; j < VEC; ++j) { cs[j] = colsum ? scale_of(colsum[e * a.C + c + j], col_count) : 1.f; acc[j] = 0.f; }
   for (long long r = r0; r < r1; ++r) {
     const long long i = (e * a.R + r) * a.C + c;
-    const float rs = rowsum ? scale_of(rowsum[e * a.R + r], row_count) : 1.f;
+    const float rs = rowsum ? rsm[r - r0] : 1.f;
     if (VEC == 4) {
       float4 g, v = mom4(a, i, g);
       const float v0 = v.x * cs[0] * rs, v1 = v.y * cs[1 % VEC] * rs, v2 = v.z * cs[2 % VEC] * rs, v3 = v.w * cs[3 % VEC] * rs;
@@ -523,8 +529,9 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
     int rows_per_block = (int)std::max<long long>(8, (a.R + want_chunks - 1) / want_chunks);
     int chunks = (int)((a.R + rows_per_block - 1) / rows_per_block);
     dim3 grid(strips, chunks, (unsigned)a.E);
-    if (vec) instinct_stat_cols<4><<<grid, threads, 0, st>>>(a, colsum, Rf, rowsum, Cf, out, rows_per_block);
-    else instinct_stat_cols<1><<<grid, threads, 0, st>>>(a, colsum, Rf, rowsum, Cf, out, rows_per_block);
+    const size_t smem = rowsum ? (size_t)rows_per_block * sizeof(float) : 0;     // <= R floats; raised when above 48 KB
+    if (vec) { raise(instinct_stat_cols<4>, smem); instinct_stat_cols<4><<<grid, threads, smem, st>>>(a, colsum, Rf, rowsum, Cf, out, rows_per_block); }
+    else { raise(instinct_stat_cols<1>, smem); instinct_stat_cols<1><<<grid, threads, smem, st>>>(a, colsum, Rf, rowsum, Cf, out, rows_per_block); }
     ++launches;
   };
   auto rowcol = [&](const float* colsum_in, float* rows_out, float* cols_out, const int* skip_if) {

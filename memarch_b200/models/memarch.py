@@ -311,9 +311,13 @@ class MemArchLM(nn.Module):
         c = self.cfg
         B, T = x.shape
         win = self.window if T > self.window else None
-        h = self.emb(x)
+        # on the GPU the token row, the gated candidate rows (INDUCT_IN) and the phrase row are summed by one kernel
+        # further down; `h` stays None until then
+        fuse_in = not c.resid_bf16 and ops._ext.use_cuda(self.emb.weight)
+        h = None if fuse_in else self.emb(x)
         if c.resid_bf16 and x.is_cuda:
             h = h.to(torch.bfloat16)
+        in_cand = in_sel = None
         self._tongue = self._mix = None
         if hasattr(self, "ind_a"):
             if prep and "ind_cand" in prep:
@@ -336,8 +340,12 @@ class MemArchLM(nn.Module):
             self.stats["trust"] = tw.detach().float().mean()
             if c.induct_in:
                 gi = torch.sigmoid(self.ind_in_g[:cand.shape[-1]])
-                sel = (val != 0).to(h.dtype) * gi[None, None].to(h.dtype)
-                h = h + (self.emb(cand) * sel[..., None]).sum(2).type_as(h)
+                hd = torch.float32 if h is None else h.dtype
+                sel = (val != 0).to(hd) * gi[None, None].to(hd)
+                if h is None:
+                    in_cand, in_sel = cand, sel
+                else:
+                    h = h + (self.emb(cand) * sel[..., None]).sum(2).type_as(h)
         if hasattr(self, "tg_a"):
             V0 = c.phr_v
             xc = x.clamp(max=V0 - 1)
@@ -348,7 +356,10 @@ class MemArchLM(nn.Module):
             cand = torch.where(hit, self.tg_tri_idx[pos], self.tg_bi_idx[xc])
             val = torch.where(hit, self.tg_tri_val[pos].float() * self.tg_a[1], self.tg_bi_val[xc].float() * self.tg_a[0])
             self._tongue = (cand, val)
-        if hasattr(self, "phr"):
+        if h is None:
+            pidx = (prep["phr"] if prep and "phr" in prep else self._phr_idx(x)) if hasattr(self, "phr") else None
+            h = ops.embed_sum(self.emb.weight, x, in_cand, in_sel, self.phr.weight if pidx is not None else None, pidx)
+        elif hasattr(self, "phr"):
             h = h + self.phr(prep["phr"] if prep and "phr" in prep else self._phr_idx(x)).type_as(h)
         if hasattr(self, "phr4"):
             h = h + self.phr4(prep["phr4"] if prep and "phr4" in prep else self._phr4_idx(x)).type_as(h)

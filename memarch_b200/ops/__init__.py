@@ -4,4 +4,5 @@ from .basic import rmsnorm, relu2, swiglu, linear, linear_act, gemm, gemm_ok, re
 from .attention import attention                                   # noqa: F401
 from .ce import linear_ce, chunk_ce                                # noqa: F401
 from .anchors import select_anchors, find_locks, gather_tokens, scatter_back   # noqa: F401
+from .embed import embed_sum                                      # noqa: F401
 from .moe import slot_gather, combine, expert_ffn, route_and_slot  # noqa: F401

@@ -8,9 +8,10 @@ loss fed to the optimizer, the situation vector and the anchor threshold `tau` a
 Two modes share this interface:
   * `fused=False`  NCCL (or gloo on CPU) collectives only: all-to-all for the experts, asynchronous all-reduce of
                    each weight's gradient overlapped with the rest of backward.  The baseline and the CPU test path.
-  * `fused=True`   the peer-memory kernels of `memarch_b200.parallel.fused`: expert GEMMs that load their A tiles
-                   from the owners' symmetric buffers and store results into them, and the reduce-scatter + Instinct
-                   update + weight broadcast kernels.
+  * `fused=True`   the peer-memory kernels of `memarch_b200.parallel.fused`: expert rows pulled from the owners'
+                   symmetric buffers, expert GEMMs whose epilogue stores result rows into the owners' buffers, and
+                   the one-shot peer / NVLS all-reduce of each replicated weight's gradient on a side stream ahead
+                   of that weight's Instinct step.
 """
 from __future__ import annotations
 
@@ -218,6 +219,12 @@ class ParallelEngine:
         trainer.opt.grad_sync = self.grad_sync
         if self.fused_impl is not None:
             self.fused_impl.attach(trainer)
+
+    def check(self):
+        """Raise if a bounded peer wait (barrier) ran out since the last check.  Host sync: call it where the loop
+        already waits for the device (log interval, before a checkpoint, end of a benchmark)."""
+        if self.fused_impl is not None:
+            self.fused_impl.heap.check()
 
     # ------------------------------------------------------------------------------------------ control values
     def sync_control(self, loss, sit, model):

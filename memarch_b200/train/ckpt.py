@@ -10,6 +10,11 @@ Writing never blocks the step longer than the device->pinned-host copy: `Checkpo
 pinned buffers on a side stream, then a writer thread serialises to `latest.pt.tmp`, fsyncs and `os.replace`s it, so a
 kill at any moment leaves either the previous or the new complete file (ckpt.py:134-192 of the reference's JAX port
 has the same snapshot-then-write split).  `keep > 0` also keeps `step_<n>.pt` hard links of the last `keep` saves.
+
+Several ranks: a rank's state is not the whole state (it holds its own experts, their momentum and its own data
+position), so every rank writes its own file `latest.rank<r>of<W>.pt` (the single-rank file keeps the reference's name
+and layout) and rank 0 adds `latest.json` = {step, world}.  On resume every rank loads its own file and the ranks
+agree on the step (one tiny all-reduce) before anything is restored; files of another world size are refused.
 """
 from __future__ import annotations
 
@@ -131,9 +136,12 @@ class FileStore:
 
 
 class Checkpointer:
-    def __init__(self, directory, rid=None, keep=0, background=True, mirror=None, mirror_keep=2):
+    def __init__(self, directory, rid=None, keep=0, background=True, mirror=None, mirror_keep=2, rank=0, world=1):
         self.dir, self.rid, self.keep, self.background = directory, rid, keep, background
+        self.rank, self.world = int(rank), int(world)
         os.makedirs(directory, exist_ok=True)
+        if mirror and self.world > 1:
+            mirror = os.path.join(mirror, f"rank{self.rank}of{self.world}")     # one mirrored series per rank
         self.store = FileStore(mirror, rid, mirror_keep) if mirror else None
         self.snap = _PinnedSnapshot()
         self.thread = None
@@ -141,7 +149,13 @@ class Checkpointer:
 
     @property
     def path(self):
+        if self.world > 1:
+            return os.path.join(self.dir, f"latest.rank{self.rank}of{self.world}.pt")
         return os.path.join(self.dir, "latest.pt")
+
+    @property
+    def manifest(self):
+        return os.path.join(self.dir, "latest.json")
 
     # ---------------------------------------------------------------------------------------------- save
     def _device_state(self, trainer):
@@ -174,7 +188,7 @@ class Checkpointer:
             host, done = self.snap.take(dev_state), None         # own buffers: the previous write has finished (wait above)
         st = {"step": int(step), "log": list(log), "banks": bank_layout(trainer.model), "model": host["model"],
               "opt": host["opt"], "corpus": corpus_state, "run_id": self.rid, "extra": extra,
-              "rng": {"cpu": torch.get_rng_state()}}
+              "rng": {"cpu": torch.get_rng_state()}, "rank": self.rank, "world": self.world}
 
         def write():
             try:
@@ -186,12 +200,18 @@ class Checkpointer:
                     f.flush()
                     os.fsync(f.fileno())
                 os.replace(tmp, self.path)
+                if self.world > 1 and self.rank == 0:
+                    with open(self.manifest + ".tmp", "w") as f:
+                        json.dump({"step": int(step), "world": self.world, "run_id": self.rid}, f)
+                    os.replace(self.manifest + ".tmp", self.manifest)
                 if self.keep > 0:
-                    hist = os.path.join(self.dir, f"step_{int(step):08d}.pt")
+                    hist = os.path.join(self.dir, f"step_{int(step):08d}" + (f".rank{self.rank}of{self.world}" if self.world > 1 else "") + ".pt")
                     if os.path.exists(hist):
                         os.remove(hist)
                     os.link(self.path, hist)
-                    old = sorted(f for f in os.listdir(self.dir) if f.startswith("step_") and f.endswith(".pt"))
+                    tail = (f".rank{self.rank}of{self.world}.pt" if self.world > 1 else ".pt")
+                    old = sorted(f for f in os.listdir(self.dir) if f.startswith("step_") and f.endswith(tail)
+                                 and (self.world > 1 or ".rank" not in f))
                     for f in old[:-self.keep]:
                         os.remove(os.path.join(self.dir, f))
                 if self.store is not None:
@@ -219,9 +239,23 @@ class Checkpointer:
         """Resume from `latest.pt` if present.  Returns (next step, log); (first step, []) when there is nothing."""
         if not os.path.exists(self.path) and self.store is not None:
             self.store.fetch_latest(self.path)                   # local disk lost: take this run's newest mirrored copy
-        if not os.path.exists(self.path):
+        st = torch.load(self.path, map_location="cpu", weights_only=False) if os.path.exists(self.path) else None
+        if self.world > 1:
+            # all ranks resume from the same step or none does: a rank whose file is missing or older (killed between
+            # two ranks' writes) must not pair with ranks that are a save ahead
+            import torch.distributed as dist
+            mine = int(st["step"]) if st is not None else -1
+            if st is not None and int(st.get("world", self.world)) != self.world:
+                raise RuntimeError(f"checkpoint {self.path} was written by {st.get('world')} ranks, this run has {self.world}")
+            dev = trainer.device if trainer.device.type == "cuda" else torch.device("cpu")
+            lo, hi = torch.tensor([mine], device=dev), torch.tensor([mine], device=dev)
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            if int(lo) != int(hi):
+                raise RuntimeError(f"ranks disagree on the checkpoint step (between {int(lo)} and {int(hi)}; -1 = no file): "
+                                   f"remove the newer files or restore the missing ones in {self.dir}")
+        if st is None:
             return 1, []
-        st = torch.load(self.path, map_location="cpu", weights_only=False)
         if strict_run and self.rid is not None and st.get("run_id") not in (None, self.rid):
             raise RuntimeError(f"checkpoint {self.path} belongs to run {st.get('run_id')}, this run is {self.rid}")
         restore(trainer, st, corpus)

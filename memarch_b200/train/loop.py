@@ -299,6 +299,19 @@ def _schedules(args, env, tr):
     return cfg, apply, micro0
 
 
+def device_status(tr):
+    """Read the status words of the GEMM and peer kernels (host sync); raise if a bounded device wait ran out."""
+    from ..ops import _ext
+    if tr.device.type != "cuda" or not _ext.available():
+        return
+    st = _ext.C().gemm_status(tr.device.index or 0)
+    if st:
+        raise RuntimeError(f"a GEMM kernel gave up a bounded wait (status {st}); results since the last check are not valid")
+    par = getattr(tr, "parallel", None)
+    if par is not None:
+        par.check()
+
+
 def train(args, device=None, env=None, out=None, parallel=None):
     """Returns {model name: log} where log = [{step, time, val}, ...] (also written to results/<name>_<stage>.json)."""
     from .ckpt import Checkpointer, run_id
@@ -317,7 +330,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
         ck = None
         if env.get("CKPT_DIR"):
             ck = Checkpointer(env["CKPT_DIR"], rid=run_id(name, getattr(tr.model, "cfg", None)), keep=int(env.get("CKPT_KEEP", 0)),
-                              mirror=env.get("CKPT_MIRROR") or None)
+                              mirror=env.get("CKPT_MIRROR") or None, rank=rank, world=world if parallel is not None else 1)
         ck_every = int(env.get("CKPT_EVERY", 0))
         start = 1
         if ck is not None:
@@ -379,8 +392,11 @@ def train(args, device=None, env=None, out=None, parallel=None):
             return b, pr, ev
 
         def sync():
+            """Wait for the device; this is also where the kernels' status words are read (a bounded wait that ran
+            out inside a GEMM or a peer barrier means later kernels worked on incomplete data): raises then."""
             if tr.device.type == "cuda":
                 torch.cuda.synchronize()
+                device_status(tr)
         phase = {"data": 0.0, "enqueue": 0.0, "eval": 0.0, "ckpt": 0.0, "n": 0.0}
         sync()
         t0 = time.time()
@@ -474,6 +490,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     t0 = time.time()
                 if ck is not None and ck_every and (step % ck_every == 0 or (step == last and env.get("NO_FINAL_CKPT") != "1")):
                     nan.flush()                                  # never save a state that already went non-finite
+                    sync()                                       # nor one made after a device wait ran out
                     tc = time.time()
                     ck.save(tr, step, log, data.state_dict())
                     phase["ckpt"] += time.time() - tc

@@ -406,3 +406,41 @@ def test_windowed_attention_routes_agree():
     rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
     assert rel(o_train, o_ref) < 1e-2 and rel(o_eval, o_ref) < 1e-2
     assert rel(g_train, qkv.grad) < 3e-2
+
+
+@pytest.mark.parametrize("with_cand,with_phr", [(True, True), (False, True), (True, False), (False, False)])
+def test_embed_sum_matches_torch(with_cand, with_phr):
+    """Fused input embedding (token + gated candidates + phrase row) against the PyTorch statement, forward and all
+    gradients; repeated indices (hot rows) included."""
+    from memarch_b200 import ops
+    torch.manual_seed(11)
+    B, T, K, V, P, d = 3, 257, 3, 500, 300, 256
+    emb = torch.randn(V, d, device="cuda").requires_grad_()
+    phr = torch.randn(P, d, device="cuda").requires_grad_() if with_phr else None
+    x = torch.randint(0, 20, (B, T), device="cuda")                       # few distinct tokens: many collisions
+    cand = torch.randint(0, V, (B, T, K), device="cuda") if with_cand else None
+    gate = torch.randn(K, device="cuda").requires_grad_() if with_cand else None
+    on = (torch.rand(B, T, K, device="cuda") > 0.5).float() if with_cand else None
+    pidx = torch.randint(0, P, (B, T), device="cuda") if with_phr else None
+    if with_phr:
+        pidx[:, ::2] = P - 1                                              # the shared "no phrase" row: a hot row
+    go = torch.randn(B, T, d, device="cuda")
+
+    def run(fused):
+        for t in (emb, phr, gate):
+            if t is not None:
+                t.grad = None
+        sel = on * torch.sigmoid(gate)[None, None] if with_cand else None
+        if fused:
+            h = ops.embed_sum(emb, x, cand, sel, phr, pidx)
+        else:
+            h = torch.nn.functional.embedding(x, emb)
+            if with_cand:
+                h = h + (torch.nn.functional.embedding(cand, emb) * sel[..., None]).sum(2)
+            if with_phr:
+                h = h + torch.nn.functional.embedding(pidx, phr)
+        h.backward(go)
+        return [h.detach()] + [t.grad.clone() for t in (emb, phr, gate) if t is not None]
+
+    for a, b in zip(run(True), run(False)):
+        assert _rel(a, b) < 1e-5, _rel(a, b)

@@ -361,10 +361,7 @@ constexpr int BH_BYTES = 128 * BK * 2, STAGE2_BYTES = A_BYTES + BH_BYTES;
 // Shared-memory descriptors are built once and advanced by integer adds.  Per-group extents let padded expert rows
 // cost neither loads nor MMAs.
 constexpr int EPI_BUF_BYTES = 4096;
-// 5 operand stages leave room for 4 staging tiles per epilogue warp, 6 stages for 2
-constexpr int epi_nbuf(int stages) { return stages >= 6 ? 2 : 4; }
-constexpr int smem3_bytes(int stages) { return stages * STAGE2_BYTES + 4 * epi_nbuf(stages) * EPI_BUF_BYTES + 1024 + 256; }
-enum { DBG_NO_STORE = 2, DBG_DIRECT_STORE = 8, DBG_L2_HINTS = 16, DBG_SIX_STAGES = 32 };   // test / measurement switches
+enum { DBG_NO_STORE = 2, DBG_DIRECT_STORE = 8, DBG_L2_HINTS = 16, DBG_TALL_OFF = 32, DBG_TALL_ON = 64 };   // test / measurement switches
 
 // row `lane` of a staging tile, 16-byte piece j (the tile is 1024-byte aligned: TMA's 128B swizzle = piece ^ (row & 7))
 __device__ __forceinline__ uint4* stage_piece(uint8_t* buf, int row, int j) {
@@ -643,14 +640,28 @@ __device__ __forceinline__ int group_kblocks(const GemmParams& p, int g) {
   return (k + BK - 1) / BK;
 }
 
-template <bool A_MN, bool B_MN, int STAGES3>
+// MH = 256-row MMA blocks per tile.  MH 1: 256 x 256 tile, 5 operand stages of 32 KB, accumulators double-buffered in
+// TMEM (2 x 256 columns), so the epilogue of a tile runs under the MMAs of the next.  MH 2: 512 x 256 tile - every
+// B k-block feeds two MMAs, so the pair pulls 96 KB per 512x256x64 of work instead of 128 KB (a quarter less L2 and
+// shared-memory traffic, which on a power-capped part is clock) - 4 stages of 48 KB; the two 256-column accumulators
+// fill TMEM, so the epilogue is only half hidden (the MMAs of the next tile's first block start as soon as the
+// first half is drained): worth it when the contraction is long.
+template <int MH> struct PairCfg {
+  static constexpr int STAGES = MH == 2 ? 4 : 5;
+  static constexpr int NBUF = MH == 2 ? 2 : 4;
+  static constexpr int STAGE_BYTES = MH * A_BYTES + BH_BYTES;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 4 * NBUF * EPI_BUF_BYTES + 1024 + 256;
+};
+
+template <bool A_MN, bool B_MN, int MH>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmO2, const GemmParams p) {
+  constexpr int STAGES3 = PairCfg<MH>::STAGES, EPI_NBUF = PairCfg<MH>::NBUF, STAGE_B = PairCfg<MH>::STAGE_BYTES;
+  constexpr int TILE_M = 256 * MH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi_smem = smem + STAGES3 * STAGE2_BYTES;
-  constexpr int EPI_NBUF = epi_nbuf(STAGES3);
+  uint8_t* epi_smem = smem + STAGES3 * STAGE_B;
   uint64_t* full = reinterpret_cast<uint64_t*>(epi_smem + 4 * EPI_NBUF * EPI_BUF_BYTES);
   uint64_t* empty = full + STAGES3;
   uint64_t* tfull = empty + STAGES3;
@@ -693,7 +704,7 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
         int g, mt, nt;
         tile_coords(t, p, g, mt, nt);
         const int seg = mt / p.tiles_per_seg;
-        const int mseg0 = (mt - seg * p.tiles_per_seg) * 256;
+        const int mseg0 = (mt - seg * p.tiles_per_seg) * TILE_M;
         if (seg * p.seg_M + mseg0 >= group_rows(p, g)) continue;            // a tile of padding rows
         const int m0 = mseg0 + (int)rank * BM;
         const CUtensorMap* tA = &tmAs.m[seg];
@@ -705,16 +716,20 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
           if (!mbar_try_wait(&empty[stage], phase ^ 1) && !mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_WAIT_EMPTY); *abort_flag = 1; ok = false; break;
           }
-          uint8_t* sA = smem + stage * STAGE2_BYTES;
-          uint8_t* sB = sA + A_BYTES;
+          uint8_t* sA = smem + stage * STAGE_B;
+          uint8_t* sB = sA + MH * A_BYTES;
           const uint32_t lfull = mapa_shared(smem_u32(&full[stage]), 0);      // the leader's barrier
-          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE2_BYTES);          // bytes of both CTAs
+          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_B);               // bytes of both CTAs
           const int k0 = kb * BK;
-          if (!A_MN) {
-            tma_load_3d_pair(sA, tA, lfull, k0, m0, ga);
-          } else {
-            tma_load_3d_pair(sA, tA, lfull, m0, k0, ga);
-            tma_load_3d_pair(sA + 8192, tA, lfull, m0 + 64, k0, ga);
+#pragma unroll
+          for (int h = 0; h < MH; ++h) {                                       // this CTA's 128 rows of each 256-row block
+            const int mh = m0 + h * 256;
+            if (!A_MN) {
+              tma_load_3d_pair(sA + h * A_BYTES, tA, lfull, k0, mh, ga);
+            } else {
+              tma_load_3d_pair(sA + h * A_BYTES, tA, lfull, mh, k0, ga);
+              tma_load_3d_pair(sA + h * A_BYTES + 8192, tA, lfull, mh + 64, k0, ga);
+            }
           }
           if (!B_MN) {
             tma_load_3d_pair(sB, &tmB, lfull, k0, nb, g);
@@ -738,13 +753,13 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
     if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
-      int acc = 0;
+      int acc = 0;                 // MH 1: accumulator buffer in use; MH 2: always 0 (tempty[h] = half h drained)
       uint32_t acc_phase = 0;
       bool ok = true;
       constexpr uint32_t KSTEP_A = (A_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4, KSTEP_B = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
-      constexpr uint32_t STAGE_STEP = STAGE2_BYTES >> 4;
+      constexpr uint32_t STAGE_STEP = STAGE_B >> 4;
       const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem), A_MN ? BK * 128 : 0, 1024);
-      const uint64_t bdesc0 = smem_desc_sw128(smem_u32(smem) + A_BYTES, B_MN ? BK * 128 : 0, 1024);
+      const uint64_t bdesc0 = smem_desc_sw128(smem_u32(smem) + MH * A_BYTES, B_MN ? BK * 128 : 0, 1024);
       uint32_t soff = 0;                                                   // stage * STAGE_STEP
       // (k-blocks, instruction descriptor) of tile t; 0 k-blocks = nothing to issue (padding rows, empty contraction)
       auto tile_info = [&](int t, int& nkb, uint32_t& idesc) {
@@ -753,7 +768,7 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
         int g_, mt_, nt_;
         tile_coords(t, p, g_, mt_, nt_);
         const int seg = mt_ / p.tiles_per_seg;
-        if (seg * p.seg_M + (mt_ - seg * p.tiles_per_seg) * 256 >= group_rows(p, g_)) return;
+        if (seg * p.seg_M + (mt_ - seg * p.tiles_per_seg) * TILE_M >= group_rows(p, g_)) return;
         nkb = group_kblocks(p, g_);
         idesc = idesc_bf16(256, tile_n_eff(p, nt_), A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       };
@@ -766,7 +781,7 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
           atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (MH == 1 ? acc * BN : 0);
         bool ready = mbar_try_wait(&full[stage], phase);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ready && !mbar_wait(&full[stage], phase, abort_flag)) {
@@ -781,13 +796,26 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
           umma_bf16_pair(d_tmem, ad, bd, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, ad + k * KSTEP_A, bd + k * KSTEP_B, idesc, 1u);
+          if (MH == 2) {
+            if (kb == 0) {                                                 // the second half of the last tile must be drained
+              if (!mbar_try_wait(&tempty[1], acc_phase ^ 1) && !mbar_wait(&tempty[1], acc_phase ^ 1, abort_flag)) {
+                atomicCAS(p.status, 0, ST_WAIT_TMEM_EMPTY); *abort_flag = 1; ok = false; break;
+              }
+              tc_fence_after();
+            }
+            const uint64_t ad2 = ad + (A_BYTES >> 4);
+            umma_bf16_pair(d_tmem + BN, ad2, bd, idesc, kb > 0 ? 1u : 0u);
+#pragma unroll
+            for (int k = 1; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem + BN, ad2 + k * KSTEP_A, bd + k * KSTEP_B, idesc, 1u);
+          }
           umma_commit_pair(&empty[stage], 3);       // frees this stage in both CTAs
           if (kb == 0) tile_info(t + npairs, nxt_kb, nxt_idesc);
           stage = ns; phase = nph; soff = nsoff;
         }
         if (!ok) break;
-        umma_commit_pair(&tfull[acc], 3);           // accumulators of both CTAs complete
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        umma_commit_pair(&tfull[MH == 1 ? acc : 0], 3);           // accumulators of both CTAs complete
+        if (MH == 1) { if (++acc == 2) { acc = 0; acc_phase ^= 1; } }
+        else acc_phase ^= 1;
         num_kb = nxt_kb; idesc = nxt_idesc;
       }
     }
@@ -809,24 +837,31 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
       int g, mt, nt;
       tile_coords(t, p, g, mt, nt);
       const int seg = mt / p.tiles_per_seg;
-      const int mseg0 = (mt - seg * p.tiles_per_seg) * 256;
-      const int row0_l = mseg0 + (int)rank * BM + q * 32;
-      const int row0 = seg * p.seg_M + row0_l;
+      const int mseg0 = (mt - seg * p.tiles_per_seg) * TILE_M;
       const bool zero_tile = seg * p.seg_M + mseg0 >= group_rows(p, g) || group_kblocks(p, g) == 0;
       if (!zero_tile) {
-        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+        if (!mbar_wait(&tfull[MH == 1 ? acc : 0], acc_phase, abort_flag)) {
           if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_TMEM_FULL); *abort_flag = 1; }
           ok = false; break;
         }
         tc_fence_after();
       }
-      epilogue_tile3(p, &tmO, &tmO2, g, seg, row0, row0_l, nt, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, ring,
-                     lane, zero_tile);
+#pragma unroll 1
+      for (int h = 0; h < MH; ++h) {
+        const int row0_l = mseg0 + h * 256 + (int)rank * BM + q * 32;
+        const int row0 = seg * p.seg_M + row0_l;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (MH == 1 ? acc * BN : h * BN);
+        epilogue_tile3(p, &tmO, &tmO2, g, seg, row0, row0_l, nt, taddr, ring, lane, zero_tile);
+        if (!zero_tile) {
+          tc_fence_before();
+          __syncwarp();
+          // the leader's MMA thread waits on it (MH 2: per half, so the next tile's first MMAs start early)
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[MH == 1 ? acc : h]), 0));
+        }
+      }
       if (!zero_tile) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));   // the leader's MMA thread waits on it
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (MH == 1) { if (++acc == 2) { acc = 0; acc_phase ^= 1; } }
+        else acc_phase ^= 1;
       }
     }
     if (ring.tma && lane == 0) bulk_wait_all<0>();           // staged tiles must be read before the CTA's smem goes away
@@ -930,13 +965,27 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
                      : make_tmap_bf16(A_list[i], K, seg_M, a_groups, a_rows_pitch, a_gs, 64, BM);
   for (int i = n_seg; i < 8; ++i) tmAs.m[i] = tmAs.m[0];
   const bool pair = use_pair_kernel() && seg_M >= 256;
-  const int tile_m = pair ? 256 : BM;
-  p.n_seg = n_seg; p.seg_M = seg_M; p.tiles_per_seg = (seg_M + tile_m - 1) / tile_m;
   const bool sw = p.epi == EPI_SWIGLU;
+  const int n_tiles = sw ? ((N / 2) + 127) / 128 : (N + BN - 1) / BN;
+  // 512-row tiles (see PairCfg) when the contraction is long enough to pay for the half-exposed epilogue and the
+  // coarser tiling does not cost more in the last, partly filled wave of tiles than it saves
+  bool tall = false;
+  if (pair && n_seg == 1 && p.count_mode == 0 && seg_M >= 1024 && !(sw && p.out2)) {
+    auto wave_eff = [&](int tm) {
+      const long long tiles = (long long)G * ((seg_M + tm - 1) / tm) * n_tiles, pairs = std::max(1, max_ctas / 2);
+      return (double)tiles / (double)(((tiles + pairs - 1) / pairs) * pairs);
+    };
+    static const bool tall_env = []() { const char* e = std::getenv("MEMARCH_GEMM_TALL"); return !(e && e[0] == '0'); }();
+    tall = tall_env && K >= 8192 && wave_eff(512) >= wave_eff(256) - 0.02;
+    if (g_dbg & DBG_TALL_OFF) tall = false;
+    if (g_dbg & DBG_TALL_ON) tall = true;
+  }
+  const int tile_m = pair ? (tall ? 512 : 256) : BM;
+  p.n_seg = n_seg; p.seg_M = seg_M; p.tiles_per_seg = (seg_M + tile_m - 1) / tile_m;
   CUtensorMap tmB = b_mn ? make_tmap_bf16(B, N, K, G, b_rows_pitch, b_gs, 64, 64)
                          : make_tmap_bf16(B, K, N, G, b_rows_pitch, b_gs, 64, (sw || pair) ? 128 : BN);
   p.m_tiles = n_seg * p.tiles_per_seg;
-  p.n_tiles = sw ? ((N / 2) + 127) / 128 : (N + BN - 1) / BN;
+  p.n_tiles = n_tiles;
   static const bool ntail_on = []() { const char* e = std::getenv("MEMARCH_GEMM_NTAIL"); return !(e && e[0] == '0'); }();
   p.ntail = ntail_on ? 1 : 0;
   const int total = G * p.m_tiles * p.n_tiles;
@@ -944,8 +993,7 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
   if (grid <= 0) return;
   const bool v3 = pair;
   TORCH_CHECK(v3 || p.count_mode == 0, "gemm: per-group extents need the pair kernel (>= 256 rows)");
-  const bool six = v3 && (g_dbg & DBG_SIX_STAGES) && !(p.epi == EPI_SWIGLU && p.out2);
-  const int smem_bytes = v3 ? smem3_bytes(six ? 6 : 5) : SMEM_BYTES;
+  const int smem_bytes = v3 ? (tall ? PairCfg<2>::SMEM : PairCfg<1>::SMEM) : SMEM_BYTES;
   CUtensorMap tmO = tmB, tmO2 = tmB;
   if (v3) {
     p.dbg = g_dbg;
@@ -978,16 +1026,16 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
       kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, p);
   };
   const int id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
-  if (v3 && six) {
-    if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 6>, 12 + id);
-    else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 6>, 12 + id);
-    else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 6>, 12 + id);
-    else launch(gemm_pair_kernel<true, true, 6>, 12 + id);
+  if (v3 && tall) {
+    if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 2>, 12 + id);
+    else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 2>, 12 + id);
+    else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 2>, 12 + id);
+    else launch(gemm_pair_kernel<true, true, 2>, 12 + id);
   } else if (v3) {
-    if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 5>, 8 + id);
-    else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 5>, 8 + id);
-    else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 5>, 8 + id);
-    else launch(gemm_pair_kernel<true, true, 5>, 8 + id);
+    if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 1>, 8 + id);
+    else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 1>, 8 + id);
+    else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 1>, 8 + id);
+    else launch(gemm_pair_kernel<true, true, 1>, 8 + id);
   } else {
     if (!a_mn && !b_mn) launch(gemm_tc_kernel<false, false>, id);
     else if (!a_mn && b_mn) launch(gemm_tc_kernel<false, true>, id);

@@ -242,7 +242,8 @@ def cmd_sweep(a):
     shapes = {"square8k": (8192, 8192, 8192, 0, 0), "qkv": (32768, 6144, 2048, 0, 0), "o": (32768, 2048, 2048, 0, 0),
               "up": (32768, 16384, 2048, 0, 0), "down": (32768, 2048, 8192, 0, 0),
               "dgrad_up": (32768, 2048, 16384, 0, 1), "wgrad_up": (16384, 2048, 32768, 1, 1),
-              "wgrad_qkv": (6144, 2048, 32768, 1, 1), "head": (4096, 50304, 2064, 0, 0)}
+              "wgrad_qkv": (6144, 2048, 32768, 1, 1), "wgrad_down": (2048, 8192, 32768, 1, 1),
+              "dgrad_qkv": (32768, 2048, 6144, 0, 1), "head": (4096, 50304, 2064, 0, 0)}
     names = a.shapes.split(",") if a.shapes else list(shapes)
     def parse(x):
         f = [int(t) for t in x.split(":")] + [0]

@@ -182,14 +182,14 @@ def test_gemm_is_deterministic_and_leaves_the_status_clean():
 
 
 # ------------------------------------------------------------------------------------------------ pair kernel, staged epilogue
-def _epilogue_suite(direct):
+def _epilogue_suite(direct, tall=False):
     """Every epilogue of the CTA-pair kernel on ragged shapes, through TMA stores or through the coalesced row stores
-    (`direct`: the path peer buffers and segmented outputs take)."""
+    (`direct`: the path peer buffers and segmented outputs take); `tall`: the 512-row tile variant."""
     from memarch_b200.ops import gemm
     C = _ext()
-    C.gemm_set_debug(8 if direct else 0)
+    C.gemm_set_debug((8 if direct else 0) | (64 if tall else 32))
     try:
-        M, N, K = 600, 720, 320                                  # ragged M (3 row tiles of 256) and N (720 = 2*256 + 208)
+        M, N, K = (1100 if tall else 600), 720, 320              # ragged M (row tiles of 256 / 512) and N (720 = 2*256 + 208)
         A, B = _mk((M, K), seed=41), _mk((N, K), 0.1, seed=42)
         acc = A.float() @ B.float().t()
         assert _rel(gemm(A, B), acc) < 1e-2
@@ -233,6 +233,32 @@ def test_pair_staged_epilogue_tma_stores():
 
 def test_pair_staged_epilogue_direct_stores():
     _epilogue_suite(True)
+
+
+@pytest.mark.parametrize("direct", [False, True])
+def test_pair_tall_tiles(direct):
+    """512-row tiles (two MMA row blocks per B tile, single-buffered accumulators) on the same suite."""
+    _epilogue_suite(direct, tall=True)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_pair_tall_tiles_operand_layouts(a_mn, b_mn):
+    from memarch_b200.ops import gemm
+    C = _ext()
+    M, N, K = 1536, 520, 1088
+    A, B = _mk((M, K), seed=81), _mk((N, K), 0.1, seed=82)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    C.gemm_set_debug(64)
+    try:
+        o1 = gemm(a, b, a_mn=a_mn, b_mn=b_mn).clone()
+        o2 = gemm(a, b, a_mn=a_mn, b_mn=b_mn).clone()
+        torch.cuda.synchronize()
+        st = C.gemm_status(0)
+    finally:
+        C.gemm_set_debug(0)
+    assert st == 0 and torch.equal(o1, o2)
+    assert _rel(o1, A.float() @ B.float().t()) < 1e-2
 
 
 @pytest.mark.parametrize("direct", [False, True])

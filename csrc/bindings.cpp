@@ -13,6 +13,7 @@ torch::Tensor gemm_peer(std::vector<int64_t> a_ptrs, int64_t seg_M, int64_t K, i
                         c10::optional<torch::Tensor> out2, c10::optional<torch::Tensor> aux, int64_t epi, int64_t groups);
 void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, double timeout_ms);
 int64_t peer_status_read();
+void peer_gather(std::vector<int64_t> src_ptrs, torch::Tensor dst, int64_t rank, int64_t C, int64_t g_off);
 void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,
                     int64_t numel, bool is_bf16, int64_t rank, double scale);
 void gemm_set_pair(bool on);
@@ -68,6 +69,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_peer", &mb::gemm_peer, "segmented GEMM: A tiles from peer buffers, result rows to the owners' buffers");
   m.def("peer_barrier", &mb::peer_barrier, "bounded device-side barrier over symmetric flags");
   m.def("peer_status_read", &mb::peer_status_read);
+  m.def("peer_gather", &mb::peer_gather, "rows of this rank's experts from every rank's dispatch buffer, one kernel");
   m.def("peer_allreduce", &mb::peer_allreduce, "one-shot all-reduce by peer loads/stores or NVLS multimem");
   m.def("rmsnorm_fwd", &mb::rmsnorm_fwd);
   m.def("rmsnorm_bwd", &mb::rmsnorm_bwd);

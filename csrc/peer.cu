@@ -76,6 +76,62 @@ int64_t peer_status_read() {
   return v;
 }
 
+// ------------------------------------------------------------------------------------------------ expert-row gather
+// dst (G, W*C, d) <- rows of this rank's G experts from every rank's dispatch buffer src_s (E, C, d):
+//   dst[g, s*C + c, :] = src_s[g_off + g, c, :]
+// One kernel over all W sources (plain 16-byte peer loads over NVLink, four in flight per thread) instead of W
+// back-to-back copies; sources are walked starting at this rank, so the W ranks read from W different GPUs first.
+__global__ void peer_gather_kernel(PeerPtrs src, uint4* __restrict__ dst, int W, int rank, long long G, long long C,
+                                   long long d16, long long g_off) {
+  const long long per_src = G * C * d16;
+  const long long total = per_src * W;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    uint4 v[4];
+    long long o[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long j = i + u * stride;
+      const int si = (int)(j / per_src);
+      const int s = (rank + si) % W;
+      const long long r = j - si * per_src;
+      const long long g = r / (C * d16), rc = r - g * (C * d16);
+      v[u] = *(reinterpret_cast<const uint4*>(src.p[s]) + (g_off + g) * C * d16 + rc);
+      o[u] = (g * W * C + (long long)s * C) * d16 + rc;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dst[o[u]] = v[u];
+  }
+  for (; i < total; i += stride) {
+    const int si = (int)(i / per_src);
+    const int s = (rank + si) % W;
+    const long long r = i - si * per_src;
+    const long long g = r / (C * d16), rc = r - g * (C * d16);
+    dst[(g * W * C + (long long)s * C) * d16 + rc] = *(reinterpret_cast<const uint4*>(src.p[s]) + (g_off + g) * C * d16 + rc);
+  }
+}
+
+// src_ptrs: base pointers of the W ranks' (E, C, d) bf16 buffers; dst: (G, W*C, d) bf16, contiguous.
+void peer_gather(std::vector<int64_t> src_ptrs, torch::Tensor dst, int64_t rank, int64_t C, int64_t g_off) {
+  const int W = (int)src_ptrs.size();
+  TORCH_CHECK(W >= 1 && W <= 8, "peer_gather: 1..8 ranks");
+  TORCH_CHECK(dst.is_cuda() && dst.dim() == 3 && dst.is_contiguous() && dst.scalar_type() == torch::kBFloat16, "peer_gather: dst (G, W*C, d) bf16");
+  const long long G = dst.size(0), d = dst.size(2);
+  TORCH_CHECK(dst.size(1) == W * C && d % 8 == 0, "peer_gather: dst rows = W*C, d % 8 == 0");
+  const c10::cuda::CUDAGuard guard(dst.device());
+  PeerPtrs sp{};
+  for (int i = 0; i < W; ++i) {
+    sp.p[i] = reinterpret_cast<void*>(src_ptrs[i]);
+    TORCH_CHECK((src_ptrs[i] & 15) == 0, "peer_gather: 16-byte aligned buffers");
+  }
+  const long long total = (long long)W * G * C * (d / 8);
+  if (total == 0) return;
+  const int grid = (int)std::min<long long>((total + 1023) / 1024, 148 * 8);
+  peer_gather_kernel<<<grid, 256, 0, cur_stream()>>>(sp, reinterpret_cast<uint4*>(dst.data_ptr()), W, (int)rank, G, C, d / 8, g_off);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 // ------------------------------------------------------------------------------------------------ all-reduce (P2P)
 // Rank r owns the r-th slice of [0, n): it loads that slice from every rank's `in` buffer, sums in fp32, scales, and
 // stores the result into every rank's `out` buffer (reduce-scatter and all-gather in one kernel, 16-byte accesses).

@@ -66,7 +66,6 @@ class ModelConfig:
     students: int = 5
     err_thr: float = 0.3
     moe_cap_align: int = 0        # MOE_CAP_ALIGN
-    moe_dispatch: str = "slot"    # "slot" (scatter table) | "gather" | "inv" | "onehot" | "gmm"
     moe_group: int = 512
     heavy_attn: bool = False
     heavy_attn_detach: bool = False
@@ -76,7 +75,6 @@ class ModelConfig:
     blk: Tuple[str, ...] = ()     # subset of {zero, ve, x0, relu2, relu2c, qk, qkv3, smear}
     light_ffn: float = 0.0        # LIGHT_FFN width in units of d
     light_moe: str = ""           # "E:k"
-    attn_impl: str = ""           # "", "block", "block2" window attention implementation
     rope_half: bool = False
     resid_bf16: bool = False
     # phrasebook / locks / heads
@@ -114,7 +112,7 @@ class ModelConfig:
 @dataclass
 class OptConfig:
     """InstinctOptB constructor (exp_opt.py:437-439) plus the env switches around it."""
-    kind: str = "instinct"        # instinct | adamw | surprise | muon
+    kind: str = "instinct"        # instinct | adamw | surprise
     lr: float = 1e-3
     weight_decay: float = 0.1
     cards: int = 4
@@ -214,10 +212,9 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("BANK_Q"): kw["bank_q"] = g("BANK_Q")
     if g("WAVE_WARM"): kw["wave_warm"] = int(g("WAVE_WARM"))
     if g("MOE_CAP_ALIGN"): kw["moe_cap_align"] = int(g("MOE_CAP_ALIGN"))
-    if g("MOE_GMM") == "1": kw["moe_dispatch"] = "gmm"
-    elif g("MOE_DISP") == "onehot": kw["moe_dispatch"] = "onehot"
-    elif g("MOE_GATHER") and g("MOE_DISP") == "inv": kw["moe_dispatch"] = "inv"
-    elif g("MOE_GATHER"): kw["moe_dispatch"] = "gather"
+    # MOE_GMM / MOE_DISP / MOE_GATHER choose among the reference's dispatch forms; this build has one form (slot
+    # table + inverse gather) and its grouped GEMMs always skip the padding rows of an expert (per-expert fill
+    # counts), which is what the reference's dropless MOE_GMM path buys - the switches are accepted and ignored
     if g("MOE_GROUP"): kw["moe_group"] = int(g("MOE_GROUP"))
     if g("HEAVY_ATTN"): kw["heavy_attn"] = True
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
@@ -226,7 +223,7 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("BLK"): kw["blk"] = tuple(s for s in g("BLK").split(",") if s)
     if g("LIGHT_FFN"): kw["light_ffn"] = float(g("LIGHT_FFN"))
     if g("LIGHT_MOE"): kw["light_moe"] = g("LIGHT_MOE")
-    if g("ATTN_IMPL"): kw["attn_impl"] = g("ATTN_IMPL")
+    # ATTN_IMPL (block / block2 window forms of the reference) is accepted and ignored: one windowed attention here
     if g("ROPE_HALF") == "1": kw["rope_half"] = True
     if g("RESID_BF16") == "1": kw["resid_bf16"] = True
     if g("PHRASE_INIT"): kw["phrase_init"] = g("PHRASE_INIT")
@@ -357,7 +354,7 @@ def preset(name: str, vocab: int = 50304, env=None) -> ModelConfig:
                         memory=M(fresh=64, dim=64, dim_max=96), induct="lock", induct_mix=True)
     elif name == "longctx_1024":
         c = ModelConfig(vocab=vocab, d=1024, heads=16, light_a=4, light_b=4, heavy=6, final=2, window=256,
-                        attn_impl="block", moe="fixed", n_exp=8, bank=True)
+                        moe="fixed", n_exp=8, bank=True)
     else:
         raise ValueError(f"unknown memarch model name: {name}")
     return model_from_env(c, env)

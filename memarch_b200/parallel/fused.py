@@ -91,11 +91,12 @@ class _FusedExpertFFN(torch.autograd.Function):
                 a = C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, None, [], 0, 0, 0, None, None, 0, n_local)
                 h = C.swiglu_fwd(a)
         else:
-            # rows of my experts land in local memory first (bandwidth-bound peer copies), the GEMM reads them locally:
-            # a remote tile costs an NVLink round trip, more than the 6-stage shared-memory ring can hide
+            # rows of my experts land in local memory first (one bandwidth-bound gather kernel over the peer
+            # pointers), the GEMM reads them locally: a remote tile costs an NVLink round trip, more than the
+            # shared-memory ring can hide
             xin = torch.empty(n_local, M, d, device=xe.device, dtype=torch.bfloat16)
-            for s in _rotated(W, r):                    # every rank starts at another owner: no hot GPU
-                xin[:, s * Cn:(s + 1) * Cn].copy_(Xh.get_buffer(s, (E, Cn, d), torch.bfloat16)[g_off:g_off + n_local])
+            C.peer_gather([int(p) for p in Xh.buffer_ptrs], xin, r, Cn, g_off)      # one kernel over all W owners
+            _ext.count()
             if act == "relu2":
                 gemm(xin, up, b_mn=True, out=h, out2=a, epi=1, groups=n_local)
             else:
@@ -138,12 +139,10 @@ class _FusedExpertFFN(torch.autograd.Function):
         pull_x = ctx.train_w and xe_all is None
         if pull_x:
             xe_all = torch.empty(nl, M, d, device=dy.device, dtype=torch.bfloat16)
-        for s in _rotated(W, r):
-            src = DYh.get_buffer(s, (E, Cn, d), torch.bfloat16)
-            dy_all[:, s * Cn:(s + 1) * Cn].copy_(src[g_off:g_off + nl])
-            if pull_x:
-                srcx = Xh.get_buffer(s, (E, Cn, d), torch.bfloat16)
-                xe_all[:, s * Cn:(s + 1) * Cn].copy_(srcx[g_off:g_off + nl])
+        C.peer_gather([int(p) for p in DYh.buffer_ptrs], dy_all, r, Cn, g_off)
+        if pull_x:
+            C.peer_gather([int(p) for p in Xh.buffer_ptrs], xe_all, r, Cn, g_off)
+        _ext.count(2 if pull_x else 1)
         if act == "relu2":
             da = gemm(dy_all, down, epi=2, aux=a, groups=nl)
         else:

@@ -94,6 +94,30 @@ def _single_rank(q):
             res["selftest"] = eng.fused_impl.selftest()
         res[mode] = (losses, {k: v.detach().float().cpu().numpy() for k, v in m.state_dict().items()
                               if v.dtype.is_floating_point and 0 < v.numel() < 1 << 22})
+        if eng is not None:
+            # a bank layer with frozen experts runs the fused exchange twice (learning and frozen experts) over shared
+            # gradient buffers: the input gradient must equal the local computation, rows of the other bank included
+            from memarch_b200.models.moe import AnchorMoE
+            torch.manual_seed(3)
+            moe = AnchorMoE(256, E=4, k_avg=2, k_max=2, bank=True, act="relu2", w_dtype=torch.bfloat16).cuda()
+            moe.grow_bank(4)
+            xe0 = (torch.randn(moe.E, 300, 256, device="cuda") * 0.5).bfloat16()
+            go = torch.randn(moe.E, 300, 256, device="cuda").bfloat16()
+            outs = []
+            for fused in (False, True):
+                xe = xe0.clone().requires_grad_()
+                moe.up.grad = moe.down.grad = None
+                moe._counts = None
+                if fused:
+                    eng.fused_impl.ep.ffn(moe, xe).backward(go)            # twice: stale rows of an earlier call must not leak
+                    xe.grad = moe.up.grad = moe.down.grad = None
+                    y = eng.fused_impl.ep.ffn(moe, xe)
+                else:
+                    y = moe._experts(xe, None, 300)
+                y.backward(go)
+                outs.append((y.detach().float(), xe.grad.float(), moe.up.grad.float(), moe.down.grad.float()))
+            rel = lambda a, b: float((a - b).norm() / b.norm().clamp(min=1e-9))
+            res["bank_err"] = [rel(a, b) for a, b in zip(outs[1], outs[0])]
     q.put(res)
     dist.destroy_process_group()
 
@@ -110,8 +134,37 @@ def test_fused_kernels_on_one_rank_match_plain_path():
     res = q.get(timeout=240)
     p.join(60)
     assert res["selftest"] == (True, "ok"), res["selftest"]          # the pre-run check of the peer paths itself
+    assert max(res["bank_err"]) < 1e-2, res["bank_err"]              # y, d xe, d up, d down of a layer with frozen experts
     for a, b in zip(res["plain"][0], res["fused"][0]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (res["plain"][0], res["fused"][0])
     for k, v in res["plain"][1].items():
         w = res["fused"][1][k]
         assert np.abs(v - w).max() / (np.abs(v).max() + 1e-6) < 5e-2, k
+
+
+def test_bounded_barrier_wait_runs_out_and_reports():
+    """A device-side barrier whose peer never arrives: the wait gives up after its limit, the status word says so,
+    `SymmetricHeap.check` raises, and the device keeps working.  The "peer" is a second flag array in this GPU's own
+    memory that nobody signals, so nothing waits on another process and nothing faults."""
+    import time
+    from memarch_b200.ops import _ext
+    from memarch_b200.parallel.fused import SymmetricHeap
+    C = _ext.C()
+    assert C.peer_status_read() == 0
+    mine = torch.zeros(256, dtype=torch.int32, device="cuda")
+    other = torch.zeros(256, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    C.peer_barrier([mine.data_ptr(), other.data_ptr()], 0, 0, 5.0)        # rank 0 of 2, limit 5 ms
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 2.0
+    heap = SymmetricHeap.__new__(SymmetricHeap)                           # only `check` is exercised
+    heap.wait_ms = 5.0
+    with pytest.raises(RuntimeError, match="peer wait timed out"):
+        heap.check()
+    assert C.peer_status_read() == 0                                      # read-and-clear
+    x = torch.arange(1024, device="cuda", dtype=torch.float32)
+    assert float((x * 2).sum()) == 1023 * 1024                            # the context is alive
+    # a complete barrier of one rank still passes afterwards
+    C.peer_barrier([mine.data_ptr()], 0, 1, 5.0)
+    torch.cuda.synchronize()
+    assert C.peer_status_read() == 0

@@ -126,6 +126,38 @@ def test_checkpoint_round_trip_continues_bit_exact(tmp_path):
     assert {"m", "w", "gain", "keys", "used", "expect", "seen", "rel", "n_step", "_lr"} <= set(st["opt"])
 
 
+def test_lagged_homeostasis_state_round_trips_through_a_checkpoint(tmp_path):
+    """`hs_lag`: the previous step's second-axis mean squares (`cs`) are optimizer state; a resumed run continues
+    bit-exact, and the blob keeps one learning rate per parameter group (a list, the reference's layout)."""
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.train import Trainer
+    from memarch_b200.train.ckpt import Checkpointer
+
+    def mk(seed):
+        torch.manual_seed(seed)
+        m = build("tiny", 256, env={"NO_MEM": "1", "MOE_ACT": "relu2"})
+        return Trainer(m, TrainConfig(name="tiny", stage="ABX", steps=50, batch=4, micro=4, seq=32, lr=1e-2, warmup=2),
+                       OptConfig(lr=1e-2, norm="hs", scale=0.12, rel_every=2, hs_lag=True), stage="ABX")
+    xs = batches(7, seed=3)
+    a = mk(0)
+    for s in range(3):
+        a.step(xs[s], s)
+    assert any(c is not None and bool((c > 0).any()) for c in a.opt.cs)
+    ck = Checkpointer(str(tmp_path), rid="lag")
+    ck.save(a, 3)
+    ck.wait()
+    want = [float(a.step(xs[s], s)) for s in range(3, 7)]
+    b = mk(5)
+    Checkpointer(str(tmp_path), rid="lag").load(b)
+    assert [float(b.step(xs[s], s)) for s in range(3, 7)] == want
+    st = torch.load(os.path.join(str(tmp_path), "latest.pt"), weights_only=False)
+    assert isinstance(st["opt"]["_lr"], list) and len(st["opt"]["_lr"]) == len(a.opt.param_groups)
+    # a blob with a scalar rate (older files) still loads
+    st["opt"]["_lr"] = float(st["opt"]["_lr"][0])
+    b.opt.load_state_dict(st["opt"])
+    assert b.opt.param_groups[0]["lr"] == st["opt"]["_lr"]
+
+
 KILL_SCRIPT = r"""
 import os, sys, time, torch
 sys.path.insert(0, {root!r})

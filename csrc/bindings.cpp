@@ -56,6 +56,7 @@ torch::Tensor embed_sum_fwd(torch::Tensor emb, torch::Tensor x, c10::optional<to
                             c10::optional<torch::Tensor> phr, c10::optional<torch::Tensor> pidx);
 std::vector<torch::Tensor> embed_sum_bwd(torch::Tensor dh, torch::Tensor emb, torch::Tensor x, c10::optional<torch::Tensor> cand,
                                          c10::optional<torch::Tensor> sel, int64_t P, c10::optional<torch::Tensor> pidx);
+torch::Tensor table_pair_dot(torch::Tensor A, torch::Tensor Bt, torch::Tensor ia, torch::Tensor ib);
 torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Tensor k_tok, torch::Tensor real, torch::Tensor dw,
                             c10::optional<torch::Tensor> dprobs, c10::optional<torch::Tensor> dpsum);
 }  // namespace mb
@@ -101,6 +102,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mem_read_bwd", &mb::mem_read_bwd);
   m.def("moe_route_fwd", &mb::moe_route_fwd);
   m.def("moe_route_bwd", &mb::moe_route_bwd);
+  m.def("table_pair_dot", &mb::table_pair_dot, "out[n] = <A[ia[n]], B[ib[n]]>");
   m.def("embed_sum_fwd", &mb::embed_sum_fwd, "token + gated candidate + phrase rows in one gather-sum");
   m.def("embed_sum_bwd", &mb::embed_sum_bwd, "gradient rows scattered into the tables, d sel");
 }

@@ -78,6 +78,59 @@ __global__ void embed_sum_bwd_kernel(const float* __restrict__ dh, const float* 
   }
 }
 
+// out[n] = <A[ia[n]], B[ib[n]]> in fp32; tables fp32 or bf16 (same dtype); one warp per n
+template <typename T>
+__global__ void table_pair_dot_kernel(const T* __restrict__ A, const T* __restrict__ Bt, const long long* __restrict__ ia,
+                                      const long long* __restrict__ ib, float* __restrict__ out, long long N, int d) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long n = warp; n < N; n += nwarps) {
+    const T* a = A + ia[n] * d;
+    const T* b = Bt + ib[n] * d;
+    float acc = 0.f;
+    for (int c = lane * 4; c < d; c += 128) {
+      float4 x, y;
+      if (sizeof(T) == 2) {
+        const uint2 ux = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(a) + c);
+        const uint2 uy = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(b) + c);
+        const float2 x0 = unpack_bf16(ux.x), x1 = unpack_bf16(ux.y), y0 = unpack_bf16(uy.x), y1 = unpack_bf16(uy.y);
+        x = make_float4(x0.x, x0.y, x1.x, x1.y); y = make_float4(y0.x, y0.y, y1.x, y1.y);
+      } else {
+        x = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a) + c);
+        y = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(b) + c);
+      }
+      acc += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[n] = acc;
+  }
+}
+
+torch::Tensor table_pair_dot(torch::Tensor A, torch::Tensor Bt, torch::Tensor ia, torch::Tensor ib) {
+  const c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.dim() == 2 && Bt.dim() == 2 && A.is_contiguous() && Bt.is_contiguous() && A.size(1) == Bt.size(1) &&
+              A.scalar_type() == Bt.scalar_type() && A.size(1) % 4 == 0, "table_pair_dot: two (rows, d) tables of one dtype, d % 4 == 0");
+  TORCH_CHECK(A.scalar_type() == torch::kFloat32 || A.scalar_type() == torch::kBFloat16, "table_pair_dot: fp32 or bf16 tables");
+  TORCH_CHECK(ia.scalar_type() == torch::kInt64 && ib.scalar_type() == torch::kInt64 && ia.is_contiguous() && ib.is_contiguous() &&
+              ia.numel() == ib.numel(), "table_pair_dot: two contiguous int64 index tensors of one size");
+  const long long N = ia.numel();
+  auto out = torch::empty(ia.sizes(), A.options().dtype(torch::kFloat32));
+  if (N) {
+    const int grid = (int)std::min<long long>((N * 32 + 255) / 256, 148 * 16);
+    const long long* pa = reinterpret_cast<const long long*>(ia.data_ptr<int64_t>());
+    const long long* pb = reinterpret_cast<const long long*>(ib.data_ptr<int64_t>());
+    if (A.scalar_type() == torch::kBFloat16)
+      table_pair_dot_kernel<bf16><<<grid, 256, 0, es()>>>(reinterpret_cast<const bf16*>(A.data_ptr()), reinterpret_cast<const bf16*>(Bt.data_ptr()),
+                                                         pa, pb, out.data_ptr<float>(), N, (int)A.size(1));
+    else
+      table_pair_dot_kernel<float><<<grid, 256, 0, es()>>>(A.data_ptr<float>(), Bt.data_ptr<float>(), pa, pb, out.data_ptr<float>(), N,
+                                                          (int)A.size(1));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  }
+  return out;
+}
+
 static void check_idx(const torch::Tensor& t, const char* what) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt64 && t.is_contiguous(), "embed_sum: ", what, " must be contiguous int64");
 }

@@ -206,8 +206,8 @@ class MemArchLM(nn.Module):
         if c.opaque and "ent" in ph:
             self.register_buffer("ent_t", ph["ent"].float(), persistent=False)
         if c.surp_phrase:
-            self.register_buffer("sp_E", ((E / rms) * c.phrase_c).to(torch.bfloat16), persistent=False)
-            self.register_buffer("sp_H", H.to(torch.bfloat16), persistent=False)
+            self.register_buffer("sp_E", ((E / rms) * c.phrase_c).to(torch.bfloat16).contiguous(), persistent=False)
+            self.register_buffer("sp_H", H.to(torch.bfloat16).contiguous(), persistent=False)
             self.register_buffer("sp_lp", ph["logp_next"].float(), persistent=False)
             self.register_buffer("sp_lse", ph["lse"].float(), persistent=False)
 
@@ -268,7 +268,12 @@ class MemArchLM(nn.Module):
         n = self.sp_lse.numel()
         ok = (xp < n) & (xc < n)
         xp, xc = xp.clamp(max=n - 1), xc.clamp(max=n - 1)
-        lo = (self.sp_E[xp].float() * self.sp_H[xc].float()).sum(-1) + self.sp_lp[xc]
+        if (ops._ext.use_cuda(self.sp_E) and self.sp_E.dtype == self.sp_H.dtype and self.sp_E.shape[1] % 4 == 0
+                and self.sp_E.is_contiguous() and self.sp_H.is_contiguous()):
+            ops._ext.count()                          # one gather-dot kernel instead of two row gathers, a product and a sum
+            lo = ops._ext.C().table_pair_dot(self.sp_E, self.sp_H, xp.contiguous(), xc.contiguous()) + self.sp_lp[xc]
+        else:
+            lo = (self.sp_E[xp].float() * self.sp_H[xc].float()).sum(-1) + self.sp_lp[xc]
         s_[:, 1:] = torch.where(ok, self.sp_lse[xp] - lo, torch.full_like(lo, 1e4))
         return s_
 
@@ -325,7 +330,10 @@ class MemArchLM(nn.Module):
             else:
                 cand, on, bk, src = self._locks_raw(x)
             if hasattr(self, "lock_w"):
-                val = torch.stack([on[..., k].float() * self.lock_w[k][bk] for k in range(on.shape[-1])], -1)
+                # index_select: its backward is an index_add (atomics on 7 values), not the sort-based index_put of `w[bk]`
+                bkf = bk.reshape(-1)
+                val = torch.stack([on[..., k].float() * self.lock_w[k].index_select(0, bkf).view_as(bk)
+                                   for k in range(on.shape[-1])], -1)
             else:
                 val = on.float() * self.ind_a[:on.shape[-1]]
             self._tongue = (cand, val)
@@ -333,7 +341,8 @@ class MemArchLM(nn.Module):
                 anyon = on.any(-1)
                 kk = on.float().argmax(-1)
                 c1 = (cand * on).sum(-1)
-                g = torch.sigmoid(self.mix_w[kk, bk]) * anyon
+                nb_ = self.mix_w.shape[1]
+                g = torch.sigmoid(self.mix_w.reshape(-1).index_select(0, (kk * nb_ + bk).reshape(-1)).view_as(bk)) * anyon
                 self._mix = (c1, g)
                 self.stats["mix_g"] = (g.sum() / anyon.sum().clamp(min=1)).detach()
             tw = self.lock_w if hasattr(self, "lock_w") else self.ind_a

@@ -37,7 +37,8 @@ class _ErrProbe(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         with torch.no_grad():
-            ctx.buf.mul_(0.9).add_(0.1 * g.float().norm(dim=-1).mean(1))
+            # fp32 accumulation straight from the bf16 gradient: no fp32 copy of the (E, C, d) tensor
+            ctx.buf.mul_(0.9).add_(0.1 * torch.linalg.vector_norm(g, dim=-1, dtype=torch.float32).mean(1))
         return g, None
 
 

@@ -298,6 +298,7 @@ def run_ours(args):
              {"parallel_detail": "replicated weights + expert parallel" if world > 1 else "single",
               "mode": args.mode if world > 1 else "single", "selftest": selftest,
               "loss_first": round(first, 4), "loss_last": round(last, 4), "kernel_status": st, "peer_status": peer_st,
+              "losses": [round(float(l), 4) for l in losses[:16]],
               "launches_per_step": round(per_step_launches, 1), "cuda_graph": bool(args.graph) and not tr._graph_failed,
               "params_b": round(sum(p.numel() for p in model.parameters()) / 1e9, 3),
               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),

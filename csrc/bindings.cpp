@@ -13,6 +13,8 @@ torch::Tensor gemm_peer(std::vector<int64_t> a_ptrs, int64_t seg_M, int64_t K, i
                         c10::optional<torch::Tensor> out2, c10::optional<torch::Tensor> aux, int64_t epi, int64_t groups);
 void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t channel, double timeout_ms);
 int64_t peer_status_read();
+void peer_reduce_to_local(std::vector<int64_t> in_ptrs, int64_t mc_in, torch::Tensor dst, int64_t offset, double scale);
+void peer_broadcast_from_local(std::vector<int64_t> out_ptrs, int64_t mc_out, int64_t offset_bytes, int64_t nbytes, int64_t rank);
 void peer_gather(std::vector<int64_t> src_ptrs, torch::Tensor dst, int64_t rank, int64_t C, int64_t g_off);
 void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,
                     int64_t numel, bool is_bf16, int64_t rank, double scale);
@@ -37,7 +39,7 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
                       c10::optional<torch::Tensor> cs, torch::Tensor gvec, int64_t index, torch::Tensor stake,
                       torch::Tensor lr_t, c10::optional<torch::Tensor> rel, double beta, double wd, int64_t kind, bool sr,
                       torch::Tensor seed_t, c10::optional<torch::Tensor> frozen, c10::optional<torch::Tensor> scratch,
-                      c10::optional<torch::Tensor> cs_ok, c10::optional<torch::Tensor> shadow);
+                      c10::optional<torch::Tensor> cs_ok, c10::optional<torch::Tensor> shadow, int64_t phase, int64_t col_rows);
 std::vector<torch::Tensor> anchor_select(torch::Tensor s, torch::Tensor tau, int64_t A);
 std::vector<torch::Tensor> moe_slots(torch::Tensor e_flat, int64_t E, int64_t C);
 std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_keys, bool longest_only);
@@ -70,6 +72,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_peer", &mb::gemm_peer, "segmented GEMM: A tiles from peer buffers, result rows to the owners' buffers");
   m.def("peer_barrier", &mb::peer_barrier, "bounded device-side barrier over symmetric flags");
   m.def("peer_status_read", &mb::peer_status_read);
+  m.def("peer_reduce_to_local", &mb::peer_reduce_to_local, "this rank's slice of a staged buffer summed over all ranks into local memory");
+  m.def("peer_broadcast_from_local", &mb::peer_broadcast_from_local, "this rank's slice of a symmetric buffer written to every peer");
   m.def("peer_gather", &mb::peer_gather, "rows of this rank's experts from every rank's dispatch buffer, one kernel");
   m.def("peer_allreduce", &mb::peer_allreduce, "one-shot all-reduce by peer loads/stores or NVLS multimem");
   m.def("rmsnorm_fwd", &mb::rmsnorm_fwd);
@@ -90,7 +94,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("cs"), pybind11::arg("gvec"), pybind11::arg("index"), pybind11::arg("stake"), pybind11::arg("lr_t"),
         pybind11::arg("rel"), pybind11::arg("beta"), pybind11::arg("wd"), pybind11::arg("kind"), pybind11::arg("sr"),
         pybind11::arg("seed_t"), pybind11::arg("frozen"), pybind11::arg("scratch") = pybind11::none(),
-        pybind11::arg("cs_ok") = pybind11::none(), pybind11::arg("shadow") = pybind11::none());
+        pybind11::arg("cs_ok") = pybind11::none(), pybind11::arg("shadow") = pybind11::none(), pybind11::arg("phase") = 0,
+        pybind11::arg("col_rows") = 0);
   m.def("anchor_select", &mb::anchor_select);
   m.def("moe_slots", &mb::moe_slots);
   m.def("lock_find", &mb::lock_find);

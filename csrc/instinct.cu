@@ -33,7 +33,7 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
                       torch::Tensor lr_t, c10::optional<torch::Tensor> rel_, double beta, double wd, int64_t kind,
                       bool sr, torch::Tensor seed_t, c10::optional<torch::Tensor> frozen_,
                       c10::optional<torch::Tensor> scratch_, c10::optional<torch::Tensor> cs_ok_,
-                      c10::optional<torch::Tensor> shadow_) {
+                      c10::optional<torch::Tensor> shadow_, int64_t phase, int64_t col_rows) {
   const c10::cuda::CUDAGuard guard(p.device());
   TORCH_CHECK(p.is_contiguous() && grad.is_contiguous() && m.is_contiguous(), "instinct_step: contiguous tensors");
   TORCH_CHECK(grad.numel() == p.numel() && m.numel() == p.numel(), "instinct_step: shape mismatch");
@@ -85,11 +85,13 @@ int64_t instinct_step(torch::Tensor p, torch::Tensor grad, torch::Tensor m, c10:
     TORCH_CHECK(scratch_->scalar_type() == torch::kFloat32 && scratch_->is_contiguous() &&
                 (reinterpret_cast<uintptr_t>(scratch_->data_ptr()) & 15) == 0, "instinct_step: scratch arena");
     scratch = *scratch_;
-    C10_CUDA_CHECK(cudaMemsetAsync(scratch.data_ptr(), 0, sizeof(float) * (size_t)need, cur_stream()));
+    if (phase != 2)          // phase 2 continues on the statistics phase 1 left (and the caller summed over the ranks)
+      C10_CUDA_CHECK(cudaMemsetAsync(scratch.data_ptr(), 0, sizeof(float) * (size_t)need, cur_stream()));
   } else {
+    TORCH_CHECK(phase == 0, "instinct_step: a split step needs the caller's scratch arena");
     scratch = torch::zeros({need}, p.options().dtype(torch::kFloat32));
   }
-  const int64_t n = instinct_launch(a, (int)kind, scratch.data_ptr<float>(), rel, cur_stream(), cs, cs_ok);
+  const int64_t n = instinct_launch(a, (int)kind, scratch.data_ptr<float>(), rel, cur_stream(), cs, cs_ok, (int)phase, col_rows);
   TORCH_CHECK(n >= 0, "instinct_step: a row of ", C, " columns is too long for this kind on the kernels");
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return n;

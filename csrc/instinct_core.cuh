@@ -482,8 +482,12 @@ constexpr size_t INSTINCT_SMEM_MAX = 200 * 1024;     // dynamic shared memory th
 // Launch sequence; returns the number of kernels launched, or -1 when this weight cannot take the requested form
 // (nothing is launched then).  `cs` / `cs_ok`: lagged homeostasis state (previous step's second-axis mean squares and
 // the "all positive" flag), or null for the exact form.
+// `phase` / `col_rows` serve a weight whose rows are split between ranks (kind hs only): phase 1 launches the
+// statistics of this rank's rows and stops (the caller then sums the column sums - and the |g|/|w| sums - over the
+// ranks, in place in `scratch`), phase 2 launches the update alone; `col_rows` is the row count of the whole weight
+// (what a column sum is divided by).  phase 0 = everything, col_rows 0 = the rows of `a`.
 inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, float* rel_out, cudaStream_t st,
-                               float* cs = nullptr, int* cs_ok = nullptr) {
+                               float* cs = nullptr, int* cs_ok = nullptr, int phase = 0, long long col_rows = 0) {
   const long long ER = a.E * a.R, EC = a.E * a.C, n = ER * a.C;
   const long long ERp = instinct_pad4(ER), ECp = instinct_pad4(EC);
   float* rowA = scratch;
@@ -498,8 +502,9 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
                    (a.shadow == nullptr || (reinterpret_cast<uintptr_t>(a.shadow) & 7) == 0) && (EC % 4 == 0 || a.E == 1);
   int64_t launches = 0;
   const int E = (int)a.E;
-  const float Rf = (float)a.R, Cf = (float)a.C;
+  const float Rf = (float)(col_rows > 0 ? col_rows : a.R), Cf = (float)a.C;
   const size_t Cb = (size_t)a.C * sizeof(float);
+  if (phase != 0 && (kind != 4 || cs)) return -1;
   const bool stage1 = Cb <= INSTINCT_SMEM_MAX, stage2 = 2 * Cb <= INSTINCT_SMEM_MAX, stage3 = 3 * Cb <= INSTINCT_SMEM_MAX;
   if ((kind == 4 || kind == 5) && !stage1) return -1;          // column scales are staged in shared memory
   if (kind == 4 && cs && !stage3) return -1;                   // lagged hs stages three rows
@@ -548,7 +553,7 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
     else { raise(instinct_apply<1>, smem); instinct_apply<1><<<grid, row_threads, smem, st>>>(a, rs, Cf, rs2, c1, c2, Rf, fuse ? 1 : 0, rabs, rel2, rel_out); }
     ++launches;
   };
-  if (rel_out) {
+  if (rel_out && phase != 2) {
     const int grid = (int)std::max<long long>(1, std::min<long long>((n + 255) / 256, 148 * 8));
     instinct_rel_sums<<<grid, 256, 0, st>>>(a, rel2);
     ++launches;
@@ -565,8 +570,11 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
         launches += 2;
         break;
       }
-      stat_rows(nullptr, rowA, nullptr);
-      stat_cols(nullptr, rowA, colA);
+      if (phase != 2) {
+        stat_rows(nullptr, rowA, nullptr);
+        stat_cols(nullptr, rowA, colA);
+      }
+      if (phase == 1) break;
       if (stage2) {
         apply(rowA, nullptr, colA, nullptr, true, nullptr);        // the last row norm on the row staged in shared memory
       } else {

@@ -198,6 +198,106 @@ __global__ void allreduce_nvls_kernel(const void* mc_in, void* mc_out, long long
   }
 }
 
+// ------------------------------------------------------------------------------------------------ reduce-scatter / all-gather halves
+// reduce_to_local: dst[i] = scale * sum_q in_q[offset + i] for i in [0, numel) - this rank's slice of a staged
+// gradient summed over all ranks into LOCAL memory (the reduce-scatter half; multimem.ld_reduce when `mc_in`).
+template <bool BF16>
+__global__ void reduce_to_local_kernel(PeerPtrs in, const void* mc_in, void* __restrict__ dst, long long offset, long long numel,
+                                       int world, float scale) {
+  constexpr int PER = BF16 ? 8 : 4;
+  const long long n16 = numel / PER;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+    const long long off = offset + i * PER;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (mc_in) {
+      if (BF16) {
+        uint32_t a, b, c, d;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(reinterpret_cast<const bf16*>(mc_in) + off) : "memory");
+        float2 f0 = unpack_bf16(a), f1 = unpack_bf16(b), f2 = unpack_bf16(c), f3 = unpack_bf16(d);
+        acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+      } else {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(acc[0]), "=f"(acc[1]), "=f"(acc[2]), "=f"(acc[3]) : "l"(reinterpret_cast<const float*>(mc_in) + off) : "memory");
+      }
+    } else {
+#pragma unroll 1
+      for (int q = 0; q < world; ++q) {
+        if (BF16) {
+          uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(in.p[q]) + off);
+          const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        } else {
+          float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in.p[q]) + off);
+          acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+        }
+      }
+    }
+    if (BF16) {
+      *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + i * PER) =
+          make_uint4(pack_bf16(acc[0] * scale, acc[1] * scale), pack_bf16(acc[2] * scale, acc[3] * scale),
+                     pack_bf16(acc[4] * scale, acc[5] * scale), pack_bf16(acc[6] * scale, acc[7] * scale));
+    } else {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + i * PER) =
+          make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
+    }
+  }
+}
+
+void peer_reduce_to_local(std::vector<int64_t> in_ptrs, int64_t mc_in, torch::Tensor dst, int64_t offset, double scale) {
+  const int W = (int)in_ptrs.size();
+  TORCH_CHECK(W >= 1 && W <= 8, "peer_reduce_to_local: 1..8 ranks");
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && (dst.scalar_type() == torch::kBFloat16 || dst.scalar_type() == torch::kFloat32),
+              "peer_reduce_to_local: contiguous bf16 / fp32 destination");
+  const bool bf = dst.scalar_type() == torch::kBFloat16;
+  const int per = bf ? 8 : 4;
+  const long long numel = dst.numel();
+  TORCH_CHECK(offset % per == 0 && numel % per == 0, "peer_reduce_to_local: 16-byte units");
+  if (!numel) return;
+  const c10::cuda::CUDAGuard guard(dst.device());
+  PeerPtrs in{};
+  for (int i = 0; i < W; ++i) in.p[i] = reinterpret_cast<void*>(in_ptrs[i]);
+  const int grid = (int)std::min<long long>((numel / per + 255) / 256, 148 * 4);
+  if (bf) reduce_to_local_kernel<true><<<grid, 256, 0, cur_stream()>>>(in, reinterpret_cast<const void*>(mc_in), dst.data_ptr(), offset, numel, W, (float)scale);
+  else reduce_to_local_kernel<false><<<grid, 256, 0, cur_stream()>>>(in, reinterpret_cast<const void*>(mc_in), dst.data_ptr(), offset, numel, W, (float)scale);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// broadcast_from_local: out_q[offset + i] = this rank's out[offset + i] for every OTHER rank q (the all-gather half:
+// this rank's rows of an updated weight to all peers; one multimem.st per 16 bytes when `mc_out`, which also rewrites
+// the local copy with the same bytes).
+__global__ void broadcast_from_local_kernel(PeerPtrs out, void* mc_out, long long offset16, long long n16, int world, int rank) {
+  const uint4* src = reinterpret_cast<const uint4*>(out.p[rank]) + offset16;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    if (mc_out) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(reinterpret_cast<uint4*>(mc_out) + offset16 + i),
+                   "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+    } else {
+      for (int q = 1; q < world; ++q) {
+        const int t = (rank + q) % world;
+        *(reinterpret_cast<uint4*>(out.p[t]) + offset16 + i) = v;
+      }
+    }
+  }
+}
+
+// out_ptrs: per-rank base pointers of one symmetric buffer; [offset_bytes, offset_bytes + nbytes) of this rank's copy
+// goes to every rank.
+void peer_broadcast_from_local(std::vector<int64_t> out_ptrs, int64_t mc_out, int64_t offset_bytes, int64_t nbytes, int64_t rank) {
+  const int W = (int)out_ptrs.size();
+  TORCH_CHECK(W >= 1 && W <= 8, "peer_broadcast_from_local: 1..8 ranks");
+  TORCH_CHECK(offset_bytes % 16 == 0 && nbytes % 16 == 0, "peer_broadcast_from_local: 16-byte units");
+  if (!nbytes || W == 1) return;
+  PeerPtrs out{};
+  for (int i = 0; i < W; ++i) out.p[i] = reinterpret_cast<void*>(out_ptrs[i]);
+  const long long n16 = nbytes / 16;
+  const int grid = (int)std::min<long long>((n16 + 255) / 256, 148 * 4);
+  broadcast_from_local_kernel<<<grid, 256, 0, cur_stream()>>>(out, reinterpret_cast<void*>(mc_out), offset_bytes / 16, n16, W, (int)rank);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 // in/out: per-rank base pointers of two symmetric buffers; the region is [offset, offset + numel) elements of `bf16` or
 // fp32.  mc_in / mc_out non-zero selects the NVLS path.  The caller brackets this with peer barriers.
 void peer_allreduce(std::vector<int64_t> in_ptrs, std::vector<int64_t> out_ptrs, int64_t mc_in, int64_t mc_out, int64_t offset,

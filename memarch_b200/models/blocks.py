@@ -92,6 +92,11 @@ class LightBlock(nn.Module):
             self.moe = FineMoE(d, E, k)
             del self.up, self.down
         self.cur_ve = self.cur_x0 = self.cur_sel = None
+        for nm in ("qkv", "o", "up", "down"):
+            if hasattr(self, nm):
+                # used once per step through a bf16 shadow: the data-parallel engine may keep its optimizer state
+                # and update row-sharded across the ranks
+                getattr(self, nm).weight._shard_ok = True
 
     def _act(self, h):
         return ops.relu2(h) if self.relu2 else ops.swiglu(h)

@@ -213,9 +213,12 @@ class _WeightBf16(torch.autograd.Function):
     def forward(ctx, w):
         ctx.w = w
         sh = getattr(w, "_bf16_shadow", None)
-        if sh is None or getattr(w, "_shadow_ver", None) != w._version or sh.shape != w.shape:
+        if sh is None or sh.shape != w.shape:
             sh = w.detach().to(torch.bfloat16)
             w._bf16_shadow, w._shadow_ver = sh, w._version
+        elif getattr(w, "_shadow_ver", None) != w._version:
+            sh.copy_(w.detach())                   # refreshed in place: the buffer may be one that other ranks write into
+            w._shadow_ver = w._version
         return sh.detach()
 
     @staticmethod

@@ -327,7 +327,9 @@ class Instinct:
         return upd / (upd.pow(2).mean(1, keepdim=True).sqrt() + 1e-8)
 
     def _arena(self, p, kind):
-        """One fp32 scratch arena per device for the row / column statistics, sized for the largest weight seen."""
+        """One fp32 scratch arena per (device, stream) for the row / column statistics, sized for the largest weight
+        seen there.  Per stream, because the data-parallel engine steps replicated weights on a side stream while the
+        expert weights are stepped on the main one: two steps in flight must not share their statistics."""
         if kind in ("hs", "vocab"):
             E, R, Cn = 1, p.shape[0], p.shape[1]
         elif kind in ("hs3", "row3"):
@@ -337,7 +339,7 @@ class Instinct:
         else:
             E, R, Cn = 1, 1, p.numel()
         need = 3 * ((E * R + 3) // 4 * 4) + 2 * ((E * Cn + 3) // 4 * 4) + 4
-        key = ("arena", p.device)
+        key = ("arena", p.device, torch.cuda.current_stream(p.device).cuda_stream)
         cur = self._scratch.get(key)
         if cur is None or cur.numel() < need:
             cur = self._scratch[key] = torch.empty(max(need, 1 << 16), device=p.device, dtype=torch.float32)
@@ -363,6 +365,41 @@ class Instinct:
                             self.rel if want_rel else None, float(self.beta), float(wd), _kind_code(kind),
                             bool(self.sr), self._seed_t, fr, self._arena(p, kind), self.cs_ok[i] if lag else None,
                             getattr(p, "_bf16_shadow", None))
+        _ext.count(int(n) + 1)
+
+    def can_shard(self, p):
+        """True when `update_sharded` can step this weight: a 2-D weight of kind "hs" - bf16 with its exact fp32 copy
+        here, or fp32 (the caller provides the bf16 shadow the GEMMs read) - none of the per-tensor brakes (they need
+        whole-tensor sums) and no lag / offload / stochastic rounding."""
+        c = self.cfg
+        i = self.idx[id(p)]
+        layout = (p.dtype == torch.bfloat16 and self.w[i] is not None) or (p.dtype == torch.float32 and self.w[i] is None)
+        return (p.dim() == 2 and layout and self.spec(p)[0] == "hs" and not self.hs_lag and not self.offload
+                and not self.sr and self.dv is None and self.snr_v is None and c.surge_thr <= 0)
+
+    @torch.no_grad()
+    def update_sharded(self, p, g_rows, r0, r1, scratch, shadow_rows, exchange):
+        """Step rows [r0, r1) of a weight whose rows are split between the ranks (the reference's kind `hsS`,
+        exp_opt.py:271-280: rows are local, a column's norm is a sum over all ranks).  `g_rows` is the rank-mean
+        gradient of these rows, `scratch` an fp32 arena every rank can reach (the statistics are summed in place),
+        `shadow_rows` the rows of the bf16 copy the GEMMs read (None for a bf16 weight: it is its own), `exchange(offset, count)` sums `scratch[offset:
+        offset + count]` over the ranks (device-side, on the current stream).  Momentum and the fp32 weight are touched
+        in these rows only: every other row of `p` and of the momentum is another rank's to keep."""
+        C = _ext.C()
+        i = self.idx[id(p)]
+        self._sync_lr()
+        kind, wd, _ = self.spec(p)
+        want_rel = self.n_step % self.rel_every == 0
+        wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
+        R, Cn = r1 - r0, p.shape[1]
+        pr, mr = p[r0:r1], self.m[i][r0:r1]
+        wr = self.w[i][r0:r1] if self.w[i] is not None else None
+        args = (wr, None, self.g, int(i), self.stake, self._lr_t, self.rel if want_rel else None, float(self.beta),
+                float(wd_v), _kind_code("hs"), False, self._seed_t, None, scratch, None, shadow_rows)
+        n = C.instinct_step(pr, g_rows, mr, *args, 1, int(p.shape[0]))
+        pad4 = lambda v: (v + 3) // 4 * 4
+        exchange(3 * pad4(R), 2 * pad4(Cn) + 4)                 # column sums (and the |g|, |w| sums behind them)
+        n += C.instinct_step(pr, g_rows, mr, *args, 2, int(p.shape[0]))
         _ext.count(int(n) + 1)
 
     def _update_rows(self, i, p, grad, rows, lr_t):

@@ -220,6 +220,11 @@ class ParallelEngine:
         if self.fused_impl is not None:
             self.fused_impl.attach(trainer)
 
+    def before_checkpoint(self):
+        """Make every rank's copy of the row-sharded weights and their momentum whole (collective)."""
+        if self.fused_impl is not None:
+            self.fused_impl.dp.materialize()
+
     def check(self):
         """Raise if a bounded peer wait (barrier) ran out since the last check.  Host sync: call it where the loop
         already waits for the device (log interval, before a checkpoint, end of a benchmark)."""

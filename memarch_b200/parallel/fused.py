@@ -215,7 +215,17 @@ class FusedExpertExchange:
 
 
 class FusedGradReduce:
-    """Data-parallel gradient mean fused with the optimizer step, on a side stream that overlaps backward."""
+    """Data-parallel gradient exchange fused with the optimizer step, on a side stream that overlaps backward.
+
+    Two forms.  Row-sharded (`MEMARCH_DP_SHARD`, default on; the 2-D "hs" weights whose GEMMs read a bf16 matrix -
+    the weight itself under BF16_W, else the bf16 shadow of the light-block linears): the reduce-scatter + update + all-gather of the reference's FSDP path (fastloop.py:269-307)
+    with the cross-shard column norms of its `hsS` kind (exp_opt.py:271-280).  Rank r owns rows [r R/W, (r+1) R/W) of
+    every such weight: it sums those rows of the staged gradients from all ranks into local memory (`multimem.ld_reduce`
+    or peer loads), runs the Instinct statistics on them, the ranks sum the column sums in place in a symmetric
+    scratch (one tiny one-shot all-reduce), the update writes momentum and fp32 weight of these rows only, and the new
+    bf16 rows go to every rank's shadow (`multimem.st` or peer stores) - optimizer work and touched optimizer state
+    are 1/W per rank, and the weight all-gather is the store of the update.  Replicated (everything else): one-shot
+    all-reduce of the gradient, then the full Instinct step on every rank."""
 
     def __init__(self, heap, nvls=True):
         self.heap, self.W, self.rank = heap, heap.W, heap.rank
@@ -227,6 +237,8 @@ class FusedGradReduce:
         self.trainer = None
         self.used = False
         self.cap = 0
+        self.shard = os.environ.get("MEMARCH_DP_SHARD", "1") != "0"
+        self.sharded = {}            # id(param) -> (byte offset of its shadow, rows per rank)
 
     def allocate(self, params):
         """Symmetric staging (each rank's gradient) and result (the rank mean) regions for every replicated weight."""
@@ -246,6 +258,68 @@ class FusedGradReduce:
             self.mc_out = int(self.gout_h.multicast_ptr) if mc_ok else 0
         except Exception:     # noqa: BLE001
             self.mc_in = self.mc_out = 0
+        self._allocate_shards(params, mc_ok)
+
+    def _allocate_shards(self, params, mc_ok):
+        """The bf16 matrices the GEMMs read (the weight itself when it lives in bf16 with an fp32 copy in the optimizer,
+        else its bf16 shadow) move into one symmetric buffer, because peers write their rows into them; plus the
+        symmetric statistics scratch and a local buffer for this rank's reduced gradient rows."""
+        opt, W = self.trainer.opt, self.W
+        if not self.shard:
+            return
+        todo = [p for p in params if not getattr(p, "_ep_local", False) and opt.can_shard(p)
+                and (p.dtype == torch.bfloat16 or getattr(p, "_shard_ok", False))
+                and p.numel() >= 4096 and p.shape[0] % W == 0 and (p.shape[0] // W * p.shape[1]) % 8 == 0]
+        if not todo:
+            return
+        tot = sum((p.numel() * 2 + 255) // 256 * 256 for p in todo)
+        self.wsh, self.wsh_h = self.heap.alloc((tot,), torch.uint8)
+        self.wsh_ptrs = [int(x) for x in self.wsh_h.buffer_ptrs]
+        try:
+            self.mc_wsh = int(self.wsh_h.multicast_ptr) if mc_ok else 0
+        except Exception:     # noqa: BLE001
+            self.mc_wsh = 0
+        need = max(3 * ((p.shape[0] // W + 3) // 4 * 4) + 2 * ((p.shape[1] + 3) // 4 * 4) + 4 for p in todo)
+        self.scr, self.scr_h = self.heap.alloc(((need + 63) // 64 * 64,), torch.float32)
+        self.scr_ptrs = [int(x) for x in self.scr_h.buffer_ptrs]
+        self.gred = torch.empty(max(p.numel() // W for p in todo), device=self.wsh.device, dtype=torch.bfloat16)
+        off = 0
+        with torch.no_grad():
+            for p in todo:
+                sh = self.wsh[off:off + p.numel() * 2].view(torch.bfloat16).view(p.shape)
+                sh.copy_(p.detach())
+                if p.dtype == torch.bfloat16:
+                    p.data = sh                                   # the parameter itself now lives where peers can write
+                else:
+                    p._bf16_shadow, p._shadow_ver = sh, p._version
+                self.sharded[id(p)] = (off, p.shape[0] // W)
+                off += (p.numel() * 2 + 255) // 256 * 256
+        self.heap.barrier(0)
+
+    def _exchange(self, offset, count):
+        """Sum `count` floats at `offset` of the symmetric statistics scratch over the ranks, in place (every rank
+        reduces its own 1/W of the range from all peers and writes it back to all of them)."""
+        if self.W == 1:
+            return
+        self.heap.barrier(1)
+        _ext.C().peer_allreduce(self.scr_ptrs, self.scr_ptrs, 0, 0, offset, count, False, self.rank, 1.0)
+        _ext.count()
+        self.heap.barrier(1)
+
+    def materialize(self):
+        """fp32 weights and momentum of the row-sharded weights are current only in the owner's rows; before anything
+        reads them whole (a checkpoint in the single-file layout, an evaluation that bypasses the shadows) the ranks
+        exchange their rows.  Collective; not on the training path."""
+        if not self.sharded or self.W == 1:
+            return
+        opt = self.trainer.opt
+        for p in self.trainer.params:
+            if id(p) in self.sharded:
+                i = opt.idx[id(p)]
+                whole = [opt.m[i]] + ([opt.w[i]] if opt.w[i] is not None else [p.data])
+                for t in whole:
+                    parts = list(t.chunk(self.W, 0))
+                    dist.all_gather(parts, parts[self.rank].clone(), group=self.heap.group)
 
     def _region(self, p, grad):
         k = id(p)
@@ -272,6 +346,22 @@ class FusedGradReduce:
         ev.record()
         C = _ext.C()
         heap = self.heap
+        sh = self.sharded.get(id(p)) if grad.dtype == torch.bfloat16 else None
+        if sh is not None:
+            woff, rows = sh
+            r0, r1 = self.rank * rows, (self.rank + 1) * rows
+            cols = p.shape[1]
+            with torch.cuda.stream(self.stream):
+                self.stream.wait_event(ev)
+                heap.barrier(1)                                      # every rank has staged this weight's gradient
+                g_rows = self.gred[:rows * cols].view(rows, cols)
+                C.peer_reduce_to_local(self.in_ptrs, self.mc_in, g_rows, off // es + r0 * cols, 1.0 / self.W)
+                self.trainer.opt.update_sharded(p, g_rows, r0, r1, self.scr,
+                                                None if p.dtype == torch.bfloat16 else p._bf16_shadow[r0:r1], self._exchange)
+                C.peer_broadcast_from_local(self.wsh_ptrs, self.mc_wsh, woff + r0 * cols * 2, rows * cols * 2, self.rank)
+                _ext.count(2)
+            self.used = self.pushed = True
+            return None
         with torch.cuda.stream(self.stream):
             self.stream.wait_event(ev)
             heap.barrier(1)                                          # every rank has staged this weight's gradient
@@ -298,6 +388,9 @@ class FusedGradReduce:
         if self.used:
             torch.cuda.current_stream().wait_stream(self.stream)
             self.used = False
+        if getattr(self, "pushed", False):
+            self.heap.barrier(0)             # every rank's rows of the updated shadows have landed before the next forward
+            self.pushed = False
 
 
 class FusedParallel:

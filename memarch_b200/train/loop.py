@@ -491,6 +491,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 if ck is not None and ck_every and (step % ck_every == 0 or (step == last and env.get("NO_FINAL_CKPT") != "1")):
                     nan.flush()                                  # never save a state that already went non-finite
                     sync()                                       # nor one made after a device wait ran out
+                    if parallel is not None:
+                        parallel.before_checkpoint()             # rows kept by other ranks come home first
                     tc = time.time()
                     ck.save(tr, step, log, data.state_dict())
                     phase["ckpt"] += time.time() - tc

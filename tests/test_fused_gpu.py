@@ -36,6 +36,8 @@ def _worker(rank, world, port, q):
         if eng.fused_impl is not None:
             eng.fused_impl.heap.check()
             res["selftest"] = eng.fused_impl.selftest()
+            res["n_sharded"] = len(eng.fused_impl.dp.sharded)
+            eng.before_checkpoint()                     # rows of the sharded weights kept by the other rank come home
         res[mode] = (losses, {k: v.detach().float().cpu().numpy() for k, v in m.state_dict().items()
                               if v.dtype.is_floating_point and 0 < v.numel() < 1 << 22})
     q.put((rank, res))
@@ -58,6 +60,7 @@ def test_fused_matches_nccl_on_two_gpus():
         p.join(60)
     for rank, res in out:
         assert res["selftest"] == (True, "ok"), (rank, res["selftest"])
+        assert res["n_sharded"] > 0, "the row-sharded optimizer path was not taken"
         ln, lf = res["nccl"][0], res["fused"][0]
         for a, b in zip(ln, lf):
             assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (rank, ln, lf)
@@ -92,6 +95,7 @@ def _single_rank(q):
         if eng is not None:
             eng.fused_impl.heap.check()
             res["selftest"] = eng.fused_impl.selftest()
+            res["n_sharded"] = len(eng.fused_impl.dp.sharded)
         res[mode] = (losses, {k: v.detach().float().cpu().numpy() for k, v in m.state_dict().items()
                               if v.dtype.is_floating_point and 0 < v.numel() < 1 << 22})
         if eng is not None:
@@ -134,6 +138,7 @@ def test_fused_kernels_on_one_rank_match_plain_path():
     res = q.get(timeout=240)
     p.join(60)
     assert res["selftest"] == (True, "ok"), res["selftest"]          # the pre-run check of the peer paths itself
+    assert res["n_sharded"] > 0, "the row-sharded optimizer path was not taken"
     assert max(res["bank_err"]) < 1e-2, res["bank_err"]              # y, d xe, d up, d down of a layer with frozen experts
     for a, b in zip(res["plain"][0], res["fused"][0]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (res["plain"][0], res["fused"][0])

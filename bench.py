@@ -254,7 +254,7 @@ def run_ours(args):
     if world > 1:
         from memarch_b200.parallel import ParallelEngine
         parallel = ParallelEngine(rank, world, local, fused=args.mode == "fused")
-        if parallel.fused_impl is not None:
+        if parallel.init_fused() is not None:
             # the peer paths are checked on this set of GPUs before the run; if anything is off, the run uses NCCL
             ok, why = parallel.fused_impl.selftest()
             selftest = dict(parallel.fused_impl.selftest_errors, ok=ok)

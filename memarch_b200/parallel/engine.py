@@ -189,13 +189,19 @@ class ParallelEngine:
         import os
         self.dp_mode = os.environ.get("MEMARCH_DP", "fused")           # "fused" | "nccl" (gradient mean of the replicated weights)
 
+    def init_fused(self):
+        """Create the peer-memory machinery (symmetric heap, fused EP and DP objects) if this engine is in fused mode
+        and has none yet; returns it (None in NCCL mode)."""
+        if self.fused and self.fused_impl is None:
+            from .fused import FusedParallel
+            self.fused_impl = FusedParallel(self)
+        return self.fused_impl
+
     # ------------------------------------------------------------------------------------------ model sharding
     def shard_model(self, model):
         """Keep this rank's experts only; replicate the rest (identical init on every rank: same seed)."""
         from ..models.moe import AnchorMoE
-        if self.fused:
-            from .fused import FusedParallel
-            self.fused_impl = FusedParallel(self)
+        self.init_fused()
         for mod in model.modules():
             if isinstance(mod, AnchorMoE):
                 mod.ep_shard(self.rank, self.W, self.fused_impl.ep if self.fused_impl else self.ep)

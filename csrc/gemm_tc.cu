@@ -24,7 +24,7 @@ constexpr int GEMM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int GROUP_M = 8;
 
-enum { EPI_NONE = 0, EPI_RELU2 = 1, EPI_DRELU2 = 2, EPI_SWIGLU = 3, EPI_ROWSCALE = 4 };
+enum { EPI_NONE = 0, EPI_RELU2 = 1, EPI_DRELU2 = 2, EPI_SWIGLU = 3, EPI_ROWSCALE = 4, EPI_DSWIGLU = 5 };
 
 struct GemmParams {
   int M, N, K, G;                 // logical per-group problem; for EPI_SWIGLU N = 2H (B rows), out has H columns
@@ -47,6 +47,7 @@ struct GemmParams {
   // counts: valid extent per group (device ints) - count_mode 1: rows of A/out (tiles wholly past it are not
   // computed and are written as zeros), 2: length of the contraction (k-blocks past it are not read).
   int store_tma, count_mode, dbg, group_m;
+  int aux_tma;             // the aux operand of an epilogue (pre-activations) is prefetched by TMA into the staging tiles
   const int* counts;
 };
 
@@ -448,11 +449,69 @@ __device__ __forceinline__ void epi_send(const GemmParams& p, const EpiRing& rin
   }
 }
 
+// ---- aux prefetch.  The activation-backward epilogues (relu², SwiGLU) multiply the accumulator by a function of the
+// forward's pre-activations, a second operand of the tile's own shape.  Fetching it when the accumulator is ready
+// puts a global-memory round trip (microseconds while the GEMM itself loads HBM) into every 64-column chunk and
+// made the epilogue the bottleneck (dgrad 0.74 ms plain, 1.37 ms with the relu² factor, 3.49 ms with SwiGLU's).  So
+// each epilogue warp keeps a queue of TMA loads `slots` chunks ahead - across tile boundaries, i.e. issued while
+// it waits for the next accumulator - into the very staging tiles the results are later stored from.
+struct AuxPipe {
+  uint64_t* bars;          // this warp's mbarriers, one per slot
+  int slots, nb;           // nb staging tiles per chunk (1: relu² backward, 2: SwiGLU backward), slots = tiles / nb
+  uint32_t issued, consumed;
+  int pf_t, pf_hc;         // cursor of the next chunk to fetch: tile, half * 4 + chunk
+  const CUtensorMap* tm;
+  int rank, q, npairs, total, mh;
+  bool on;
+};
+
+__device__ __forceinline__ void tma_load_3d_local(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ int group_rows(const GemmParams& p, int g);
+__device__ __forceinline__ int group_kblocks(const GemmParams& p, int g);
+
+// Issue loads until `slots` chunks are in flight or the tile list ends.  Walks tiles and chunks exactly as the
+// epilogue does (padding tiles and chunks past the last column are skipped).  Lane 0 only.
+__device__ __forceinline__ void aux_issue(const GemmParams& p, AuxPipe& a, uint8_t* ring_base) {
+  while (a.issued - a.consumed < (uint32_t)a.slots && a.pf_t < a.total) {
+    int g, mt, nt;
+    tile_coords(a.pf_t, p, g, mt, nt);
+    const int seg = mt / p.tiles_per_seg;
+    const int mseg0 = (mt - seg * p.tiles_per_seg) * 256 * a.mh;
+    const bool skip_tile = seg * p.seg_M + mseg0 >= group_rows(p, g) || group_kblocks(p, g) == 0;
+    const int h = a.pf_hc >> 2, c = a.pf_hc & 3;
+    const int col0 = nt * BN + c * 64;
+    if (skip_tile || col0 >= p.N) {                     // next half / tile
+      if (skip_tile || h + 1 >= a.mh) { a.pf_t += a.npairs; a.pf_hc = 0; }
+      else a.pf_hc = (h + 1) << 2;
+      continue;
+    }
+    const int row0 = seg * p.seg_M + mseg0 + h * 256 + a.rank * BM + a.q * 32;
+    const int slot = a.issued % a.slots;
+    uint8_t* b = ring_base + slot * a.nb * EPI_BUF_BYTES;
+    mbar_expect_tx(&a.bars[slot], a.nb * EPI_BUF_BYTES);
+    tma_load_3d_local(b, a.tm, &a.bars[slot], col0, row0, g);
+    if (a.nb == 2) tma_load_3d_local(b + EPI_BUF_BYTES, a.tm, &a.bars[slot], p.N + col0, row0, g);
+    ++a.issued;
+    if (c == 3) {
+      if (h + 1 >= a.mh) { a.pf_t += a.npairs; a.pf_hc = 0; }
+      else a.pf_hc = (h + 1) << 2;
+    } else {
+      ++a.pf_hc;
+    }
+  }
+}
+
 // Drain this warp's 32 TMEM lanes x 256 columns of one accumulator through the fused epilogue.
 // row0 = first row of the warp in the local (M) problem, row0_l = the same inside its M-segment.
 __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtensorMap* tmO, const CUtensorMap* tmO2, int g,
                                                int seg, int row0, int row0_l, int nt, uint32_t taddr, EpiRing& ring, int lane,
-                                               bool zero_tile) {
+                                               bool zero_tile, AuxPipe* aux, volatile int* abort_flag) {
   const int rows_valid = max(0, min(32, p.seg_M - row0_l));
   const int row = row0 + lane;
   const int esz = p.out_f32 ? 4 : 2;
@@ -471,6 +530,23 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
   if (zero_tile) {
     // a tile of padding rows: no accumulator was produced; the outputs are zeros (an accumulating output stays)
     if (p.accumulate) return;
+    if (aux != nullptr && aux->on) {
+      // the staging tiles belong to the prefetch queue: zeros go out by plain 16-byte stores
+      const int wide = p.epi == EPI_DSWIGLU ? 2 : 1;
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col0 = nt * BN + c * 64;
+        if (col0 >= p.N) break;
+        const int pieces = min(8, (p.N - col0 + 7) >> 3), pc = lane & 7;
+        for (int w = 0; w < wide; ++w)
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3);
+            if (r < rows_valid && pc < pieces)
+              *reinterpret_cast<uint4*>(o.base + r * o.pitch + (static_cast<long long>(w) * p.N + col0) * 2 + pc * 16) =
+                  make_uint4(0, 0, 0, 0);
+          }
+      }
+      return;
+    }
     const int bi = ring.take(lane);
     *stage_piece(ring.buf(bi), lane, 0) = make_uint4(0, 0, 0, 0);
 #pragma unroll
@@ -495,6 +571,12 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
         if (col0 >= p.N) break;
         epi_send(p, ring, bi, o, col0, row0, og, rows_valid, p.N, esz, false, lane);
         if (p.epi == EPI_RELU2) epi_send(p, ring, bi, o2, col0, row0, g, rows_valid, p.N, 2, false, lane);
+        if (p.epi == EPI_DSWIGLU) {
+          EpiOut oz = o;
+          oz.tm = tmO2;
+          oz.base = o.base + static_cast<long long>(p.N) * 2;
+          epi_send(p, ring, bi, oz, col0, row0, og, rows_valid, p.N, 2, false, lane);
+        }
       }
     }
     if (ring.tma && lane == 0) bulk_commit();
@@ -573,7 +655,10 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
   }
 
   // bf16 output, 64 columns per staged tile
-  const int nb = p.epi == EPI_RELU2 ? 2 : 1;
+  const int nb = (p.epi == EPI_RELU2 || p.epi == EPI_DSWIGLU) ? 2 : 1;
+  EpiOut oh = o;                       // SwiGLU backward: second half of the output row (the `up` gradient), via tmO2
+  oh.tm = tmO2;
+  oh.base = o.base + static_cast<long long>(p.N) * 2;
 #pragma unroll 1
   for (int c = 0; c < BN / 64; ++c) {
     const int col0 = nt * BN + c * 64;
@@ -582,7 +667,19 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
     tmem_ld32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
     tmem_ld32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
     tmem_ld_wait();
-    const int bi = ring.take(lane);
+    const bool piped = aux != nullptr && aux->on;
+    int bi;
+    if (piped) {
+      // the chunk's pre-activations were fetched ahead into the slot the results will be stored from
+      const int slot = aux->consumed % aux->slots;
+      bi = slot * aux->nb;
+      if (!mbar_wait(&aux->bars[slot], (aux->consumed / aux->slots) & 1, abort_flag)) {
+        if (lane == 0) { atomicCAS(p.status, 0, ST_WAIT_FULL); *abort_flag = 1; }
+        return;
+      }
+    } else {
+      bi = ring.take(lane);
+    }
     uint8_t* b0 = ring.buf(bi);
     if (p.epi == EPI_RELU2) {
       uint8_t* b1 = ring.buf(bi + 1);
@@ -599,10 +696,41 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
         *stage_piece(b0, lane, j) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
         *stage_piece(b1, lane, j) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
       }
+    } else if (p.epi == EPI_DSWIGLU) {
+      // acc = dh (columns of the hidden width H = p.N); aux = (gate | up) pre-activations, 2H columns.
+      // dg = dh * u * s * (1 + g * (1 - s)), du = dh * g * s with s = sigmoid(g)
+      uint8_t* b1 = ring.buf(bi + 1);
+      const char* ab = reinterpret_cast<const char*>(p.aux) + (g * p.aux_gs + static_cast<long long>(row0) * p.ldaux + col0) * 2;
+      const int pv = min(8, (p.N - col0 + 7) >> 3);
+      if (!piped) {
+        coop_load(b0, ab, static_cast<long long>(p.ldaux) * 2, rows_valid, pv, lane);
+        coop_load(b1, ab + static_cast<long long>(p.N) * 2, static_cast<long long>(p.ldaux) * 2, rows_valid, pv, lane);
+        __syncwarp();
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4* pg = stage_piece(b0, lane, j);
+        uint4* pu = stage_piece(b1, lane, j);
+        const uint4 ug = *pg, uu = *pu;
+        const uint32_t wg[4] = {ug.x, ug.y, ug.z, ug.w}, wu[4] = {uu.x, uu.y, uu.z, uu.w};
+        uint32_t og[4], ou[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 gg = unpack_bf16(wg[q]), uv = unpack_bf16(wu[q]);
+          const float d0 = __uint_as_float(r[8 * j + 2 * q]), d1 = __uint_as_float(r[8 * j + 2 * q + 1]);
+          const float s0 = 1.f / (1.f + __expf(-gg.x)), s1 = 1.f / (1.f + __expf(-gg.y));
+          og[q] = pack_bf16(d0 * uv.x * s0 * (1.f + gg.x * (1.f - s0)), d1 * uv.y * s1 * (1.f + gg.y * (1.f - s1)));
+          ou[q] = pack_bf16(d0 * gg.x * s0, d1 * gg.y * s1);
+        }
+        *pg = make_uint4(og[0], og[1], og[2], og[3]);
+        *pu = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      }
     } else if (p.epi == EPI_DRELU2) {
       const char* ab = reinterpret_cast<const char*>(p.aux) + (g * p.aux_gs + static_cast<long long>(row0) * p.ldaux + col0) * 2;
-      coop_load(b0, ab, static_cast<long long>(p.ldaux) * 2, rows_valid, min(8, (p.N - col0 + 7) >> 3), lane);
-      __syncwarp();
+      if (!piped) {
+        coop_load(b0, ab, static_cast<long long>(p.ldaux) * 2, rows_valid, min(8, (p.N - col0 + 7) >> 3), lane);
+        __syncwarp();
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint4* pp = stage_piece(b0, lane, j);
@@ -626,8 +754,18 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
     fence_async_smem();
     __syncwarp();
     epi_send(p, ring, bi, o, col0, row0, og, rows_valid, p.N, 2, false, lane);
-    if (nb == 2) epi_send(p, ring, bi + 1, o2, col0, row0, g, rows_valid, p.N, 2, false, lane);
+    if (p.epi == EPI_DSWIGLU) epi_send(p, ring, bi + 1, oh, col0, row0, og, rows_valid, p.N, 2, false, lane);
+    else if (nb == 2) epi_send(p, ring, bi + 1, o2, col0, row0, g, rows_valid, p.N, 2, false, lane);
     if (ring.tma && lane == 0) bulk_commit();
+    if (piped) {
+      ++aux->consumed;
+      __syncwarp();                               // direct stores: every lane has read the slot
+      if (lane == 0) {
+        bulk_wait_read<0>();                      // TMA stores have read it too: it may take the chunk `slots` ahead
+        fence_async_smem();
+        aux_issue(p, *aux, ring.base);
+      }
+    }
   }
 }
 
@@ -656,7 +794,8 @@ template <int MH> struct PairCfg {
 template <bool A_MN, bool B_MN, int MH>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmO2, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmO2,
+                const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
   constexpr int STAGES3 = PairCfg<MH>::STAGES, EPI_NBUF = PairCfg<MH>::NBUF, STAGE_B = PairCfg<MH>::STAGE_BYTES;
   constexpr int TILE_M = 256 * MH;
   extern __shared__ uint8_t smem_raw[];
@@ -668,6 +807,7 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* auxbars = full + 16;              // 4 epilogue warps x 4 slots of the aux prefetch queue (bytes 128..255)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -682,7 +822,12 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
     mbar_fence_init();
     for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tmAs.m[i]);
     tma_prefetch_desc(&tmB);
-    if (p.store_tma) { tma_prefetch_desc(&tmO); if (p.out2) tma_prefetch_desc(&tmO2); }
+    if (p.store_tma) { tma_prefetch_desc(&tmO); if (p.out2 || p.epi == EPI_DSWIGLU) tma_prefetch_desc(&tmO2); }
+    if (p.aux_tma) {
+      for (int i = 0; i < 16; ++i) mbar_init(&auxbars[i], 1);
+      mbar_fence_init();
+      tma_prefetch_desc(&tmX);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -831,8 +976,18 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
     ring.nbuf = EPI_NBUF;
     ring.hint = (p.dbg & DBG_L2_HINTS) != 0;
     ring.store_policy = l2_policy_evict_first();
-    ring.nb = p.epi == EPI_RELU2 ? 2 : (p.epi == EPI_SWIGLU && p.out2 ? 3 : 1);
+    ring.nb = (p.epi == EPI_RELU2 || p.epi == EPI_DSWIGLU) ? 2 : (p.epi == EPI_SWIGLU && p.out2 ? 3 : 1);
     ring.tma = p.store_tma != 0;
+    AuxPipe aux;
+    aux.on = p.aux_tma != 0;
+    aux.bars = auxbars + q * 4;
+    aux.nb = ring.nb;
+    aux.slots = EPI_NBUF / ring.nb;
+    aux.issued = aux.consumed = 0;
+    aux.pf_t = pair; aux.pf_hc = 0;
+    aux.tm = &tmX;
+    aux.rank = (int)rank; aux.q = q; aux.npairs = npairs; aux.total = total; aux.mh = MH;
+    if (aux.on && lane == 0) aux_issue(p, aux, ring.base);
     for (int t = pair; t < total && ok; t += npairs) {
       int g, mt, nt;
       tile_coords(t, p, g, mt, nt);
@@ -851,7 +1006,8 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
         const int row0_l = mseg0 + h * 256 + (int)rank * BM + q * 32;
         const int row0 = seg * p.seg_M + row0_l;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (MH == 1 ? acc * BN : h * BN);
-        epilogue_tile3(p, &tmO, &tmO2, g, seg, row0, row0_l, nt, taddr, ring, lane, zero_tile);
+        epilogue_tile3(p, &tmO, &tmO2, g, seg, row0, row0_l, nt, taddr, ring, lane, zero_tile, &aux, abort_flag);
+        if (*abort_flag) { ok = false; break; }
         if (!zero_tile) {
           tc_fence_before();
           __syncwarp();
@@ -865,6 +1021,12 @@ gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ C
       }
     }
     if (ring.tma && lane == 0) bulk_wait_all<0>();           // staged tiles must be read before the CTA's smem goes away
+    if (aux.on && lane == 0 && !ok) {
+      // gave up with prefetches in flight: let them land (bounded) before the CTA's shared memory goes away
+      for (uint32_t i = aux.consumed; i < aux.issued; ++i)
+        for (uint32_t spin = 0; spin < MB_SPIN_LIMIT; ++spin)
+          if (mbar_try_wait(&aux.bars[i % aux.slots], (i / aux.slots) & 1)) break;
+    }
   }
 
   tc_fence_before();
@@ -970,7 +1132,8 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
   // 512-row tiles (see PairCfg) when the contraction is long enough to pay for the half-exposed epilogue and the
   // coarser tiling does not cost more in the last, partly filled wave of tiles than it saves
   bool tall = false;
-  if (pair && n_seg == 1 && p.count_mode == 0 && seg_M >= 1024 && !(sw && p.out2)) {
+  if (pair && n_seg == 1 && p.count_mode == 0 && seg_M >= 1024 && !(sw && p.out2) && p.epi != EPI_DRELU2 &&
+      p.epi != EPI_DSWIGLU) {
     auto wave_eff = [&](int tm) {
       const long long tiles = (long long)G * ((seg_M + tm - 1) / tm) * n_tiles, pairs = std::max(1, max_ctas / 2);
       return (double)tiles / (double)(((tiles + pairs - 1) / pairs) * pairs);
@@ -1009,6 +1172,21 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
       const int No = sw ? N / 2 : N;
       tmO = make_tmap(p.out, esz, No, p.M, G, p.ldo, p.out_gs, p.out_f32 ? 32 : 64, 32, false);
       if (p.out2) tmO2 = make_tmap(p.out2, 2, N, p.M, G, p.ldo2, p.out2_gs, 64, 32, false);
+      // SwiGLU backward writes (d gate | d up) side by side: one map per half, so a ragged last chunk of the first
+      // half is clipped at H instead of running into the second
+      if (p.epi == EPI_DSWIGLU)
+        tmO2 = make_tmap(reinterpret_cast<const char*>(p.out) + (size_t)N * 2, 2, N, p.M, G, p.ldo, p.out_gs, 64, 32, false);
+    }
+  }
+  CUtensorMap tmX = tmB;
+  p.aux_tma = 0;
+  if (v3 && (p.epi == EPI_DRELU2 || p.epi == EPI_DSWIGLU)) {
+    // the pre-activations are prefetched by TMA (see AuxPipe); MEMARCH_GEMM_AUX_TMA=0 keeps the warp's own loads
+    static const bool aux_off = []() { const char* e = std::getenv("MEMARCH_GEMM_AUX_TMA"); return e && e[0] == '0'; }();
+    const int Nx = p.epi == EPI_DSWIGLU ? 2 * N : N;
+    if (!aux_off && (p.ldaux * 2) % 16 == 0 && (G == 1 || (p.aux_gs * 2) % 16 == 0) && N % 8 == 0) {
+      tmX = make_tmap(p.aux, 2, Nx, (uint64_t)n_seg * seg_M, G, p.ldaux, p.aux_gs, 64, 32, false);
+      p.aux_tma = 1;
     }
   }
   auto launch = [&](auto kern, int id) {
@@ -1020,8 +1198,8 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
                   "cannot raise dynamic shared memory for the GEMM kernel");
       attr_set[dev & 15][id] = true;
     }
-    if constexpr (std::is_invocable_v<decltype(kern), TmapSet, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams>)
-      kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, tmO, tmO2, p);
+    if constexpr (std::is_invocable_v<decltype(kern), TmapSet, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams>)
+      kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, tmO, tmO2, tmX, p);
     else
       kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmAs, tmB, p);
   };
@@ -1077,7 +1255,7 @@ torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor
   const int M = a_mn ? A.size(2) : A.size(1), K = a_mn ? A.size(1) : A.size(2);
   const int N = b_mn ? B.size(2) : B.size(1), Kb = b_mn ? B.size(1) : B.size(2);
   TORCH_CHECK(K == Kb, "gemm: K mismatch ", K, " vs ", Kb);
-  const int Nout = epi == EPI_SWIGLU ? N / 2 : N;
+  const int Nout = epi == EPI_SWIGLU ? N / 2 : (epi == EPI_DSWIGLU ? 2 * N : N);
   torch::Tensor out;
   if (out_.has_value() && out_->defined()) {
     out = *out_;
@@ -1109,12 +1287,15 @@ torch::Tensor gemm(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor
       p.aux = aux_->data_ptr(); p.aux_gs = G > 1 ? M : 0;
     } else {
       torch::Tensor X = as3(*aux_);
-      TORCH_CHECK(X.scalar_type() == torch::kBFloat16 && X.stride(2) == 1 && X.size(1) == M && X.size(2) == N, "gemm: aux");
+      TORCH_CHECK(X.scalar_type() == torch::kBFloat16 && X.stride(2) == 1 && X.size(1) == M &&
+                  X.size(2) == (epi == EPI_DSWIGLU ? 2 * N : N), "gemm: aux");
       p.aux = X.data_ptr(); p.ldaux = (int)X.stride(1); p.aux_gs = G > 1 ? X.stride(0) : 0;
       TORCH_CHECK(p.ldaux % 8 == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0, "gemm: aux alignment");
     }
   }
-  TORCH_CHECK((epi != EPI_DRELU2 && epi != EPI_ROWSCALE) || p.aux != nullptr, "gemm: epilogue needs aux");
+  TORCH_CHECK((epi != EPI_DRELU2 && epi != EPI_ROWSCALE && epi != EPI_DSWIGLU) || p.aux != nullptr, "gemm: epilogue needs aux");
+  TORCH_CHECK(epi != EPI_DSWIGLU || (!out_f32 && N % 8 == 0 && M >= 256 && use_pair_kernel()),
+              "gemm: the SwiGLU-backward epilogue writes bf16, needs a hidden width that is a multiple of 8 and the pair kernel (>= 256 rows)");
   if (counts_.has_value() && counts_->defined() && count_mode != 0) {
     TORCH_CHECK(counts_->is_cuda() && counts_->scalar_type() == torch::kInt32 && counts_->is_contiguous() &&
                 counts_->numel() >= G, "gemm: counts must be a contiguous int32 CUDA tensor with one entry per group");

@@ -132,8 +132,7 @@ class LightBlock(nn.Module):
             y = ops.linear(self._act(ops.linear(xs, self.up.weight)), self.down.weight) * ok[..., None].to(dt)
             return fin(x.scatter_add(1, idx[..., None].expand(-1, -1, D), y.to(x.dtype)))
         x, n2 = ops.add_rmsnorm(x, ops.linear(a, self.o.weight, direct=True), self.n2.weight, self.n2.eps)
-        y = ops.linear(ops.linear_act(n2, self.up.weight, "relu2" if self.relu2 else "swiglu", direct=True),
-                       self.down.weight, direct=True)
+        y = ops.ffn(n2, self.up.weight, self.down.weight, "relu2" if self.relu2 else "swiglu", direct=True)
         if defer:
             return x, y
         return ops.resid_add(x, y)

@@ -145,6 +145,46 @@ def main(argv=None):
     tfb = timed(fb(fused_fwd), a.iters, W)
     tnb = timed(fb(nccl_fwd), a.iters, W)
     say(f"EP FFN layer fwd+bwd: fused {tfb:.3f} ms ({roof_fb / tfb:.2f} of its roofline {roof_fb:.3f} ms), NCCL path {tnb:.3f} ms")
+    # ---- data-parallel optimizer step of replicated weights: row-sharded (reduce-scatter + update of the owned rows +
+    #      all-gather of the new bf16 rows) against all-reduce + full update on every rank
+    import types
+    from ..config import OptConfig
+    from ..optim import Instinct
+    from ..parallel.fused import FusedGradReduce
+    R_, C_, nw = 2048, 8192, 8
+    res = {}
+    for mode in ("sharded", "replicated", "nccl"):
+        torch.manual_seed(5)
+        ps = [torch.nn.Parameter((torch.randn(R_, C_, device=dev) * 0.02).bfloat16()) for _ in range(nw)]
+        opt = Instinct(ps, OptConfig(lr=1e-3, norm="hs", scale=0.12, m_bf16=True, rel_every=1 << 30))
+        opt.prepare(torch.tensor(3.0, device=dev), torch.randn(64, device=dev))
+        opt.n_step = 1                                         # no |g|/|w| sums in the timed steps
+        gs = [torch.randn(R_, C_, device=dev).bfloat16() for _ in range(nw)]
+        if mode == "nccl":
+            def step():
+                for p_, g_ in zip(ps, gs):
+                    g2 = g_.clone()
+                    if W > 1:
+                        dist.all_reduce(g2)
+                    opt.update(p_, g2.div_(W))
+        else:
+            dp = FusedGradReduce(heap)
+            dp.shard = mode == "sharded"
+            dp.trainer = types.SimpleNamespace(opt=opt, params=ps)
+            dp.allocate(ps)
+
+            def step(dp=dp):
+                for p_, g_ in zip(ps, gs):
+                    dp.grad_ready(p_, g_)
+                dp.flush()
+        res[mode] = timed(step, a.iters, W) / nw
+    n_el = R_ * C_
+    link_ms = (W - 1) / W * n_el * 2 / (LINK_GBS * 1e9) * 1e3           # rows in (reduce) and out (gather) run in both directions at once
+    hbm_ms = (8 + 28 / W) * n_el / 6.45e12 * 1e3                          # staging, peers' reads, statistics and update of the owned rows, incoming rows
+    roof = max(link_ms, hbm_ms)
+    say(f"DP optimizer step per {R_}x{C_} bf16 weight ({nw} in flight): row-sharded {res['sharded'] * 1e3:.0f} us "
+        f"({roof / res['sharded']:.2f} of its roofline {roof * 1e3:.0f} us = max(link {link_ms * 1e3:.0f}, HBM {hbm_ms * 1e3:.0f})), "
+        f"all-reduce + full update {res['replicated'] * 1e3:.0f} us, NCCL all-reduce + full update {res['nccl'] * 1e3:.0f} us")
     torch.cuda.synchronize()
     heap.check()
     if W > 1:

@@ -339,3 +339,30 @@ def test_expert_ffn_with_counts_equals_padded(act):
     for a, b in zip(*res):
         assert _rel(b, a) < 1e-3, (_rel(b, a))
     assert _ext().gemm_status(0) == 0
+
+
+@pytest.mark.parametrize("act,fuse", [("swiglu", False), ("swiglu", True), ("relu2", True)])
+def test_ffn_node_matches_fp32(act, fuse, monkeypatch):
+    """Feed-forward half of a light block as one autograd node (activation backward in the dgrad GEMM's epilogue,
+    ragged hidden width) against fp32 autograd."""
+    from memarch_b200.ops import basic
+    monkeypatch.setattr(basic, "FUSE_DSWIGLU", fuse)
+    M, d, H = 520, 256, 328
+    x = _mk((M, d), seed=91).requires_grad_()
+    wu = _mk(((2 * H if act == "swiglu" else H), d), 0.1, seed=92).requires_grad_()
+    wd = _mk((d, H), 0.1, seed=93).requires_grad_()
+    y = basic.ffn(x, wu, wd, act)
+    go = _mk((M, d), seed=94)
+    y.backward(go)
+    xr, ur, dr = (t.detach().float().requires_grad_() for t in (x, wu, wd))
+    pre = xr @ ur.t()
+    if act == "swiglu":
+        g, u = pre.chunk(2, -1)
+        hr = torch.nn.functional.silu(g) * u
+    else:
+        hr = torch.relu(pre) ** 2
+    (hr @ dr.t()).backward(go.float())
+    assert _rel(y, hr @ dr.t()) < 2e-2
+    for a, b in ((x.grad, xr.grad), (wu.grad, ur.grad), (wd.grad, dr.grad)):
+        assert _rel(a, b) < 2e-2, _rel(a, b)
+    assert _ext().gemm_status(0) == 0

@@ -49,6 +49,13 @@ std::vector<torch::Tensor> mem_read_fwd(torch::Tensor q, torch::Tensor faces, to
 std::vector<torch::Tensor> mem_read_bwd(torch::Tensor q, torch::Tensor faces, torch::Tensor valid, torch::Tensor w,
                                         torch::Tensor best, torch::Tensor dw, c10::optional<torch::Tensor> dsc, int64_t Fn,
                                         double scale);
+std::vector<torch::Tensor> reread_fwd(torch::Tensor sc, torch::Tensor pos, torch::Tensor qpos, torch::Tensor rows,
+                                      torch::Tensor ids, torch::Tensor table, torch::Tensor offset, torch::Tensor hv,
+                                      torch::Tensor hb, torch::Tensor hh, torch::Tensor Wr, torch::Tensor cp, int64_t k);
+std::vector<torch::Tensor> reread_bwd(torch::Tensor dgot, torch::Tensor dcostw, torch::Tensor top_j, torch::Tensor p,
+                                      torch::Tensor sc, torch::Tensor pos, torch::Tensor qpos, torch::Tensor rows,
+                                      torch::Tensor ids, torch::Tensor table, torch::Tensor offset, torch::Tensor hv,
+                                      torch::Tensor hb, torch::Tensor hh, torch::Tensor Wr, torch::Tensor cp);
 std::vector<torch::Tensor> attn_fwd_tc(torch::Tensor q, torch::Tensor k, torch::Tensor v, int64_t window, double scale);
 int64_t attn_status_read();
 std::vector<torch::Tensor> attn_bwd_tc(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor dout, torch::Tensor lse,
@@ -105,6 +112,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_bwd_status_read", &mb::attn_bwd_status_read);
   m.def("mem_read_fwd", &mb::mem_read_fwd);
   m.def("mem_read_bwd", &mb::mem_read_bwd);
+  m.def("reread_fwd", &mb::reread_fwd);
+  m.def("reread_bwd", &mb::reread_bwd);
   m.def("moe_route_fwd", &mb::moe_route_fwd);
   m.def("moe_route_bwd", &mb::moe_route_bwd);
   m.def("table_pair_dot", &mb::table_pair_dot, "out[n] = <A[ia[n]], B[ib[n]]>");

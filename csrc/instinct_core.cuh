@@ -76,11 +76,20 @@ __device__ __forceinline__ float mom1(const InstinctArgs& a, long long i, float&
 // Column scales of expert e into shared memory: dst[c] = scale(sum1[e,c]) * scale(sum2[e,c]) (either may be null).
 __device__ __forceinline__ void load_colscale(float* dst, const float* sum1, const float* sum2, long long e, long long C,
                                               float count) {
-  for (long long c = threadIdx.x; c < C; c += blockDim.x) {
-    float k = 1.f;
-    if (sum1) k *= scale_of(sum1[e * C + c], count);
-    if (sum2) k *= scale_of(sum2[e * C + c], count);
-    dst[c] = k;
+  // four columns per thread and round: the loads go out together (dst may alias the sums as far as the compiler knows)
+  for (long long c0 = threadIdx.x; c0 < C; c0 += 4ll * blockDim.x) {
+    float s1[4], s2[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long c = c0 + (long long)u * blockDim.x;
+      s1[u] = (sum1 && c < C) ? sum1[e * C + c] : 1.f;
+      s2[u] = (sum2 && c < C) ? sum2[e * C + c] : 1.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long c = c0 + (long long)u * blockDim.x;
+      if (c < C) dst[c] = (sum1 ? scale_of(s1[u], count) : 1.f) * (sum2 ? scale_of(s2[u], count) : 1.f);
+    }
   }
   __syncthreads();
 }
@@ -372,6 +381,223 @@ __global__ void instinct_apply(InstinctArgs a, const float* __restrict__ rowsum,
   }
 }
 
+// ---- streaming forms.  A block that walks one row at a time and reduces it across its warps has one short burst of
+// loads in flight, then two barriers (1.7 TB/s for the row sums, 3.6 TB/s for the update on the expert shapes), and
+// a warp that loads a few chunks of its row into registers, then computes, does little better (2.6 / 4.4 TB/s): HBM
+// wants well over 100 KB in flight per SM all the time.  So here every thread keeps a ring of S chunks (8 elements of
+// each input array) in shared memory, filled by 16-byte cp.async copies issued S chunks ahead of the one it consumes;
+// a warp owns a contiguous run of rows, so its stream is one linear span of memory, and the ring runs across row
+// boundaries.  One block per SM; C % 256 == 0 (a chunk of 32 lanes x 8 never straddles rows).
+__device__ __forceinline__ void cp_async16(void* s, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(s)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct Ring8 {             // this thread's ring: slot (stage, q) is 16 bytes; slots of one (stage, q) are contiguous over threads
+  uint4* base;
+  int T, nslot;
+  __device__ __forceinline__ uint4* slot(int stage, int q) const { return base + (stage * nslot + q) * T; }
+  __device__ __forceinline__ void issue8(int stage, int q0, const void* arr, long long i, int is_bf16) const {
+    if (is_bf16) {
+      cp_async16(slot(stage, q0), reinterpret_cast<const bf16*>(arr) + i);
+    } else {
+      cp_async16(slot(stage, q0), reinterpret_cast<const float*>(arr) + i);
+      cp_async16(slot(stage, q0 + 1), reinterpret_cast<const float*>(arr) + i + 4);
+    }
+  }
+  __device__ __forceinline__ void read8(int stage, int q0, int is_bf16, float* o) const {
+    const uint4 u = *slot(stage, q0);
+    if (is_bf16) {
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+    } else {
+      const uint4 v = *slot(stage, q0 + 1);
+      o[0] = __uint_as_float(u.x); o[1] = __uint_as_float(u.y); o[2] = __uint_as_float(u.z); o[3] = __uint_as_float(u.w);
+      o[4] = __uint_as_float(v.x); o[5] = __uint_as_float(v.y); o[6] = __uint_as_float(v.z); o[7] = __uint_as_float(v.w);
+    }
+  }
+};
+__device__ __forceinline__ void st8_f32(float* dst, const float* v) {
+  reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void st8_bf16(bf16* dst, const float* v) {
+  *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+}
+
+// rowsq / rowabs as instinct_stat_rows.  grid (blocks); dynamic shared memory: C floats when colsum is given, then
+// the rings (blockDim * S * 16 * (slots of g + slots of m) bytes).
+template <int S>
+__global__ void __launch_bounds__(512) instinct_stat_rows_s8(InstinctArgs a, const float* __restrict__ colsum, float col_count,
+                                                             float* __restrict__ rowsq, float* __restrict__ rowabs) {
+  extern __shared__ __align__(16) float sm[];
+  float* cs = colsum ? sm : nullptr;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const float b = a.beta, b1 = 1.f - a.beta;
+  const int gs = a.g_bf16 ? 1 : 2, ms = a.m_bf16 ? 1 : 2;
+  Ring8 ring;
+  ring.base = reinterpret_cast<uint4*>(sm + (colsum ? a.C : 0)) + threadIdx.x;
+  ring.T = blockDim.x;
+  ring.nslot = gs + ms;
+  const long long cpr = a.C >> 8;                       // chunks per row
+  const long long ER = a.E * a.R;
+  const long long lo = ER * blockIdx.x / gridDim.x, hi = ER * (blockIdx.x + 1) / gridDim.x;
+  for (long long seg = lo; seg < hi;) {
+    const long long e = seg / a.R, seg_hi = min(hi, (e + 1) * a.R);
+    if (cs) {
+      __syncthreads();
+      load_colscale(cs, colsum, nullptr, e, a.C, col_count);
+    }
+    const long long rpw = (seg_hi - seg + nw - 1) / nw;
+    const long long r0 = min(seg_hi, seg + warp * rpw), r1 = min(seg_hi, r0 + rpw);
+    const long long total = (r1 - r0) * cpr;
+    const long long el0 = r0 * a.C + lane * 8;
+    auto issue = [&](int stage, long long k) {
+      ring.issue8(stage, 0, a.g, el0 + (k << 8), a.g_bf16);
+      ring.issue8(stage, gs, a.m, el0 + (k << 8), a.m_bf16);
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < S; ++s0) {
+      if (s0 < total) issue(s0, s0);
+      cp_async_commit();
+    }
+    int stage = 0;
+    long long row = r0, cin = 0;
+    float ss = 0.f, sa = 0.f;
+    for (long long k = 0; k < total; ++k) {
+      cp_async_wait<S - 1>();
+      float g[8], m[8];
+      ring.read8(stage, 0, a.g_bf16, g);
+      ring.read8(stage, gs, a.m_bf16, m);
+      if (k + S < total) issue(stage, k + S);
+      cp_async_commit();
+      const long long c = (cin << 8) + lane * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = b * m[j] + b1 * g[j];
+        if (cs) v *= cs[c + j];
+        ss += v * v;
+        sa += fabsf(g[j]);
+      }
+      if (++cin == cpr) {
+        ss = warp_sum(ss);
+        if (rowabs) sa = warp_sum(sa);
+        if (lane == 0) {
+          rowsq[row] = ss;
+          if (rowabs) rowabs[row] = sa;
+        }
+        ++row; cin = 0; ss = 0.f; sa = 0.f;
+      }
+      if (++stage == S) stage = 0;
+    }
+    cp_async_wait<0>();
+    seg = seg_hi;
+  }
+}
+
+// The update without the staged last row norm (instinct_apply with fuse_row_norm = 0), streamed.  Stochastic
+// rounding keeps the per-element hash of the block-per-row kernel, so both produce the same bits.
+// Dynamic shared memory: C floats with column sums, then the rings (g, m and the weight's exact copy).
+template <int S>
+__global__ void __launch_bounds__(384) instinct_apply_s8(InstinctArgs a, const float* __restrict__ rowsum, float row_count,
+                                                         const float* __restrict__ rowsum2, const float* __restrict__ colsum1,
+                                                         const float* __restrict__ colsum2, float col_count,
+                                                         const float* __restrict__ rowabs, const float* __restrict__ rel2,
+                                                         float* __restrict__ rel_out) {
+  extern __shared__ __align__(16) float sm[];
+  const long long C = a.C;
+  const bool has_col = colsum1 || colsum2;
+  float* colk = has_col ? sm : nullptr;
+  const float lr = *a.lr;
+  const float eff = 1.f + (*a.gain - 1.f) * (*a.stake);
+  const float step = lr * eff, decay = (a.wd != 0.f) ? 1.f - lr * a.wd : 1.f;
+  const uint32_t seed = a.sr ? (uint32_t)((*a.seed) * 1000003ll) * 0x9E3779B9u + a.salt : 0u;
+  if (rel_out && blockIdx.x == 0 && threadIdx.x == 0) *rel_out = sqrtf(rel2[0]) / (sqrtf(rel2[1]) + 1e-8f);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const float b = a.beta, b1 = 1.f - a.beta;
+  const void* wsrc = a.w ? (const void*)a.w : (const void*)a.p;
+  const int w_bf16 = a.w ? 0 : a.p_bf16;
+  const int gs = a.g_bf16 ? 1 : 2, ms = a.m_bf16 ? 1 : 2, ws = w_bf16 ? 1 : 2;
+  Ring8 ring;
+  ring.base = reinterpret_cast<uint4*>(sm + (has_col ? C : 0)) + threadIdx.x;
+  ring.T = blockDim.x;
+  ring.nslot = gs + ms + ws;
+  const long long cpr = C >> 8;
+  const long long ER = a.E * a.R;
+  const long long lo = ER * blockIdx.x / gridDim.x, hi = ER * (blockIdx.x + 1) / gridDim.x;
+  for (long long seg = lo; seg < hi;) {
+    const long long e = seg / a.R, seg_hi = min(hi, (e + 1) * a.R);
+    if (has_col) {
+      __syncthreads();
+      load_colscale(colk, colsum1, colsum2, e, C, col_count);
+    }
+    const long long rpw = (seg_hi - seg + nw - 1) / nw;
+    const long long r0 = min(seg_hi, seg + warp * rpw), r1 = min(seg_hi, r0 + rpw);
+    const long long total = (r1 - r0) * cpr;
+    const long long el0 = r0 * C + lane * 8;
+    auto issue = [&](int stage, long long k) {
+      ring.issue8(stage, 0, a.g, el0 + (k << 8), a.g_bf16);
+      ring.issue8(stage, gs, a.m, el0 + (k << 8), a.m_bf16);
+      ring.issue8(stage, gs + ms, wsrc, el0 + (k << 8), w_bf16);
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < S; ++s0) {
+      if (s0 < total) issue(s0, s0);
+      cp_async_commit();
+    }
+    int stage = 0;
+    long long row = r0, cin = 0;
+    float rs = 1.f;
+    bool moves = true;
+    for (long long k = 0; k < total; ++k) {
+      if (cin == 0) {
+        rs = rowsum ? scale_of(rowsum[row], row_count) : 1.f;
+        if (rowsum2) rs *= scale_of(rowsum2[row] * rs * rs, row_count);
+        const bool frozen = a.frozen && a.frozen[(row * C) / a.frozen_stride];
+        moves = !(rowabs && !(rowabs[row] > 0.f)) && !frozen;
+      }
+      cp_async_wait<S - 1>();
+      float g[8], m[8], t[8];
+      ring.read8(stage, 0, a.g_bf16, g);
+      ring.read8(stage, gs, a.m_bf16, m);
+      ring.read8(stage, gs + ms, w_bf16, t);
+      if (k + S < total) issue(stage, k + S);
+      cp_async_commit();
+      const long long c = (cin << 8) + lane * 8;
+      const long long i0 = el0 + (k << 8);
+      float mf[8], upd[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        mf[j] = b * m[j] + b1 * g[j];
+        upd[j] = mf[j] * rs * (colk ? colk[c + j] : 1.f);
+      }
+      if (a.sr) {                                         // per-element hashes: the 4-wide store path has them
+        store_chunk<4>(a, i0, mf, t, upd, moves, step, decay, seed);
+        store_chunk<4>(a, i0 + 4, mf + 4, t + 4, upd + 4, moves, step, decay, seed);
+      } else {
+        if (a.m_bf16) st8_bf16(reinterpret_cast<bf16*>(a.m) + i0, mf);
+        else st8_f32(reinterpret_cast<float*>(a.m) + i0, mf);
+        if (moves) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[j] = t[j] * decay - upd[j] * step;
+          if (a.w) st8_f32(a.w + i0, t);
+          if (a.p_bf16) {
+            st8_bf16(reinterpret_cast<bf16*>(a.p) + i0, t);
+          } else {
+            st8_f32(reinterpret_cast<float*>(a.p) + i0, t);
+            if (a.shadow) st8_bf16(reinterpret_cast<bf16*>(a.shadow) + i0, t);
+          }
+        }
+      }
+      if (++cin == cpr) { ++row; cin = 0; }
+      if (++stage == S) stage = 0;
+    }
+    cp_async_wait<0>();
+    seg = seg_hi;
+  }
+}
+
 // Lagged homeostasis of a 2-D weight in ONE pass over g, m and the weight: the column norm comes from the previous
 // step (`cs_prev`, mean squares; where it is not positive the fresh value `now_sum / R` is used - `now_sum` was made
 // by `instinct_rowcol` in that case), the new column sums are gathered on the way into `colsq_out`.
@@ -519,8 +745,29 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
   auto raise = [](auto kern, size_t smem) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)INSTINCT_SMEM_MAX);
   };
+  // streaming forms: 16-byte accesses on every array, whole chunks of 256 columns, enough rows to fill the GPU
+  const bool s8 = vec && a.C % 256 == 0 && (a.shadow == nullptr || (reinterpret_cast<uintptr_t>(a.shadow) & 15) == 0) &&
+                  ER >= 148 * 16;
+  constexpr size_t S8_SMEM = 216 * 1024;
+  // launch `kern<S>` with the deepest ring that fits beside `head` bytes: T threads, `slots` 16-byte slots per stage
+  auto s8_launch = [&](auto k12, auto k8, auto k6, auto k4, int T, int slots, size_t head, auto&&... args) {
+    const size_t per = (size_t)T * slots * 16;
+    const int S = head + 12 * per <= S8_SMEM ? 12 : head + 8 * per <= S8_SMEM ? 8 : head + 6 * per <= S8_SMEM ? 6 : 4;
+    const size_t smem = head + S * per;
+    auto go = [&](auto kern) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S8_SMEM);
+      kern<<<148, T, smem, st>>>(args...);
+    };
+    if (S == 12) go(k12); else if (S == 8) go(k8); else if (S == 6) go(k6); else go(k4);
+    ++launches;
+  };
   auto stat_rows = [&](const float* colsum, float* out, float* absout) {
     const size_t smem = colsum ? Cb : 0;
+    if (s8 && smem + 4 * 512 * 4 * 16 <= S8_SMEM) {
+      s8_launch(instinct_stat_rows_s8<12>, instinct_stat_rows_s8<8>, instinct_stat_rows_s8<6>, instinct_stat_rows_s8<4>, 512,
+                (a.g_bf16 ? 1 : 2) + (a.m_bf16 ? 1 : 2), smem, a, colsum, Rf, out, absout);
+      return;
+    }
     dim3 grid(blocks_per_expert(smem), E);
     if (vec) { raise(instinct_stat_rows<4>, smem); instinct_stat_rows<4><<<grid, row_threads, smem, st>>>(a, colsum, Rf, out, absout); }
     else { raise(instinct_stat_rows<1>, smem); instinct_stat_rows<1><<<grid, row_threads, smem, st>>>(a, colsum, Rf, out, absout); }
@@ -548,6 +795,12 @@ inline int64_t instinct_launch(const InstinctArgs& a, int kind, float* scratch, 
   };
   auto apply = [&](const float* rs, const float* rs2, const float* c1, const float* c2, bool fuse, const float* rabs) {
     const size_t smem = ((c1 || c2) ? Cb : 0) + (fuse ? Cb : 0);
+    if (s8 && !fuse && smem + 4 * 384 * 6 * 16 <= S8_SMEM) {
+      const int slots = (a.g_bf16 ? 1 : 2) + (a.m_bf16 ? 1 : 2) + ((a.w == nullptr && a.p_bf16) ? 1 : 2);
+      s8_launch(instinct_apply_s8<12>, instinct_apply_s8<8>, instinct_apply_s8<6>, instinct_apply_s8<4>, 384, slots, smem, a, rs,
+                Cf, rs2, c1, c2, Rf, rabs, rel2, rel_out);
+      return;
+    }
     dim3 grid(blocks_per_expert(smem), E);
     if (vec) { raise(instinct_apply<4>, smem); instinct_apply<4><<<grid, row_threads, smem, st>>>(a, rs, Cf, rs2, c1, c2, Rf, fuse ? 1 : 0, rabs, rel2, rel_out); }
     else { raise(instinct_apply<1>, smem); instinct_apply<1><<<grid, row_threads, smem, st>>>(a, rs, Cf, rs2, c1, c2, Rf, fuse ? 1 : 0, rabs, rel2, rel_out); }

@@ -112,7 +112,8 @@ class ModelConfig:
 @dataclass
 class OptConfig:
     """InstinctOptB constructor (exp_opt.py:437-439) plus the env switches around it."""
-    kind: str = "instinct"        # instinct | adamw | surprise
+    kind: str = "instinct"        # instinct | adamw | surprise | muon (OPT=muon: Muon on hidden matrices + AdamW)
+    muon_mul: float = 1.0         # MUON_MUL: Muon's learning rate as a multiple of the shared one
     lr: float = 1e-3
     weight_decay: float = 0.1
     cards: int = 4
@@ -262,6 +263,9 @@ def opt_from_env(cfg: OptConfig, env=None) -> OptConfig:
         for k, v in json.loads(env["OPT_KW"]).items():
             if k in OptConfig.__dataclass_fields__:
                 kw[k] = v
+    if env.get("OPT") == "muon":
+        kw["kind"] = "muon"
+        kw["muon_mul"] = float(env.get("MUON_MUL", 1))
     if env.get("OPT_HS_LAG") == "1": kw["hs_lag"] = True
     if (env.get("BF16_ALL") == "1" or env.get("OPT_SR") == "1") and env.get("OPT_SR_OFF") != "1": kw["sr"] = True
     if env.get("BF16_ALL") == "1": kw["no_master"] = True

@@ -42,6 +42,29 @@ class _ErrProbe(torch.autograd.Function):
         return g, None
 
 
+class _ErrProbeWords(torch.autograd.Function):
+    """The same probe read off the gradient of the combined word outputs (N, d), for the exchange that sums a word's
+    experts on the owning rank so that no per-place output exists here: the gradient of place (e, c) is its combine
+    weight times its word's gradient, hence its norm |w| * |g_word|; empty places (table == N) count as zero.
+    (full2.py:347-364)"""
+
+    @staticmethod
+    def forward(ctx, out, buf, table, wtab, E):
+        ctx.buf, ctx.E = buf, E
+        ctx.save_for_backward(table, wtab)
+        return out.view_as(out)
+
+    @staticmethod
+    def backward(ctx, g):
+        table, wtab = ctx.saved_tensors
+        with torch.no_grad():
+            N = g.shape[0]
+            word = torch.linalg.vector_norm(g, dim=-1, dtype=torch.float32)
+            place = torch.where(table < N, word[table.clamp(max=N - 1)], word.new_zeros(())) * wtab.float().abs()
+            ctx.buf.mul_(0.9).add_(0.1 * place.view(ctx.E, -1).mean(1))
+        return g, None, None, None, None
+
+
 class AnchorMoE(nn.Module):
     def __init__(self, d, E=8, k_avg=2, k_max=4, budget=True, wave="", wave_every=50, students=5, hint_w=1.0,
                  frozen=0, bank=False, act="swiglu", w_dtype=torch.float32, bank_q="", wave_warm=500,
@@ -128,8 +151,10 @@ class AnchorMoE(nn.Module):
         xf, table, wtab, flat_idx, C = self._route(x, surprise)
         N, d = xf.shape
         eng = self.ep_engine if self.ep_W > 1 else None
-        if eng is not None and getattr(eng, "dedup", False) and not (self.bank and self.has_F) and not self.wave:
+        if eng is not None and getattr(eng, "dedup", False) and not (self.bank and self.has_F) and not (self.wave and not self.bank):
             out = eng.forward_dedup(self, xf, table, wtab, C, eng.dedup_cap)
+            if self.wave and self.training:
+                out = _ErrProbeWords.apply(out, self.err, table, wtab, self.E)
             return ops.resid_add(x, out.view_as(x))
         xe = ops.slot_gather(xf, table, flat_idx).view(self.E, C, d)
         ye = self._experts(xe, wtab, C)

@@ -1,1 +1,2 @@
 from .instinct import Instinct, SurpriseAdamW   # noqa: F401
+from .muon import MuonAdamW   # noqa: F401

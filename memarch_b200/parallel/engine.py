@@ -239,12 +239,16 @@ class ParallelEngine:
 
     # ------------------------------------------------------------------------------------------ control values
     def sync_control(self, loss, sit, model):
-        """One small all-reduce: mean loss, true batch-mean situation vector and the shared anchor threshold."""
+        """One small all-reduce: mean loss, true batch-mean situation vector and the shared anchor threshold.  NCCL in
+        the baseline mode; in the fused mode the one-shot peer all-reduce on a symmetric buffer."""
         tau = model.tau if hasattr(model, "tau") else loss.new_zeros(())
         buf = torch.cat([loss.reshape(1).float(), tau.reshape(1).float(), sit.float().reshape(-1)])
         if self.W > 1:
-            dist.all_reduce(buf, group=self.group)
-            buf /= self.W
+            if self.fused_impl is not None and buf.is_cuda:
+                self.fused_impl.mean_small(buf)              # peer loads / stores between two device barriers
+            else:
+                dist.all_reduce(buf, group=self.group)
+                buf /= self.W
         if hasattr(model, "tau"):
             model.tau.copy_(buf[1])
         return buf[0], buf[2:]

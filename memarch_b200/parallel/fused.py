@@ -399,6 +399,28 @@ class FusedParallel:
         self.heap = SymmetricHeap(engine.rank, engine.W, engine.group, wait_ms)
         self.ep = FusedExpertExchange(self.heap)
         self.dp = FusedGradReduce(self.heap)
+        self.ctrl, ch = self.heap.alloc((4096,), torch.float32, zero=True)      # the per-step control vector
+        self.ctrl_ptrs = [int(p) for p in ch.buffer_ptrs]
+        self.heap.barrier(0)
+
+    def mean_small(self, buf):
+        """Mean over the ranks of a small fp32 vector, in place, on the current stream: copy into the symmetric
+        control buffer, one-shot all-reduce by peer loads and stores between two device barriers, copy back (no NCCL
+        kernel, no host synchronisation).  Every rank must call it at the same point of its main stream."""
+        n = buf.numel()
+        if n > self.ctrl.numel():
+            raise ValueError(f"control vector of {n} floats exceeds the {self.ctrl.numel()}-float buffer")
+        W = self.heap.W
+        pad = (n + 4 * W - 1) // (4 * W) * (4 * W)                  # every rank reduces a 16-byte multiple
+        self.ctrl[:n].copy_(buf)
+        if pad > n:
+            self.ctrl[n:pad].zero_()
+        self.heap.barrier(2)
+        _ext.C().peer_allreduce(self.ctrl_ptrs, self.ctrl_ptrs, 0, 0, 0, pad, False, self.heap.rank, 1.0 / W)
+        _ext.count()
+        self.heap.barrier(2)
+        buf.copy_(self.ctrl[:n])
+        return buf
 
     def attach(self, trainer):
         self.dp.trainer = trainer

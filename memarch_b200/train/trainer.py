@@ -70,6 +70,10 @@ class Trainer:
                 with (torch.cuda.stream(self._gstream) if self._gstream is not None else contextlib.nullcontext()):
                     for p in self.params:
                         p.register_post_accumulate_grad_hook(self._hook)
+        elif self.ocfg.kind == "muon":
+            from ..optim.muon import MuonAdamW
+            self.opt = MuonAdamW(self.params, lr=tcfg.lr, weight_decay=0.1, betas=(0.9, 0.95), mul=self.ocfg.muon_mul)
+            self.in_backward = False
         elif "S" in st:
             self.opt = SurpriseAdamW(self.params, lr=tcfg.lr, betas=(0.9, 0.95), weight_decay=0.1)
             self.in_backward = False

@@ -249,6 +249,21 @@ def _w_dedup(rank, world, port, q):
         y.backward(go)
         res[mode] = (y.detach().clone(), x.grad.clone(), moe.up.grad.clone(), moe.router.weight.grad.clone(),
                      float(moe.dropped))
+    # a bank layer (experts with the "stopped changing" wave): the error probe reads the word gradients in the
+    # deduplicated exchange and the per-place gradients in the plain one - same numbers
+    torch.manual_seed(1)
+    bank = AnchorMoE(32, E=4, k_avg=2, k_max=2, bank=True, act="relu2")
+    bank.ep_shard(rank, world, eng)
+    bank.train()
+    errs = {}
+    for mode in ("plain", "dedup"):
+        eng.dedup, eng.dedup_cap = mode == "dedup", 1.0
+        bank.err.zero_()
+        x = x0.clone().requires_grad_(True)
+        yb = bank(x, None)
+        yb.backward(go)
+        errs[mode] = (bank.err.clone().numpy(), yb.detach().numpy())
+    res["bank_err"] = [errs["plain"][0], errs["dedup"][0], errs["plain"][1], errs["dedup"][1]]
     q.put((rank, {k: [t.numpy() if torch.is_tensor(t) else t for t in v] for k, v in res.items()}))
     dist.barrier()
     dist.destroy_process_group()
@@ -268,3 +283,6 @@ def test_deduplicated_expert_exchange_matches_the_plain_one():
         assert abs(r["plain"][4] - r["dedup"][4]) < 1e-6                          # same drops
         assert r["capped"][4] > r["plain"][4] + 0.05                              # pairs beyond the parcel are dropped
         assert np.isfinite(r["capped"][0]).all() and np.abs(r["capped"][0] - r["plain"][0]).max() > 1e-3
+        e_plain, e_dedup, y_plain, y_dedup = r["bank_err"]
+        assert np.abs(y_plain - y_dedup).max() < 2e-5 * max(1.0, np.abs(y_plain).max())
+        assert e_plain.max() > 0 and np.abs(e_plain - e_dedup).max() < 1e-5 * e_plain.max() + 1e-9

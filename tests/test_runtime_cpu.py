@@ -471,3 +471,32 @@ def test_recipe_runs_both_models_end_to_end(tmp_path, monkeypatch, capsys):
     assert "[recipe] T tiny" in out and "[recipe] ours tiny" in out
     assert "trust" in out.split("[recipe] T tiny")[1] and "trust" not in out.split("[recipe] T tiny")[0]   # locks: ours only
     assert os.path.exists(tmp_path / "art" / "env.json")
+
+
+def test_muon_combo_follows_torch_muon():
+    """Muon on hidden matrices + AdamW on the rest (the reference's OPT=muon race optimizer, fastloop.py:63-82):
+    three steps against torch.optim.Muon(adjust_lr_fn="match_rms_adamw") + AdamW on the same gradients."""
+    import torch
+    from memarch_b200.optim.muon import MuonAdamW, orthogonalise
+    torch.manual_seed(0)
+    shapes = [(48, 32), (32, 64), (20000, 8), (16,)]
+    mk = lambda: [torch.nn.Parameter(torch.randn(*s) * 0.1) for s in shapes]
+    torch.manual_seed(1); a = mk()
+    torch.manual_seed(1); b = mk()
+    ours = MuonAdamW(a, lr=0.02, weight_decay=0.1, betas=(0.9, 0.95), mul=1.5)
+    assert [tuple(p.shape) for p in ours.mats] == [(48, 32), (32, 64)]             # the word table and the vector go to AdamW
+    ref_m = torch.optim.Muon(b[:2], lr=0.02 * 1.5, weight_decay=0.1, adjust_lr_fn="match_rms_adamw")
+    ref_a = torch.optim.AdamW(b[2:], lr=0.02, betas=(0.9, 0.95), weight_decay=0.1)
+    for step in range(3):
+        g = torch.Generator().manual_seed(10 + step)
+        for p, r in zip(a, b):
+            p.grad = torch.randn(p.shape, generator=g)
+            r.grad = p.grad.clone()
+        ours.step(); ref_m.step(); ref_a.step()
+    for p, r in zip(a, b):
+        assert (p - r).abs().max() < 5e-3 * max(1.0, float(r.abs().max())), float((p - r).abs().max())   # torch iterates in bf16
+    o = orthogonalise(torch.randn(24, 40))
+    sv = torch.linalg.svdvals(o)
+    assert sv.min() > 0.5 and sv.max() < 1.3                                       # singular values pushed towards 1
+    sd = ours.state_dict()
+    ours.load_state_dict(sd)

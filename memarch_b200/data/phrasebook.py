@@ -7,6 +7,10 @@
                      H, a vector to add to the input (tools/phr/trigram_init.py:9-28).
   * `lock_trust`   - hit-rate of the 1/2/3-word locks by rarity bucket of the current word -> initial trust
                      (tools/phr/lock_trust.py:15-31).
+  * `context_table` order 3 - the three-word table (`PHRASE4`, tools/phr/quad_init.py); `skip_table` - "draft ahead"
+                     vectors for offsets 2..4 (`SKIP`, tools/phr/skip_init.py); `phrase_units` - phrase vocabulary and
+                     the rewritten corpus (tools/phr/phrase_tok.py); `slice_report` - per-slice loss gap against a
+                     rival model (tools/phr/diag_analyze.py).
   * `token_counts` - unigram counts.
   * `prior_top`    - top-32 continuations per word (tools/phr/prior_top.py), `entropy` per word (ent.py).
 `build_all(tokens, d, out_dir)` writes bigram.pt, trigram.pt, lock_trust.pt, token_counts.npy.
@@ -53,28 +57,161 @@ def bigram_init(a, d, vocab=50257, phrase_c=0.05, niter=4, seed=0, with_ent=Fals
     return out
 
 
-def phrase_table(a, H, K, vocab=50257, device="cpu"):
+def _project_onto_head(H, rows, cols, vals, n_rows, device="cpu"):
+    """Rows of a sparse (n_rows, V) PPMI matrix M expressed in the basis of the output table H (V, d): the ridge
+    solution P of P · Hᵀ ≈ M, so that a row of P can be added to the model's input like a word vector."""
+    Hd = H.to(device).double()
+    M = torch.sparse_coo_tensor(torch.tensor(np.stack([rows, cols])), torch.tensor(vals), (n_rows, Hd.shape[0])).coalesce().to(device)
+    gram = Hd.T @ Hd + 1e-3 * torch.eye(Hd.shape[1], dtype=Hd.dtype, device=device)
+    return torch.linalg.solve(gram, (M @ Hd).T).T.float()
+
+
+def context_table(a, H, K, order=2, vocab=50257, device="cpu"):
+    """The K most frequent contexts of `order` consecutive words -> a vector forecasting the word after them.
+    order 2 is the phrase table (tools/phr/trigram_init.py:9-28), order 3 the three-word table the model loads as
+    `PHRASE4` (tools/phr/quad_init.py:9-27).  Key of a context: its words as digits of a base-`vocab` number, first
+    word most significant; returns {"keys": sorted int64 (K,), "vec": (K, d)}."""
     a = np.asarray(a, dtype=np.int64)
-    V = vocab
-    ctx = a[:-2] * V + a[1:-1]
+    V, n = vocab, order
+    span = len(a) - n                                    # contexts that have a next word
+    ctx = np.zeros(span, dtype=np.int64)
+    for j in range(n):
+        ctx = ctx * V + a[j:j + span]
+    nxt_all = a[n:]
     uc, cc = np.unique(ctx, return_counts=True)
     K = min(K, len(uc))
-    top = uc[np.argsort(-cc, kind="stable")[:K]]
-    keys = np.sort(top)
+    keys = np.sort(uc[np.argsort(-cc, kind="stable")[:K]])
     pos = np.searchsorted(keys, ctx)
     hit = (pos < K) & (keys[np.minimum(pos, K - 1)] == ctx)
-    row, nxt = pos[hit], a[2:][hit]
-    trip = row * V + nxt
-    ut, ct = np.unique(trip, return_counts=True)
-    r, n = ut // V, ut % V
-    crow = np.bincount(row, minlength=K).astype(np.float64)
-    cn = np.bincount(a[2:], minlength=V).astype(np.float64)
-    pmi = np.log(ct * len(a) / (crow[r] * cn[n]))
+    row, nxt = pos[hit], nxt_all[hit]
+    ut, ct = np.unique(row * V + nxt, return_counts=True)
+    r, w = ut // V, ut % V
+    per_row = np.bincount(row, minlength=K).astype(np.float64)
+    per_word = np.bincount(nxt_all, minlength=V).astype(np.float64)
+    pmi = np.log(ct * len(a) / (per_row[r] * per_word[w]))
     keep = (pmi > 0) & (ct >= 2)
-    Hd = H.to(device).double()
-    M = torch.sparse_coo_tensor(torch.tensor(np.stack([r[keep], n[keep]])), torch.tensor(pmi[keep]), (K, V)).coalesce().to(device)
-    P = torch.linalg.solve(Hd.T @ Hd + 1e-3 * torch.eye(Hd.shape[1], dtype=Hd.dtype, device=device), (M @ Hd).T).T
-    return {"keys": torch.tensor(keys), "vec": P.float()}
+    return {"keys": torch.tensor(keys), "vec": _project_onto_head(H, r[keep], w[keep], pmi[keep], K, device)}
+
+
+def phrase_table(a, H, K, vocab=50257, device="cpu"):
+    return context_table(a, H, K, 2, vocab, device)
+
+
+def skip_table(a, H, offsets=(2, 3, 4), vocab=50257, min_count=3, device="cpu"):
+    """"Draft ahead": what usually stands o words after this word, for each o in `offsets` - PPMI(word_t, word_t+o)
+    in the basis of H; the file the model loads as `SKIP` is {o: (V, d)} (tools/phr/skip_init.py:9-21)."""
+    a = np.asarray(a, dtype=np.int64)
+    V = vocab
+    freq = np.bincount(a, minlength=V).astype(np.float64)
+    out = {}
+    for o in offsets:
+        u, c = np.unique(a[:-o] * V + a[o:], return_counts=True)
+        first, later = u // V, u % V
+        pmi = np.log(c * (len(a) - o) / (freq[first] * freq[later]))
+        keep = (pmi > 0) & (c >= min_count)
+        out[int(o)] = _project_onto_head(H, first[keep], later[keep], pmi[keep], V, device)
+    return out
+
+
+def phrase_units(a, n_units, vocab=50257, eot=50256, count_from=None):
+    """Phrase vocabulary: the `n_units` n-grams (n = 2..4, not crossing a document end) whose merging saves the most
+    steps (count x (n-1)) become units with ids vocab, vocab+1, ...; the text is rewritten greedily, longest units
+    first, left to right within a length (tools/phr/phrase_tok.py:6-61).  Returns (rewritten tokens uint32, units as
+    an (n_units, 4) int64 array padded with -1).  `count_from`: slice of `a` the frequencies are taken from."""
+    a = np.asarray(a, dtype=np.int64)
+    V = vocab
+    src = a[count_from] if count_from is not None else a
+
+    def keys_of(t, n):
+        k = np.zeros(len(t) - n + 1, dtype=np.int64)
+        for j in range(n):
+            k = k * V + t[j:len(t) - n + 1 + j]
+        return k
+
+    scored = []
+    for n in (2, 3, 4):
+        if len(src) < n:
+            continue
+        k = keys_of(src, n)
+        inside = np.ones(len(k), dtype=bool)
+        for j in range(n):
+            inside &= src[j:len(src) - n + 1 + j] != eot
+        u, c = np.unique(k[inside], return_counts=True)
+        best = np.argsort(-c, kind="stable")[:n_units]
+        scored += [(int(c[i]) * (n - 1), n, int(u[i])) for i in best]
+    scored.sort(reverse=True)
+    by_len = {}
+    for _, n, key in scored[:n_units]:
+        by_len.setdefault(n, []).append(key)
+    units, unit_id = [], {}
+    for n in (4, 3, 2):
+        for key in by_len.get(n, []):
+            unit_id[(n, key)] = V + len(units)
+            digits = [(key // V ** (n - 1 - j)) % V for j in range(n)]
+            units.append(digits + [-1] * (4 - n))
+    covered = np.zeros(len(a), dtype=bool)
+    starts = np.full(len(a), -1, dtype=np.int64)
+    for n in (4, 3, 2):
+        if n not in by_len or len(a) < n:
+            continue
+        k = keys_of(a, n)
+        table = np.sort(np.asarray(by_len[n], dtype=np.int64))
+        at = np.searchsorted(table, k).clip(max=len(table) - 1)
+        free_from = 0                                       # first position not inside a unit of this length
+        for i in np.nonzero(table[at] == k)[0]:
+            if i >= free_from and not covered[i:i + n].any():
+                covered[i:i + n] = True
+                starts[i] = unit_id[(n, int(k[i]))]
+                free_from = i + n
+    keep = ~covered | (starts >= 0)
+    return np.where(starts >= 0, starts, a)[keep].astype(np.uint32), np.asarray(units, dtype=np.int64).reshape(-1, 4)
+
+
+def slice_report(ours, theirs, x, y, counts, ph=None, T=1024, phrase_c=0.05):
+    """Where a rival model is better: mean per-word loss of both and the share of the total gap, by slices of the
+    target word's frequency, the position in the window, the pair forecaster's surprise (with `ph`, the bigram
+    artefact) and whether the target already occurred in the window (tools/phr/diag_analyze.py:3-41).
+    ours / theirs: per-word losses; x / y: inputs and targets (flat, windows of T).  Returns {slice group: rows}
+    with rows (label, share of words, ours, theirs, gap, share of the gap)."""
+    ours, theirs = np.asarray(ours, dtype=np.float64), np.asarray(theirs, dtype=np.float64)
+    x, y = np.asarray(x, dtype=np.int64), np.asarray(y, dtype=np.int64)
+    gap = ours - theirs
+    total = gap.sum()
+
+    def rows(masks, labels):
+        out = []
+        for m, l in zip(masks, labels):
+            if m.any():
+                out.append((l, float(m.mean()), float(ours[m].mean()), float(theirs[m].mean()), float(gap[m].mean()),
+                            float(gap[m].sum() / total) if total else 0.0))
+            else:
+                out.append((l, 0.0, float("nan"), float("nan"), float("nan"), 0.0))
+        return out
+
+    fq = np.asarray(counts)[np.minimum(y, len(counts) - 1)]
+    pos = np.tile(np.arange(T), len(x) // T + 1)[:len(x)]
+    rep = np.zeros(len(x), dtype=bool)
+    for w0 in range(0, len(x), T):
+        seen = set()
+        for i in range(w0, min(w0 + T, len(x))):
+            rep[i] = y[i] in seen
+            seen.add(x[i])
+    report = {
+        "frequency of the target": rows([fq >= 1e5, (fq >= 1e4) & (fq < 1e5), (fq >= 1e3) & (fq < 1e4), (fq >= 100) & (fq < 1e3),
+                                         fq < 100], [">=100k", "10k-100k", "1k-10k", "100-1k", "<100"]),
+        "position in the window": rows([pos < 16, (pos >= 16) & (pos < 128), (pos >= 128) & (pos < 512), pos >= 512],
+                                       ["0-15", "16-127", "128-511", "512+"]),
+        "target seen in the window": rows([rep, ~rep], ["seen", "new"]),
+    }
+    if ph is not None:
+        E, H, lp = ph["emb"], ph["head"], ph["logp_next"]
+        En = E / E.pow(2).mean(1, keepdim=True).sqrt().clamp(min=1e-6)
+        top = E.shape[0] - 1
+        xx, yy = torch.tensor(np.minimum(x, top)), torch.tensor(np.minimum(y, top))
+        sp = (ph["lse"][xx] - (phrase_c * (En[xx] * H[yy]).sum(-1) + lp[yy])).numpy()
+        report["surprise of the pair forecaster"] = rows([sp < 2, (sp >= 2) & (sp < 5), (sp >= 5) & (sp < 8), sp >= 8],
+                                                         ["<2", "2-5", "5-8", ">=8 (anchors)"])
+    return report
 
 
 def lock_trust(a, vocab, counts, T=1024, max_tokens=4_000_000, device="cpu"):
@@ -109,8 +246,9 @@ def prior_top(ph, k=32, phrase_c=0.05):
     return torch.cat(idx), torch.cat(val)
 
 
-def build_all(tokens, d, out_dir, vocab=50257, phrase_k=262144, seed=0):
-    """Write every artefact of the published recipe under `out_dir`; returns the paths."""
+def build_all(tokens, d, out_dir, vocab=50257, phrase_k=262144, seed=0, quad_k=0, skip=False):
+    """Write every artefact of the published recipe under `out_dir` (plus the three-word table with `quad_k` and the
+    draft-ahead tables with `skip`); returns the paths."""
     os.makedirs(out_dir, exist_ok=True)
     paths = {k: os.path.join(out_dir, v) for k, v in
              dict(bigram="bigram.pt", trigram="trigram.pt", lock="lock_trust.pt", counts="token_counts.npy").items()}
@@ -120,6 +258,12 @@ def build_all(tokens, d, out_dir, vocab=50257, phrase_k=262144, seed=0):
     torch.save(ph, paths["bigram"])
     torch.save(phrase_table(tokens, ph["head"], phrase_k, vocab), paths["trigram"])
     torch.save(lock_trust(tokens, vocab, cnt), paths["lock"])
+    if quad_k:
+        paths["quad"] = os.path.join(out_dir, "quad.pt")
+        torch.save(context_table(tokens, ph["head"], quad_k, 3, vocab), paths["quad"])
+    if skip:
+        paths["skip"] = os.path.join(out_dir, "skip.pt")
+        torch.save(skip_table(tokens, ph["head"], vocab=vocab), paths["skip"])
     return paths
 
 

@@ -427,3 +427,53 @@ def test_weight_tree_round_trip_through_npz(tmp_path):
     grads = {"emb.weight": torch.ones(512, 4), "heavy.0.up": torch.zeros(2, 3, 4), "heavy.1.up": torch.ones(2, 3, 4)}
     gt, _ = convert.to_tree(grads)                                           # partial dicts convert too
     assert gt["heavy"]["up"].shape == (2, 2, 3, 4) and set(gt["heavy"]) == {"up"}
+
+
+def test_three_word_table_skip_tables_and_phrase_units(tmp_path):
+    """The remaining phrase builders: three-word context table and draft-ahead tables load into the model and feed its
+    input; the phrase vocabulary rewrites a corpus reversibly; the slice report accounts for the whole gap."""
+    import numpy as np
+    from memarch_b200.build import build
+    from memarch_b200.data import phrasebook
+    from memarch_b200.data.synth import MarkovCorpus
+    vocab, phr_v, d = 512, 500, 256
+    toks = MarkovCorpus(vocab=phr_v, n_succ=8, seed=0).stream(40_000, text_len=256, seed=1)
+    paths = phrasebook.build_all(toks, d, str(tmp_path), vocab=phr_v, phrase_k=1024, quad_k=512, skip=True)
+    quad, skip = torch.load(paths["quad"]), torch.load(paths["skip"])
+    assert quad["keys"].shape == (512,) and quad["vec"].shape == (512, d)
+    assert bool((quad["keys"][1:] > quad["keys"][:-1]).all())
+    # a stored key is the three words as base-V digits, and that triple occurs in the corpus
+    k0 = int(quad["keys"][100])
+    w = [k0 // phr_v ** 2, (k0 // phr_v) % phr_v, k0 % phr_v]
+    a = np.asarray(toks, dtype=np.int64)
+    assert ((a[:-2] == w[0]) & (a[1:-1] == w[1]) & (a[2:] == w[2])).any()
+    assert sorted(skip) == [2, 3, 4] and all(skip[o].shape == (phr_v, d) for o in skip)
+    np.save(tmp_path / "token_counts.npy", phrasebook.token_counts(toks, vocab))
+    env = {"PHRASE_INIT": paths["bigram"], "PHRASE3": paths["trigram"], "PHRASE4": paths["quad"], "SKIP": paths["skip"],
+           "PHR_V": str(phr_v), "VOCAB": str(vocab), "NO_MEM": "1"}
+    m = build("Fv2s", vocab, env=env)
+    assert hasattr(m, "phr4") and hasattr(m, "skip")
+    x = torch.tensor(a[:2 * 65].reshape(2, 65))
+    out, cost = m(x[:, :-1])
+    loss = m.train_loss(out, x[:, 1:], True)
+    loss.backward()
+    assert torch.isfinite(loss) and m.phr4.weight.grad is not None
+
+    # phrase vocabulary: every unit expands back to the original words
+    eot = phr_v - 1
+    new, units = phrasebook.phrase_units(a[:20_000], 200, vocab=phr_v, eot=eot)
+    assert units.shape == (200, 4) and len(new) < 20_000
+    back = []
+    for t in new.astype(np.int64):
+        back += [int(t)] if t < phr_v else [int(u) for u in units[t - phr_v] if u >= 0]
+    assert back == a[:20_000].tolist()
+    assert not (units == eot).any()                                  # no unit crosses a document end
+
+    # slice report: the shares of the gap sum to one inside every slice group
+    g = np.random.default_rng(0)
+    x1, y1 = a[:4096], a[1:4097]
+    ours, theirs = g.random(4096) + 3.0, g.random(4096) + 2.8
+    rep = phrasebook.slice_report(ours, theirs, x1, y1, phrasebook.token_counts(toks, vocab), torch.load(paths["bigram"]), T=1024)
+    assert len(rep) == 4
+    for rows in rep.values():
+        assert abs(sum(r[5] for r in rows) - 1.0) < 1e-9 and abs(sum(r[1] for r in rows) - 1.0) < 1e-9

@@ -141,6 +141,13 @@ class OptConfig:
     damp_p: float = 1.0           #     into the momentum and the tensor's step shrinks by (damp x usual / |g|)^damp_p
     damp_beta: float = 0.99       #     EMA of the usual squared norm (per situation card)
     damp_cap: float = 2.0         #     a surge enters that EMA as at most (cap x usual)^2: the brake does not get used to it
+    err_step: bool = False        # with damp > 0: every tensor's step x clip(usual |g| / |g| now, 0, err_cap) ("divide by
+    err_cap: float = 3.0          #     the sensitivity"); the gradient enters the momentum unclipped
+    gearbox: bool = False         # with damp > 0: per-tensor gears (0.25, 0.5, 1, gb_top) shifted one at a time - down when
+    gb_down: float = 2.0          #     |g| > gb_down x usual (or when above the limit 1.0 while the loss is worse than
+    gb_up: float = 1.3            #     expected), up when |g| < gb_up x usual and the speed has reached the gear; the
+    gb_acc: float = 0.05          #     step multiplier moves towards the gear by at most gb_acc per step
+    gb_top: float = 1.25
     snr: bool = False             # confidence brake: step x clip(|m_new| / sqrt(EMA |g|^2) / snr_ref, snr_floor, 1) per tensor
     snr_beta: float = 0.95
     snr_ref: float = 1.0

@@ -76,6 +76,9 @@ class Instinct:
         self.lr_mul_dev = None         # optional 0-dim device tensor multiplying the step (set by the rollback guard)
         self.dv = torch.zeros(cfg.cards, P, device=dev) if cfg.damp > 0 else None   # usual |g|^2 per (card, weight)
         self.df = torch.ones(P, device=dev) if cfg.damp > 0 else None               # last damping factor (for the log)
+        geared = cfg.damp > 0 and cfg.gearbox
+        self.gear = torch.full((P,), 2, dtype=torch.long, device=dev) if geared else None   # index into the gear table
+        self.speed = torch.ones(P, device=dev) if geared else None                          # current step multiplier
         self.snr_v = torch.zeros(P, device=dev) if cfg.snr else None                # EMA of |g|^2 (or of c^2, dead-zone form)
         self.snr_f = torch.ones(P, device=dev) if cfg.snr else None                 # last factor (for the log)
         self.rows = {}
@@ -197,7 +200,9 @@ class Instinct:
         if self.cfg.surge_thr > 0:                       # surprise brake (device scalars only)
             bad = (-self.s).clamp(min=self.cfg.surge_thr)
             lr_t = lr_t * (self.cfg.surge_thr / bad) ** 2
-        if self.dv is not None and not vocab:
+        if self.dv is not None and (self.cfg.gearbox or self.cfg.err_step):
+            lr_t = self._pace(i, grad, lr_t)
+        elif self.dv is not None and not vocab:
             grad, lr_t = self._damp(i, grad, lr_t)
         if self.snr_v is not None and not vocab and self.m[i].shape == grad.shape:
             lr_t = self._snr(i, grad, lr_t)
@@ -231,6 +236,38 @@ class Instinct:
         self.dv[:, i] += self.oh * (torch.where(gg > 0, new, dv) - dv)
         self.df[i] = f
         return (grad * f.to(grad.dtype), lr_t * f ** c.damp_p)
+
+    def _pace(self, i, grad, lr_t):
+        """Two step-length rules of the reference's JAX Instinct that read |g| against its usual value on the current
+        card and leave the gradient itself alone (instinct.py:150-172, 753-772, 918-937).
+        err_step: step x clip(usual |g| / |g|, 0, err_cap) - a tensor whose sensitivity surges 28x takes a 28x shorter
+        step.  gearbox: the multiplier follows a gear (0.25, 0.5, 1, gb_top), shifted one gear per step - down on a
+        surge above gb_down x usual, or when driving above 1.0 while the step's loss is worse than expected; up when
+        calm (below gb_up x usual) and the speed has caught up with the current gear - and the speed itself changes by
+        at most gb_acc per step.  Device-side, no host sync."""
+        c = self.cfg
+        gg = grad.float().pow(2).sum()
+        dv = (self.oh @ self.dv)[i]
+        live, started = gg > 0, dv > 0
+        into = torch.minimum(gg, (c.damp_cap ** 2) * dv)
+        usual = torch.where(started, c.damp_beta * dv + (1 - c.damp_beta) * into, gg)
+        self.dv[:, i] += self.oh * (torch.where(live, usual, dv) - dv)
+        if c.gearbox:
+            gears = torch.tensor([0.25, 0.5, 1.0, c.gb_top], device=gg.device)
+            ratio = torch.where(started & live, (gg / dv.clamp(min=1e-38)).sqrt(), torch.ones_like(gg))
+            v, gi = self.speed[i], self.gear[i]
+            fined = (v > 1.0) & (self.s < 0)
+            down = (ratio > c.gb_down) | fined
+            up = (ratio < c.gb_up) & ~fined & (v >= gears[gi] - 1e-3)
+            shift = torch.where(down, -1, torch.where(up, 1, 0))
+            gi_new = torch.where(live, (gi + shift).clamp(0, 3), gi)
+            v_new = torch.where(live, v + (gears[gi_new] - v).clamp(-c.gb_acc, c.gb_acc), v)
+            self.gear[i], self.speed[i] = gi_new, v_new
+            f = v_new
+        else:
+            f = torch.where(started & live, (dv / gg.clamp(min=1e-38)).sqrt().clamp(0, c.err_cap), torch.ones_like(gg))
+        self.df[i] = f
+        return lr_t * f
 
     def _snr(self, i, grad, lr_t):
         """Confidence of a tensor's direction (the reference's JAX Instinct, instinct.py:76-84, 100-104, 953-975):

@@ -500,3 +500,45 @@ def test_muon_combo_follows_torch_muon():
     assert sv.min() > 0.5 and sv.max() < 1.3                                       # singular values pushed towards 1
     sd = ours.state_dict()
     ours.load_state_dict(sd)
+
+
+def test_err_step_and_gearbox_pace_the_step():
+    """Step-length rules on |g| against its usual value: err_step divides by the sensitivity; the gearbox shifts one
+    gear at a time and its speed moves by at most gb_acc per step (JAX Instinct, instinct.py:150-172, 753-772)."""
+    import torch
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    torch.manual_seed(0)
+    sit = torch.randn(16)
+
+    def run(cfg, scales):
+        p = torch.nn.Parameter(torch.randn(32, 24) * 0.1)
+        opt = Instinct([p], cfg)
+        g0 = torch.randn(32, 24)
+        facs = []
+        for sc in scales:
+            opt.prepare(torch.tensor(3.0), sit)
+            p.grad = g0 * sc
+            opt.update(p)
+            p.grad = None
+            opt.finish()
+            facs.append(float(opt.df[0]))
+        return facs, opt
+
+    calm = [1.0] * 12
+    f, _ = run(OptConfig(lr=1e-3, damp=3.0, err_step=True), calm + [4.0, 1.0])
+    assert all(abs(x - 1.0) < 1e-5 for x in f[1:12])            # usual |g|: the step is what it was
+    assert abs(f[12] - 0.25) < 1e-3                               # 4x the sensitivity: a quarter of the step
+    assert abs(f[13] - 1.0) < 0.2                                 # the surge entered the usual norm capped: back to ~1
+    f, _ = run(OptConfig(lr=1e-3, damp=3.0, err_step=True, err_cap=2.0), calm + [0.1])
+    assert abs(f[12] - 2.0) < 1e-5                                # capped
+
+    f, opt = run(OptConfig(lr=1e-3, damp=3.0, gearbox=True), calm + [3.0, 3.0, 3.0, 1.0])
+    assert 1.0 <= f[0] <= 1.05 + 1e-6
+    top = max(f[:12])
+    assert 1.0 < top <= 1.25 + 1e-6                               # calm driving shifts up towards the top gear
+    steps = [abs(b - a) for a, b in zip(f, f[1:])]
+    assert max(steps) <= 0.05 + 1e-6                              # the speed never jumps
+    assert f[14] < f[11] and int(opt.gear[0]) < 3                 # three surges: geared down, slowing
+    sd = opt.state_dict()
+    assert "gear" in sd and "speed" in sd

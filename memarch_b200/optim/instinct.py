@@ -25,6 +25,8 @@ from ..ops import _ext, ref
 
 
 def _kind_code(kind):
+    """Kernel form of a normalisation kind, -1 = PyTorch statement (hsn<n> with two or more "columns, rows" rounds;
+    one round, `norm="hs1"`, is `hs` itself and takes its kernels - see `Instinct.spec`)."""
     return {"tensor": 0, "row": 1, "row3": 2, "vocab": 3, "hs": 4, "hs3": 5}.get(kind, -1)
 
 
@@ -149,7 +151,7 @@ class Instinct:
     def spec(self, p):
         """(kind, has weight decay, is a word table) from the weight's shape (exp_opt.py:653-665)."""
         vocab_table = p.dim() == 2 and p.shape[0] >= 10000
-        n = self.norm
+        n = "hs" if self.norm == "hs1" else self.norm          # one homeostasis round is the plain form
         if vocab_table:
             kind = "vocab"
         elif n == "row" and p.dim() == 3:

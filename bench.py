@@ -60,6 +60,10 @@ def parse():
         a.wave = a.wave or 40
     elif a.config == 4:
         a.model, a.batch, a.seq, a.mem = "longctx_1024", 4, 16384, True
+    if a.graph:
+        # one graph is captured after three eager steps and a second one at the first step that also measures
+        # |g|/|w| (every 8th step of the recipe): both captures must fall into the warm-up
+        a.warmup = max(a.warmup, 10)
     return a
 
 

@@ -5,6 +5,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace mb {
@@ -308,7 +310,9 @@ torch::Tensor moe_route_bwd(torch::Tensor probs, torch::Tensor top_e, torch::Ten
 }
 
 // Keys and locks: for each position t and n-gram length n = 1..n_keys, the latest j < t whose n-gram ending at j
-// equals the one ending at t; the candidate is the token after j.  One block per text, tokens staged in shared memory.
+// equals the one ending at t; the candidate is the token after j.  The text is staged in shared memory; grid (texts,
+// slices): a block takes runs of blockDim positions spread evenly over the text (late positions scan further back, so
+// contiguous halves would be unbalanced), which keeps a batch of few long texts (4 x 16 384) on all SMs.
 __global__ void lock_find_kernel(const long long* __restrict__ x, long long* __restrict__ cand, bool* __restrict__ on,
                                  long long* __restrict__ src, int T, int n_keys, int longest_only) {
   extern __shared__ int tok[];
@@ -316,7 +320,7 @@ __global__ void lock_find_kernel(const long long* __restrict__ x, long long* __r
   const long long* xr = x + (long long)b * T;
   for (int t = threadIdx.x; t < T; t += blockDim.x) tok[t] = (int)xr[t];
   __syncthreads();
-  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+  for (int t = blockIdx.y * blockDim.x + threadIdx.x; t < T; t += gridDim.y * blockDim.x) {
     int last[3] = {-1, -1, -1};
     const int a0 = tok[t], a1 = t >= 1 ? tok[t - 1] : -1, a2 = t >= 2 ? tok[t - 2] : -1;
     int need = n_keys;                                   // how many key lengths are still unresolved
@@ -361,7 +365,9 @@ std::vector<torch::Tensor> lock_find(torch::Tensor x, int64_t vocab, int64_t n_k
     size_t smem = (size_t)T * 4;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(lock_find_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    lock_find_kernel<<<B, 1024, smem, cur_stream()>>>(reinterpret_cast<const long long*>(x.data_ptr<int64_t>()),
+    const int threads = 256;
+    const int slices = std::max(1, std::min((T + threads - 1) / threads, (4 * 148 + B - 1) / B));
+    lock_find_kernel<<<dim3(B, slices), threads, smem, cur_stream()>>>(reinterpret_cast<const long long*>(x.data_ptr<int64_t>()),
         reinterpret_cast<long long*>(cand.data_ptr<int64_t>()), on.data_ptr<bool>(),
         reinterpret_cast<long long*>(src.data_ptr<int64_t>()), T, (int)n_keys, longest_only ? 1 : 0);
   }

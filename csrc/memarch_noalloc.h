@@ -15,8 +15,11 @@
  *
  * Limits and rules
  *   - Scratch: a file-scope __device__ array of MEMARCH_NOALLOC_SCRATCH_FLOATS floats (4 MiB), present once on every
- *     GPU that loads the library until the process exits.  A call needs about 3*rows + 2*cols (+ up to 21) floats of it; larger
- *     problems are refused with MEMARCH_NOALLOC_TOO_LARGE and a message on stderr - nothing is launched.
+ *     GPU that loads the library until the process exits.  A call needs 3*pad4(rows) + 2*pad4(cols) + 4 floats of it
+ *     (pad4 = rounded up to a multiple of 4; at most 3*rows + 2*cols + 19); larger problems are refused with
+ *     MEMARCH_NOALLOC_TOO_LARGE and a message on stderr - nothing is launched.
+ *   - Rows of more than 51 200 columns are refused the same way: the kernels stage one row of column scales
+ *     (4 bytes per column) in shared memory and ask for at most 200 KB of it.
  *   - The first call on a device looks up the device address of that array (cudaGetSymbolAddress, with that device
  *     current) and keeps it.  Make this first call outside of any CUDA stream capture.
  *   - Every call uses the same array and the array keeps what the previous call left; the function clears the

@@ -63,11 +63,11 @@ def test_fused_matches_nccl_on_two_gpus():
         assert res["n_sharded"] > 0, "the row-sharded optimizer path was not taken"
         ln, lf = res["nccl"][0], res["fused"][0]
         for a, b in zip(ln, lf):
-            assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (rank, ln, lf)
-        for k, v in res["nccl"][1].items():
-            w = res["fused"][1][k]
-            den = np.abs(v).max() + 1e-6
-            assert np.abs(v - w).max() / den < 5e-2, (rank, k)
+            assert abs(a - b) < 5e-3 * max(1.0, abs(a)), (rank, ln, lf)
+        worst = max((np.abs(v - res["fused"][1][k]).max() / (np.abs(v).max() + 1e-6), k) for k, v in res["nccl"][1].items())
+        print(f"rank {rank}: losses {ln} / {lf}; largest weight difference {worst[0]:.2e} of the weight's range ({worst[1]})")
+        # bf16 weights stepped with stochastic rounding by two different reduction orders: a few bf16 steps apart
+        assert worst[0] < 2e-2, worst
 
 
 def _single_rank(q):
@@ -141,10 +141,10 @@ def test_fused_kernels_on_one_rank_match_plain_path():
     assert res["n_sharded"] > 0, "the row-sharded optimizer path was not taken"
     assert max(res["bank_err"]) < 1e-2, res["bank_err"]              # y, d xe, d up, d down of a layer with frozen experts
     for a, b in zip(res["plain"][0], res["fused"][0]):
-        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (res["plain"][0], res["fused"][0])
+        assert abs(a - b) < 5e-3 * max(1.0, abs(a)), (res["plain"][0], res["fused"][0])
     for k, v in res["plain"][1].items():
         w = res["fused"][1][k]
-        assert np.abs(v - w).max() / (np.abs(v).max() + 1e-6) < 5e-2, k
+        assert np.abs(v - w).max() / (np.abs(v).max() + 1e-6) < 2e-2, k            # a few bf16 steps (stochastic rounding)
 
 
 def test_bounded_barrier_wait_runs_out_and_reports():

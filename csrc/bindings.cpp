@@ -49,6 +49,8 @@ std::vector<torch::Tensor> mem_read_fwd(torch::Tensor q, torch::Tensor faces, to
 std::vector<torch::Tensor> mem_read_bwd(torch::Tensor q, torch::Tensor faces, torch::Tensor valid, torch::Tensor w,
                                         torch::Tensor best, torch::Tensor dw, c10::optional<torch::Tensor> dsc, int64_t Fn,
                                         double scale);
+std::vector<torch::Tensor> quant_rows_i8(torch::Tensor x);
+torch::Tensor gemm_i8(torch::Tensor a, torch::Tensor b, torch::Tensor sa, torch::Tensor sb, bool out_f32);
 std::vector<torch::Tensor> reread_fwd(torch::Tensor sc, torch::Tensor pos, torch::Tensor qpos, torch::Tensor rows,
                                       torch::Tensor ids, torch::Tensor table, torch::Tensor offset, torch::Tensor hv,
                                       torch::Tensor hb, torch::Tensor hh, torch::Tensor Wr, torch::Tensor cp, int64_t k);
@@ -112,6 +114,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_bwd_status_read", &mb::attn_bwd_status_read);
   m.def("mem_read_fwd", &mb::mem_read_fwd);
   m.def("mem_read_bwd", &mb::mem_read_bwd);
+  m.def("quant_rows_i8", &mb::quant_rows_i8);
+  m.def("gemm_i8", &mb::gemm_i8);
   m.def("reread_fwd", &mb::reread_fwd);
   m.def("reread_bwd", &mb::reread_bwd);
   m.def("moe_route_fwd", &mb::moe_route_fwd);

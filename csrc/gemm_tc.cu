@@ -1054,7 +1054,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 3-D tensor map: dims (inner, rows, groups), 128-byte swizzle, zero fill outside.  `esz` 2 = bf16, 4 = fp32.
+// 3-D tensor map: dims (inner, rows, groups), 128-byte swizzle, zero fill outside.  `esz` 1 = 8-bit, 2 = bf16, 4 = fp32.
 CUtensorMap make_tmap(const void* base, int esz, uint64_t inner, uint64_t rows, uint64_t groups, uint64_t row_pitch_el,
                       uint64_t group_pitch_el, uint32_t box_inner, uint32_t box_rows, bool promote) {
   // cuTensorMapEncodeTiled is a driver call: a thread that has made no runtime call yet (an autograd worker) has no
@@ -1068,7 +1068,9 @@ CUtensorMap make_tmap(const void* base, int esz, uint64_t inner, uint64_t rows, 
   cuuint32_t estr[3] = {1, 1, 1};
   TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA operand must be 16-byte aligned");
   TORCH_CHECK(strides[0] % 16 == 0 && strides[1] % 16 == 0, "TMA operand pitches must be multiples of 16 bytes");
-  CUresult r = encode_fn()(&m, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+  const CUtensorMapDataType dt = esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                : esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = encode_fn()(&m, dt, 3,
                            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B,
                            promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -1090,6 +1092,8 @@ static int* status_word(int device) {
   }
   return words[device];
 }
+
+int* gemm_status_word(int device) { return status_word(device); }
 
 int gemm_status(int device) {
   int v = 0;

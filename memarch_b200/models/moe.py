@@ -16,6 +16,7 @@ err_freeze, move_peak, last_move, hint_avg, learned, up_snap, L_idx, F_idx, up_f
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.nn as nn
@@ -63,6 +64,39 @@ class _ErrProbeWords(torch.autograd.Function):
             place = torch.where(table < N, word[table.clamp(max=N - 1)], word.new_zeros(())) * wtab.float().abs()
             ctx.buf.mul_(0.9).add_(0.1 * place.view(ctx.E, -1).mean(1))
         return g, None, None, None, None
+
+
+class _FrozenBankI8(torch.autograd.Function):
+    """Forward of the frozen int8 bank on the int8 tensor cores: rows of the input and of the hidden activation are
+    quantised (absmax / 127 per row), both products run as `tcgen05.mma.kind::i8` GEMMs against the stored int8 weights
+    with the per-output-column scales applied in the epilogue (the reference's int8 bank: full2.py:919-958 with the
+    matmul of int8mm.py:35-88).  Only the input gets a gradient (the bank is frozen); it is computed in bf16 from the
+    dequantised weights, like the bf16 bank."""
+
+    @staticmethod
+    def forward(ctx, xe, up_t, up_s, down_t, down_s, moe):
+        from ..ops import _ext, int8
+        C = _ext.C()
+        a = int8.quant_mm_stored(xe, up_t, up_s)                               # (F, C, width_in) bf16 pre-activations
+        h = C.relu2_fwd(a) if moe.act == "relu2" else C.swiglu_fwd(a)
+        y = int8.quant_mm_stored(h, down_t, down_s)
+        _ext.count(1)
+        ctx.save_for_backward(a)
+        ctx.moe = moe
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import _ext
+        a, = ctx.saved_tensors
+        moe, C = ctx.moe, _ext.C()
+        up, down = moe._bank_weights("up"), moe._bank_weights("down")          # (F, d, width_in), (F, width_out, d) bf16
+        F_ = up.shape[0]
+        dh = ops.gemm(dy.contiguous(), down, groups=F_)                        # dy (F,C,d) · down (F,width_out,d)ᵀ
+        da = C.relu2_bwd(dh, a) if moe.act == "relu2" else C.swiglu_bwd(dh, a)
+        dx = ops.gemm(da, up, groups=F_)                                       # da (F,C,width_in) · up (F,d,width_in)ᵀ
+        _ext.count(1)
+        return dx, None, None, None, None, None
 
 
 class AnchorMoE(nn.Module):
@@ -192,7 +226,22 @@ class AnchorMoE(nn.Module):
         q = ((q[:, 0::2] & 0x0F) | (q[:, 1::2] << 4)).to(torch.int8)
         return q.contiguous(), sc[:, :, 0].bfloat16().contiguous()
 
+    def _bank_i8(self):
+        """The int8 bank in the layout the int8 GEMM reads (contraction contiguous): (F, out, in) copies of the stored
+        (F, in, out) tables and their fp32 column scales, rebuilt when the bank's tensors change."""
+        key = (self.up_f.data_ptr(), self.down_f.data_ptr(), tuple(self.up_f.shape))
+        if getattr(self, "_i8_key", None) != key:
+            self._i8_cache = (self.up_f.transpose(1, 2).contiguous(), self.up_fs.float().reshape(self.up_f.shape[0], -1).contiguous(),
+                              self.down_f.transpose(1, 2).contiguous(), self.down_fs.float().reshape(self.down_f.shape[0], -1).contiguous())
+            self._i8_key = key
+        return self._i8_cache
+
     def _ffn_frozen(self, xe, counts=None):
+        from ..ops import _ext, int8
+        if (self.bank_q == "int8" and _ext.use_cuda(xe) and xe.dtype == torch.bfloat16 and self.up_f.dtype == torch.int8
+                and int8.i8_ok(xe.shape[1], self.up_f.shape[2], xe.shape[2]) and self.down_f.shape[1] % 16 == 0
+                and os.environ.get("MEMARCH_BANK_I8", "1") != "0"):
+            return _FrozenBankI8.apply(xe.contiguous(), *self._bank_i8(), self)
         return self._ffn(xe, self._bank_weights("up"), self._bank_weights("down"), train_w=False, counts=counts)
 
     def _experts(self, xe, wtab, C):

@@ -81,27 +81,17 @@ class _FusedExpertFFN(torch.autograd.Function):
         M = W * Cn
         h = torch.empty(n_local, M, H, device=xe.device, dtype=torch.bfloat16)
         a = torch.empty_like(h) if act == "relu2" else None
-        xin = None
-        if ep.pull == "tma":
-            # A tiles fetched from the owners' buffers by the GEMM's own TMA loads (one tensor map per source GPU)
-            xptrs = [int(p) for p in Xh.buffer_ptrs]
-            if act == "relu2":
-                C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, h, [], 0, 0, 0, a, None, 1, n_local)
-            else:
-                a = C.gemm_peer(xptrs, Cn, d, E, d, Cn * d, g_off, up, True, None, [], 0, 0, 0, None, None, 0, n_local)
-                h = C.swiglu_fwd(a)
+        # rows of my experts land in local memory first (one bandwidth-bound gather kernel over the peer pointers),
+        # the GEMM reads them locally: fetching remote tiles with the GEMM's own loads put an NVLink round trip into
+        # every stage of its shared-memory ring (measured 22 ms per step slower) and was dropped
+        xin = torch.empty(n_local, M, d, device=xe.device, dtype=torch.bfloat16)
+        C.peer_gather([int(p) for p in Xh.buffer_ptrs], xin, r, Cn, g_off)          # one kernel over all W owners
+        _ext.count()
+        if act == "relu2":
+            gemm(xin, up, b_mn=True, out=h, out2=a, epi=1, groups=n_local)
         else:
-            # rows of my experts land in local memory first (one bandwidth-bound gather kernel over the peer
-            # pointers), the GEMM reads them locally: a remote tile costs an NVLink round trip, more than the
-            # shared-memory ring can hide
-            xin = torch.empty(n_local, M, d, device=xe.device, dtype=torch.bfloat16)
-            C.peer_gather([int(p) for p in Xh.buffer_ptrs], xin, r, Cn, g_off)      # one kernel over all W owners
-            _ext.count()
-            if act == "relu2":
-                gemm(xin, up, b_mn=True, out=h, out2=a, epi=1, groups=n_local)
-            else:
-                a = gemm(xin, up, b_mn=True, groups=n_local)
-                h = C.swiglu_fwd(a)
+            a = gemm(xin, up, b_mn=True, groups=n_local)
+            h = C.swiglu_fwd(a)
         # down-GEMM: A = h, cut into W row segments; segment s goes to rank s's output buffer
         hp = h.data_ptr()
         Hh = h.shape[2]
@@ -114,7 +104,7 @@ class _FusedExpertFFN(torch.autograd.Function):
         _ext.count(3)
         heap.barrier(0)                                             # every expert's rows have landed here
         # the staged rows are kept for the weight gradient: the backward then pulls only dY (E x C x d bf16 per layer)
-        ctx.has_xin = xin is not None and train_w
+        ctx.has_xin = train_w
         ctx.save_for_backward(up, down, a, h, *([xin] if ctx.has_xin else []))
         ctx.ep, ctx.key, ctx.act, ctx.g_off, ctx.n_local, ctx.train_w = ep, key, act, g_off, n_local, train_w
         ctx.shape = (E, Cn, d)
@@ -177,7 +167,6 @@ class FusedExpertExchange:
     def __init__(self, heap):
         self.heap, self.W, self.rank = heap, heap.W, heap.rank
         self._layers, self._grads = {}, {}
-        self.pull = os.environ.get("MEMARCH_EP_PULL", "copy")        # "copy" | "tma"
 
     def layer_buffers(self, key, E, C, d):
         k = (key, E, C, d)

@@ -76,6 +76,19 @@ def report(name, ms, flops=None, nbytes=None, extra=""):
 def cmd_gemm(a):
     from memarch_b200.ops import gemm
     M, N, K, G = a.m, a.n, a.k, a.groups
+    if a.i8:
+        from memarch_b200.ops import _ext
+        C = _ext.C()
+        qa = torch.randint(-127, 128, (G, M, K), device="cuda", dtype=torch.int8)
+        qb = torch.randint(-127, 128, (G, N, K), device="cuda", dtype=torch.int8)
+        sa, sb = torch.rand(G, M, device="cuda") + 0.5, torch.rand(G, N, device="cuda") + 0.5
+        o = C.gemm_i8(qa, qb, sa, sb, True)
+        ref = (qa[:1, :256].double() @ qb[:1].double().transpose(1, 2)) * sa[:1, :256, None].double() * sb[:1, None].double()
+        print(f"parity (first 256 rows) rel err {rel(o[:1, :256], ref):.2e}")
+        report(f"tcgen05 int8 gemm (kind::i8, dequantising epilogue) M{M} N{N} K{K} G{G}",
+               timeit(lambda: C.gemm_i8(qa, qb, sa, sb, False), a.iters, flush=not a.no_flush), 2.0 * M * N * K * G,
+               extra="(integer operations; the denominator is the bf16 figure)")
+        return
     A = torch.randn(G, M, K, device="cuda").bfloat16()
     B = torch.randn(G, N, K, device="cuda").bfloat16()
     Bm = B.transpose(1, 2).contiguous() if a.b_mn else B
@@ -288,6 +301,7 @@ def main(argv=None):
     g.add_argument("--k", type=int, default=8192); g.add_argument("--groups", type=int, default=1)
     g.add_argument("--a-mn", dest="a_mn", action="store_true"); g.add_argument("--b-mn", dest="b_mn", action="store_true")
     g.add_argument("--no-lib", action="store_true"); g.add_argument("--no-flush", action="store_true")
+    g.add_argument("--i8", action="store_true", help="the int8 tensor-core GEMM instead of the bf16 one")
     c = sub.add_parser("ce")
     c.add_argument("--rows", type=int, default=8192); c.add_argument("--d", type=int, default=2064)
     c.add_argument("--vocab", type=int, default=50304); c.add_argument("--mix", action="store_true")

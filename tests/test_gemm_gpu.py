@@ -366,3 +366,72 @@ def test_ffn_node_matches_fp32(act, fuse, monkeypatch):
     for a, b in ((x.grad, xr.grad), (wu.grad, ur.grad), (wd.grad, dr.grad)):
         assert _rel(a, b) < 2e-2, _rel(a, b)
     assert _ext().gemm_status(0) == 0
+
+
+# ------------------------------------------------------------------------------------------------ int8 tensor cores
+@pytest.mark.parametrize("G,M,N,K", [(1, 128, 256, 128), (1, 300, 520, 272), (1, 2049, 2048, 2048), (3, 200, 384, 256),
+                                      (1, 40, 72, 48)])
+def test_int8_gemm_is_exact(G, M, N, K):
+    """kind::i8 GEMM: integer products are exact, so the fp32 output equals (a · bᵀ in int64) x row scale x column
+    scale to fp32 rounding; ragged M / N / K tails and grouped launch included."""
+    C = _ext()
+    g = torch.Generator(device="cuda").manual_seed(G * 1000 + M)
+    shp = (lambda *s: s) if G == 1 else (lambda *s: (G, *s))
+    a = torch.randint(-127, 128, shp(M, K), device="cuda", generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, shp(N, K), device="cuda", generator=g, dtype=torch.int8)
+    sa = torch.rand(shp(M), device="cuda", generator=g) + 0.5
+    sb = torch.rand(shp(N), device="cuda", generator=g) + 0.5
+    out = C.gemm_i8(a, b, sa, sb, True)
+    torch.cuda.synchronize()
+    assert C.gemm_status(0) == 0
+    ref = (a.double() @ b.double().transpose(-1, -2)) * sa.double()[..., :, None] * sb.double()[..., None, :]
+    assert (out.double() - ref).abs().max() <= 1e-6 * ref.abs().max()
+    o16 = C.gemm_i8(a, b, sa, sb, False)
+    assert o16.dtype == torch.bfloat16 and _rel(o16, ref) < 4e-3
+
+
+def test_int8_row_quantiser_and_linear():
+    from memarch_b200.ops import int8
+    C = _ext()
+    x = _mk((300, 272), seed=71)
+    q, s = C.quant_rows_i8(x)
+    qr, sr = int8.fq(x, 1)
+    assert torch.equal(q.float(), qr.float()) and torch.allclose(s, sr.squeeze(1), rtol=1e-6)
+    # linear through the int8 tensor cores against the floating-point statement of the same quantised product
+    w = _mk((520, 272), 0.1, seed=72)
+    y = int8.quant_mm(x, w, torch.float32)
+    qw, sw = int8.fq(w, 1)
+    ref = (qr.float() @ qw.float().t()) * sr * sw.t()
+    assert _rel(y, ref) < 1e-5
+    xg = x.clone().requires_grad_()
+    wg = w.clone().requires_grad_()
+    go = _mk((300, 520), seed=73)
+    int8.linear_i8(xg, wg).backward(go)
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    (xr @ wr.t()).backward(go.float())
+    assert _rel(xg.grad, xr.grad) < 3e-2 and _rel(wg.grad, wr.grad) < 2e-2          # int8 quantisation error
+    assert C.gemm_status(0) == 0
+
+
+@pytest.mark.parametrize("act", ["relu2", "swiglu"])
+def test_frozen_int8_bank_on_tensor_cores(act, monkeypatch):
+    """Bank layer with int8 storage: the tensor-core int8 forward against the dequantised bf16 path of the same
+    weights (difference = quantisation of the activations), input gradient included."""
+    from memarch_b200.models.moe import AnchorMoE
+    torch.manual_seed(0)
+    moe = AnchorMoE(256, E=4, k_avg=2, k_max=2, bank=True, act=act, w_dtype=torch.bfloat16, bank_q="int8").cuda()
+    moe.rebank([True, True, False, False])                       # experts 0, 1 move into the int8 bank
+    assert moe.up_f.dtype == torch.int8 and moe.up_f.shape[0] == 2
+    xe = (torch.randn(2, 300, 256, device="cuda") * 0.5).bfloat16()
+    go = torch.randn(2, 300, 256, device="cuda").bfloat16()
+    res = []
+    for on in ("1", "0"):
+        monkeypatch.setenv("MEMARCH_BANK_I8", on)
+        x = xe.clone().requires_grad_()
+        y = moe._ffn_frozen(x)
+        y.backward(go)
+        res.append((y.detach().float(), x.grad.float()))
+    assert _rel(res[0][0], res[1][0]) < 3e-2, _rel(res[0][0], res[1][0])
+    assert _rel(res[0][1], res[1][1]) < 3e-2, _rel(res[0][1], res[1][1])
+    assert not torch.equal(res[0][0], res[1][0])                 # the int8 path did run
+    assert _ext().gemm_status(0) == 0

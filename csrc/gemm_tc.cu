@@ -67,7 +67,16 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& g, 
   nt = rr / gsz;
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// x * sigmoid(x) with sigmoid = (tanh(x / 2) + 1) / 2: one special-function instruction and two FMAs, no division
+__device__ __forceinline__ float silu_f(float x) {
+  const float h = 0.5f * x;
+  return fmaf(h, tanh_approx(h), h);
+}
 
 // Drain one accumulator tile (this warp's 32 TMEM lanes x 256 columns) through the fused epilogue to global memory.
 // `row_l` = this thread's row inside M-segment `seg`; `taddr` = TMEM address of the warp's lanes, column 0 of the tile.
@@ -718,7 +727,9 @@ __device__ __forceinline__ void epilogue_tile3(const GemmParams& p, const CUtens
         for (int q = 0; q < 4; ++q) {
           const float2 gg = unpack_bf16(wg[q]), uv = unpack_bf16(wu[q]);
           const float d0 = __uint_as_float(r[8 * j + 2 * q]), d1 = __uint_as_float(r[8 * j + 2 * q + 1]);
-          const float s0 = 1.f / (1.f + __expf(-gg.x)), s1 = 1.f / (1.f + __expf(-gg.y));
+          // sigmoid through the hardware tanh (one special-function instruction, no division): with one epilogue
+          // warp per scheduler the dependent chain of exp + IEEE division per element was what bound this epilogue
+          const float s0 = fmaf(tanh_approx(0.5f * gg.x), 0.5f, 0.5f), s1 = fmaf(tanh_approx(0.5f * gg.y), 0.5f, 0.5f);
           og[q] = pack_bf16(d0 * uv.x * s0 * (1.f + gg.x * (1.f - s0)), d1 * uv.y * s1 * (1.f + gg.y * (1.f - s1)));
           ou[q] = pack_bf16(d0 * gg.x * s0, d1 * gg.y * s1);
         }
@@ -784,19 +795,22 @@ __device__ __forceinline__ int group_kblocks(const GemmParams& p, int g) {
 // shared-memory traffic, which on a power-capped part is clock) - 4 stages of 48 KB; the two 256-column accumulators
 // fill TMEM, so the epilogue is only half hidden (the MMAs of the next tile's first block start as soon as the
 // first half is drained): worth it when the contraction is long.
-template <int MH> struct PairCfg {
-  static constexpr int STAGES = MH == 2 ? 4 : 5;
-  static constexpr int NBUF = MH == 2 ? 2 : 4;
+// DEEP (256-row tiles only): one operand stage less and six staging tiles per epilogue warp instead of four, for the
+// SwiGLU-backward epilogue, which moves two tiles in and two out per 64 accumulator columns and needs three chunks of
+// pre-activations in flight per warp to keep HBM busy.
+template <int MH, bool DEEP = false> struct PairCfg {
+  static constexpr int STAGES = (MH == 2 || DEEP) ? 4 : 5;
+  static constexpr int NBUF = MH == 2 ? 2 : (DEEP ? 6 : 4);
   static constexpr int STAGE_BYTES = MH * A_BYTES + BH_BYTES;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 4 * NBUF * EPI_BUF_BYTES + 1024 + 256;
 };
 
-template <bool A_MN, bool B_MN, int MH>
+template <bool A_MN, bool B_MN, int MH, bool DEEP = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ TmapSet tmAs, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmO2,
                 const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
-  constexpr int STAGES3 = PairCfg<MH>::STAGES, EPI_NBUF = PairCfg<MH>::NBUF, STAGE_B = PairCfg<MH>::STAGE_BYTES;
+  constexpr int STAGES3 = PairCfg<MH, DEEP>::STAGES, EPI_NBUF = PairCfg<MH, DEEP>::NBUF, STAGE_B = PairCfg<MH, DEEP>::STAGE_BYTES;
   constexpr int TILE_M = 256 * MH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1160,7 +1174,8 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
   if (grid <= 0) return;
   const bool v3 = pair;
   TORCH_CHECK(v3 || p.count_mode == 0, "gemm: per-group extents need the pair kernel (>= 256 rows)");
-  const int smem_bytes = v3 ? (tall ? PairCfg<2>::SMEM : PairCfg<1>::SMEM) : SMEM_BYTES;
+  const bool deep = v3 && !tall && p.epi == EPI_DSWIGLU && !a_mn;
+  const int smem_bytes = v3 ? (tall ? PairCfg<2>::SMEM : deep ? PairCfg<1, true>::SMEM : PairCfg<1>::SMEM) : SMEM_BYTES;
   CUtensorMap tmO = tmB, tmO2 = tmB;
   if (v3) {
     p.dbg = g_dbg;
@@ -1189,7 +1204,8 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
     static const bool aux_off = []() { const char* e = std::getenv("MEMARCH_GEMM_AUX_TMA"); return e && e[0] == '0'; }();
     const int Nx = p.epi == EPI_DSWIGLU ? 2 * N : N;
     if (!aux_off && (p.ldaux * 2) % 16 == 0 && (G == 1 || (p.aux_gs * 2) % 16 == 0) && N % 8 == 0) {
-      tmX = make_tmap(p.aux, 2, Nx, (uint64_t)n_seg * seg_M, G, p.ldaux, p.aux_gs, 64, 32, false);
+      // 256-byte L2 promotion: a row's next 128-byte piece (the next chunk of the same tile) arrives with this one
+      tmX = make_tmap(p.aux, 2, Nx, (uint64_t)n_seg * seg_M, G, p.ldaux, p.aux_gs, 64, 32, true);
       p.aux_tma = 1;
     }
   }
@@ -1213,6 +1229,9 @@ void launch_gemm_seg(const void* const* A_list, int n_seg, int seg_M, int a_grou
     else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 2>, 12 + id);
     else if (a_mn && !b_mn) launch(gemm_pair_kernel<true, false, 2>, 12 + id);
     else launch(gemm_pair_kernel<true, true, 2>, 12 + id);
+  } else if (deep) {
+    if (!b_mn) launch(gemm_pair_kernel<false, false, 1, true>, 4);
+    else launch(gemm_pair_kernel<false, true, 1, true>, 5);
   } else if (v3) {
     if (!a_mn && !b_mn) launch(gemm_pair_kernel<false, false, 1>, 8 + id);
     else if (!a_mn && b_mn) launch(gemm_pair_kernel<false, true, 1>, 8 + id);

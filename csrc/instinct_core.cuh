@@ -385,7 +385,7 @@ __global__ void instinct_apply(InstinctArgs a, const float* __restrict__ rowsum,
 // loads in flight, then two barriers (1.7 TB/s for the row sums, 3.6 TB/s for the update on the expert shapes), and
 // a warp that loads a few chunks of its row into registers, then computes, does little better (2.6 / 4.4 TB/s): HBM
 // wants well over 100 KB in flight per SM all the time.  So here every thread keeps a ring of S chunks (8 elements of
-// each input array) in shared memory, filled by 16-byte cp.async copies issued S chunks ahead of the one it consumes;
+// each input array) in shared memory, filled by cp.async copies issued S chunks ahead of the one it consumes;
 // a warp owns a contiguous run of rows, so its stream is one linear span of memory, and the ring runs across row
 // boundaries.  One block per SM; C % 256 == 0 (a chunk of 32 lanes x 8 never straddles rows).
 __device__ __forceinline__ void cp_async16(void* s, const void* g) {
@@ -394,16 +394,27 @@ __device__ __forceinline__ void cp_async16(void* s, const void* g) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// A lane's 8 elements of a 256-element chunk are two groups of four, 128 elements apart: columns lane*4 .. +3 and
+// 128 + lane*4 .. +3.  Every warp-wide load or store then covers one contiguous span of full 32-byte sectors whatever
+// the element size (with 8 consecutive elements per lane an fp32 array needs two 16-byte accesses at a 32-byte lane
+// stride, each touching all sectors of the chunk and using half of each: the word tables with their fp32 gradients
+// ran at 1.8 TB/s).
+__device__ __forceinline__ void cp_async8(void* s, const void* g) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(s)), "l"(g) : "memory");
+}
 struct Ring8 {             // this thread's ring: slot (stage, q) is 16 bytes; slots of one (stage, q) are contiguous over threads
   uint4* base;
   int T, nslot;
   __device__ __forceinline__ uint4* slot(int stage, int q) const { return base + (stage * nslot + q) * T; }
+  // `i` = index of the lane's first element (chunk start + lane * 4)
   __device__ __forceinline__ void issue8(int stage, int q0, const void* arr, long long i, int is_bf16) const {
     if (is_bf16) {
-      cp_async16(slot(stage, q0), reinterpret_cast<const bf16*>(arr) + i);
+      uint8_t* d = reinterpret_cast<uint8_t*>(slot(stage, q0));
+      cp_async8(d, reinterpret_cast<const bf16*>(arr) + i);
+      cp_async8(d + 8, reinterpret_cast<const bf16*>(arr) + i + 128);
     } else {
       cp_async16(slot(stage, q0), reinterpret_cast<const float*>(arr) + i);
-      cp_async16(slot(stage, q0 + 1), reinterpret_cast<const float*>(arr) + i + 4);
+      cp_async16(slot(stage, q0 + 1), reinterpret_cast<const float*>(arr) + i + 128);
     }
   }
   __device__ __forceinline__ void read8(int stage, int q0, int is_bf16, float* o) const {
@@ -418,12 +429,14 @@ struct Ring8 {             // this thread's ring: slot (stage, q) is 16 bytes; s
     }
   }
 };
+// store the lane's two groups of four at dst + i and dst + i + 128
 __device__ __forceinline__ void st8_f32(float* dst, const float* v) {
-  reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
-  reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 128) = make_float4(v[4], v[5], v[6], v[7]);
 }
 __device__ __forceinline__ void st8_bf16(bf16* dst, const float* v) {
-  *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+  *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+  *reinterpret_cast<uint2*>(dst + 128) = make_uint2(pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
 }
 
 // rowsq / rowabs as instinct_stat_rows.  grid (blocks); dynamic shared memory: C floats when colsum is given, then
@@ -452,10 +465,17 @@ __global__ void __launch_bounds__(512) instinct_stat_rows_s8(InstinctArgs a, con
     const long long rpw = (seg_hi - seg + nw - 1) / nw;
     const long long r0 = min(seg_hi, seg + warp * rpw), r1 = min(seg_hi, r0 + rpw);
     const long long total = (r1 - r0) * cpr;
-    const long long el0 = r0 * a.C + lane * 8;
+    // both arrays bf16: 8 consecutive elements per lane are one full 16-byte copy each (faster than two 8-byte ones)
+    const bool packed = a.g_bf16 && a.m_bf16;
+    const long long el0 = r0 * a.C + lane * (packed ? 8 : 4);
     auto issue = [&](int stage, long long k) {
-      ring.issue8(stage, 0, a.g, el0 + (k << 8), a.g_bf16);
-      ring.issue8(stage, gs, a.m, el0 + (k << 8), a.m_bf16);
+      if (packed) {
+        cp_async16(ring.slot(stage, 0), reinterpret_cast<const bf16*>(a.g) + el0 + (k << 8));
+        cp_async16(ring.slot(stage, 1), reinterpret_cast<const bf16*>(a.m) + el0 + (k << 8));
+      } else {
+        ring.issue8(stage, 0, a.g, el0 + (k << 8), a.g_bf16);
+        ring.issue8(stage, gs, a.m, el0 + (k << 8), a.m_bf16);
+      }
     };
 #pragma unroll
     for (int s0 = 0; s0 < S; ++s0) {
@@ -472,11 +492,15 @@ __global__ void __launch_bounds__(512) instinct_stat_rows_s8(InstinctArgs a, con
       ring.read8(stage, gs, a.m_bf16, m);
       if (k + S < total) issue(stage, k + S);
       cp_async_commit();
-      const long long c = (cin << 8) + lane * 8;
+      const long long c = (cin << 8) + lane * (packed ? 8 : 4);
+      float ck[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+      if (cs) {
+        const float4 k0 = *reinterpret_cast<const float4*>(cs + c), k1 = *reinterpret_cast<const float4*>(cs + c + (packed ? 4 : 128));
+        ck[0] = k0.x; ck[1] = k0.y; ck[2] = k0.z; ck[3] = k0.w; ck[4] = k1.x; ck[5] = k1.y; ck[6] = k1.z; ck[7] = k1.w;
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float v = b * m[j] + b1 * g[j];
-        if (cs) v *= cs[c + j];
+        const float v = (b * m[j] + b1 * g[j]) * ck[j];
         ss += v * v;
         sa += fabsf(g[j]);
       }
@@ -535,7 +559,7 @@ __global__ void __launch_bounds__(384) instinct_apply_s8(InstinctArgs a, const f
     const long long rpw = (seg_hi - seg + nw - 1) / nw;
     const long long r0 = min(seg_hi, seg + warp * rpw), r1 = min(seg_hi, r0 + rpw);
     const long long total = (r1 - r0) * cpr;
-    const long long el0 = r0 * C + lane * 8;
+    const long long el0 = r0 * C + lane * 4;
     auto issue = [&](int stage, long long k) {
       ring.issue8(stage, 0, a.g, el0 + (k << 8), a.g_bf16);
       ring.issue8(stage, gs, a.m, el0 + (k << 8), a.m_bf16);
@@ -564,17 +588,22 @@ __global__ void __launch_bounds__(384) instinct_apply_s8(InstinctArgs a, const f
       ring.read8(stage, gs + ms, w_bf16, t);
       if (k + S < total) issue(stage, k + S);
       cp_async_commit();
-      const long long c = (cin << 8) + lane * 8;
+      const long long c = (cin << 8) + lane * 4;
       const long long i0 = el0 + (k << 8);
       float mf[8], upd[8];
+      float ck[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+      if (colk) {
+        const float4 k0 = *reinterpret_cast<const float4*>(colk + c), k1 = *reinterpret_cast<const float4*>(colk + c + 128);
+        ck[0] = k0.x; ck[1] = k0.y; ck[2] = k0.z; ck[3] = k0.w; ck[4] = k1.x; ck[5] = k1.y; ck[6] = k1.z; ck[7] = k1.w;
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         mf[j] = b * m[j] + b1 * g[j];
-        upd[j] = mf[j] * rs * (colk ? colk[c + j] : 1.f);
+        upd[j] = mf[j] * rs * ck[j];
       }
       if (a.sr) {                                         // per-element hashes: the 4-wide store path has them
         store_chunk<4>(a, i0, mf, t, upd, moves, step, decay, seed);
-        store_chunk<4>(a, i0 + 4, mf + 4, t + 4, upd + 4, moves, step, decay, seed);
+        store_chunk<4>(a, i0 + 128, mf + 4, t + 4, upd + 4, moves, step, decay, seed);
       } else {
         if (a.m_bf16) st8_bf16(reinterpret_cast<bf16*>(a.m) + i0, mf);
         else st8_f32(reinterpret_cast<float*>(a.m) + i0, mf);

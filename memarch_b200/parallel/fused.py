@@ -218,7 +218,13 @@ class FusedGradReduce:
 
     def __init__(self, heap, nvls=True):
         self.heap, self.W, self.rank = heap, heap.W, heap.rank
-        self.stream = torch.cuda.Stream()
+        # the per-weight chains (barrier, reduce, statistics, exchange, update, all-gather) are latency-bound, so
+        # several run side by side: weight i takes lane i % lanes = its own stream, barrier channel, statistics
+        # scratch and reduced-gradient buffer (the same assignment on every rank)
+        self.lanes = max(1, min(8, int(os.environ.get("MEMARCH_DP_LANES", 4))))
+        self.streams = [torch.cuda.Stream() for _ in range(self.lanes)]
+        self.stream = self.streams[0]
+        self.lane_of = {}
         self.nvls = nvls
         self.offsets = {}
         self.top = 0
@@ -269,9 +275,12 @@ class FusedGradReduce:
         except Exception:     # noqa: BLE001
             self.mc_wsh = 0
         need = max(3 * ((p.shape[0] // W + 3) // 4 * 4) + 2 * ((p.shape[1] + 3) // 4 * 4) + 4 for p in todo)
-        self.scr, self.scr_h = self.heap.alloc(((need + 63) // 64 * 64,), torch.float32)
-        self.scr_ptrs = [int(x) for x in self.scr_h.buffer_ptrs]
-        self.gred = torch.empty(max(p.numel() // W for p in todo), device=self.wsh.device, dtype=torch.bfloat16)
+        self.scr, self.scr_ptrs, self.gred = [], [], []
+        for _ in range(self.lanes):
+            t, h = self.heap.alloc(((need + 63) // 64 * 64,), torch.float32)
+            self.scr.append(t)
+            self.scr_ptrs.append([int(x) for x in h.buffer_ptrs])
+            self.gred.append(torch.empty(max(p.numel() // W for p in todo), device=self.wsh.device, dtype=torch.bfloat16))
         off = 0
         with torch.no_grad():
             for p in todo:
@@ -285,15 +294,15 @@ class FusedGradReduce:
                 off += (p.numel() * 2 + 255) // 256 * 256
         self.heap.barrier(0)
 
-    def _exchange(self, offset, count):
-        """Sum `count` floats at `offset` of the symmetric statistics scratch over the ranks, in place (every rank
+    def _exchange(self, offset, count, lane=0):
+        """Sum `count` floats at `offset` of a lane's symmetric statistics scratch over the ranks, in place (every rank
         reduces its own 1/W of the range from all peers and writes it back to all of them)."""
         if self.W == 1:
             return
-        self.heap.barrier(1)
-        _ext.C().peer_allreduce(self.scr_ptrs, self.scr_ptrs, 0, 0, offset, count, False, self.rank, 1.0)
+        self.heap.barrier(4 + lane)
+        _ext.C().peer_allreduce(self.scr_ptrs[lane], self.scr_ptrs[lane], 0, 0, offset, count, False, self.rank, 1.0)
         _ext.count()
-        self.heap.barrier(1)
+        self.heap.barrier(4 + lane)
 
     def materialize(self):
         """fp32 weights and momentum of the row-sharded weights are current only in the owner's rows; before anything
@@ -335,29 +344,32 @@ class FusedGradReduce:
         ev.record()
         C = _ext.C()
         heap = self.heap
+        lane = self.lane_of.setdefault(id(p), len(self.lane_of) % self.lanes)      # first-use order: backward's order, the same on every rank
+        stream = self.streams[lane]
         sh = self.sharded.get(id(p)) if grad.dtype == torch.bfloat16 else None
         if sh is not None:
             woff, rows = sh
             r0, r1 = self.rank * rows, (self.rank + 1) * rows
             cols = p.shape[1]
-            with torch.cuda.stream(self.stream):
-                self.stream.wait_event(ev)
-                heap.barrier(1)                                      # every rank has staged this weight's gradient
-                g_rows = self.gred[:rows * cols].view(rows, cols)
+            with torch.cuda.stream(stream):
+                stream.wait_event(ev)
+                heap.barrier(4 + lane)                               # every rank has staged this weight's gradient
+                g_rows = self.gred[lane][:rows * cols].view(rows, cols)
                 C.peer_reduce_to_local(self.in_ptrs, self.mc_in, g_rows, off // es + r0 * cols, 1.0 / self.W)
-                self.trainer.opt.update_sharded(p, g_rows, r0, r1, self.scr,
-                                                None if p.dtype == torch.bfloat16 else p._bf16_shadow[r0:r1], self._exchange)
+                self.trainer.opt.update_sharded(p, g_rows, r0, r1, self.scr[lane],
+                                                None if p.dtype == torch.bfloat16 else p._bf16_shadow[r0:r1],
+                                                lambda o_, n_, lane=lane: self._exchange(o_, n_, lane))
                 C.peer_broadcast_from_local(self.wsh_ptrs, self.mc_wsh, woff + r0 * cols * 2, rows * cols * 2, self.rank)
                 _ext.count(2)
             self.used = self.pushed = True
             return None
-        with torch.cuda.stream(self.stream):
-            self.stream.wait_event(ev)
-            heap.barrier(1)                                          # every rank has staged this weight's gradient
+        with torch.cuda.stream(stream):
+            stream.wait_event(ev)
+            heap.barrier(4 + lane)                                   # every rank has staged this weight's gradient
             C.peer_allreduce(self.in_ptrs, self.out_ptrs, self.mc_in, self.mc_out, off // es, n, grad.dtype == torch.bfloat16,
                              self.rank, 1.0 / self.W)
             _ext.count()
-            heap.barrier(1)                                          # every slice of the mean has landed here
+            heap.barrier(4 + lane)                                   # every slice of the mean has landed here
             red = self.gout[off:off + n * es].view(grad.dtype).view(grad.shape)
             self.trainer.opt.update(p, red, synced=True)
         self.used = True
@@ -375,7 +387,8 @@ class FusedGradReduce:
                 off += n
             self.small.clear()
         if self.used:
-            torch.cuda.current_stream().wait_stream(self.stream)
+            for st in self.streams:
+                torch.cuda.current_stream().wait_stream(st)
             self.used = False
         if getattr(self, "pushed", False):
             self.heap.barrier(0)             # every rank's rows of the updated shadows have landed before the next forward

@@ -12,7 +12,9 @@
                      the rewritten corpus (tools/phr/phrase_tok.py); `slice_report` - per-slice loss gap against a
                      rival model (tools/phr/diag_analyze.py).
   * `token_counts` - unigram counts.
-  * `prior_top`    - top-32 continuations per word (tools/phr/prior_top.py), `entropy` per word (ent.py).
+  * `prior_top`    - top-32 continuations per word from the pair forecaster; `tongue_tables` - the counted top
+                     continuations of words and pair contexts the model loads as `TONGUE` (tools/phr/prior_top.py);
+                     `entropy` per word (ent.py).
 `build_all(tokens, d, out_dir)` writes bigram.pt, trigram.pt, lock_trust.pt, token_counts.npy.
 """
 from __future__ import annotations
@@ -244,6 +246,42 @@ def prior_top(ph, k=32, phrase_c=0.05):
         idx.append(j)
         val.append(v)
     return torch.cat(idx), torch.cat(val)
+
+
+def _top_continuations(ctx, nxt, n_ctx, log_unigram, vocab, k_top):
+    """For every context row the `k_top` next words with the highest PMI (log of the conditional frequency minus the
+    log unigram probability), among (context, next) pairs seen at least twice; PMI below zero is stored as zero.
+    Returns (idx (n_ctx, k_top) int32, val (n_ctx, k_top) float16), empty places zero."""
+    pair, cnt = np.unique(ctx * vocab + nxt, return_counts=True)
+    row, word = pair // vocab, pair % vocab
+    per_row = np.bincount(row, weights=cnt, minlength=n_ctx)
+    pmi = np.where(cnt >= 2, np.log(cnt / per_row[row]) - log_unigram[word], -1e9)
+    by_score = np.argsort(-pmi, kind="stable")
+    order = by_score[np.argsort(row[by_score], kind="stable")]          # rows ascending, best PMI first inside a row
+    row, word, pmi = row[order], word[order], pmi[order]
+    place = np.arange(len(row)) - np.searchsorted(row, np.arange(n_ctx))[row]
+    keep = place < k_top
+    idx = np.zeros((n_ctx, k_top), dtype=np.int64)
+    val = np.zeros((n_ctx, k_top), dtype=np.float32)
+    idx[row[keep], place[keep]] = word[keep]
+    val[row[keep], place[keep]] = np.maximum(pmi[keep], 0)
+    return torch.tensor(idx, dtype=torch.int32), torch.tensor(val, dtype=torch.float16)
+
+
+def tongue_tables(a, keys, vocab=50257, k_top=32):
+    """"Words on the tip of the tongue": counted top continuations of every word and of every pair context of the
+    phrase table `keys`, with their PMI - the file the model loads as `TONGUE` and adds to its output logits
+    ({bi_idx, bi_val, tri_idx, tri_val, keys}; tools/phr/prior_top.py:3-32)."""
+    a = np.asarray(a, dtype=np.int64)
+    freq = np.bincount(a, minlength=vocab).astype(np.float64)
+    log_unigram = np.log((freq + 1) / freq.sum())
+    bi_idx, bi_val = _top_continuations(a[:-1], a[1:], vocab, log_unigram, vocab, k_top)
+    kk = np.asarray(keys, dtype=np.int64)
+    pair = a[:-2] * vocab + a[1:-1]
+    at = np.searchsorted(kk, pair).clip(max=len(kk) - 1)
+    known = kk[at] == pair
+    tri_idx, tri_val = _top_continuations(at[known], a[2:][known], len(kk), log_unigram, vocab, k_top)
+    return {"bi_idx": bi_idx, "bi_val": bi_val, "tri_idx": tri_idx, "tri_val": tri_val, "keys": torch.as_tensor(kk)}
 
 
 def build_all(tokens, d, out_dir, vocab=50257, phrase_k=262144, seed=0, quad_k=0, skip=False):

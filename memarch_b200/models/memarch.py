@@ -251,6 +251,49 @@ class MemArchLM(nn.Module):
                                torch.where(self.phr_hkey[s2] == ctx, self.phr_hval[s2], torch.full_like(ctx, K)))
         return ref.phrase_index(x, self.phr_keys, self.phr_V)
 
+    def _lock_votes(self, x, prep=None):
+        """Keys and locks: for each position the words that followed the last earlier occurrence of its 1-, 2- and
+        3-word endings (`cand`), and how strongly each of them votes for the next word: the lock's trust (per key
+        length and rarity bucket of the current word when a trust table is loaded, else one scalar per key length),
+        zero where the lock found nothing.  Returns (cand, votes, on, bucket).  (full2.py:1540-1559)"""
+        if prep and "ind_cand" in prep:
+            cand, on, bk = prep["ind_cand"], prep["ind_on"], prep["ind_bk"]
+        else:
+            cand, on, bk, _ = self._locks_raw(x)
+        n_keys = on.shape[-1]
+        if hasattr(self, "lock_w"):
+            # index_select: its backward is an index_add (atomics on 7 values), not the sort-based index_put of `w[bk]`
+            flat = bk.reshape(-1)
+            trust = torch.stack([self.lock_w[k].index_select(0, flat).view_as(bk) for k in range(n_keys)], -1)
+        else:
+            trust = self.ind_a[:n_keys]
+        return cand, on.float() * trust, on, bk
+
+    def _mix_gate(self, cand, on, bk):
+        """Pointer mixture: the candidate of the first lock that fired (longest key first) and the learned share of the
+        output distribution it takes, by key length and rarity bucket.  Returns (candidate (B,T), share (B,T))."""
+        fired = on.any(-1)
+        first = on.float().argmax(-1)
+        pick = (cand * on).sum(-1)
+        n_buckets = self.mix_w.shape[1]
+        share = torch.sigmoid(self.mix_w.reshape(-1).index_select(0, (first * n_buckets + bk).reshape(-1)).view_as(bk)) * fired
+        self.stats["mix_g"] = (share.sum() / fired.sum().clamp(min=1)).detach()
+        return pick, share
+
+    def _tongue_from_tables(self, x):
+        """"Tongue" bias from fixed tables instead of locks: the stored top continuations of the (previous, current)
+        pair where the pair is in the phrase table, else of the current word alone, scaled by the two learned
+        strengths `tg_a`.  Returns (candidates (B,T,k), bias values (B,T,k)).  (full2.py:1582-1591)"""
+        V0 = self.cfg.phr_v
+        word = x.clamp(max=V0 - 1)
+        pair = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1) * V0 + x
+        K = self.tg_keys.numel()
+        at = torch.searchsorted(self.tg_keys, pair).clamp(max=K - 1)
+        known = (self.tg_keys[at] == pair)[..., None]
+        cand = torch.where(known, self.tg_tri_idx[at], self.tg_bi_idx[word])
+        val = torch.where(known, self.tg_tri_val[at].float() * self.tg_a[1], self.tg_bi_val[word].float() * self.tg_a[0])
+        return cand, val
+
     def _phr4_idx(self, x):
         V = self.phr_V
         p1 = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1)
@@ -325,46 +368,21 @@ class MemArchLM(nn.Module):
         in_cand = in_sel = None
         self._tongue = self._mix = None
         if hasattr(self, "ind_a"):
-            if prep and "ind_cand" in prep:
-                cand, on, bk, src = prep["ind_cand"], prep["ind_on"], prep["ind_bk"], prep.get("ind_src")
-            else:
-                cand, on, bk, src = self._locks_raw(x)
-            if hasattr(self, "lock_w"):
-                # index_select: its backward is an index_add (atomics on 7 values), not the sort-based index_put of `w[bk]`
-                bkf = bk.reshape(-1)
-                val = torch.stack([on[..., k].float() * self.lock_w[k].index_select(0, bkf).view_as(bk)
-                                   for k in range(on.shape[-1])], -1)
-            else:
-                val = on.float() * self.ind_a[:on.shape[-1]]
-            self._tongue = (cand, val)
+            cand, votes, on, bk = self._lock_votes(x, prep)
+            self._tongue = (cand, votes)
             if hasattr(self, "mix_w"):
-                anyon = on.any(-1)
-                kk = on.float().argmax(-1)
-                c1 = (cand * on).sum(-1)
-                nb_ = self.mix_w.shape[1]
-                g = torch.sigmoid(self.mix_w.reshape(-1).index_select(0, (kk * nb_ + bk).reshape(-1)).view_as(bk)) * anyon
-                self._mix = (c1, g)
-                self.stats["mix_g"] = (g.sum() / anyon.sum().clamp(min=1)).detach()
-            tw = self.lock_w if hasattr(self, "lock_w") else self.ind_a
-            self.stats["trust"] = tw.detach().float().mean()
+                self._mix = self._mix_gate(cand, on, bk)
+            self.stats["trust"] = (self.lock_w if hasattr(self, "lock_w") else self.ind_a).detach().float().mean()
             if c.induct_in:
-                gi = torch.sigmoid(self.ind_in_g[:cand.shape[-1]])
+                # the words the locks point at also enter the input, each through its own learned gate
                 hd = torch.float32 if h is None else h.dtype
-                sel = (val != 0).to(hd) * gi[None, None].to(hd)
+                sel = (votes != 0).to(hd) * torch.sigmoid(self.ind_in_g[:cand.shape[-1]]).to(hd)[None, None]
                 if h is None:
                     in_cand, in_sel = cand, sel
                 else:
                     h = h + (self.emb(cand) * sel[..., None]).sum(2).type_as(h)
         if hasattr(self, "tg_a"):
-            V0 = c.phr_v
-            xc = x.clamp(max=V0 - 1)
-            ctx = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1) * V0 + x
-            K = self.tg_keys.numel()
-            pos = torch.searchsorted(self.tg_keys, ctx).clamp(max=K - 1)
-            hit = (self.tg_keys[pos] == ctx)[..., None]
-            cand = torch.where(hit, self.tg_tri_idx[pos], self.tg_bi_idx[xc])
-            val = torch.where(hit, self.tg_tri_val[pos].float() * self.tg_a[1], self.tg_bi_val[xc].float() * self.tg_a[0])
-            self._tongue = (cand, val)
+            self._tongue = self._tongue_from_tables(x)
         if h is None:
             pidx = (prep["phr"] if prep and "phr" in prep else self._phr_idx(x)) if hasattr(self, "phr") else None
             h = ops.embed_sum(self.emb.weight, x, in_cand, in_sel, self.phr.weight if pidx is not None else None, pidx)

@@ -192,3 +192,23 @@ def test_loss_curve_of_the_tiny_benchmark_configuration(tmp_path):
     assert abs(ours[0] - ref[0]) < 0.02
     assert ref[-1] < ref[0] - 0.3 and ours[-1] < ours[0] - 0.3
     assert max(abs(a - b) for a, b in zip(ours, ref)) < 0.01, list(zip(ours, ref))      # measured: 0.001
+
+
+def test_tongue_tables_model_matches_reference(tmp_path):
+    """The counted "tip of the tongue" tables built here, loaded by both code bases (TONGUE): same loss and gradients,
+    the two learned strengths included."""
+    from memarch_b200.build import build
+    from memarch_b200.data import phrasebook
+    env, toks = artefacts(tmp_path, 256, 512, 500, 2048)
+    keys = torch.load(tmp_path / "trigram.pt")["keys"]
+    tg = phrasebook.tongue_tables(toks, keys.numpy(), vocab=500, k_top=8)
+    assert tg["bi_idx"].shape == (500, 8) and tg["tri_idx"].shape == (len(keys), 8) and float(tg["bi_val"].float().max()) > 0
+    torch.save(tg, tmp_path / "tongue.pt")
+    for k in ("INDUCT", "LOCK_TRUST", "INDUCT_IN", "INDUCT_MIX"):
+        env.pop(k)
+    env.update({"TONGUE": str(tmp_path / "tongue.pt"), "NO_MEM": "1", "WAVE_WARM": "1000000"})
+    d = oracle(tmp_path, {"what": "model", "name": "Fv2moeKs8", "vocab": 512, "B": 2, "T": 128, "env": env})
+    m = build("Fv2moeKs8", 512, env=env)
+    assert hasattr(m, "tg_a")
+    compare(d, m, rtol=1e-3)
+    assert m.tg_a.grad is not None and m.tg_a.grad.abs().sum() > 0

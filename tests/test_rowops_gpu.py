@@ -444,3 +444,29 @@ def test_embed_sum_matches_torch(with_cand, with_phr):
 
     for a, b in zip(run(True), run(False)):
         assert _rel(a, b) < 1e-5, _rel(a, b)
+
+
+def test_momentum_host_offload_on_the_gpu():
+    """Momentum kept in pinned host memory and brought to the device only for its weight's update: the same weights as
+    the resident optimizer after three steps (the only difference allowed is the atomics' summation order, as in the
+    determinism test above), and the momentum really lives on the host between steps."""
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    outs = []
+    for off in (False, True):
+        torch.manual_seed(0)
+        ps = [torch.nn.Parameter(torch.randn(512, 1024, device="cuda").bfloat16()),
+              torch.nn.Parameter(torch.randn(4, 256, 512, device="cuda").bfloat16())]
+        opt = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, m_bf16=True, offload_m=off))
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for s in range(3):
+            opt.prepare(torch.tensor(3.0 - 0.1 * s, device="cuda"), torch.ones(8, device="cuda"))
+            for p in ps:
+                opt.update(p, (torch.randn(p.shape, device="cuda", generator=g) * 0.01).bfloat16())
+            opt.finish()
+        torch.cuda.synchronize()
+        if off:
+            assert all(t.device.type == "cpu" and t.is_pinned() for t in opt.m)
+        outs.append([p.detach().float().clone() for p in ps])
+    for a, b in zip(*outs):
+        assert (a - b).abs().max().item() <= 0.04 and (a != b).float().mean().item() < 1e-3

@@ -565,26 +565,40 @@ class MemArchLM(nn.Module):
         lo = self._logits(hn)
         return F.cross_entropy(lo.reshape(-1, lo.shape[-1]), y.reshape(-1), reduction="none")
 
-    def _short_logp(self, h, y):
-        """log P(y) of the two-level head (full2.py:1875-1898)."""
+    def _short_rows(self):
+        """Rows and biases of the first level: the `short_v` frequent words followed by one "rare" bucket row (a word of
+        the vocabulary lends its output vector; its bias is the log share of rare words, or zero with a trained bias)."""
         W, b = self.head.weight, getattr(self, "head_bias", None)
-        K, N = self.short_v, h.shape[0]
-        Ws = torch.cat([W[self.sv_ids], W[self.sv_bucket:self.sv_bucket + 1]])
-        bs = (torch.cat([b[self.sv_ids].float(), h.new_full((1,), self.sv_prior1, dtype=torch.float32)]) if b is not None
-              else torch.cat([h.new_zeros(K, dtype=torch.float32), h.new_full((1,), self.sv_prior0, dtype=torch.float32)]))
-        ys = self.sv_pos[y]
-        ch = self.cfg.ce_chunk or 16768
-        lse_s, ly_s = ops.chunk_ce(h, Ws, bs, ys, min(ch, K + 1))
-        logp = ly_s - lse_s
-        rare = ys == K
-        C = min(N, -(-int(round(self.rare_cap * N)) // 256) * 256)
-        key = rare.float() * 2 - torch.arange(N, device=h.device, dtype=torch.float32) / N
-        idx = key.detach().topk(C).indices
-        hit = rare[idx]
-        br = (b.float() if b is not None else W.new_zeros(W.shape[0], dtype=torch.float32)) + self.sv_mask
-        lse_r, ly_r = ops.chunk_ce(h[idx], W, br, y[idx], ch)
-        logp = logp.index_add(0, idx, torch.where(hit, ly_r - lse_r, torch.zeros_like(ly_r)))
-        self.stats["rare_drop"] = (rare.sum() - hit.sum()).float() / N
+        rows = torch.cat([W[self.sv_ids], W[self.sv_bucket:self.sv_bucket + 1]])
+        if b is not None:
+            bias = torch.cat([b[self.sv_ids].float(), b.new_full((1,), self.sv_prior1, dtype=torch.float32)])
+        else:
+            bias = torch.cat([W.new_zeros(self.short_v, dtype=torch.float32), W.new_full((1,), self.sv_prior0, dtype=torch.float32)])
+        return rows, bias
+
+    def _short_logp(self, h, y):
+        """log P(y) of the two-level head: every position pays the small softmax over frequent words + the rare bucket;
+        positions whose target is rare add the log-probability inside the bucket, computed over the full vocabulary
+        with the frequent words masked out - but only for the first `rare_cap` share of positions (static shape), the
+        rest of the rare targets keep the bucket's probability alone and are counted in `rare_drop`.
+        (full2.py:1875-1898)"""
+        N, K = h.shape[0], self.short_v
+        chunk = self.cfg.ce_chunk or 16768
+        rows, bias = self._short_rows()
+        level1 = self.sv_pos[y]                                      # index among the frequent words, K = rare
+        lse1, hit1 = ops.chunk_ce(h, rows, bias, level1, min(chunk, K + 1))
+        logp = hit1 - lse1
+        rare = level1 == K
+        # the rare positions first (in text order), padded with frequent ones up to the static capacity
+        cap = min(N, -(-int(round(self.rare_cap * N)) // 256) * 256)
+        rank = rare.float() * 2 - torch.arange(N, device=h.device, dtype=torch.float32) / N
+        take = rank.detach().topk(cap).indices
+        served = rare[take]
+        b = getattr(self, "head_bias", None)
+        inside = (b.float() if b is not None else self.head.weight.new_zeros(self.head.weight.shape[0], dtype=torch.float32)) + self.sv_mask
+        lse2, hit2 = ops.chunk_ce(h[take], self.head.weight, inside, y[take], chunk)
+        logp = logp.index_add(0, take, torch.where(served, hit2 - lse2, torch.zeros_like(hit2)))
+        self.stats["rare_drop"] = (rare.sum() - served.sum()).float() / N
         return logp
 
     @torch.no_grad()

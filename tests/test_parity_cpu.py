@@ -212,3 +212,19 @@ def test_tongue_tables_model_matches_reference(tmp_path):
     assert hasattr(m, "tg_a")
     compare(d, m, rtol=1e-3)
     assert m.tg_a.grad is not None and m.tg_a.grad.abs().sum() > 0
+
+
+def test_short_vocabulary_head_matches_reference(tmp_path):
+    """Two-level output head (SHORT_V): frequent words + a "rare" bucket first, the full vocabulary only for a capped
+    share of rare targets - loss and gradients against the reference."""
+    from memarch_b200.build import build
+    from memarch_b200.data.synth import MarkovCorpus
+    from memarch_b200.data import phrasebook
+    toks = MarkovCorpus(vocab=500, n_succ=8, seed=0).stream(60_000, text_len=256, seed=1)
+    np.save(tmp_path / "token_counts.npy", phrasebook.token_counts(toks, 512))
+    env = {"SHORT_V": "64", "TOKEN_COUNTS": str(tmp_path / "token_counts.npy"), "NO_MEM": "1", "VOCAB": "512",
+           "WAVE_WARM": "1000000"}
+    d = oracle(tmp_path, {"what": "model", "name": "Fv2moeKs8", "vocab": 512, "B": 2, "T": 128, "env": env})
+    m = build("Fv2moeKs8", 512, env=env)
+    assert m.short_v == 64
+    compare(d, m, rtol=1e-3)

@@ -175,12 +175,43 @@ class TransformerLM(nn.Module):
         self.head = nn.Linear(d, vocab, bias=False)
         self.stats = {}
 
+    def vocab_shard(self, rank, world, group=None):
+        """Vocabulary parallelism: keep rows [rank V/W, (rank+1) V/W) of the input table and of the output head.  Every
+        rank then serves its rows for the tokens of all ranks (`parallel/vocab.py`: ids and states are gathered, the
+        cross-entropy is a two-stage log-sum-exp), so a 131k-word vocabulary costs each GPU 1/W of both tables, of
+        their optimizer state and of the head's FLOPs.  The shards are rank-local parameters: their gradient already
+        holds the contribution of every rank's tokens, W times the scale of a rank-mean gradient (see `train_loss`), and
+        is divided by W in a hook."""
+        from ..parallel import vocab as vp
+        assert self.vocab % world == 0, "vocabulary rows must divide by the world size"
+        self._vp = (rank, world, group, rank * (self.vocab // world))
+        for mod in (self.emb, self.head):
+            shard = nn.Parameter(vp.shard_rows(mod.weight.detach(), rank, world)[0])
+            shard._ep_local = True                       # no data-parallel averaging: see above
+            shard.register_hook(lambda g, w=world: g / w)
+            mod.weight = shard
+        return self
+
     def forward(self, x, prep=None):
-        h = self.emb(x)
+        vpar = getattr(self, "_vp", None)
+        if vpar is not None:
+            from ..parallel import vocab as vp
+            h = vp.take_dp(self.emb.weight, x, vpar[3], vpar[2])
+        else:
+            h = self.emb(x)
         h = run_blocks(self.blocks, h, None)
         return ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=_cdt(h)), torch.zeros((), device=x.device)
 
     def train_loss(self, out, y, train=True):
+        vpar = getattr(self, "_vp", None)
+        if vpar is not None:
+            # S = summed loss of ALL ranks' tokens (the same number on every rank); this rank's backward reaches the
+            # replicated weights only through its own tokens.  Gradient of S / (own token count): its mean over the
+            # ranks is the gradient of the mean loss per token, which is what data-parallel averaging assumes.
+            # Value: the mean loss per token of the whole batch.
+            from ..parallel import vocab as vp
+            per_own = vp.ce_dp(out.reshape(-1, out.shape[-1]).float(), self.head.weight.float(), y.reshape(-1), vpar[3], vpar[2]) / y.numel()
+            return per_own.detach() / vpar[1] + (per_own - per_own.detach())
         if self.fused_ce and self.training:
             return ops.linear_ce(out, self.head.weight, y) / y.numel()
         lo = ops.linear(out, self.head.weight).float()

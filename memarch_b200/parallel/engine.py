@@ -15,6 +15,8 @@ Two modes share this interface:
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -205,6 +207,8 @@ class ParallelEngine:
         for mod in model.modules():
             if isinstance(mod, AnchorMoE):
                 mod.ep_shard(self.rank, self.W, self.fused_impl.ep if self.fused_impl else self.ep)
+        if self.W > 1 and os.environ.get("MEMARCH_VP") == "1" and hasattr(model, "vocab_shard"):
+            model.vocab_shard(self.rank, self.W, self.group)      # row-sharded word tables (large vocabularies)
         def bcast(t):
             if t.is_contiguous():
                 dist.broadcast(t, 0, group=self.group)

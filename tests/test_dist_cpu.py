@@ -286,3 +286,53 @@ def test_deduplicated_expert_exchange_matches_the_plain_one():
         e_plain, e_dedup, y_plain, y_dedup = r["bank_err"]
         assert np.abs(y_plain - y_dedup).max() < 2e-5 * max(1.0, np.abs(y_plain).max())
         assert e_plain.max() > 0 and np.abs(e_plain - e_dedup).max() < 1e-5 * e_plain.max() + 1e-9
+
+
+def _w_vp_model(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.models.blocks import TransformerLM
+    torch.manual_seed(0)
+    V, d, T = 64, 32, 12
+    full = TransformerLM(V, d=d, layers=2, heads=2, fused_ce=False)
+    torch.manual_seed(0)
+    vpm = TransformerLM(V, d=d, layers=2, heads=2, fused_ce=False).vocab_shard(rank, world)
+    g = torch.Generator().manual_seed(7)
+    xy_all = torch.randint(0, V, (2 * world, T + 1), generator=g)          # the whole batch, rank r owns rows 2r, 2r+1
+    mine = xy_all[2 * rank:2 * rank + 2]
+    full.train(); vpm.train()
+    out, _ = vpm(mine[:, :-1])
+    loss = vpm.train_loss(out, mine[:, 1:])
+    loss.backward()
+    out_f, _ = full(xy_all[:, :-1])
+    loss_f = full.train_loss(out_f, xy_all[:, 1:])
+    loss_f.backward()
+    res = {"loss": (float(loss), float(loss_f))}
+    # replicated weights: the rank mean of the local gradients is the gradient of the whole-batch mean loss
+    gq = vpm.blocks[0].qkv.weight.grad.clone()
+    dist.all_reduce(gq)
+    res["qkv"] = float((gq / world - full.blocks[0].qkv.weight.grad).abs().max() / full.blocks[0].qkv.weight.grad.abs().max())
+    lo, hi = rank * V // world, (rank + 1) * V // world
+    for nm, a, b in (("emb", vpm.emb.weight.grad, full.emb.weight.grad[lo:hi]), ("head", vpm.head.weight.grad, full.head.weight.grad[lo:hi])):
+        res[nm] = float((a - b).abs().max() / b.abs().max().clamp(min=1e-9))
+    res["rows"] = (tuple(vpm.emb.weight.shape), tuple(vpm.head.weight.shape))
+    q.put((rank, res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_transformer_matches_the_unsharded_one():
+    """TransformerLM with its word tables row-sharded over 2 ranks, each rank on its own rows of the batch: loss and
+    gradients equal those of the unsharded model on the whole batch (replicated weights after the data-parallel mean,
+    table shards after their 1/W hook)."""
+    world, port = 2, 29655
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_vp_model, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = [q.get(timeout=180) for _ in ps]
+    [p.join(30) for p in ps]
+    for _, r in res:
+        assert r["rows"] == ((32, 32), (32, 32))
+        assert abs(r["loss"][0] - r["loss"][1]) < 1e-5
+        assert r["qkv"] < 1e-4 and r["emb"] < 1e-4 and r["head"] < 1e-4, r

@@ -424,22 +424,33 @@ class Instinct:
         `shadow_rows` the rows of the bf16 copy the GEMMs read (None for a bf16 weight: it is its own), `exchange(offset, count)` sums `scratch[offset:
         offset + count]` over the ranks (device-side, on the current stream).  Momentum and the fp32 weight are touched
         in these rows only: every other row of `p` and of the momentum is another rank's to keep."""
-        C = _ext.C()
+        region = self.shard_stats(p, g_rows, r0, r1, scratch, shadow_rows)
+        exchange(*region)                                       # column sums (and the |g|, |w| sums behind them)
+        self.shard_apply(p, g_rows, r0, r1, scratch, shadow_rows)
+
+    def _shard_call(self, p, g_rows, r0, r1, scratch, shadow_rows, phase):
         i = self.idx[id(p)]
         self._sync_lr()
-        kind, wd, _ = self.spec(p)
+        _, wd, _ = self.spec(p)
         want_rel = self.n_step % self.rel_every == 0
         wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
-        R, Cn = r1 - r0, p.shape[1]
         pr, mr = p[r0:r1], self.m[i][r0:r1]
         wr = self.w[i][r0:r1] if self.w[i] is not None else None
-        args = (wr, None, self.g, int(i), self.stake, self._lr_t, self.rel if want_rel else None, float(self.beta),
-                float(wd_v), _kind_code("hs"), False, self._seed_t, None, scratch, None, shadow_rows)
-        n = C.instinct_step(pr, g_rows, mr, *args, 1, int(p.shape[0]))
+        n = _ext.C().instinct_step(pr, g_rows, mr, wr, None, self.g, int(i), self.stake, self._lr_t,
+                                   self.rel if want_rel else None, float(self.beta), float(wd_v), _kind_code("hs"), False,
+                                   self._seed_t, None, scratch, None, shadow_rows, phase, int(p.shape[0]))
+        _ext.count(int(n))
+
+    def shard_stats(self, p, g_rows, r0, r1, scratch, shadow_rows=None):
+        """First half of `update_sharded`: the statistics of rows [r0, r1) into `scratch`.  Returns (offset, count) of
+        the part of `scratch` that must be summed over the ranks before `shard_apply`."""
+        self._shard_call(p, g_rows, r0, r1, scratch, shadow_rows, 1)
         pad4 = lambda v: (v + 3) // 4 * 4
-        exchange(3 * pad4(R), 2 * pad4(Cn) + 4)                 # column sums (and the |g|, |w| sums behind them)
-        n += C.instinct_step(pr, g_rows, mr, *args, 2, int(p.shape[0]))
-        _ext.count(int(n) + 1)
+        return 3 * pad4(r1 - r0), 2 * pad4(p.shape[1]) + 4
+
+    def shard_apply(self, p, g_rows, r0, r1, scratch, shadow_rows=None):
+        """Second half: the update of rows [r0, r1) from the summed statistics."""
+        self._shard_call(p, g_rows, r0, r1, scratch, shadow_rows, 2)
 
     def _update_rows(self, i, p, grad, rows, lr_t):
         """Word / phrase tables: only rows used in this step move (exp_opt.py:306-318)."""

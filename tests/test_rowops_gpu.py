@@ -470,3 +470,43 @@ def test_momentum_host_offload_on_the_gpu():
         outs.append([p.detach().float().clone() for p in ps])
     for a, b in zip(*outs):
         assert (a - b).abs().max().item() <= 0.04 and (a != b).float().mean().item() < 1e-3
+
+
+def test_row_sharded_update_of_two_virtual_ranks_matches_the_whole_weight():
+    """The row-sharded optimizer step with the two ranks played one after the other on this GPU: statistics of each
+    half into its own scratch, the column sums (and the norm sums behind them) added across the two scratches as the
+    cross-rank exchange does, then the update of each half - against the plain step of the whole weight."""
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    R, Cn, W = 512, 1024, 2
+    torch.manual_seed(0)
+    w0 = (torch.randn(R, Cn, device="cuda") * 0.05).bfloat16()
+    grads = [(torch.randn(R, Cn, device="cuda") * 0.01).bfloat16() for _ in range(3)]
+    outs = []
+    for sharded in (False, True):
+        p = torch.nn.Parameter(w0.clone())
+        opt = Instinct([p], OptConfig(lr=1e-2, norm="hs", scale=0.12, m_bf16=True, rel_every=1))
+        rows = R // W
+        need = 3 * rows + 2 * Cn + 4
+        scr = [torch.zeros(need, device="cuda") for _ in range(W)]
+        for s, g in enumerate(grads):
+            opt.prepare(torch.tensor(3.0 - 0.1 * s, device="cuda"), torch.ones(8, device="cuda"))
+            if not sharded:
+                opt.update(p, g)
+            else:
+                parts = [g[r * rows:(r + 1) * rows].contiguous() for r in range(W)]
+                regions = [opt.shard_stats(p, parts[r], r * rows, (r + 1) * rows, scr[r]) for r in range(W)]
+                off, cnt = regions[0]
+                total = sum(t[off:off + cnt] for t in scr)
+                for t in scr:
+                    t[off:off + cnt] = total
+                for r in range(W):
+                    opt.shard_apply(p, parts[r], r * rows, (r + 1) * rows, scr[r])
+            opt.finish()
+        torch.cuda.synchronize()
+        outs.append((p.detach().float().clone(), opt.m[0].float().clone(), opt.w[0].clone(), opt.rel.clone()))
+    (pa, ma, wa, ra), (pb, mb_, wb, rb) = outs
+    assert (wa - wb).abs().max() <= 2e-5 * wa.abs().max(), float((wa - wb).abs().max())      # fp32 masters
+    assert (pa - pb).abs().max() <= 0.004 and (pa != pb).float().mean() < 1e-3
+    assert (ma - mb_).abs().max() <= 1e-4
+    assert torch.allclose(ra, rb, rtol=1e-4)

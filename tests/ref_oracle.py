@@ -50,13 +50,18 @@ def main():
                                steps=spec["total_steps"])
         tr = fastloop.Trainer(spec["name"], spec.get("stage", "ABX"), a)
         sd = {k: v.clone() for k, v in tr.model.state_dict().items()}
+        if spec.get("wave_every"):                        # shorter wave period so that a few steps exercise the waves
+            for b in tr.model.heavy:
+                b.wave_every = int(spec["wave_every"])
         data = fastloop.GPUData(np.load(spec["tokens"]), seed=1)
         batches, losses = [], []
         for s_ in range(spec["steps"]):
             xy = data.batch(spec["B"], spec["T"])
             batches.append(xy.clone())
             losses.append(float(tr.step(xy, s_)))
-        torch.save({"sd": sd, "batches": batches, "losses": losses}, out)
+        waves = {k: v.clone() for k, v in tr.model.state_dict().items()
+                 if k.split(".")[-1] in ("learned", "err", "err_peak", "err_freeze", "move_peak", "last_move")}
+        torch.save({"sd": sd, "batches": batches, "losses": losses, "waves": waves}, out)
     elif spec["what"] == "instinct":
         import exp_opt
         torch.manual_seed(3)

@@ -228,3 +228,38 @@ def test_short_vocabulary_head_matches_reference(tmp_path):
     m = build("Fv2moeKs8", 512, env=env)
     assert m.short_v == 64
     compare(d, m, rtol=1e-3)
+
+
+def test_wave_bookkeeping_follows_the_reference(tmp_path):
+    """Bank MoE with the "stopped changing" wave switched on early (warm-up 2 steps, a wave every 3) over a 16-step run
+    whose learning rate decays to a tenth, so the experts' movement falls below its peak share and they get marked as
+    learned: from the reference's weights on the reference's batches every layer ends with the same `learned` experts
+    and the same error / movement statistics."""
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.config import opt_from_env
+    from memarch_b200.train import Trainer
+    env, toks = artefacts(tmp_path, 256, 2048, 2000, 4096)
+    np.save(tmp_path / "tokens.npy", toks.astype(np.int32))
+    okw = {"norm": "hs", "scale": 0.12, "rel_every": 4}
+    env.update({"NO_MEM": "1", "WAVE_WARM": "2", "WARMUP": "2", "OPT_KW": json.dumps(okw)})
+    steps = 16
+    d = oracle(tmp_path, {"what": "train", "name": "Fv2moeKs8", "B": 4, "T": 128, "lr": 3e-3, "steps": steps,
+                          "total_steps": steps, "tokens": str(tmp_path / "tokens.npy"), "env": env, "wave_every": 3})
+    m = build("Fv2moeKs8", 2048, env=env)
+    m.load_state_dict(d["sd"])
+    for b in m.heavy:
+        b.wave_every = 3
+    tr = Trainer(m, TrainConfig(name="waves", stage="ABX", steps=steps, batch=4, micro=4, seq=128, lr=3e-3, warmup=2),
+                 opt_from_env(OptConfig(lr=3e-3), env), stage="ABX")
+    ours = [float(tr.step(xy, s)) for s, xy in enumerate(d["batches"])]
+    assert max(abs(a - b) for a, b in zip(ours, d["losses"])) < 0.03, list(zip(ours, d["losses"]))
+    sd = m.state_dict()
+    moved = 0
+    for k, v in d["waves"].items():
+        w = sd[k]
+        if v.dtype == torch.bool:
+            assert torch.equal(w, v), (k, w, v)
+            moved += int(v.sum())
+        else:
+            assert torch.allclose(w.float(), v.float(), rtol=0.15, atol=1e-6), (k, w, v)      # the reference runs bf16 autocast
+    assert moved > 0, "no expert was marked as learned: the test did not exercise the waves"

@@ -4,6 +4,7 @@
     python -m memarch_b200.utils.kernel_bench ce --rows 8192 --d 2064 --vocab 50304
     python -m memarch_b200.utils.kernel_bench instinct --kind hs3 --shape 8,2048,6144
     python -m memarch_b200.utils.kernel_bench experts --e 8 --c 2049 --d 2048 --h 6144
+    python -m memarch_b200.utils.kernel_bench reread --rows 256 --words 128 --cards 320
 
 Each command checks the kernel against the PyTorch fp32 statement on the same inputs, then times it with CUDA events
 after warm-up (inputs larger than L2, or an L2 flush between iterations) and prints achieved TFLOP/s or GB/s next to
@@ -137,6 +138,45 @@ def cmd_instinct(a):
     per = (2 if a.bf16 else 4) * 2 + 2 * 2 + (8 if a.bf16 else 0)       # minimal traffic: g, p r/w, m r/w, master r/w
     report(f"instinct step kind={kind}{' lagged' if a.lag else ''} shape={shape}", timeit(lambda: opt.update(p, g), a.iters), nbytes=float(n) * per,
            extra=f"(algorithmic {per} B/weight, one pass)")
+
+
+def cmd_reread(a):
+    """Re-reading kernels on the shapes of a memory model's step: rows = texts x segments, S words each, C cards."""
+    import math
+    from memarch_b200.models.reread import Reread
+    from memarch_b200.ops import _ext
+    torch.manual_seed(0)
+    B, S, Cn, d, T = a.rows, a.words, a.cards, a.d, a.text
+    mod = Reread(d).cuda()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rn = lambda *s_: torch.randn(*s_, device="cuda", generator=g)
+    h, faces, contents = rn(B, S, d).requires_grad_(), rn(B, Cn, 2, 64), rn(B, Cn, d)
+    valid = torch.rand(B, Cn, device="cuda", generator=g) > 0.2
+    pos = torch.randint(0, T, (B, Cn), device="cuda", generator=g)
+    qpos = torch.randint(0, T, (B, S), device="cuda", generator=g)
+    n_texts = max(1, B // 8)
+    rows = torch.randint(0, n_texts, (B,), device="cuda", generator=g)
+    ids = torch.randint(0, 50000, (n_texts, T), device="cuda", generator=g)
+    table = (rn(50304, 128) * 0.5).requires_grad_()
+
+    def step():
+        o, cost = mod(h, ids, table, faces, contents, pos, valid, qpos, rows)
+        (o.sum() + cost).backward()
+        h.grad = table.grad = None
+
+    use = _ext.use_cuda
+    step()
+    o1, c1 = mod(h, ids, table, faces, contents, pos, valid, qpos, rows)
+    _ext.use_cuda = lambda t: False
+    try:
+        o0, c0 = mod(h[:8], ids, table, faces[:8], contents[:8], pos[:8], valid[:8], qpos[:8], rows[:8])
+        t_torch = timeit(step, max(2, a.iters // 3), flush=False)
+    finally:
+        _ext.use_cuda = use
+    o1s, _ = mod(h[:8], ids, table, faces[:8], contents[:8], pos[:8], valid[:8], qpos[:8], rows[:8])
+    print(f"parity (8 rows) output rel err {rel(o1s, o0):.2e}")
+    t_k = timeit(step, a.iters, flush=False)
+    print(f"re-reading forward + backward, {B * S} words x {Cn} cards: kernels {t_k:.3f} ms, PyTorch statement {t_torch:.3f} ms", flush=True)
 
 
 def cmd_experts(a):
@@ -308,6 +348,10 @@ def main(argv=None):
     i = sub.add_parser("instinct")
     i.add_argument("--shape", default="8,2048,6144"); i.add_argument("--bf16", action="store_true", default=True)
     i.add_argument("--fp32", dest="bf16", action="store_false"); i.add_argument("--lag", action="store_true")
+    r = sub.add_parser("reread")
+    r.add_argument("--rows", type=int, default=256); r.add_argument("--words", type=int, default=128)
+    r.add_argument("--cards", type=int, default=320); r.add_argument("--d", type=int, default=1024)
+    r.add_argument("--text", type=int, default=1024)
     e = sub.add_parser("experts")
     e.add_argument("--e", type=int, default=8); e.add_argument("--c", type=int, default=2049)
     e.add_argument("--d", type=int, default=2048); e.add_argument("--h", type=int, default=6144)
@@ -318,11 +362,12 @@ def main(argv=None):
     w = sub.add_parser("sweep")
     w.add_argument("--shapes", default=""); w.add_argument("--variants", default="0", help="dbg[:group_m],...")
     w.add_argument("--seconds", type=float, default=0.6)
-    for p in (g, c, i, e, w):
+    for p in (g, c, i, e, w, r):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
-    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "attn": cmd_attn, "sweep": cmd_sweep}[a.cmd](a)
+    {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "attn": cmd_attn, "sweep": cmd_sweep,
+     "reread": cmd_reread}[a.cmd](a)
 
 
 if __name__ == "__main__":

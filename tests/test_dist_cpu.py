@@ -336,3 +336,59 @@ def test_vocab_parallel_transformer_matches_the_unsharded_one():
         assert r["rows"] == ((32, 32), (32, 32))
         assert abs(r["loss"][0] - r["loss"][1]) < 1e-5
         assert r["qkv"] < 1e-4 and r["emb"] < 1e-4 and r["head"] < 1e-4, r
+
+
+def _w_ckpt(rank, world, port, folder, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.parallel import ParallelEngine
+    from memarch_b200.train import Trainer
+    from memarch_b200.train.ckpt import Checkpointer
+
+    def make(seed):
+        torch.manual_seed(seed)
+        m = build("tiny", 512)
+        eng = ParallelEngine(rank, world, 0, fused=False)
+        return m, Trainer(m, TrainConfig(batch=4, micro=4, seq=64, lr=1e-3, warmup=2, steps=10),
+                          OptConfig(norm="hs", scale=0.12, rel_every=1), stage="ABX", parallel=eng)
+
+    g = torch.Generator().manual_seed(11 + rank)                          # every rank its own data
+    xs = [torch.randint(0, 512, (4, 65), generator=g) for _ in range(6)]
+    m, tr = make(0)
+    for s in range(3):
+        tr.step(xs[s], s)
+    ck = Checkpointer(folder, rid="run", rank=rank, world=world)
+    ck.save(tr, 3, log=[{"step": 3}], corpus_state={"rank": rank})
+    ck.wait()
+    dist.barrier()
+    want = [float(tr.step(xs[s], s)) for s in range(3, 6)]
+    mine = {k: v.detach().clone() for k, v in m.state_dict().items() if k.endswith((".up", ".down"))}
+    m2, tr2 = make(5)                                                       # another init: everything comes from the files
+    nxt, log = Checkpointer(folder, rid="run", rank=rank, world=world).load(tr2)
+    got = [float(tr2.step(xs[s], s)) for s in range(3, 6)]
+    same_experts = all(torch.equal(v, m2.state_dict()[k]) for k, v in mine.items())
+    files = sorted(os.listdir(folder))
+    q.put((rank, nxt, log, want, got, same_experts, files, {k: tuple(v.shape) for k, v in mine.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_checkpoint_resumes_every_rank_from_its_own_file(tmp_path):
+    """Expert-parallel run on 2 gloo ranks: each rank saves its own experts, optimizer state and data position to its
+    own file, rank 0 adds the manifest; two freshly initialised ranks resume from those files and continue with the
+    same losses and the same expert weights as the uninterrupted run."""
+    world, port = 2, 29667
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_ckpt, args=(r, world, port, str(tmp_path), q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted([q.get(timeout=300) for _ in ps], key=lambda t: t[0])
+    [p.join(60) for p in ps]
+    for rank, nxt, log, want, got, same_experts, files, shapes in res:
+        assert nxt == 4 and log == [{"step": 3}]
+        assert got == want, (rank, want, got)
+        assert same_experts
+        assert {"latest.json", "latest.rank0of2.pt", "latest.rank1of2.pt"} <= set(files), files
+        assert all(s[0] * world == 4 or s[0] * world == 8 for s in shapes.values()), shapes     # half of the experts each

@@ -542,3 +542,38 @@ def test_err_step_and_gearbox_pace_the_step():
     assert f[14] < f[11] and int(opt.gear[0]) < 3                 # three surges: geared down, slowing
     sd = opt.state_dict()
     assert "gear" in sd and "speed" in sd
+
+
+def test_training_loop_raises_when_a_device_wait_has_run_out(monkeypatch):
+    """The loop reads the kernels' status words wherever it synchronises with the host anyway; a non-zero word (a
+    bounded device wait gave up) must stop the run with an exception, not pass as silently wrong weights.  The device
+    is faked: a status reader that returns a code, and an engine whose check raises as `SymmetricHeap.check` does."""
+    import types
+    import torch
+    from memarch_b200.ops import _ext
+    from memarch_b200.train import loop
+
+    class FakeC:
+        def __init__(self, st):
+            self.st = st
+
+        def gemm_status(self, dev):
+            return self.st
+
+    class Engine:
+        def check(self):
+            raise RuntimeError("peer wait timed out (status 5): a rank did not reach the barrier within 4000.0 ms")
+
+    tr = types.SimpleNamespace(device=torch.device("cuda", 0), parallel=None)
+    monkeypatch.setattr(_ext, "available", lambda: True)
+    monkeypatch.setattr(_ext, "C", lambda: FakeC(0))
+    loop.device_status(tr)                                        # clean words: nothing happens
+    monkeypatch.setattr(_ext, "C", lambda: FakeC(3))
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        loop.device_status(tr)
+    monkeypatch.setattr(_ext, "C", lambda: FakeC(0))
+    tr.parallel = Engine()
+    with pytest.raises(RuntimeError, match="peer wait timed out"):
+        loop.device_status(tr)
+    tr_cpu = types.SimpleNamespace(device=torch.device("cpu"), parallel=Engine())
+    loop.device_status(tr_cpu)                                    # CPU runs have no status words

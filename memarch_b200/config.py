@@ -66,6 +66,7 @@ class ModelConfig:
     students: int = 5
     err_thr: float = 0.3
     moe_cap_align: int = 0        # MOE_CAP_ALIGN
+    moe_dropless: bool = False    # MOE_GMM: no token is dropped (a place for every anchor in every expert; padding costs no GEMM work)
     moe_group: int = 512
     heavy_attn: bool = False
     heavy_attn_detach: bool = False
@@ -220,9 +221,11 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("BANK_Q"): kw["bank_q"] = g("BANK_Q")
     if g("WAVE_WARM"): kw["wave_warm"] = int(g("WAVE_WARM"))
     if g("MOE_CAP_ALIGN"): kw["moe_cap_align"] = int(g("MOE_CAP_ALIGN"))
-    # MOE_GMM / MOE_DISP / MOE_GATHER choose among the reference's dispatch forms; this build has one form (slot
-    # table + inverse gather) and its grouped GEMMs always skip the padding rows of an expert (per-expert fill
-    # counts), which is what the reference's dropless MOE_GMM path buys - the switches are accepted and ignored
+    # MOE_DISP / MOE_GATHER choose among the reference's dispatch forms; this build has one form (slot table + inverse
+    # gather): accepted and ignored.  MOE_GMM (the reference's dropless grouped-GEMM path, full2.py:1048-1100) turns on
+    # `moe_dropless`: every expert gets a place for every anchor, so nothing is dropped, and the grouped GEMMs skip the
+    # unfilled places through the per-expert fill counts
+    if g("MOE_GMM") == "1": kw["moe_dropless"] = True
     if g("MOE_GROUP"): kw["moe_group"] = int(g("MOE_GROUP"))
     if g("HEAVY_ATTN"): kw["heavy_attn"] = True
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True

@@ -105,7 +105,7 @@ class MemArchLM(nn.Module):
                           budget=c.moe == "budget", wave=c.wave, wave_every=c.wave_every, students=c.students,
                           hint_w=c.hint_w, frozen=c.n_frozen, bank=c.bank, act=c.moe_act if c.bank else "swiglu",
                           w_dtype=w_dtype if c.bank else torch.float32, bank_q=c.bank_q, wave_warm=c.wave_warm,
-                          err_thr=c.err_thr, cap_align=c.moe_cap_align)
+                          err_thr=c.err_thr, cap_align=c.moe_cap_align, dropless=c.moe_dropless)
                 for _ in range(c.heavy))
         else:
             self.heavy = nn.ModuleList(DenseFFN(d) for _ in range(c.heavy))

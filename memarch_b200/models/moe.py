@@ -102,8 +102,9 @@ class _FrozenBankI8(torch.autograd.Function):
 class AnchorMoE(nn.Module):
     def __init__(self, d, E=8, k_avg=2, k_max=4, budget=True, wave="", wave_every=50, students=5, hint_w=1.0,
                  frozen=0, bank=False, act="swiglu", w_dtype=torch.float32, bank_q="", wave_warm=500,
-                 err_thr=0.3, cap_align=0, local_experts=None):
+                 err_thr=0.3, cap_align=0, local_experts=None, dropless=False):
         super().__init__()
+        self.dropless = dropless
         self.E, self.k_avg, self.k_max, self.budget = E, k_avg, k_max, budget
         self.bank, self.act, self.bank_q, self.cap_align = bank, act, bank_q, cap_align
         self.fill = 1.0
@@ -154,6 +155,10 @@ class AnchorMoE(nn.Module):
 
     # ------------------------------------------------------------------------------------------ routing
     def capacity(self, N):
+        if self.dropless:
+            # a token picks an expert at most once, so N places per expert hold everything; the places past an
+            # expert's fill count are padding that the grouped GEMMs neither load nor multiply
+            return -(-N // 8) * 8
         cf = 1.6 if self.budget else 1.25
         C = int(cf * self.fill * N * self.k_avg / self.E) + 1
         if self.cap_align:

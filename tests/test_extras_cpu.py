@@ -477,3 +477,32 @@ def test_three_word_table_skip_tables_and_phrase_units(tmp_path):
     assert len(rep) == 4
     for rows in rep.values():
         assert abs(sum(r[5] for r in rows) - 1.0) < 1e-9 and abs(sum(r[1] for r in rows) - 1.0) < 1e-9
+
+
+def test_dropless_moe_keeps_every_token():
+    """MOE_GMM: with a place for every anchor in every expert nothing is dropped and the layer equals the capacity
+    form at a capacity large enough to hold everything; the default capacity does drop on a skewed router."""
+    from memarch_b200.models.moe import AnchorMoE
+    torch.manual_seed(0)
+    kw = dict(E=4, k_avg=2, k_max=4, budget=False, act="relu2")
+    a, b = AnchorMoE(32, dropless=True, **kw), AnchorMoE(32, **kw)
+    b.load_state_dict(a.state_dict())
+    with torch.no_grad():                                     # a skewed router: most tokens want expert 0
+        a.router.weight[0] += 2.0
+        b.router.weight[0] += 2.0
+    a.train(); b.train()
+    x = torch.randn(2, 40, 32) + 0.5                           # positive mean: the raised router row wins almost everywhere
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya = a(xa)
+    assert a.capacity(80) == 80 and float(a.dropped) == 0.0
+    yb = b(xb)
+    assert float(b.dropped) > 0                                # the capacity form loses tokens here
+    b.fill = 10.0                                              # room for everything
+    yb = b(xb)
+    assert float(b.dropped) == 0.0
+    assert torch.allclose(ya, yb, atol=1e-5)
+    go = torch.randn_like(ya)
+    ya.backward(go); yb.backward(go)
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-5) and torch.allclose(a.up.grad, b.up.grad, atol=1e-5)
+    from memarch_b200.config import model_from_env, ModelConfig
+    assert model_from_env(ModelConfig(vocab=64), {"MOE_GMM": "1"}).moe_dropless

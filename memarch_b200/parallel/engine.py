@@ -41,6 +41,49 @@ class _AllToAll(torch.autograd.Function):
         return torch.ops._c10d_functional.wait_tensor(t), None
 
 
+# ---- split all-to-all: start now, wait where the data is needed.  K-chunk pipelining of the expert exchange (the
+# reference's JAX port, moe.py:263-287: the exchange of chunk k+1 runs under the expert FFN of chunk k) is built from
+# these two halves; in backward the halves swap roles, so the gradient exchange of a chunk overlaps the FFN backward
+# of its neighbour the same way.
+_IN_FLIGHT = {}          # data_ptr of the receive buffer -> (work handle, send buffer kept alive)
+
+
+def _a2a_begin(x, group):
+    src = x.contiguous()
+    out = torch.empty_like(src)
+    _IN_FLIGHT[out.data_ptr()] = (dist.all_to_all_single(out, src, group=group, async_op=True), src)
+    return out
+
+
+def _a2a_end(t):
+    pending = _IN_FLIGHT.pop(t.data_ptr(), None)
+    if pending is not None:
+        pending[0].wait()
+    return t
+
+
+class _ExchangeStart(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _a2a_begin(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_end(g), None
+
+
+class _ExchangeWait(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, t, group):
+        ctx.group = group
+        return _a2a_end(t).view_as(t)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_begin(g, ctx.group), None
+
+
 def ring_exchange(x, group=None):
     """The same permutation as the equal-split all-to-all over dim 0, as W-1 point-to-point steps: in step s every
     rank sends its block for rank (r+s) and receives the block of rank (r-s).  The reference's JAX port keeps such a
@@ -84,6 +127,7 @@ class NcclExpertExchange:
         self.ring = os.environ.get("MEMARCH_EP_A2A", "a2a") == "ring"
         self.dedup = os.environ.get("EP_A2A_DEDUP") == "1"
         self.dedup_cap = float(os.environ.get("EP_DEDUP_CAP", 1.0))
+        self.chunks = max(1, int(os.environ.get("MEMARCH_EP_CHUNKS", 1)))      # K-chunk pipelined exchange (all-to-all form)
 
     def _move(self, x, gname):
         return _Ring.apply(x, self.group) if self.ring else _AllToAll.apply(x, gname)
@@ -161,13 +205,25 @@ class NcclExpertExchange:
         if perm is not None:
             xe = xe[perm]
         n = El + Fl
-        r = self._move(xe, gname)
-        r = r.view(W, n, C, d).transpose(0, 1).reshape(n, W * C, d)
-        y = moe._ffn(r[:El], moe.up, moe.down)
-        if Fl:
-            y = torch.cat([y, moe._ffn_frozen(r[El:])])
-        y = y.view(n, W, C, d).transpose(0, 1).reshape(E, C, d).contiguous()
-        y = self._move(y, gname)
+
+        def experts(r, c):
+            """Rows received from every rank (W*n, c, d) -> outputs in the layout of the way back."""
+            r = r.view(W, n, c, d).transpose(0, 1).reshape(n, W * c, d)
+            y = moe._ffn(r[:El], moe.up, moe.down)
+            if Fl:
+                y = torch.cat([y, moe._ffn_frozen(r[El:])])
+            return y.view(n, W, c, d).transpose(0, 1).reshape(E, c, d).contiguous()
+
+        K = min(self.chunks, C)
+        if K > 1 and not self.ring:
+            # the places of every expert in K slices: all dispatches start at once, a slice's FFN runs as soon as its
+            # rows are here, its outputs start their way back while the next slice is computed
+            cuts = [C * k // K for k in range(K + 1)]
+            there = [_ExchangeStart.apply(xe[:, a:b], self.group) for a, b in zip(cuts, cuts[1:])]
+            back = [_ExchangeStart.apply(experts(_ExchangeWait.apply(t, self.group), t.shape[1]), self.group) for t in there]
+            y = torch.cat([_ExchangeWait.apply(t, self.group) for t in back], 1)
+        else:
+            y = self._move(experts(self._move(xe, gname), C), gname)
         if perm is not None:
             inv = torch.empty_like(perm)
             inv[perm] = torch.arange(E, device=perm.device)

@@ -392,3 +392,50 @@ def test_two_rank_checkpoint_resumes_every_rank_from_its_own_file(tmp_path):
         assert same_experts
         assert {"latest.json", "latest.rank0of2.pt", "latest.rank1of2.pt"} <= set(files), files
         assert all(s[0] * world == 4 or s[0] * world == 8 for s in shapes.values()), shapes     # half of the experts each
+
+
+def _w_chunks(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.models.moe import AnchorMoE
+    from memarch_b200.parallel.engine import NcclExpertExchange
+    torch.manual_seed(0)
+    moe = AnchorMoE(32, E=4, k_avg=2, k_max=4, budget=True, act="relu2")
+    eng = NcclExpertExchange(rank, world)
+    moe.ep_shard(rank, world, eng)
+    moe.train()
+    g = torch.Generator().manual_seed(3 + rank)
+    x0 = torch.randn(2, 24, 32, generator=g)
+    sur = torch.rand(2, 24, generator=g) * 4
+    go = torch.randn(2, 24, 32, generator=g)
+    res = {}
+    s_mean = moe.s_mean.clone()
+    for K in (1, 2, 3):
+        eng.chunks = K
+        moe.s_mean.copy_(s_mean)
+        x = x0.clone().requires_grad_(True)
+        moe.up.grad = moe.down.grad = moe.router.weight.grad = None
+        y = moe(x, sur)
+        y.backward(go)
+        res[K] = [t.detach().clone().numpy() for t in (y, x.grad, moe.up.grad, moe.down.grad, moe.router.weight.grad)]
+    from memarch_b200.parallel import engine
+    q.put((rank, res, len(engine._IN_FLIGHT)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_chunked_expert_exchange_equals_the_single_exchange():
+    """K-chunk pipelined expert exchange (exchange of slice k+1 in flight under the FFN of slice k, forward and
+    backward): outputs and every gradient equal the one-exchange form for K = 2 and 3; nothing is left in flight."""
+    world, port = 2, 29671
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_chunks, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = [q.get(timeout=180) for _ in ps]
+    [p.join(30) for p in ps]
+    for _, r, left in res:
+        assert left == 0
+        for K in (2, 3):
+            for a, b in zip(r[1], r[K]):
+                assert np.abs(a - b).max() < 1e-6 * max(1.0, np.abs(a).max()), K

@@ -263,3 +263,34 @@ def test_wave_bookkeeping_follows_the_reference(tmp_path):
         else:
             assert torch.allclose(w.float(), v.float(), rtol=0.15, atol=1e-6), (k, w, v)      # the reference runs bf16 autocast
     assert moved > 0, "no expert was marked as learned: the test did not exercise the waves"
+
+
+def test_three_word_and_draft_ahead_tables_match_reference(tmp_path):
+    """The PHRASE4 and SKIP artefacts built here, loaded by both code bases: same loss and gradients (the tables feed
+    the input of the model)."""
+    from memarch_b200.build import build
+    from memarch_b200.data import phrasebook
+    env, toks = artefacts(tmp_path, 256, 512, 500, 2048)
+    ph = torch.load(tmp_path / "bigram.pt")
+    torch.save(phrasebook.context_table(toks, ph["head"], 1024, 3, 500), tmp_path / "quad.pt")
+    torch.save(phrasebook.skip_table(toks, ph["head"], vocab=500), tmp_path / "skip.pt")
+    env.update({"PHRASE4": str(tmp_path / "quad.pt"), "SKIP": str(tmp_path / "skip.pt"), "NO_MEM": "1", "WAVE_WARM": "1000000"})
+    d = oracle(tmp_path, {"what": "model", "name": "Fv2moeKs8", "vocab": 512, "B": 2, "T": 128, "env": env})
+    m = build("Fv2moeKs8", 512, env=env)
+    assert hasattr(m, "phr4") and hasattr(m, "skip")
+    compare(d, m, rtol=1e-3)
+
+
+def test_dropless_moe_matches_the_reference_grouped_path(tmp_path):
+    """MOE_GMM=1: the reference's dropless grouped-matmul dispatch against this build's dropless capacity form - same
+    loss and gradients (nothing is dropped in either)."""
+    from memarch_b200.build import build
+    env = {"NO_MEM": "1", "WAVE_WARM": "1000000", "MOE_GMM": "1", "VOCAB": "512"}
+    try:
+        d = oracle(tmp_path, {"what": "model", "name": "Fv2moeKs8", "vocab": 512, "B": 2, "T": 128, "env": env})
+    except AssertionError as e:                                  # the reference's grouped matmul may not exist on this CPU build
+        pytest.skip("the reference's MOE_GMM path does not run here: " + str(e)[-200:])
+    m = build("Fv2moeKs8", 512, env=env)
+    assert m.heavy[0].dropless
+    compare(d, m, rtol=1e-3)
+    assert float(m.stats["moe_drop"]) == 0.0

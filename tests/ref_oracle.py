@@ -29,6 +29,11 @@ def main():
         m = lm.build(spec["name"], spec["vocab"])
         m.train()
         sd = {k: v.clone() for k, v in m.state_dict().items()}
+        if spec.get("freeze"):                            # move these experts of every bank layer into the frozen bank
+            for b in m.heavy:
+                b.learned.zero_()
+                b.learned[spec["freeze"]] = True
+            m.rebank(1000)
         g = torch.Generator().manual_seed(1)
         xy = torch.randint(0, spec["vocab"], (spec["B"], spec["T"] + 1), generator=g)
         outp, cost = m(xy[:, :-1])

@@ -294,3 +294,41 @@ def test_dropless_moe_matches_the_reference_grouped_path(tmp_path):
     assert m.heavy[0].dropless
     compare(d, m, rtol=1e-3)
     assert float(m.stats["moe_drop"]) == 0.0
+
+
+@pytest.mark.parametrize("bank_q", ["", "int8", "int4"])
+def test_frozen_bank_after_rebank_matches_reference(tmp_path, bank_q):
+    """Experts 1, 4 and 6 of every bank layer move into the frozen bank (bf16, int8 or int4 storage) by the models' own
+    `rebank`; the layer then runs learners and bank side by side: loss and gradients against the reference, the
+    learners' weights keeping their gradients and the bank none."""
+    from memarch_b200.build import build
+    env = {"NO_MEM": "1", "WAVE_WARM": "1000000", "VOCAB": "512", "MOE_ACT": "relu2"}
+    if bank_q:
+        env["BANK_Q"] = bank_q
+    freeze = [1, 4, 6]
+    d = oracle(tmp_path, {"what": "model", "name": "Fv2moeKs8", "vocab": 512, "B": 2, "T": 128, "env": env, "freeze": freeze})
+    m = build("Fv2moeKs8", 512, env=env)
+    m.load_state_dict(d["sd"])
+    for b in m.heavy:
+        b.learned.zero_()
+        b.learned[freeze] = True
+    assert len(m.rebank(1000)) == 2 * len(m.heavy)               # (up, down) of every layer changed hands
+    assert m.heavy[0].Fz == freeze and m.heavy[0].up.shape[0] == 5
+    if bank_q:
+        assert m.heavy[0].up_f.dtype == torch.int8
+    m.train()
+    xy = d["xy"]
+    out, cost = m(xy[:, :-1])
+    loss = m.train_loss(out, xy[:, 1:], True)
+    assert abs(loss.item() - d["loss"].item()) < 2e-5 * max(1, abs(d["loss"].item())), (loss.item(), d["loss"].item())
+    (loss + 0.01 * cost.float()).backward()
+    checked = 0
+    for n, p in m.named_parameters():
+        g = d["grads"].get(n)
+        assert (g is None) == (p.grad is None), n
+        if g is not None and g.float().abs().max() > 1e-7:
+            assert g.shape == p.grad.shape, n
+            # the bank's bf16 weights (and bf16 scale arithmetic of the quantised forms) leave differences of bf16 size
+            assert (p.grad.float() - g.float()).abs().max() <= 5e-3 * g.float().abs().max(), n
+            checked += 1
+    assert checked > 20

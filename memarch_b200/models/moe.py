@@ -205,31 +205,35 @@ class AnchorMoE(nn.Module):
         return ops.expert_ffn(xe, up.to(xe.dtype) if up.dtype != xe.dtype else up,
                               down.to(xe.dtype) if down.dtype != xe.dtype else down, self.act, train_w, counts)
 
+    # ------------------------------------------------------------------------------------------ frozen bank storage
+    # Stored form of a frozen table (F, in, out): bf16 as is; int8 with one scale per output column; int4 with one
+    # scale per output column and block of 128 inputs, two values per byte (even input in the low nibble).
+    # (full2.py:919-958)
     def _bank_weights(self, which):
-        """Frozen weights in bf16 (expanded from int8 / int4 storage) (full2.py:948-958)."""
-        q = getattr(self, which + "_f")
+        """The frozen `up` / `down` table expanded to bf16."""
+        stored, scale = getattr(self, which + "_f"), getattr(self, which + "_fs")
         if not self.bank_q:
-            return q
-        sc = getattr(self, which + "_fs")
-        if self.bank_q == "int4":
-            Fn, K2, N = q.shape
-            q = torch.stack([(q << 4) >> 4, q >> 4], 2).reshape(Fn, K2 * 2 // 128, 128, N)
-            return (q.to(torch.bfloat16) * sc[:, :, None]).reshape(Fn, K2 * 2, N)
-        return q.to(torch.bfloat16) * sc
+            return stored
+        if self.bank_q == "int8":
+            return stored.to(torch.bfloat16) * scale
+        n_f, half, n_out = stored.shape
+        low, high = (stored << 4) >> 4, stored >> 4                       # sign-extending nibble extraction
+        vals = torch.stack([low, high], 2).reshape(n_f, 2 * half // 128, 128, n_out)
+        return (vals.to(torch.bfloat16) * scale[:, :, None]).reshape(n_f, 2 * half, n_out)
 
     def _quantise(self, w):
-        """float (F, in, out) -> (stored, per-output-column scale) (full2.py:919-932)."""
+        """float (F, in, out) -> (stored table, scales) in the layout above."""
         if not self.bank_q:
             return w.bfloat16().contiguous(), w.new_zeros(w.shape[0], 1, w.shape[2]).bfloat16()
         if self.bank_q == "int8":
-            sc = (w.abs().amax(1, keepdim=True) / 127).clamp(min=1e-8)
-            return (w / sc).round().clamp(-127, 127).to(torch.int8).contiguous(), sc.bfloat16()
-        Fn, K, N = w.shape
-        wg = w.view(Fn, K // 128, 128, N)
-        sc = (wg.abs().amax(2, keepdim=True) / 7).clamp(min=1e-8)
-        q = (wg / sc).round().clamp(-7, 7).to(torch.int8).view(Fn, K, N)
-        q = ((q[:, 0::2] & 0x0F) | (q[:, 1::2] << 4)).to(torch.int8)
-        return q.contiguous(), sc[:, :, 0].bfloat16().contiguous()
+            scale = (w.abs().amax(1, keepdim=True) / 127).clamp(min=1e-8)
+            return (w / scale).round().clamp(-127, 127).to(torch.int8).contiguous(), scale.bfloat16()
+        n_f, n_in, n_out = w.shape
+        blocks = w.view(n_f, n_in // 128, 128, n_out)
+        scale = (blocks.abs().amax(2, keepdim=True) / 7).clamp(min=1e-8)
+        vals = (blocks / scale).round().clamp(-7, 7).to(torch.int8).view(n_f, n_in, n_out)
+        packed = ((vals[:, 0::2] & 0x0F) | (vals[:, 1::2] << 4)).to(torch.int8)
+        return packed.contiguous(), scale[:, :, 0].bfloat16().contiguous()
 
     def _bank_i8(self):
         """The int8 bank in the layout the int8 GEMM reads (contraction contiguous): (F, out, in) copies of the stored
@@ -343,39 +347,51 @@ class AnchorMoE(nn.Module):
         self.err_freeze.copy_(torch.where(newly, self.err, self.err_freeze))
         self.learned.copy_((self.learned | newly) & ~relearn)
 
+    def _moves(self, learned_cpu):
+        """(experts that leave the learning bank, experts that come back from the frozen one) for a `learned` mask."""
+        return [e for e in self.L if learned_cpu[e]], [e for e in self.Fz if not learned_cpu[e]]
+
     @torch.no_grad()
     def wants_rebank(self, learned_cpu):
-        to_freeze = [e for e in self.L if learned_cpu[e]]
-        to_thaw = [e for e in self.Fz if not learned_cpu[e]]
-        return bool(to_thaw) or len(to_freeze) >= max(1, self.E // 4) or (bool(to_freeze) and len(to_freeze) == len(self.L))
+        """Moving experts costs a re-layout of both tables: do it when anyone must thaw, when at least a quarter of the
+        experts is ready to freeze, or when all remaining learners are."""
+        freeze, thaw = self._moves(learned_cpu)
+        return bool(thaw) or len(freeze) >= max(1, self.E // 4) or (bool(freeze) and len(freeze) == len(self.L))
+
+    def _whole_table(self, which):
+        """All E experts of `up` / `down` in fp32, learners and (expanded) frozen ones at their expert index."""
+        live = getattr(self, which)
+        table = torch.empty(self.E, *live.shape[1:], device=live.device, dtype=torch.float32)
+        if self.L:
+            table[self.L_idx] = live.detach().float()
+        if self.Fz:
+            table[self.F_idx] = self._bank_weights(which).float()
+        return table
 
     @torch.no_grad()
     def rebank(self, learned_cpu):
         """Move experts between the learning and the frozen bank.  Returns [(old param, new param, slot map)] so
         the optimizer can carry momentum of the experts that keep learning (full2.py:1206-1242)."""
-        to_freeze = {e for e in self.L if learned_cpu[e]}
-        to_thaw = {e for e in self.Fz if not learned_cpu[e]}
-        newL = sorted((set(self.L) - to_freeze) | to_thaw)
-        newF = sorted((set(self.Fz) - to_thaw) | to_freeze)
+        freeze, thaw = self._moves(learned_cpu)
+        learners = sorted((set(self.L) - set(freeze)) | set(thaw))
+        bank = sorted((set(self.Fz) - set(thaw)) | set(freeze))
+        came_from = [self.L.index(e) if e in self.L else None for e in learners]      # old row of every new learner
+        dev = self.up.device
         changes = []
-        for nm in ("up", "down"):
-            old = getattr(self, nm)
-            full = torch.empty(self.E, *old.shape[1:], device=old.device, dtype=torch.float32)
-            if self.L:
-                full[torch.tensor(self.L, device=old.device)] = old.detach().float()
-            if self.Fz:
-                full[torch.tensor(self.Fz, device=old.device)] = self._bank_weights(nm).float()
-            sel = torch.tensor(newL, device=old.device, dtype=torch.long)
-            new = nn.Parameter((full[sel] if newL else full[:0]).to(self.w_dtype).contiguous())
-            setattr(self, nm, new)
-            if newF:
-                q, sc = self._quantise(full[torch.tensor(newF, device=old.device, dtype=torch.long)])
+        for which in ("up", "down"):
+            old = getattr(self, which)
+            table = self._whole_table(which)
+            rows = table[torch.tensor(learners, device=dev, dtype=torch.long)] if learners else table[:0]
+            new = nn.Parameter(rows.to(self.w_dtype).contiguous())
+            setattr(self, which, new)
+            if bank:
+                stored, scale = self._quantise(table[torch.tensor(bank, device=dev, dtype=torch.long)])
             else:
-                q, sc = getattr(self, nm + "_f")[:0], getattr(self, nm + "_fs")[:0]
-            setattr(self, nm + "_f", q)
-            setattr(self, nm + "_fs", sc)
-            changes.append((old, new, [self.L.index(e) if e in self.L else None for e in newL]))
-        self.set_banks(newL, newF)
+                stored, scale = getattr(self, which + "_f")[:0], getattr(self, which + "_fs")[:0]
+            setattr(self, which + "_f", stored)
+            setattr(self, which + "_fs", scale)
+            changes.append((old, new, came_from))
+        self.set_banks(learners, bank)
         return changes
 
     def set_banks(self, L, Fz):

@@ -142,6 +142,10 @@ class OptConfig:
     damp_p: float = 1.0           #     into the momentum and the tensor's step shrinks by (damp x usual / |g|)^damp_p
     damp_beta: float = 0.99       #     EMA of the usual squared norm (per situation card)
     damp_cap: float = 2.0         #     a surge enters that EMA as at most (cap x usual)^2: the brake does not get used to it
+    gnorm: bool = False           # every weight's gradient is divided by its own rms before it enters the momentum
+    wd_norm: float = 0.0          # >0: decoupled weight decay towards zero for the 1-D norm weights (norm, l_norm, *.n1, *.n2)
+    norm_anchor: bool = False     # 1-D norm weights of the light / final blocks are pulled towards 1: w -= lr wd (w - 1)
+    lr_mul: tuple = ()            # ((name prefix, multiplier), ...): step multiplier of the weights under a prefix
     err_step: bool = False        # with damp > 0: every tensor's step x clip(usual |g| / |g| now, 0, err_cap) ("divide by
     err_cap: float = 3.0          #     the sensitivity"); the gradient enters the momentum unclipped
     gearbox: bool = False         # with damp > 0: per-tensor gears (0.25, 0.5, 1, gb_top) shifted one at a time - down when

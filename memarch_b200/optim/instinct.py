@@ -31,7 +31,7 @@ def _kind_code(kind):
 
 
 class Instinct:
-    def __init__(self, params, cfg: OptConfig = None, d_sit=None, **kw):
+    def __init__(self, params, cfg: OptConfig = None, d_sit=None, names=None, **kw):
         cfg = cfg or OptConfig()
         if kw:
             import dataclasses
@@ -41,6 +41,12 @@ class Instinct:
         self.rel_every, self.n_step = cfg.rel_every, 0
         self.plist = list(params)
         self.idx = {id(p): i for i, p in enumerate(self.plist)}
+        # parameter names (optional): the switches that address weights by name need them (wd_norm, norm_anchor, lr_mul)
+        self.names = list(names) if names is not None else [""] * len(self.plist)
+        is_norm = lambda n: n in ("norm.weight", "l_norm.weight") or n.endswith((".n1.weight", ".n2.weight"))
+        self._norm_w = [p.dim() == 1 and is_norm(n) for p, n in zip(self.plist, self.names)]
+        self._anchor = [nw and n.startswith(("light_a.", "light_b.", "final.")) for nw, n in zip(self._norm_w, self.names)]
+        self._mul = [next((float(m) for pref, m in cfg.lr_mul if n.startswith(pref)), 1.0) for n in self.names]
         self.param_groups = [dict(lr=cfg.lr, weight_decay=cfg.weight_decay)]
         self.K, self.beta, self.new_card, self.ema = cfg.cards, cfg.beta, cfg.new_card, cfg.ema
         self.good, self.bad, self.top, self.relax = cfg.good, cfg.bad, cfg.top, cfg.relax
@@ -202,6 +208,11 @@ class Instinct:
         if self.cfg.surge_thr > 0:                       # surprise brake (device scalars only)
             bad = (-self.s).clamp(min=self.cfg.surge_thr)
             lr_t = lr_t * (self.cfg.surge_thr / bad) ** 2
+        if self.cfg.gnorm:                               # a step with a large gradient does not drown the small ones in the momentum
+            g32 = grad.float()
+            grad = (g32 * torch.rsqrt(g32.pow(2).mean() + 1e-30)).to(grad.dtype if grad.dtype == torch.float32 else torch.float32)
+        if self._mul[i] != 1.0:
+            lr_t = lr_t * self._mul[i]
         if self.dv is not None and (self.cfg.gearbox or self.cfg.err_step):
             lr_t = self._pace(i, grad, lr_t)
         elif self.dv is not None and not vocab:
@@ -209,6 +220,10 @@ class Instinct:
         if self.snr_v is not None and not vocab and self.m[i].shape == grad.shape:
             lr_t = self._snr(i, grad, lr_t)
         wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
+        if not wd and self.cfg.wd_norm > 0 and self._norm_w[i]:
+            wd_v = self.cfg.wd_norm / self.scale             # norm weights otherwise take constant-length steps with no pull back
+        if self.cfg.norm_anchor and self._anchor[i]:
+            self._anchor_norm(i, p)
         rows = self.rows.get(id(p)) if vocab else None
         if rows is not None:
             self._update_rows(i, p, grad, rows, lr_t)
@@ -221,6 +236,15 @@ class Instinct:
             self._update_cuda(i, p, grad, kind, wd_v, lr_t, want_rel)
         else:
             self._update_ref(i, p, grad, kind, wd_v, lr_t, want_rel)
+
+    def _anchor_norm(self, i, p):
+        """w <- w - lr wd (w - 1) on a 1-D norm weight (and its exact copy): what weight decay is for matrices, with 1
+        as the resting point (the JAX Instinct's `norm_anchor`, instinct.py:393-401)."""
+        pull = self._lr_t / self.scale * self.param_groups[0]["weight_decay"]
+        t = self.w[i] if self.w[i] is not None else p.data
+        t.sub_((t - 1.0) * pull.to(t.dtype))
+        if self.w[i] is not None:
+            p.data.copy_(t)
 
     def _damp(self, i, grad, lr_t):
         """Per-tensor gradient-surge damping (the reference's JAX Instinct, instinct.py:132-150): the optimizer

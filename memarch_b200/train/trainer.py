@@ -58,7 +58,9 @@ class Trainer:
         self.acc = {}
         if "X" in st and self.ocfg.kind == "instinct":
             import dataclasses
-            self.opt = Instinct(self.params, dataclasses.replace(self.ocfg, lr=tcfg.lr))
+            by_id = {id(p): n for n, p in model.named_parameters()}
+            self.opt = Instinct(self.params, dataclasses.replace(self.ocfg, lr=tcfg.lr),
+                                names=[by_id.get(id(p), "") for p in self.params])
             self.in_backward = "B" in st and self.ocfg.in_backward
             if parallel is not None:
                 parallel.attach(self)

@@ -577,3 +577,52 @@ def test_training_loop_raises_when_a_device_wait_has_run_out(monkeypatch):
         loop.device_status(tr)
     tr_cpu = types.SimpleNamespace(device=torch.device("cpu"), parallel=Engine())
     loop.device_status(tr_cpu)                                    # CPU runs have no status words
+
+
+def test_named_weight_switches_of_the_optimizer():
+    """gnorm (gradient scale does not matter), wd_norm (norm weights decay), norm_anchor (norm weights of the light
+    blocks rest at 1), lr_mul (step multiplier by name prefix) - switches of the reference's JAX Instinct
+    (instinct.py:65-131, 393-401)."""
+    import torch
+    from memarch_b200.config import OptConfig
+    from memarch_b200.optim.instinct import Instinct
+    sit = torch.ones(8)
+
+    def run(cfg, names, gscale=1.0, steps=1, grad_fn=None):
+        torch.manual_seed(0)
+        ps = [torch.nn.Parameter(torch.randn(16, 12)), torch.nn.Parameter(torch.ones(12) * 1.5),
+              torch.nn.Parameter(torch.ones(12) * 1.5)]
+        opt = Instinct(ps, cfg, names=names)
+        g = torch.Generator().manual_seed(1)
+        for s in range(steps):
+            opt.prepare(torch.tensor(3.0), sit)
+            for p in ps:
+                gr = torch.randn(p.shape, generator=g) * gscale if grad_fn is None else grad_fn(p)
+                opt.update(p, gr)
+            opt.finish()
+        return [p.detach().clone() for p in ps]
+
+    names = ["light_a.0.qkv.weight", "light_a.0.n1.weight", "norm.weight"]
+    base = OptConfig(lr=1e-2, norm="hs", weight_decay=0.1)
+    # gnorm: a thousand times larger gradients give the same momentum direction and the same first step anyway
+    # (Instinct normalises the update), but the momentum itself is scale-free only with gnorm
+    import dataclasses
+    a = run(dataclasses.replace(base, gnorm=True), names, 1.0)
+    b = run(dataclasses.replace(base, gnorm=True), names, 1000.0)
+    assert all(torch.allclose(x, y, atol=1e-6) for x, y in zip(a, b))
+    # lr_mul: the matrix under "light_a." moves half as far, the rest as before
+    w0 = run(base, names, steps=0)
+    full = run(base, names)
+    half = run(dataclasses.replace(base, lr_mul=(("light_a.0.qkv", 0.5),)), names)
+    # decay is part of the step: compare the distance from the start
+    d_full, d_half = (full[0] - w0[0]).norm(), (half[0] - w0[0]).norm()
+    assert abs(float(d_half / d_full) - 0.5) < 0.02 and torch.equal(full[2], half[2])
+    # wd_norm: zero gradients, so only the decay acts - norm weights shrink, and only with the switch
+    zero = lambda p: torch.zeros_like(p)
+    still = run(base, names, steps=3, grad_fn=zero)
+    decayed = run(dataclasses.replace(base, wd_norm=0.5), names, steps=3, grad_fn=zero)
+    assert torch.equal(still[1], w0[1]) and float(decayed[1].mean()) < 1.5 and float(decayed[2].mean()) < 1.5
+    assert torch.equal(still[0], decayed[0])
+    # norm_anchor: the light block's norm weight is pulled from 1.5 towards 1, the final norm (no light_* prefix) is not
+    anchored = run(dataclasses.replace(base, norm_anchor=True), names, steps=3, grad_fn=zero)
+    assert 1.0 < float(anchored[1].mean()) < 1.5 and torch.equal(anchored[2], w0[2])

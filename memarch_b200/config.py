@@ -113,7 +113,7 @@ class ModelConfig:
 @dataclass
 class OptConfig:
     """InstinctOptB constructor (exp_opt.py:437-439) plus the env switches around it."""
-    kind: str = "instinct"        # instinct | adamw | surprise | muon (OPT=muon: Muon on hidden matrices + AdamW)
+    kind: str = "instinct"        # instinct | experience (the first card optimizer, host-synchronous) | adamw | surprise | muon
     muon_mul: float = 1.0         # MUON_MUL: Muon's learning rate as a multiple of the shared one
     lr: float = 1e-3
     weight_decay: float = 0.1

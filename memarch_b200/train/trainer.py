@@ -72,6 +72,12 @@ class Trainer:
                 with (torch.cuda.stream(self._gstream) if self._gstream is not None else contextlib.nullcontext()):
                     for p in self.params:
                         p.register_post_accumulate_grad_hook(self._hook)
+        elif "X" in st and self.ocfg.kind == "experience":
+            from ..optim.experience import ExperienceOpt
+            self.opt = ExperienceOpt(self.params, lr=tcfg.lr, weight_decay=0.1, cards=self.ocfg.cards, beta=self.ocfg.beta,
+                                     new_card=self.ocfg.new_card, ema=self.ocfg.ema, norm=self.ocfg.norm,
+                                     scale=self.ocfg.scale, m_dtype="bf16" if self.ocfg.m_bf16 else "fp32")
+            self.in_backward = False
         elif self.ocfg.kind == "muon":
             from ..optim.muon import MuonAdamW
             self.opt = MuonAdamW(self.params, lr=tcfg.lr, weight_decay=0.1, betas=(0.9, 0.95), mul=self.ocfg.muon_mul)
@@ -240,6 +246,8 @@ class Trainer:
             torch.nn.utils.clip_grad_norm_(self.params, 1.0)
             if isinstance(self.opt, SurpriseAdamW):
                 self.opt.step(total)
+            elif hasattr(self.opt, "pick"):                       # experience cards: loss (host read) and situation
+                self.opt.step(total, self.situation(xy))
             else:
                 self.opt.step()
             self.opt.zero_grad(set_to_none=True)

@@ -4,6 +4,7 @@ usage: python ref_oracle.py <reference dir> <out.pt> <json spec>
 spec: {"name", "vocab", "env": {...}, "B", "T", "seed", "what": "model" | "instinct"}
 The reference reads its switches from the environment at import time, hence the separate process."""
 import json
+import math
 import os
 import sys
 
@@ -67,6 +68,24 @@ def main():
         waves = {k: v.clone() for k, v in tr.model.state_dict().items()
                  if k.split(".")[-1] in ("learned", "err", "err_peak", "err_freeze", "move_peak", "last_move")}
         torch.save({"sd": sd, "batches": batches, "losses": losses, "waves": waves}, out)
+    elif spec["what"] == "experience":
+        import exp_opt
+        torch.manual_seed(3)
+        shapes = [tuple(s_) for s_ in spec["shapes"]]
+        ps = [torch.nn.Parameter(torch.randn(*s_) * 0.1) for s_ in shapes]
+        w0 = [p.detach().clone() for p in ps]
+        opt = exp_opt.ExperienceOpt(ps, lr=spec["lr"], **spec.get("kw", {}))
+        feed, ws = [], []
+        for step in range(spec["steps"]):
+            gs = [torch.randn(*s_) * 0.01 for s_ in shapes]
+            sit = torch.randn(spec["d"]) + (3.0 if step % 3 == 0 else -3.0) * torch.ones(spec["d"])   # two kinds of batches
+            loss = 3.0 + 0.4 * math.sin(step)
+            for p, g_ in zip(ps, gs):
+                p.grad = g_.clone()
+            opt.step(torch.tensor(loss), sit)
+            feed.append((gs, sit, loss))
+            ws.append([p.detach().clone() for p in ps])
+        torch.save({"w0": w0, "feed": feed, "ws": ws, "used": opt.used.clone()}, out)
     elif spec["what"] == "instinct":
         import exp_opt
         torch.manual_seed(3)

@@ -332,3 +332,21 @@ def test_frozen_bank_after_rebank_matches_reference(tmp_path, bank_q):
             assert (p.grad.float() - g.float()).abs().max() <= 5e-3 * g.float().abs().max(), n
             checked += 1
     assert checked > 20
+
+
+@pytest.mark.parametrize("kw", [{"m_dtype": "fp32"}, {"m_dtype": "fp32", "norm": "row", "cards": 3}])
+def test_experience_optimizer_matches_reference(tmp_path, kw):
+    """The first card optimizer (a momentum per card and weight, surprise-scaled steps) over 8 steps of alternating
+    situations and rising / falling losses: same weights as the reference after every step, word table included."""
+    from memarch_b200.optim.experience import ExperienceOpt
+    shapes = [(24, 16), (10000, 4), (3, 8, 6), (16,)]
+    d = oracle(tmp_path, {"what": "experience", "shapes": shapes, "lr": 1e-2, "kw": kw, "steps": 8, "d": 12})
+    ps = [torch.nn.Parameter(w.clone()) for w in d["w0"]]
+    opt = ExperienceOpt(ps, lr=1e-2, **kw)
+    for step, (gs, sit, loss) in enumerate(d["feed"]):
+        for p, g in zip(ps, gs):
+            p.grad = g.clone()
+        opt.step(torch.tensor(loss), sit)
+        for p, w in zip(ps, d["ws"][step]):
+            assert (p.detach() - w).abs().max().item() <= 1e-5 * max(w.abs().max().item(), 1e-3), (step, tuple(p.shape))
+    assert opt.used == d["used"].tolist() and sum(opt.used) >= 2          # both kinds of batches got their own card

@@ -626,3 +626,20 @@ def test_named_weight_switches_of_the_optimizer():
     # norm_anchor: the light block's norm weight is pulled from 1.5 towards 1, the final norm (no light_* prefix) is not
     anchored = run(dataclasses.replace(base, norm_anchor=True), names, steps=3, grad_fn=zero)
     assert 1.0 < float(anchored[1].mean()) < 1.5 and torch.equal(anchored[2], w0[2])
+
+
+def test_trainer_with_the_experience_card_optimizer_learns():
+    """Stage AX with `OptConfig(kind="experience")`: the host-synchronous card optimizer behind the trainer; a repeated
+    batch is learned and the batch's situation picked a card."""
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.optim.experience import ExperienceOpt
+    from memarch_b200.train import Trainer
+    torch.manual_seed(0)
+    m = build("tiny", 256, env={"NO_MEM": "1", "MOE_ACT": "relu2"})
+    tr = Trainer(m, TrainConfig(name="tiny", stage="AX", steps=50, batch=4, micro=4, seq=32, lr=3e-3, warmup=2),
+                 OptConfig(kind="experience", lr=3e-3, norm="row"), stage="AX")
+    assert isinstance(tr.opt, ExperienceOpt)
+    xy = batches(1)[0]
+    losses = [float(tr.step(xy, s)) for s in range(8)]
+    assert losses[-1] < losses[0] - 0.2, losses
+    assert any(tr.opt.used) and tr.opt.last["card"] == 0

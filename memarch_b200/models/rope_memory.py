@@ -5,8 +5,10 @@ Anchors are the surprising tokens.  Every anchor owns the span of text from itse
 opens its top-`K` anchors and attends with ONE softmax over its local window (`win` tokens, causal) and the tokens of
 the opened spans that lie before the window.  The cost per token does not depend on the text length: window + K spans.
 
-Routing is exact (every query against every anchor's links) and runs under `no_grad`; with `rgrad` the routing score of
-an opened anchor is added as a bias to all keys of its span, which is how the choice receives a gradient.
+Routing runs under `no_grad`, either exact (every query against every anchor's links) or two-level (`route_hier`:
+groups of anchors ranked per block of queries, exact scores among the anchors of the kept groups only); with `rgrad`
+the routing score of an opened anchor is added as a bias to all keys of its span, which is how the choice receives a
+gradient.
 Reading is the dense-mask formulation (scores against all T keys, spans as a mask), chunked over queries with
 recomputation: the same numbers as the gathered form and no gather capacity to overflow.  Spans of different anchors
 never overlap, so every token enters the softmax at most once.
@@ -30,6 +32,10 @@ class RopeCfg:
     links: int = 8              # keys that represent an anchor in the search
     win: int = 64               # local causal window
     span_cap: int = 256         # longest span read after an anchor
+    route: str = "hier"         # "hier": two-level search over groups of anchors; "exact": every anchor
+    G: int = 64                 # hier: anchors per group
+    NB: int = 16                # hier: groups kept per block of queries
+    BM: int = 64                # hier: queries per block
     excl_win: bool = True       # an anchor opens only once its span start has left the window
     rgrad: bool = True          # routing score as a bias on the span's keys
     rgrad_scale: float = 1.0
@@ -68,38 +74,147 @@ def next_anchor(apos, avalid, T):
     return torch.where(nv, na, torch.full_like(apos, T))
 
 
+def _links(k, own, apos, avalid, L):
+    """The first L keys of every anchor's own span: kl (B,H,A,L,hd), lval (B,A,L) which of them exist, lp (B,A,L)
+    their positions."""
+    B, H, T, hd = k.shape
+    A = apos.shape[1]
+    lp = apos[:, :, None] + torch.arange(L, device=k.device)
+    inb = lp < T
+    lp = lp.clamp(max=T - 1)
+    own_lp = own.gather(1, lp.reshape(B, A * L)).view(B, A, L)
+    lval = inb & avalid[:, :, None] & (own_lp == torch.arange(A, device=k.device)[None, :, None])
+    kl = k.gather(2, lp.reshape(B, 1, A * L, 1).expand(B, H, A * L, hd)).view(B, H, A, L, hd)
+    return kl, lval, lp
+
+
+def _open_from(apos, avalid, T, cfg):
+    """First query position that may open each anchor: once its span is complete and (excl_win) has left the window."""
+    nxt = next_anchor(apos, avalid, T)
+    return torch.maximum(nxt, apos + cfg.win) if cfg.excl_win else nxt
+
+
+def _best_of(qc, kl, lval, lp, ok, kk, hd):
+    """Score queries qc (..., M, hd) against link keys kl (..., N, L, hd) of N anchors, keep each anchor's best link,
+    mask by ok (..., M, N) and take the top kk.  lval / lp (..., N, L) broadcast over heads.
+    Returns (slot in N, valid, position of the best link), each (..., M, kk)."""
+    s = torch.einsum("...md,...nld->...mnl", qc.float(), kl.float()) / math.sqrt(hd)
+    s = s.masked_fill(~lval[..., None, :, :], -float("inf"))
+    s_a, best_l = s.max(-1)
+    s_a = s_a.masked_fill(~ok, -float("inf"))
+    top_v, top_i = s_a.topk(kk, -1)
+    val = top_v > -float("inf")
+    lpa = lp[..., None, :, :].expand(*s.shape).gather(-1, best_l[..., None]).squeeze(-1)
+    zero = torch.zeros_like(top_i)
+    return torch.where(val, top_i, zero), val, torch.where(val, lpa.gather(-1, top_i), zero)
+
+
 @torch.no_grad()
 def route_exact(q, k, own, apos, avalid, cfg: RopeCfg):
     """q, k (B,H,T,hd).  Returns tidx (B,H,T,K) anchor numbers, tval (valid), tpos (position of the best link)."""
     B, H, T, hd = q.shape
     A = apos.shape[1]
     kk, L = min(cfg.K, A), min(cfg.links, cfg.span_cap)
-    lp = apos[:, :, None] + torch.arange(L, device=q.device)
-    inb = lp < T
-    lp = lp.clamp(max=T - 1)
-    own_lp = own.gather(1, lp.reshape(B, A * L)).view(B, A, L)
-    lval = inb & avalid[:, :, None] & (own_lp == torch.arange(A, device=q.device)[None, :, None])
-    kl = k.gather(2, lp.reshape(B, 1, A * L, 1).expand(B, H, A * L, hd)).view(B, H, A, L, hd)
-    nxt = next_anchor(apos, avalid, T)
-    nx = torch.maximum(nxt, apos + cfg.win) if cfg.excl_win else nxt
+    kl, lval, lp = _links(k, own, apos, avalid, L)
+    nx = _open_from(apos, avalid, T, cfg)
     qi = torch.arange(T, device=q.device)
-    tidx = torch.zeros(B, H, T, kk, dtype=torch.long, device=q.device)
-    tval = torch.zeros(B, H, T, kk, dtype=torch.bool, device=q.device)
-    tpos = torch.zeros(B, H, T, kk, dtype=torch.long, device=q.device)
+    out = []
     for c0 in range(0, T, cfg.chunk):
-        qc = q[:, :, c0:c0 + cfg.chunk].float()
-        s = torch.einsum("bhmd,bhald->bhmal", qc, kl.float()) / math.sqrt(hd)
-        s = s.masked_fill(~lval[:, None, None], -float("inf"))
-        s_a, best_l = s.max(-1)
         ok = avalid[:, None, :] & (nx[:, None, :] <= qi[None, c0:c0 + cfg.chunk, None])
-        s_a = s_a.masked_fill(~ok[:, None], -float("inf"))
-        top_v, top_i = s_a.topk(kk, -1)
-        val = top_v > -float("inf")
-        lpa = lp[:, None, None].expand(B, H, qc.shape[2], A, L).gather(-1, best_l[..., None]).squeeze(-1)
-        tidx[:, :, c0:c0 + cfg.chunk] = torch.where(val, top_i, torch.zeros_like(top_i))
-        tval[:, :, c0:c0 + cfg.chunk] = val
-        tpos[:, :, c0:c0 + cfg.chunk] = torch.where(val, lpa.gather(-1, top_i), torch.zeros_like(top_i))
-    return tidx, tval, tpos
+        out.append(_best_of(q[:, :, c0:c0 + cfg.chunk], kl, lval[:, None], lp[:, None], ok[:, None], kk, hd))
+    return tuple(torch.cat(t, 2) for t in zip(*out))
+
+
+@torch.no_grad()
+def route_hier(q, k, own, apos, avalid, cfg: RopeCfg):
+    """Two-level search (rope.py:147-262 of the reference's JAX port): the cost per query does not grow with the
+    number of anchors.
+
+    Anchors are taken `G` at a time in order; a group is known by the mean of its link keys.  Queries are taken `BM`
+    at a time; a block looks only at groups all of whose anchors were complete before the block began, ranks them by
+    the mean query of the PREVIOUS block (every query of that block lies in the past of every query of this one, so
+    nothing leaks backwards in time) and keeps the best `NB`.  The anchors after the last complete group, including
+    the ones that appear while the block runs (at most one per query), are always candidates.  Each query is then
+    scored exactly against the candidates only, with the same rule for which anchors may open as the exact search.
+    When `NB` covers all complete groups the result is that of the exact search."""
+    B, H, T, hd = q.shape
+    A = apos.shape[1]
+    dev = q.device
+    kk, L = min(cfg.K, A), min(cfg.links, cfg.span_cap)
+    G, BM = cfg.G, cfg.BM
+    NG = -(-A // G)
+    nb = min(cfg.NB, NG)
+    kl, lval, lp = _links(k, own, apos, avalid, L)
+    nxt = next_anchor(apos, avalid, T)
+    nx = _open_from(apos, avalid, T, cfg)
+
+    # level 1: one key per group of anchors, one query per block of queries
+    pad = NG * G - A
+    w = F.pad(lval, (0, 0, 0, pad)).view(B, 1, NG, G * L, 1).float()
+    gkey = (F.pad(kl, (0, 0, 0, 0, 0, pad)).view(B, H, NG, G * L, hd).float() * w).sum(3) / w.sum(3).clamp(min=1.0)
+    NMB = -(-T // BM)
+    qp = F.pad(q, (0, 0, 0, NMB * BM - T)).view(B, H, NMB, BM, hd)
+    m0 = torch.arange(NMB, device=dev) * BM
+    last = (m0 + BM).clamp(max=T) - 1
+    qmean = qp.float().sum(3) / (last - m0 + 1).float()[None, None, :, None]
+    gsc = torch.einsum("bhnd,bhgd->bhng", qmean, gkey)
+    gsc = torch.cat([torch.zeros_like(gsc[:, :, :1]), gsc[:, :, :-1]], 2)
+    done = (avalid[:, None, :] & (nxt[:, None, :] <= m0[None, :, None])).sum(-1)             # (B,NMB)
+    nfg = done // G
+    g = torch.arange(NG, device=dev)
+    gok = g < nfg[..., None]
+    if cfg.excl_win:
+        out_of_win = (avalid[:, None, :] & (apos[:, None, :] + cfg.win <= last[None, :, None])).sum(-1)
+        gok = gok & (g * G < out_of_win[..., None])
+    top_gv, top_gi = gsc.masked_fill(~gok[:, None], -float("inf")).topk(nb, -1)               # (B,H,NMB,nb)
+
+    # candidates of a block: the anchors of its groups, then the tail after the last complete group
+    ar = torch.arange(G, device=dev)
+    grp = (top_gi[..., None] * G + ar).flatten(-2)
+    grp_ok = ((top_gv > -float("inf"))[..., None] & ((top_gi[..., None] * G + ar) < A)).flatten(-2)
+    tail = (nfg[:, None, :, None] * G + torch.arange(G + BM, device=dev)).expand(B, H, NMB, G + BM)
+    cand = torch.cat([grp, tail], -1)
+    cand_ok = torch.cat([grp_ok, tail < A], -1)
+    cand = torch.where(cand_ok, cand, torch.zeros_like(cand))
+    Cn = cand.shape[-1]
+
+    # level 2: exact scores against the candidates, a few blocks at a time
+    per = max(1, min(max(1, cfg.chunk // BM), (1 << 26) // max(1, B * H * Cn * L * hd)))
+    out = []
+    for b0 in range(0, NMB, per):
+        ca, cv = cand[:, :, b0:b0 + per], cand_ok[:, :, b0:b0 + per]
+        n = ca.shape[2]
+        flat = ca.reshape(B, H, n * Cn)
+        kl_c = kl.gather(2, flat[..., None, None].expand(B, H, n * Cn, L, hd)).view(B, H, n, Cn, L, hd)
+        pick = lambda t: t[:, None].expand(B, H, *t.shape[1:]).gather(
+            2, flat.view(B, H, n * Cn, *([1] * (t.dim() - 2))).expand(B, H, n * Cn, *t.shape[2:])
+        ).view(B, H, n, Cn, *t.shape[2:])
+        qi = (m0[b0:b0 + per, None] + torch.arange(BM, device=dev))                          # (n,BM)
+        ok = cv[:, :, :, None, :] & pick(avalid)[:, :, :, None, :] & (pick(nx)[:, :, :, None, :] <= qi[None, None, :, :, None])
+        slot, val, pos = _best_of(qp[:, :, b0:b0 + per], kl_c, pick(lval), pick(lp), ok, kk, hd)
+        idx = ca[:, :, :, None, :].expand(B, H, n, BM, Cn).gather(-1, slot)
+        out.append((torch.where(val, idx, torch.zeros_like(idx)), val, pos))
+    return tuple(torch.cat(t, 2).view(B, H, NMB * BM, kk)[:, :, :T] for t in zip(*out))
+
+
+def route(q, k, own, apos, avalid, cfg: RopeCfg):
+    if cfg.route == "exact":
+        return route_exact(q, k, own, apos, avalid, cfg)
+    if cfg.route == "hier":
+        return route_hier(q, k, own, apos, avalid, cfg)
+    raise ValueError(f"unknown route mode {cfg.route!r}")
+
+
+def mask_route(tidx, tval, apos, qmask=None, docs=None):
+    """Queries outside `qmask` (B,T) open nothing and read their window only; with `docs` (B,T) document numbers an
+    anchor of another document than the query's is not opened (rope.py:277-287)."""
+    if qmask is not None:
+        tval = tval & qmask[:, None, :, None]
+    if docs is not None:
+        B, H, T, K = tidx.shape
+        da = docs.gather(1, apos).gather(1, tidx.reshape(B, -1)).view(B, H, T, K)
+        tval = tval & (da == docs[:, None, :, None])
+    return tval
 
 
 def _read_chunk(qc, kr, v, k0, q0c, c0, st, en, tval, tpos, W, rgrad, rgrad_scale):
@@ -127,11 +242,13 @@ def _read_chunk(qc, kr, v, k0, q0c, c0, st, en, tval, tpos, W, rgrad, rgrad_scal
     return out, share
 
 
-def rope_attention(qr, kr, v, own, apos, avalid, cfg: RopeCfg, routed=None):
+def rope_attention(qr, kr, v, own, apos, avalid, cfg: RopeCfg, routed=None, qmask=None, docs=None):
     """qr, kr rotated queries / keys, v values, all (B,H,T,hd).  Returns (out (B,H,T,hd), share of softmax mass that
-    went to opened spans, (tidx, tval, tpos))."""
+    went to opened spans, (tidx, tval, tpos)).  `routed` reuses another layer's choice; `qmask` / `docs` as in
+    `mask_route`."""
     B, H, T, hd = qr.shape
-    tidx, tval, tpos = route_exact(qr, kr, own, apos, avalid, cfg) if routed is None else routed
+    tidx, tval, tpos = route(qr, kr, own, apos, avalid, cfg) if routed is None else routed
+    tval = mask_route(tidx, tval, apos, qmask, docs)
     nxt = next_anchor(apos, avalid, T)
     outs, shares = [], []
     qi_all = torch.arange(T, device=qr.device)
@@ -162,7 +279,7 @@ class RopeMemoryAttention(nn.Module):
         self.o = nn.Linear(d, d, bias=False)
         self.stats = {}
 
-    def forward(self, x, surprise, tau, cap=0.25, routed=None):
+    def forward(self, x, surprise, tau, cap=0.25, routed=None, qmask=None, docs=None):
         B, T, D = x.shape
         hd = D // self.heads
         q, k, v = self.qkv(x).view(B, T, 3, self.heads, hd).permute(2, 0, 3, 1, 4)
@@ -170,6 +287,6 @@ class RopeMemoryAttention(nn.Module):
         q, k = ref.apply_rope(q, cos, sin, False), ref.apply_rope(k, cos, sin, False)
         with torch.no_grad():
             own, apos, avalid = anchors_from_surprise(surprise.clone(), tau, max(1, round(T * cap)))
-        out, share, route = rope_attention(q, k, v, own, apos, avalid, self.cfg, routed)
+        out, share, route = rope_attention(q, k, v, own, apos, avalid, self.cfg, routed, qmask, docs)
         self.stats["rope_share"] = share
         return self.o(out.transpose(1, 2).reshape(B, T, D)), route

@@ -3,6 +3,7 @@ uroboros selection, int8 numerics, recall toy task."""
 import math
 
 import numpy as np
+import pytest
 import torch
 
 from memarch_b200.models import fishki
@@ -63,6 +64,61 @@ def test_rope_memory_matches_brute_force_and_has_gradients():
     layer = rm.RopeMemoryAttention(32, 2, cfg)
     y, _ = layer(torch.randn(2, 96, 32), s, 1.4)
     assert y.shape == (2, 96, 32)
+
+
+def _rope_case(T=200, A=60, seed=0):
+    torch.manual_seed(seed)
+    B, H, hd = 2, 2, 16
+    q, k = torch.randn(B, H, T, hd), torch.randn(B, H, T, hd)
+    s = torch.rand(B, T) * 2
+    return q, k, s, rm.anchors_from_surprise(s.clone(), 1.3, A)
+
+
+def test_rope_two_level_search():
+    q, k, s, (own, apos, avalid) = _rope_case()
+    base = dict(K=3, links=3, win=8, span_cap=12, chunk=64, G=4, BM=16)
+    exact = rm.route_exact(q, k, own, apos, avalid, rm.RopeCfg(route="exact", **base))
+    # every complete group kept: the exact search (T not a multiple of BM, A not a multiple of G)
+    full = rm.route_hier(q, k, own, apos, avalid, rm.RopeCfg(NB=64, **base))
+    for a, b in zip(exact, full):
+        assert torch.equal(a, b)
+    # few groups kept: a subset of what may open, recent anchors (the tail) always reachable
+    cfg = rm.RopeCfg(NB=2, **base)
+    tidx, tval, tpos = rm.route_hier(q, k, own, apos, avalid, cfg)
+    assert bool(tval.any()) and not all(torch.equal(a, b) for a, b in zip(exact, (tidx, tval, tpos)))
+    nx = rm._open_from(apos, avalid, q.shape[2], cfg)
+    qi = torch.arange(q.shape[2])[None, None, :, None]
+    opened_at = nx.gather(1, tidx.reshape(2, -1)).view_as(tidx)
+    assert bool(((opened_at <= qi) | ~tval).all())
+    assert bool((own.gather(1, tpos.reshape(2, -1)).view_as(tidx) == tidx)[tval].all())
+    # nothing flows backwards in time: what lies after position t does not change the choice up to t
+    t = 117
+    q2, k2 = q.clone(), k.clone()
+    q2[:, :, t + 1:], k2[:, :, t + 1:] = torch.randn_like(q2[:, :, t + 1:]), torch.randn_like(k2[:, :, t + 1:])
+    again = rm.route_hier(q2, k2, own, apos, avalid, cfg)
+    for a, b in zip((tidx, tval, tpos), again):
+        assert torch.equal(a[:, :, :t + 1], b[:, :, :t + 1])
+    with pytest.raises(ValueError):
+        rm.route(q, k, own, apos, avalid, rm.RopeCfg(route="flat"))
+
+
+def test_rope_query_and_document_masks():
+    q, k, s, (own, apos, avalid) = _rope_case(T=96, A=30, seed=1)
+    v = torch.randn_like(q)
+    cfg = rm.RopeCfg(K=2, links=3, win=8, span_cap=12, chunk=32, G=4, BM=16)
+    out, share, (tidx, tval, _) = rm.rope_attention(q, k, v, own, apos, avalid, cfg)
+    qmask = torch.rand(2, 96) < 0.5
+    out_m, share_m, _ = rm.rope_attention(q, k, v, own, apos, avalid, cfg, qmask=qmask)
+    only_win, _, _ = rm.rope_attention(q, k, v, own, apos, avalid, cfg, qmask=torch.zeros(2, 96, dtype=torch.bool))
+    sel = qmask[:, None, :, None].expand_as(out)
+    assert torch.allclose(out_m[sel], out[sel]) and torch.allclose(out_m[~sel], only_win[~sel])
+    assert float(share_m) < float(share)
+    docs = (torch.arange(96)[None] >= torch.tensor([[40], [70]])).long()
+    tv = rm.mask_route(tidx, tval, apos, docs=docs)
+    a_doc = docs.gather(1, apos).gather(1, tidx.reshape(2, -1)).view_as(tidx)
+    assert bool((a_doc == docs[:, None, :, None])[tv].all()) and int(tv.sum()) < int(tval.sum())
+    out_d, _, _ = rm.rope_attention(q, k, v, own, apos, avalid, cfg, docs=docs)
+    assert torch.allclose(out_d[0, :, :40], out[0, :, :40]) and not torch.allclose(out_d, out)
 
 
 def test_fishki_pool_and_router():

@@ -72,6 +72,17 @@ class ModelConfig:
     heavy_attn_detach: bool = False
     n_draft: int = 0
     draft_loss: float = 0.0
+    # loss on the answers of recall needles (data.reminders); 0 = the batch's "rem" mask is only scored, not trained on
+    remind_w: float = 0.0         # REMIND_W: weight of the term (sum of the answers' NLL / (B * remind_q))
+    remind_q: int = 16            # questions per needle row (the normaliser)
+    remind_cap: int = 0           # answers read per row (0: remind_q); more with several needles per row
+    remind_mean: bool = False     # REMIND_MEAN: mean over the batch's answers (episode rows have many)
+    remind_only: bool = False     # REMIND_ONLY: stage one, the main loss does not train
+    remind_cand: bool = False     # REMIND_CAND: softmax over the 64 value tokens only
+    remind_mask_main: bool = False  # REMIND_MASK_MAIN: needle tokens do not train the main loss
+    remind_strict: bool = False   # REMIND_STRICT: nothing earned after a row's first wrong answer + penalty on guessing
+    remind_strict_w: float = 1.0
+    remind_tok0: int = 1000       # REMIND_TOK0: first needle token (keys 512, values 64, marker)
     # light block variants (BLK set)
     blk: Tuple[str, ...] = ()     # subset of {zero, ve, x0, relu2, relu2c, qk, qkv3, smear}
     light_ffn: float = 0.0        # LIGHT_FFN width in units of d
@@ -235,6 +246,13 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
     if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("REMIND_W"): kw["remind_w"] = float(g("REMIND_W"))
+    if g("REMIND_N"): kw["remind_q"] = int(g("REMIND_N"))
+    if g("REMIND_PER_ROW"): kw["remind_cap"] = int(g("REMIND_PER_ROW")) * int(g("REMIND_N") or 16)
+    for k_ in ("mean", "only", "cand", "mask_main", "strict"):
+        if g("REMIND_" + k_.upper()) == "1": kw["remind_" + k_] = True
+    if g("REMIND_STRICT_W"): kw["remind_strict_w"] = float(g("REMIND_STRICT_W"))
+    if g("REMIND_TOK0"): kw["remind_tok0"] = int(g("REMIND_TOK0"))
     if g("BLK"): kw["blk"] = tuple(s for s in g("BLK").split(",") if s)
     if g("LIGHT_FFN"): kw["light_ffn"] = float(g("LIGHT_FFN"))
     if g("LIGHT_MOE"): kw["light_moe"] = g("LIGHT_MOE")

@@ -17,9 +17,14 @@ Behaviour follows the reference's host-side data tools (memarch_jax/memarch_jax/
 * `synth` batches are filler plus one needle (the pure recall task);
 * `near`: a share of the needles at distance 0..near_max, inside the attention window;
 * `per_row` / `far_log`: several marker-free needles per row of text with log-uniform far distances;
-* `blank`: the value after each question key is replaced by the marker, the true value is returned in `rem_y` (B, T).
-
-Not carried over: the densely packed synthetic episodes and their own level table.
+* `same_fmt`: one needle per row in the marker-free format of the synthetic episodes, `[k v]*n` ... `[k v]*n`, with
+  every other occurrence of a needle token scrubbed from the row;
+* `blank`: the true values are returned in `rem_y` (B, T); with `same_fmt` and in the episodes the value after each
+  question key is also replaced by the marker in the text: "the answers are seen only after the test";
+* `pack`: the `synth` batches are the short-row episodes of `data.episodes.Episodes` with their own curriculum, and
+  `mix=(shares, length)` keeps a decaying share of synthetic batches after the stage: phase k of `length` batches has
+  the share `shares[k]`, the last share stays for good (which batches are synthetic depends on the number only);
+* `__call__(..., pack=(pairs, fill))` (evaluation): rows densely laid out with episodes of exactly that shape.
 """
 from __future__ import annotations
 
@@ -27,13 +32,17 @@ import zlib
 
 import numpy as np
 
+from .episodes import Episodes
+
 N_KEYS, N_VALS = 512, 64
+GOLDEN = 0.6180339887498949                          # batch number -> evenly spread point of [0, 1)
 
 
 class Reminders:
     def __init__(self, p, T, n=16, dist=2048, tok0=1000, seed=0, V=None, p0=None, warm=0, decay=0, ladder=None,
                  thr=0.9, win=800, lag=5, dmin=0, synth=0, doc_eos=None, near=0.0, near_max=0, blank=False,
-                 per_row=1, far_log=None):
+                 per_row=1, far_log=None, same_fmt=False, pack=None, mix=None):
+        """`pack`: None, True or a dict of `Episodes` options."""
         self.p, self.T, self.n, self.dist, self.seed = float(p), int(T), int(n), int(dist), int(seed)
         self.p0 = None if p0 is None else float(p0)
         self.warm, self.decay = int(warm), int(decay)
@@ -43,7 +52,9 @@ class Reminders:
         self.doc_eos = None if doc_eos is None or int(doc_eos) < 0 else int(doc_eos)
         self.near, self.near_max = float(near), int(near_max)
         self.per_row, self.far_log = int(per_row), (None if far_log is None else float(far_log))
-        self.blank = bool(blank)                     # answers are not visible in the questions: the target is in rem_y
+        self.blank, self.same_fmt = bool(blank), bool(same_fmt)
+        self.n_keys, self.n_vals = N_KEYS, N_VALS
+        self.mix_shares, self.mix_len = (list(mix[0]), int(mix[1])) if mix else (None, 250)
         self.k0, self.v0, self.mark = tok0, tok0 + N_KEYS, tok0 + N_KEYS + N_VALS
         self.L = 2 * self.n + 2                      # one block: marker, n (key, value) pairs, marker
         self.changes = [(0, 0)]                      # (first batch, level)
@@ -56,6 +67,7 @@ class Reminders:
             raise ValueError(f"T={T} too short for two blocks of {self.L} and a distance of {dist}")
         if self.ladder and self.ladder[-1] > self.T + 1 - 2 * self.L:
             raise ValueError(f"ladder {self.ladder} exceeds the row")
+        self.pack = Episodes(self, **(pack if isinstance(pack, dict) else {})) if pack else None
 
     # ------------------------------------------------------------------------------------------------ schedule
     def p_at(self, i):
@@ -66,7 +78,14 @@ class Reminders:
         return self.p0 + (self.p - self.p0) * min(1.0, (i - self.warm) / max(self.decay, 1))
 
     def synth_at(self, i):
-        return i is not None and i < self.synth
+        if i is None:
+            return False
+        if i < self.synth:
+            return True
+        if not self.mix_shares:
+            return False
+        phase = min((i - self.synth) // max(self.mix_len, 1), len(self.mix_shares) - 1)
+        return (i * GOLDEN) % 1.0 < self.mix_shares[phase]
 
     def level_at(self, i):
         k = 0
@@ -83,6 +102,8 @@ class Reminders:
 
     def observe(self, i, hits, n_ans):
         """After step i: needle accuracy of the training batch -> maybe a level change; returns a log line or None."""
+        if self.pack is not None and self.synth_at(i):
+            return self.pack.observe(i, hits, n_ans)
         if not self.ladder:
             return None
         self.hits += hits
@@ -99,11 +120,16 @@ class Reminders:
         return f"reminders: level {k} -> {k + 1} (accuracy {acc:.3f}), from batch {i + self.lag} distance {lo}..{hi}"
 
     def state(self):
-        return {"changes": [list(c) for c in self.changes], "acc_h": self.hits, "acc_n": self.answers}
+        st = {"changes": [list(c) for c in self.changes], "acc_h": self.hits, "acc_n": self.answers}
+        if self.pack is not None:
+            st.update(self.pack.state())
+        return st
 
     def load(self, st):
         self.changes = [tuple(c) for c in st["changes"]]
         self.hits, self.answers = st["acc_h"], st["acc_n"]
+        if self.pack is not None:
+            self.pack.load(st)
 
     # ------------------------------------------------------------------------------------------------ rows
     def _filler(self, rng, n):
@@ -130,16 +156,25 @@ class Reminders:
                 raise ValueError(f"distance {exact} does not fit a row of {T1}")
             s = int(rng.integers(0, T1 - 2 * L - exact + 1))
             q = s + L + exact
+        facts = np.stack([keys, vals], 1).reshape(-1)
         order = rng.permutation(n)
-        row[s] = row[s + L - 1] = row[q] = row[q + L - 1] = self.mark
-        row[s + 1:s + L - 1] = np.stack([keys, vals], 1).reshape(-1)
-        row[q + 1:q + L - 1] = np.stack([keys[order], vals[order]], 1).reshape(-1)
+        asks = np.stack([keys[order], vals[order]], 1).reshape(-1)
+        if self.same_fmt:                            # needle tokens are ordinary words of real text: 5-7 % of a row
+            stray = (row >= self.k0) & (row <= self.mark)   # would look like facts, so none stays outside the needle
+            if stray.any():
+                row[stray] = self._filler(rng, int(stray.sum()))
+            row[s:s + 2 * n], row[q:q + 2 * n] = facts, asks
+            first = q
+        else:
+            row[s] = row[s + L - 1] = row[q] = row[q + L - 1] = self.mark
+            row[s + 1:s + L - 1], row[q + 1:q + L - 1] = facts, asks
+            first = q + 1
         if self.doc_eos is not None:                 # a document boundary between facts and questions would hide them
             seg = row[s:q + L]
             hit = seg == self.doc_eos
             if hit.any():
                 seg[hit] = self._filler(rng, int(hit.sum()))
-        return q + 1 + 2 * np.arange(n)              # positions of the question keys in x (y there is the value)
+        return first + 2 * np.arange(n)              # positions of the question keys in x (y there is the value)
 
     def _several(self, row, rng):
         """Several needles in one row of text, without markers: facts `[k v]*n`, questions `[k v]*n` in another order.
@@ -183,7 +218,7 @@ class Reminders:
                 break
         return np.sort(np.concatenate(found)) if found else np.zeros(0, np.int64)
 
-    def __call__(self, xy, p=None, exact=None, n=None, synth=None):
+    def __call__(self, xy, p=None, exact=None, n=None, synth=None, pack=None):
         """xy (B, T+1) tokens -> (xy with needles, {"rem": (B, T) int8}).  `n` = number of the training batch."""
         if synth is None:
             synth = self.synth_at(n)
@@ -192,14 +227,20 @@ class Reminders:
             p = self.p_at(n)
             level_range = self.range_at(n) if self.ladder else None
         p = self.p if p is None else p
+        if synth and self.pack is not None and n is not None and pack is None:
+            return self.pack.batch(xy.shape, n)
+        dense = (self.pack or Episodes(self)) if synth and pack is not None else None
         xy = np.array(xy, copy=True)
         B, T1 = xy.shape
         rem = np.zeros((B, T1 - 1), np.int8)
         rem_y = np.zeros((B, T1 - 1), np.int32) if self.blank else None
         for b in range(B):
             rng = np.random.default_rng([self.seed, zlib.crc32(xy[b].tobytes())])
-            pq = None
-            if synth:
+            pq, hide = None, self.same_fmt
+            if dense is not None:
+                xy[b] = self._filler(rng, T1)
+                pq, hide = dense.fill_row(xy[b], rng, *pack), True
+            elif synth:
                 xy[b] = self._filler(rng, T1)
                 pq = self._needle(xy[b], rng, exact, level_range)
             elif rng.random() < p:
@@ -213,9 +254,10 @@ class Reminders:
                     pq = self._needle(xy[b], rng, ex, None if ex is not None else level_range)
             if pq is not None:
                 rem[b, pq] = 1
-                if self.blank:                           # "the answers are seen only after the test"
+                if self.blank:
                     rem_y[b, pq] = xy[b, pq + 1]
-                    xy[b, pq + 1] = self.mark
+                    if hide:
+                        xy[b, pq + 1] = self.mark
         out = {"rem": rem}
         if self.blank:
             out["rem_y"] = rem_y

@@ -614,7 +614,8 @@ class MemArchLM(nn.Module):
         best, j = lo[:, :K].max(-1)
         return (best - lse).exp(), self.sv_ids[j]
 
-    def _ce_part(self, hn, y, j):
+    def _nll_tok(self, hn, y, j):
+        """Per-token -log P(y) of positions j.. of the rows (pointer mixture and tongue included)."""
         c = self.cfg
         mix = self._mix
         tongue = self._tongue if mix is None else None
@@ -638,13 +639,126 @@ class MemArchLM(nn.Module):
             c1, g = mix
             c1, g = c1[:, j:j + T_], g[:, j:j + T_]
             py = (ly - lse).exp()
-            return -torch.log(((1 - g) * py + g * (c1 == y).float()).clamp(min=1e-30)).sum()
-        return (lse - ly).sum()
+            return -torch.log(((1 - g) * py + g * (c1 == y).float()).clamp(min=1e-30))
+        return lse - ly
 
-    def train_loss(self, out, y, train=True):
+    def _ce_part(self, hn, y, j):
+        return self._nll_tok(hn, y, j).sum()
+
+    def _ce_kept(self, hn, y, keep, j):
+        return (self._nll_tok(hn, y, j) * keep).sum()
+
+    # ------------------------------------------------------------------------------------------ recall needles
+    def _logp_rows(self, h, tok, add=None):
+        """log P(tok[:, j]) under the output distribution at the states h (N,D), for every column j of tok (N,J)."""
+        if self.short_v:
+            return torch.stack([self._short_logp(h, tok[:, j]) for j in range(tok.shape[1])], 1)
+        lo = self._logits(h[None])[0]
+        if add is not None:
+            lo = lo.scatter_add(-1, add[0].long(), add[1].float())
+        return lo.log_softmax(-1).gather(1, tok)
+
+    def remind_term(self, hn, y, extra):
+        """Loss on the answers of recall needles (memarch_jax/memarch_jax/model.py:455-531 of the reference's JAX
+        port).  `extra["rem"]` (B,T) marks the question keys, whose target is the value; the first `remind_cap`
+        answers of a row are read (static shape, no host sync).  Sum of the answers' -log P over B * remind_q, or
+        their mean with `remind_mean`.  `remind_cand`: the softmax runs over the 64 value tokens only, so the common
+        part of their head rows gets no gradient.  `remind_strict` (with `extra["rem_vals"]`, the values of the row's
+        facts): answers after the first wrong one of a row earn nothing (they could be had by elimination), and
+        probability put on the row's other values is penalised.  Returns (term, statistics)."""
+        c = self.cfg
+        rem = extra["rem"] > 0
+        B, T = y.shape
+        Q = min(T, c.remind_cap or c.remind_q)
+        order = rem.float() * (T - torch.arange(T, device=y.device, dtype=torch.float32))
+        pos = order.topk(Q, 1).indices                                    # the first Q answers of each row, in order
+        av = rem.gather(1, pos).float()
+        h = hn.gather(1, pos[..., None].expand(B, Q, hn.shape[-1])).reshape(B * Q, -1)
+        yq = y.gather(1, pos)
+        v0 = c.remind_tok0 + 512
+        vals = extra.get("rem_vals") if c.remind_strict else None
+        tok = yq.reshape(-1, 1)
+        if vals is not None:
+            vals = vals.long()
+            tok = torch.cat([tok, vals.clamp(min=0)[:, None, :].expand(B, Q, vals.shape[1]).reshape(B * Q, -1)], 1)
+        add = None
+        if self._mix is None and self._tongue is not None:
+            add = tuple(t.gather(1, pos[..., None].expand(B, Q, t.shape[-1])).reshape(B * Q, -1) for t in self._tongue)
+        rows = 2048
+
+        def logp_of(h_, tok_, *add_):
+            return self._logp_rows(h_, tok_, add_ or None)
+
+        parts = []
+        for r0 in range(0, B * Q, rows):
+            a = (h[r0:r0 + rows], tok[r0:r0 + rows]) + (tuple(t[r0:r0 + rows] for t in add) if add else ())
+            if B * Q > rows and torch.is_grad_enabled() and h.requires_grad:
+                parts.append(checkpoint(logp_of, *a, use_reentrant=False))
+            else:
+                parts.append(logp_of(*a))
+        logp = torch.cat(parts).float()                                   # (B*Q, 1 + n)
+        if c.remind_cand:
+            ids = torch.arange(v0, v0 + 64, device=y.device)
+            lv = ops.linear(h[None], self.head.weight[ids])[0].float()
+            if hasattr(self, "head_bias"):
+                lv = lv + self.head_bias[ids].float()
+            py = lv.log_softmax(-1).gather(1, (yq.reshape(-1, 1) - v0).clamp(0, 63))[:, 0].exp().view(B, Q)
+        else:
+            py = logp[:, 0].exp().view(B, Q)
+        if self._mix is not None:
+            c1, g = (t.gather(1, pos) for t in self._mix)
+            py = (1 - g) * py + g * (c1 == yq).float()
+        nll = -torch.log(py.clamp(min=1e-30))
+        hit = (py > 0.5).float().detach()                                 # p(answer) > 0.5: the argmax is right
+        den = float(B * c.remind_q)
+        st = {"remind_hit": (hit * av).sum() / den, "remind_n": av.sum() / den}
+        if c.remind_mean or c.remind_strict:                              # accuracy by question number within the row
+            qn = av.cumsum(1) * av
+            for k in range(1, 5):
+                st[f"remind_hit_q{k}"] = (hit * (qn == k)).sum() / den
+                st[f"remind_n_q{k}"] = (qn == k).float().sum() / den
+        counted = av
+        pen = None
+        if vals is not None:
+            wrong = av * (1.0 - hit)
+            counted = av * ((wrong.cumsum(1) - wrong) < 0.5).float()
+            st["remind_strict_keep"] = counted.sum() / av.sum().clamp(min=1.0)
+            other = ((vals >= 0)[:, None, :] & (vals[:, None, :] != yq[..., None])).float()
+            p_other = (logp[:, 1:].exp().view(B, Q, -1) * other).sum(-1)
+            pen = (-torch.log((1.0 - p_other).clamp(min=1e-6)) * av).sum() / av.sum().clamp(min=1.0)
+            st["remind_strict_pen"] = pen.detach()
+            st["remind_strict_pother"] = ((p_other * av).sum() / av.sum().clamp(min=1.0)).detach()
+        term = (nll * counted).sum() / den
+        st["remind_nll"] = ((nll * av).sum() / den).detach()
+        if c.remind_mean:
+            term = term * (den / counted.sum().clamp(min=1.0))
+        if pen is not None:
+            term = term + c.remind_strict_w * pen
+        return term, {k: v.detach() for k, v in st.items()}
+
+
+    def train_loss(self, out, y, train=True, extra=None):
+        """`extra`: what the data pipeline knows about recall needles in this batch - "rem" (B,T) marks the question
+        keys, "rem_y" the true values where the text shows a blank, "rem_vals" the values of each row's facts."""
         c = self.cfg
         hn, lh = out
-        if train and self.training and self.panic:
+        rem = extra.get("rem") if isinstance(extra, dict) else None
+        if rem is not None and "rem_y" in extra:          # the answer is not in the text, only in the target
+            y = torch.where(rem > 0, extra["rem_y"].to(y.dtype), y)
+        if rem is not None and c.remind_mask_main:
+            # in rows with needles the needle tokens (random keys, values, marker) do not teach the main loss: a full
+            # softmax on them lifts the whole group of tokens everywhere in the text (model.py:437-446)
+            k0 = c.remind_tok0
+            keep = (~((y >= k0) & (y <= k0 + 576) & (rem > 0).any(1, keepdim=True))).float()
+            self.stats["remind_main_masked"] = 1.0 - keep.mean()
+            loss = 0
+            for j in range(0, hn.shape[1], 8192):
+                part = (hn[:, j:j + 8192], y[:, j:j + 8192], keep[:, j:j + 8192])
+                if self.training and torch.is_grad_enabled():
+                    loss = loss + checkpoint(self._ce_kept, *part, j, use_reentrant=False)
+                else:
+                    loss = loss + self._ce_kept(*part, j)
+        elif train and self.training and self.panic:
             loss = 0
             for j in range(0, hn.shape[1], 8192):
                 ce = checkpoint(self._ce_tok, hn[:, j:j + 8192], y[:, j:j + 8192], use_reentrant=False)
@@ -660,7 +774,14 @@ class MemArchLM(nn.Module):
                     loss = loss + checkpoint(self._ce_part, *part, j, use_reentrant=False)
                 else:
                     loss = loss + self._ce_part(*part, j)
-        loss = loss / y.numel()
+        loss = main = loss / y.numel()
+        if rem is not None and (c.remind_w > 0 or not train):
+            term, st = self.remind_term(hn, y, extra)
+            self.stats.update(st)
+            if train:
+                loss = loss + c.remind_w * term
+                if c.remind_only:                         # stage one: the answers only (auxiliary terms stay)
+                    loss = loss - main
         if train and self.moe:
             loss = loss + 0.01 * sum(b.aux for b in self.heavy) / len(self.heavy)
         if train and len(self.light_a) and hasattr(self.light_a[0], "moe"):

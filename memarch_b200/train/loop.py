@@ -213,6 +213,16 @@ class _CorpusData:
         if float(env.get("REMIND_P", 0) or 0) > 0:
             from ..data.reminders import Reminders
             lad = [int(v) for v in env["REMIND_LADDER"].split(",")] if env.get("REMIND_LADDER") else None
+            floats = lambda k: [float(v) for v in env[k].split(",")] if env.get(k) else None
+            pack = None
+            if env.get("REMIND_PACK") == "1":        # stage one as short episode rows with their own curriculum
+                pack = dict(gap=int(env.get("REMIND_PACK_GAP", 0)), round_to=int(env.get("REMIND_PACK_ROUND", 1)),
+                            rows_mult=int(env.get("REMIND_PACK_MULT", 1)), frac=floats("REMIND_PACK_FRAC"),
+                            win_ref=int(env["REMIND_WIN_REF"]) if env.get("REMIND_WIN_REF") else None,
+                            tail=env.get("REMIND_TAIL") == "1", strict=env.get("REMIND_STRICT") == "1",
+                            far_frac=float(env["REMIND_FAR_FRAC"]) if env.get("REMIND_FAR_FRAC") else None,
+                            far_win=int(env.get("REMIND_FAR_WIN", 2048)))
+            mix = (floats("REMIND_MIX"), int(env.get("REMIND_MIX_LEN", 250))) if env.get("REMIND_MIX") else None
             self.remind = Reminders(float(env["REMIND_P"]), seq, n=int(env.get("REMIND_N", 16)),
                                     dist=int(env.get("REMIND_DIST", min(2048, seq // 4))), seed=int(env.get("CORPUS_SEED", 0)),
                                     tok0=int(env.get("REMIND_TOK0", 1000)), V=int(env["VOCAB"]) if env.get("VOCAB") else None,
@@ -222,8 +232,10 @@ class _CorpusData:
                                     lag=int(env.get("REMIND_LAG", 5)), doc_eos=self.corpus.eos,
                                     dmin=int(env.get("REMIND_DMIN", 0)), synth=int(env.get("REMIND_SYNTH", 0)),
                                     near=float(env.get("REMIND_NEAR", 0.0)), near_max=int(env.get("REMIND_NEAR_MAX", 0)),
-                                    per_row=int(env.get("REMIND_PER_ROW", 1)),   # hidden answers need separate targets: not here
-                                    far_log=float(env["REMIND_FAR_LOG"]) if env.get("REMIND_FAR_LOG") else None)
+                                    per_row=int(env.get("REMIND_PER_ROW", 1)),
+                                    far_log=float(env["REMIND_FAR_LOG"]) if env.get("REMIND_FAR_LOG") else None,
+                                    blank=env.get("REMIND_BLANK") == "1", same_fmt=env.get("REMIND_SAME_FMT") == "1",
+                                    pack=pack, mix=mix)
 
     def _xform(self, xy, n):
         return self.remind(xy, n=n)
@@ -423,7 +435,11 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     td = time.time()
                     xy_b = data.batch(args.batch * (args.seq // seq), seq)
                     ts = time.time()
-                    loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1)
+                    npreps = None
+                    if (rb is None and getattr(data, "remind", None) is not None and data.extra is not None
+                            and getattr(getattr(tr.model, "cfg", None), "remind_w", 0) > 0):
+                        npreps = needle_preps(tr.model, xy_b, data.extra, tr.cfg.micro or len(xy_b))
+                    loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1, npreps)
                     phase["data"] += ts - td
                     phase["enqueue"] += time.time() - ts
                     phase["n"] += 1
@@ -470,7 +486,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     sets = run_evals()
                     rm = getattr(data, "remind", None)
                     if rm is not None and data.extra is not None and data.extra["rem"].any():
-                        hits, n_ans = needle_hits(tr.model, xy_b, torch.from_numpy(data.extra["rem"]).to(tr.device) > 0)
+                        hits, n_ans = needle_hits(tr.model, xy_b, torch.from_numpy(data.extra["rem"]).to(tr.device) > 0,
+                                                  data.extra.get("rem_y"))
                         sets["needles"] = hits / max(n_ans, 1.0)
                         msg = rm.observe(data.loader.n_done - 1, hits, n_ans)
                         if msg:
@@ -516,14 +533,34 @@ def train(args, device=None, env=None, out=None, parallel=None):
     return logs
 
 
+def needle_preps(model, xy, extra, micro):
+    """One `prep` dict per micro-batch that carries the needle masks of the data pipeline as device tensors under
+    "remind" (the model's loss reads them).  Where the model has induction locks they are switched off at the question
+    positions: the lock "last earlier occurrence of this word -> the word after it" would hand over the answer
+    without any memory (memarch_jax/memarch_jax/data.py:333-341 of the reference)."""
+    ex = {k: torch.from_numpy(np.ascontiguousarray(v)).to(xy.device, non_blocking=True) for k, v in extra.items()}
+    out = []
+    for i0 in range(0, len(xy), micro):
+        sl = {k: v[i0:i0 + micro] for k, v in ex.items()}
+        pr = model.prep(xy[i0:i0 + micro, :-1]) if hasattr(model, "ind_a") and hasattr(model, "prep") else {}
+        if "ind_on" in pr:
+            pr["ind_on"] = pr["ind_on"] & ~(sl["rem"] > 0)[..., None]
+        pr["remind"] = sl
+        out.append(pr)
+    return out
+
+
 @torch.no_grad()
-def needle_hits(model, xy, rem):
+def needle_hits(model, xy, rem, rem_y=None):
     """(hits, answers) on the marked question positions of a training batch: an answer counts when the value gets more
-    than half of the probability (it is then certainly the arg-max).  One extra forward without gradient."""
+    than half of the probability (it is then certainly the arg-max).  One extra forward without gradient.  `rem_y`:
+    the true values where the text shows a blank."""
     was = model.training
     model.eval()
     out, _ = model(xy[:, :-1])
     y = xy[:, 1:]
+    if rem_y is not None:
+        y = torch.where(rem, torch.as_tensor(rem_y).to(y), y)
     if hasattr(model, "_ce_tok"):
         ce = model._ce_tok(out[0], y).float().view_as(y)
     else:

@@ -123,7 +123,8 @@ class Trainer:
         m = self.model
         x_in, y_t = xy[:, :-1], xy[:, 1:]
         out, cost = m(x_in, prep) if prep is not None else m(x_in)
-        loss = m.train_loss(out, y_t, True)
+        needles = prep.get("remind") if isinstance(prep, dict) else None
+        loss = m.train_loss(out, y_t, True, extra=needles) if needles is not None else m.train_loss(out, y_t, True)
         return loss + self.cfg.read_cost * cost.float()
 
     def set_lr(self, step, mul=1.0):

@@ -1,6 +1,7 @@
 """Recall needles in real text (schedule, ladder curriculum, determinism), the per-kind corpus, and the
 single-process stand-in for torch.distributed."""
 import json
+import os
 
 import numpy as np
 import pytest
@@ -100,14 +101,19 @@ def test_ladder_levels_follow_success_with_a_lag_and_survive_resume():
     assert all(check_needle(near, out[b], e["rem"][b]) <= 8 for b in range(6))
     hits, n_ans = Reminders.score(out[:, 1:], out, e["rem"])              # a perfect predictor
     assert hits == n_ans == 24
-    hidden = Reminders(1.0, T=1024, n=4, dist=256, blank=True)
-    plain = Reminders(1.0, T=1024, n=4, dist=256)
+    hidden = Reminders(1.0, T=1024, n=4, dist=256, blank=True, same_fmt=True)
+    plain = Reminders(1.0, T=1024, n=4, dist=256, same_fmt=True)
     oh, eh = hidden(xy)
     op, ep = plain(xy)
     assert np.array_equal(eh["rem"], ep["rem"])
     m = ep["rem"] > 0
     assert (oh[:, 1:][m] == hidden.mark).all() and np.array_equal(eh["rem_y"][m], op[:, 1:][m])   # answers only in rem_y
     assert (eh["rem_y"][~m] == 0).all() and np.array_equal(np.where(m, 0, oh[:, 1:]), np.where(m, 0, op[:, 1:]))
+    assert not (op == plain.mark).any()                                   # the marker-free format
+    seen = Reminders(1.0, T=1024, n=4, dist=256, blank=True)              # with markers the answers stay in the text
+    os_, es = seen(xy)
+    ms = es["rem"] > 0
+    assert np.array_equal(es["rem_y"][ms], os_[:, 1:][ms]) and (os_[:, 1:][ms] != seen.mark).all()
 
 
 def test_kind_corpus_schedule_pools_and_resume(tmp_path):
@@ -236,3 +242,133 @@ def test_several_marker_free_needles_per_row():
         assert len(pos) == 4
         first_fact = min(int(np.flatnonzero(o1[b, :p_] == o1[b, p_])[0]) for p_ in pos)
         assert pos[0] - (first_fact + 8) >= 64                       # far needles keep the minimum distance
+
+
+def test_episode_stage_curriculum_and_rows():
+    r = Reminders(1.0, T=1024, n=16, dist=64, seed=5, V=30000, synth=40, thr=0.9, win=50, lag=3, blank=True,
+                  pack=dict(round_to=64, rows_mult=2, strict=True), mix=([0.75, 0.25], 10))
+    ep = r.pack
+    assert ep.steps[:4] == [(4, 16), (8, 16), (16, 16), (4, 32)] and ep.steps[-1][0] == 16
+    assert all(4 * 16 + f <= 1025 for _, f in ep.steps)
+    shape = (4, 1025)
+    xy, ex = r(np.zeros(shape, np.int32), n=0)
+    pairs, fill = ep.shape_at(0)
+    assert (pairs, fill) == (4, 64 + 1 - 16) and xy.shape == (4 * 1024 // 64, 65) and xy.shape[0] % 2 == 0
+    assert set(ex) == {"rem", "rem_vals", "rem_y"} and ex["rem"].shape == (64, 64)
+    for row, rem, vals, y in zip(xy, ex["rem"], ex["rem_vals"], ex["rem_y"]):
+        facts = dict(zip(row[0:2 * pairs:2], row[1:2 * pairs:2]))
+        q = np.nonzero(rem)[0]
+        assert len(q) == pairs and len(facts) == pairs and q[0] == 2 * pairs + fill
+        assert [facts[k] for k in row[q]] == list(y[q]) and (row[q + 1] == r.mark).all()          # hidden answers
+        assert list(vals[:pairs]) == list(row[1:2 * pairs:2]) and (vals[pairs:] == -1).all()
+        mid = row[2 * pairs:2 * pairs + fill]
+        assert ((mid < r.k0) | (mid > r.mark)).all()
+    again, _ = r(np.ones(shape, np.int32), n=0)
+    assert np.array_equal(xy, again)                                      # a function of the batch number only
+    # the curriculum moves on success, `lag` batches later, and survives a checkpoint
+    assert r.observe(0, 10, 60) is None                                   # accuracy too low: the window restarts
+    msg = r.observe(1, 60, 60)
+    assert "step 0 -> 1" in msg and ep.step_at(3) == 0 and ep.step_at(4) == 1
+    assert r(np.zeros(shape, np.int32), n=4)[0].shape[1] == 64 + 1 and ep.shape_at(4)[0] == 8
+    r2 = Reminders(1.0, T=1024, n=16, dist=64, seed=5, V=30000, synth=40, thr=0.9, win=50, lag=3, blank=True,
+                   pack=dict(round_to=64, rows_mult=2, strict=True))
+    r2.load(r.state())
+    assert r2.pack.changes == ep.changes and np.array_equal(r2(np.zeros(shape, np.int32), n=4)[0],
+                                                            r(np.zeros(shape, np.int32), n=4)[0])
+    # last step: the fill of every batch is drawn from all lengths
+    ep.changes.append((20, len(ep.steps) - 1))
+    assert len({ep.shape_at(i)[1] for i in range(20, 40)}) > 2
+    # after the stage a decaying share of the batches stays synthetic
+    share = lambda lo, hi: np.mean([r.synth_at(i) for i in range(lo, hi)])
+    assert share(0, 40) == 1.0 and share(40, 50) > share(50, 60) > 0 and abs(share(1000, 1400) - 0.25) < 0.03
+    assert not Reminders(1.0, T=1024, n=16, dist=64, synth=40).synth_at(40)
+    # with `tail` the fill stays nominal and the padding follows the questions
+    t = Reminders(1.0, T=1024, n=16, dist=64, seed=5, V=30000, synth=40, pack=dict(round_to=64, tail=True))
+    xt, et = t(np.zeros(shape, np.int32), n=0)
+    assert t.pack.shape_at(0) == (4, 16) and xt.shape[1] == 65 and np.nonzero(et["rem"][0])[0][0] == 8 + 16
+    with pytest.raises(ValueError):
+        Reminders(1.0, T=1024, n=16, dist=64, pack=dict(frac=[0.5]))
+
+
+def test_dense_episode_rows_for_evaluation():
+    r = Reminders(1.0, T=2048, n=8, dist=64, seed=2, V=30000, pack=dict(gap=3))
+    xy = np.random.default_rng(0).integers(0, 900, (3, 2049)).astype(np.int32)
+    out, ex = r(xy, synth=True, pack=(4, 32))
+    for row, rem in zip(out, ex["rem"]):
+        q = np.nonzero(rem)[0]
+        assert len(q) == 4 * ((2049 + 3) // (48 + 3))
+        keys = row[q]
+        assert len(set(keys)) == len(keys)                                 # no key twice in a row
+        for e0 in q[::4]:                                                  # every episode: facts, 32 words, questions
+            b0 = e0 - 32 - 8
+            facts = dict(zip(row[b0:b0 + 8:2], row[b0 + 1:b0 + 8:2]))
+            assert [facts[k] for k in row[e0:e0 + 8:2]] == list(row[e0 + 1:e0 + 8:2])
+            if b0 >= 3:
+                assert (row[b0 - 3:b0] == r.mark).all()
+
+
+def _reference_data():
+    import importlib.util
+    root = os.environ.get("MEMARCH_REF_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                                          "baseline", "_ref"))
+    path = os.path.join(root, "memarch_jax", "memarch_jax", "data.py")
+    if not os.path.exists(path):
+        pytest.skip("reference tree not present")
+    spec = importlib.util.spec_from_file_location("reference_data", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("kw,attrs", [
+    ({}, {}),
+    ({"ladder": [32, 128, 512], "dmin": 4}, {}),
+    ({"synth": 3, "doc_eos": 7}, {}),
+    ({"near": 0.5, "near_max": 8, "p0": 1.0, "warm": 2, "decay": 4}, {}),
+    ({"blank": True}, {}),
+    ({"blank": True}, {"same_fmt": True}),
+    ({"blank": True, "near": 0.3, "near_max": 16}, {"same_fmt": True, "per_row": 3}),
+    ({}, {"far_log": 1.0}),
+    ({"synth": 6, "pack": True}, {}),
+    ({"synth": 6, "pack": True, "blank": True, "strict": True, "pack_round": 64, "pack_mult": 2}, {}),
+    ({"synth": 6, "pack": True, "tail": True, "pack_round": 128}, {}),
+    ({"synth": 6, "pack": True, "pack_round": 64, "pack_frac": [0.05, 0.1, 0.25, 0.5, 1.0], "win_ref": 512}, {}),
+    ({"synth": 6, "pack": True}, {"far_frac": 0.7, "far_win": 100, "mix_fracs": [0.9, 0.5], "mix_len": 3}),
+])
+def test_same_batches_as_the_reference(kw, attrs):
+    """Needles, masks, schedules and curriculum steps equal the reference's host-side injector bit for bit."""
+    ref = _reference_data()
+    a = ref.Reminders(0.7, 1024, n=8, dist=64, seed=3, V=30000, thr=0.5, win=20, lag=2, **kw)
+    for k, v in attrs.items():
+        setattr(a, k, v)
+    ours = {k: v for k, v in kw.items() if k not in ("pack", "strict", "tail", "pack_round", "pack_mult", "pack_frac",
+                                                     "win_ref")}
+    if kw.get("pack"):
+        ours["pack"] = dict(strict=kw.get("strict", False), tail=kw.get("tail", False), round_to=kw.get("pack_round", 1),
+                            rows_mult=kw.get("pack_mult", 1), frac=kw.get("pack_frac"), win_ref=kw.get("win_ref"),
+                            far_frac=attrs.get("far_frac"), far_win=attrs.get("far_win", 2048))
+    if "mix_fracs" in attrs:
+        ours["mix"] = (attrs["mix_fracs"], attrs["mix_len"])
+    ours.update({k: v for k, v in attrs.items() if k in ("same_fmt", "per_row", "far_log")})
+    b = Reminders(0.7, 1024, n=8, dist=64, seed=3, V=30000, thr=0.5, win=20, lag=2, **ours)
+    if kw.get("pack"):
+        assert b.pack.steps == a.plevels
+    g = np.random.default_rng(1)
+    for n in range(14):
+        xy = g.integers(0, 5000, (4, 1025)).astype(np.int32)
+        xa, ea = a(xy, n=n)
+        xb, eb = b(xy, n=n)
+        assert a.synth_at(n) == b.synth_at(n)
+        assert xa.shape == xb.shape and np.array_equal(xa, xb), n
+        assert set(ea) == set(eb) and all(np.array_equal(ea[k], eb[k]) for k in ea), n
+        hits = float(ea["rem"].sum()) * (0.9 if n % 3 else 0.2)
+        assert (a.observe(n, hits, float(ea["rem"].sum())) is None) == (b.observe(n, hits, float(eb["rem"].sum())) is None)
+        if kw.get("pack") and a.synth_at(n):
+            assert a.pack_fill_at(n) == b.pack.shape_at(n)
+    sa, sb = a.state(), b.state()
+    assert sa == sb
+    xy = g.integers(0, 5000, (2, 1025)).astype(np.int32)
+    for call in (dict(exact=100), dict(p=1.0), dict(synth=True, pack=(4, 40))):
+        xa, ea = a(xy, **call)
+        xb, eb = b(xy, **call)
+        assert np.array_equal(xa, xb) and all(np.array_equal(ea[k], eb[k]) for k in ea), call

@@ -3,6 +3,7 @@ train/speed loops, CLI."""
 import io
 import json
 import os
+import math
 import signal
 import subprocess
 import sys
@@ -11,6 +12,7 @@ import time
 import numpy as np
 import pytest
 import torch
+import torch.nn.functional as F
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -643,3 +645,117 @@ def test_trainer_with_the_experience_card_optimizer_learns():
     losses = [float(tr.step(xy, s)) for s in range(8)]
     assert losses[-1] < losses[0] - 0.2, losses
     assert any(tr.opt.used) and tr.opt.last["card"] == 0
+
+
+def _needle_model(**env):
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    e = {"NO_MEM": "1", "MOE_ACT": "relu2", "REMIND_W": "1.0", "REMIND_N": "4", "REMIND_TOK0": "1000"}
+    e.update(env)
+    return build("tiny", 2048, env=e).train()
+
+
+def _needle_batch(blank=False, strict=False, B=6, T=64, n=4):
+    from memarch_b200.data.reminders import Reminders
+    r = Reminders(1.0, T=T, n=n, dist=8, seed=1, V=2048, tok0=1000, synth=10 ** 6, blank=blank,
+                  pack=dict(strict=strict, round_to=T))
+    xy, ex = r(np.zeros((B, T + 1), np.int32), n=0)
+    return torch.from_numpy(xy).long(), {k: torch.from_numpy(v) for k, v in ex.items()}
+
+
+def test_answer_loss_of_recall_needles():
+    xy, ex = _needle_batch()
+    x, y = xy[:, :-1], xy[:, 1:]
+    rem = ex["rem"] > 0
+    m = _needle_model()
+    out, _ = m(x)
+    plain = m.train_loss(out, y, True)
+    with_term = m.train_loss(out, y, True, extra=ex)
+    lo = m._logits(out[0]).float()
+    nll = F.cross_entropy(lo.reshape(-1, lo.shape[-1]), y.reshape(-1), reduction="none").view_as(y)
+    want = (nll * rem).sum() / (len(y) * 4)                                # sum over answers / (B * questions per row)
+    assert abs(float(with_term - plain) - float(want)) < 1e-4
+    assert abs(float(m.stats["remind_nll"]) - float(want)) < 1e-4 and abs(float(m.stats["remind_n"]) - 1.0) < 1e-6
+    hits = ((nll < math.log(2.0)) & rem).sum() / (len(y) * 4)
+    assert abs(float(m.stats["remind_hit"]) - float(hits)) < 1e-6
+    # mean over the answers instead, the answers only (auxiliary terms stay), a softmax over the values only
+    mean = _needle_model(REMIND_MEAN="1")
+    mean.load_state_dict(m.state_dict())
+    out2, _ = mean(x)
+    d = mean.train_loss(out2, y, True, extra=ex) - mean.train_loss(out2, y, True)
+    assert abs(float(d) - float((nll * rem).sum() / rem.sum())) < 1e-4 and "remind_hit_q2" in mean.stats
+    only = _needle_model(REMIND_ONLY="1")
+    only.load_state_dict(m.state_dict())
+    out3, _ = only(x)
+    main = float(nll.mean())
+    assert abs(float(only.train_loss(out3, y, True, extra=ex)) - (float(with_term) - main)) < 1e-4
+    cand = _needle_model(REMIND_CAND="1")
+    cand.load_state_dict(m.state_dict())
+    out4, _ = cand(x)
+    d = cand.train_loss(out4, y, True, extra=ex) - cand.train_loss(out4, y, True)
+    lv = lo[..., 1512:1576].log_softmax(-1).gather(-1, (y - 1512).clamp(0, 63)[..., None])[..., 0]
+    assert abs(float(d) - float((-lv * rem).sum() / (len(y) * 4))) < 1e-4
+    loss = cand.train_loss(out4, y, True, extra=ex)
+    loss.backward()
+    g = cand.head.weight.grad
+    assert g is not None and torch.isfinite(g).all()
+    # needle tokens do not teach the main loss
+    mm = _needle_model(REMIND_MASK_MAIN="1", REMIND_W="0.0")
+    mm.load_state_dict(m.state_dict())
+    out5, _ = mm(x)
+    keep = ~((y >= 1000) & (y <= 1576))
+    base = _needle_model(REMIND_W="0.0")
+    base.load_state_dict(m.state_dict())
+    aux = float(base.train_loss(base(x)[0], y, True)) - main
+    assert abs(float(mm.train_loss(out5, y, True, extra=ex)) - aux - float((nll * keep).sum() / y.numel())) < 1e-4
+    assert 0 < float(mm.stats["remind_main_masked"]) < 1
+
+
+def test_hidden_answers_and_the_strict_test():
+    xy, ex = _needle_batch(blank=True, strict=True)
+    x, y = xy[:, :-1], xy[:, 1:]
+    rem = ex["rem"] > 0
+    assert (y[rem] == 1000 + 576).all()                                    # the text shows the marker
+    m = _needle_model(REMIND_STRICT="1", REMIND_STRICT_W="0.5")
+    out, _ = m(x)
+    total = m.train_loss(out, y, True, extra=ex)
+    base = m.train_loss(out, torch.where(rem, ex["rem_y"].long(), y), True)  # main and auxiliaries on the true targets
+    lo = m._logits(out[0]).float()
+    lsm = lo.log_softmax(-1)
+    yt = torch.where(rem, ex["rem_y"].long(), y)
+    nll = -lsm.gather(-1, yt[..., None])[..., 0]
+    hit = nll < math.log(2.0)
+    term, pen, n_ans = 0.0, 0.0, 0
+    for b in range(len(y)):
+        ok = True
+        vals = ex["rem_vals"][b]
+        vals = vals[vals >= 0].long()
+        for t in torch.nonzero(rem[b])[:, 0]:
+            if ok:
+                term += float(nll[b, t])
+            ok = ok and bool(hit[b, t])
+            others = vals[vals != yt[b, t]]
+            pen += -math.log(max(1.0 - float(lsm[b, t, others].exp().sum()), 1e-6))
+            n_ans += 1
+    want = term / (len(y) * 4) + 0.5 * pen / n_ans
+    assert abs(float(total - base) - want) < 1e-3
+    assert 0 < float(m.stats["remind_strict_keep"]) <= 1 and float(m.stats["remind_strict_pother"]) > 0
+    total.backward()
+    assert torch.isfinite(m.head.weight.grad).all()
+
+
+def test_episode_stage_trains_through_the_loop(tmp_path, monkeypatch):
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    w = make_corpus(str(tmp_path / "corpus"), docs=60)
+    env = {"VOCAB": "2048", "NO_MEM": "1", "WATCHDOG": "0", "CORPUS": json.dumps(w), "CORPUS_ROOT": str(tmp_path / "corpus"),
+           "REMIND_P": "1.0", "REMIND_N": "4", "REMIND_DIST": "4", "REMIND_TOK0": "1000", "REMIND_SYNTH": "4",
+           "REMIND_PACK": "1", "REMIND_PACK_ROUND": "16", "REMIND_BLANK": "1", "REMIND_WIN": "4", "REMIND_THR": "0.0",
+           "REMIND_LAG": "1", "REMIND_W": "1.0", "REMIND_MEAN": "1", "REMIND_ONLY": "1", "INDUCT": "lock",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
+    a = Args(seq=64, batch=4, micro=4, steps=6, eval_every=1)
+    buf = io.StringIO()
+    log = train(a, "cpu", env=env, out=buf)["tiny"]
+    text = buf.getvalue()
+    assert "episodes: step 0 -> 1" in text and "remind_hit" in text         # short rows, then text rows, one run
+    assert all(math.isfinite(e["val"]) for e in log) and "needles" in log[-1]["sets"]

@@ -157,6 +157,9 @@ class OptConfig:
     wd_norm: float = 0.0          # >0: decoupled weight decay towards zero for the 1-D norm weights (norm, l_norm, *.n1, *.n2)
     norm_anchor: bool = False     # 1-D norm weights of the light / final blocks are pulled towards 1: w -= lr wd (w - 1)
     lr_mul: tuple = ()            # ((name prefix, multiplier), ...): step multiplier of the weights under a prefix
+    culprit: str = "abs"          # "abs": the tensors with the largest |g|/|w| are blamed; "ema": the largest against their own mean
+    g_max: float = 3.0            # ceiling of a gain
+    card_by_kind: bool = False    # the kind of the step (a number given to `prepare`) names the card
     err_step: bool = False        # with damp > 0: every tensor's step x clip(usual |g| / |g| now, 0, err_cap) ("divide by
     err_cap: float = 3.0          #     the sensitivity"); the gradient enters the momentum unclipped
     gearbox: bool = False         # with damp > 0: per-tensor gears (0.25, 0.5, 1, gb_top) shifted one at a time - down when

@@ -61,6 +61,13 @@ class Instinct:
         self.expect = torch.zeros(cfg.cards, device=dev)
         self.seen = torch.zeros(cfg.cards, device=dev)
         self.rel = torch.zeros(P, device=dev)
+        # culprit="ema": a tensor is to blame for a bad step when its |g|/|w| is high against ITS OWN running mean,
+        # not against the other tensors (whose ranking hardly changes, so the same few were blamed at every step)
+        self.culprit, self.g_max, self.card_by_kind = cfg.culprit, cfg.g_max, cfg.card_by_kind
+        if self.culprit not in ("abs", "ema"):
+            raise ValueError(f"culprit must be 'abs' or 'ema', not {cfg.culprit!r}")
+        if self.culprit == "ema":
+            self.rel_avg = torch.zeros(P, device=dev)
         self.m = [torch.zeros_like(p, dtype=self.m_dtype) for p in self.plist]
         # optimizer-state offload (memarch_jax/memarch_jax/dist.py:311-322, step.py:154-155): the momentum of every weight
         # rests in pinned host memory and visits the device only for its own update, on the stream of that update
@@ -101,18 +108,23 @@ class Instinct:
 
     # ------------------------------------------------------------------------------------------ card logic
     @torch.no_grad()
-    def prepare(self, loss, situation):
-        """Pick the situation card, its expectation and the surprise of this step's loss (exp_opt.py:349-372)."""
+    def prepare(self, loss, situation, card=None):
+        """Pick the situation card, its expectation and the surprise of this step's loss (exp_opt.py:349-372).
+        With `card_by_kind` and a `card` number the kind of the step names the card instead of the similarity of the
+        input (memarch_jax/memarch_jax/instinct.py:486-495)."""
         sit = F.normalize(situation.float().flatten(), dim=0)
         if self.keys is None:
             self.keys = torch.zeros(self.K, sit.numel(), device=sit.device)
         self._sync_lr()
         used = self.used
-        best_sim, best = (self.keys @ sit).masked_fill(~used, -2).max(0)
-        free = ~used
-        first_free = free.int().argmax()
-        newer = (best_sim < self.new_card) & free.any()
-        k = torch.where(~used.any(), torch.zeros_like(best), torch.where(newer, first_free, best))
+        if self.card_by_kind and card is not None:
+            k = torch.as_tensor(card, device=sit.device).long().reshape(()).clamp(0, self.K - 1)
+        else:
+            best_sim, best = (self.keys @ sit).masked_fill(~used, -2).max(0)
+            free = ~used
+            first_free = free.int().argmax()
+            newer = (best_sim < self.new_card) & free.any()
+            k = torch.where(~used.any(), torch.zeros_like(best), torch.where(newer, first_free, best))
         oh = F.one_hot(k, self.K).float()
         was = (oh * used).sum() > 0
         key_k = oh @ self.keys
@@ -131,13 +143,20 @@ class Instinct:
     @torch.no_grad()
     def finish(self):
         """The instinct learns: gains of the card move by the outcome of the step (exp_opt.py:375-383)."""
-        self.n_step += 1
         s, gk = self.s, self.g.clone()
-        culprit = (self.rel >= self.rel.quantile(1 - self.top)).float()
+        if self.culprit == "ema":
+            avg = torch.where(self.rel_avg > 0, self.rel_avg, self.rel)      # the first time: no surprise
+            ratio = self.rel / (avg + 1e-12)
+            culprit = (ratio >= ratio.quantile(1 - self.top)).float()
+            fresh = self.n_step % self.rel_every == 0                         # |g|/|w| was measured at this very step
+            self.rel_avg.copy_(0.9 * avg + 0.1 * self.rel if fresh else avg)
+        else:
+            culprit = (self.rel >= self.rel.quantile(1 - self.top)).float()
+        self.n_step += 1
         gk += torch.where(s < 0, culprit * self.bad * (-s * 10).clamp(max=1), torch.zeros_like(gk))
         gk += torch.where(s > 0, self.good * (s * 10).clamp(max=1) * (1 - gk), torch.zeros_like(gk))
         gk += self.relax * (1 - gk)
-        gk = gk.clamp(0.5, 3.0)
+        gk = gk.clamp(0.5, self.g_max)
         self.gain.add_(self.oh[:, None] * (gk / gk.mean() - self.gain))
 
     def _sync_lr(self):

@@ -55,6 +55,7 @@ class Trainer:
         self.params = [p for p in model.parameters() if p.requires_grad]
         st = self.stage
         self.apply_now = False
+        self.card = None                 # kind of the coming step (a number), for `OptConfig.card_by_kind`
         self.acc = {}
         if "X" in st and self.ocfg.kind == "instinct":
             import dataclasses
@@ -225,7 +226,7 @@ class Trainer:
                 sit = self.situation(xy)
                 if self.parallel is not None:
                     tl, sit = self.parallel.sync_control(tl, sit, m)
-                self.opt.prepare(tl, sit)
+                self.opt.prepare(tl, sit, card=self.card)
             if self.parallel is not None:
                 self.parallel.before_backward(self)
             (loss * w).backward()
@@ -277,7 +278,7 @@ class Trainer:
         total = torch.stack(losses).sum()
         self.apply_now = True
         if isinstance(self.opt, Instinct):
-            self.opt.prepare(total.detach(), self.situation(xy))
+            self.opt.prepare(total.detach(), self.situation(xy), card=self.card)
         total.backward()
         self._after_backward(total.detach(), xy)
         return total.detach()

@@ -759,3 +759,45 @@ def test_episode_stage_trains_through_the_loop(tmp_path, monkeypatch):
     text = buf.getvalue()
     assert "episodes: step 0 -> 1" in text and "remind_hit" in text         # short rows, then text rows, one run
     assert all(math.isfinite(e["val"]) for e in log) and "needles" in log[-1]["sets"]
+
+
+def test_instinct_blames_by_own_history_and_cards_by_kind():
+    from memarch_b200 import OptConfig
+    from memarch_b200.optim import Instinct
+    torch.manual_seed(0)
+    ps = [torch.nn.Parameter(torch.randn(8, 8)) for _ in range(10)]
+    cfg = OptConfig(lr=1e-2, norm="hs", scale=0.12, rel_every=2, culprit="ema", top=0.2, g_max=1.5, card_by_kind=True,
+                    cards=4, bad=0.5)
+    opt = Instinct(ps, cfg)
+    sit = torch.randn(16)
+    opt.prepare(torch.tensor(1.0), sit, card=2)
+    assert int(opt.k) == 2 and bool(opt.used[2]) and not bool(opt.used[0])
+    opt.prepare(torch.tensor(1.0), sit, card=9)
+    assert int(opt.k) == 3                                                  # clipped to the last card
+    opt.prepare(torch.tensor(1.0), -sit)                                    # no number: by similarity (a new card)
+    assert int(opt.k) == 0
+    # blame: tensor 7 is far above its own mean although tensors 0, 1 are the largest in absolute terms
+    opt.rel_avg.copy_(torch.tensor([5.0, 4.0] + [1.0] * 8))
+    opt.rel.copy_(torch.tensor([5.0, 4.0, 1, 1, 1, 1, 1, 3.0, 1.2, 1]))
+    opt.s = torch.tensor(-0.2)
+    opt.g = torch.ones(10)
+    opt.oh = F.one_hot(torch.tensor(1), 4).float()
+    opt.n_step = 4
+    opt.finish()
+    row = opt.gain[1]
+    assert row.argmax() == 7 and row[8] > row[0] and abs(float(row[0]) - float(row[1])) < 1e-6
+    assert torch.allclose(opt.rel_avg[7], torch.tensor(0.9 * 1.0 + 0.1 * 3.0)) and opt.n_step == 5
+    before = opt.rel_avg.clone()
+    opt.finish()                                                            # step 5: |g|/|w| not measured, mean stays
+    assert torch.equal(opt.rel_avg, before)
+    opt.g = torch.full((10,), 1.4)
+    opt.s = torch.tensor(-1.0)
+    opt.finish()
+    assert float((opt.gain[1] * 0 + 1).sum()) == 10 and "rel_avg" in opt.state_dict()
+    plain = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, top=0.2))
+    plain.rel.copy_(opt.rel)
+    plain.s, plain.g, plain.oh = torch.tensor(-0.2), torch.ones(10), opt.oh
+    plain.finish()
+    assert plain.gain[1].argmax() in (0, 1) and not hasattr(plain, "rel_avg")
+    with pytest.raises(ValueError):
+        Instinct(ps, OptConfig(culprit="mean"))

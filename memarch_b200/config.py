@@ -72,6 +72,31 @@ class ModelConfig:
     heavy_attn_detach: bool = False
     n_draft: int = 0
     draft_loss: float = 0.0
+    # anchor-routed long-range read ("tether", models/rope_memory.py) in the light blocks after the memory point,
+    # instead of the segment memory and the re-reading (ROPE_MEM=1; sets no_mem)
+    rope_mem: bool = False
+    rope_k: int = 4               # anchors a query opens
+    rope_links: int = 8           # keys that represent an anchor in the search
+    rope_win: int = 64            # local window of the tethered layers
+    rope_span_cap: int = 256
+    rope_route: str = "hier"      # "hier" | "exact"
+    rope_hier_g: int = 64
+    rope_hier_nb: int = 16
+    rope_hier_bm: int = 64
+    rope_excl_win: bool = True
+    rope_rgrad: bool = True
+    rope_chunk: int = 256
+    rope_layers: int = 0          # how many of the first light_b layers are tethered (0: all)
+    rope_share_route: bool = False  # later layers reuse the first layer's choice of anchors
+    rope_tau0: float = 5.0        # initial surprise threshold of the tether's anchors
+    rope_frac: float = 0.0        # share of words that become tether anchors (0: the heavy anchors' share)
+    rope_cap: float = 0.0         # ceiling of tether anchors as a share of T (0: the heavy anchors' ceiling)
+    rope_anchor_top: bool = False  # over the ceiling keep the most surprising anchors, not the first ones
+    rope_qfrac: float = 1.0       # share of words that read the tether at all (the rest: window only)
+    rope_qtau0: float = 5.0
+    rope_doc_eos: int = -1        # >= 0: anchors of another document than the query's are not opened
+    rope_key_diag: bool = False   # statistics: how many needle keys the search can see
+    remind_use_w: float = 0.0     # REMIND_USE_W: penalty mean(1 - tether share) on the needle questions
     # loss on the answers of recall needles (data.reminders); 0 = the batch's "rem" mask is only scored, not trained on
     remind_w: float = 0.0         # REMIND_W: weight of the term (sum of the answers' NLL / (B * remind_q))
     remind_q: int = 16            # questions per needle row (the normaliser)
@@ -249,6 +274,17 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
     if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("ROPE_MEM") == "1":
+        kw["rope_mem"], kw["no_mem"] = True, True
+        for k_, t_ in (("k", int), ("links", int), ("win", int), ("span_cap", int), ("route", str), ("hier_g", int),
+                       ("hier_nb", int), ("hier_bm", int), ("chunk", int), ("layers", int), ("tau0", float),
+                       ("frac", float), ("cap", float), ("qfrac", float), ("qtau0", float), ("doc_eos", int)):
+            if g("ROPE_" + k_.upper()): kw["rope_" + k_] = t_(g("ROPE_" + k_.upper()))
+        for k_ in ("share_route", "anchor_top", "key_diag"):
+            if g("ROPE_" + k_.upper()) == "1": kw["rope_" + k_] = True
+        if g("ROPE_EXCL_WIN") == "0": kw["rope_excl_win"] = False
+        if g("ROPE_RGRAD") == "0": kw["rope_rgrad"] = False
+    if g("REMIND_USE_W"): kw["remind_use_w"] = float(g("REMIND_USE_W"))
     if g("REMIND_W"): kw["remind_w"] = float(g("REMIND_W"))
     if g("REMIND_N"): kw["remind_q"] = int(g("REMIND_N"))
     if g("REMIND_PER_ROW"): kw["remind_cap"] = int(g("REMIND_PER_ROW")) * int(g("REMIND_N") or 16)

@@ -101,9 +101,12 @@ class LightBlock(nn.Module):
     def _act(self, h):
         return ops.relu2(h) if self.relu2 else ops.swiglu(h)
 
-    def forward(self, x, window=None, pending=None, defer=False):
+    def forward(self, x, window=None, pending=None, defer=False, tether=None):
         """`pending`: the previous block's FFN output not yet added to the stream (added here, fused with n1).
-        `defer=True` returns (x, ffn_out) and leaves the last residual add to the next block."""
+        `defer=True` returns (x, ffn_out) and leaves the last residual add to the next block.
+        `tether` = (own, apos, avalid, RopeCfg, routed, qmask, docs): the attention becomes the anchor-routed read of
+        `models.rope_memory` (local window + the spans of the anchors each query opens); what it chose and how much
+        of the softmax mass went there is left in `self.tether_out` = (share, route, mass per position)."""
         B, T, D = x.shape
         hd = D // self.heads
         dt = _cdt(x)
@@ -120,7 +123,20 @@ class LightBlock(nn.Module):
             g = 2 * torch.sigmoid(F.linear(x, self.ve_gate.weight.to(x.dtype)))[..., None]        # (B,T,H,1)
             v = qkv[:, :, 2] + (g * self.cur_ve.view(B, T, self.heads, hd)).to(qkv.dtype)
             qkv = torch.stack([qkv[:, :, 0], qkv[:, :, 1], v], 2)
-        a = ops.attention(qkv, window, self.rope_half, qk_norm="qk" in self.blk)
+        if tether is not None:
+            from ..ops import ref
+            from .rope_memory import rope_attention
+            q, k, v = qkv.permute(2, 0, 3, 1, 4)
+            if "qk" in self.blk:
+                q, k = F.rms_norm(q, (hd,)), F.rms_norm(k, (hd,))
+            cos, sin = ref.rope_angles(T, hd, x.device)
+            q, k = ref.apply_rope(q, cos, sin, self.rope_half), ref.apply_rope(k, cos, sin, self.rope_half)
+            own, apos, avalid, rcfg, routed, qmask, docs = tether
+            a, share, route, mass = rope_attention(q, k, v, own, apos, avalid, rcfg, routed, qmask, docs, want_mass=True)
+            self.tether_out = (share, route, mass)
+            a = a.transpose(1, 2).reshape(B, T, D).to(dt)
+        else:
+            a = ops.attention(qkv, window, self.rope_half, qk_norm="qk" in self.blk)
         fin = (lambda t: (t, None)) if defer else (lambda t: t)
         if hasattr(self, "moe") or self.cur_sel is not None:
             x = ops.resid_add(x, ops.linear(a, self.o.weight))

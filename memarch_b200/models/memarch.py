@@ -116,6 +116,11 @@ class MemArchLM(nn.Module):
         self.norm = nn.RMSNorm(d)
         self.head = nn.Linear(d, vocab, bias=False)
         self.register_buffer("tau", torch.tensor(5.0))
+        if c.rope_mem:
+            self.register_buffer("rope_tau", torch.tensor(float(c.rope_tau0)))
+            if c.rope_qfrac < 1.0:
+                self.register_buffer("rope_qtau", torch.tensor(float(c.rope_qtau0)))
+        self._tether_mass = None
         self.stats = {}
         self.panic = c.panic
         self.short_v = c.short_v
@@ -423,7 +428,10 @@ class MemArchLM(nn.Module):
             h = h + reads.type_as(h)
             self.stats["mem_cards"] = st["valid"].float().sum(1).mean()
 
-        h = run_blocks(self.light_b, h, win, self._run)
+        if c.rope_mem:
+            h = self._tether_pass(h, x, win)
+        else:
+            h = run_blocks(self.light_b, h, win, self._run)
         lh = ops.rmsnorm(h, self.l_norm.weight, self.l_norm.eps)
 
         # surprise -> anchors: the light part's own prediction error decides where to think hard
@@ -477,6 +485,53 @@ class MemArchLM(nn.Module):
         o, cost = self._reread_pass(h, x, snaps, seg)
         h = h + o.type_as(h)
         return (ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt), lh), cost
+
+    def _tether_pass(self, h, x, win):
+        """The light blocks after the memory point with the anchor-routed read instead of plain attention
+        (memarch_jax/memarch_jax/model.py:266-324 of the reference's JAX port).  Anchors are the words that surprise
+        the light head after the first light blocks; the threshold follows the quantile of that surprise (updated
+        first, then used, frozen in evaluation)."""
+        from .rope_memory import RopeCfg, anchors_from_surprise
+        c = self.cfg
+        B, T = x.shape
+        with torch.no_grad():
+            sr = self._light_surprise(ops.rmsnorm(h, self.l_norm.weight, self.l_norm.eps).detach(), x)
+            if self.training:
+                self.rope_tau.mul_(0.9).add_(0.1 * ref.tau_quantile(sr, c.rope_frac or self.frac))
+            A = max(1, round(T * (c.rope_cap or self.cap)))
+            own, apos, avalid = anchors_from_surprise(sr.clone(), self.rope_tau, A, top=c.rope_anchor_top)
+            self.stats["rope_anchors"] = avalid.float().sum(1).mean() / T
+            if c.rope_key_diag:                   # needle keys among the links the search sees / among the anchors
+                is_key = (x >= c.remind_tok0) & (x < c.remind_tok0 + 512)
+                a_of = apos.gather(1, own.clamp(0, apos.shape[1] - 1))
+                t = torch.arange(T, device=x.device)[None]
+                n = is_key.float().sum().clamp(min=1.0)
+                self.stats["rope_key_link"] = (is_key & (own >= 0) & (t - a_of < c.rope_links)).float().sum() / n
+                self.stats["rope_key_anch"] = (is_key & (own >= 0) & (t == a_of)).float().sum() / n
+            docs = (x == c.rope_doc_eos).long().cumsum(1) if c.rope_doc_eos >= 0 else None
+            qmask = None
+            if c.rope_qfrac < 1.0:                # only the surprised words read the tether
+                if self.training:
+                    self.rope_qtau.mul_(0.9).add_(0.1 * ref.tau_quantile(sr, c.rope_qfrac))
+                qmask = sr >= self.rope_qtau
+                self.stats["rope_qfrac_real"] = qmask.float().mean()
+        rcfg = RopeCfg(K=c.rope_k, links=c.rope_links, win=c.rope_win, span_cap=c.rope_span_cap, route=c.rope_route,
+                       G=c.rope_hier_g, NB=c.rope_hier_nb, BM=c.rope_hier_bm, excl_win=c.rope_excl_win, rgrad=c.rope_rgrad,
+                       chunk=c.rope_chunk, mgrad=c.remind_use_w > 0)
+        pending, routed, masses = None, None, []
+        for bi, b in enumerate(self.light_b):
+            if c.rope_layers and bi >= c.rope_layers:
+                h, pending = self._run(b, h, win, pending, True)
+                continue
+            # the read recomputes its own chunks, so the block is not wrapped in another checkpoint
+            h, pending = b(h, win, pending, True, (own, apos, avalid, rcfg, routed, qmask, docs))
+            share, route, mass = b.tether_out
+            masses.append(mass)
+            routed = route if c.rope_share_route else None
+            if bi == 0:
+                self.stats["rope_share"] = share
+        self._tether_mass = sum(masses) / len(masses) if masses else None
+        return h if pending is None else ops.resid_add(h, pending)
 
     def _light_surprise(self, lhd, x):
         """lse - logit[target] of the light head for every position but the last (full2.py:1650-1667)."""
@@ -775,13 +830,20 @@ class MemArchLM(nn.Module):
                 else:
                     loss = loss + self._ce_part(*part, j)
         loss = main = loss / y.numel()
-        if rem is not None and (c.remind_w > 0 or not train):
+        if rem is not None and (c.remind_w > 0 or c.remind_use_w > 0 or not train):
             term, st = self.remind_term(hn, y, extra)
             self.stats.update(st)
             if train:
                 loss = loss + c.remind_w * term
                 if c.remind_only:                         # stage one: the answers only (auxiliary terms stay)
                     loss = loss - main
+            mass = getattr(self, "_tether_mass", None)
+            if mass is not None:                          # how much of the questions' attention went down the tether
+                mk, den = (rem > 0).float(), float(len(y) * c.remind_q)
+                use = (mass.float() * mk).sum() / den
+                self.stats["remind_rope_share"] = use.detach()
+                if train and c.remind_use_w > 0:
+                    loss = loss + c.remind_use_w * (mk.sum() / den - use)
         if train and self.moe:
             loss = loss + 0.01 * sum(b.aux for b in self.heavy) / len(self.heavy)
         if train and len(self.light_a) and hasattr(self.light_a[0], "moe"):

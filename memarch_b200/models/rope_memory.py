@@ -40,6 +40,7 @@ class RopeCfg:
     rgrad: bool = True          # routing score as a bias on the span's keys
     rgrad_scale: float = 1.0
     chunk: int = 256            # queries per recomputed chunk
+    mgrad: bool = False         # the share of mass on opened spans keeps its gradient (a penalty may push it up)
 
 
 def anchors_from_surprise(s, tau, A, top=False):
@@ -217,7 +218,7 @@ def mask_route(tidx, tval, apos, qmask=None, docs=None):
     return tval
 
 
-def _read_chunk(qc, kr, v, k0, q0c, c0, st, en, tval, tpos, W, rgrad, rgrad_scale):
+def _read_chunk(qc, kr, v, k0, q0c, c0, st, en, tval, tpos, W, rgrad, rgrad_scale, mgrad=False):
     B, H, C, hd = qc.shape
     T = kr.shape[2]
     sc = 1.0 / math.sqrt(hd)
@@ -238,14 +239,14 @@ def _read_chunk(qc, kr, v, k0, q0c, c0, st, en, tval, tpos, W, rgrad, rgrad_scal
     s_all = torch.where(win[None, None], s, torch.where(span, s_span, torch.full_like(s, -float("inf"))))
     p = s_all.softmax(-1)
     out = torch.einsum("bhct,bhtd->bhcd", p, v.float()).to(v.dtype)
-    share = (p * (span & ~win[None, None])).sum(-1).detach()
-    return out, share
+    share = (p * (span & ~win[None, None])).sum(-1)
+    return out, share if mgrad else share.detach()
 
 
-def rope_attention(qr, kr, v, own, apos, avalid, cfg: RopeCfg, routed=None, qmask=None, docs=None):
+def rope_attention(qr, kr, v, own, apos, avalid, cfg: RopeCfg, routed=None, qmask=None, docs=None, want_mass=False):
     """qr, kr rotated queries / keys, v values, all (B,H,T,hd).  Returns (out (B,H,T,hd), share of softmax mass that
     went to opened spans, (tidx, tval, tpos)).  `routed` reuses another layer's choice; `qmask` / `docs` as in
-    `mask_route`."""
+    `mask_route`.  `want_mass` adds a fourth result: that share per position (B,T), mean over heads."""
     B, H, T, hd = qr.shape
     tidx, tval, tpos = route(qr, kr, own, apos, avalid, cfg) if routed is None else routed
     tval = mask_route(tidx, tval, apos, qmask, docs)
@@ -259,14 +260,17 @@ def rope_attention(qr, kr, v, own, apos, avalid, cfg: RopeCfg, routed=None, qmas
         nx = nxt.gather(1, ti.reshape(B, -1)).view_as(ti)
         en = torch.minimum(torch.minimum(nx, st + cfg.span_cap), (qi_all[sl] - cfg.win + 1)[None, None, :, None])
         args = (qr[:, :, sl], kr, v, kr.detach(), qr[:, :, sl].detach(), c0, st, en, tval[:, :, sl] & (en > st),
-                tpos[:, :, sl], cfg.win, cfg.rgrad, cfg.rgrad_scale)
+                tpos[:, :, sl], cfg.win, cfg.rgrad, cfg.rgrad_scale, cfg.mgrad)
         if torch.is_grad_enabled() and qr.requires_grad:
             o, sh = checkpoint(_read_chunk, *args, use_reentrant=False)
         else:
             o, sh = _read_chunk(*args)
         outs.append(o)
         shares.append(sh)
-    return torch.cat(outs, 2), torch.cat(shares, 2).mean(), (tidx, tval, tpos)
+    mass = torch.cat(shares, 2)
+    if want_mass:
+        return torch.cat(outs, 2), mass.mean().detach(), (tidx, tval, tpos), mass.mean(1)
+    return torch.cat(outs, 2), mass.mean().detach(), (tidx, tval, tpos)
 
 
 class RopeMemoryAttention(nn.Module):

@@ -437,7 +437,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     ts = time.time()
                     npreps = None
                     if (rb is None and getattr(data, "remind", None) is not None and data.extra is not None
-                            and getattr(getattr(tr.model, "cfg", None), "remind_w", 0) > 0):
+                            and max(getattr(getattr(tr.model, "cfg", None), "remind_w", 0),
+                                    getattr(getattr(tr.model, "cfg", None), "remind_use_w", 0)) > 0):
                         npreps = needle_preps(tr.model, xy_b, data.extra, tr.cfg.micro or len(xy_b))
                     loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1, npreps)
                     phase["data"] += ts - td

@@ -562,3 +562,45 @@ def test_dropless_moe_keeps_every_token():
     assert torch.allclose(xa.grad, xb.grad, atol=1e-5) and torch.allclose(a.up.grad, b.up.grad, atol=1e-5)
     from memarch_b200.config import model_from_env, ModelConfig
     assert model_from_env(ModelConfig(vocab=64), {"MOE_GMM": "1"}).moe_dropless
+
+
+def test_tether_inside_the_main_model():
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2", "ROPE_MEM": "1", "ROPE_WIN": "8", "ROPE_SPAN_CAP": "12", "ROPE_LINKS": "3",
+           "ROPE_K": "2", "ROPE_HIER_G": "4", "ROPE_HIER_BM": "16", "ROPE_CHUNK": "32", "ROPE_TAU0": "5.5",
+           "ROPE_DOC_EOS": "7", "ROPE_QFRAC": "0.6", "ROPE_KEY_DIAG": "1", "REMIND_USE_W": "0.5", "REMIND_W": "1.0",
+           "REMIND_N": "4", "REMIND_TOK0": "100"}
+    m = build("tiny", 256, env=env).train()
+    assert m.cfg.rope_mem and m.cfg.no_mem and "rope_tau" in m.state_dict() and "rope_qtau" in m.state_dict()
+    xy = torch.randint(0, 256, (2, 97))
+    x, y = xy[:, :-1], xy[:, 1:]
+    tau0 = float(m.rope_tau)
+    out, cost = m(x)
+    assert float(m.rope_tau) != tau0                                       # the threshold follows the surprise
+    for k in ("rope_anchors", "rope_share", "rope_qfrac_real", "rope_key_link"):
+        assert k in m.stats and math.isfinite(float(m.stats[k])), k
+    assert 0 < float(m.stats["rope_anchors"]) <= m.cfg.cap + 1e-6 and 0 < float(m.stats["rope_qfrac_real"]) < 1
+    rem = torch.zeros(2, 96, dtype=torch.int8)
+    rem[:, 60:68:2] = 1
+    loss = m.train_loss(out, y, True, extra={"rem": rem})
+    plain = m.train_loss(out, y, True)
+    use = float(m.stats["remind_rope_share"])
+    assert 0 <= use <= 1
+    loss.backward()
+    g = m.light_b[0].qkv.weight.grad
+    assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
+    # the local window alone (tether closed for every word) differs from the tethered read
+    m.eval()
+    with torch.no_grad():
+        a, _ = m(x)
+        frozen = float(m.rope_tau)
+        m.rope_qtau.fill_(1e9)
+        b, _ = m(x)
+    assert float(m.rope_tau) == frozen and not torch.allclose(a[0], b[0])
+    # only the first layers tethered, the choice of anchors shared
+    m2 = build("tiny", 256, env=dict(env, ROPE_LAYERS="1", ROPE_SHARE_ROUTE="1", ROPE_QFRAC="1.0")).train()
+    o2, _ = m2(x)
+    assert hasattr(m2.light_b[0], "tether_out") and torch.isfinite(o2[0]).all()
+    if len(m2.light_b) > 1:
+        assert not hasattr(m2.light_b[1], "tether_out")

@@ -182,6 +182,17 @@ class OptConfig:
     wd_norm: float = 0.0          # >0: decoupled weight decay towards zero for the 1-D norm weights (norm, l_norm, *.n1, *.n2)
     norm_anchor: bool = False     # 1-D norm weights of the light / final blocks are pulled towards 1: w -= lr wd (w - 1)
     lr_mul: tuple = ()            # ((name prefix, multiplier), ...): step multiplier of the weights under a prefix
+    stream_proj: bool = False     # light-block matrices: gradient and momentum lose their component along the stream's common vector
+    stream_d: int = 0             # width of the stream (0: taken from the matrices)
+    m_rate: bool = False          # ... and the common-vector part of their move is rate-limited, the excess banked
+    m_rate_kappa: float = 2.0
+    m_rate_warm: int = 100
+    m_rate_gate: bool = False
+    gnorm_rawrel: bool = False    # with gnorm: |g|/|w| (blame, cards) from the raw gradient
+    snr_skip: Tuple[str, ...] = ()  # the confidence brake leaves tensors with these name prefixes alone
+    snr_only: Tuple[str, ...] = ()  # ... or acts only on these
+    safe16: bool = False          # light blocks + output norms: step direction never against the fresh gradient
+    safe16_prefix: Tuple[str, ...] = ("light_a.", "light_b.", "final.")
     culprit: str = "abs"          # "abs": the tensors with the largest |g|/|w| are blamed; "ema": the largest against their own mean
     g_max: float = 3.0            # ceiling of a gain
     card_by_kind: bool = False    # the kind of the step (a number given to `prepare`) names the card

@@ -61,6 +61,8 @@ class FishPool(nn.Module):
             up, down = up[:, r * d // W:(r + 1) * d // W].clone(), down[:, r * hf // W:(r + 1) * hf // W].clone()
         self.norm = nn.Parameter(torch.ones(n, d))
         self.up, self.down = nn.Parameter(up), nn.Parameter(down)
+        for t in (self.norm, self.up, self.down):        # the optimizer leaves the units of a step's idle kinds alone
+            t._idle_rows = True
         self.router = nn.Linear(d, kinds, bias=False)
 
     def _weights(self, i):

@@ -121,6 +121,7 @@ class MemArchLM(nn.Module):
             if c.rope_qfrac < 1.0:
                 self.register_buffer("rope_qtau", torch.tensor(float(c.rope_qtau0)))
         self._tether_mass = None
+        self.want_stream_mean = False
         self.stats = {}
         self.panic = c.panic
         self.short_v = c.short_v
@@ -480,10 +481,12 @@ class MemArchLM(nn.Module):
         h = run_blocks(self.final, h, win, self._run)
 
         dt = _cdt(h)
-        if c.no_mem or c.no_reread:
-            return (ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt), lh), torch.zeros((), device=x.device)
-        o, cost = self._reread_pass(h, x, snaps, seg)
-        h = h + o.type_as(h)
+        cost = torch.zeros((), device=x.device)
+        if not (c.no_mem or c.no_reread):
+            o, cost = self._reread_pass(h, x, snaps, seg)
+            h = h + o.type_as(h)
+        if self.want_stream_mean:                     # for the optimizer's rules on the stream's common vector
+            self.stats["stream_mean"] = h.detach().float().mean((0, 1))
         return (ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt), lh), cost
 
     def _tether_pass(self, h, x, win):

@@ -46,6 +46,12 @@ class Instinct:
         is_norm = lambda n: n in ("norm.weight", "l_norm.weight") or n.endswith((".n1.weight", ".n2.weight"))
         self._norm_w = [p.dim() == 1 and is_norm(n) for p, n in zip(self.plist, self.names)]
         self._anchor = [nw and n.startswith(("light_a.", "light_b.", "final.")) for nw, n in zip(self._norm_w, self.names)]
+        # safe16: the light blocks and the two output norms take their step direction from a momentum that never
+        # moves against the fresh gradient (PyTorch statement of the update; the stored momentum stays the plain EMA)
+        self._safe = [bool(cfg.safe16) and (n.startswith(tuple(cfg.safe16_prefix)) or n in ("norm.weight", "l_norm.weight"))
+                      for n in self.names]
+        self._snr_on = [not n.startswith(tuple(cfg.snr_skip)) and (not cfg.snr_only or n.startswith(tuple(cfg.snr_only)))
+                        if (cfg.snr_skip or cfg.snr_only) else True for n in self.names]
         self._mul = [next((float(m) for pref, m in cfg.lr_mul if n.startswith(pref)), 1.0) for n in self.names]
         self.param_groups = [dict(lr=cfg.lr, weight_decay=cfg.weight_decay)]
         self.K, self.beta, self.new_card, self.ema = cfg.cards, cfg.beta, cfg.new_card, cfg.ema
@@ -68,6 +74,24 @@ class Instinct:
             raise ValueError(f"culprit must be 'abs' or 'ema', not {cfg.culprit!r}")
         if self.culprit == "ema":
             self.rel_avg = torch.zeros(P, device=dev)
+        # rules on the stream's common vector (stream_proj, m_rate): the matrices of the light blocks that write into or
+        # read from the residual stream, and along which of their axes the stream runs.  The JAX port addresses "the
+        # first axis of size d" of its (in, out) layout; weights here are (out, in), hence the axes in reverse order
+        self.U = None
+        self._stream_ax = [None] * P
+        if cfg.stream_proj or cfg.m_rate:
+            hit = lambda n: n.startswith(("light_a.", "light_b.", "final.")) and n.endswith((".o.weight", ".down.weight", ".qkv.weight"))
+            d = cfg.stream_d or min((p.shape[-1] for p, n in zip(self.plist, self.names) if p.dim() >= 2 and hit(n)), default=0)
+            for j, (p, n) in enumerate(zip(self.plist, self.names)):
+                if p.dim() >= 2 and hit(n):
+                    self._stream_ax[j] = next((ax for ax in reversed(range(p.dim())) if p.shape[ax] == d), None)
+            if cfg.m_rate:
+                self.mrl_n = 0
+                shape = lambda p, ax: p.shape[:ax] + p.shape[ax + 1:]
+                self.mrl_bank = [None if ax is None else torch.zeros(shape(p, ax), device=dev) for p, ax in zip(self.plist, self._stream_ax)]
+                self.mrl_v = [None if b is None else torch.zeros_like(b) for b in self.mrl_bank]
+                self.mrl_base = [None if b is None else torch.zeros((), device=dev) for b in self.mrl_bank]
+                self.mrl_cut = torch.zeros((), device=dev)
         self.m = [torch.zeros_like(p, dtype=self.m_dtype) for p in self.plist]
         # optimizer-state offload (memarch_jax/memarch_jax/dist.py:311-322, step.py:154-155): the momentum of every weight
         # rests in pinned host memory and visits the device only for its own update, on the stream of that update
@@ -108,6 +132,15 @@ class Instinct:
 
     # ------------------------------------------------------------------------------------------ card logic
     @torch.no_grad()
+    def observe_stream(self, stream_mean, update=True, beta=0.9):
+        """U <- unit(beta U + (1 - beta) unit(mean state of the stream before the final norm)); the first time just the
+        unit mean (memarch_jax/memarch_jax/instinct.py:370-383)."""
+        mv = F.normalize(stream_mean.detach().float().flatten(), dim=0, eps=1e-8)
+        if self.U is None:
+            self.U = mv.clone()
+        elif update:
+            self.U.copy_(F.normalize(beta * self.U + (1 - beta) * mv, dim=0, eps=1e-8))
+
     def prepare(self, loss, situation, card=None):
         """Pick the situation card, its expectation and the surprise of this step's loss (exp_opt.py:349-372).
         With `card_by_kind` and a `card` number the kind of the step names the card instead of the similarity of the
@@ -153,6 +186,8 @@ class Instinct:
         else:
             culprit = (self.rel >= self.rel.quantile(1 - self.top)).float()
         self.n_step += 1
+        if self.cfg.m_rate and self.U is not None:
+            self.mrl_n += 1
         gk += torch.where(s < 0, culprit * self.bad * (-s * 10).clamp(max=1), torch.zeros_like(gk))
         gk += torch.where(s > 0, self.good * (s * 10).clamp(max=1) * (1 - gk), torch.zeros_like(gk))
         gk += self.relax * (1 - gk)
@@ -220,6 +255,77 @@ class Instinct:
             self.m[i] = home
 
     def _step_one(self, i, p, grad):
+        """A weight stacked over units of which only a few work in a step (`p._idle_rows`, the layer pool of
+        `models.fishki`): a unit whose gradient is all zero stays exactly as it was - no weight decay, no coasting on
+        momentum - as an unused parameter does under an optimizer that skips `grad is None`.  Otherwise weight decay
+        would wipe a unit that idles 97 % of the steps (the JAX Instinct's `_freeze_idle`, instinct.py:1165-1195)."""
+        if not getattr(p, "_idle_rows", False):
+            return self._step_stream(i, p, grad)
+        n = p.shape[0]
+        act = (grad.reshape(n, -1).abs().sum(1) > 0)
+        pick = lambda new, old: torch.where(act.view(-1, *([1] * (new.dim() - 1))), new, old.to(new.dtype))
+        old_p, old_m = p.detach().clone(), self.m[i].clone()
+        old_w = self.w[i].clone() if self.w[i] is not None else None
+        old_cs = self.cs[i].clone() if torch.is_tensor(self.cs[i]) else None
+        self._step_stream(i, p, grad)
+        p.data.copy_(pick(p.data, old_p))
+        self.m[i].copy_(pick(self.m[i], old_m))
+        if old_w is not None:
+            self.w[i].copy_(pick(self.w[i], old_w))
+        cs = self.cs[i]
+        if old_cs is not None and torch.is_tensor(cs) and cs.shape == old_cs.shape and cs.shape[:1] == (n,):
+            cs.copy_(pick(cs, old_cs))                  # only statistics that run over the units
+
+    def _step_stream(self, i, p, grad):
+        """The two rules on the stream's common vector U (the running mean direction of the state before the final
+        norm), for the matrices of the light blocks.  `stream_proj`: the component along U is taken out of the gradient
+        and of the momentum, so the optimizer itself never pulls on the common vector.  `m_rate`: after the step the
+        U-component of the weight's move, c = dW.U, is limited by its coherent speed v = EMA(c) <= kappa x its usual
+        size; the excess waits in a bank and is released by later steps, nothing is thrown away (with `m_rate_gate`
+        only where the fresh gradient still agrees).  (instinct.py:370-484 of the reference's JAX port)"""
+        ax = self._stream_ax[i]
+        if ax is None or self.U is None:
+            return self._step_body(i, p, grad)
+        c = self.cfg
+        U = self.U
+
+        def off(x):
+            xf = x.float().movedim(ax, -1)
+            return (xf - (xf @ U)[..., None] * U).movedim(-1, ax).to(x.dtype)
+        if c.stream_proj:
+            grad = off(grad)
+            self.m[i].copy_(off(self.m[i]))
+        if not c.m_rate:
+            return self._step_body(i, p, grad)
+        t = self.w[i] if self.w[i] is not None else p.data
+        old = t.detach().float().clone()
+        self._step_body(i, p, grad)
+        new = t.float().movedim(ax, -1)
+        moved = (new - old.movedim(ax, -1)) @ U
+        bank, v, base = self.mrl_bank[i], self.mrl_v[i], self.mrl_base[i]
+        if c.m_rate_gate:                                # what waits is released only where the model still wants it
+            bank = torch.where(bank * (grad.float().movedim(ax, -1) @ U) < 0, bank, torch.zeros_like(bank))
+        want = moved + bank
+        bv = 0.9
+        v_new = bv * v + (1 - bv) * want
+        size = v_new.norm()
+        warm = self.mrl_n < c.m_rate_warm                # first steps: only learn the usual size
+        scale = torch.ones_like(size) if warm else (c.m_rate_kappa * base / size.clamp(min=1e-30)).clamp(max=1.0)
+        v_cut = v_new * scale
+        out = torch.where(scale < 1.0, (v_cut - bv * v) / (1 - bv), want)
+        self.mrl_bank[i] = want - out
+        self.mrl_v[i] = v_cut
+        sz = v_cut.norm()
+        if warm:
+            base.copy_(sz if self.mrl_n == 0 else 0.95 * base + 0.05 * sz)
+        else:
+            base.copy_(0.998 * base + 0.002 * torch.minimum(sz, base))          # no ratchet: pressure does not lift the limit
+        self.mrl_cut += (scale < 1.0).float()
+        t.copy_((new + (out - moved)[..., None] * U).movedim(-1, ax).to(t.dtype))
+        if self.w[i] is not None:
+            p.data.copy_(t)
+
+    def _step_body(self, i, p, grad):
         self._sync_lr()
         kind, wd, vocab = self.spec(p)
         want_rel = self.n_step % self.rel_every == 0
@@ -227,6 +333,7 @@ class Instinct:
         if self.cfg.surge_thr > 0:                       # surprise brake (device scalars only)
             bad = (-self.s).clamp(min=self.cfg.surge_thr)
             lr_t = lr_t * (self.cfg.surge_thr / bad) ** 2
+        raw = grad if (self.cfg.gnorm and self.cfg.gnorm_rawrel) else None
         if self.cfg.gnorm:                               # a step with a large gradient does not drown the small ones in the momentum
             g32 = grad.float()
             grad = (g32 * torch.rsqrt(g32.pow(2).mean() + 1e-30)).to(grad.dtype if grad.dtype == torch.float32 else torch.float32)
@@ -236,7 +343,7 @@ class Instinct:
             lr_t = self._pace(i, grad, lr_t)
         elif self.dv is not None and not vocab:
             grad, lr_t = self._damp(i, grad, lr_t)
-        if self.snr_v is not None and not vocab and self.m[i].shape == grad.shape:
+        if self.snr_v is not None and not vocab and self.m[i].shape == grad.shape and self._snr_on[i]:
             lr_t = self._snr(i, grad, lr_t)
         wd_v = self.param_groups[0]["weight_decay"] / self.scale if wd else 0.0
         if not wd and self.cfg.wd_norm > 0 and self._norm_w[i]:
@@ -250,11 +357,16 @@ class Instinct:
                 self.rel[i] = 0.0
             return
         if (_ext.use_cuda(p) and _kind_code(kind) >= 0 and p.is_contiguous() and grad.is_contiguous()
-                and getattr(p, "_row_shard", None) is None
+                and getattr(p, "_row_shard", None) is None and not self._safe[i]
                 and not (self.hs_lag and kind in ("hs", "hs3") and not self._lag_on_gpu(p, kind))):
             self._update_cuda(i, p, grad, kind, wd_v, lr_t, want_rel)
         else:
             self._update_ref(i, p, grad, kind, wd_v, lr_t, want_rel)
+        if raw is not None and want_rel:
+            # the normalised gradient has the same length for every tensor, so |g|/|w| would only say whose |w| shrinks:
+            # who is to blame is measured on the raw gradient
+            t = self.w[i] if self.w[i] is not None else p
+            self.rel[i] = raw.float().norm() / (t.float().norm() + 1e-8)
 
     def _anchor_norm(self, i, p):
         """w <- w - lr wd (w - 1) on a 1-D norm weight (and its exact copy): what weight decay is for matrices, with 1
@@ -350,6 +462,7 @@ class Instinct:
     def _update_ref(self, i, p, grad, kind, wd, lr_t, want_rel):
         m, w = self.m[i], self.w[i]
         grad = grad.float()
+        m_old = m.float().clone() if self._safe[i] else None
         mf = m.float() * self.beta + grad * (1 - self.beta)
         if self.sr and m.dtype == torch.bfloat16:
             self._seed_t.add_(1)
@@ -365,7 +478,22 @@ class Instinct:
                 self.cs[i] = torch.zeros(shp, device=p.device, dtype=torch.float32)
             cs = self.cs[i]
         shard = getattr(p, "_row_shard", None)
-        if shard is not None and kind == "hs":
+        if self._safe[i]:
+            # (1) the part of the old momentum that points against the fresh gradient is projected out (per input
+            # column of a matrix - the first axis of the JAX port's (in, out) layout - or for a whole 1-D tensor),
+            # (2) coordinates of the step that still go against the gradient are masked ("cautious"), (3) 1-D norm
+            # weights step relative to |w| (at most 2x), so near-zero sink channels are not kicked out
+            # (memarch_jax/memarch_jax/instinct.py:1033-1043)
+            dims = tuple(range(grad.dim() - 1)) if grad.dim() >= 2 else None
+            tot = (lambda t: t.sum(dims, keepdim=True)) if dims is not None else (lambda t: t.sum())
+            mg, gg = tot(m_old * grad), tot(grad * grad) + 1e-30
+            mstep = (m_old - mg.clamp(max=0.0) / gg * grad) * self.beta + grad * (1 - self.beta)
+            mstep = torch.where(mstep * grad >= 0, mstep, torch.zeros_like(mstep))
+            upd, new_cs = ref.instinct_direction(mstep, grad, kind, cs)
+            if p.dim() == 1:
+                w0 = (p if w is None else w).float()
+                lr_t = lr_t * (w0.abs() / (w0.pow(2).mean().sqrt() + 1e-8)).clamp(max=2.0)
+        elif shard is not None and kind == "hs":
             upd, new_cs = self._direction_row_sharded(mf, shard), None
         else:
             upd, new_cs = ref.instinct_direction(mf, grad, kind, cs)

@@ -301,17 +301,22 @@ class ParallelEngine:
     def sync_control(self, loss, sit, model):
         """One small all-reduce: mean loss, true batch-mean situation vector and the shared anchor threshold.  NCCL in
         the baseline mode; in the fused mode the one-shot peer all-reduce on a symmetric buffer."""
-        tau = model.tau if hasattr(model, "tau") else loss.new_zeros(())
-        buf = torch.cat([loss.reshape(1).float(), tau.reshape(1).float(), sit.float().reshape(-1)])
+        taus = [getattr(model, n) for n in ("tau", "rope_tau", "rope_qtau") if hasattr(model, n)]
+        buf = torch.cat([loss.reshape(1).float()] + [t.reshape(1).float() for t in taus] + [sit.float().reshape(-1)])
+        self.mean_vector(buf)
+        for j, t in enumerate(taus):
+            t.copy_(buf[1 + j])
+        return buf[0], buf[1 + len(taus):]
+
+    def mean_vector(self, buf):
+        """Rank-mean of a small fp32 vector, in place."""
         if self.W > 1:
             if self.fused_impl is not None and buf.is_cuda:
                 self.fused_impl.mean_small(buf)              # peer loads / stores between two device barriers
             else:
                 dist.all_reduce(buf, group=self.group)
                 buf /= self.W
-        if hasattr(model, "tau"):
-            model.tau.copy_(buf[1])
-        return buf[0], buf[2:]
+        return buf
 
     # ------------------------------------------------------------------------------------------ gradients
     def before_backward(self, trainer):

@@ -63,6 +63,8 @@ class Trainer:
             self.opt = Instinct(self.params, dataclasses.replace(self.ocfg, lr=tcfg.lr),
                                 names=[by_id.get(id(p), "") for p in self.params])
             self.in_backward = "B" in st and self.ocfg.in_backward
+            if (self.ocfg.stream_proj or self.ocfg.m_rate) and hasattr(model, "want_stream_mean"):
+                model.want_stream_mean = True
             if parallel is not None:
                 parallel.attach(self)
             # Graph mode runs the whole step on one private stream: the per-parameter AccumulateGrad nodes (kept alive
@@ -132,6 +134,13 @@ class Trainer:
         lr = lr_at(step, self.cfg) * mul
         for g in self.opt.param_groups:
             g["lr"] = lr
+
+    def _stream_to_opt(self):
+        sm = getattr(self.model, "stats", {}).get("stream_mean") if (self.ocfg.stream_proj or self.ocfg.m_rate) else None
+        if sm is not None:
+            if self.parallel is not None and hasattr(self.parallel, "mean_vector"):
+                sm = self.parallel.mean_vector(sm.clone())
+            self.opt.observe_stream(sm)
 
     def situation(self, xy):
         with torch.no_grad():
@@ -226,6 +235,7 @@ class Trainer:
                 sit = self.situation(xy)
                 if self.parallel is not None:
                     tl, sit = self.parallel.sync_control(tl, sit, m)
+                self._stream_to_opt()
                 self.opt.prepare(tl, sit, card=self.card)
             if self.parallel is not None:
                 self.parallel.before_backward(self)
@@ -278,6 +288,7 @@ class Trainer:
         total = torch.stack(losses).sum()
         self.apply_now = True
         if isinstance(self.opt, Instinct):
+            self._stream_to_opt()
             self.opt.prepare(total.detach(), self.situation(xy), card=self.card)
         total.backward()
         self._after_backward(total.detach(), xy)

@@ -801,3 +801,185 @@ def test_instinct_blames_by_own_history_and_cards_by_kind():
     assert plain.gain[1].argmax() in (0, 1) and not hasattr(plain, "rel_avg")
     with pytest.raises(ValueError):
         Instinct(ps, OptConfig(culprit="mean"))
+
+
+def test_idle_units_of_a_layer_pool_do_not_move():
+    from memarch_b200 import OptConfig
+    from memarch_b200.models.fishki import FishPool
+    from memarch_b200.optim import Instinct
+    torch.manual_seed(0)
+    pool = FishPool(16, n=6, hf=32, kinds=3, pool=3)
+    ps = [pool.up, pool.down, pool.norm]
+    opt = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, weight_decay=0.1, rel_every=1), names=["up", "down", "norm"])
+    used = pool.sets[1]
+    idle = [i for i in range(6) if i not in used]
+    for step in range(3):
+        before = [p.detach().clone() for p in ps]
+        m_before = [m.clone() for m in opt.m]
+        h = torch.randn(2, 5, 16)
+        pool(h, used).square().sum().backward()
+        opt.prepare(torch.tensor(1.0), torch.randn(8))
+        for p in ps:
+            opt.update(p)
+            p.grad = None
+        opt.finish()
+        for p, b, m, mb in zip(ps, before, opt.m, m_before):
+            assert torch.equal(p[idle], b[idle]) and torch.equal(m[idle], mb[idle])      # neither decay nor momentum
+            assert not torch.equal(p[used], b[used])
+    # without the mark the idle units would have decayed
+    pool.up._idle_rows = False
+    before = pool.up.detach().clone()
+    pool(torch.randn(2, 5, 16), used).square().sum().backward()
+    opt.prepare(torch.tensor(1.0), torch.randn(8))
+    opt.update(pool.up)
+    assert not torch.equal(pool.up[idle], before[idle])
+
+
+def test_rules_on_the_common_vector_of_the_stream():
+    from memarch_b200 import OptConfig
+    from memarch_b200.optim import Instinct
+    torch.manual_seed(0)
+    d = 16
+    names = ["light_b.0.o.weight", "light_b.0.down.weight", "light_b.0.qkv.weight", "light_b.0.up.weight", "heavy.0.o.weight"]
+    shapes = [(d, d), (d, 4 * d), (3 * d, d), (8 * d, d), (d, d)]
+    mk = lambda: [torch.nn.Parameter(torch.randn(*s) * 0.1) for s in shapes]
+    ps = mk()
+    opt = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, stream_proj=True), names=names)
+    # the port's "first axis of size d" in (in, out) layout: o and qkv along their inputs, down along its outputs
+    assert opt._stream_ax == [1, 0, 1, None, None]
+    sm = torch.randn(d)
+    opt.observe_stream(sm)
+    U = F.normalize(sm, dim=0)
+    assert torch.allclose(opt.U, U, atol=1e-6)
+    opt.observe_stream(-sm)                                                # a running mean, renormalised
+    assert torch.allclose(opt.U, F.normalize(0.9 * U + 0.1 * (-U), dim=0), atol=1e-6)
+    U = opt.U.clone()
+    opt.prepare(torch.tensor(1.0), torch.randn(8))
+    before = [p.detach().clone() for p in ps]
+    for p in ps:
+        p.grad = torch.randn_like(p)
+        opt.update(p)
+    along = lambda t, ax: (t.movedim(ax, -1) @ U).abs().max()
+    assert along(opt.m[0], 1) < 1e-6 and along(opt.m[1], 0) < 1e-6 and along(opt.m[2], 1) < 1e-6   # nothing along U
+    assert along(opt.m[3], 1) > 1e-3 and along(opt.m[4], 1) > 1e-3                                  # others untouched
+    assert all(not torch.equal(p, b) for p, b in zip(ps, before))
+
+    # rate limit: in the warm-up the weights are exactly those of the plain optimizer; afterwards a surge along U is cut
+    # to kappa x the usual speed, the rest waits in the bank and comes out later
+    torch.manual_seed(1)
+    pa, pb = mk(), None
+    torch.manual_seed(1)
+    pb = mk()
+    a = Instinct(pa, OptConfig(lr=1e-2, norm="hs", scale=0.12, m_rate=True, m_rate_warm=4, m_rate_kappa=1.5), names=names)
+    b = Instinct(pb, OptConfig(lr=1e-2, norm="hs", scale=0.12), names=names)
+    a.observe_stream(sm)
+    g = torch.Generator().manual_seed(5)
+    for step in range(4):
+        for o_, ps_ in ((a, pa), (b, pb)):
+            o_.prepare(torch.tensor(1.0), torch.ones(8))
+        gs = [torch.randn(*s, generator=g) for s in shapes]
+        for o_, ps_ in ((a, pa), (b, pb)):
+            for p, gr in zip(ps_, gs):
+                o_.update(p, gr.clone())
+            o_.finish()
+    assert all(torch.allclose(x, y, atol=1e-7) for x, y in zip(pa, pb)) and a.mrl_n == 4 and float(a.mrl_cut) == 0
+    assert float(a.mrl_base[0]) > 0 and a.mrl_bank[3] is None
+    u = a.U
+    for step in range(3):                                                  # every weight is pushed along U, hard
+        for o_ in (a, b):
+            o_.prepare(torch.tensor(1.0), torch.ones(8))
+        for o_, ps_ in ((a, pa), (b, pb)):
+            w0 = ps_[1].detach().clone()
+            o_.update(ps_[1], (torch.ones(4 * d)[None, :] * u[:, None]) * 50)
+            o_.finish()
+            if o_ is a:
+                ca = (ps_[1] - w0).T @ u
+            else:
+                cb = (ps_[1] - w0).T @ u
+    assert float(a.mrl_cut) > 0 and ca.norm() < cb.norm() and a.mrl_bank[1].norm() > 0
+    moved_total = a.mrl_bank[1].norm()
+    a.m[1].zero_()
+    w0 = pa[1].detach().clone()
+    for step in range(200):                                                # no more pressure along U: the bank drains
+        a.prepare(torch.tensor(1.0), torch.ones(8))
+        gr = torch.randn(d, 4 * d, generator=g)
+        a.update(pa[1], gr - u[:, None] * (u @ gr)[None, :])
+        a.finish()
+    assert a.mrl_bank[1].norm() < 0.5 * moved_total
+    released = (pa[1].detach() - w0).T @ u                                 # ... into the weights: nothing is thrown away
+    assert released.norm() > 0.4 * moved_total
+    sd = a.state_dict()
+    assert "U" in sd and "mrl_bank" in sd and "mrl_base" in sd and sd["mrl_n"] == a.mrl_n
+
+
+def test_trainer_feeds_the_stream_mean_to_the_optimizer():
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.train import Trainer
+    torch.manual_seed(0)
+    m = build("tiny", 256, env={"NO_MEM": "1", "MOE_ACT": "relu2"})
+    tr = Trainer(m, TrainConfig(name="tiny", stage="ABX", steps=50, batch=4, micro=4, seq=32, lr=1e-2, warmup=2),
+                 OptConfig(lr=1e-2, norm="hs", scale=0.12, rel_every=2, stream_proj=True, m_rate=True, m_rate_warm=2),
+                 stage="ABX")
+    assert m.want_stream_mean and any(ax is not None for ax in tr.opt._stream_ax)
+    losses = [float(tr.step(xy, s)) for s, xy in enumerate(batches(6))]
+    assert tr.opt.U is not None and abs(float(tr.opt.U.norm()) - 1) < 1e-5 and tr.opt.mrl_n == 6
+    assert all(math.isfinite(v) for v in losses) and losses[-1] < losses[0] + 0.5
+
+
+def test_safe_step_never_goes_against_the_fresh_gradient():
+    from memarch_b200 import OptConfig
+    from memarch_b200.optim import Instinct
+    torch.manual_seed(0)
+    names = ["light_a.0.up.weight", "norm.weight", "heavy.0.up.weight"]
+    def mk():
+        g = torch.Generator().manual_seed(3)
+        return [torch.nn.Parameter(torch.randn(12, 8, generator=g) * 0.1),
+                torch.nn.Parameter(torch.cat([torch.ones(7), torch.tensor([0.004])])),
+                torch.nn.Parameter(torch.randn(12, 8, generator=g) * 0.1)]
+    ps = mk()
+    opt = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, safe16=True, weight_decay=0.0), names=names)
+    plain = Instinct(mk(), OptConfig(lr=1e-2, norm="hs", scale=0.12, weight_decay=0.0), names=names)
+    assert opt._safe == [True, True, False]
+    g0 = [torch.randn_like(p) for p in ps]
+    for o_ in (opt, plain):
+        o_.prepare(torch.tensor(1.0), torch.ones(8))
+        for p, g in zip(o_.plist, g0):
+            o_.update(p, g.clone())
+        o_.finish()
+    # first step: momentum and gradient agree everywhere, both optimizers take the same step on the matrix
+    assert torch.allclose(opt.plist[0], plain.plist[0], atol=1e-7)
+    # the sink channel (|w| = 0.004) of the norm weight moves in proportion to its size, not by a full step
+    w_before = mk()[1]
+    assert abs(float(opt.plist[1][7] - w_before[7])) < 0.05 * abs(float(plain.plist[1][7] - w_before[7]))
+    # second step with a gradient that turned round: the plain step still coasts along the old momentum (up the
+    # fresh gradient), the safe one moves up it nowhere
+    g1 = -0.5 * g0[0]
+    for o_ in (opt, plain):
+        o_.prepare(torch.tensor(1.0), torch.ones(8))
+        before = o_.plist[0].detach().clone()
+        o_.update(o_.plist[0], g1.clone())
+        o_.finish()
+        step = o_.plist[0].detach() - before
+        assert bool(((step * g1) > 1e-12).any()) == (o_ is plain)
+    assert torch.allclose(opt.m[0], plain.m[0], atol=1e-7)                    # the stored momentum is the plain EMA
+    assert torch.allclose(opt.plist[2], plain.plist[2])                       # other tensors: untouched by the rule
+
+
+def test_raw_gradient_blame_and_brake_scopes():
+    from memarch_b200 import OptConfig
+    from memarch_b200.optim import Instinct
+    torch.manual_seed(0)
+    names = ["light_a.0.up.weight", "fish.up", "heavy.0.up.weight"]
+    ps = [torch.nn.Parameter(torch.randn(8, 8)) for _ in names]
+    a = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, gnorm=True, gnorm_rawrel=True, rel_every=1, snr=True,
+                               snr_skip=("fish.",)), names=names)
+    assert a._snr_on == [True, False, True]
+    b = Instinct(ps, OptConfig(lr=1e-2, norm="hs", scale=0.12, snr=True, snr_only=("light_a.",)), names=names)
+    assert b._snr_on == [True, False, False]
+    a.prepare(torch.tensor(1.0), torch.ones(4))
+    gs = [torch.randn(8, 8) * s for s in (1.0, 10.0, 100.0)]
+    w = [p.detach().clone() for p in ps]
+    for p, g in zip(ps, gs):
+        a.update(p, g.clone())
+    want = torch.stack([g.norm() / (x.norm() + 1e-8) for g, x in zip(gs, w)])
+    assert torch.allclose(a.rel, want, rtol=2e-2) and a.rel[2] > 50 * a.rel[0]    # not the constant of a unit gradient

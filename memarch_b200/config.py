@@ -72,6 +72,25 @@ class ModelConfig:
     heavy_attn_detach: bool = False
     n_draft: int = 0
     draft_loss: float = 0.0
+    # layer pool (models/fishki.py::FishPool): the heavy MoE layers are replaced by fish_n equal FFN layers; every step
+    # is one kind of text and runs through a combination of fish_c layers of that kind's set (FISH_N=<n>)
+    fish_n: int = 0
+    fish_hf: int = 1024           # width of one layer
+    fish_kinds: int = 5
+    fish_pool: int = 17           # layers in a kind's set
+    fish_c: int = 2               # layers per training step
+    fish_eval: bool = False       # finished model: the router picks each row's kind, the row runs the whole set
+    fish_eval_c: int = 0          # ... or a fixed subset of this many layers of the set
+    fish_center: bool = False     # a layer's input without the stream's common vector
+    # "hoop" (models/fishki.py::Uroboros): the heavy layers get the words where the model itself expects to be wrong -
+    # a small head predicts the model's own loss per word - instead of the light head's surprise against a threshold
+    uroboros: bool = False        # UROBOROS=1
+    uroboros_budget: float = 0.25  # share of words sent to the heavy layers (hard top-k)
+    uroboros_levels: Tuple[float, ...] = (0.25, 0.18, 0.12, 0.08)   # budgets the loop may step down through
+    uroboros_eat: float = 1.0     # a word counts as "eaten" when its predicted loss is below this many nats
+    uroboros_w: float = 0.1       # weight of the head's squared error in the loss
+    uroboros_thr: float = -1.0    # >= 0: causal choice (evaluation): a word goes heavy when its prediction exceeds this
+    uroboros_at: str = "light_b"  # where the head reads: "light_b" (after the memory point) | "light_a" (before)
     # anchor-routed long-range read ("tether", models/rope_memory.py) in the light blocks after the memory point,
     # instead of the segment memory and the re-reading (ROPE_MEM=1; sets no_mem)
     rope_mem: bool = False
@@ -285,6 +304,17 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
     if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("FISH_N"):
+        kw["fish_n"] = int(g("FISH_N"))
+        for k_ in ("hf", "kinds", "pool", "c", "eval_c"):
+            if g("FISH_" + k_.upper()): kw["fish_" + k_] = int(g("FISH_" + k_.upper()))
+        for k_ in ("eval", "center"):
+            if g("FISH_" + k_.upper()) == "1": kw["fish_" + k_] = True
+    if g("UROBOROS") == "1" or g("HOOP") == "1":
+        kw["uroboros"] = True
+        for k_, t_ in (("budget", float), ("eat", float), ("w", float), ("thr", float), ("at", str)):
+            if g("UROBOROS_" + k_.upper()): kw["uroboros_" + k_] = t_(g("UROBOROS_" + k_.upper()))
+        if g("UROBOROS_LEVELS"): kw["uroboros_levels"] = tuple(float(v) for v in g("UROBOROS_LEVELS").split(","))
     if g("ROPE_MEM") == "1":
         kw["rope_mem"], kw["no_mem"] = True, True
         for k_, t_ in (("k", int), ("links", int), ("win", int), ("span_cap", int), ("route", str), ("hier_g", int),

@@ -261,6 +261,10 @@ class HostLoader:
                 if self.xform is not None:
                     xy, extra = self.xform(xy, self.n_next)
                     xy = np.ascontiguousarray(xy, dtype=np.int64)
+                if hasattr(self.corpus, "extra"):            # per-kind corpus: the kind and layer combination of the step
+                    kx = self.corpus.extra()
+                    if kx:                                   # (synthetic rows may have changed the number of rows)
+                        extra = dict(extra or {}, **{k: np.repeat(v[:1], len(xy), 0) for k, v in kx.items()})
                 self.n_next += 1
                 x = torch.from_numpy(xy)
                 if self.pin:

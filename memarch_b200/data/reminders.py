@@ -285,7 +285,7 @@ class KindCorpus:
         base = seed if doc_seed is None else doc_seed             # other documents, same schedule of kinds
         self.subs = [ShardCorpus(kinds[k], root, seq=seq, seed=base + 7919 * i, rank=rank, world=world, eos=eos)
                      for i, k in enumerate(self.names)]
-        self.eos = self.subs[0].eos
+        self.eos, self.seq = self.subs[0].eos, seq
         self.pools, self.c, self.seed = pools, int(c), seed
         self.full = False
         self.n = 0

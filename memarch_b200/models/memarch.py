@@ -97,9 +97,14 @@ class MemArchLM(nn.Module):
         self.light_b = nn.ModuleList(blk() for _ in range(c.light_b))
         self.l_norm = nn.RMSNorm(d)
         self.l_head = nn.Sequential(nn.Linear(d, 128, bias=False), nn.Linear(128, vocab, bias=False))
-        self.moe = c.moe
+        self.moe = c.moe and not c.fish_n
         w_dtype = torch.bfloat16 if c.bf16_experts else torch.float32
-        if c.moe:
+        self._fish_aux = None
+        if c.fish_n:
+            from .fishki import FishPool
+            self.fish = FishPool(d, n=c.fish_n, hf=c.fish_hf, kinds=c.fish_kinds, pool=c.fish_pool, center=c.fish_center)
+            self.heavy = nn.ModuleList()
+        elif c.moe:
             self.heavy = nn.ModuleList(
                 AnchorMoE(d, E=c.n_exp, k_avg=c.moe_k if c.bank else 2, k_max=max(4, c.moe_k) if c.bank else 4,
                           budget=c.moe == "budget", wave=c.wave, wave_every=c.wave_every, students=c.students,
@@ -122,6 +127,11 @@ class MemArchLM(nn.Module):
                 self.register_buffer("rope_qtau", torch.tensor(float(c.rope_qtau0)))
         self._tether_mass = None
         self.want_stream_mean = False
+        self._hoop = None
+        if c.uroboros:
+            from .fishki import Uroboros
+            self.hoop = Uroboros(d)
+            self.hoop_budget = c.uroboros_budget         # the training loop may step it down (`Uroboros.next_budget`)
         self.stats = {}
         self.panic = c.panic
         self.short_v = c.short_v
@@ -420,6 +430,7 @@ class MemArchLM(nn.Module):
                 b.cur_ve = self.ve[i](x) if "ve" in c.blk else None
                 b.cur_x0 = h if "x0" in c.blk else None
         h = run_blocks(self.light_a, h, win, self._run)
+        h_a = h if (c.uroboros and c.uroboros_at == "light_a") else None
 
         seg = min(self.seg, T)
         snaps = None
@@ -435,6 +446,9 @@ class MemArchLM(nn.Module):
             h = run_blocks(self.light_b, h, win, self._run)
         lh = ops.rmsnorm(h, self.l_norm.weight, self.l_norm.eps)
 
+        if hasattr(self, "fish"):
+            return self._tail(self._fish_pass(h, lh, prep), lh, x, snaps, seg, win)
+
         # surprise -> anchors: the light part's own prediction error decides where to think hard
         with torch.no_grad():
             if hasattr(self, "sp_lse"):
@@ -442,10 +456,27 @@ class MemArchLM(nn.Module):
             else:
                 s_ = self._light_surprise(lh.detach(), x)
             A = max(1, round(T * self.cap))
-            idx, valid = ops.select_anchors(s_, self.tau, A)        # this step's threshold is the one before its update
-            if self.training:
-                self.tau.mul_(0.9).add_(0.1 * ref.tau_quantile(s_, self.frac))
-            self.stats["anchors"] = valid.float().mean() * A / T
+            if not c.uroboros:
+                idx, valid = ops.select_anchors(s_, self.tau, A)    # this step's threshold is the one before its update
+                if self.training:
+                    self.tau.mul_(0.9).add_(0.1 * ref.tau_quantile(s_, self.frac))
+                self.stats["anchors"] = valid.float().mean() * A / T
+        self._hoop = None
+        if c.uroboros:
+            # the model predicts its own error before the heavy layers and hands them only the words it has not
+            # "eaten" (memarch_jax/memarch_jax/model.py:364-378 of the reference's JAX port)
+            feat = lh if h_a is None else ops.rmsnorm(h_a, self.l_norm.weight, self.l_norm.eps)
+            pred = self.hoop.predict(feat, s_)
+            with torch.no_grad():
+                if c.uroboros_thr >= 0:                  # per word, no ranking over the sequence: causal
+                    idx = torch.arange(T, device=x.device).expand(B, T).contiguous()
+                    valid = pred > c.uroboros_thr
+                    valid[:, 0] = True
+                else:
+                    idx, valid = self.hoop.select(pred, self.hoop_budget)
+                self.stats["anchors"] = valid.float().mean() * idx.shape[1] / T
+            self._hoop = (pred, idx)
+            s_, A = pred.detach(), idx.shape[1]          # what the heavy layers see as the words' surprise
 
         a_in = ops.gather_tokens(h, idx)
         a = a_in
@@ -478,6 +509,37 @@ class MemArchLM(nn.Module):
                 if self.heavy[0].wave == "still":
                     self.stats["move_r"] = sum((b.last_move / b.move_peak.clamp(min=1e-12)).min() for b in self.heavy) / L
 
+        return self._tail(h, lh, x, snaps, seg, win)
+
+    def _fish_pass(self, h, lh, prep):
+        """The layer pool instead of anchors + heavy layers (memarch_jax/memarch_jax/model.py:339-363 of the reference's
+        JAX port).  Training: the whole step is one kind of text (`prep["kind"]`) and every row runs through the step's
+        combination of layers (`prep["fish"]`); a small router learns to tell the kind from the light state.  Finished
+        model (`fish_eval`, or no combination given): the router picks each row's kind and the row runs that kind's
+        whole set, or a fixed subset of `fish_eval_c` layers of it."""
+        c = self.cfg
+        kind = prep.get("kind") if isinstance(prep, dict) else None
+        self._fish_aux = None
+        if kind is not None:
+            ce, acc, logits = self.fish.router_loss(lh, kind.reshape(-1).long())
+            self._fish_aux = ce
+            self.stats["fish_router_acc"] = acc.detach()
+        else:
+            logits = self.fish.router(lh.detach().float().mean(1))
+        order = prep.get("fish") if isinstance(prep, dict) else None
+        if c.fish_eval or order is None:
+            kinds = logits.argmax(-1)
+            out = torch.zeros_like(h)
+            for k, pool in enumerate(self.fish.sets):
+                if 0 < c.fish_eval_c < len(pool):
+                    import numpy as np
+                    pool = [int(v) for v in np.random.default_rng(1000 + k).permutation(pool)[:c.fish_eval_c]]
+                out = out + torch.where((kinds == k)[:, None, None], self.fish(h, pool), torch.zeros_like(h))
+            return out
+        return self.fish(h, [int(i) for i in order.reshape(-1, order.shape[-1])[0].tolist()])
+
+    def _tail(self, h, lh, x, snaps, seg, win):
+        c = self.cfg
         h = run_blocks(self.final, h, win, self._run)
 
         dt = _cdt(h)
@@ -816,6 +878,17 @@ class MemArchLM(nn.Module):
                     loss = loss + checkpoint(self._ce_kept, *part, j, use_reentrant=False)
                 else:
                     loss = loss + self._ce_kept(*part, j)
+        elif train and self._hoop is not None:
+            # the head's target is the model's true error on every word, so the per-word form of the loss runs
+            parts = []
+            for j in range(0, hn.shape[1], 8192):
+                part = (hn[:, j:j + 8192], y[:, j:j + 8192])
+                if self.training and torch.is_grad_enabled():
+                    parts.append(checkpoint(self._nll_tok, *part, j, use_reentrant=False))
+                else:
+                    parts.append(self._nll_tok(*part, j))
+            nll_tok = torch.cat(parts, 1)
+            loss = nll_tok.sum()
         elif train and self.training and self.panic:
             loss = 0
             for j in range(0, hn.shape[1], 8192):
@@ -833,6 +906,10 @@ class MemArchLM(nn.Module):
                 else:
                     loss = loss + self._ce_part(*part, j)
         loss = main = loss / y.numel()
+        if train and self._hoop is not None:
+            pred, hidx = self._hoop
+            loss = loss + c.uroboros_w * self.hoop.loss(pred, nll_tok)
+            self.stats.update(self.hoop.stats(pred, nll_tok, hidx, c.uroboros_eat))
         if rem is not None and (c.remind_w > 0 or c.remind_use_w > 0 or not train):
             term, st = self.remind_term(hn, y, extra)
             self.stats.update(st)
@@ -847,6 +924,8 @@ class MemArchLM(nn.Module):
                 self.stats["remind_rope_share"] = use.detach()
                 if train and c.remind_use_w > 0:
                     loss = loss + c.remind_use_w * (mk.sum() / den - use)
+        if train and self._fish_aux is not None:
+            loss = loss + 0.1 * self._fish_aux                   # the router's cross-entropy
         if train and self.moe:
             loss = loss + 0.01 * sum(b.aux for b in self.heavy) / len(self.heavy)
         if train and len(self.light_a) and hasattr(self.light_a[0], "moe"):

@@ -198,6 +198,15 @@ class _CorpusData:
         held = int(env.get("HELDOUT_TOK", 0))           # tail of every source's last shard kept out of training
         self.corpus = ShardCorpus(w, root, seq=seq, seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world,
                                   heldout_tok=held)
+        if env.get("KINDS"):
+            # layer-pool training: every step is one kind of text, KINDS = {"kind": {"source": weight}}; the batch
+            # carries its kind and the step's combination of layers (validation stays on the CORPUS mix)
+            from ..data.reminders import KindCorpus
+            from ..models.fishki import pools
+            kinds = json.loads(env["KINDS"])
+            sets = pools(len(kinds), int(env["FISH_N"]), int(env.get("FISH_POOL", 17)))
+            self.corpus = KindCorpus(kinds, sets, int(env.get("FISH_C", 2)), root, seq=seq,
+                                     seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world)
         self.loader, self.device, self.seq = None, device, seq
         if env.get("VAL_NPY"):
             self.val = TokenStore(np.load(env["VAL_NPY"]), 0, device)
@@ -436,10 +445,13 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     xy_b = data.batch(args.batch * (args.seq // seq), seq)
                     ts = time.time()
                     npreps = None
-                    if (rb is None and getattr(data, "remind", None) is not None and data.extra is not None
-                            and max(getattr(getattr(tr.model, "cfg", None), "remind_w", 0),
-                                    getattr(getattr(tr.model, "cfg", None), "remind_use_w", 0)) > 0):
-                        npreps = needle_preps(tr.model, xy_b, data.extra, tr.cfg.micro or len(xy_b))
+                    ex_ = getattr(data, "extra", None)
+                    mc_ = getattr(tr.model, "cfg", None)
+                    if rb is None and ex_ is not None and (
+                            "kind" in ex_ or ("rem" in ex_ and max(getattr(mc_, "remind_w", 0), getattr(mc_, "remind_use_w", 0)) > 0)):
+                        npreps = needle_preps(tr.model, xy_b, ex_, tr.cfg.micro or len(xy_b))
+                        if "kind" in ex_:
+                            tr.card = int(ex_["kind"][0, 0])        # OptConfig.card_by_kind: one card per kind of text
                     loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1, npreps)
                     phase["data"] += ts - td
                     phase["enqueue"] += time.time() - ts
@@ -485,8 +497,18 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     extra = "".join(f"  {k} {float(v):.2f}" for k, v in getattr(tr.model, "stats", {}).items()
                                     if torch.is_tensor(v) and v.numel() == 1)
                     sets = run_evals()
+                    hoop = getattr(tr.model, "hoop", None)
+                    if hoop is not None and "uroboros_eaten" in tr.model.stats:
+                        # the heavy layers' budget steps down one level once enough words are "eaten"
+                        st_ = tr.model.stats
+                        nb = hoop.next_budget(tr.model.hoop_budget, st_["uroboros_eaten"], tr.model.cfg.uroboros_levels,
+                                              corr=st_["uroboros_corr"])
+                        if nb != tr.model.hoop_budget:
+                            print(f"hoop: budget {tr.model.hoop_budget} -> {nb} (eaten {float(st_['uroboros_eaten']):.2f})",
+                                  file=out, flush=True)
+                            tr.model.hoop_budget = nb
                     rm = getattr(data, "remind", None)
-                    if rm is not None and data.extra is not None and data.extra["rem"].any():
+                    if rm is not None and data.extra is not None and "rem" in data.extra and data.extra["rem"].any():
                         hits, n_ans = needle_hits(tr.model, xy_b, torch.from_numpy(data.extra["rem"]).to(tr.device) > 0,
                                                   data.extra.get("rem_y"))
                         sets["needles"] = hits / max(n_ans, 1.0)
@@ -535,8 +557,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
 
 
 def needle_preps(model, xy, extra, micro):
-    """One `prep` dict per micro-batch that carries the needle masks of the data pipeline as device tensors under
-    "remind" (the model's loss reads them).  Where the model has induction locks they are switched off at the question
+    """One `prep` dict per micro-batch that carries what the data pipeline knows about the batch as device tensors:
+    the needle masks under "remind" (the model's loss reads them) and, with a per-kind corpus, "kind" and "fish".  Where the model has induction locks they are switched off at the question
     positions: the lock "last earlier occurrence of this word -> the word after it" would hand over the answer
     without any memory (memarch_jax/memarch_jax/data.py:333-341 of the reference)."""
     ex = {k: torch.from_numpy(np.ascontiguousarray(v)).to(xy.device, non_blocking=True) for k, v in extra.items()}
@@ -544,9 +566,14 @@ def needle_preps(model, xy, extra, micro):
     for i0 in range(0, len(xy), micro):
         sl = {k: v[i0:i0 + micro] for k, v in ex.items()}
         pr = model.prep(xy[i0:i0 + micro, :-1]) if hasattr(model, "ind_a") and hasattr(model, "prep") else {}
-        if "ind_on" in pr:
-            pr["ind_on"] = pr["ind_on"] & ~(sl["rem"] > 0)[..., None]
-        pr["remind"] = sl
+        needles = {k: v for k, v in sl.items() if k.startswith("rem")}
+        if needles:
+            if "ind_on" in pr:
+                pr["ind_on"] = pr["ind_on"] & ~(sl["rem"] > 0)[..., None]
+            pr["remind"] = needles
+        for k in ("kind", "fish"):                       # layer pool: the step's kind of text and combination of layers
+            if k in sl:
+                pr[k] = sl[k]
         out.append(pr)
     return out
 

@@ -604,3 +604,72 @@ def test_tether_inside_the_main_model():
     assert hasattr(m2.light_b[0], "tether_out") and torch.isfinite(o2[0]).all()
     if len(m2.light_b) > 1:
         assert not hasattr(m2.light_b[1], "tether_out")
+
+
+def test_hoop_inside_the_main_model():
+    from memarch_b200 import build
+    from memarch_b200.models.fishki import Uroboros
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2", "UROBOROS": "1", "UROBOROS_BUDGET": "0.25", "UROBOROS_W": "0.2"}
+    m = build("tiny", 256, env=env).train()
+    assert isinstance(m.hoop, Uroboros) and m.hoop_budget == 0.25
+    xy = torch.randint(0, 256, (2, 65))
+    x, y = xy[:, :-1], xy[:, 1:]
+    tau0 = float(m.tau)
+    out, _ = m(x)
+    pred, idx = m._hoop
+    assert idx.shape == (2, 16) and bool((idx[:, 0] == 0).all()) and float(m.tau) == tau0     # a budget, no threshold
+    assert abs(float(m.stats["anchors"]) - 0.25) < 1e-6
+    top = pred.detach().clone()
+    top[:, 0] = 1e9
+    assert torch.equal(idx, top.topk(16, -1).indices.sort(-1).values)                         # the words it fears most
+    loss = m.train_loss(out, y, True)
+    lo = m._logits(out[0]).float()
+    nll = torch.nn.functional.cross_entropy(lo.reshape(-1, 256), y.reshape(-1), reduction="none").view_as(y)
+    for k in ("uroboros_eaten", "uroboros_corr", "uroboros_nll_sel", "uroboros_nll_skip"):
+        assert k in m.stats
+    m._hoop = None
+    base = m.train_loss(out, y, True)                                                         # same terms without the head's
+    want = 0.2 * (pred.clamp(0, 20) - nll.clamp(0, 20)).pow(2).mean()
+    assert abs(float(loss - base) - float(want)) < 1e-4
+    m._hoop = (pred, idx)
+    m.train_loss(out, y, True).backward()
+    assert m.hoop.l1.weight.grad.abs().sum() > 0 and m.head.weight.grad.abs().sum() > 0
+    # causal choice by a threshold (evaluation), and the head before the memory point
+    m2 = build("tiny", 256, env=dict(env, UROBOROS_THR="2.5", UROBOROS_AT="light_a")).eval()
+    with torch.no_grad():
+        o2, _ = m2(x)
+    p2, i2 = m2._hoop
+    assert i2.shape == (2, 64) and torch.isfinite(o2[0]).all()
+    assert abs(float(m2.stats["anchors"]) - float(((p2 > 2.5) | (torch.arange(64) == 0)).float().mean())) < 1e-6
+
+
+def test_layer_pool_inside_the_main_model():
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "FISH_N": "8", "FISH_HF": "64", "FISH_KINDS": "3", "FISH_POOL": "4", "FISH_C": "2"}
+    m = build("tiny", 256, env=env).train()
+    assert len(m.heavy) == 0 and not m.moe and m.fish.up.shape[0] == 8 and len(m.fish.sets) == 3
+    xy = torch.randint(0, 256, (3, 49))
+    x, y = xy[:, :-1], xy[:, 1:]
+    order = m.fish.sets[1][:2]
+    prep = {"kind": torch.full((3, 1), 1), "fish": torch.tensor([order] * 3)}
+    out, _ = m(x, prep)
+    loss = m.train_loss(out, y, True)
+    assert "fish_router_acc" in m.stats and m._fish_aux is not None
+    loss.backward()
+    used = {i for i in range(8) if m.fish.up.grad[i].abs().sum() > 0}
+    assert used == set(order) and m.fish.router.weight.grad.abs().sum() > 0                  # only the step's layers work
+    base = float(loss) - 0.1 * float(m._fish_aux)
+    m._fish_aux = None
+    assert abs(float(m.train_loss(out, y, True)) - base) < 1e-5
+    # finished model: the router sends each row through the whole set of its kind
+    m.eval()
+    with torch.no_grad():
+        a, _ = m(x)
+    assert torch.isfinite(a[0]).all()
+    m2 = build("tiny", 256, env=dict(env, FISH_EVAL="1", FISH_EVAL_C="2")).eval()
+    m2.load_state_dict(m.state_dict())
+    with torch.no_grad():
+        b, _ = m2(x, prep)
+    assert torch.isfinite(b[0]).all() and not torch.allclose(a[0], b[0])                     # a subset of the set

@@ -983,3 +983,26 @@ def test_raw_gradient_blame_and_brake_scopes():
         a.update(p, g.clone())
     want = torch.stack([g.norm() / (x.norm() + 1e-8) for g, x in zip(gs, w)])
     assert torch.allclose(a.rel, want, rtol=2e-2) and a.rel[2] > 50 * a.rel[0]    # not the constant of a unit gradient
+
+
+def test_layer_pool_training_by_kind_through_the_loop(tmp_path, monkeypatch):
+    from memarch_b200.train.loop import make_data, train
+    monkeypatch.chdir(tmp_path)
+    w = make_corpus(str(tmp_path / "corpus"), docs=60)
+    env = {"VOCAB": "2048", "NO_MEM": "1", "WATCHDOG": "0", "CORPUS": json.dumps(w), "CORPUS_ROOT": str(tmp_path / "corpus"),
+           "KINDS": json.dumps({"prose": {"web": 2.0}, "formal": {"code": 1.0}}), "FISH_N": "6", "FISH_HF": "64",
+           "FISH_KINDS": "2", "FISH_POOL": "4", "FISH_C": "2",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12, "card_by_kind": True, "cards": 3})}
+    a = Args(seq=48, batch=4, micro=4, steps=6, eval_every=3)
+    data = make_data(a, "cpu", env)
+    kinds = []
+    for _ in range(6):
+        data.batch(4, 48)
+        ex = data.extra
+        assert ex["kind"].shape == (4, 1) and ex["fish"].shape == (4, 2)
+        kinds.append(int(ex["kind"][0, 0]))
+    assert kinds.count(0) == 4 and kinds.count(1) == 2                     # 2:1 by the weights of the kinds
+    data.loader.close()
+    buf = io.StringIO()
+    log = train(a, "cpu", env=env, out=buf)["tiny"]
+    assert all(math.isfinite(e["val"]) for e in log) and "fish_router_acc" in buf.getvalue()

@@ -72,6 +72,9 @@ class ModelConfig:
     heavy_attn_detach: bool = False
     n_draft: int = 0
     draft_loss: float = 0.0
+    heavy_rotate: bool = False    # HEAVY_ROTATE: every heavy_full_every-th step one heavy layer (in rotation) runs on ALL words
+    heavy_full_every: int = 1
+    heavy_all: bool = False       # HEAVY_ALL: every heavy layer on all words (last phase / finished model)
     # layer pool (models/fishki.py::FishPool): the heavy MoE layers are replaced by fish_n equal FFN layers; every step
     # is one kind of text and runs through a combination of fish_c layers of that kind's set (FISH_N=<n>)
     fish_n: int = 0
@@ -304,6 +307,9 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
     if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("HEAVY_ROTATE") == "1": kw["heavy_rotate"] = True
+    if g("HEAVY_FULL_EVERY"): kw["heavy_full_every"] = int(g("HEAVY_FULL_EVERY"))
+    if g("HEAVY_ALL") == "1": kw["heavy_all"] = True
     if g("FISH_N"):
         kw["fish_n"] = int(g("FISH_N"))
         for k_ in ("hf", "kinds", "pool", "c", "eval_c"):

@@ -100,6 +100,7 @@ class MemArchLM(nn.Module):
         self.moe = c.moe and not c.fish_n
         w_dtype = torch.bfloat16 if c.bf16_experts else torch.float32
         self._fish_aux = None
+        self._hfull = -1
         if c.fish_n:
             from .fishki import FishPool
             self.fish = FishPool(d, n=c.fish_n, hf=c.fish_hf, kinds=c.fish_kinds, pool=c.fish_pool, center=c.fish_center)
@@ -484,11 +485,32 @@ class MemArchLM(nn.Module):
         if self.moe:
             sa = torch.where(valid, s_.gather(1, idx).clamp(0, 50), torch.full_like(s_[:, :A], -1.0))
         ctx = h.detach() if c.heavy_attn_detach else h
-        for li, b in enumerate(self.heavy):
-            if hasattr(self, "h_attn"):
-                a = self.h_attn[li](a, ctx, idx)
-            a = self._run(b, a, sa, heavy=True)
-        h = ops.scatter_back(h, idx, (a - a_in) * valid[..., None])
+        full = self._full_layer(prep)
+        if full is None:
+            for li, b in enumerate(self.heavy):
+                if hasattr(self, "h_attn"):
+                    a = self.h_attn[li](a, ctx, idx)
+                a = self._run(b, a, sa, heavy=True)
+            h = ops.scatter_back(h, idx, (a - a_in) * valid[..., None])
+        else:
+            # a "full" layer works on all words instead of the anchors only: the anchors' states are written into the
+            # stream, the layer runs over every word (all places real: fill 1), the anchors are read back; the order
+            # of the layers does not change (memarch_jax/memarch_jax/moe.py:298-354 of the reference's JAX port)
+            gi = idx[..., None].expand(-1, -1, h.shape[-1])
+            put = lambda hh, a_: hh.scatter(1, gi, torch.where(valid[..., None], a_.to(hh.dtype), hh.gather(1, gi)))
+            s_all = s_.clamp(0, 50) if self.moe else None
+            hh = h
+            for li, b in enumerate(self.heavy):
+                if hasattr(self, "h_attn"):
+                    a = self.h_attn[li](a, ctx, idx)
+                if full < 0 or full == li:
+                    fill, b.fill = b.fill, 1.0
+                    hh = self._run(b, put(hh, a), s_all, heavy=True)
+                    b.fill = fill
+                    a = hh.gather(1, gi)
+                else:
+                    a = self._run(b, a, sa, heavy=True)
+            h = put(hh, a)
         if self.n_draft:
             an = self.draft_norm(a)
             self._drafts = []
@@ -510,6 +532,17 @@ class MemArchLM(nn.Module):
                     self.stats["move_r"] = sum((b.last_move / b.move_peak.clamp(min=1e-12)).min() for b in self.heavy) / L
 
         return self._tail(h, lh, x, snaps, seg, win)
+
+    def _full_layer(self, prep):
+        """None: every heavy layer on the anchors.  -1: every layer on all words (`heavy_all`).  k: layer k on all
+        words in this step - from `prep["hfull"]`, or by rotation over the steps (`heavy_rotate`, set by `before_step`)."""
+        c = self.cfg
+        if c.heavy_all:
+            return -1
+        if not c.heavy_rotate or not self.training:
+            return None
+        k = int(prep["hfull"].reshape(-1)[0]) if isinstance(prep, dict) and "hfull" in prep else self._hfull
+        return k if 0 <= k < len(self.heavy) else None
 
     def _fish_pass(self, h, lh, prep):
         """The layer pool instead of anchors + heavy layers (memarch_jax/memarch_jax/model.py:339-363 of the reference's
@@ -970,6 +1003,10 @@ class MemArchLM(nn.Module):
         return changes
 
     def before_step(self, step):
+        c = self.cfg
+        if c.heavy_rotate and len(self.heavy):
+            k = max(1, c.heavy_full_every)
+            self._hfull = (step // k) % len(self.heavy) if step % k == 0 else -1
         for b in self.heavy:
             if hasattr(b, "before_step"):
                 b.before_step(step)

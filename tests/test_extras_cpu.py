@@ -673,3 +673,46 @@ def test_layer_pool_inside_the_main_model():
     with torch.no_grad():
         b, _ = m2(x, prep)
     assert torch.isfinite(b[0]).all() and not torch.allclose(a[0], b[0])                     # a subset of the set
+
+
+def test_heavy_layers_on_all_words():
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2"}
+    base = build("tiny", 256, env=env).train()
+    rot = build("tiny", 256, env=dict(env, HEAVY_ROTATE="1", HEAVY_FULL_EVERY="2")).train()
+    full = build("tiny", 256, env=dict(env, HEAVY_ALL="1")).train()
+    rot.load_state_dict(base.state_dict())
+    full.load_state_dict(base.state_dict())
+    L = len(base.heavy)
+    x = torch.randint(0, 256, (2, 64))
+    # the rotation: every second step one layer, in turn
+    seen = []
+    for step in range(2 * L + 2):
+        rot.before_step(step)
+        seen.append(rot._hfull)
+    assert seen[:4] == [0, -1, 1 % L, -1] and seen[2 * L] == 0
+    for m in (base, rot, full):
+        m.tau.fill_(5.0)
+    rot.before_step(1)                                                     # no full layer in this step: the plain model
+    a, _ = base(x)
+    b, _ = rot(x)
+    assert torch.allclose(a[0], b[0], atol=1e-5)
+    rot.tau.fill_(5.0)
+    rot.before_step(0)                                                     # layer 0 on all words
+    c, _ = rot(x)
+    assert not torch.allclose(a[0], c[0], atol=1e-4)
+    rot.tau.fill_(5.0)
+    d, _ = rot(x, {"hfull": torch.full((2, 1), L - 1)})                    # the step's data may name the layer
+    assert not torch.allclose(c[0], d[0], atol=1e-4) or L == 1
+    e, _ = full(x)
+    assert torch.isfinite(e[0]).all() and not torch.allclose(a[0], e[0], atol=1e-4)
+    # words that are no anchors change only through a full layer
+    e[0].square().mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in full.heavy[0].parameters() if p.requires_grad)
+    rot.eval()
+    with torch.no_grad():
+        base.eval()
+        f, _ = rot(x)
+        g, _ = base(x)
+    assert torch.allclose(f[0], g[0], atol=1e-5)                           # evaluation: anchors only

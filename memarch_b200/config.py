@@ -72,6 +72,12 @@ class ModelConfig:
     heavy_attn_detach: bool = False
     n_draft: int = 0
     draft_loss: float = 0.0
+    norm_dump_proj: bool = False  # NORM_DUMP_PROJ: the final norm removes the component along the stream's common direction
+    safe_norm_ratio: float = 0.0  # SAFE_NORM_RATIO: after the final norm the common vector is capped at ratio x the words' signal
+    safe_norm_t0: int = 256
+    hn_guard_w: float = 0.0       # HN_GUARD_W: hinge penalty on the trunk: |row mean of hn| > hn_guard_mean or mean |hn| > hn_guard_len
+    hn_guard_mean: float = 15.0
+    hn_guard_len: float = 42.0
     heavy_rotate: bool = False    # HEAVY_ROTATE: every heavy_full_every-th step one heavy layer (in rotation) runs on ALL words
     heavy_full_every: int = 1
     heavy_all: bool = False       # HEAVY_ALL: every heavy layer on all words (last phase / finished model)
@@ -307,6 +313,12 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
     if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("NORM_DUMP_PROJ") == "1": kw["norm_dump_proj"] = True
+    if g("SAFE_NORM_RATIO"): kw["safe_norm_ratio"] = float(g("SAFE_NORM_RATIO"))
+    if g("SAFE_NORM_T0"): kw["safe_norm_t0"] = int(g("SAFE_NORM_T0"))
+    if g("HN_GUARD_W"): kw["hn_guard_w"] = float(g("HN_GUARD_W"))
+    if g("HN_GUARD_MEAN"): kw["hn_guard_mean"] = float(g("HN_GUARD_MEAN"))
+    if g("HN_GUARD_LEN"): kw["hn_guard_len"] = float(g("HN_GUARD_LEN"))
     if g("HEAVY_ROTATE") == "1": kw["heavy_rotate"] = True
     if g("HEAVY_FULL_EVERY"): kw["heavy_full_every"] = int(g("HEAVY_FULL_EVERY"))
     if g("HEAVY_ALL") == "1": kw["heavy_all"] = True

@@ -101,6 +101,7 @@ class MemArchLM(nn.Module):
         w_dtype = torch.bfloat16 if c.bf16_experts else torch.float32
         self._fish_aux = None
         self._hfull = -1
+        self.stream_u = None                             # running common direction of the stream (the trainer copies the optimizer's U here)
         if c.fish_n:
             from .fishki import FishPool
             self.fish = FishPool(d, n=c.fish_n, hf=c.fish_hf, kinds=c.fish_kinds, pool=c.fish_pool, center=c.fish_center)
@@ -582,7 +583,15 @@ class MemArchLM(nn.Module):
             h = h + o.type_as(h)
         if self.want_stream_mean:                     # for the optimizer's rules on the stream's common vector
             self.stats["stream_mean"] = h.detach().float().mean((0, 1))
-        return (ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt), lh), cost
+        if c.norm_dump_proj:                          # the common vector is taken out whatever channel it sits in
+            from ..ops.extras import dump_proof_norm
+            hn = dump_proof_norm(h, self.norm.weight, self.stream_u, self.norm.eps or 1e-6).to(dt)
+        else:
+            hn = ops.rmsnorm(h, self.norm.weight, self.norm.eps, out_dtype=dt)
+        if c.safe_norm_ratio > 0:
+            from ..ops.extras import cap_shared
+            hn = cap_shared(hn, c.safe_norm_ratio, c.safe_norm_t0)
+        return (hn, lh), cost
 
     def _tether_pass(self, h, x, win):
         """The light blocks after the memory point with the anchor-routed read instead of plain attention
@@ -957,6 +966,15 @@ class MemArchLM(nn.Module):
                 self.stats["remind_rope_share"] = use.detach()
                 if train and c.remind_use_w > 0:
                     loss = loss + c.remind_use_w * (mk.sum() / den - use)
+        if train and c.hn_guard_w > 0:
+            # hinge on the trunk after the final norm: nothing (value and gradient zero) while the row mean of hn and
+            # the mean length of hn stay under their thresholds (memarch_jax/memarch_jax/model.py:539-551)
+            h32 = hn.float()
+            mn = (h32.mean(1).pow(2).sum(-1) + 1e-12).sqrt()
+            ln = (h32.pow(2).sum(-1) + 1e-12).sqrt().mean(1)
+            over = lambda v, thr: (v / thr - 1.0).clamp(min=0.0).pow(2).mean()
+            self.stats["hn_mean"], self.stats["hn_len"] = mn.mean().detach(), ln.mean().detach()
+            loss = loss + c.hn_guard_w * (over(mn, c.hn_guard_mean) + over(ln, c.hn_guard_len))
         if train and self._fish_aux is not None:
             loss = loss + 0.1 * self._fish_aux                   # the router's cross-entropy
         if train and self.moe:

@@ -141,6 +141,8 @@ class Trainer:
             if self.parallel is not None and hasattr(self.parallel, "mean_vector"):
                 sm = self.parallel.mean_vector(sm.clone())
             self.opt.observe_stream(sm)
+            if hasattr(self.model, "stream_u"):
+                self.model.stream_u = self.opt.U         # the final norm's `norm_dump_proj` uses the same direction
 
     def situation(self, xy):
         with torch.no_grad():

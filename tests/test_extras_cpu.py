@@ -716,3 +716,38 @@ def test_heavy_layers_on_all_words():
         f, _ = rot(x)
         g, _ = base(x)
     assert torch.allclose(f[0], g[0], atol=1e-5)                           # evaluation: anchors only
+
+
+def test_final_norm_variants_and_trunk_guard_in_the_model():
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2"}
+    base = build("tiny", 256, env=env).train()
+    x = torch.randint(0, 256, (2, 64))
+    y = torch.randint(0, 256, (2, 64))
+    a, _ = base(x)
+    dp = build("tiny", 256, env=dict(env, NORM_DUMP_PROJ="1")).train()
+    dp.load_state_dict(base.state_dict())
+    dp.tau.fill_(float(5.0)); base.tau.fill_(5.0)
+    u = torch.randn(dp.cfg.d)
+    dp.stream_u = u
+    b, _ = dp(x)
+    uh = u / u.norm()
+    w = dp.norm.weight.detach().float()
+    assert ((b[0].float() / w) @ uh).abs().max() < 1e-4                    # nothing along the common direction
+    cap = build("tiny", 256, env=dict(env, SAFE_NORM_RATIO="0.05", SAFE_NORM_T0="8")).train()
+    cap.load_state_dict(base.state_dict())
+    c_, _ = cap(x)
+    a2, _ = base(x)
+    assert torch.equal(c_[0][:, :8], a2[0][:, :8]) and not torch.equal(c_[0][:, 8:], a2[0][:, 8:])
+    g = build("tiny", 256, env=dict(env, HN_GUARD_W="2.0", HN_GUARD_MEAN="0.01", HN_GUARD_LEN="1000")).train()
+    g.load_state_dict(base.state_dict())
+    o, _ = g(x)
+    with_guard = g.train_loss(o, y, True)
+    o2, _ = base(x)
+    plain = base.train_loss(o2, y, True)
+    assert float(with_guard) > float(plain) and float(g.stats["hn_mean"]) > 0.01 and "hn_len" in g.stats
+    quiet = build("tiny", 256, env=dict(env, HN_GUARD_W="2.0", HN_GUARD_MEAN="1e6", HN_GUARD_LEN="1e6")).train()
+    quiet.load_state_dict(base.state_dict())
+    o3, _ = quiet(x)
+    assert abs(float(quiet.train_loss(o3, y, True)) - float(base.train_loss(base(x)[0], y, True))) < 1e-3

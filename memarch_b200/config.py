@@ -72,6 +72,20 @@ class ModelConfig:
     heavy_attn_detach: bool = False
     n_draft: int = 0
     draft_loss: float = 0.0
+    # "instinct on words" (INST_WORD=1): nothing extra for a word guessed well (p >= iw_ok); a gentle push of the right
+    # word up to iw_target where the distribution is smeared (leader < iw_spread); the one wrong word the model is sure
+    # of (leader != target, p > iw_cw) is pressed down to iw_cw, no further
+    inst_word: bool = False
+    iw_ok: float = 0.5
+    iw_spread: float = 0.35
+    iw_target: float = 0.3
+    iw_spread_w: float = 0.2
+    iw_cw: float = 0.5
+    iw_cw_w: float = 0.1
+    iw_rewrite: bool = False      # IW_REWRITE: the rewritten answer as target: the right word +delta, its top competitors -delta
+    iw_delta: float = 0.05
+    iw_random: bool = False       # IW_RANDOM: -delta goes to one random word per row instead (no top-k)
+    iw_k: int = 4
     norm_dump_proj: bool = False  # NORM_DUMP_PROJ: the final norm removes the component along the stream's common direction
     safe_norm_ratio: float = 0.0  # SAFE_NORM_RATIO: after the final norm the common vector is capped at ratio x the words' signal
     safe_norm_t0: int = 256
@@ -313,6 +327,13 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))
     if g("DRAFT_LOSS"): kw["draft_loss"] = float(g("DRAFT_LOSS"))
+    if g("INST_WORD") == "1":
+        kw["inst_word"] = True
+        for k_ in ("ok", "spread", "target", "spread_w", "cw", "cw_w", "delta"):
+            if g("IW_" + k_.upper()): kw["iw_" + k_] = float(g("IW_" + k_.upper()))
+        if g("IW_K"): kw["iw_k"] = int(g("IW_K"))
+        for k_ in ("rewrite", "random"):
+            if g("IW_" + k_.upper()) == "1": kw["iw_" + k_] = True
     if g("NORM_DUMP_PROJ") == "1": kw["norm_dump_proj"] = True
     if g("SAFE_NORM_RATIO"): kw["safe_norm_ratio"] = float(g("SAFE_NORM_RATIO"))
     if g("SAFE_NORM_T0"): kw["safe_norm_t0"] = int(g("SAFE_NORM_T0"))

@@ -101,6 +101,7 @@ class MemArchLM(nn.Module):
         w_dtype = torch.bfloat16 if c.bf16_experts else torch.float32
         self._fish_aux = None
         self._hfull = -1
+        self._mix = self._tongue = None
         self.stream_u = None                             # running common direction of the stream (the trainer copies the optimizer's U here)
         if c.fish_n:
             from .fishki import FishPool
@@ -810,6 +811,56 @@ class MemArchLM(nn.Module):
     def _ce_kept(self, hn, y, keep, j):
         return (self._nll_tok(hn, y, j) * keep).sum()
 
+    # ------------------------------------------------------------------------------------------ instinct on words
+    def _iw_part(self, hn, y, mult, j):
+        """Sums over the positions j.. of the rows: [term, smeared, sure-but-wrong, fine, acted on] (term not yet
+        divided by the number of words).  Probabilities are those of the full softmax of the head.
+        (memarch_jax/memarch_jax/model.py:563-650 of the reference's JAX port)"""
+        c = self.cfg
+        lo = self._logits(hn)
+        if self._mix is None and self._tongue is not None:
+            cand, val = self._tongue
+            lo = lo.scatter_add(-1, cand[:, j:j + y.shape[1]].long(), val[:, j:j + y.shape[1]].float())
+        lsm = lo.log_softmax(-1)
+        lp = lsm.gather(-1, y[..., None])[..., 0]
+        ok = lp.detach().exp() >= c.iw_ok
+        if c.iw_random:
+            # the right word is known: +delta for it, -delta for ONE random other word per row; the rewritten answer
+            # q = p + d (e_right - e_other) as a cross-entropy target gives the gradient d (e_other - e_right): two
+            # words only, sum zero; d = min(delta, p_other), a word cannot give more than it has
+            V = lo.shape[-1]
+            h_ = (y.sum(1) * 2654435761 + 40503 * torch.arange(len(y), device=y.device)) % (self.short_v or V)
+            other = self.sv_ids[h_] if self.short_v else h_
+            lpo = lsm.gather(-1, other[:, None, None].expand(-1, y.shape[1], 1))[..., 0]
+            act = ~ok & (other[:, None] != y)
+            d_eff = lpo.detach().exp().clamp(max=c.iw_delta)
+            term = mult * (d_eff * (lpo - lp) * act).sum()
+            spread, cw = act, torch.zeros_like(act)
+        elif c.iw_rewrite:
+            # ... or for the top competitors of the right word, in proportion to what each of them has
+            pk, ipk = lsm.detach().exp().topk(c.iw_k + 1, -1)
+            rival = ipk != y[..., None]
+            sel = rival & (rival.long().cumsum(-1) <= c.iw_k)
+            pc = torch.where(sel, pk, torch.zeros_like(pk))
+            S = pc.sum(-1)
+            act = ~ok & (S > 0)
+            d_eff = S.clamp(max=c.iw_delta)
+            w = pc / S.clamp(min=1e-30)[..., None]
+            d = (w * lsm.gather(-1, ipk)).sum(-1) - lp
+            term = mult * (d_eff * d * act).sum()
+            spread = ~ok & (pk[..., 0] < c.iw_spread)
+            cw = ~ok & (pk[..., 0] > c.iw_cw) & (ipk[..., 0] != y)
+        else:
+            lpt, top = lsm.max(-1)
+            p_top = lpt.detach().exp()
+            spread = ~ok & (p_top < c.iw_spread)
+            cw = ~ok & (p_top > c.iw_cw) & (top != y)
+            act = spread | cw
+            l_sp = (math.log(c.iw_target) - lp).clamp(min=0.0) * spread
+            l_cw = (-torch.log1p(-lpt.exp().clamp(max=1 - 1e-6)) + math.log1p(-c.iw_cw)).clamp(min=0.0) * cw
+            term = c.iw_spread_w * l_sp.sum() + c.iw_cw_w * mult * l_cw.sum()
+        return torch.stack([term] + [t.float().sum() for t in (spread, cw, ok, act)])
+
     # ------------------------------------------------------------------------------------------ recall needles
     def _logp_rows(self, h, tok, add=None):
         """log P(tok[:, j]) under the output distribution at the states h (N,D), for every column j of tok (N,J)."""
@@ -966,6 +1017,17 @@ class MemArchLM(nn.Module):
                 self.stats["remind_rope_share"] = use.detach()
                 if train and c.remind_use_w > 0:
                     loss = loss + c.remind_use_w * (mk.sum() / den - use)
+        if train and c.inst_word:
+            mult = extra.get("iw_mult", 1.0) if isinstance(extra, dict) else 1.0
+            tot = 0
+            for j in range(0, hn.shape[1], 2048):
+                part = (hn[:, j:j + 2048], y[:, j:j + 2048], mult, j)
+                tot = tot + (checkpoint(self._iw_part, *part, use_reentrant=False)
+                             if self.training and torch.is_grad_enabled() else self._iw_part(*part))
+            tot = tot / y.numel()
+            loss = loss + tot[0]
+            self.stats.update({"iw": tot[0].detach(), "iw_spread_frac": tot[1].detach(), "iw_cw_frac": tot[2].detach(),
+                               "iw_ok_frac": tot[3].detach(), "iw_act_frac": tot[4].detach()})
         if train and c.hn_guard_w > 0:
             # hinge on the trunk after the final norm: nothing (value and gradient zero) while the row mean of hn and
             # the mean length of hn stay under their thresholds (memarch_jax/memarch_jax/model.py:539-551)

@@ -751,3 +751,59 @@ def test_final_norm_variants_and_trunk_guard_in_the_model():
     quiet.load_state_dict(base.state_dict())
     o3, _ = quiet(x)
     assert abs(float(quiet.train_loss(o3, y, True)) - float(base.train_loss(base(x)[0], y, True))) < 1e-3
+
+
+def test_instinct_on_words_terms():
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2"}
+    base = build("tiny", 256, env=env).train()
+    x, y = torch.randint(0, 256, (2, 48)), torch.randint(0, 256, (2, 48))
+    o, _ = base(x)
+    plain = float(base.train_loss(o, y, True))
+    lsm = base._logits(o[0]).float().log_softmax(-1).detach()
+    lp = lsm.gather(-1, y[..., None])[..., 0]
+    ok = lp.exp() >= 0.02
+    lpt, top = lsm.max(-1)
+
+    def model(**kw):
+        m = build("tiny", 256, env=dict(env, INST_WORD="1", IW_OK="0.02", **kw)).train()
+        m.load_state_dict(base.state_dict())
+        m.tau.fill_(float(5.0))
+        return m
+    base.tau.fill_(5.0)
+    # base form: smeared distributions are pushed up to the target, a confident wrong leader is pressed down
+    m = model(IW_SPREAD="0.5", IW_TARGET="0.3", IW_CW="0.01", IW_SPREAD_W="0.2", IW_CW_W="0.1")
+    o1, _ = m(x)
+    total = m.train_loss(o1, y, True)
+    spread = ~ok & (lpt.exp() < 0.5)
+    cw = ~ok & (lpt.exp() > 0.01) & (top != y)
+    l_sp = ((math.log(0.3) - lp).clamp(min=0) * spread).sum()
+    l_cw = ((-torch.log1p(-lpt.exp().clamp(max=1 - 1e-6)) + math.log1p(-0.01)).clamp(min=0) * cw).sum()
+    want = (0.2 * l_sp + 0.1 * l_cw) / y.numel()
+    assert abs(float(total) - plain - float(want)) < 1e-4 and float(want) > 0
+    assert abs(float(m.stats["iw_ok_frac"]) - float(ok.float().mean())) < 1e-6
+    assert abs(float(m.stats["iw_spread_frac"]) - float(spread.float().mean())) < 1e-6
+    total.backward()
+    assert torch.isfinite(m.head.weight.grad).all()
+    # rewritten answer: the gradient on the logits touches the right word and its k competitors only, and sums to zero
+    for kw in (dict(IW_REWRITE="1", IW_K="3", IW_DELTA="0.05"), dict(IW_RANDOM="1", IW_DELTA="0.05")):
+        m = model(**kw)
+        hn = o[0].detach().clone().requires_grad_(True)
+        lo_holder = {}
+        real = m._logits
+
+        def spy(h_):
+            lo_holder["lo"] = real(h_)
+            lo_holder["lo"].retain_grad()
+            return lo_holder["lo"]
+        m._logits = spy
+        part = m._iw_part(hn, y, 1.0, 0)
+        part[0].backward()
+        g = lo_holder["lo"].grad
+        assert g.sum(-1).abs().max() < 1e-6
+        n_touched = (g.abs() > 1e-7).sum(-1)
+        assert int(n_touched.max()) <= (4 if "IW_REWRITE" in kw else 2)
+        acted = n_touched > 0
+        assert bool((g.gather(-1, y[..., None])[..., 0][acted] < 0).all())      # the right word goes up
+        assert abs(float(part[4]) - float(acted.sum())) < 1e-6 and float(part[0]) != 0

@@ -105,3 +105,40 @@ def test_legacy_families_run_on_device(name):
     assert abs(loss_g.item() - loss_c.item()) < 2e-2 * max(1.0, abs(loss_c.item()))
     assert abs(float(cost_g.detach()) - float(cost_c.detach())) < 2e-2 * max(1.0, abs(float(cost_c.detach())))
     assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in mg.parameters())
+
+
+@pytest.mark.parametrize("name,env", [
+    ("tether", {"ROPE_MEM": "1", "ROPE_WIN": "16", "ROPE_SPAN_CAP": "24", "ROPE_LINKS": "3", "ROPE_K": "2", "ROPE_HIER_G": "4",
+                "ROPE_HIER_BM": "32", "ROPE_CHUNK": "64", "ROPE_QFRAC": "0.7", "REMIND_USE_W": "0.5"}),
+    ("hoop", {"UROBOROS": "1", "UROBOROS_BUDGET": "0.25"}),
+    ("pool", {"FISH_N": "6", "FISH_HF": "128", "FISH_KINDS": "2", "FISH_POOL": "4"}),
+    ("all_words", {"HEAVY_ALL": "1"}),
+    ("words", {"INST_WORD": "1", "IW_OK": "0.05", "IW_REWRITE": "1", "NORM_DUMP_PROJ": "1", "HN_GUARD_W": "1.0",
+               "HN_GUARD_MEAN": "0.1"}),
+    ("needles", {"REMIND_CAND": "1", "REMIND_MASK_MAIN": "1", "REMIND_STRICT": "1"}),
+])
+def test_main_model_switches_device_matches_cpu(name, env):
+    """The experiment switches of the main model (anchor-routed read, hoop, layer pool, heavy layers on all words,
+    word-level rules, needle terms): loss on the device against the same weights on the CPU, and a finite backward."""
+    from memarch_b200 import build
+    dev = _dev()
+    torch.manual_seed(0)
+    e = {"NO_MEM": "1", "MOE_ACT": "relu2", "REMIND_W": "1.0", "REMIND_N": "4", "REMIND_TOK0": "100"}
+    e.update(env)
+    mc = build("tiny", 1024, env=e).train()
+    mg = copy.deepcopy(mc).to(dev)
+    xy = torch.randint(0, 1024, (2, 129))
+    rem = torch.zeros(2, 128, dtype=torch.int8)
+    rem[:, 90:98:2] = 1
+    xy[:, 91:99:2] = torch.randint(612, 676, (2, 4))                       # targets of the answers: value tokens (< vocabulary)
+    extra = {"rem": rem, "rem_vals": xy[:, 91:99:2].int()}
+    prep = {"kind": torch.ones(2, 1, dtype=torch.long), "fish": torch.tensor([mc.fish.sets[1][:2]] * 2)} if name == "pool" else None
+    on = lambda t, d: {k: v.to(d) for k, v in t.items()} if t is not None else None
+    losses = []
+    for m, d in ((mc, torch.device("cpu")), (mg, dev)):
+        out, cost = m(xy[:, :-1].to(d), on(prep, d))
+        loss = m.train_loss(out, xy[:, 1:].to(d), True, extra=on(extra, d))
+        loss.backward()
+        losses.append(float(loss))
+        assert all(torch.isfinite(p.grad).all() for p in m.parameters() if p.grad is not None)
+    assert abs(losses[0] - losses[1]) < 3e-2 * max(1.0, abs(losses[0])), (name, losses)

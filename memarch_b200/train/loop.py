@@ -341,11 +341,15 @@ def train(args, device=None, env=None, out=None, parallel=None):
     env = os.environ if env is None else env
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     rank, world = int(env.get("RANK", 0)), int(env.get("WORLD_SIZE", env.get("WORLD", 1)))
+    from .diag import Diag
+    diag = Diag(env, out)
     data = make_data(args, device, env, rank, world)
+    diag.phase("data ready")
     bpu = float(env.get("BYTES_PER_UNIT", 4.6361))
     logs = {}
     for name in args.models:
         tr = make_trainer(name, args.stage, args, device, env, parallel)
+        diag.phase(f"model {name} and optimizer built")
         cfg, apply, micro0 = _schedules(args, env, tr)
         log, train_time = [], 0.0
         ck = None
@@ -426,6 +430,9 @@ def train(args, device=None, env=None, out=None, parallel=None):
         try:
             for step in range(start, last + 1):
                 seq = apply(cfg(step))
+                diag.step(step)
+                if step == start + 1:
+                    diag.phase("first step enqueued")
                 pn = env.get("PANIC")
                 if pn:
                     pfrac, pw = (float(x) for x in pn.split(":"))
@@ -537,6 +544,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     ck.save(tr, step, log, data.state_dict())
                     phase["ckpt"] += time.time() - tc
         finally:
+            diag.close()
             if dog:
                 dog.close()
             if ck is not None:

@@ -1006,3 +1006,23 @@ def test_layer_pool_training_by_kind_through_the_loop(tmp_path, monkeypatch):
     buf = io.StringIO()
     log = train(a, "cpu", env=env, out=buf)["tiny"]
     assert all(math.isfinite(e["val"]) for e in log) and "fish_router_acc" in buf.getvalue()
+
+
+def test_total_diagnostics_of_a_run(tmp_path, monkeypatch):
+    from memarch_b200.train.diag import Diag
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    quiet = io.StringIO()
+    d = Diag({}, quiet)
+    d.phase("x"), d.step(50), d.close()
+    assert quiet.getvalue() == ""                                          # off: nothing at all
+    buf = io.StringIO()
+    env = {"VOCAB": "512", "NO_MEM": "1", "WATCHDOG": "0", "DIAG": "1", "DIAG_EVERY": "2", "DIAG_PROF": "2",
+           "DIAG_DIR": str(tmp_path / "tr"), "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
+    train(Args(seq=32, batch=2, micro=2, steps=6, eval_every=6), "cpu", env=env, out=buf)
+    text = buf.getvalue()
+    for want in ("[diag] phase 'start'", "phase 'data ready'", "phase 'model tiny and optimizer built'",
+                 "phase 'first step enqueued'", "[diag] step 2:", "[diag] step 4:", "host RSS", "trace: started at step 2"):
+        assert want in text, want
+    trace = tmp_path / "tr" / "trace_step2.json"
+    assert trace.exists() and trace.stat().st_size > 1000 and "trace: written" in text

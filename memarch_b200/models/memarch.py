@@ -102,6 +102,7 @@ class MemArchLM(nn.Module):
         self._fish_aux = None
         self._hfull = -1
         self._mix = self._tongue = None
+        self._vp = None
         self.stream_u = None                             # running common direction of the stream (the trainer copies the optimizer's U here)
         if c.fish_n:
             from .fishki import FishPool
@@ -359,12 +360,46 @@ class MemArchLM(nn.Module):
 
     @torch.no_grad()
     def table_rows(self, x):
+        if self._vp is not None:                         # row-sharded tables: the rows of all ranks' tokens move
+            return {}
         rows = {id(self.emb.weight): x.reshape(-1)}
         if hasattr(self, "phr"):
             rows[id(self.phr.weight)] = self._phr_idx(x).reshape(-1)
         if hasattr(self, "phr4"):
             rows[id(self.phr4.weight)] = self._phr4_idx(x).reshape(-1)
         return rows
+
+    # ------------------------------------------------------------------------------------------ vocabulary parallel
+    def vocab_shard(self, rank, world, group=None):
+        """Vocabulary parallelism (the JAX port's `VocabShard`, memarch_jax/memarch_jax/dist.py:106-187): keep rows
+        [rank V/W, (rank+1) V/W) of the input table, of the output head and of the light head's output table.  Every
+        rank serves its rows for the tokens of all ranks (`parallel/vocab.py`); the losses are computed per token of
+        the rank's own rows, so everything built on them (pointer mixture, auxiliary terms) is unchanged.  The shards
+        are rank-local parameters whose gradient sums over all ranks' tokens: a hook divides it by W.
+        Not combined with: the short-vocabulary head, the frequency bias, the tongue tables, the needle terms."""
+        from ..parallel import vocab as vp
+        if self.short_v or hasattr(self, "head_bias") or hasattr(self, "tg_a"):
+            raise NotImplementedError("vocabulary parallelism: short-vocabulary head / head bias / tongue tables are not sharded")
+        assert self.vocab % world == 0, "vocabulary rows must divide by the world size"
+        self._vp = (rank, world, group, rank * (self.vocab // world))
+        for mod in (self.emb, self.head, self.l_head[1]):
+            shard = nn.Parameter(vp.shard_rows(mod.weight.detach(), rank, world)[0])
+            shard._ep_local = True
+            shard._vocab_table = mod.weight.shape[0] >= 10000     # stays a word table for the optimizer, whatever its slice
+            shard.register_hook(lambda g, w=world: g / w)
+            mod.weight = shard
+        return self
+
+    def _emb_rows(self, ids):
+        if self._vp is None:
+            return self.emb(ids)
+        from ..parallel import vocab as vp
+        return vp.take_dp(self.emb.weight, ids, self._vp[3], self._vp[2])
+
+    def _nll_vp(self, h, w, y):
+        """Per-token -log softmax(h W^T)[y] against a row-sharded table: (B,T)."""
+        from ..parallel import vocab as vp
+        return vp.nll_dp(h.reshape(-1, h.shape[-1]).float(), w.float(), y.reshape(-1), self._vp[3], self._vp[2]).view_as(y)
 
     # ------------------------------------------------------------------------------------------ forward
     def _run(self, blk, *a, heavy=False):
@@ -380,8 +415,8 @@ class MemArchLM(nn.Module):
         win = self.window if T > self.window else None
         # on the GPU the token row, the gated candidate rows (INDUCT_IN) and the phrase row are summed by one kernel
         # further down; `h` stays None until then
-        fuse_in = not c.resid_bf16 and ops._ext.use_cuda(self.emb.weight)
-        h = None if fuse_in else self.emb(x)
+        fuse_in = not c.resid_bf16 and ops._ext.use_cuda(self.emb.weight) and self._vp is None
+        h = None if fuse_in else self._emb_rows(x)
         if c.resid_bf16 and x.is_cuda:
             h = h.to(torch.bfloat16)
         in_cand = in_sel = None
@@ -399,7 +434,7 @@ class MemArchLM(nn.Module):
                 if h is None:
                     in_cand, in_sel = cand, sel
                 else:
-                    h = h + (self.emb(cand) * sel[..., None]).sum(2).type_as(h)
+                    h = h + (self._emb_rows(cand) * sel[..., None]).sum(2).type_as(h)
         if hasattr(self, "tg_a"):
             self._tongue = self._tongue_from_tables(x)
         if h is None:
@@ -646,6 +681,9 @@ class MemArchLM(nn.Module):
         B, T = x.shape
         s_ = torch.full((B, T), 1e4, device=x.device)
         w0, W2 = self.l_head[0].weight, self.l_head[1].weight
+        if self._vp is not None:
+            s_[:, 1:] = self._nll_vp(ops.linear(lhd[:, :-1], w0), W2, x[:, 1:])
+            return s_
         ch = self.cfg.ce_chunk
         for j in range(0, T - 1, 8192):
             hj = lhd[:, j:min(j + 8192, T - 1)]
@@ -719,6 +757,8 @@ class MemArchLM(nn.Module):
         return ops.linear_ce(hn, w, y)
 
     def _logits(self, hn):
+        if self._vp is not None:
+            raise NotImplementedError("full logits are not formed under vocabulary parallelism")
         lo = ops.linear(hn, self.head.weight).float()
         if hasattr(self, "head_bias"):
             lo = lo + self.head_bias.float()
@@ -783,7 +823,12 @@ class MemArchLM(nn.Module):
         mix = self._mix
         tongue = self._tongue if mix is None else None
         B_, T_ = y.shape
-        if c.ce_chunk and tongue is None:
+        if self._vp is not None:
+            if tongue is not None:
+                raise NotImplementedError("vocabulary parallelism: lock votes added to the logits need the full row; use the pointer mixture")
+            nll = self._nll_vp(hn, self.head.weight, y)
+            lse, ly = nll, torch.zeros_like(nll)
+        elif c.ce_chunk and tongue is None:
             if self.short_v:
                 logp = self._short_logp(hn.reshape(B_ * T_, -1), y.reshape(-1)).view(B_, T_)
                 lse, ly = torch.zeros_like(logp), logp
@@ -988,7 +1033,7 @@ class MemArchLM(nn.Module):
                 ce = checkpoint(self._ce_tok, hn[:, j:j + 8192], y[:, j:j + 8192], use_reentrant=False)
                 w = (ce / ce.mean()).detach().clamp(0.25, 4.0) ** self.panic
                 loss = loss + (ce * (w / w.mean())).sum()
-        elif c.fused_ce and self.training and not self.short_v:
+        elif c.fused_ce and self.training and not self.short_v and self._vp is None:
             loss = self._fused_ce(hn, y)
         else:
             loss = 0
@@ -1056,7 +1101,9 @@ class MemArchLM(nn.Module):
             V = self.head.out_features
             h4, y4 = lh[:, ::4], y[:, ::4]
             h128 = ops.linear(h4, self.l_head[0].weight)
-            if c.ce_chunk:
+            if self._vp is not None:
+                loss = loss + 0.3 * self._nll_vp(h128, self.l_head[1].weight, y4).mean()
+            elif c.ce_chunk:
                 lse, ly = ops.chunk_ce(h128.reshape(-1, h128.shape[-1]), self.l_head[1].weight, None, y4.reshape(-1),
                                        c.ce_chunk)
                 loss = loss + 0.3 * (lse - ly).mean()

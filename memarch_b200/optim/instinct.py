@@ -210,7 +210,7 @@ class Instinct:
     # ------------------------------------------------------------------------------------------ per-weight step
     def spec(self, p):
         """(kind, has weight decay, is a word table) from the weight's shape (exp_opt.py:653-665)."""
-        vocab_table = p.dim() == 2 and p.shape[0] >= 10000
+        vocab_table = p.dim() == 2 and (p.shape[0] >= 10000 or getattr(p, "_vocab_table", False))
         n = "hs" if self.norm == "hs1" else self.norm          # one homeostasis round is the plain form
         if vocab_table:
             kind = "vocab"

@@ -53,7 +53,7 @@ def take(shard, ids, lo, group=None):
 
 
 class _ShardCE(torch.autograd.Function):
-    """Sum over rows of (global LSE − correct logit); h (N,d) replicated rows, head shard (Vs,d)."""
+    """Per row: global LSE − correct logit; h (N,d) replicated rows, head shard (Vs,d).  Returns (N,) fp32."""
 
     @staticmethod
     def forward(ctx, h, w, y, lo, group, chunk):
@@ -77,7 +77,7 @@ class _ShardCE(torch.autograd.Function):
         lse = m + acc[0].log()
         ctx.save_for_backward(h, w, local, mine, lse)
         ctx.chunk, ctx.group = chunk, group
-        return (lse - acc[1]).sum()
+        return lse - acc[1]
 
     @staticmethod
     def backward(ctx, go):
@@ -85,21 +85,28 @@ class _ShardCE(torch.autograd.Function):
         N, Vs = h.shape[0], w.shape[0]
         gh = torch.zeros_like(h, dtype=torch.float32)
         gw = torch.zeros_like(w, dtype=torch.float32)
+        go = go.float()
         for i in range(0, N, ctx.chunk):
             hc = h[i:i + ctx.chunk]
             p = ((hc @ w.t()).float() - lse[i:i + ctx.chunk, None]).exp()
             rows = torch.arange(p.shape[0], device=h.device)[mine[i:i + ctx.chunk]]
             p[rows, local[i:i + ctx.chunk][mine[i:i + ctx.chunk]]] -= 1.0
+            p = p * go[i:i + ctx.chunk, None]                                 # each row's own cotangent
             gh[i:i + ctx.chunk] = p @ w.float()
             gw += p.t() @ hc.float()
         if dist.is_initialized():
             dist.all_reduce(gh, group=ctx.group)                              # every slice contributes to dh
-        return (gh * go).to(h.dtype), (gw * go).to(w.dtype), None, None, None, None
+        return gh.to(h.dtype), gw.to(w.dtype), None, None, None, None
+
+
+def nll(h, head_shard, y, lo, group=None, chunk=4096):
+    """Per-token cross-entropy (N,) with the head sharded by vocabulary rows; h rows are the same on every rank."""
+    return _ShardCE.apply(h.reshape(-1, h.shape[-1]), head_shard, y.reshape(-1), lo, group, chunk)
 
 
 def ce(h, head_shard, y, lo, group=None, chunk=4096):
     """Summed token cross-entropy with the head sharded by vocabulary rows."""
-    return _ShardCE.apply(h.reshape(-1, h.shape[-1]), head_shard, y.reshape(-1), lo, group, chunk)
+    return nll(h, head_shard, y, lo, group, chunk).sum()
 
 
 # ------------------------------------------------------------------------------------------------ rank-local data
@@ -151,6 +158,14 @@ def take_dp(shard, ids, lo, group=None):
     flat = _gather(ids.reshape(-1), group)
     rows = _OwnRows.apply(take(shard, flat, lo, group), group)
     return rows.view(*ids.shape, shard.shape[-1])
+
+
+def nll_dp(h, head_shard, y, lo, group=None, chunk=4096):
+    """Per-token cross-entropy of this rank's OWN tokens, h (N, d), y (N,), with the head sharded by vocabulary rows.
+    In the backward every rank receives the cotangents of all ranks' tokens, so a head shard's gradient is the sum
+    over the tokens of all ranks (divide by W for the gradient of a rank-mean loss)."""
+    hg = _AllRows.apply(h.reshape(-1, h.shape[-1]), group)
+    return _OwnRows.apply(nll(hg, head_shard, _gather(y.reshape(-1), group), lo, group, chunk), group)
 
 
 def ce_dp(h, head_shard, y, lo, group=None, chunk=4096):

@@ -338,6 +338,66 @@ def test_vocab_parallel_transformer_matches_the_unsharded_one():
         assert r["qkv"] < 1e-4 and r["emb"] < 1e-4 and r["head"] < 1e-4, r
 
 
+def _w_vp_main(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from memarch_b200.config import ModelConfig
+    from memarch_b200.models.memarch import MemArchLM
+    V, T = 64, 24
+
+    def make():
+        torch.manual_seed(0)
+        c = ModelConfig(vocab=V, d=32, heads=2, light_a=1, light_b=1, heavy=1, final=1, window=16, seg=8, moe="",
+                        no_mem=True, frac=0.3, cap=0.5, induct="lock", induct_mix=True, induct_in=True)
+        return MemArchLM(c).train()
+    full, vpm = make(), make()
+    vpm.vocab_shard(rank, world)
+    g = torch.Generator().manual_seed(7)
+    xy_all = torch.randint(0, 12, (2 * world, T + 1), generator=g)        # few distinct words: the locks fire often
+    mine = xy_all[2 * rank:2 * rank + 2]
+    out, _ = vpm(mine[:, :-1])
+    loss = vpm.train_loss(out, mine[:, 1:])
+    loss.backward()
+    out_f, _ = full(xy_all[:, :-1])
+    loss_f = full.train_loss(out_f, xy_all[:, 1:])
+    loss_f.backward()
+    lm = loss.detach().clone()
+    dist.all_reduce(lm)
+    res = {"loss": (float(lm / world), float(loss_f)), "tau": (float(vpm.tau), float(full.tau))}
+    for nm in ("light_a.0.qkv.weight", "heavy.0.up.weight", "l_head.0.weight", "norm.weight"):
+        a, b = dict(vpm.named_parameters())[nm].grad.clone(), dict(full.named_parameters())[nm].grad
+        dist.all_reduce(a)
+        res[nm] = float((a / world - b).abs().max() / b.abs().max().clamp(min=1e-9))
+    lo, hi = rank * V // world, (rank + 1) * V // world
+    for nm in ("emb.weight", "head.weight", "l_head.1.weight"):
+        a, b = dict(vpm.named_parameters())[nm].grad, dict(full.named_parameters())[nm].grad[lo:hi]
+        res[nm] = float((a - b).abs().max() / b.abs().max().clamp(min=1e-9))
+        res[nm + ".rows"] = a.shape[0]
+    q.put((rank, res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_main_model_matches_the_unsharded_one():
+    """MemArchLM with emb, head and the light head's output table row-sharded over 2 ranks, each rank on its own rows
+    of the batch: the rank-mean loss, the replicated weights' rank-mean gradients and the shards' gradients equal
+    those of the unsharded model on the whole batch."""
+    world, port = 2, 29671
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_vp_main, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = [q.get(timeout=240) for _ in ps]
+    [p.join(30) for p in ps]
+    for _, r in res:
+        assert abs(r["loss"][0] - r["loss"][1]) < 1e-5, r
+        for nm in ("light_a.0.qkv.weight", "heavy.0.up.weight", "l_head.0.weight", "norm.weight", "emb.weight", "head.weight",
+                   "l_head.1.weight"):
+            assert r[nm] < 2e-4, (nm, r)
+        assert r["emb.weight.rows"] == 32 and r["l_head.1.weight.rows"] == 32
+
+
 def _w_ckpt(rank, world, port, folder, q):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))

@@ -92,6 +92,8 @@ class ModelConfig:
     hn_guard_w: float = 0.0       # HN_GUARD_W: hinge penalty on the trunk: |row mean of hn| > hn_guard_mean or mean |hn| > hn_guard_len
     hn_guard_mean: float = 15.0
     hn_guard_len: float = 42.0
+    attn_gain: float = 1.0        # ATTN_GAIN: multiplier of the light blocks' attention scores
+    prev_in: bool = False         # PREV_IN: every word also receives the previous word's input vector through a learned gate
     heavy_rotate: bool = False    # HEAVY_ROTATE: every heavy_full_every-th step one heavy layer (in rotation) runs on ALL words
     heavy_full_every: int = 1
     heavy_all: bool = False       # HEAVY_ALL: every heavy layer on all words (last phase / finished model)
@@ -137,9 +139,11 @@ class ModelConfig:
     rope_qfrac: float = 1.0       # share of words that read the tether at all (the rest: window only)
     rope_qtau0: float = 5.0
     rope_doc_eos: int = -1        # >= 0: anchors of another document than the query's are not opened
+    rope_pcut: float = 0.0        # ROPE_PCUT: tethered layers rotate only frequencies with a wavelength <= this many words
     rope_key_diag: bool = False   # statistics: how many needle keys the search can see
     remind_use_w: float = 0.0     # REMIND_USE_W: penalty mean(1 - tether share) on the needle questions
     # loss on the answers of recall needles (data.reminders); 0 = the batch's "rem" mask is only scored, not trained on
+    remind_w_synth: float = -1.0  # REMIND_W_SYNTH: the weight on synthetic steps (-1: remind_w); lets the text weight move alone
     remind_w: float = 0.0         # REMIND_W: weight of the term (sum of the answers' NLL / (B * remind_q))
     remind_q: int = 16            # questions per needle row (the normaliser)
     remind_cap: int = 0           # answers read per row (0: remind_q); more with several needles per row
@@ -340,6 +344,8 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("HN_GUARD_W"): kw["hn_guard_w"] = float(g("HN_GUARD_W"))
     if g("HN_GUARD_MEAN"): kw["hn_guard_mean"] = float(g("HN_GUARD_MEAN"))
     if g("HN_GUARD_LEN"): kw["hn_guard_len"] = float(g("HN_GUARD_LEN"))
+    if g("ATTN_GAIN"): kw["attn_gain"] = float(g("ATTN_GAIN"))
+    if g("PREV_IN") == "1": kw["prev_in"] = True
     if g("HEAVY_ROTATE") == "1": kw["heavy_rotate"] = True
     if g("HEAVY_FULL_EVERY"): kw["heavy_full_every"] = int(g("HEAVY_FULL_EVERY"))
     if g("HEAVY_ALL") == "1": kw["heavy_all"] = True
@@ -358,7 +364,8 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
         kw["rope_mem"], kw["no_mem"] = True, True
         for k_, t_ in (("k", int), ("links", int), ("win", int), ("span_cap", int), ("route", str), ("hier_g", int),
                        ("hier_nb", int), ("hier_bm", int), ("chunk", int), ("layers", int), ("tau0", float),
-                       ("frac", float), ("cap", float), ("qfrac", float), ("qtau0", float), ("doc_eos", int)):
+                       ("frac", float), ("cap", float), ("qfrac", float), ("qtau0", float), ("doc_eos", int),
+                       ("pcut", float)):
             if g("ROPE_" + k_.upper()): kw["rope_" + k_] = t_(g("ROPE_" + k_.upper()))
         for k_ in ("share_route", "anchor_top", "key_diag"):
             if g("ROPE_" + k_.upper()) == "1": kw["rope_" + k_] = True
@@ -366,6 +373,7 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
         if g("ROPE_RGRAD") == "0": kw["rope_rgrad"] = False
     if g("REMIND_USE_W"): kw["remind_use_w"] = float(g("REMIND_USE_W"))
     if g("REMIND_W"): kw["remind_w"] = float(g("REMIND_W"))
+    if g("REMIND_W_SYNTH"): kw["remind_w_synth"] = float(g("REMIND_W_SYNTH"))
     if g("REMIND_N"): kw["remind_q"] = int(g("REMIND_N"))
     if g("REMIND_PER_ROW"): kw["remind_cap"] = int(g("REMIND_PER_ROW")) * int(g("REMIND_N") or 16)
     for k_ in ("mean", "only", "cand", "mask_main", "strict"):

@@ -64,6 +64,7 @@ class LightBlock(nn.Module):
     def __init__(self, d, heads, blk=(), light_ffn=0.0, light_moe="", vocab_heads=None, rope_half=False):
         super().__init__()
         self.heads, self.blk, self.rope_half = heads, set(blk), rope_half
+        self.attn_gain, self.tether_pcut = 1.0, 0.0      # sharper attention scores; p-RoPE of a tethered layer
         self.n1 = nn.RMSNorm(d)
         self.qkv = nn.Linear(d, 3 * d, bias=False)
         self.o = nn.Linear(d, d, bias=False)
@@ -119,6 +120,8 @@ class LightBlock(nn.Module):
         else:
             n1 = ops.rmsnorm(x, self.n1.weight, self.n1.eps, out_dtype=dt)
         qkv = ops.linear(n1, self.qkv.weight, direct=True).view(B, T, 3, self.heads, hd)
+        if self.attn_gain != 1.0:
+            qkv = torch.stack([qkv[:, :, 0] * self.attn_gain, qkv[:, :, 1], qkv[:, :, 2]], 2)
         if self.cur_ve is not None:
             g = 2 * torch.sigmoid(F.linear(x, self.ve_gate.weight.to(x.dtype)))[..., None]        # (B,T,H,1)
             v = qkv[:, :, 2] + (g * self.cur_ve.view(B, T, self.heads, hd)).to(qkv.dtype)
@@ -129,7 +132,7 @@ class LightBlock(nn.Module):
             q, k, v = qkv.permute(2, 0, 3, 1, 4)
             if "qk" in self.blk:
                 q, k = F.rms_norm(q, (hd,)), F.rms_norm(k, (hd,))
-            cos, sin = ref.rope_angles(T, hd, x.device)
+            cos, sin = ref.rope_angles(T, hd, x.device, pcut=self.tether_pcut)
             q, k = ref.apply_rope(q, cos, sin, self.rope_half), ref.apply_rope(k, cos, sin, self.rope_half)
             own, apos, avalid, rcfg, routed, qmask, docs = tether
             a, share, route, mass = rope_attention(q, k, v, own, apos, avalid, rcfg, routed, qmask, docs, want_mass=True)

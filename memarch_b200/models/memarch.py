@@ -121,6 +121,12 @@ class MemArchLM(nn.Module):
         for b in self.heavy:
             b.fill = c.frac / c.cap
         self.final = nn.ModuleList(blk() for _ in range(c.final))
+        for b in list(self.light_a) + list(self.light_b) + list(self.final):
+            b.attn_gain = c.attn_gain
+        for b in self.light_b:
+            b.tether_pcut = c.rope_pcut
+        if c.prev_in:
+            self.prev_g = nn.Parameter(torch.full((1,), -1.0))
         self.reread = Reread(d)
         self.norm = nn.RMSNorm(d)
         self.head = nn.Linear(d, vocab, bias=False)
@@ -449,6 +455,9 @@ class MemArchLM(nn.Module):
                 xs = torch.cat([x[:, :1].expand(-1, o - 1), x[:, :-(o - 1)]], 1)
                 m = (torch.arange(T, device=x.device) >= o - 1).to(h.dtype)[None, :, None]
                 h = h + t(xs).type_as(h) * m
+        if c.prev_in:                                  # the word knows the word before it (as a two-word lock would)
+            e0 = self._emb_rows(x).type_as(h)
+            h = h + torch.sigmoid(self.prev_g).type_as(h) * torch.cat([torch.zeros_like(e0[:, :1]), e0[:, :-1]], 1)
         if hasattr(self, "smear"):
             h = torch.cat([h[:, :1], h[:, 1:] + torch.sigmoid(self.smear(h[:, 1:])) * h[:, :-1]], 1)
         lights = list(self.light_a) + list(self.light_b)
@@ -1052,7 +1061,8 @@ class MemArchLM(nn.Module):
             term, st = self.remind_term(hn, y, extra)
             self.stats.update(st)
             if train:
-                loss = loss + c.remind_w * term
+                synth = bool(extra.get("synth", False)) if isinstance(extra, dict) else False
+                loss = loss + (c.remind_w_synth if (synth and c.remind_w_synth >= 0) else c.remind_w) * term
                 if c.remind_only:                         # stage one: the answers only (auxiliary terms stay)
                     loss = loss - main
             mass = getattr(self, "_tether_mass", None)

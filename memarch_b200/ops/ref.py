@@ -32,8 +32,12 @@ def swiglu(gu):
 
 
 # ----------------------------------------------------------------------------------------------- rope / attention
-def rope_angles(T, hd, device, base=10000.0, pos=None):
+def rope_angles(T, hd, device, base=10000.0, pos=None, pcut=0.0):
+    """`pcut` > 0: only the frequencies whose wavelength 2 pi / inv is at most `pcut` words rotate; the other
+    dimensions carry no position at all (memarch_jax/memarch_jax/prims.py:48-58 of the reference's JAX port)."""
     inv = 1.0 / base ** (torch.arange(0, hd, 2, device=device).float() / hd)
+    if pcut > 0:
+        inv = torch.where(2 * math.pi / inv <= pcut, inv, torch.zeros_like(inv))
     p = torch.arange(T, device=device).float() if pos is None else pos.float()
     ang = p[:, None] * inv[None]
     return ang.cos(), ang.sin()

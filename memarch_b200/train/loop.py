@@ -205,8 +205,10 @@ class _CorpusData:
             from ..models.fishki import pools
             kinds = json.loads(env["KINDS"])
             sets = pools(len(kinds), int(env["FISH_N"]), int(env.get("FISH_POOL", 17)))
+            reseed = int(env.get("DATA_RESEED", -1))         # a control: other documents, the same schedule of kinds and layers
             self.corpus = KindCorpus(kinds, sets, int(env.get("FISH_C", 2)), root, seq=seq,
-                                     seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world)
+                                     seed=int(env.get("CORPUS_SEED", 0)), rank=rank, world=world,
+                                     doc_seed=reseed if reseed >= 0 else None)
         self.loader, self.device, self.seq = None, device, seq
         if env.get("VAL_NPY"):
             self.val = TokenStore(np.load(env["VAL_NPY"]), 0, device)
@@ -393,6 +395,14 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 logs[name] = log
                 del tr
                 continue
+        ramp, text_seen = int(env.get("TEXT_LR_RAMP", 0)), 0
+        fish_full = int(env.get("FISH_FULL_FROM", -1))
+        if start > 1 and env.get("OPT_RESET_GAIN") == "1" and hasattr(tr.opt, "gain"):
+            tr.opt.gain.fill_(1.0)                              # resume with every card's gains back at 1
+        rm0 = getattr(data, "remind", None)
+        if rm0 is not None and rm0.pack is not None and env.get("REMIND_PACK_LEVEL") and len(rm0.pack.changes) == 1:
+            # resume from a checkpoint without the episode curriculum's state: continue from this step of the table
+            rm0.pack.changes = [(0, min(int(env["REMIND_PACK_LEVEL"]), len(rm0.pack.steps) - 1))]
         nan = NanGuard(int(env.get("NAN_EVERY", 10)))
         nan_at = int(env.get("TRAIN_NAN_AT", 0))              # inject a non-finite loss at this step (on the host)
         spikes = SpikeLog(float(env.get("SPIKE", 2.0)))
@@ -451,15 +461,24 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     td = time.time()
                     xy_b = data.batch(args.batch * (args.seq // seq), seq)
                     ts = time.time()
-                    npreps = None
+                    npreps, lr_mul_ = None, 1.0
+                    if fish_full >= 0 and step >= fish_full and hasattr(getattr(data, "corpus", None), "full"):
+                        data.corpus.full = True              # last phase: every step runs the whole set of its kind
                     ex_ = getattr(data, "extra", None)
                     mc_ = getattr(tr.model, "cfg", None)
                     if rb is None and ex_ is not None and (
                             "kind" in ex_ or ("rem" in ex_ and max(getattr(mc_, "remind_w", 0), getattr(mc_, "remind_use_w", 0)) > 0)):
-                        npreps = needle_preps(tr.model, xy_b, ex_, tr.cfg.micro or len(xy_b))
+                        rm_ = getattr(data, "remind", None)
+                        synth_ = bool(rm_ is not None and rm_.synth_at(data.loader.n_done - 1))
+                        npreps = needle_preps(tr.model, xy_b, ex_, tr.cfg.micro or len(xy_b), synth_)
+                        if ramp and rm_ is not None and not synth_:
+                            # after the synthetic stage the step on TEXT batches grows from 0 to full over `ramp`
+                            # text batches (synthetic batches keep the full step); the count is not checkpointed
+                            text_seen += 1
+                            lr_mul_ = min(1.0, text_seen / ramp)
                         if "kind" in ex_:
                             tr.card = int(ex_["kind"][0, 0])        # OptConfig.card_by_kind: one card per kind of text
-                    loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1, npreps)
+                    loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1, npreps, lr_mul_)
                     phase["data"] += ts - td
                     phase["enqueue"] += time.time() - ts
                     phase["n"] += 1
@@ -564,7 +583,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
     return logs
 
 
-def needle_preps(model, xy, extra, micro):
+def needle_preps(model, xy, extra, micro, synth=False):
     """One `prep` dict per micro-batch that carries what the data pipeline knows about the batch as device tensors:
     the needle masks under "remind" (the model's loss reads them) and, with a per-kind corpus, "kind" and "fish".  Where the model has induction locks they are switched off at the question
     positions: the lock "last earlier occurrence of this word -> the word after it" would hand over the answer
@@ -578,7 +597,7 @@ def needle_preps(model, xy, extra, micro):
         if needles:
             if "ind_on" in pr:
                 pr["ind_on"] = pr["ind_on"] & ~(sl["rem"] > 0)[..., None]
-            pr["remind"] = needles
+            pr["remind"] = dict(needles, synth=synth)
         for k in ("kind", "fish"):                       # layer pool: the step's kind of text and combination of layers
             if k in sl:
                 pr[k] = sl[k]

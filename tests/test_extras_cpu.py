@@ -807,3 +807,37 @@ def test_instinct_on_words_terms():
         acted = n_touched > 0
         assert bool((g.gather(-1, y[..., None])[..., 0][acted] < 0).all())      # the right word goes up
         assert abs(float(part[4]) - float(acted.sum())) < 1e-6 and float(part[0]) != 0
+
+
+def test_small_switches_of_the_light_blocks_and_inputs():
+    from memarch_b200 import build
+    from memarch_b200.ops import ref
+    cos, sin = ref.rope_angles(16, 32, "cpu", pcut=40.0)
+    cos0, _ = ref.rope_angles(16, 32, "cpu")
+    inv = 1.0 / 10000.0 ** (torch.arange(0, 32, 2).float() / 32)
+    rot = 2 * math.pi / inv <= 40.0
+    assert 0 < int(rot.sum()) < 16 and torch.equal(cos[:, rot], cos0[:, rot])
+    assert bool((cos[:, ~rot] == 1).all()) and bool((sin[:, ~rot] == 0).all())
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2"}
+    base = build("tiny", 256, env=env).eval()
+    x = torch.randint(0, 256, (2, 48))
+    with torch.no_grad():
+        a, _ = base(x)
+        for kw in ({"ATTN_GAIN": "1.5"}, {"PREV_IN": "1"},
+                   {"ROPE_MEM": "1", "ROPE_WIN": "8", "ROPE_SPAN_CAP": "12", "ROPE_K": "2", "ROPE_PCUT": "16"}):
+            m = build("tiny", 256, env=dict(env, **kw)).eval()
+            missing = m.load_state_dict(base.state_dict(), strict=False)
+            assert set(missing.missing_keys) <= {"prev_g", "rope_tau"} and not missing.unexpected_keys
+            b, _ = m(x)
+            assert torch.isfinite(b[0]).all() and not torch.allclose(a[0], b[0], atol=1e-4), kw
+        assert m.light_b[0].tether_pcut == 16.0 and m.light_a[0].tether_pcut == 0.0
+    g = build("tiny", 256, env=dict(env, REMIND_W="1.0", REMIND_W_SYNTH="3.0", REMIND_N="4")).train()
+    o, _ = g(x)
+    y = torch.randint(0, 256, (2, 48))
+    rem = torch.zeros(2, 48, dtype=torch.int8)
+    rem[:, 30:38:2] = 1
+    plain = float(g.train_loss(o, y, True))
+    text = float(g.train_loss(o, y, True, extra={"rem": rem, "synth": False})) - plain
+    synth = float(g.train_loss(o, y, True, extra={"rem": rem, "synth": True})) - plain
+    assert abs(synth - 3.0 * text) < 1e-4 and text > 0

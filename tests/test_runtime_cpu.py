@@ -759,6 +759,19 @@ def test_episode_stage_trains_through_the_loop(tmp_path, monkeypatch):
     text = buf.getvalue()
     assert "episodes: step 0 -> 1" in text and "remind_hit" in text         # short rows, then text rows, one run
     assert all(math.isfinite(e["val"]) for e in log) and "needles" in log[-1]["sets"]
+    # the curriculum may start further up its table, and the step on text batches ramps up after the stage
+    import memarch_b200.train.loop as loop_mod
+    seen = []
+    real = loop_mod.Trainer.step
+
+    def spy(self, xy, step, preps=None, lr_mul=1.0):
+        seen.append((tuple(xy.shape), lr_mul))
+        return real(self, xy, step, preps, lr_mul)
+    monkeypatch.setattr(loop_mod.Trainer, "step", spy)
+    train(Args(seq=64, batch=4, micro=4, steps=5, eval_every=5), "cpu",
+          env=dict(env, REMIND_SYNTH="2", REMIND_PACK_LEVEL="3", REMIND_THR="2.0", TEXT_LR_RAMP="3"), out=io.StringIO())
+    assert seen[0][0][1] == 49                                             # step 3 of the table: 4 pairs, fill 32 -> rows of 48 + 1
+    assert [m for _, m in seen] == [1.0, 1.0, 1 / 3, 2 / 3, 1.0]
 
 
 def test_instinct_blames_by_own_history_and_cards_by_kind():

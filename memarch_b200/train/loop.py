@@ -383,7 +383,12 @@ def train(args, device=None, env=None, out=None, parallel=None):
             eval_sets = {k: TokenStore(np.load(v), 0, device) for k, v in json.loads(env["EVAL_SETS"]).items()}
 
         def run_evals():
-            return {k: float(val_loss(tr.model, st_, args.seq, n=int(env.get("EVAL_BATCHES", 20)))) for k, st_ in eval_sets.items()}
+            ev_ = {k: float(val_loss(tr.model, st_, args.seq, n=int(env.get("EVAL_BATCHES", 20)))) for k, st_ in eval_sets.items()}
+            rm_e = getattr(data, "remind", None)
+            if rm_e is not None and env.get("REMIND_EVAL") is not None:
+                ev_.update(recall_by_distance(tr.model, data.val, args.seq, rm_e, env["REMIND_EVAL"],
+                                              getattr(tr.model, "window", args.seq)))
+            return ev_
         if env.get("EVAL_ONLY") == "1" or (env.get("EVAL_AT_RESUME") == "1" and start > 1):
             ev = dict(run_evals(), val=float(val_loss(tr.model, data.val, args.seq)))
             print(f"{name}[{args.stage}]  eval at step {start - 1}: " + "  ".join(f"{k} {v:.4f}" for k, v in ev.items()),
@@ -581,6 +586,26 @@ def train(args, device=None, env=None, out=None, parallel=None):
         logs[name] = log
         del tr
     return logs
+
+
+@torch.no_grad()
+def recall_by_distance(model, store, seq, remind, spec, window, rows=8):
+    """Needle accuracy on held-out text with exactly d words between facts and questions, for each d of `spec`
+    ("a,b,c"; empty: half the window, the window, twice the window and the farthest that fits the row).  Fixed
+    validation windows, every row gets a needle.  -> {"recall_d<d>": accuracy}"""
+    room = seq + 1 - 2 * remind.L
+    ds = [int(v) for v in spec.split(",") if v] or [window // 2, window, 2 * window, room]
+    ds = sorted({d for d in ds if 0 <= d <= room})
+    g = torch.Generator(device=store.device).manual_seed(1)
+    start = torch.randint(0, len(store.t) - seq - 1, (rows,), device=store.device, generator=g)
+    base = store.t[start[:, None] + torch.arange(seq + 1, device=store.device)].cpu().numpy()
+    out = {}
+    for d in ds:
+        xy, ex = remind(base, p=1.0, exact=d)
+        xy_t = torch.from_numpy(np.ascontiguousarray(xy)).long().to(store.device)
+        hits, n_ans = needle_hits(model, xy_t, torch.from_numpy(ex["rem"]).to(store.device) > 0, ex.get("rem_y"))
+        out[f"recall_d{d}"] = hits / max(n_ans, 1.0)
+    return out
 
 
 def needle_preps(model, xy, extra, micro, synth=False):

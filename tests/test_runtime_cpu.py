@@ -441,6 +441,11 @@ def test_needles_in_the_training_text_follow_the_loader_and_resume(tmp_path, mon
     log = train(a, "cpu", env=env, out=buf)["tiny"]
     assert "needles" in log[-1]["sets"] and 0.0 <= log[-1]["sets"]["needles"] <= 1.0
     assert "reminders: level 0 -> 1" in buf.getvalue()                          # threshold 0: the ladder moves on
+    # recall at fixed distances on held-out text, at every evaluation
+    log = train(Args(seq=48, batch=4, micro=4, steps=2, eval_every=2), "cpu", env=dict(env, REMIND_EVAL="4,20,400"),
+                out=io.StringIO())["tiny"]
+    assert {"recall_d4", "recall_d20"} <= set(log[-1]["sets"]) and "recall_d400" not in log[-1]["sets"]
+    assert all(0.0 <= log[-1]["sets"][k] <= 1.0 for k in ("recall_d4", "recall_d20"))
 
 
 def test_recipe_plan_and_step_count(tmp_path, capsys):

@@ -384,6 +384,14 @@ def train(args, device=None, env=None, out=None, parallel=None):
 
         def run_evals():
             ev_ = {k: float(val_loss(tr.model, st_, args.seq, n=int(env.get("EVAL_BATCHES", 20)))) for k, st_ in eval_sets.items()}
+            fish_ = getattr(tr.model, "fish", None)
+            if fish_ is not None and env.get("EVAL_NOFISH") == "1":
+                # what the layer pool contributes: the same validation with every pool layer's output zeroed
+                with torch.no_grad():
+                    keep_ = fish_.down.detach().clone()
+                    fish_.down.zero_()
+                    ev_["val_nofish"] = float(val_loss(tr.model, data.val, args.seq))
+                    fish_.down.copy_(keep_)
             rm_e = getattr(data, "remind", None)
             if rm_e is not None and env.get("REMIND_EVAL") is not None:
                 ev_.update(recall_by_distance(tr.model, data.val, args.seq, rm_e, env["REMIND_EVAL"],
@@ -400,6 +408,22 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 logs[name] = log
                 del tr
                 continue
+        if start > 1 and env.get("FISH_RESET") == "1" and hasattr(tr.model, "fish"):
+            # resume with the layer pool back at its initial weights and without optimizer momentum
+            from ..models.fishki import FishPool
+            old, mc_ = tr.model.fish, tr.model.cfg
+            torch.manual_seed(int(env.get("SEED", 0)))
+            fresh = FishPool(mc_.d, n=mc_.fish_n, hf=mc_.fish_hf, kinds=mc_.fish_kinds, pool=mc_.fish_pool, center=mc_.fish_center)
+            with torch.no_grad():
+                for nm in ("up", "down", "norm"):
+                    p_ = getattr(old, nm)
+                    p_.copy_(getattr(fresh, nm).to(p_))
+                    i_ = getattr(tr.opt, "idx", {}).get(id(p_))
+                    if i_ is not None:
+                        tr.opt.m[i_].zero_()
+                        if tr.opt.w[i_] is not None:
+                            tr.opt.w[i_].copy_(p_.float())
+            print("layer pool reset to its initial weights", file=out, flush=True)
         ramp, text_seen = int(env.get("TEXT_LR_RAMP", 0)), 0
         fish_full = int(env.get("FISH_FULL_FROM", -1))
         if start > 1 and env.get("OPT_RESET_GAIN") == "1" and hasattr(tr.opt, "gain"):

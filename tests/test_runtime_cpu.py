@@ -1022,8 +1022,14 @@ def test_layer_pool_training_by_kind_through_the_loop(tmp_path, monkeypatch):
     assert kinds.count(0) == 4 and kinds.count(1) == 2                     # 2:1 by the weights of the kinds
     data.loader.close()
     buf = io.StringIO()
-    log = train(a, "cpu", env=env, out=buf)["tiny"]
+    env2 = dict(env, EVAL_NOFISH="1", CKPT_DIR=str(tmp_path / "ck"), CKPT_EVERY="3")
+    log = train(a, "cpu", env=env2, out=buf)["tiny"]
     assert all(math.isfinite(e["val"]) for e in log) and "fish_router_acc" in buf.getvalue()
+    assert "val_nofish" in log[-1]["sets"] and log[-1]["sets"]["val_nofish"] != log[-1]["val"]
+    buf = io.StringIO()
+    a2 = Args(seq=48, batch=4, micro=4, steps=8, eval_every=8)
+    train(a2, "cpu", env=dict(env2, FISH_RESET="1", FISH_FULL_FROM="8"), out=buf)
+    assert "resuming at step 7" in buf.getvalue() and "layer pool reset to its initial weights" in buf.getvalue()
 
 
 def test_total_diagnostics_of_a_run(tmp_path, monkeypatch):

@@ -274,10 +274,18 @@ def run_ours(args):
     def step_dev(s):
         losses.append(tr.step(store.batch(args.batch, args.seq), s))
 
-    n0 = _ext.launch_count
+    n0, f0 = _ext.launch_count, _ext.gemm_flops
     sampler = ClockSampler(local) if rank == 0 else None
     ms, clocks = timed_loop(step_dev, args.steps, args.warmup, world, sampler)
     per_step_launches = (_ext.launch_count - n0) / (args.steps + args.warmup)
+    # tensor-core work of this package's own GEMMs per step and GPU (nominal 2MNK; attention and the optimizer's
+    # element-wise work are not in it), against the measured sustained cuBLAS rate when the driver wrote one
+    gemm_tflop = (_ext.gemm_flops - f0) / (args.steps + args.warmup) / 1e12
+    peak = None
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("bf16_tflops_sustained") or 0) or None
+    except (OSError, ValueError, AttributeError):
+        pass
     e2e = None
     if not args.no_e2e:
         feeder = HostFeeder(toks, seed=100 + rank, device=dev, B=args.batch, T=args.seq)
@@ -303,6 +311,9 @@ def run_ours(args):
               "mode": args.mode if world > 1 else "single", "selftest": selftest,
               "loss_first": round(first, 4), "loss_last": round(last, 4), "kernel_status": st, "peer_status": peer_st,
               "losses": [round(float(l), 4) for l in losses[:16]],
+              "gemm_tflop_per_step": round(gemm_tflop, 2),
+              "gemm_tflops_achieved": round(gemm_tflop / (ms / 1e3), 1),
+              "gemm_share_of_measured_sustained": round(gemm_tflop / (ms / 1e3) / peak, 3) if peak else None,
               "launches_per_step": round(per_step_launches, 1), "cuda_graph": bool(args.graph) and not tr._graph_failed,
               "params_b": round(sum(p.numel() for p in model.parameters()) / 1e9, 3),
               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),

@@ -17,6 +17,7 @@ _lock = threading.Lock()
 _mod = None
 _err = None
 launch_count = 0          # kernels of this package launched since process start (bench.py reports the delta)
+gemm_flops = 0            # nominal 2·M·N·K of the tensor-core GEMMs issued through `ops.gemm` (padding places included)
 
 
 def _pkg_dir():
@@ -73,3 +74,8 @@ def use_cuda(*tensors) -> bool:
 def count(n: int = 1):
     global launch_count
     launch_count += n
+
+
+def count_flops(n: int):
+    global gemm_flops
+    gemm_flops += n

@@ -166,6 +166,9 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, ac
     """
     C = _ext.C()
     _ext.count()
+    m_, k_ = (a.shape[-1], a.shape[-2]) if a_mn else (a.shape[-2], a.shape[-1])
+    n_ = b.shape[-1] if b_mn else b.shape[-2]
+    _ext.count_flops(2 * m_ * n_ * k_ * max(1, int(groups)))
     return C.gemm(a, b, out, out2, aux, bool(a_mn), bool(b_mn), bool(accumulate), int(epi),
                   out_dtype == torch.float32, int(groups), counts, int(count_mode) if counts is not None else 0)
 

@@ -100,6 +100,7 @@ class _FusedExpertFFN(torch.autograd.Function):
         order = _rotated(W, r)
         a_ptrs = [hp + s * Cn * Hh * 2 for s in order]
         yptrs = [int(Yh.buffer_ptrs[s]) for s in order]
+        _ext.count_flops(2 * M * Hh * d * n_local)
         C.gemm_peer(a_ptrs, Cn, Hh, n_local, Hh, M * Hh, 0, down, True, None, yptrs, d, Cn * d, g_off, None, None, 0, n_local)
         _ext.count(3)
         heap.barrier(0)                                             # every expert's rows have landed here
@@ -146,6 +147,7 @@ class _FusedExpertFFN(torch.autograd.Function):
         order = _rotated(W, r)
         a_ptrs = [da.data_ptr() + s * Cn * Hh * 2 for s in order]
         dxptrs = [int(DXh.buffer_ptrs[s]) for s in order]
+        _ext.count_flops(2 * M * Hh * d * nl)
         C.gemm_peer(a_ptrs, Cn, Hh, nl, Hh, M * Hh, 0, up, False, None, dxptrs, d, Cn * d, g_off, None, None, 0, nl)
         _ext.count()
         heap.barrier(0)

@@ -192,7 +192,7 @@ class Trainer:
             static_xy = xy.clone()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            n0, step0 = _ext.launch_count, self.opt.n_step
+            n0, f0, step0 = _ext.launch_count, _ext.gemm_flops, self.opt.n_step
             try:
                 with torch.cuda.graph(g, pool=self._graph_pool, stream=self._gstream):
                     out = self._core(static_xy, None)
@@ -204,14 +204,15 @@ class Trainer:
                 return self._core(xy, None)
             if self._graph_pool is None:
                 self._graph_pool = g.pool()
-            ent = self._graphs[key] = (g, static_xy, out, _ext.launch_count - n0)
+            ent = self._graphs[key] = (g, static_xy, out, _ext.launch_count - n0, _ext.gemm_flops - f0)
             self.opt.n_step = step0              # capture ran the host bookkeeping once; the replay below is the real step
-        g, static_xy, out, launches = ent
+        g, static_xy, out, launches, flops = ent
         static_xy.copy_(xy)
         g.replay()
         self.opt.n_step += 1
         from ..ops import _ext
         _ext.count(launches)
+        _ext.count_flops(flops)
         return out
 
     def _core(self, xy, preps=None):

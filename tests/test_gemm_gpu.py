@@ -61,13 +61,18 @@ def test_gemm_grouped_and_strided_views():
     from memarch_b200.ops import gemm
     E, Cn, d, H = 4, 200, 256, 384
     x, up = _mk((E, Cn, d), seed=5), _mk((E, d, H), 0.1, seed=6)
+    from memarch_b200.ops import _ext as ext
+    f0 = ext.gemm_flops
     y = gemm(x, up, b_mn=True, groups=E)
+    assert ext.gemm_flops - f0 == 2 * Cn * H * d * E                        # the work counter behind bench.py's GEMM share
     ref = torch.bmm(x.float(), up.float())
     assert _rel(y, ref) < 1e-2
     big = _mk((1000, 512), seed=7)
     w = _mk((256, 512), seed=8)
     out = torch.zeros(1000, 256, device="cuda", dtype=torch.bfloat16)
+    f0 = ext.gemm_flops
     gemm(big[128:640], w, out=out[128:640])
+    assert ext.gemm_flops - f0 == 2 * 512 * 256 * 512
     assert _rel(out[128:640], big[128:640].float() @ w.float().t()) < 1e-2
     assert out[:128].abs().sum() == 0 and out[640:].abs().sum() == 0
 

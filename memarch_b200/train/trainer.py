@@ -172,7 +172,8 @@ class Trainer:
         inst = isinstance(self.opt, Instinct)
         if inst:
             self.opt._sync_lr()
-        if self.graph and xy.is_cuda and preps is None and inst and "C" not in self.stage:
+        host_rules = self.ocfg.m_rate or self.ocfg.culprit == "ema"      # their step counters live on the host
+        if self.graph and xy.is_cuda and preps is None and inst and "C" not in self.stage and not host_rules:
             total = self._step_graphed(xy)
         else:
             total = self._core(xy, preps)

@@ -58,6 +58,8 @@ std::vector<torch::Tensor> reread_bwd(torch::Tensor dgot, torch::Tensor dcostw, 
                                       torch::Tensor sc, torch::Tensor pos, torch::Tensor qpos, torch::Tensor rows,
                                       torch::Tensor ids, torch::Tensor table, torch::Tensor offset, torch::Tensor hv,
                                       torch::Tensor hb, torch::Tensor hh, torch::Tensor Wr, torch::Tensor cp);
+std::vector<torch::Tensor> rope_route_topk(torch::Tensor S, torch::Tensor lval, torch::Tensor lp, torch::Tensor avalid,
+                                           torch::Tensor open_from, int64_t H, int64_t K, int64_t q0, double scale);
 std::vector<torch::Tensor> attn_fwd_tc(torch::Tensor q, torch::Tensor k, torch::Tensor v, int64_t window, double scale);
 int64_t attn_status_read();
 std::vector<torch::Tensor> attn_bwd_tc(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor dout, torch::Tensor lse,
@@ -118,6 +120,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_i8", &mb::gemm_i8);
   m.def("reread_fwd", &mb::reread_fwd);
   m.def("reread_bwd", &mb::reread_bwd);
+  m.def("rope_route_topk", &mb::rope_route_topk);
   m.def("moe_route_fwd", &mb::moe_route_fwd);
   m.def("moe_route_bwd", &mb::moe_route_bwd);
   m.def("table_pair_dot", &mb::table_pair_dot, "out[n] = <A[ia[n]], B[ib[n]]>");

@@ -139,6 +139,7 @@ class ModelConfig:
     rope_qfrac: float = 1.0       # share of words that read the tether at all (the rest: window only)
     rope_qtau0: float = 5.0
     rope_doc_eos: int = -1        # >= 0: anchors of another document than the query's are not opened
+    rope_route_bf16: bool = False  # ROPE_ROUTE_BF16: exact search on bf16 operands: tensor-core scores + top-k kernel on a GPU
     rope_pcut: float = 0.0        # ROPE_PCUT: tethered layers rotate only frequencies with a wavelength <= this many words
     rope_key_diag: bool = False   # statistics: how many needle keys the search can see
     remind_use_w: float = 0.0     # REMIND_USE_W: penalty mean(1 - tether share) on the needle questions
@@ -367,7 +368,7 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
                        ("frac", float), ("cap", float), ("qfrac", float), ("qtau0", float), ("doc_eos", int),
                        ("pcut", float)):
             if g("ROPE_" + k_.upper()): kw["rope_" + k_] = t_(g("ROPE_" + k_.upper()))
-        for k_ in ("share_route", "anchor_top", "key_diag"):
+        for k_ in ("share_route", "anchor_top", "key_diag", "route_bf16"):
             if g("ROPE_" + k_.upper()) == "1": kw["rope_" + k_] = True
         if g("ROPE_EXCL_WIN") == "0": kw["rope_excl_win"] = False
         if g("ROPE_RGRAD") == "0": kw["rope_rgrad"] = False

@@ -669,7 +669,7 @@ class MemArchLM(nn.Module):
                 self.stats["rope_qfrac_real"] = qmask.float().mean()
         rcfg = RopeCfg(K=c.rope_k, links=c.rope_links, win=c.rope_win, span_cap=c.rope_span_cap, route=c.rope_route,
                        G=c.rope_hier_g, NB=c.rope_hier_nb, BM=c.rope_hier_bm, excl_win=c.rope_excl_win, rgrad=c.rope_rgrad,
-                       chunk=c.rope_chunk, mgrad=c.remind_use_w > 0)
+                       chunk=c.rope_chunk, mgrad=c.remind_use_w > 0, route_bf16=c.rope_route_bf16)
         pending, routed, masses = None, None, []
         for bi, b in enumerate(self.light_b):
             if c.rope_layers and bi >= c.rope_layers:

@@ -40,6 +40,8 @@ class RopeCfg:
     rgrad: bool = True          # routing score as a bias on the span's keys
     rgrad_scale: float = 1.0
     chunk: int = 256            # queries per recomputed chunk
+    route_bf16: bool = False    # exact search with bf16 operands (fp32 accumulate): on a GPU the scores are one tensor-core
+                                # GEMM per chunk and the choice is the `rope_route_topk` kernel
     mgrad: bool = False         # the share of mass on opened spans keeps its gradient (a penalty may push it up)
 
 
@@ -118,11 +120,36 @@ def route_exact(q, k, own, apos, avalid, cfg: RopeCfg):
     kk, L = min(cfg.K, A), min(cfg.links, cfg.span_cap)
     kl, lval, lp = _links(k, own, apos, avalid, L)
     nx = _open_from(apos, avalid, T, cfg)
+    if cfg.route_bf16:
+        if q.is_cuda and kk <= 8 and (A * L) % 8 == 0 and hd % 8 == 0 and hd >= 16 and cfg.chunk % 8 == 0 and T % 8 == 0:
+            return _route_exact_kernel(q, kl, lval, lp, avalid, nx, kk, cfg.chunk)
+        q, kl = q.to(torch.bfloat16).float(), kl.to(torch.bfloat16).float()     # the same operands, PyTorch statement
     qi = torch.arange(T, device=q.device)
     out = []
     for c0 in range(0, T, cfg.chunk):
         ok = avalid[:, None, :] & (nx[:, None, :] <= qi[None, c0:c0 + cfg.chunk, None])
         out.append(_best_of(q[:, :, c0:c0 + cfg.chunk], kl, lval[:, None], lp[:, None], ok[:, None], kk, hd))
+    return tuple(torch.cat(t, 2) for t in zip(*out))
+
+
+def _route_exact_kernel(q, kl, lval, lp, avalid, nx, kk, chunk):
+    """Scores of a chunk of queries against all link keys as ONE grouped tensor-core GEMM (a group per batch x head,
+    bf16 operands, fp32 result), then `rope_route_topk` (csrc/rope_route.cu): best existing link per anchor the query
+    may open, K best anchors, no (B,H,M,A,L) tensor of masked scores in between."""
+    from ..ops import _ext, gemm
+    B, H, T, hd = q.shape
+    A, L = lval.shape[1], lval.shape[2]
+    klb = kl.to(torch.bfloat16).reshape(B * H, A * L, hd).contiguous()
+    lval8, av8 = lval.to(torch.uint8).contiguous(), avalid.to(torch.uint8).contiguous()
+    lp32, nx32 = lp.to(torch.int32).contiguous(), nx.clamp(max=2 ** 31 - 1).to(torch.int32).contiguous()
+    out = []
+    for c0 in range(0, T, chunk):
+        qc = q[:, :, c0:c0 + chunk].to(torch.bfloat16).reshape(B * H, -1, hd).contiguous()
+        S = gemm(qc, klb, groups=B * H, out_dtype=torch.float32)
+        ti, tv, tp = _ext.C().rope_route_topk(S, lval8, lp32, av8, nx32, H, kk, c0, 1.0 / math.sqrt(hd))
+        _ext.count()
+        M = qc.shape[1]
+        out.append((ti.view(B, H, M, kk), tv.view(B, H, M, kk).bool(), tp.view(B, H, M, kk)))
     return tuple(torch.cat(t, 2) for t in zip(*out))
 
 

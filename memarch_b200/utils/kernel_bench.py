@@ -333,6 +333,29 @@ def cmd_sweep(a):
         torch.cuda.empty_cache()
 
 
+def cmd_route(a):
+    """Anchor search of the long-range read: bf16 tensor-core scores + `rope_route_topk` against the PyTorch statement
+    (fp32 einsum, masked max over links, top-k) on the same inputs."""
+    import dataclasses
+    from memarch_b200.models import rope_memory as rm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    B, H, T, hd, A = a.batch, a.heads, a.seq, 64, a.anchors
+    q, k = torch.randn(B, H, T, hd, device=dev), torch.randn(B, H, T, hd, device=dev)
+    s = torch.rand(B, T, device=dev) * 2
+    tau = float(s.flatten().kthvalue(int(s.numel() * (1 - A / T))).values)
+    own, apos, avalid = rm.anchors_from_surprise(s.clone(), tau, A)
+    cfg = rm.RopeCfg(K=4, links=8, win=64, span_cap=256, chunk=256, route="exact", route_bf16=True)
+    plain = dataclasses.replace(cfg, route_bf16=False)
+    fast = rm.route_exact(q, k, own, apos, avalid, cfg)
+    slow = rm.route_exact(q, k, own, apos, avalid, plain)
+    same = ((fast[0] == slow[0]) & (fast[1] == slow[1])).float().mean().item()
+    flops = 2.0 * B * H * T * A * 8 * hd
+    report(f"route kernel  B{B} H{H} T{T} A{A} L8", timeit(lambda: rm.route_exact(q, k, own, apos, avalid, cfg), a.iters),
+           flops, extra=f"same choice as the fp32 statement on {same:.4f} of the slots; anchors {float(avalid.float().sum(1).mean()):.0f}")
+    report("route PyTorch fp32", timeit(lambda: rm.route_exact(q, k, own, apos, avalid, plain), max(3, a.iters // 3)), flops)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="memarch_b200 bench-kernel")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -359,15 +382,18 @@ def main(argv=None):
     t.add_argument("--batch", type=int, default=32); t.add_argument("--heads", type=int, default=32)
     t.add_argument("--seq", type=int, default=1024); t.add_argument("--window", type=int, default=0)
     t.add_argument("--iters", type=int, default=10)
+    rt = sub.add_parser("route")
+    rt.add_argument("--batch", type=int, default=4); rt.add_argument("--heads", type=int, default=8)
+    rt.add_argument("--seq", type=int, default=4096); rt.add_argument("--anchors", type=int, default=1024)
     w = sub.add_parser("sweep")
     w.add_argument("--shapes", default=""); w.add_argument("--variants", default="0", help="dbg[:group_m],...")
     w.add_argument("--seconds", type=float, default=0.6)
-    for p in (g, c, i, e, w, r):
+    for p in (g, c, i, e, w, r, rt):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
     {"gemm": cmd_gemm, "ce": cmd_ce, "instinct": cmd_instinct, "experts": cmd_experts, "attn": cmd_attn, "sweep": cmd_sweep,
-     "reread": cmd_reread}[a.cmd](a)
+     "reread": cmd_reread, "route": cmd_route}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -100,6 +100,10 @@ def test_rope_two_level_search():
         assert torch.equal(a[:, :, :t + 1], b[:, :, :t + 1])
     with pytest.raises(ValueError):
         rm.route(q, k, own, apos, avalid, rm.RopeCfg(route="flat"))
+    # bf16 operands (the device path's arithmetic): the exact search on the rounded queries and keys
+    rounded = rm.route_exact(q.bfloat16().float(), k.bfloat16().float(), own, apos, avalid, rm.RopeCfg(route="exact", **base))
+    low = rm.route_exact(q, k, own, apos, avalid, rm.RopeCfg(route="exact", route_bf16=True, **base))
+    assert all(torch.equal(a, b) for a, b in zip(rounded, low))
 
 
 def test_rope_query_and_document_masks():

@@ -79,15 +79,18 @@ def _get(opt, h):
 
 
 class RollbackGuard:
-    def __init__(self, trainer, ratio=1.5, beta=0.98, lr_mul=0.5, warm=50):
+    def __init__(self, trainer, ratio=1.5, beta=0.98, lr_mul=0.5, warm=50, kinds=1):
+        """`kinds` > 1: one running mean of the loss and one "just rejected" flag per kind of step (`step(..., kind=k)`):
+        kinds of text differ in their loss level, and a kind whose step was rejected learns at its next step, or a kind
+        with a raised loss would never learn again (memarch_jax/memarch_jax/step.py:64-124 of the reference's JAX port)."""
         self.tr, self.ratio, self.beta, self.lr_mul, self.warm = trainer, ratio, beta, lr_mul, warm
         if getattr(trainer.opt, "offload", False):
             raise ValueError("the device-side rollback keeps a copy of the optimizer state on the device: "
                              "it cannot be combined with the host offload of the momentum (offload_m)")
         dev = trainer.device
-        self.lema = torch.zeros((), device=dev)            # running mean of the loss (0 = not started)
+        self.lema = torch.zeros(kinds, device=dev)         # running mean of the loss per kind (0 = not started)
         self.rep = torch.zeros((), dtype=torch.bool, device=dev)     # next step replays the kept batch
-        self.cool = torch.zeros((), dtype=torch.bool, device=dev)    # last step was rejected: do not reject again
+        self.cool = torch.zeros(kinds, dtype=torch.bool, device=dev)  # the kind's last step was rejected: not again
         self.n_hit = torch.zeros((), dtype=torch.long, device=dev)
         self.n = 0
         self.prev_xy = None
@@ -102,8 +105,19 @@ class RollbackGuard:
         return [p.data for p in tr.params], [_get(tr.opt, h) for h in self.handles]
 
     @torch.no_grad()
-    def step(self, xy, step, **kw):
+    def step(self, xy, step, kind=0, **kw):
         tr = self.tr
+        k = min(max(int(kind), 0), self.lema.numel() - 1)
+        if self.prev_xy is not None and self.prev_xy.shape != xy.shape:
+            # a step of another shape (a batch of short synthetic rows): it is neither judged nor kept for a replay,
+            # but the state before it becomes the snapshot, so the next ordinary step can still undo its update
+            ps, os_ = self._state()
+            before_p, before_o = [t.clone() for t in ps], [t.clone() for t in os_]
+            with torch.enable_grad():
+                loss = tr.step(xy, step, **kw)
+            self.snap_p, self.snap_o = before_p, before_o
+            self.n += 1
+            return loss
         if self.prev_xy is None:
             self.prev_xy = xy.clone()
         xy_eff = torch.where(self.rep, self.prev_xy, xy)
@@ -114,7 +128,8 @@ class RollbackGuard:
         with torch.enable_grad():
             loss = tr.step(xy_eff, step, **kw)
         l = loss.detach().float()
-        hit = (l > self.ratio * self.lema) & (self.lema > 0) & ~self.cool & ~self.rep
+        lema = self.lema[k]
+        hit = (l > self.ratio * lema) & (lema > 0) & ~self.cool[k] & ~self.rep
         if self.n < self.warm or self.snap_p is None:
             hit = torch.zeros_like(hit)
         if self.snap_p is not None:
@@ -128,9 +143,9 @@ class RollbackGuard:
         # new snapshot: the state before this step; kept batch: this step's batch unless a replay is pending
         self.snap_p, self.snap_o = before_p, before_o
         self.prev_xy = torch.where(hit, self.prev_xy, xy_eff)
-        new_l = torch.where(self.lema > 0, self.beta * self.lema + (1 - self.beta) * torch.minimum(l, self.lema * self.ratio), l)
-        self.lema = torch.where(self.rep, self.lema, new_l)
-        self.cool = hit
+        new_l = torch.where(lema > 0, self.beta * lema + (1 - self.beta) * torch.minimum(l, lema * self.ratio), l)
+        self.lema[k] = torch.where(self.rep, lema, new_l)
+        self.cool[k] = torch.where(self.rep, self.cool[k], hit)          # a replayed batch leaves the kind's flag alone
         self.rep = hit
         self.n_hit += hit.long()
         self.n += 1

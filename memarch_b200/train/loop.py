@@ -436,7 +436,9 @@ def train(args, device=None, env=None, out=None, parallel=None):
         nan_at = int(env.get("TRAIN_NAN_AT", 0))              # inject a non-finite loss at this step (on the host)
         spikes = SpikeLog(float(env.get("SPIKE", 2.0)))
         rb = RollbackGuard(tr, ratio=float(env.get("RB_RATIO", 1.5)), lr_mul=float(env.get("RB_LR", 0.5)),
-                           warm=int(env.get("RB_WARM", 50))) if env.get("ROLLBACK") == "1" else None
+                           warm=int(env.get("RB_WARM", 50)),
+                           kinds=getattr(tr.opt, "K", 1) if getattr(tr.ocfg, "card_by_kind", False) else 1) \
+            if env.get("ROLLBACK") == "1" else None
         dog = Watchdog(float(env.get("WATCHDOG", 180)), 120.0) if env.get("WATCHDOG", "180") != "0" else None
         ema_start, ema_beta = float(env.get("EMA_START", 0) or 0), float(env.get("EMA_BETA", 0.98))
         ema_every = int(env.get("EMA_EVERY", 1))
@@ -507,7 +509,10 @@ def train(args, device=None, env=None, out=None, parallel=None):
                             lr_mul_ = min(1.0, text_seen / ramp)
                         if "kind" in ex_:
                             tr.card = int(ex_["kind"][0, 0])        # OptConfig.card_by_kind: one card per kind of text
-                    loss = rb.step(xy_b, step - 1) if rb is not None else tr.step(xy_b, step - 1, npreps, lr_mul_)
+                    ex0_ = getattr(data, "extra", None)
+                    if rb is not None and ex0_ is not None and "kind" in ex0_:
+                        tr.card = int(ex0_["kind"][0, 0])
+                    loss = rb.step(xy_b, step - 1, kind=tr.card or 0) if rb is not None else tr.step(xy_b, step - 1, npreps, lr_mul_)
                     phase["data"] += ts - td
                     phase["enqueue"] += time.time() - ts
                     phase["n"] += 1

@@ -1050,3 +1050,43 @@ def test_total_diagnostics_of_a_run(tmp_path, monkeypatch):
         assert want in text, want
     trace = tmp_path / "tr" / "trace_step2.json"
     assert trace.exists() and trace.stat().st_size > 1000 and "trace: written" in text
+
+
+def test_rollback_guard_by_kind_and_steps_of_another_shape():
+    from memarch_b200.train.guards import RollbackGuard
+    xs = batches(8)
+    tr = tiny_trainer()
+    rb = RollbackGuard(tr, ratio=1.5, warm=2, lr_mul=0.5, kinds=3)
+    real = tr.step
+    scale = {"v": 1.0}
+
+    def scaled(xy, step, **kw):
+        return real(xy, step, **kw) * scale["v"]
+    tr.step = scaled
+    for s in range(3):
+        rb.step(xs[s], s, kind=0)
+    scale["v"] = 3.0                                         # kind 1 lives at three times the loss: its own running mean
+    rb.step(xs[3], 3, kind=1)
+    assert int(rb.n_hit) == 0 and float(rb.lema[1]) > 2 * float(rb.lema[0]) and float(rb.lema[2]) == 0
+    rb.step(xs[4], 4, kind=1)
+    assert int(rb.n_hit) == 0                                # judged against kind 1's mean: no spike
+    rb.step(xs[5], 5, kind=0)                                # the same loss under kind 0 IS a spike
+    assert int(rb.n_hit) == 1 and bool(rb.cool[0]) and not bool(rb.cool[1]) and bool(rb.rep)
+    scale["v"] = 1.0
+    rb.step(xs[6], 6, kind=0)                                # the replay; the kind's flag stays until its own next step
+    assert bool(rb.cool[0]) and not bool(rb.rep)
+    scale["v"] = 3.0
+    rb.step(xs[7], 7, kind=0)                                # just rejected: this time the kind learns
+    assert int(rb.n_hit) == 1 and not bool(rb.cool[0])
+    # a batch of another shape (short synthetic rows) is stepped, not judged, and becomes undoable
+    scale["v"] = 1.0
+    before = [p.detach().clone() for p in tr.params]
+    short = torch.randint(0, 256, (8, 17))
+    n0 = rb.n
+    rb.step(short, 8, kind=2)
+    assert rb.n == n0 + 1 and float(rb.lema[2]) == 0 and rb.prev_xy.shape == xs[0].shape
+    assert all(torch.equal(a, b) for a, b in zip(rb.snap_p, before))
+    scale["v"] = 100.0
+    rb.step(xs[0], 9, kind=1)                                # a spike right after it: the synthetic step is undone too
+    assert int(rb.n_hit) == 2
+    assert all(torch.equal(p.data, b) for p, b in zip(tr.params, before))

@@ -291,61 +291,68 @@ class AnchorMoE(nn.Module):
                 self.aux = self.aux + self.hint_w * self.hint
         return ye
 
+    def _teachers(self):
+        """For every expert the learned expert that teaches it: the students, in order, are dealt out `students` to a
+        teacher, the teachers taken in order and round again.  (index per expert, who is a student at all)"""
+        student = ~self.learned
+        n_teachers = self.learned.sum()
+        ranked = student.long().argsort(stable=True)              # learned experts first, in order
+        seat = student.long().cumsum(0) - 1                       # a student's number among the students
+        return ranked[(seat // self.students) % n_teachers.clamp(min=1)], student & (n_teachers > 0)
+
     def _hint(self, xe, ye, wt):
         """A learned expert (teacher) briefly pulls its students' outputs towards its own on the students' worst
         10 % of places (full2.py:604-619)."""
-        learned = self.learned
-        n_t = learned.sum()
-        order = (~learned).long().argsort(stable=True)
-        rank = (~learned).long().cumsum(0) - 1
-        teacher = order[(rank // self.students) % n_t.clamp(min=1)]
+        teacher, student = self._teachers()
         with torch.no_grad():
-            yt = self._ffn(xe, self.up[teacher], self.down[teacher], train_w=False)
-        diff = (ye.float() - yt.float()).pow(2).mean(-1) * (wt > 0)
-        k = max(1, diff.shape[1] // 10)
-        worst = diff.topk(k, dim=1).values.mean(1)
-        is_student = (~learned) & (n_t > 0)
-        return (worst * is_student).sum() / is_student.sum().clamp(min=1)
+            target = self._ffn(xe, self.up[teacher], self.down[teacher], train_w=False)
+        gap = (ye.float() - target.float()).pow(2).mean(-1) * (wt > 0)          # per place, filled places only
+        tenth = max(1, gap.shape[1] // 10)
+        return (gap.topk(tenth, dim=1).values.mean(1) * student).sum() / student.sum().clamp(min=1)
 
     # ------------------------------------------------------------------------------------------ waves
+    def _relative_move(self):
+        """How far every expert's `up` moved since the last look, relative to its size; the look is renewed.  With a
+        bank only the learning experts have weights here: the others count as not moved."""
+        now, then = self.up.float(), self.up_snap.float()
+        moved = (now - then).flatten(1).norm(dim=1) / (then.flatten(1).norm(dim=1) + 1e-8) if now.shape[0] else now.new_zeros(0)
+        self.up_snap.copy_(self.up)
+        if not self.bank:
+            return moved.to(self.err.dtype)
+        return torch.zeros(self.E, device=self.err.device).index_copy(0, self.L_idx, moved) if self.L else \
+            torch.zeros(self.E, device=self.err.device)
+
+    def _settled(self):
+        """Experts that look finished at this check: by their error against its peak (`err`), or by how little they
+        still move against their largest move (`still`; only experts that are learning here can be judged)."""
+        if self.wave == "err":
+            return self.err < self.err_thr * self.err_peak
+        move = self._relative_move()
+        self.move_peak.copy_(torch.maximum(self.move_peak, move.masked_fill(self.learned, 0.0)))
+        self.last_move.copy_(move)
+        quiet = (move < 0.3 * self.move_peak) & ~self.learned
+        if self.bank:
+            here = torch.zeros(self.E, dtype=torch.bool, device=move.device).index_fill(0, self.L_idx, True)
+            quiet = quiet & here
+        return quiet
+
     @torch.no_grad()
     def before_step(self, step):
         """Once per step, device-only: who has learned / who is a student again (full2.py:621-643, 1176-1196)."""
         if not self.wave:
             return
+        check = step % self.wave_every == 0
+        self.hint_now = (not self.bank) and step > 0 and check and bool(self.training)
         if not self.bank:
-            self.up._frozen_rows = self.down._frozen_rows = self.learned
-            self.hint_now = step > 0 and step % self.wave_every == 0 and bool(self.training)
-        else:
-            self.hint_now = False
-        if step % self.wave_every or step < self.warm:
+            self.up._frozen_rows = self.down._frozen_rows = self.learned        # the optimizer leaves these rows alone
+        if not check or step < self.warm:
             return
         self.err_peak.copy_(torch.maximum(self.err_peak, self.err))
-        if self.wave == "err":
-            cand = self.err < self.err_thr * self.err_peak
-        else:
-            if self.bank:
-                move = torch.zeros(self.E, device=self.err.device)
-                if self.L:
-                    mL = ((self.up.float() - self.up_snap.float()).flatten(1).norm(dim=1)
-                          / (self.up_snap.float().flatten(1).norm(dim=1) + 1e-8))
-                    move = move.index_copy(0, self.L_idx, mL)
-                    self.up_snap.copy_(self.up)
-            else:
-                move = ((self.up - self.up_snap).flatten(1).norm(dim=1)
-                        / (self.up_snap.flatten(1).norm(dim=1) + 1e-8))
-            self.move_peak.copy_(torch.maximum(self.move_peak, torch.where(self.learned, 0.0, move)))
-            self.last_move.copy_(move)
-            cand = (move < 0.3 * self.move_peak) & ~self.learned
-            if self.bank:
-                in_L = torch.zeros(self.E, dtype=torch.bool, device=move.device).index_fill(0, self.L_idx, True)
-                cand &= in_L
-            else:
-                self.up_snap.copy_(self.up)
-        relearn = self.learned & (self.err > 1.5 * self.err_freeze)
-        newly = ~self.learned & cand
-        self.err_freeze.copy_(torch.where(newly, self.err, self.err_freeze))
-        self.learned.copy_((self.learned | newly) & ~relearn)
+        settled = self._settled()
+        fresh = settled & ~self.learned
+        slipped = self.learned & (self.err > 1.5 * self.err_freeze)             # error grew since it froze: learn again
+        self.err_freeze.copy_(torch.where(fresh, self.err, self.err_freeze))
+        self.learned.copy_((self.learned | fresh) & ~slipped)
 
     def _moves(self, learned_cpu):
         """(experts that leave the learning bank, experts that come back from the frozen one) for a `learned` mask."""

@@ -31,31 +31,27 @@ class FineMoE(nn.Module):
         self.aux = torch.zeros(())
 
     def forward(self, x):
-        shp = x.shape
-        xf = x.reshape(-1, shp[-1])
-        N = xf.shape[0]
-        logits = F.linear(xf.float(), self.router.weight.float())
-        gate, ex = logits.topk(self.k, -1)
-        gate = gate.softmax(-1)
-        prob = logits.softmax(-1)
-        frac = F.one_hot(ex, self.E).float().sum(1).mean(0) / self.k
-        self.aux = self.E * (frac * prob.mean(0)).sum()
-        C = int(1.25 * N * self.k / self.E) + 1
-        e_flat = ex.reshape(-1)
-        order = e_flat.argsort(stable=True)
-        es = e_flat[order]
-        start = torch.searchsorted(es, torch.arange(self.E, device=x.device))
-        slot = torch.arange(N * self.k, device=x.device) - start[es]
-        keep = slot < C
-        tok = order // self.k
-        dest = torch.where(keep, es * C + slot, torch.full_like(slot, self.E * C))
-        buf = xf.new_zeros(self.E * C + 1, shp[-1]).index_copy(0, dest, xf[tok])
-        hb = buf[:-1].view(self.E, C, -1).to(_cdt(x))
-        yb = ops.expert_ffn(hb, self.up, self.down, "swiglu").reshape(self.E * C, -1)
-        yb = torch.cat([yb, yb.new_zeros(1, yb.shape[-1])])
-        w = gate.reshape(-1)[order] * keep
-        y = xf.new_zeros(N, shp[-1]).index_add(0, tok, (yb[dest] * w[:, None].to(yb.dtype)).to(xf.dtype))
-        return y.view(shp)
+        """Dispatch without a sort and combine without atomics: a (token, choice) pair's place inside its expert is
+        the running count of earlier pairs of that expert (token order, so the first to ask are served when an expert
+        is over capacity, as the reference's stable sort by expert does); every token then sums its own k results."""
+        E, k, d = self.E, self.k, x.shape[-1]
+        tokens = x.reshape(-1, d)
+        N = tokens.shape[0]
+        scores = F.linear(tokens.float(), self.router.weight.float())
+        top, chosen = scores.topk(k, -1)
+        share = top.softmax(-1)                                             # (N,k) weights of the chosen experts
+        asked = F.one_hot(chosen, E)                                        # (N,k,E)
+        self.aux = E * ((asked.float().sum(1).mean(0) / k) * scores.softmax(-1).mean(0)).sum()   # load x importance
+        cap = int(1.25 * N * k / E) + 1
+        place = (asked.view(N * k, E).cumsum(0) - 1).gather(1, chosen.view(-1, 1)).view(N, k)
+        served = place < cap
+        spill = E * cap                                                      # one extra row takes what does not fit
+        cell = torch.where(served, chosen * cap + place, torch.full_like(place, spill))
+        rows = tokens.new_zeros(spill + 1, d).index_copy(0, cell.view(-1), tokens.repeat_interleave(k, 0))
+        out = ops.expert_ffn(rows[:-1].view(E, cap, d).to(_cdt(x)), self.up, self.down, "swiglu").reshape(spill, d)
+        out = torch.cat([out, out.new_zeros(1, d)])
+        mine = out[cell] * (share * served)[..., None].to(out.dtype)         # (N,k,d), zero where dropped
+        return mine.to(tokens.dtype).sum(1).view(x.shape)
 
 
 class LightBlock(nn.Module):

@@ -77,6 +77,7 @@ def compare(d, m, rtol=2e-4):
     ("Fv2s_nomem", {"ATTN_IMPL": "block"}, 160),                  # sliding window shorter than the text, ragged tail
     ("Fv2s", {"ATTN_IMPL": "block"}, 256),                        # dense heavy stack; memory demotes and prunes
     ("Fv3s", {"ATTN_IMPL": "block"}, 256),                        # volume memory (v3): pieces, merge on prune
+    ("Fv2moeKs8", {"LIGHT_MOE": "8:2", "NO_MEM": "1"}, 64),       # light layers with their own small MoE
 ])
 def test_model_matches_reference(tmp_path, name, env, T):
     from memarch_b200.build import build

@@ -27,56 +27,59 @@ from .memory import CardMemory, VolumeMemory
 from .moe import AnchorMoE
 from .reread import Reread
 
-_HC1, _HC2 = -7046029254386353131, -4658895280553007687
+_BUCKET_MUL = -2960836687051489901       # odd 64-bit multiplier (0xD6E8FEB86659FD93 as a signed number)
+_BUCKET_W = 8                             # keys per bucket: one 64-byte row
 
 
-def cuckoo_table(keys, max_kick=500):
-    """Two-choice cuckoo hash of the phrase keys at load <= 1/8: lookup = 2 probes (full2.py:126-150)."""
-    M = 1 << max(10, int(np.ceil(np.log2(max(len(keys), 1) * 8))))
-    mask = M - 1
-    with np.errstate(over="ignore"):
-        h1 = ((keys * np.int64(_HC1)) >> 24) & mask
-        h2 = ((keys * np.int64(_HC2)) >> 24) & mask
-    owner = np.full(M, -1, dtype=np.int64)
-    for i in range(len(keys)):
-        cur, slot = i, h1[i]
-        for _ in range(max_kick):
-            if owner[slot] < 0:
-                owner[slot] = cur
-                break
-            owner[slot], cur = cur, owner[slot]
-            slot = h2[cur] if slot == h1[cur] else h1[cur]
-        else:
-            raise RuntimeError("cuckoo: could not place a key - enlarge the table")
-    hk = np.full(M, -(1 << 62), dtype=np.int64)
-    hv = np.zeros(M, dtype=np.int64)
-    used = owner >= 0
-    hk[used] = keys[owner[used]]
-    hv[used] = owner[used]
-    return hk, hv, mask
+def bucket_table(keys, width=_BUCKET_W):
+    """Phrase keys -> (bucket rows of keys (M, width), rows of their numbers, M - 1).  A key lives in the row its hash
+    names, anywhere among the row's `width` places: a lookup is ONE hash and one 64-byte row to compare, no second
+    probe and no chain.  Built without a Python loop over the keys: sort by bucket, number the keys inside their
+    bucket, and double the table in the rare case that a bucket overflows (at one key per bucket on average the chance
+    that any of 2^18 buckets gets more than eight is below 1e-3).  Stands where the reference has a two-choice cuckoo
+    table (full2.py:126-150); the tables are not part of a checkpoint, so the layout is free."""
+    n = len(keys)
+    M = 1 << max(8, int(np.ceil(np.log2(max(n, 1)))))
+    while True:
+        with np.errstate(over="ignore"):
+            bucket = ((keys * np.int64(_BUCKET_MUL)) >> 40) & (M - 1)
+        order = np.argsort(bucket, kind="stable")
+        b_sorted = bucket[order]
+        place = np.arange(n) - np.searchsorted(b_sorted, b_sorted, side="left")
+        if n == 0 or place.max() < width:
+            break
+        M *= 2
+    rows = np.full((M, width), -(1 << 62), dtype=np.int64)               # no key is that negative
+    numbers = np.zeros((M, width), dtype=np.int64)
+    rows[b_sorted, place] = keys[order]
+    numbers[b_sorted, place] = order
+    return rows, numbers, M - 1
 
 
 class HeavyCtxAttn(nn.Module):
-    """Optional: a heavy layer looks back into the light states of earlier words (full2.py:1245-1266)."""
+    """Optional: before a heavy layer every anchor looks back into the light states of the words up to itself
+    (cross-attention without positions; zero-initialised output, so the model starts as if it were absent).
+    (full2.py:1245-1266)"""
 
     def __init__(self, d, heads=8):
         super().__init__()
         self.h = heads
         self.nq, self.nk = nn.RMSNorm(d), nn.RMSNorm(d)
-        self.q = nn.Linear(d, d, bias=False)
-        self.kv = nn.Linear(d, 2 * d, bias=False)
-        self.o = nn.Linear(d, d, bias=False)
+        self.q, self.kv, self.o = (nn.Linear(d, n * d, bias=False) for n in (1, 2, 1))
         nn.init.zeros_(self.o.weight)
 
+    def _heads(self, t, parts):
+        """(B, L, parts * D) -> parts tensors (B, heads, L, D / heads)"""
+        B, L, _ = t.shape
+        return t.view(B, L, parts, self.h, -1).permute(2, 0, 3, 1, 4)
+
     def forward(self, a, ctx, idx):
-        B, A, D = a.shape
-        T = ctx.shape[1]
-        hd = D // self.h
-        q = self.q(self.nq(a)).view(B, A, self.h, hd).transpose(1, 2)
-        k, v = self.kv(self.nk(ctx)).view(B, T, 2, self.h, hd).permute(2, 0, 3, 1, 4)
-        mask = (torch.arange(T, device=a.device)[None, None, :] <= idx[:, :, None])[:, None]
-        y = F.scaled_dot_product_attention(q, k.type_as(q), v.type_as(q), attn_mask=mask)
-        return a + self.o(y.transpose(1, 2).reshape(B, A, D))
+        (q,) = self._heads(self.q(self.nq(a)), 1)
+        k, v = self._heads(self.kv(self.nk(ctx)), 2)
+        word = torch.arange(ctx.shape[1], device=a.device)
+        may_see = (word[None, None, :] <= idx[:, :, None])[:, None]            # anchor at position p sees words <= p
+        y = F.scaled_dot_product_attention(q, k.type_as(q), v.type_as(q), attn_mask=may_see)
+        return a + self.o(y.transpose(1, 2).flatten(2))
 
 
 class MemArchLM(nn.Module):
@@ -242,7 +245,7 @@ class MemArchLM(nn.Module):
         K = len(tg["keys"])
         self.register_buffer(name + "_keys", tg["keys"].long(), persistent=False)
         if name == "phr" and c.phr_hash:
-            hk, hv, self.phr_hmask = cuckoo_table(tg["keys"].long().numpy())
+            hk, hv, self.phr_hmask = bucket_table(tg["keys"].long().numpy())
             self.register_buffer("phr_hkey", torch.from_numpy(hk), persistent=False)
             self.register_buffer("phr_hval", torch.from_numpy(hv), persistent=False)
         emb = nn.Embedding(K + 1, c.d)
@@ -270,11 +273,10 @@ class MemArchLM(nn.Module):
     def _phr_idx(self, x):
         if hasattr(self, "phr_hkey"):
             ctx = torch.cat([torch.full_like(x[:, :1], -1), x[:, :-1]], 1) * self.phr_V + x
-            K = self.phr_keys.numel()
-            s1 = ((ctx * _HC1) >> 24) & self.phr_hmask
-            s2 = ((ctx * _HC2) >> 24) & self.phr_hmask
-            return torch.where(self.phr_hkey[s1] == ctx, self.phr_hval[s1],
-                               torch.where(self.phr_hkey[s2] == ctx, self.phr_hval[s2], torch.full_like(ctx, K)))
+            row = ((ctx * _BUCKET_MUL) >> 40) & self.phr_hmask
+            same = self.phr_hkey[row] == ctx[..., None]                 # at most one place of the row holds the key
+            found = (self.phr_hval[row] * same).sum(-1)
+            return torch.where(same.any(-1), found, torch.full_like(ctx, self.phr_keys.numel()))
         return ref.phrase_index(x, self.phr_keys, self.phr_V)
 
     def _lock_votes(self, x, prep=None):

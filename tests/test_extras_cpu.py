@@ -845,3 +845,28 @@ def test_small_switches_of_the_light_blocks_and_inputs():
     text = float(g.train_loss(o, y, True, extra={"rem": rem, "synth": False})) - plain
     synth = float(g.train_loss(o, y, True, extra={"rem": rem, "synth": True})) - plain
     assert abs(synth - 3.0 * text) < 1e-4 and text > 0
+
+
+def test_one_probe_bucket_table_for_phrase_keys():
+    import numpy as np
+    from memarch_b200.models.memarch import _BUCKET_MUL, bucket_table
+    rng = np.random.default_rng(0)
+    V = 50304
+    for K in (0, 1, 700, 40000):
+        keys = np.unique(rng.integers(0, V * V, K).astype(np.int64))
+        rows, numbers, mask = bucket_table(keys)
+        assert rows.shape == numbers.shape and rows.shape[1] == 8 and rows.shape[0] == mask + 1
+        assert int((rows >= 0).sum()) == len(keys)                            # every key sits in exactly one place
+        probe = torch.from_numpy(np.concatenate([keys[:3000], rng.integers(-V, V * V, 3000)])).long()
+        row = ((probe * _BUCKET_MUL) >> 40) & mask
+        same = torch.from_numpy(rows)[row] == probe[..., None]
+        got = torch.where(same.any(-1), (torch.from_numpy(numbers)[row] * same).sum(-1), torch.full_like(probe, len(keys)))
+        kt = torch.from_numpy(keys)
+        if len(keys):
+            pos = torch.searchsorted(kt, probe).clamp(max=len(keys) - 1)
+            want = torch.where(kt[pos] == probe, pos, torch.full_like(pos, len(keys)))
+        else:
+            want = torch.zeros_like(probe)
+        assert torch.equal(got, want)
+    rows, _, mask = bucket_table((np.arange(4000, dtype=np.int64) * 7919) ** 2, width=2)
+    assert int((rows >= 0).sum()) == 4000 and mask + 1 > 4096

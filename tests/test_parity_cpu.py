@@ -78,6 +78,7 @@ def compare(d, m, rtol=2e-4):
     ("Fv2s", {"ATTN_IMPL": "block"}, 256),                        # dense heavy stack; memory demotes and prunes
     ("Fv3s", {"ATTN_IMPL": "block"}, 256),                        # volume memory (v3): pieces, merge on prune
     ("Fv2moeKs8", {"LIGHT_MOE": "8:2", "NO_MEM": "1"}, 64),       # light layers with their own small MoE
+    ("Fv2moeKs8", {"HEAVY_ATTN": "1", "NO_MEM": "1"}, 64),        # anchors look back into the light states
 ])
 def test_model_matches_reference(tmp_path, name, env, T):
     from memarch_b200.build import build

@@ -731,20 +731,19 @@ class MemArchLM(nn.Module):
         return torch.cat(reads, 1), snaps, st
 
     def _reread_pass(self, h, x, snaps, seg):
-        """Re-reading for all segments as one batch: segment k sees memory snapshot k (full2.py:1820-1840)."""
+        """Re-reading for all segments as one batch (full2.py:1820-1840).  The batch is segment-major: row j * B + b
+        is segment j of text b, and it reads the memory as it stood BEFORE that segment (snapshot j)."""
         B, T, d = h.shape
         n = len(snaps)
-        pad = n * seg - T
-        hs = F.pad(h.float(), (0, 0, 0, pad)).view(B, n, seg, d).transpose(0, 1).reshape(n * B, seg, d)
-        cat = lambda i: torch.stack([sn[i] for sn in snaps]).reshape(n * B, *snaps[0][i].shape[1:])
-        faces, contents, pos, valid = cat(0), cat(1), cat(2), cat(3)
-        qpos = (torch.arange(n, device=h.device)[:, None] * seg + torch.arange(seg, device=h.device)).repeat_interleave(B, 0)
-        rows = torch.arange(B, device=h.device).repeat(n)
-        o, cost = self.reread(hs, x.contiguous(), self.book.weight, faces, contents, pos, valid, qpos, rows)
+        words = F.pad(h.float(), (0, 0, 0, n * seg - T)).unflatten(1, (n, seg))              # (B, n, seg, d)
+        faces, contents, pos, valid = (torch.stack(part).flatten(0, 1) for part in zip(*snaps))
+        where = torch.arange(n * seg, device=h.device).view(n, 1, seg).expand(n, B, seg).flatten(0, 1)
+        text = torch.arange(B, device=h.device).repeat(n)
+        o, cost = self.reread(words.transpose(0, 1).flatten(0, 1), x.contiguous(), self.book.weight,
+                              faces, contents, pos, valid, where, text)
         if not self.use_memory:
             o, cost = o * 0, cost * 0
-        o = o.view(n, B, seg, d).transpose(0, 1).reshape(B, n * seg, d)[:, :T]
-        return o, cost
+        return o.unflatten(0, (n, B)).transpose(0, 1).flatten(1, 2)[:, :T], cost
 
     # ------------------------------------------------------------------------------------------ loss
     def _head_w(self, hn):

@@ -251,16 +251,20 @@ def _read_chunk(qc, kr, v, k0, q0c, c0, st, en, tval, tpos, W, rgrad, rgrad_scal
     sc = 1.0 / math.sqrt(hd)
     qi = c0 + torch.arange(C, device=qc.device)
     t = torch.arange(T, device=qc.device)
-    in_k = (st[..., None] <= t) & (t < en[..., None]) & tval[..., None]           # (B,H,C,K,T)
     s = torch.einsum("bhcd,bhtd->bhct", qc.float(), kr.float()) * sc
+    gb = None
     if rgrad:
         kb = k0.gather(2, tpos.reshape(B, H, -1, 1).expand(-1, -1, -1, hd)).view(B, H, C, -1, hd)
         rsel = torch.einsum("bhcd,bhckd->bhck", q0c.float(), kb.float()) * sc
         gb = torch.where(tval, rsel * rgrad_scale, torch.zeros_like(rsel))
-        s_span = s + torch.einsum("bhck,bhckt->bhct", gb, in_k.float())
-    else:
-        s_span = s
-    span = in_k.any(-2)
+    # one opened anchor at a time: the (query, anchor, key) table never exists, only (query, key) ones
+    span = torch.zeros_like(s, dtype=torch.bool)
+    s_span = s
+    for j in range(st.shape[-1]):
+        inside = (st[..., j, None] <= t) & (t < en[..., j, None]) & tval[..., j, None]
+        span = span | inside
+        if gb is not None:
+            s_span = s_span + gb[..., j, None] * inside
     dist = qi[:, None] - t[None, :]
     win = (dist >= 0) & (dist < W)
     s_all = torch.where(win[None, None], s, torch.where(span, s_span, torch.full_like(s, -float("inf"))))

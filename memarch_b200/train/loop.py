@@ -361,7 +361,8 @@ def train(args, device=None, env=None, out=None, parallel=None):
         ck_every = int(env.get("CKPT_EVERY", 0))
         start = 1
         if ck is not None:
-            start, log0 = ck.load(tr, data)
+            # RESUME_FORCE=1: take a checkpoint written under other run arguments, knowingly
+            start, log0 = ck.load(tr, data, strict_run=env.get("RESUME_FORCE") != "1")
             log += log0
             if start > 1:
                 print(f"resuming at step {start} from {ck.path}", file=out, flush=True)

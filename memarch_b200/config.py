@@ -68,6 +68,7 @@ class ModelConfig:
     moe_cap_align: int = 0        # MOE_CAP_ALIGN
     moe_dropless: bool = False    # MOE_GMM: no token is dropped (a place for every anchor in every expert; padding costs no GEMM work)
     moe_group: int = 512
+    layer_stats: bool = False     # LAYER_STATS: per-layer MoE statistics (dropped share, experts in use) and the mean fill
     heavy_attn: bool = False
     heavy_attn_detach: bool = False
     n_draft: int = 0
@@ -328,6 +329,7 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     # unfilled places through the per-expert fill counts
     if g("MOE_GMM") == "1": kw["moe_dropless"] = True
     if g("MOE_GROUP"): kw["moe_group"] = int(g("MOE_GROUP"))
+    if g("LAYER_STATS") == "1": kw["layer_stats"] = True
     if g("HEAVY_ATTN"): kw["heavy_attn"] = True
     if g("HEAVY_ATTN_DETACH"): kw["heavy_attn_detach"] = True
     if g("DRAFT"): kw["n_draft"] = int(g("DRAFT"))

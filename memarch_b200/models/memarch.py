@@ -123,6 +123,8 @@ class MemArchLM(nn.Module):
             self.heavy = nn.ModuleList(DenseFFN(d) for _ in range(c.heavy))
         for b in self.heavy:
             b.fill = c.frac / c.cap
+            if c.layer_stats and hasattr(b, "layer_stats"):
+                b.layer_stats = True
         self.final = nn.ModuleList(blk() for _ in range(c.final))
         for b in list(self.light_a) + list(self.light_b) + list(self.final):
             b.attn_gain = c.attn_gain
@@ -569,6 +571,10 @@ class MemArchLM(nn.Module):
                 dj = lin(an)
                 self._drafts.append((dj, pj.clamp(max=T - 1), okj))
                 h = ops.scatter_back(h, pj.clamp(max=T - 1), dj * okj[..., None])
+        if self.moe and c.layer_stats:
+            self.stats["moe_fill"] = sum(b.fill_now for b in self.heavy) / len(self.heavy)
+            self.stats["moe_drop_l"] = torch.stack([torch.as_tensor(b.dropped, dtype=torch.float32, device=h.device) for b in self.heavy])
+            self.stats["moe_active_l"] = torch.stack([b.active_now for b in self.heavy])
         if self.moe:
             self.stats["moe_drop"] = sum(b.dropped for b in self.heavy) / len(self.heavy)
             if self.heavy[0].wave:

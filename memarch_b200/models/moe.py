@@ -127,6 +127,8 @@ class AnchorMoE(nn.Module):
         self.w_dtype = w_dtype
         self.aux = torch.zeros(())
         self.dropped = torch.zeros(())
+        self.layer_stats = False
+        self.fill_now = self.active_now = torch.zeros(())
         self.register_buffer("s_mean", torch.tensor(5.0))
         self.wave, self.wave_every, self.students, self.hint_w = wave, wave_every, students, hint_w
         self.warm, self.err_thr = wave_warm, err_thr
@@ -184,6 +186,13 @@ class AnchorMoE(nn.Module):
             want_counts=True)
         self.aux, self.dropped = aux, dropped
         self._counts = counts                # filled places per expert (GPU): the expert GEMMs skip the padding
+        if self.layer_stats:                 # share of the capacity in use, experts with at least one place (collapse watch)
+            with torch.no_grad():
+                used = (flat_idx < self.E * C)
+                per_expert = torch.zeros(self.E + 1, device=x.device).index_add_(
+                    0, torch.where(used, flat_idx // C, torch.full_like(flat_idx, self.E)).reshape(-1),
+                    torch.ones(flat_idx.numel(), device=x.device))[:-1]
+                self.fill_now, self.active_now = used.float().sum() / float(self.E * C), (per_expert > 0).float().sum()
         return xf, table, wtab, flat_idx, C
 
     def forward(self, x, surprise=None):

@@ -557,6 +557,9 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     spikes.check(step, float(loss))
                     extra = "".join(f"  {k} {float(v):.2f}" for k, v in getattr(tr.model, "stats", {}).items()
                                     if torch.is_tensor(v) and v.numel() == 1)
+                    extra += "".join(f"  {k} [{' '.join(f'{x:.2f}' for x in v.tolist())}]"       # per-layer statistics
+                                     for k, v in getattr(tr.model, "stats", {}).items()
+                                     if torch.is_tensor(v) and v.dim() == 1 and 1 < v.numel() <= 64 and k.endswith("_l"))
                     sets = run_evals()
                     hoop = getattr(tr.model, "hoop", None)
                     if hoop is not None and "uroboros_eaten" in tr.model.stats:

@@ -870,3 +870,19 @@ def test_one_probe_bucket_table_for_phrase_keys():
         assert torch.equal(got, want)
     rows, _, mask = bucket_table((np.arange(4000, dtype=np.int64) * 7919) ** 2, width=2)
     assert int((rows >= 0).sum()) == 4000 and mask + 1 > 4096
+
+
+def test_moe_layer_statistics():
+    from memarch_b200 import build
+    torch.manual_seed(0)
+    m = build("tiny", 256, env={"NO_MEM": "1", "MOE_ACT": "relu2", "LAYER_STATS": "1"}).train()
+    quiet = build("tiny", 256, env={"NO_MEM": "1", "MOE_ACT": "relu2"}).train()
+    x = torch.randint(0, 256, (2, 64))
+    m(x), quiet(x)
+    L = len(m.heavy)
+    assert m.stats["moe_drop_l"].shape == (L,) and m.stats["moe_active_l"].shape == (L,)
+    assert abs(float(m.stats["moe_drop_l"].mean()) - float(m.stats["moe_drop"])) < 1e-6
+    assert 0 < float(m.stats["moe_fill"]) <= 1 and bool((m.stats["moe_active_l"] <= m.heavy[0].E).all())
+    b = m.heavy[0]
+    # filled share = kept (token, choice) pairs over the capacity
+    assert "moe_fill" not in quiet.stats and "moe_drop_l" not in quiet.stats

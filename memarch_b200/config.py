@@ -187,6 +187,7 @@ class ModelConfig:
     ce_save: bool = False
     short_v: int = 0
     rare_cap: float = 0.3
+    reread_anch: float = 0.0      # REREAD_ANCH: only this share of every segment's words, the most surprising ones, re-read
     panic: float = 0.0
     head_dim: int = 64
 
@@ -413,6 +414,7 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("CE_SAVE") == "1": kw["ce_save"] = True
     if g("SHORT_V"): kw["short_v"] = int(g("SHORT_V"))
     if g("RARE_CAP"): kw["rare_cap"] = float(g("RARE_CAP"))
+    if g("REREAD_ANCH"): kw["reread_anch"] = float(g("REREAD_ANCH"))
     if g("MEM_LEAN") == "0": kw["memory"] = dataclasses.replace(cfg.memory, lean=False)
     return cfg.replace(**kw)
 

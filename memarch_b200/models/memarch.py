@@ -106,6 +106,7 @@ class MemArchLM(nn.Module):
         self._hfull = -1
         self._mix = self._tongue = None
         self._vp = None
+        self._surp = None                                # the light head's surprise of the last forward (B,T)
         self.stream_u = None                             # running common direction of the stream (the trainer copies the optimizer's U here)
         if c.fish_n:
             from .fishki import FishPool
@@ -506,6 +507,7 @@ class MemArchLM(nn.Module):
                 s_ = prep["surp"] if prep and "surp" in prep else self._phr_surp(x)
             else:
                 s_ = self._light_surprise(lh.detach(), x)
+            self._surp = s_
             A = max(1, round(T * self.cap))
             if not c.uroboros:
                 idx, valid = ops.select_anchors(s_, self.tau, A)    # this step's threshold is the one before its update
@@ -741,12 +743,23 @@ class MemArchLM(nn.Module):
         is segment j of text b, and it reads the memory as it stood BEFORE that segment (snapshot j)."""
         B, T, d = h.shape
         n = len(snaps)
-        words = F.pad(h.float(), (0, 0, 0, n * seg - T)).unflatten(1, (n, seg))              # (B, n, seg, d)
+        seg_major = lambda t: t.unflatten(1, (n, seg)).transpose(0, 1).flatten(0, 1)           # (B, n*seg, ..) -> (n*B, seg, ..)
+        words = seg_major(F.pad(h.float(), (0, 0, 0, n * seg - T)))
         faces, contents, pos, valid = (torch.stack(part).flatten(0, 1) for part in zip(*snaps))
         where = torch.arange(n * seg, device=h.device).view(n, 1, seg).expand(n, B, seg).flatten(0, 1)
         text = torch.arange(B, device=h.device).repeat(n)
-        o, cost = self.reread(words.transpose(0, 1).flatten(0, 1), x.contiguous(), self.book.weight,
-                              faces, contents, pos, valid, where, text)
+        book = (x.contiguous(), self.book.weight, faces, contents, pos, valid)
+        surp = self._surp if self.cfg.reread_anch else None
+        if surp is None:
+            o, cost = self.reread(words, *book, where, text)
+        else:
+            # only the most surprising words of every segment re-read (full2.py:1794-1808); the rest get nothing
+            k = max(1, int(round(seg * self.cfg.reread_anch)))
+            rank = seg_major(F.pad(surp.float(), (0, n * seg - T), value=-1e9))
+            chosen = rank.topk(k, -1).indices.sort(-1).values                                     # (n*B, k) in text order
+            at = chosen[..., None].expand(-1, -1, d)
+            o_k, cost = self.reread(words.gather(1, at), *book, where.gather(1, chosen), text)
+            o = torch.zeros(n * B, seg, d, dtype=o_k.dtype, device=h.device).scatter(1, at, o_k)
         if not self.use_memory:
             o, cost = o * 0, cost * 0
         return o.unflatten(0, (n, B)).transpose(0, 1).flatten(1, 2)[:, :T], cost

@@ -79,6 +79,7 @@ def compare(d, m, rtol=2e-4):
     ("Fv3s", {"ATTN_IMPL": "block"}, 256),                        # volume memory (v3): pieces, merge on prune
     ("Fv2moeKs8", {"LIGHT_MOE": "8:2", "NO_MEM": "1"}, 64),       # light layers with their own small MoE
     ("Fv2moeKs8", {"HEAVY_ATTN": "1", "NO_MEM": "1"}, 64),        # anchors look back into the light states
+    ("Fv2moeKs8", {"REREAD_SEP": "1", "REREAD_ANCH": "0.25", "ATTN_IMPL": "block"}, 160),                  # only the surprising words re-read; ragged last segment
 ])
 def test_model_matches_reference(tmp_path, name, env, T):
     from memarch_b200.build import build

@@ -316,6 +316,10 @@ def model_from_env(cfg: ModelConfig, env=None) -> ModelConfig:
     if g("ANCHOR_CAP"): kw["cap"] = float(g("ANCHOR_CAP"))
     if g("ANCHOR_FRAC"): kw["frac"] = float(g("ANCHOR_FRAC"))
     if g("CKPT"): kw["ckpt"] = g("CKPT")
+    # ACT_CKPT (the reference's per-layer activation checkpointing, fastloop.py:180-262): every layer recomputes in the
+    # backward pass.  Its "sel" policy keeps the outputs of library matmuls and recomputes the cheap ops; the layers
+    # here run on own autograd functions that already keep exactly what their backward needs, so "sel" is the same as on
+    elif g("ACT_CKPT"): kw["ckpt"] = "1"
     if g("NO_MEM"): kw["no_mem"] = True
     if g("NO_REREAD"): kw["no_reread"] = True
     if g("MOE_K"): kw["moe_k"] = int(g("MOE_K"))

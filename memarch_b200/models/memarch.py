@@ -82,6 +82,27 @@ class HeavyCtxAttn(nn.Module):
         return a + self.o(y.transpose(1, 2).flatten(2))
 
 
+class _HostPrep:
+    """CPU copies of the buffers that `MemArchLM.prep` reads, with that method and its helpers borrowed."""
+
+    _TABLES = ("phr_keys", "phr_hkey", "phr_hval", "phr4_keys", "lock_bucket", "sp_E", "sp_H", "sp_lp", "sp_lse")
+
+    def __init__(self, model):
+        self.vocab = model.vocab
+        for name in self._TABLES:
+            if hasattr(model, name):
+                setattr(self, name, getattr(model, name).detach().cpu())
+        for name in ("phr_V", "phr_hmask"):
+            if hasattr(model, name):
+                setattr(self, name, getattr(model, name))
+        for flag in ("phr", "phr4", "ind_a", "lock_w"):          # only their presence is asked for
+            if hasattr(model, flag):
+                setattr(self, flag, True)
+
+    def __call__(self, x):
+        return self.prep(x.cpu())
+
+
 class MemArchLM(nn.Module):
     def __init__(self, cfg: ModelConfig):
         super().__init__()
@@ -368,6 +389,13 @@ class MemArchLM(nn.Module):
         if hasattr(self, "sp_lse"):
             p["surp"] = self._phr_surp(x)
         return p
+
+    def host_prep(self):
+        """A stand-in that computes `prep` on the CPU (for the data loader's worker thread): copies of the token-only
+        tables on the host and the same functions.  What it returns is moved to the device with the batch, so the
+        step itself finds no lock, phrase index or phrase surprise left to compute (the reference's `CpuFeeder`,
+        fastloop.py:108-139)."""
+        return _HostPrep(self)
 
     @torch.no_grad()
     def table_rows(self, x):
@@ -1167,3 +1195,7 @@ class MemArchLM(nn.Module):
         for b in self.heavy:
             if hasattr(b, "before_step"):
                 b.before_step(step)
+
+
+for _name in ("prep", "_phr_idx", "_phr4_idx", "_phr_surp", "_locks_raw"):
+    setattr(_HostPrep, _name, getattr(MemArchLM, _name))

@@ -219,6 +219,7 @@ class _CorpusData:
             vc = ShardCorpus(w, root, seq=seq, seed=10 ** 6)
             self.val = TokenStore(vc.batch(max(2, 160 * 1024 // seq)).reshape(-1), 0, device)
         self._B, self._n = None, 0
+        self.host_prep = None                            # set by the loop with CPU_PREP=1 (`model.host_prep()`)
         # recall needles written into the training text (REMIND_P > 0): p schedule, optional distance ladder
         self.remind = None
         if float(env.get("REMIND_P", 0) or 0) > 0:
@@ -249,7 +250,15 @@ class _CorpusData:
                                     pack=pack, mix=mix)
 
     def _xform(self, xy, n):
-        return self.remind(xy, n=n)
+        extra = None
+        if self.remind is not None:
+            xy, extra = self.remind(xy, n=n)
+        if self.host_prep is not None:                   # token-only preparation on this (the loader's) thread
+            import torch
+            with torch.no_grad():
+                pr = self.host_prep(torch.from_numpy(np.ascontiguousarray(xy[:, :-1], dtype=np.int64)))
+            extra = dict(extra or {}, **{"prep_" + k: v.numpy() for k, v in pr.items()})
+        return xy, extra
 
     def batch(self, B, T):
         assert T == self.seq, "the corpus serves windows of one fixed length"
@@ -261,7 +270,7 @@ class _CorpusData:
                 self._n = st.get("loader_n", self._n)
             from ..data.loader import HostLoader
             self.loader, self._B = HostLoader(self.corpus, B, device=self.device, first=self._n,
-                                              xform=self._xform if self.remind is not None else None), B
+                                              xform=self._xform if (self.remind is not None or self.host_prep is not None) else None), B
         return self.loader.next()
 
     @property
@@ -352,6 +361,11 @@ def train(args, device=None, env=None, out=None, parallel=None):
     for name in args.models:
         tr = make_trainer(name, args.stage, args, device, env, parallel)
         diag.phase(f"model {name} and optimizer built")
+        if env.get("CPU_PREP") == "1" and hasattr(tr.model, "host_prep") and hasattr(data, "host_prep"):
+            if data.loader is not None:                  # a loader started for an earlier model: restart it with the new tables
+                st_ = data.state_dict()
+                data.load_state_dict(st_)
+            data.host_prep = tr.model.host_prep()        # locks, phrase indices and phrase surprise on the loader's thread
         cfg, apply, micro0 = _schedules(args, env, tr)
         log, train_time = [], 0.0
         ck = None
@@ -499,7 +513,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     ex_ = getattr(data, "extra", None)
                     mc_ = getattr(tr.model, "cfg", None)
                     if rb is None and ex_ is not None and (
-                            "kind" in ex_ or ("rem" in ex_ and max(getattr(mc_, "remind_w", 0), getattr(mc_, "remind_use_w", 0)) > 0)):
+                            "kind" in ex_ or any(k.startswith("prep_") for k in ex_) or ("rem" in ex_ and max(getattr(mc_, "remind_w", 0), getattr(mc_, "remind_use_w", 0)) > 0)):
                         rm_ = getattr(data, "remind", None)
                         synth_ = bool(rm_ is not None and rm_.synth_at(data.loader.n_done - 1))
                         npreps = needle_preps(tr.model, xy_b, ex_, tr.cfg.micro or len(xy_b), synth_)
@@ -650,7 +664,11 @@ def needle_preps(model, xy, extra, micro, synth=False):
     out = []
     for i0 in range(0, len(xy), micro):
         sl = {k: v[i0:i0 + micro] for k, v in ex.items()}
-        pr = model.prep(xy[i0:i0 + micro, :-1]) if hasattr(model, "ind_a") and hasattr(model, "prep") else {}
+        ready = {k[5:]: v for k, v in sl.items() if k.startswith("prep_")}
+        if ready:
+            pr = ready                                   # prepared on the loader's thread
+        else:
+            pr = model.prep(xy[i0:i0 + micro, :-1]) if hasattr(model, "ind_a") and hasattr(model, "prep") else {}
         needles = {k: v for k, v in sl.items() if k.startswith("rem")}
         if needles:
             if "ind_on" in pr:

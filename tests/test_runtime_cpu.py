@@ -1090,3 +1090,34 @@ def test_rollback_guard_by_kind_and_steps_of_another_shape():
     rb.step(xs[0], 9, kind=1)                                # a spike right after it: the synthetic step is undone too
     assert int(rb.n_hit) == 2
     assert all(torch.equal(p.data, b) for p, b in zip(tr.params, before))
+
+
+def test_token_preparation_on_the_loader_thread(tmp_path, monkeypatch):
+    from memarch_b200 import build
+    from memarch_b200.train.loop import train
+    import memarch_b200.train.loop as loop_mod
+    monkeypatch.chdir(tmp_path)
+    torch.manual_seed(0)
+    m = build("tiny", 2048, env={"NO_MEM": "1", "INDUCT": "lock", "INDUCT_MIX": "1"})
+    hp = m.host_prep()
+    x = torch.randint(0, 50, (3, 40))
+    want, got = m.prep(x), hp(x)
+    assert set(want) == set(got) and all(torch.equal(want[k], got[k]) for k in want)
+    w = make_corpus(str(tmp_path / "corpus"), docs=60)
+    env = {"VOCAB": "2048", "NO_MEM": "1", "WATCHDOG": "0", "CORPUS": json.dumps(w), "CORPUS_ROOT": str(tmp_path / "corpus"),
+           "INDUCT": "lock", "INDUCT_MIX": "1", "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
+    a = Args(seq=48, batch=4, micro=2, steps=4, eval_every=4)
+    seen = []
+    real = loop_mod.Trainer.step
+
+    def spy(self, xy, step, preps=None, lr_mul=1.0):
+        seen.append(preps)
+        return real(self, xy, step, preps, lr_mul)
+    monkeypatch.setattr(loop_mod.Trainer, "step", spy)
+    plain = train(a, "cpu", env=env, out=io.StringIO())["tiny"]
+    assert all(p is None for p in seen)
+    seen.clear()
+    fed = train(a, "cpu", env=dict(env, CPU_PREP="1"), out=io.StringIO())["tiny"]
+    assert len(seen) == 4 and all(len(p) == 2 and {"ind_cand", "ind_on", "ind_bk", "ind_src"} <= set(p[0]) for p in seen)
+    assert seen[0][0]["ind_cand"].shape[0] == 2                            # one dict per micro-batch
+    assert abs(plain[-1]["val"] - fed[-1]["val"]) < 1e-5                   # the same run, prepared elsewhere

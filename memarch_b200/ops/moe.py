@@ -9,6 +9,8 @@ fp32 accumulate), `row_dot` (slot-weight grads) and the grouped tcgen05 GEMMs wi
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _ext, ref
@@ -202,6 +204,11 @@ def route_and_slot(xf, router_w, real, k_tok, k_max, E, C, want_counts=False):
         else:
             table, _, flat_idx, dropped = ref.moe_slots(e_flat, w.detach(), E, C)
     ok = flat_idx < E * C
+    if not _ext.use_cuda(xf) and os.environ.get("CHECK") == "1":
+        # CHECK=1 (CPU only): every choice that got a place and that place point at each other (full2.py:567-570)
+        tok = torch.arange(flat_idx.shape[0], device=xf.device)[:, None].expand_as(flat_idx)
+        assert bool((table[flat_idx[ok]] == tok[ok]).all()), "slot table and inverse table disagree"
+        assert int((table < flat_idx.shape[0]).sum()) == int(ok.sum()), "filled places and placed choices differ"
     # slot weights as a differentiable gather-free scatter: wtab[flat_idx[n,j]] = w[n,j]
     wtab = torch.zeros(E * C + 1, device=xf.device, dtype=w.dtype).scatter(
         0, flat_idx.reshape(-1), (w * ok).reshape(-1))[:-1]

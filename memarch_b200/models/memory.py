@@ -164,52 +164,84 @@ class CardMemory(nn.Module):
         g = torch.sigmoid(self.focus_gate(torch.cat([n, foc], -1)))
         return self.out(g * foc + (1 - g) * mem), w.detach()
 
+    # -------------------------------------------------------------------------------------------- write: shared steps
+    def _words(self, h):
+        """What a segment offers to the memory: (normed state, face, importance) of every word."""
+        n = self.norm_w(h)
+        return n, self.face(n), torch.sigmoid(self.importance(n))
+
+    @staticmethod
+    def _count_reads(st, w_read, now):
+        """Cards this segment looked at: their use count grows, a card read with weight > 0.5 counts as touched now."""
+        st = dict(st)
+        if w_read is not None:
+            used = w_read.float().sum(1).detach()
+            st["uses"] = st["uses"] + used
+            st["touched"] = torch.where(used > 0.5, torch.zeros_like(st["touched"]) + now, st["touched"])
+        return st
+
+    def _candidates(self, f, imp, st, W):
+        """The W words worth writing: new (unlike every card's faces) and important.  For each of them the most
+        similar card and whether it is similar enough to be an update.  -> (brightness of all words, cand, best, upd)"""
+        fa = F.normalize(st["faces"], dim=-1)
+        alike = lambda q: torch.einsum("bsf,bclf->bscl", F.normalize(q, dim=-1).type_as(fa), fa).amax(-1)
+        known = alike(f).masked_fill(~st["valid"][:, None], -1).amax(-1)
+        bright = (1 - known.clamp(min=0)) * imp.squeeze(-1).float()
+        cand = bright.topk(W, -1).indices
+        best_cos, best = alike(_rows(f, cand)).masked_fill(~st["valid"][:, None], -2).max(-1)
+        return bright, cand, best, best_cos > self.match
+
+    def _bank_order(self, st, now):
+        """Strength of the cards in the fresh and in the dim bank (empty places weakest of all)."""
+        strength, Fn, ok = self.score(st, now), self.Fn, st["valid"]
+        empty = torch.full_like(strength, -2e9)
+        return torch.where(ok, strength, empty)[:, :Fn], torch.where(ok, strength, empty)[:, Fn:]
+
+    def _promotion(self, w_read, st, key_f, like):
+        """A dim card that this segment read a lot (total weight > 1) trades places with the weakest fresh card."""
+        B, Fn = like.shape[0], self.Fn
+        if w_read is None:
+            zero = torch.zeros(B, dtype=torch.long, device=like.device)
+            return torch.zeros(B, dtype=torch.bool, device=like.device), zero, zero
+        heat = w_read.float().sum(1)[:, Fn:].masked_fill(~st["valid"][:, Fn:], 0)
+        hot_v, hot = heat.max(-1)
+        return hot_v > 1.0, hot, key_f.argmin(-1)
+
+    def _swap(self, fc, dc, meta, promote, hot, weak):
+        """Exchange the hot dim card and the weak fresh card (contents through the compression, every meta field)."""
+        pm, hf, wf = promote[:, None], hot[:, None], weak[:, None]
+        up_c, down_c = self.up(_rows(dc, hf)), self.down(_rows(fc, wf))
+        fc, dc = masked_put(fc, wf, up_c, pm), masked_put(dc, hf, down_c, pm)
+        hfull = hf + self.Fn
+        for k, t in meta.items():
+            a, b = _rows(t, wf), _rows(t, hfull)
+            meta[k] = masked_put(masked_put(t, wf, b, pm), hfull, a, pm)
+        return fc, dc, meta
+
+    def _dim_strength(self, meta, now):
+        return (meta["bright"] + self.w_use * meta["uses"] - self.w_age * (now - meta["touched"]))[:, self.Fn:]
+
     # -------------------------------------------------------------------------------------------- write
     @torch.no_grad()
     def plan_write(self, f, imp, st, now, w_read):
         """Discrete decisions of one write (no gradients): returns a dict of index/mask tensors."""
-        Fn = self.Fn
-        S = f.shape[1]
-        fa = F.normalize(st["faces"], dim=-1)
-        sim = torch.einsum("bsf,bclf->bscl", F.normalize(f, dim=-1).type_as(fa), fa).amax(-1)
-        sim = sim.masked_fill(~st["valid"][:, None], -1).amax(-1)
-        bright = (1 - sim.clamp(min=0)) * imp.squeeze(-1).float()
-        W = min(self.W, S)
-        cand = bright.topk(W, -1).indices
-        cos = torch.einsum("bwf,bclf->bwcl", F.normalize(_rows(f, cand), dim=-1).type_as(fa), fa).amax(-1)
-        best_cos, best = cos.masked_fill(~st["valid"][:, None], -2).max(-1)
-        upd = best_cos > self.match
+        bright, cand, best, upd = self._candidates(f, imp, st, min(self.W, f.shape[1]))
         is_new = ~upd
-        score = self.score(st, now)
-        key_f = torch.where(st["valid"][:, :Fn], score[:, :Fn], torch.full_like(score[:, :Fn], -2e9))
+        key_f, key_d = self._bank_order(st, now)
+        # a new card takes the weakest fresh place; a card that sat there moves to the weakest dim place
         slot = key_f.argsort(dim=-1, stable=True).gather(1, (_count_before(is_new) - 1).clamp(min=0))
         demote = is_new & _rows(st["valid"], slot)
-        key_d = torch.where(st["valid"][:, Fn:], score[:, Fn:], torch.full_like(score[:, Fn:], -2e9))
         dslot = key_d.argsort(dim=-1, stable=True).gather(1, (_count_before(demote) - 1).clamp(min=0))
-        B = f.shape[0]
-        if w_read is not None:
-            heat = w_read.float().sum(1)[:, Fn:].masked_fill(~st["valid"][:, Fn:], 0)
-            hot_v, hot = heat.max(-1)
-            promote = hot_v > 1.0
-            weak = key_f.argmin(-1)
-        else:
-            promote = torch.zeros(B, dtype=torch.bool, device=f.device)
-            hot = weak = torch.zeros(B, dtype=torch.long, device=f.device)
+        promote, hot, weak = self._promotion(w_read, st, key_f, f)
         return dict(bright=bright, cand=cand, best=best, upd=upd, is_new=is_new, slot=slot, demote=demote,
                     dslot=dslot, promote=promote, hot=hot, weak=weak)
 
     def write(self, h, positions, st, now, w_read=None):
         """h (B,S,d) word states in context; positions (B,S); w_read (B,S,C) how this segment read the cards."""
         Fn = self.Fn
-        n = self.norm_w(h)
-        f = self.face(n)
-        imp = torch.sigmoid(self.importance(n))
+        n, f, imp = self._words(h)
         c_all = None if self.lean else self.content(n) * imp
-        st = dict(st)
-        if w_read is not None:
-            used = w_read.float().sum(1).detach()
-            st["uses"] = st["uses"] + used
-            st["touched"] = torch.where(used > 0.5, torch.zeros_like(st["touched"]) + now, st["touched"])
+        st = self._count_reads(st, w_read, now)
         p = self.plan_write(f, imp, st, now, w_read)
         cand, best, upd, is_new, slot, demote, dslot = (p[k] for k in
                                                         ("cand", "best", "upd", "is_new", "slot", "demote", "dslot"))
@@ -242,20 +274,12 @@ class CardMemory(nn.Module):
         meta["bright"] = masked_put(meta["bright"], best, torch.maximum(bw, _rows(meta["bright"], best)), upd)
         meta["touched"] = masked_put(meta["touched"], best, now_w, upd)
         # 4) swap: hot dim card <-> weakest fresh card
-        pm = p["promote"][:, None]
-        hf, wf = p["hot"][:, None], p["weak"][:, None]
-        hot_c, weak_c = self.up(_rows(dc, hf)), self.down(_rows(fc, wf))
-        fc, dc = masked_put(fc, wf, hot_c, pm), masked_put(dc, hf, weak_c, pm)
-        hfull = hf + Fn
-        for k, t in meta.items():
-            a, b = _rows(t, wf), _rows(t, hfull)
-            meta[k] = masked_put(masked_put(t, wf, b, pm), hfull, a, pm)
+        fc, dc, meta = self._swap(fc, dc, meta, p["promote"], p["hot"], p["weak"])
         # 5) prune the dim bank back to `dim` strongest once it reaches its ceiling
         with torch.no_grad():
             valid = meta["valid"]
             over = valid[:, Fn:].sum(1) > self.Dmax - self.W
-            sc = (meta["bright"] + self.w_use * meta["uses"] - self.w_age * (now - meta["touched"]))[:, Fn:]
-            sc = sc.masked_fill(~valid[:, Fn:], -1e9)
+            sc = self._dim_strength(meta, now).masked_fill(~valid[:, Fn:], -1e9)
             keep = sc.argsort(dim=-1, descending=True, stable=True).argsort(dim=-1, stable=True) < self.Dn
             meta["valid"] = torch.cat([valid[:, :Fn], torch.where(over[:, None], valid[:, Fn:] & keep, valid[:, Fn:])], 1)
         return dict(fc=fc, dc=dc, **meta)
@@ -279,41 +303,19 @@ class VolumeMemory(CardMemory):
         B, S, d = h.shape
         Fn = self.Fn
         dev = h.device
-        n = self.norm_w(h)
-        f = self.face(n)
-        imp = torch.sigmoid(self.importance(n))
+        n, f, imp = self._words(h)
         c = self.content(n) * imp
-        st = dict(st)
-        if w_read is not None:
-            used = w_read.float().sum(1).detach()
-            st["uses"] = st["uses"] + used
-            st["touched"] = torch.where(used > 0.5, torch.zeros_like(st["touched"]) + now, st["touched"])
+        st = self._count_reads(st, w_read, now)
         with torch.no_grad():
-            fa = F.normalize(st["faces"], dim=-1)
-            sim = torch.einsum("bsf,bclf->bscl", F.normalize(f, dim=-1).type_as(fa), fa).amax(-1)
-            sim = sim.masked_fill(~st["valid"][:, None], -1).amax(-1)
-            bright = (1 - sim.clamp(min=0)) * imp.squeeze(-1).float()
             W = min(self.W, S, Fn)
-            cand = bright.topk(W, -1).indices
-            cos = torch.einsum("bwf,bclf->bwcl", F.normalize(_rows(f, cand), dim=-1).type_as(fa), fa).amax(-1)
-            best_cos, best = cos.masked_fill(~st["valid"][:, None], -2).max(-1)
-            upd = best_cos > self.match
-            new_id = st["next_id"][:, None] + torch.arange(W, device=dev)
-            cid = torch.where(upd, st["card"].gather(1, best), new_id)
-            score = self.score(st, now)
-            key_f = torch.where(st["valid"][:, :Fn], score[:, :Fn], torch.full_like(score[:, :Fn], -2e9))
-            slot = key_f.argsort(dim=-1, stable=True)[:, :W]
+            bright, cand, best, upd = self._candidates(f, imp, st, W)
+            # a piece about a known card carries that card's id, anything else starts a new card
+            cid = torch.where(upd, st["card"].gather(1, best), st["next_id"][:, None] + torch.arange(W, device=dev))
+            key_f, key_d = self._bank_order(st, now)
+            slot = key_f.argsort(dim=-1, stable=True)[:, :W]          # every written piece takes a fresh place
             demote = _rows(st["valid"], slot)
-            key_d = torch.where(st["valid"][:, Fn:], score[:, Fn:], torch.full_like(score[:, Fn:], -2e9))
             dslot = key_d.argsort(dim=-1, stable=True).gather(1, (_count_before(demote) - 1).clamp(min=0))
-            if w_read is not None:
-                heat = w_read.float().sum(1)[:, Fn:].masked_fill(~st["valid"][:, Fn:], 0)
-                hot_v, hot = heat.max(-1)
-                promote = hot_v > 1.0
-                weak = key_f.argmin(-1)
-            else:
-                promote = torch.zeros(B, dtype=torch.bool, device=dev)
-                hot = weak = torch.zeros(B, dtype=torch.long, device=dev)
+            promote, hot, weak = self._promotion(w_read, st, key_f, f)
         fw, cw, pw, bw = _rows(f, cand), _rows(c, cand), _rows(positions, cand), bright.gather(1, cand)
         fc, dc = st["fc"], st["dc"]
         meta = {k: st[k] for k in self.META}
@@ -338,19 +340,12 @@ class VolumeMemory(CardMemory):
                      ("touched", now_w), ("card", cid)):
             meta[k] = masked_put(meta[k], slot, v, yes)
         next_id = st["next_id"] + W
-        pm = promote[:, None]
-        hf, wf = hot[:, None], weak[:, None]
-        hot_c, weak_c = self.up(_rows(dc, hf)), self.down(_rows(fc, wf))
-        fc, dc = masked_put(fc, wf, hot_c, pm), masked_put(dc, hf, weak_c, pm)
-        for k, t in meta.items():
-            a, b = _rows(t, wf), _rows(t, hf + Fn)
-            meta[k] = masked_put(masked_put(t, wf, b, pm), hf + Fn, a, pm)
+        fc, dc, meta = self._swap(fc, dc, meta, promote, hot, weak)
         with torch.no_grad():
             valid = meta["valid"]
             vd = valid[:, Fn:]
             over = vd.sum(1) > self.Dmax - self.W
-            sc = (meta["bright"] + self.w_use * meta["uses"] - self.w_age * (now - meta["touched"]))[:, Fn:]
-            sc = sc.masked_fill(~vd, 1e9)
+            sc = self._dim_strength(meta, now).masked_fill(~vd, 1e9)
             rank = sc.argsort(dim=-1, stable=True).argsort(dim=-1, stable=True)
             drop = over[:, None] & vd & (rank < (vd.sum(1, keepdim=True) - self.Dn))
             cd = meta["card"][:, Fn:]

@@ -559,38 +559,7 @@ class MemArchLM(nn.Module):
             self._hoop = (pred, idx)
             s_, A = pred.detach(), idx.shape[1]          # what the heavy layers see as the words' surprise
 
-        a_in = ops.gather_tokens(h, idx)
-        a = a_in
-        sa = None
-        if self.moe:
-            sa = torch.where(valid, s_.gather(1, idx).clamp(0, 50), torch.full_like(s_[:, :A], -1.0))
-        ctx = h.detach() if c.heavy_attn_detach else h
-        full = self._full_layer(prep)
-        if full is None:
-            for li, b in enumerate(self.heavy):
-                if hasattr(self, "h_attn"):
-                    a = self.h_attn[li](a, ctx, idx)
-                a = self._run(b, a, sa, heavy=True)
-            h = ops.scatter_back(h, idx, (a - a_in) * valid[..., None])
-        else:
-            # a "full" layer works on all words instead of the anchors only: the anchors' states are written into the
-            # stream, the layer runs over every word (all places real: fill 1), the anchors are read back; the order
-            # of the layers does not change (memarch_jax/memarch_jax/moe.py:298-354 of the reference's JAX port)
-            gi = idx[..., None].expand(-1, -1, h.shape[-1])
-            put = lambda hh, a_: hh.scatter(1, gi, torch.where(valid[..., None], a_.to(hh.dtype), hh.gather(1, gi)))
-            s_all = s_.clamp(0, 50) if self.moe else None
-            hh = h
-            for li, b in enumerate(self.heavy):
-                if hasattr(self, "h_attn"):
-                    a = self.h_attn[li](a, ctx, idx)
-                if full < 0 or full == li:
-                    fill, b.fill = b.fill, 1.0
-                    hh = self._run(b, put(hh, a), s_all, heavy=True)
-                    b.fill = fill
-                    a = hh.gather(1, gi)
-                else:
-                    a = self._run(b, a, sa, heavy=True)
-            h = put(hh, a)
+        h, a = self.heavy_pass(h, idx, valid, s_, self._full_layer(prep))
         if self.n_draft:
             an = self.draft_norm(a)
             self._drafts = []
@@ -616,6 +585,42 @@ class MemArchLM(nn.Module):
                     self.stats["move_r"] = sum((b.last_move / b.move_peak.clamp(min=1e-12)).min() for b in self.heavy) / L
 
         return self._tail(h, lh, x, snaps, seg, win)
+
+    def heavy_pass(self, h, idx, valid, s_, full=None):
+        """The heavy layers on the anchors `idx` (B,A; `valid` marks the real ones), `s_` (B,T) the words' surprise.
+        `full`: None - anchors only; k - layer k works on ALL words in this step; -1 - every layer does.  A "full" layer:
+        the anchors' states are written into the stream, the layer runs over every word (all places real: fill 1),
+        the anchors are read back; the order of the layers does not change (memarch_jax/memarch_jax/moe.py:298-354 of
+        the reference's JAX port).  Returns (stream, anchor states)."""
+        c = self.cfg
+        A = idx.shape[1]
+        a_in = ops.gather_tokens(h, idx)
+        a = a_in
+        sa = None
+        if self.moe:
+            sa = torch.where(valid, s_.gather(1, idx).clamp(0, 50), torch.full_like(s_[:, :A], -1.0))
+        ctx = h.detach() if c.heavy_attn_detach else h
+        if full is None:
+            for li, b in enumerate(self.heavy):
+                if hasattr(self, "h_attn"):
+                    a = self.h_attn[li](a, ctx, idx)
+                a = self._run(b, a, sa, heavy=True)
+            return ops.scatter_back(h, idx, (a - a_in) * valid[..., None]), a
+        gi = idx[..., None].expand(-1, -1, h.shape[-1])
+        put = lambda hh, a_: hh.scatter(1, gi, torch.where(valid[..., None], a_.to(hh.dtype), hh.gather(1, gi)))
+        s_all = s_.clamp(0, 50) if self.moe else None
+        hh = h
+        for li, b in enumerate(self.heavy):
+            if hasattr(self, "h_attn"):
+                a = self.h_attn[li](a, ctx, idx)
+            if full < 0 or full == li:
+                fill, b.fill = b.fill, 1.0
+                hh = self._run(b, put(hh, a), s_all, heavy=True)
+                b.fill = fill
+                a = hh.gather(1, gi)
+            else:
+                a = self._run(b, a, sa, heavy=True)
+        return put(hh, a), a
 
     def _full_layer(self, prep):
         """None: every heavy layer on the anchors.  -1: every layer on all words (`heavy_all`).  k: layer k on all

@@ -720,6 +720,43 @@ def test_heavy_layers_on_all_words():
         f, _ = rot(x)
         g, _ = base(x)
     assert torch.allclose(f[0], g[0], atol=1e-5)                           # evaluation: anchors only
+    # the pass itself against a hand-made one: anchors in, layer k over all words with every place real, anchors out
+    torch.manual_seed(3)
+    base.train()
+    B, T, d = 2, 64, base.cfg.d
+    h = torch.randn(B, T, d)
+    s_ = torch.rand(B, T) * 6
+    idx = torch.stack([torch.randperm(T)[:16].sort().values for _ in range(B)])
+    valid = torch.rand(B, 16) < 0.8
+    is_anchor = torch.zeros(B, T, dtype=torch.bool).scatter(1, idx, valid)
+    with torch.no_grad():
+        plain, _ = base.heavy_pass(h, idx, valid, s_)
+        assert torch.equal(plain[~is_anchor], h[~is_anchor])               # without a full layer only anchors change
+        k = L - 1
+        got, a_got = base.heavy_pass(h, idx, valid, s_, full=k)
+        assert not torch.equal(got[~is_anchor], h[~is_anchor])             # a full layer changes the other words too
+        gi = idx[..., None].expand(-1, -1, d)
+        sa = torch.where(valid, s_.gather(1, idx).clamp(0, 50), torch.full_like(s_[:, :16], -1.0))
+        a = h.gather(1, gi)
+        hh = h
+        for li, blk in enumerate(base.heavy):
+            if li == k:
+                hh = hh.scatter(1, gi, torch.where(valid[..., None], a, hh.gather(1, gi)))
+                keep, blk.fill = blk.fill, 1.0
+                hh = blk(hh, s_.clamp(0, 50))
+                blk.fill = keep
+                a = hh.gather(1, gi)
+            else:
+                a = blk(a, sa)
+        want = hh.scatter(1, gi, torch.where(valid[..., None], a, hh.gather(1, gi)))
+        assert torch.allclose(got, want, atol=1e-5)
+        every, _ = base.heavy_pass(h, idx, valid, s_, full=-1)            # all layers full = the layers in turn on all words
+        hh = h
+        for blk in base.heavy:
+            keep, blk.fill = blk.fill, 1.0
+            hh = blk(hh, s_.clamp(0, 50))
+            blk.fill = keep
+        assert torch.allclose(every, hh, atol=1e-5)
 
 
 def test_final_norm_variants_and_trunk_guard_in_the_model():

@@ -915,9 +915,6 @@ class MemArchLM(nn.Module):
     def _ce_part(self, hn, y, j):
         return self._nll_tok(hn, y, j).sum()
 
-    def _ce_kept(self, hn, y, keep, j):
-        return (self._nll_tok(hn, y, j) * keep).sum()
-
     # ------------------------------------------------------------------------------------------ instinct on words
     def _iw_part(self, hn, y, mult, j):
         """Sums over the positions j.. of the rows: [term, smeared, sure-but-wrong, fine, acted on] (term not yet
@@ -1065,21 +1062,10 @@ class MemArchLM(nn.Module):
         rem = extra.get("rem") if isinstance(extra, dict) else None
         if rem is not None and "rem_y" in extra:          # the answer is not in the text, only in the target
             y = torch.where(rem > 0, extra["rem_y"].to(y.dtype), y)
-        if rem is not None and c.remind_mask_main:
-            # in rows with needles the needle tokens (random keys, values, marker) do not teach the main loss: a full
-            # softmax on them lifts the whole group of tokens everywhere in the text (model.py:437-446)
-            k0 = c.remind_tok0
-            keep = (~((y >= k0) & (y <= k0 + 576) & (rem > 0).any(1, keepdim=True))).float()
-            self.stats["remind_main_masked"] = 1.0 - keep.mean()
-            loss = 0
-            for j in range(0, hn.shape[1], 8192):
-                part = (hn[:, j:j + 8192], y[:, j:j + 8192], keep[:, j:j + 8192])
-                if self.training and torch.is_grad_enabled():
-                    loss = loss + checkpoint(self._ce_kept, *part, j, use_reentrant=False)
-                else:
-                    loss = loss + self._ce_kept(*part, j)
-        elif train and self._hoop is not None:
-            # the head's target is the model's true error on every word, so the per-word form of the loss runs
+        mask_main = rem is not None and c.remind_mask_main
+        if mask_main or (train and self._hoop is not None):
+            # the per-word form of the loss: the hoop's head needs the model's true error on every word as its target,
+            # and the needle mask drops single words from the main loss
             parts = []
             for j in range(0, hn.shape[1], 8192):
                 part = (hn[:, j:j + 8192], y[:, j:j + 8192])
@@ -1089,6 +1075,13 @@ class MemArchLM(nn.Module):
                     parts.append(self._nll_tok(*part, j))
             nll_tok = torch.cat(parts, 1)
             loss = nll_tok.sum()
+            if mask_main:
+                # in rows with needles the needle tokens (random keys, values, marker) do not teach the main loss: a
+                # full softmax on them lifts the whole group of tokens everywhere in the text (model.py:437-446)
+                k0 = c.remind_tok0
+                keep = (~((y >= k0) & (y <= k0 + 576) & (rem > 0).any(1, keepdim=True))).float()
+                self.stats["remind_main_masked"] = 1.0 - keep.mean()
+                loss = (nll_tok * keep).sum()
         elif train and self.training and self.panic:
             loss = 0
             for j in range(0, hn.shape[1], 8192):

@@ -1121,3 +1121,34 @@ def test_token_preparation_on_the_loader_thread(tmp_path, monkeypatch):
     assert len(seen) == 4 and all(len(p) == 2 and {"ind_cand", "ind_on", "ind_bk", "ind_src"} <= set(p[0]) for p in seen)
     assert seen[0][0]["ind_cand"].shape[0] == 2                            # one dict per micro-batch
     assert abs(plain[-1]["val"] - fed[-1]["val"]) < 1e-5                   # the same run, prepared elsewhere
+
+
+def test_experiment_switches_combined_train_together():
+    """Everything at once, as a long run would have it: tethered light blocks, hoop, word-level rules, needle terms,
+    rotating full heavy layer, trunk guard, dump-proof final norm, and the optimizer's late rules."""
+    from memarch_b200 import OptConfig, TrainConfig, build
+    from memarch_b200.data.reminders import Reminders
+    from memarch_b200.train import Trainer
+    from memarch_b200.train.loop import needle_preps
+    torch.manual_seed(0)
+    env = {"NO_MEM": "1", "MOE_ACT": "relu2", "ROPE_MEM": "1", "ROPE_WIN": "8", "ROPE_SPAN_CAP": "12", "ROPE_K": "2",
+           "ROPE_LINKS": "3", "ROPE_HIER_G": "4", "ROPE_HIER_BM": "16", "ROPE_CHUNK": "32", "ROPE_QFRAC": "0.8",
+           "UROBOROS": "1", "INST_WORD": "1", "IW_REWRITE": "1", "REMIND_W": "1.0", "REMIND_N": "4", "REMIND_USE_W": "0.2",
+           "REMIND_MASK_MAIN": "1", "HEAVY_ROTATE": "1", "LAYER_STATS": "1", "HN_GUARD_W": "0.5", "HN_GUARD_MEAN": "0.5",
+           "NORM_DUMP_PROJ": "1", "ATTN_GAIN": "1.1", "PREV_IN": "1"}
+    m = build("tiny", 2048, env=env)
+    tr = Trainer(m, TrainConfig(name="tiny", stage="ABX", steps=20, batch=4, micro=2, seq=64, lr=3e-3, warmup=2),
+                 OptConfig(lr=3e-3, norm="hs", scale=0.12, rel_every=2, stream_proj=True, m_rate=True, m_rate_warm=2, safe16=True,
+                           culprit="ema", gnorm=True, gnorm_rawrel=True, wd_norm=0.01, norm_anchor=True), stage="ABX")
+    rem = Reminders(1.0, T=64, n=4, dist=8, seed=0, V=2048, tok0=1000, same_fmt=True, blank=True)
+    g = np.random.default_rng(0)
+    losses = []
+    for step in range(5):
+        xy, extra = rem(g.integers(0, 900, (4, 65)).astype(np.int32), n=step)
+        xy_t = torch.from_numpy(xy).long()
+        losses.append(float(tr.step(xy_t, step, needle_preps(m, xy_t, extra, 2))))
+    assert all(math.isfinite(v) for v in losses), losses
+    assert tr.opt.U is not None and m.stream_u is tr.opt.U and tr.opt.mrl_n == 5
+    for k in ("rope_share", "uroboros_corr", "iw", "remind_hit", "remind_rope_share", "remind_main_masked", "moe_fill", "hn_mean"):
+        assert k in m.stats, k
+    assert all(torch.isfinite(p).all() for p in m.parameters())

@@ -622,6 +622,10 @@ class MemArchLM(nn.Module):
                 a = self._run(b, a, sa, heavy=True)
         return put(hh, a), a
 
+    def graph_key(self):
+        """Host-side state that decides what a step launches (a captured step is only valid for the same values)."""
+        return (self._hfull if self.cfg.heavy_rotate else None, getattr(self, "hoop_budget", None))
+
     def _full_layer(self, prep):
         """None: every heavy layer on the anchors.  -1: every layer on all words (`heavy_all`).  k: layer k on all
         words in this step - from `prep["hfull"]`, or by rotation over the steps (`heavy_rotate`, set by `before_step`)."""

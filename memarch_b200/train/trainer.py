@@ -183,7 +183,8 @@ class Trainer:
         return total
 
     def _step_graphed(self, xy):
-        key = (tuple(xy.shape), self.opt.n_step % self.opt.rel_every == 0)
+        # host-side choices that shape the captured program (which heavy layer is full, the hoop's budget) are part of the key
+        key = (tuple(xy.shape), self.opt.n_step % self.opt.rel_every == 0, getattr(self.model, "graph_key", tuple)())
         if self._eager_steps < 3 or self._graph_failed:
             self._eager_steps += 1
             return self._core(xy, None)

@@ -15,12 +15,10 @@ err_freeze, move_peak, last_move, hint_avg, learned, up_snap, L_idx, F_idx, up_f
 """
 from __future__ import annotations
 
-import math
 import os
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from .. import ops
 from .blocks import _cdt

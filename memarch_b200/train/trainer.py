@@ -10,7 +10,6 @@ from __future__ import annotations
 import math
 
 import torch
-import torch.nn.functional as F
 
 from ..config import OptConfig, TrainConfig
 from ..optim.instinct import Instinct, SurpriseAdamW

@@ -11,7 +11,6 @@ Parameter and buffer names equal the reference's so `state_dict`s interchange.
 from __future__ import annotations
 
 import math
-import os
 
 import numpy as np
 import torch

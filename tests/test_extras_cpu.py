@@ -923,3 +923,41 @@ def test_moe_layer_statistics():
     b = m.heavy[0]
     # filled share = kept (token, choice) pairs over the capacity
     assert "moe_fill" not in quiet.stats and "moe_drop_l" not in quiet.stats
+
+
+def test_light_moe_dispatch_serves_first_askers_when_over_capacity():
+    """FineMoE against a plain statement of the same layer: stable sort of the (token, choice) pairs by expert, the
+    first `cap` of every expert served, the rest dropped."""
+    import torch.nn.functional as F
+    from memarch_b200.models.blocks import FineMoE
+    torch.manual_seed(0)
+    d, E, k = 32, 4, 2
+    moe = FineMoE(d, E=E, k=k)
+    with torch.no_grad():
+        moe.router.weight[0] += 2.0 * torch.ones(d) / d ** 0.5            # expert 0 is everybody's favourite: it overflows
+    x = torch.randn(2, 40, d) + 0.5
+    y = moe(x)
+    xf = x.reshape(-1, d)
+    N = xf.shape[0]
+    logits = xf @ moe.router.weight.T
+    gate, ex = logits.topk(k, -1)
+    gate = gate.softmax(-1)
+    cap = int(1.25 * N * k / E) + 1
+    e_flat = ex.reshape(-1)
+    order = e_flat.argsort(stable=True)
+    es = e_flat[order]
+    start = torch.searchsorted(es, torch.arange(E))
+    slot = torch.arange(N * k) - start[es]
+    keep = slot < cap
+    assert int((~keep).sum()) > 0                                          # the case really drops something
+    tok = order // k
+    want = torch.zeros(N, d)
+    for j in range(N * k):
+        if keep[j]:
+            e, t = int(es[j]), int(tok[j])
+            a = xf[t] @ moe.up[e]
+            g_, u_ = a.chunk(2, -1)
+            want[t] += gate.reshape(-1)[order][j] * ((F.silu(g_) * u_) @ moe.down[e])
+    assert torch.allclose(y.reshape(N, d), want, atol=1e-4), float((y.reshape(N, d) - want).abs().max())
+    y.sum().backward()
+    assert moe.up.grad.abs().sum() > 0 and moe.router.weight.grad is not None

@@ -579,10 +579,13 @@ def train(args, device=None, env=None, out=None, parallel=None):
                     if hoop is not None and "uroboros_eaten" in tr.model.stats:
                         # the heavy layers' budget steps down one level once enough words are "eaten"
                         st_ = tr.model.stats
-                        nb = hoop.next_budget(tr.model.hoop_budget, st_["uroboros_eaten"], tr.model.cfg.uroboros_levels,
-                                              corr=st_["uroboros_corr"])
+                        seen_ = torch.stack([st_["uroboros_eaten"].float(), st_["uroboros_corr"].float()])
+                        if parallel is not None and hasattr(parallel, "mean_vector"):
+                            seen_ = parallel.mean_vector(seen_.clone())      # every rank must take the same decision:
+                        nb = hoop.next_budget(tr.model.hoop_budget, seen_[0], tr.model.cfg.uroboros_levels,   # the budget
+                                              corr=seen_[1])                                                # sets shapes
                         if nb != tr.model.hoop_budget:
-                            print(f"hoop: budget {tr.model.hoop_budget} -> {nb} (eaten {float(st_['uroboros_eaten']):.2f})",
+                            print(f"hoop: budget {tr.model.hoop_budget} -> {nb} (eaten {float(seen_[0]):.2f})",
                                   file=out, flush=True)
                             tr.model.hoop_budget = nb
                     rm = getattr(data, "remind", None)

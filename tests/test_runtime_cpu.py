@@ -1152,3 +1152,20 @@ def test_experiment_switches_combined_train_together():
     for k in ("rope_share", "uroboros_corr", "iw", "remind_hit", "remind_rope_share", "remind_main_masked", "moe_fill", "hn_mean"):
         assert k in m.stats, k
     assert all(torch.isfinite(p).all() for p in m.parameters())
+
+
+def test_hoop_budget_steps_down_in_the_loop(tmp_path, monkeypatch):
+    from memarch_b200.models.fishki import Uroboros
+    from memarch_b200.train.loop import train
+    monkeypatch.chdir(tmp_path)
+    # the head "knows its errors" and most words count as eaten: the budget goes down one level per evaluation
+    monkeypatch.setattr(Uroboros, "stats", staticmethod(lambda pred, nll, idx, eat: {
+        "uroboros_eaten": torch.tensor(0.97), "uroboros_corr": torch.tensor(0.9),
+        "uroboros_nll_sel": nll.mean().detach(), "uroboros_nll_skip": nll.mean().detach()}))
+    env = {"VOCAB": "512", "NO_MEM": "1", "WATCHDOG": "0", "UROBOROS": "1", "UROBOROS_LEVELS": "0.25,0.125,0.0625",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
+    buf = io.StringIO()
+    log = train(Args(seq=64, batch=2, micro=2, steps=3, eval_every=1), "cpu", env=env, out=buf)["tiny"]
+    text = buf.getvalue()
+    assert "hoop: budget 0.25 -> 0.125" in text and "hoop: budget 0.125 -> 0.0625" in text
+    assert all(math.isfinite(e["val"]) for e in log)

@@ -589,13 +589,20 @@ def train(args, device=None, env=None, out=None, parallel=None):
                                   file=out, flush=True)
                             tr.model.hoop_budget = nb
                     rm = getattr(data, "remind", None)
-                    if rm is not None and data.extra is not None and "rem" in data.extra and data.extra["rem"].any():
+                    # with several ranks every rank scores (the forward has collectives) and the curriculum moves on the
+                    # summed counts, so that all ranks stay on the same level (levels set batch shapes)
+                    if rm is not None and data.extra is not None and "rem" in data.extra and (
+                            parallel is not None or data.extra["rem"].any()):
                         hits, n_ans = needle_hits(tr.model, xy_b, torch.from_numpy(data.extra["rem"]).to(tr.device) > 0,
                                                   data.extra.get("rem_y"))
-                        sets["needles"] = hits / max(n_ans, 1.0)
-                        msg = rm.observe(data.loader.n_done - 1, hits, n_ans)
-                        if msg:
-                            print(msg, file=out, flush=True)
+                        if parallel is not None and hasattr(parallel, "mean_vector"):
+                            tot_ = parallel.mean_vector(torch.tensor([hits, n_ans], device=tr.device)) * parallel.W
+                            hits, n_ans = float(tot_[0]), float(tot_[1])
+                        if n_ans > 0:
+                            sets["needles"] = hits / n_ans
+                            msg = rm.observe(data.loader.n_done - 1, hits, n_ans)
+                            if msg:
+                                print(msg, file=out, flush=True)
                     extra += "".join(f"  {k} {v:.3f}" for k, v in sets.items())
                     log.append({"step": step, "time": train_time, "val": vl, **({"sets": sets} if sets else {})})
                     print(f"{name}[{args.stage}]  step {step:5d}  val {vl:.3f}  bpb {vl / bpu / math.log(2):.4f}  "

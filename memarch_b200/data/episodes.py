@@ -30,11 +30,12 @@ FILLS = tuple(16 << i for i in range(13))            # 16 .. 65536
 
 class Episodes:
     def __init__(self, host, gap=0, round_to=1, rows_mult=1, frac=None, win_ref=None, tail=False, strict=False,
-                 far_frac=None, far_win=2048):
+                 far_frac=None, far_win=2048, rank=0):
         """`host` is the `Reminders` object whose tokens, filler, seed, pair count and thresholds are used."""
         self.h = host
         self.gap, self.round_to, self.rows_mult = int(gap), max(1, int(round_to)), max(1, int(rows_mult))
         self.tail, self.strict = bool(tail), bool(strict)
+        self.rank = int(rank)                           # data-parallel rank: same shapes on every rank, other rows
         self.far_frac, self.far_win = (None if far_frac is None else float(far_frac)), int(far_win)
         n, T = host.n, host.T
         if frac:
@@ -135,6 +136,8 @@ class Episodes:
         h = self.h
         B, T1 = shape
         rng, pairs, f = self._draw(i)
+        if self.rank:                                   # the shape is decided above, identically on every rank
+            rng = np.random.default_rng([h.seed, 7919, i, self.rank])
         Ts = self.row_len(pairs, f)
         if not self.tail:
             f = Ts + 1 - 4 * pairs

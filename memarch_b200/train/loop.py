@@ -233,7 +233,7 @@ class _CorpusData:
                             win_ref=int(env["REMIND_WIN_REF"]) if env.get("REMIND_WIN_REF") else None,
                             tail=env.get("REMIND_TAIL") == "1", strict=env.get("REMIND_STRICT") == "1",
                             far_frac=float(env["REMIND_FAR_FRAC"]) if env.get("REMIND_FAR_FRAC") else None,
-                            far_win=int(env.get("REMIND_FAR_WIN", 2048)))
+                            far_win=int(env.get("REMIND_FAR_WIN", 2048)), rank=rank)
             mix = (floats("REMIND_MIX"), int(env.get("REMIND_MIX_LEN", 250))) if env.get("REMIND_MIX") else None
             self.remind = Reminders(float(env["REMIND_P"]), seq, n=int(env.get("REMIND_N", 16)),
                                     dist=int(env.get("REMIND_DIST", min(2048, seq // 4))), seed=int(env.get("CORPUS_SEED", 0)),

@@ -288,6 +288,14 @@ def test_episode_stage_curriculum_and_rows():
     assert t.pack.shape_at(0) == (4, 16) and xt.shape[1] == 65 and np.nonzero(et["rem"][0])[0][0] == 8 + 16
     with pytest.raises(ValueError):
         Reminders(1.0, T=1024, n=16, dist=64, pack=dict(frac=[0.5]))
+    # data-parallel ranks: the same shapes (also on the last step, where the fill is drawn per batch), other rows
+    mk = lambda rank: Reminders(1.0, T=1024, n=16, dist=64, seed=5, V=30000, synth=40, pack=dict(round_to=64, rank=rank))
+    r0, r1 = mk(0), mk(1)
+    for rr in (r0, r1):
+        rr.pack.changes.append((0, len(rr.pack.steps) - 1))
+    for i in range(6):
+        a, b = r0(np.zeros(shape, np.int32), n=i)[0], r1(np.zeros(shape, np.int32), n=i)[0]
+        assert a.shape == b.shape and not np.array_equal(a, b)
 
 
 def test_dense_episode_rows_for_evaluation():

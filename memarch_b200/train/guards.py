@@ -128,6 +128,9 @@ class RollbackGuard:
         with torch.enable_grad():
             loss = tr.step(xy_eff, step, **kw)
         l = loss.detach().float()
+        par = getattr(tr, "parallel", None)
+        if par is not None and hasattr(par, "mean_vector"):
+            l = par.mean_vector(l.reshape(1).clone())[0]     # one verdict for all ranks: weights must stay equal
         lema = self.lema[k]
         hit = (l > self.ratio * lema) & (lema > 0) & ~self.cool[k] & ~self.rep
         if self.n < self.warm or self.snap_p is None:

@@ -398,6 +398,51 @@ def test_vocab_parallel_main_model_matches_the_unsharded_one():
         assert r["emb.weight.rows"] == 32 and r["l_head.1.weight.rows"] == 32
 
 
+def _w_loop(rank, world, port, folder, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import io
+    import json
+    from memarch_b200.parallel import ParallelEngine
+    from memarch_b200.train.loop import train
+    from test_runtime_cpu import Args
+    env = {"VOCAB": "2048", "NO_MEM": "1", "WATCHDOG": "0", "RANK": str(rank), "WORLD_SIZE": str(world),
+           "CORPUS": json.dumps({"web": 0.7, "code": 0.3}), "CORPUS_ROOT": folder,
+           "REMIND_P": "1.0", "REMIND_N": "4", "REMIND_DIST": "4", "REMIND_TOK0": "1000", "REMIND_SYNTH": "3",
+           "REMIND_PACK": "1", "REMIND_PACK_ROUND": "16", "REMIND_BLANK": "1", "REMIND_WIN": "8", "REMIND_THR": "0.0",
+           "REMIND_LAG": "1", "REMIND_W": "1.0", "REMIND_MEAN": "1", "UROBOROS": "1", "ROLLBACK": "0",
+           "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
+    buf = io.StringIO()
+    log = train(Args(seq=64, batch=4, micro=4, steps=4, eval_every=2), "cpu", env=env, out=buf,
+                parallel=ParallelEngine(rank, world, 0, fused=False))["tiny"]
+    moves = [ln for ln in buf.getvalue().splitlines() if ln.startswith(("episodes:", "reminders:", "hoop:"))]
+    q.put((rank, moves, [e["val"] for e in log]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_curricula_stay_in_step_across_ranks(tmp_path):
+    """Two ranks with different text: the needle curriculum (which sets batch shapes) and the hoop's budget move on
+    rank-summed statistics, so both ranks log the same moves at the same batches and the run does not stall."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_runtime_cpu import make_corpus
+    make_corpus(str(tmp_path), n_shards=4, docs=60)
+    world, port = 2, 29683
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_w_loop, args=(r, world, port, str(tmp_path), q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted([q.get(timeout=400) for _ in ps], key=lambda t: t[0])
+    [p.join(30) for p in ps]
+    (_, m0, v0), (_, m1, v1) = res
+    strip = lambda ms: [ln.split("(accuracy")[0] + ln.split(")", 1)[-1] if "(accuracy" in ln else ln for ln in ms]
+    assert m0 and strip(m0) == strip(m1), (m0, m1)
+    assert any(ln.startswith("episodes: step 0 -> 1") for ln in m0)
+    assert all(torch.isfinite(torch.tensor(v0 + v1)))
+
+
 def _w_ckpt(rank, world, port, folder, q):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))

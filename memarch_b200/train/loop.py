@@ -405,7 +405,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                 with torch.no_grad():
                     keep_ = fish_.down.detach().clone()
                     fish_.down.zero_()
-                    ev_["val_nofish"] = float(val_loss(tr.model, data.val, args.seq))
+                    ev_["val_nofish"] = float(val_loss(tr.model, data.val, args.seq, n=int(env.get("VAL_BATCHES", 20))))
                     fish_.down.copy_(keep_)
             rm_e = getattr(data, "remind", None)
             if rm_e is not None and env.get("REMIND_EVAL") is not None:
@@ -413,7 +413,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                                               getattr(tr.model, "window", args.seq)))
             return ev_
         if env.get("EVAL_ONLY") == "1" or (env.get("EVAL_AT_RESUME") == "1" and start > 1):
-            ev = dict(run_evals(), val=float(val_loss(tr.model, data.val, args.seq)))
+            ev = dict(run_evals(), val=float(val_loss(tr.model, data.val, args.seq, n=int(env.get("VAL_BATCHES", 20)))))
             print(f"{name}[{args.stage}]  eval at step {start - 1}: " + "  ".join(f"{k} {v:.4f}" for k, v in ev.items()),
                   file=out, flush=True)
             log.append({"step": start - 1, "eval_only": True, **ev})
@@ -562,7 +562,7 @@ def train(args, device=None, env=None, out=None, parallel=None):
                             for p, e in zip(ps, ema):
                                 p.copy_(e)
                     te = time.time()
-                    vl = float(val_loss(tr.model, data.val, args.seq))
+                    vl = float(val_loss(tr.model, data.val, args.seq, n=int(env.get("VAL_BATCHES", 20))))
                     phase["eval"] += time.time() - te
                     if cur is not None:
                         with torch.no_grad():

@@ -408,14 +408,14 @@ def _w_loop(rank, world, port, folder, q):
     from memarch_b200.parallel import ParallelEngine
     from memarch_b200.train.loop import train
     from test_runtime_cpu import Args
-    env = {"VOCAB": "2048", "NO_MEM": "1", "WATCHDOG": "0", "RANK": str(rank), "WORLD_SIZE": str(world),
+    env = {"VOCAB": "1024", "NO_MEM": "1", "WATCHDOG": "0", "RANK": str(rank), "WORLD_SIZE": str(world),
            "CORPUS": json.dumps({"web": 0.7, "code": 0.3}), "CORPUS_ROOT": folder,
-           "REMIND_P": "1.0", "REMIND_N": "4", "REMIND_DIST": "4", "REMIND_TOK0": "1000", "REMIND_SYNTH": "3",
+           "REMIND_P": "1.0", "REMIND_N": "4", "REMIND_DIST": "4", "REMIND_TOK0": "100", "REMIND_SYNTH": "3", "VAL_BATCHES": "2",
            "REMIND_PACK": "1", "REMIND_PACK_ROUND": "16", "REMIND_BLANK": "1", "REMIND_WIN": "8", "REMIND_THR": "0.0",
            "REMIND_LAG": "1", "REMIND_W": "1.0", "REMIND_MEAN": "1", "UROBOROS": "1", "ROLLBACK": "0",
            "OPT_KW": json.dumps({"norm": "hs", "scale": 0.12})}
     buf = io.StringIO()
-    log = train(Args(seq=64, batch=4, micro=4, steps=4, eval_every=2), "cpu", env=env, out=buf,
+    log = train(Args(seq=48, batch=2, micro=2, steps=4, eval_every=2), "cpu", env=env, out=buf,
                 parallel=ParallelEngine(rank, world, 0, fused=False))["tiny"]
     moves = [ln for ln in buf.getvalue().splitlines() if ln.startswith(("episodes:", "reminders:", "hoop:"))]
     q.put((rank, moves, [e["val"] for e in log]))
